@@ -1,0 +1,160 @@
+/*
+ * voyager_b200 -- C ABI of the B200 (sm_100a) kernels behind the `quantized_ops` operators of
+ * voyager-compiler.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*), returns 0
+ * on success or a negative vq_status, never throws and never synchronises the stream.  After a
+ * non-zero return vq_last_error() gives a message for the calling thread.  All tensors are
+ * dense and contiguous in logical (row-major) order; outputs are written in full and inputs are
+ * never modified.  Citations name the upstream function each entry point replaces, by path
+ * inside the voyager-compiler source tree.
+ */
+#ifndef VOYAGER_B200_H
+#define VOYAGER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VQ_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define VQ_API __attribute__((visibility("default")))
+#else
+#define VQ_API
+#endif
+
+typedef enum vq_status {
+    VQ_OK = 0,
+    VQ_ERR_INVALID = -1,      /* bad argument (null pointer, size, alignment, dtype) */
+    VQ_ERR_UNSUPPORTED = -2,  /* valid upstream usage this build has no kernel for */
+    VQ_ERR_CUDA = -3,         /* a CUDA runtime call or launch failed */
+    VQ_ERR_DEVICE = -4        /* a kernel reported a bounded wait that ran out */
+} vq_status;
+
+typedef enum vq_dtype { VQ_F32 = 0, VQ_BF16 = 1 } vq_dtype;
+
+/* How a 16-bit bf16 pattern is turned into an output value (upstream: the 65 536-entry `qmap`
+ * argument, src/voyager_compiler/quantization/fake_quantize.py:30-98). */
+typedef enum vq_table_kind {
+    VQ_TABLE_NONE = 0,
+    VQ_TABLE_LUT16 = 1,  /* lut16[pattern] is the bf16 bit pattern of the output value */
+    VQ_TABLE_INT = 2,    /* table is known to equal clamp(round_half_even(v), lo, hi), NaN -> NaN */
+    VQ_TABLE_RUNS = 3    /* piecewise constant over the ordered finite bf16 line with <= 512 runs:
+                            branchless binary search over run starts held in shared memory;
+                            +inf, -inf and NaN inputs have their own outputs */
+} vq_table_kind;
+
+typedef struct vq_table {
+    int32_t kind;
+    int32_t n_runs;            /* RUNS: number of runs (1..512) */
+    const uint16_t* lut16;     /* LUT16: device pointer, 65 536 entries */
+    const uint8_t* lut8;       /* optional (any kind but INT): device pointer, 65 536 packed codes */
+    float lo, hi;              /* INT */
+    const uint16_t* run_keys;  /* RUNS: device pointer, n_runs-1 ascending run starts, in the
+                                  order-preserving key space key = bits ^ (bits&0x8000 ? 0xFFFF : 0x8000) */
+    const uint16_t* run_vals;  /* RUNS: device pointer, n_runs output bf16 patterns */
+    const uint8_t* run_codes;  /* RUNS, optional: n_runs packed codes */
+    uint16_t nan_val;          /* RUNS: output patterns for NaN, +inf and -inf inputs */
+    uint16_t pinf_val;
+    uint16_t ninf_val;
+    uint8_t nan_code;          /* RUNS: packed codes for NaN, +inf and -inf inputs */
+    uint8_t pinf_code;
+    uint8_t ninf_code;
+    uint8_t reserved[7];
+} vq_table;
+
+/* Where the scale (and zero point) of element i lives (upstream `expand`,
+ * src/voyager_compiler/ops/quantized.py:82-95, and plain broadcasting when block_size is None). */
+typedef enum vq_scale_mode {
+    VQ_SCALE_SCALAR = 0,    /* one scale for the whole tensor */
+    VQ_SCALE_ROWBLOCK = 1,  /* tensor viewed as [rows, K]; scale is [rows, ceil(K/block)] */
+    VQ_SCALE_STRIDED = 2    /* general: per-dimension block divisor and scale stride */
+} vq_scale_mode;
+
+typedef struct vq_scale_layout {
+    int32_t mode;
+    int32_t ndim;            /* STRIDED: 1..6 */
+    int64_t rows, K, block;  /* ROWBLOCK */
+    int64_t size[6];         /* STRIDED: tensor sizes, outermost first */
+    int64_t div[6];          /* STRIDED: coordinate divisor per dim (block size, or 1) */
+    int64_t stride[6];       /* STRIDED: scale stride per dim in elements (0 = broadcast) */
+} vq_scale_layout;
+
+/* Host-derived exponent tables for power-of-two scales (upstream:
+ * floor(log2(amax)) - floor(log2(quant_max)) and 2**e with torch CPU arithmetic in the tensor's
+ * dtype, src/voyager_compiler/quantization/mx_utils.py:42-47, ops/quantized.py:471-488,498).
+ * Index i stands for the true binary exponent e = i - 149 of amax (e in [-149, 127]).
+ *   bump_at[i]  : smallest fp32 bit pattern with true exponent e for which the CPU's rounded
+ *                 log2 already floors to e+1 (the pattern of 2^(e+1) when there is none);
+ *   scale_of[j] : the final scale, as fp32, for a floored exponent j - 149 (278 entries),
+ *                 i.e. where(2**(e - floor(log2 qmax)) > 0, ., 1). */
+#define VQ_EXP_ENTRIES 277
+typedef struct vq_exp_tables {
+    const uint32_t* bump_at;  /* device pointer, 277 entries */
+    const float* scale_of;    /* device pointer, 278 entries */
+} vq_exp_tables;
+
+VQ_API int vq_version(void);
+VQ_API const char* vq_last_error(void);
+/* Number of kernels this library has launched from the calling process so far. */
+VQ_API uint64_t vq_launch_count(void);
+
+/* Host-only self check of the index-division constants the kernels use (0 = exact). */
+VQ_API int vq_selftest_fastdiv(uint32_t d, uint32_t n);
+
+/* out[i] = table(bf16_rne(in[i])), stored in the dtype of `in`.
+ * Replaces `vmap`, src/voyager_compiler/ops/quantized.py:98-121. */
+VQ_API int vq_lut_map(const void* in, int dtype, int64_t n, const vq_table* table, void* out, void* stream);
+
+/* out[i] = table(bf16_rne(in[i] / scale[.] (+ zero_point[.]))) in the dtype of `in`; scale and
+ * zero_point have the dtype of `in`.  `out_codes`, when not NULL, also receives the packed code
+ * of every element (code_bits 8: one byte each; 4: two per byte, even element in the low nibble).
+ * `out` may be NULL when only packed codes are wanted.
+ * Replaces `quantize`, src/voyager_compiler/ops/quantized.py:131-172. */
+VQ_API int vq_quantize(const void* in, int dtype, int64_t n, const void* scale, const void* zero_point,
+                const vq_scale_layout* layout, const vq_table* table, void* out,
+                uint8_t* out_codes, int code_bits, void* stream);
+
+/* out[i] = out_table((in_table(in[i]) - zero_point[.]) * scale[.]), either table optional.
+ * Replaces `dequantize`, src/voyager_compiler/ops/quantized.py:182-227. */
+VQ_API int vq_dequantize(const void* in, int dtype, int64_t n, const void* scale, const void* zero_point,
+                  const vq_scale_layout* layout, const vq_table* in_table, const vq_table* out_table,
+                  void* out, void* stream);
+
+/* Per-block scale of a tensor viewed as [outer, L, inner] with blocks of `block` elements along
+ * L (a ragged tail block is zero padded; L < block is one block).  Output is
+ * [outer, ceil(L/block), inner] in the dtype of `in`.
+ *   pow2 == 1: scale = exp->scale_of[floor-log2 index of amax]    (needs exp)
+ *   pow2 == 0: scale = amax / quant_max, optionally through scale_table, then where(>0, ., 1)
+ *   pow2 == 2: the block maximum of |x| itself (NaN kept); chaining such passes axis by axis
+ *              gives the maxima of blocks that span several axes.
+ * Replaces `calculate_mx_qparam`, src/voyager_compiler/ops/quantized.py:442-499. */
+VQ_API int vq_mx_scale(const void* in, int dtype, int64_t outer, int64_t L, int64_t inner, int64_t block,
+                double quant_max, int pow2, const vq_exp_tables* exp, const vq_table* scale_table,
+                void* out_scale, void* stream);
+
+/* Optional extra outputs of vq_quantize_mx; any pointer may be NULL. */
+typedef struct vq_mx_extras {
+    float* scale_f32;    /* the scale widened to fp32, same shape as out_scale */
+    int8_t* exp_e8;      /* pow2 only: log2(scale) clamped to [-127, 127] */
+    uint8_t* codes;      /* packed codes, code_bits per element */
+    int32_t code_bits;   /* 8 or 4 */
+    void* dequant;       /* table value * scale in the dtype of `in` (value tables only) */
+} vq_mx_extras;
+
+/* One pass over `in`: block scale as vq_mx_scale, then codes as vq_quantize with that scale.
+ * out_scale / out_codes may be NULL when only the extras are wanted.
+ * Replaces `quantize_mx`, src/voyager_compiler/ops/quantized.py:509-529 (outputs: scale, codes). */
+VQ_API int vq_quantize_mx(const void* in, int dtype, int64_t outer, int64_t L, int64_t inner, int64_t block,
+                   double quant_max, int pow2, const vq_exp_tables* exp, const vq_table* scale_table,
+                   const vq_table* table, void* out_scale, void* out_codes,
+                   const vq_mx_extras* extras, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VOYAGER_B200_H */

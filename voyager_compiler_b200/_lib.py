@@ -1,0 +1,100 @@
+"""ctypes binding of ``libvoyager_b200.so`` (the C ABI in ``include/voyager_b200.h``).
+
+There is no fallback: if the shared library is missing or was built for another ABI version,
+importing this module raises.  Build it with ``python -m voyager_compiler_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libvoyager_b200.so")
+ABI_VERSION = 1
+
+VQ_F32, VQ_BF16 = 0, 1
+TABLE_NONE, TABLE_LUT16, TABLE_INT, TABLE_RUNS = 0, 1, 2, 3
+SCALE_SCALAR, SCALE_ROWBLOCK, SCALE_STRIDED = 0, 1, 2
+
+
+class VqTable(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32), ("n_runs", C.c_int32),
+        ("lut16", C.c_void_p), ("lut8", C.c_void_p),
+        ("lo", C.c_float), ("hi", C.c_float),
+        ("run_keys", C.c_void_p), ("run_vals", C.c_void_p), ("run_codes", C.c_void_p),
+        ("nan_val", C.c_uint16), ("pinf_val", C.c_uint16), ("ninf_val", C.c_uint16),
+        ("nan_code", C.c_uint8), ("pinf_code", C.c_uint8), ("ninf_code", C.c_uint8),
+        ("reserved", C.c_uint8 * 7),
+    ]
+
+
+class VqScaleLayout(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int32), ("ndim", C.c_int32),
+        ("rows", C.c_int64), ("K", C.c_int64), ("block", C.c_int64),
+        ("size", C.c_int64 * 6), ("div", C.c_int64 * 6), ("stride", C.c_int64 * 6),
+    ]
+
+
+class VqExpTables(C.Structure):
+    _fields_ = [("bump_at", C.c_void_p), ("scale_of", C.c_void_p)]
+
+
+class VqMxExtras(C.Structure):
+    _fields_ = [
+        ("scale_f32", C.c_void_p), ("exp_e8", C.c_void_p), ("codes", C.c_void_p),
+        ("code_bits", C.c_int32), ("dequant", C.c_void_p),
+    ]
+
+
+class VoyagerB200Error(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built "
+            "(run `python -m voyager_compiler_b200.build`). There is no CPU fallback.")
+    lib = C.CDLL(LIB_PATH)
+    lib.vq_version.restype = C.c_int
+    if lib.vq_version() != ABI_VERSION:
+        raise ImportError(f"{LIB_PATH} has ABI version {lib.vq_version()}, expected {ABI_VERSION}; rebuild it")
+    lib.vq_last_error.restype = C.c_char_p
+    lib.vq_launch_count.restype = C.c_uint64
+    vp, i64, ci, dbl = C.c_void_p, C.c_int64, C.c_int, C.c_double
+    T, L, E, X = C.POINTER(VqTable), C.POINTER(VqScaleLayout), C.POINTER(VqExpTables), C.POINTER(VqMxExtras)
+    sigs = {
+        "vq_selftest_fastdiv": [C.c_uint32, C.c_uint32],
+        "vq_lut_map": [vp, ci, i64, T, vp, vp],
+        "vq_quantize": [vp, ci, i64, vp, vp, L, T, vp, vp, ci, vp],
+        "vq_dequantize": [vp, ci, i64, vp, vp, L, T, T, vp, vp],
+        "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
+        "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = C.c_int
+    return lib
+
+
+lib = _load()
+
+
+def check(rc: int, what: str = "") -> None:
+    """Raise on a non-zero status: AssertionError-free, always a VoyagerB200Error subclass of
+    RuntimeError; unsupported argument combinations raise NotImplementedError."""
+    if rc == 0:
+        return
+    msg = lib.vq_last_error().decode(errors="replace")
+    if rc == -2:
+        raise NotImplementedError(f"{what}: {msg}" if what else msg)
+    if rc == -1:
+        raise ValueError(f"{what}: {msg}" if what else msg)
+    raise VoyagerB200Error(f"{what}: {msg} (status {rc})" if what else f"{msg} (status {rc})")
+
+
+def launch_count() -> int:
+    return int(lib.vq_launch_count())

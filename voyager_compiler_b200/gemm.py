@@ -1,0 +1,29 @@
+"""MX-quantized GEMM: ``Y = deq(A) @ deq(B)^T`` for ``linear_mx`` / ``matmul_mx``
+(src/voyager_compiler/ops/quantized.py:295-348, :371-421).
+
+``deq(T) = code[T] * expand(scale)`` is formed in the operand dtype (one rounding to bf16 for
+bf16 operands), the product accumulates in fp32 and the result is stored in the operand dtype.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+
+def mx_gemm(name: str, a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], a_scale, b_scale, block_size,
+            a_code, b_code, b_is_nk: bool) -> torch.Tensor:
+    """``a``: [..., M, K]; ``b``: [N, K] when ``b_is_nk`` (linear's weight) else [..., K, N]."""
+    from . import ops
+    from .gemm_native import native_mx_gemm, native_supported
+
+    if native_supported(a, b, bias, a_scale, b_scale, block_size, a_code, b_code, b_is_nk):
+        return native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code)
+    # General shapes (batched right operands, K-major-in-rows layouts, fp32 operands): operands are
+    # decoded by this package's dequantize kernel and multiplied by the vendor GEMM.
+    da = ops._decode_operand(name, a, a_code, a_scale, block_size)
+    db = ops._decode_operand(name, b, b_code, b_scale, block_size)
+    if b_is_nk:
+        return torch.nn.functional.linear(da, db, bias)
+    out = torch.matmul(da, db)
+    return out if bias is None else out + bias
