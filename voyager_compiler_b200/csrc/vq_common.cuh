@@ -214,7 +214,10 @@ __device__ __forceinline__ Looked table_lookup(const TableDev& t, const TableRes
     Looked o{0.0f, 0u};
     if (t.kind == VQ_TABLE_INT) {
         float vb = bf16_bits_to_f32(pat);
-        float q = fminf(fmaxf(rintf(vb), t.lo), t.hi);
+        // comparisons, not fmaxf/fminf: clamp(-0, 0, hi) must stay -0 as it does on the CPU
+        float q = rintf(vb);
+        q = (q < t.lo) ? t.lo : q;
+        q = (q > t.hi) ? t.hi : q;
         o.val = (vb != vb) ? vb : q;
         o.code = (vb != vb) ? 0u : ((uint32_t)(int)q & 0xFFu);
     } else if (t.kind == VQ_TABLE_RUNS) {

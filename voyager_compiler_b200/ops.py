@@ -243,7 +243,7 @@ def _mx_call(fn_name, x, axis, block_size, quant_max, rule, scale_qmap, table, w
         return scale, codes
     with torch.cuda.device(x.device):
         exp = exp_tables(x.dtype, quant_max, x.device).ptr() if rule == RULE_POW2 else None
-        stab = table_handle(scale_qmap, x.device).ptr() if (scale_qmap is not None and rule == RULE_AMAX_OVER_QMAX) else None
+        stab = table_handle(scale_qmap, x.device, allow_runs=False).ptr() if (scale_qmap is not None and rule == RULE_AMAX_OVER_QMAX) else None
         if table is None:
             rc = _lib.lib.vq_mx_scale(x.data_ptr(), _DT[x.dtype], outer, L, inner, block_size, float(quant_max), rule,
                                       exp, stab, scale.data_ptr(), _stream(x.device))

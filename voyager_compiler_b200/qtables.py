@@ -62,7 +62,8 @@ def _dev_u16(arr: np.ndarray, device) -> torch.Tensor:
 class TableHandle:
     """Owns the device buffers behind one ``vq_table``."""
 
-    def __init__(self, lut16_host: np.ndarray, device: torch.device, source: Optional[torch.Tensor] = None):
+    def __init__(self, lut16_host: np.ndarray, device: torch.device, source: Optional[torch.Tensor] = None,
+                 allow_runs: bool = True):
         self.source = source            # keeps the storage alive so the cache key cannot be recycled
         self.device = device
         self.analysis = tables.analyse_table(lut16_host)
@@ -76,7 +77,7 @@ class TableHandle:
         if an.is_int and _policy["allow_int"]:
             self.c.kind = _lib.TABLE_INT
             self.c.lo, self.c.hi = an.lo, an.hi
-        elif an.n_runs and an.n_runs <= _policy["runs_max"] and an.nan_consistent:
+        elif allow_runs and an.n_runs and an.n_runs <= _policy["runs_max"] and an.nan_consistent:
             self._use_runs()
         else:
             self.c.kind = _lib.TABLE_LUT16
@@ -129,27 +130,30 @@ def _to_bits_host(qmap: torch.Tensor) -> np.ndarray:
     return t.view(torch.int16).numpy().view(np.uint16).copy()
 
 
-def table_handle(qmap, device) -> TableHandle:
+def table_handle(qmap, device, allow_runs: bool = True) -> TableHandle:
     """Cached ``TableHandle`` for a table tensor (any device, bf16 / float / integer entries),
-    a numpy uint16[65536] array of bf16 patterns, or an upstream dtype string such as ``"int8"``."""
+    a numpy uint16[65536] array of bf16 patterns, or an upstream dtype string such as ``"int8"``.
+    ``allow_runs=False`` keeps the table out of the binary-search form (scale tables are read once
+    per block from global memory, where the search has nothing to gain)."""
     device = torch.device(device)
     if isinstance(qmap, str):
-        key = ("name", qmap, str(device))
+        key = ("name", qmap, str(device), allow_runs)
     elif isinstance(qmap, np.ndarray):
-        key = ("np", qmap.tobytes(), str(device))
+        key = ("np", qmap.tobytes(), str(device), allow_runs)
     else:
-        key = ("t", qmap.data_ptr(), qmap._version, qmap.dtype, str(qmap.device), tuple(qmap.shape), str(device))
+        key = ("t", qmap.data_ptr(), qmap._version, qmap.dtype, str(qmap.device), tuple(qmap.shape), str(device),
+               allow_runs)
     with _lock:
         h = _table_cache.get(key)
         if h is not None:
             _table_cache.move_to_end(key)
             return h
     if isinstance(qmap, str):
-        h = TableHandle(tables.build_table(qmap), device)
+        h = TableHandle(tables.build_table(qmap), device, allow_runs=allow_runs)
     elif isinstance(qmap, np.ndarray):
-        h = TableHandle(qmap, device)
+        h = TableHandle(qmap, device, allow_runs=allow_runs)
     else:
-        h = TableHandle(_to_bits_host(qmap), device, source=qmap)
+        h = TableHandle(_to_bits_host(qmap), device, source=qmap, allow_runs=allow_runs)
     with _lock:
         _table_cache[key] = h
         while len(_table_cache) > _CACHE_MAX:
