@@ -154,6 +154,34 @@ VQ_API int vq_quantize_mx(const void* in, int dtype, int64_t outer, int64_t L, i
                    const vq_table* table, void* out_scale, void* out_codes,
                    const vq_mx_extras* extras, void* stream);
 
+/* One tensor of a multi-tensor pass: `n` elements laid out as consecutive blocks (a [rows, K]
+ * tensor with blocks along K and K a multiple of the block).  Output pointers as in
+ * vq_quantize_mx / vq_mx_extras; any may be NULL, at least one must not be. */
+typedef struct vq_mx_item {
+    const void* in;
+    void* out_scale;
+    void* out_codes;
+    float* scale_f32;
+    int8_t* exp_e8;
+    uint8_t* codes;
+    void* dequant;
+    int64_t n;
+} vq_mx_item;
+
+/* Bytes of device workspace vq_quantize_mx_multi needs for n_items tensors. */
+VQ_API size_t vq_quantize_mx_multi_workspace(int n_items);
+
+/* vq_quantize_mx over many tensors that share dtype, block size, scale rule and tables, in ONE
+ * kernel launch (whole-model weight quantization; upstream runs calculate_mx_qparam + quantize per
+ * parameter, src/voyager_compiler/quantization/quantize_pt2e.py:485-500).  `items` is a HOST
+ * array; it is copied into `workspace` (device memory, 16-byte aligned, at least
+ * vq_quantize_mx_multi_workspace(n_items) bytes) on `stream` before the launch.  The workspace
+ * must stay untouched until the work queued on `stream` has finished. */
+VQ_API int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max,
+                                int pow2, const vq_exp_tables* exp, const vq_table* scale_table,
+                                const vq_table* table, int code_bits, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

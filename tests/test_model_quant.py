@@ -1,0 +1,108 @@
+"""Whole-model (multi-tensor) MX quantization: sharding plan on CPU, kernel parity on GPU."""
+import os
+import sys
+
+import pytest
+import torch
+
+from voyager_compiler_b200 import model_quant as mq
+from golden_util import golden_table, index_table_of, same_bits
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import voyager_oracle as vo  # noqa: E402
+
+LLAMA7B = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
+
+
+def _llama_shapes():
+    return LLAMA7B * 32 + [(32000, 4096)]
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_shard_plan_covers_every_row_once_and_balances(world):
+    shapes = _llama_shapes()
+    sizes = [r * c for r, c in shapes]
+    rows = [r for r, _ in shapes]
+    plan = mq.shard_plan(sizes, rows, world)
+    seen = {}
+    loads = []
+    for rank, items in enumerate(plan):
+        load = 0
+        for i, b, e in items:
+            assert 0 <= b < e <= rows[i]
+            seen.setdefault(i, []).append((b, e))
+            load += (e - b) * shapes[i][1]
+        loads.append(load)
+    for i, r in enumerate(rows):
+        spans = sorted(seen[i])
+        assert spans[0][0] == 0 and spans[-1][1] == r
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    assert sum(loads) == sum(sizes)
+    assert max(loads) <= 1.02 * sum(sizes) / world        # >= 7.8x ideal speed-up at 8 ranks
+
+
+def test_shard_plan_small_and_degenerate():
+    assert mq.shard_plan([], [], 4) == [[], [], [], []]
+    plan = mq.shard_plan([10], [1], 4)
+    assert sum(len(p) for p in plan) == 1
+    with pytest.raises(ValueError):
+        mq.shard_plan([1], [1], 0)
+
+
+def test_cpu_tensors_rejected():
+    with pytest.raises(RuntimeError):
+        mq.quantize_tensors_mx([torch.randn(4, 64)], "nf4", 64, 1.0)
+
+
+@pytest.mark.gpu
+def test_multi_tensor_nf4_matches_oracle_bitwise():
+    torch.manual_seed(2)
+    shapes = [(256, 4096), (64, 11008), (1, 64), (3, 5, 128), (2049, 192)]
+    ws = [(torch.randn(s) * 0.02).to(torch.bfloat16) for s in shapes]
+    ws[3][0, 0, :64] = 0                      # an all-zero block
+    ws[3][1, 1, 5] = float("nan")
+    tab_v = golden_table("nf4")
+    tab_i, levels = index_table_of("nf4")
+    packed = mq.quantize_tensors_mx([w.cuda() for w in ws], tab_v, 64, 1.0, code_bits=4)
+    floats = mq.quantize_tensors_mx([w.cuda() for w in ws], tab_v, 64, 1.0, float_outputs=True)
+    torch.cuda.synchronize()
+    for w, p, (fs, fc) in zip(ws, packed, floats):
+        s_ref = vo.mx_scale(w, (-1,), 64, 1.0, False)
+        i_ref = vo.quantize(w, s_ref, None, (-1,), 64, tab_i)
+        v_ref = vo.quantize(w, s_ref, None, (-1,), 64, tab_v)
+        assert same_bits(fs, s_ref)[0] and same_bits(fc, v_ref)[0]
+        assert same_bits(p.scale, s_ref.float())[0]           # fp32 scale is the exact widening
+        codes = mq.unpack_codes(p).cpu()
+        nan = torch.isnan(i_ref.float())
+        assert torch.equal(codes[~nan].long(), i_ref[~nan].long())
+        assert p.codes.shape[-1] * 2 == w.shape[-1]
+        assert torch.equal(p.levels, levels.float())
+
+
+@pytest.mark.gpu
+def test_multi_tensor_int8_pow2_fp32_with_exponents():
+    torch.manual_seed(0)
+    xs = [torch.randn(128, 256), torch.randn(7, 32) * 1e-3, torch.zeros(2, 64)]
+    q = golden_table("int8")
+    packed = mq.quantize_tensors_mx([x.cuda() for x in xs], q, 32, 127.0, True, code_bits=8, want_exp=True)
+    for x, p in zip(xs, packed):
+        s_ref, c_ref = vo.quantize_mx(x, q, (-1,), 32, 127.0, True)
+        assert same_bits(p.scale, s_ref)[0]
+        got = mq.unpack_codes(p).cpu().to(torch.int8).float()      # two's-complement bytes
+        assert torch.equal(got, c_ref)
+        e = torch.log2(s_ref).clamp(-127, 127).to(torch.int8)
+        assert torch.equal(p.exp_e8.cpu(), e)
+        d = mq.dequantize_packed_reference(p).cpu()
+        assert torch.equal(d, vo.dequantize(c_ref, s_ref, None, (-1,), 32))
+
+
+@pytest.mark.gpu
+def test_host_pipeline_round_trip():
+    torch.manual_seed(5)
+    host = [(torch.randn(512, 1024) * 0.02).to(torch.bfloat16).pin_memory() for _ in range(5)]
+    pipe = mq.HostPipeline("cuda:0", golden_table("nf4"), 64, 1.0, chunk_bytes=2 << 20)
+    outs = pipe.run(host)
+    direct = mq.quantize_tensors_mx([h.cuda() for h in host], golden_table("nf4"), 64, 1.0)
+    for (hc, hs), p in zip(outs, direct):
+        assert torch.equal(hc, p.codes.cpu()) and torch.equal(hs, p.scale.cpu())
+    assert pipe.h2d_bytes == sum(h.numel() * 2 for h in host) and pipe.d2h_bytes > 0

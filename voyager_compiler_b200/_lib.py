@@ -1,7 +1,7 @@
 """ctypes binding of ``libvoyager_b200.so`` (the C ABI in ``include/voyager_b200.h``).
 
 There is no fallback: if the shared library is missing or was built for another ABI version,
-importing this module raises.  Build it with ``python -m voyager_compiler_b200.build``.
+importing this module raises.  Build it with ``python voyager_compiler_b200/build.py``.
 """
 from __future__ import annotations
 
@@ -48,6 +48,13 @@ class VqMxExtras(C.Structure):
     ]
 
 
+class VqMxItem(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("out_scale", C.c_void_p), ("out_codes", C.c_void_p), ("scale_f32", C.c_void_p),
+        ("exp_e8", C.c_void_p), ("codes", C.c_void_p), ("dequant", C.c_void_p), ("n", C.c_int64),
+    ]
+
+
 class VoyagerB200Error(RuntimeError):
     pass
 
@@ -56,7 +63,7 @@ def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
             f"{LIB_PATH} is missing: the CUDA library has not been built "
-            "(run `python -m voyager_compiler_b200.build`). There is no CPU fallback.")
+            "(run `python voyager_compiler_b200/build.py`). There is no CPU fallback.")
     lib = C.CDLL(LIB_PATH)
     lib.vq_version.restype = C.c_int
     if lib.vq_version() != ABI_VERSION:
@@ -72,7 +79,10 @@ def _load():
         "vq_dequantize": [vp, ci, i64, vp, vp, L, T, T, vp, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
         "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],
+        "vq_quantize_mx_multi": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp, C.c_size_t, vp],
     }
+    lib.vq_quantize_mx_multi_workspace.argtypes = [ci]
+    lib.vq_quantize_mx_multi_workspace.restype = C.c_size_t
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args

@@ -1,6 +1,6 @@
 """Builds ``libvoyager_b200.so`` in-tree with nvcc for sm_100a.
 
-    python -m voyager_compiler_b200.build [--force] [--verbose]
+    python voyager_compiler_b200/build.py [--force] [--verbose]
 
 The library has no Python or torch dependency; it is the C ABI declared in
 ``include/voyager_b200.h``.  nvcc cross-compiles without a GPU.

@@ -9,81 +9,9 @@
 // General path: tensor viewed as [outer, L, inner] with blocks along L; one warp per block when
 // inner == 1 (ragged or unaligned rows), one thread per (outer, block, inner) column otherwise.
 #include "vq_common.cuh"
+#include "vq_mx_body.cuh"
 
 namespace {
-
-struct MxParams {
-    const void* in;
-    int64_t outer, L, inner, block, nblk;   // nblk = ceil(L / block)
-    int64_t n;
-    ScaleRule rule;
-    TableDev tab;          // kind NONE: scale only
-    void* out_scale;
-    void* out_codes;
-    float* scale_f32;
-    int8_t* exp_e8;
-    uint8_t* codes;
-    int code_bits;
-    void* dequant;
-    int group_shift;       // fast path: log2(lanes per block)
-    int smem_lut16, smem_lut8;
-};
-
-__device__ __forceinline__ int pow2_steps_mx(int n_runs) {
-    int keys = n_runs - 1, p = 1;
-    while (p <= keys) p <<= 1;
-    return p >> 1;
-}
-
-// Shared-memory staging: [lut16 128 KB][lut8 64 KB][run keys/vals/codes 2.5 KB]
-__device__ __forceinline__ void stage_mx(const MxParams& p, uint4* smem, TableDev& tab, TableRes& res) {
-    tab = p.tab;
-    res = TableRes{p.tab.lut16, p.tab.run_keys, p.tab.run_vals, 0};
-    uint8_t* s8 = reinterpret_cast<uint8_t*>(smem);
-    if (p.smem_lut16) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.tab.lut16);
-        uint4* dst = reinterpret_cast<uint4*>(s8);
-        for (int i = threadIdx.x; i < 8192; i += blockDim.x) dst[i] = __ldg(src + i);
-        res.lut = reinterpret_cast<const uint16_t*>(s8);
-        s8 += 131072;
-    }
-    if (p.smem_lut8) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.tab.lut8);
-        uint4* dst = reinterpret_cast<uint4*>(s8);
-        for (int i = threadIdx.x; i < 4096; i += blockDim.x) dst[i] = __ldg(src + i);
-        tab.lut8 = s8;
-        s8 += 65536;
-    }
-    if (p.tab.kind == VQ_TABLE_RUNS) {
-        uint16_t* keys = reinterpret_cast<uint16_t*>(s8);
-        uint16_t* vals = keys + VQ_MAX_RUNS;
-        uint8_t* rc = s8 + 4 * VQ_MAX_RUNS;
-        for (int i = threadIdx.x; i < VQ_MAX_RUNS; i += blockDim.x) {
-            keys[i] = (i < p.tab.n_runs - 1) ? p.tab.run_keys[i] : (uint16_t)0xFFFF;
-            vals[i] = (i < p.tab.n_runs) ? p.tab.run_vals[i] : (uint16_t)0;
-            rc[i] = (p.tab.run_codes && i < p.tab.n_runs) ? p.tab.run_codes[i] : (uint8_t)0;
-        }
-        res.rk = keys;
-        res.rv = vals;
-        res.steps = pow2_steps_mx(p.tab.n_runs);
-        if (p.tab.run_codes) tab.run_codes = rc;
-    }
-    __syncthreads();
-}
-
-__device__ __forceinline__ int scale_exponent(float s) {
-    uint32_t b = __float_as_uint(s);
-    if (b >= 0x7F800000u) return 127;
-    int e = (b >= 0x00800000u) ? (int)(b >> 23) - 127 : (b ? (31 - __clz(b)) - 149 : -127);
-    return e < -127 ? -127 : (e > 127 ? 127 : e);
-}
-
-template <typename T>
-__device__ __forceinline__ void emit_scale(const MxParams& p, int64_t idx, float s) {
-    if (p.out_scale) store_one<T>(reinterpret_cast<T*>(p.out_scale) + idx, s);
-    if (p.scale_f32) p.scale_f32[idx] = s;
-    if (p.exp_e8) p.exp_e8[idx] = (int8_t)scale_exponent(s);
-}
 
 template <typename T, int U>
 __global__ void __launch_bounds__(1024, 1) mx_fast_kernel(const MxParams p) {

@@ -1,0 +1,195 @@
+// Fused MX scale + quantize over MANY tensors in one persistent launch (whole-model weight
+// quantization: hundreds of tensors, one table, one block size).
+//
+// The tensors are cut into tiles of blockDim.x * U 16-byte vectors; a tile never spans two
+// tensors.  The descriptors and the running tile counts live in a small device workspace the
+// caller provides; each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... and finds the
+// tensor of a tile by a binary search over the running counts (uniform across the CTA, served
+// from L1).  Per vector the work is the same as the single-tensor fast path: lane-group shuffle
+// reduction of |x| bit patterns, scale rule, table lookup from shared memory, packed stores.
+// HBM bound; algorithmic bytes per element: sizeof(T) read + the requested outputs.
+#include "vq_mx_body.cuh"
+
+namespace {
+
+struct MultiParams {
+    const vq_mx_item* items;     // device
+    const int64_t* tile_prefix;  // device, n_items + 1 running tile counts
+    int n_items;
+    int64_t n_tiles;
+    MxParams common;             // rule, table, code_bits, group_shift, smem flags (pointers unused)
+};
+
+template <typename T, int U>
+__global__ void __launch_bounds__(1024, 1) mx_multi_kernel(const MultiParams mp) {
+    extern __shared__ uint4 smem[];
+    TableDev tab;
+    TableRes res;
+    stage_mx(mp.common, smem, tab, res);
+    const ScaleRule rule = mp.common.rule;
+    constexpr int N = Vec<T>::N;
+    const int gs = mp.common.group_shift;
+    const uint32_t tile_vecs = blockDim.x * U;
+
+    for (int64_t tile = blockIdx.x; tile < mp.n_tiles; tile += gridDim.x) {
+        // largest i with tile_prefix[i] <= tile
+        int lo = 0, hi = mp.n_items;
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (__ldg(mp.tile_prefix + mid) <= tile) lo = mid; else hi = mid;
+        }
+        const vq_mx_item* it = mp.items + lo;
+        const T* in = reinterpret_cast<const T*>(it->in);
+        T* out_scale = reinterpret_cast<T*>(it->out_scale);
+        T* out_codes = reinterpret_cast<T*>(it->out_codes);
+        float* scale_f32 = it->scale_f32;
+        int8_t* exp_e8 = it->exp_e8;
+        uint8_t* codes8 = it->codes;
+        T* dequant = reinterpret_cast<T*>(it->dequant);
+        const uint32_t nvec = (uint32_t)(it->n / N);
+        const uint32_t v0 = (uint32_t)(tile - __ldg(mp.tile_prefix + lo)) * tile_vecs + threadIdx.x;
+
+        Vec<T> x[U];
+        uint32_t vi[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            vi[u] = v0 + u * blockDim.x;
+            if (vi[u] < nvec) x[u].load_stream(in + (size_t)vi[u] * N);
+            else {
+#pragma unroll
+                for (int j = 0; j < N; ++j) x[u].v[j] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            uint32_t m = 0;
+#pragma unroll
+            for (int j = 0; j < N; ++j) m = max(m, abs_bits(x[u].v[j]));
+            for (int o = 1; o < (1 << gs); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            if (vi[u] >= nvec) continue;
+            const float s = block_scale<T>(rule, m);
+            if ((vi[u] & ((1u << gs) - 1u)) == 0) {
+                const uint32_t b = vi[u] >> gs;
+                if (out_scale) store_one<T>(out_scale + b, s);
+                if (scale_f32) scale_f32[b] = s;
+                if (exp_e8) exp_e8[b] = (int8_t)scale_exponent(s);
+            }
+            mx_emit_vector<T>(tab, res, x[u], s, (size_t)vi[u] * N, out_codes, dequant, codes8, mp.common.code_bits);
+        }
+    }
+}
+
+constexpr int kThreads = 1024;
+constexpr int kU = 2;
+
+}  // namespace
+
+extern "C" {
+
+size_t vq_quantize_mx_multi_workspace(int n_items) {
+    if (n_items < 0) return 0;
+    return (size_t)n_items * sizeof(vq_mx_item) + ((size_t)n_items + 1) * sizeof(int64_t);
+}
+
+int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                         const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+    const char* name = "vq_quantize_mx_multi";
+    VQ_REQUIRE(n_items >= 0, "%s: negative item count", name);
+    if (n_items == 0) return 0;
+    VQ_REQUIRE(items != nullptr, "%s: null item array", name);
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(pow2 == 0 || pow2 == 1, "%s: scale rule must be 0 (amax/qmax) or 1 (power of two)", name);
+    if (pow2) VQ_REQUIRE(exp && exp->bump_at && exp->scale_of, "%s: power-of-two scales need the exponent tables", name);
+    VQ_REQUIRE(table && table->kind != VQ_TABLE_NONE, "%s: a table is required", name);
+    VQ_REQUIRE(!scale_table || scale_table->kind == VQ_TABLE_NONE || scale_table->kind == VQ_TABLE_LUT16 ||
+                   scale_table->kind == VQ_TABLE_INT, "%s: the scale table must be LUT16 or INT", name);
+    VQ_REQUIRE(workspace && (uintptr_t)workspace % 16 == 0 && workspace_bytes >= vq_quantize_mx_multi_workspace(n_items),
+               "%s: workspace missing, unaligned or smaller than vq_quantize_mx_multi_workspace(n_items)", name);
+    const int N = dtype == VQ_F32 ? 4 : 8;
+    VQ_REQUIRE(block > 0 && block % N == 0, "%s: block must be a positive multiple of %d elements", name, N);
+    const int64_t g = block / N;
+    VQ_REQUIRE(g <= 32 && (g & (g - 1)) == 0, "%s: block / %d must be a power of two <= 32", name, N);
+    int gs = 0;
+    while ((1ll << gs) < g) ++gs;
+
+    bool any_codes8 = false, any_values = false;
+    const int64_t tile_elems = (int64_t)kThreads * kU * N;
+    int64_t* prefix = new int64_t[(size_t)n_items + 1];
+    prefix[0] = 0;
+    int64_t total = 0;
+    for (int i = 0; i < n_items; ++i) {
+        const vq_mx_item& it = items[i];
+        auto al = [](const void* q, size_t a) { return q == nullptr || (uintptr_t)q % a == 0; };
+        bool ok = it.in && it.n >= 0 && it.n % block == 0 && it.n < (1ll << 31) && al(it.in, 16) && al(it.out_codes, 16) &&
+                  al(it.dequant, 16) && al(it.codes, 8) && al(it.scale_f32, 4) &&
+                  (it.out_scale || it.out_codes || it.scale_f32 || it.exp_e8 || it.codes || it.dequant);
+        if (!ok) {
+            delete[] prefix;
+            return vq_set_error(VQ_ERR_INVALID,
+                                "%s: item %d needs a 16-byte aligned input, n a multiple of the block below 2^31, "
+                                "aligned outputs and at least one output", name, i);
+        }
+        if (it.exp_e8 && !pow2) {
+            delete[] prefix;
+            return vq_set_error(VQ_ERR_INVALID, "%s: item %d: exp_e8 needs power-of-two scales", name, i);
+        }
+        any_codes8 |= it.codes != nullptr;
+        any_values |= it.out_codes != nullptr || it.dequant != nullptr;
+        prefix[i + 1] = prefix[i] + (it.n + tile_elems - 1) / tile_elems;
+        total += it.n;
+    }
+    if (any_codes8) {
+        bool have = table->kind == VQ_TABLE_INT || table->lut8 || (table->kind == VQ_TABLE_RUNS && table->run_codes);
+        if (!have || (code_bits != 8 && code_bits != 4)) {
+            delete[] prefix;
+            return vq_set_error(VQ_ERR_INVALID, "%s: packed codes need code_bits 8 or 4 and a code table", name);
+        }
+    }
+
+    MultiParams mp{};
+    mp.items = reinterpret_cast<const vq_mx_item*>(workspace);
+    mp.tile_prefix = reinterpret_cast<const int64_t*>((char*)workspace + (size_t)n_items * sizeof(vq_mx_item));
+    mp.n_items = n_items;
+    mp.n_tiles = prefix[n_items];
+    mp.common.rule.pow2 = pow2;
+    mp.common.rule.qmax = (float)quant_max;
+    mp.common.rule.bump_at = exp ? exp->bump_at : nullptr;
+    mp.common.rule.scale_of = exp ? exp->scale_of : nullptr;
+    mp.common.rule.stab = to_dev(pow2 ? nullptr : scale_table);
+    mp.common.rule.sres = TableRes{mp.common.rule.stab.lut16, nullptr, nullptr, 0};
+    mp.common.tab = to_dev(table);
+    mp.common.code_bits = code_bits;
+    mp.common.group_shift = gs;
+    const bool big = total >= (1 << 21);
+    mp.common.smem_lut16 = (big && table->kind == VQ_TABLE_LUT16 && any_values) ? 1 : 0;
+    mp.common.smem_lut8 = (big && table->kind == VQ_TABLE_LUT16 && any_codes8 && table->lut8) ? 1 : 0;
+    size_t smem = (mp.common.smem_lut16 ? 131072 : 0) + (mp.common.smem_lut8 ? 65536 : 0) +
+                  (table->kind == VQ_TABLE_RUNS ? 5 * VQ_MAX_RUNS : 0);
+    if ((int)smem > vq_max_smem_optin()) { mp.common.smem_lut8 = 0; smem -= 65536; }
+
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_mx_item), cudaMemcpyHostToDevice, st);
+    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + (size_t)n_items * sizeof(vq_mx_item), prefix,
+                                     ((size_t)n_items + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st);
+    const int64_t n_tiles = prefix[n_items];
+    delete[] prefix;  // pageable copies are staged before cudaMemcpyAsync returns
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+        return vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload failed: %s", name, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    if (n_tiles == 0) return 0;
+    const int sms = vq_sm_count();
+    int blocks = (int)(n_tiles < sms ? n_tiles : sms);
+    if (dtype == VQ_F32) {
+        auto k = mx_multi_kernel<float, kU>;
+        if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<blocks, kThreads, smem, st>>>(mp);
+    } else {
+        auto k = mx_multi_kernel<bf16_t, kU>;
+        if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<blocks, kThreads, smem, st>>>(mp);
+    }
+    VQ_LAUNCH_CHECK("mx_multi_kernel");
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,238 @@
+"""Whole-model MX weight quantization: many tensors, one kernel launch.
+
+Upstream quantizes the parameters of a converted model one by one with ``calculate_mx_qparam``
+followed by ``quantize`` (src/voyager_compiler/quantization/quantize_pt2e.py:485-500), each a
+chain of full-size torch passes.  Here every parameter that shares dtype, block size and table
+goes through ``vq_quantize_mx_multi``: a single persistent launch that reads each weight once and
+writes packed codes (4 or 8 bits) plus one fp32 scale per block, or -- for drop-in use -- the same
+float ``(scale, codes)`` pair the upstream ops return.
+
+Layer-wise sharding over several GPUs is plain partitioning: :func:`shard_plan` gives every
+rank a subset of the tensors (and a row range of tensors worth splitting) balanced by element
+count; no collective is needed because blocks never cross rows.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from .qtables import exp_tables, table_handle
+
+__all__ = ["PackedMX", "quantize_tensors_mx", "unpack_codes", "dequantize_packed_reference", "shard_plan",
+           "HostPipeline"]
+
+_DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
+_workspaces: Dict[Tuple[str, int], torch.Tensor] = {}
+
+
+@dataclass
+class PackedMX:
+    """Packed result for one tensor.  ``codes``: uint8, ``code_bits`` per element along the last
+    axis (two per byte for 4 bits, even element in the low nibble).  ``scale``: fp32, one per
+    block.  ``levels``: fp32 value of each code (host tensor); value = levels[code] * scale."""
+    codes: torch.Tensor
+    scale: torch.Tensor
+    shape: Tuple[int, ...]
+    block: int
+    code_bits: int
+    levels: torch.Tensor
+    exp_e8: Optional[torch.Tensor] = None
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant_max: float,
+                        force_scale_power_of_two: bool = False, scale_qmap=None, code_bits: Optional[int] = 4,
+                        float_outputs: bool = False, want_exp: bool = False):
+    """Quantize every tensor (blocks of ``block`` along the last, contiguous axis) in one launch
+    per dtype.  ``qmap``: a 65 536-entry table tensor, a numpy pattern array or an upstream dtype
+    string.  Returns a list of :class:`PackedMX` (``code_bits`` 4 or 8), or, with
+    ``float_outputs=True``, a list of ``(scale, codes)`` float tensors exactly as
+    ``torch.ops.quantized_ops.quantize_mx`` returns them."""
+    if not tensors:
+        return []
+    device = tensors[0].device
+    if device.type != "cuda":
+        raise RuntimeError("quantize_tensors_mx: CUDA tensors only; there is no CPU path")
+    results: List = [None] * len(tensors)
+    with torch.cuda.device(device):
+        tab = table_handle(qmap, device)
+        if not float_outputs:
+            if code_bits not in (4, 8):
+                raise ValueError("code_bits must be 4 or 8")
+            tab.with_codes()
+            if code_bits == 4 and tab.levels.numel() > 16:
+                raise ValueError(f"table has {tab.levels.numel()} levels; 4-bit codes hold 16")
+        stab = table_handle(scale_qmap, device, allow_runs=False) if scale_qmap is not None else None
+        stream = torch.cuda.current_stream(device).cuda_stream
+        for dt in (torch.bfloat16, torch.float32):
+            idx = [i for i, t in enumerate(tensors) if t.dtype == dt]
+            if not idx:
+                continue
+            exp = exp_tables(dt, quant_max, device) if force_scale_power_of_two else None
+            items = (_lib.VqMxItem * len(idx))()
+            keep = []
+            for k, i in enumerate(idx):
+                t = tensors[i]
+                if t.device != device:
+                    raise ValueError("all tensors must live on one device")
+                if t.ndim < 1 or t.shape[-1] % block:
+                    raise NotImplementedError(
+                        f"tensor {i}: last dimension {tuple(t.shape)} must be a multiple of the block ({block})")
+                x = t.contiguous()
+                nblk_shape = tuple(t.shape[:-1]) + (t.shape[-1] // block,)
+                items[k].input = x.data_ptr()
+                items[k].n = x.numel()
+                if float_outputs:
+                    sc = torch.empty(nblk_shape, dtype=dt, device=device)
+                    cd = torch.empty_like(x)
+                    items[k].out_scale, items[k].out_codes = sc.data_ptr(), cd.data_ptr()
+                    results[i] = (sc, cd)
+                else:
+                    sc = torch.empty(nblk_shape, dtype=torch.float32, device=device)
+                    per_byte = 8 // code_bits
+                    cd = torch.empty(tuple(t.shape[:-1]) + (t.shape[-1] // per_byte,), dtype=torch.uint8, device=device)
+                    ex = torch.empty(nblk_shape, dtype=torch.int8, device=device) if want_exp else None
+                    items[k].scale_f32, items[k].codes = sc.data_ptr(), cd.data_ptr()
+                    if ex is not None:
+                        items[k].exp_e8 = ex.data_ptr()
+                    results[i] = PackedMX(cd, sc, tuple(t.shape), block, code_bits, tab.levels, ex)
+                keep.append(x)
+            need = _lib.lib.vq_quantize_mx_multi_workspace(len(idx))
+            ws = _workspace(device, need)
+            _lib.check(_lib.lib.vq_quantize_mx_multi(
+                items, len(idx), _DT[dt], block, float(quant_max), 1 if force_scale_power_of_two else 0,
+                exp.ptr() if exp is not None else None, stab.ptr() if stab is not None else None, tab.ptr(),
+                0 if float_outputs else code_bits, ws.data_ptr(), ws.numel(), stream), "quantize_tensors_mx")
+            del keep
+    return results
+
+
+def unpack_codes(p: PackedMX) -> torch.Tensor:
+    """uint8 code of every element, shape ``p.shape`` (torch ops; a test and debugging helper)."""
+    c = p.codes
+    if p.code_bits == 8:
+        return c.reshape(p.shape)
+    lo, hi = c & 0xF, c >> 4
+    return torch.stack([lo, hi], dim=-1).reshape(p.shape)
+
+
+def dequantize_packed_reference(p: PackedMX, dtype=torch.float32) -> torch.Tensor:
+    """``levels[code] * scale`` with torch ops (a test helper, not a product kernel)."""
+    codes = unpack_codes(p).long()
+    vals = p.levels.to(codes.device)[codes]
+    s = torch.repeat_interleave(p.scale, p.block, dim=-1)
+    return (vals * s).to(dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+def shard_plan(sizes: Sequence[int], rows: Sequence[int], world_size: int, split_threshold: float = 0.5):
+    """Balanced assignment of tensors to ranks.  ``sizes[i]`` elements, ``rows[i]`` rows of tensor
+    i.  Tensors larger than ``split_threshold`` x the per-rank share are cut by rows into
+    ``world_size`` pieces; the rest are placed greedily, largest first, on the least loaded rank.
+    Returns ``plan[rank] = [(tensor index, row_begin, row_end), ...]``; every row of every tensor
+    appears exactly once."""
+    if world_size < 1:
+        raise ValueError("world_size must be >= 1")
+    total = sum(sizes)
+    share = total / world_size
+    plan: List[List[Tuple[int, int, int]]] = [[] for _ in range(world_size)]
+    load = [0.0] * world_size
+    whole = []
+    for i, (n, r) in enumerate(zip(sizes, rows)):
+        if world_size > 1 and n > split_threshold * share and r >= world_size:
+            per_row = n // r
+            for k in range(world_size):
+                b, e = r * k // world_size, r * (k + 1) // world_size
+                if e > b:
+                    plan[k].append((i, b, e))
+                    load[k] += (e - b) * per_row
+        else:
+            whole.append(i)
+    for i in sorted(whole, key=lambda j: -sizes[j]):
+        k = min(range(world_size), key=lambda r_: load[r_])
+        plan[k].append((i, 0, rows[i]))
+        load[k] += sizes[i]
+    for p in plan:
+        p.sort()
+    return plan
+
+
+class HostPipeline:
+    """Quantize tensors that live in pinned HOST memory and return packed results in pinned host
+    memory: host->device copies, the fused kernel and device->host copies run on three streams,
+    chunk by chunk, so the transfers overlap the kernel."""
+
+    def __init__(self, device, qmap, block: int, quant_max: float, force_scale_power_of_two: bool = False,
+                 code_bits: int = 4, chunk_bytes: int = 1 << 30):
+        self.device = torch.device(device)
+        self.qmap, self.block, self.quant_max = qmap, block, quant_max
+        self.pow2, self.code_bits, self.chunk_bytes = force_scale_power_of_two, code_bits, chunk_bytes
+        self.s_in = torch.cuda.Stream(self.device)
+        self.s_k = torch.cuda.Stream(self.device)
+        self.s_out = torch.cuda.Stream(self.device)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def run(self, host_tensors: Sequence[torch.Tensor], host_out: Optional[List[Tuple[torch.Tensor, torch.Tensor]]] = None):
+        """Returns ``[(codes_host, scale_host), ...]``; ``host_out`` supplies preallocated pinned
+        destinations.  Synchronises the three streams before returning."""
+        dev = self.device
+        chunks, cur, size = [], [], 0
+        for i, t in enumerate(host_tensors):
+            cur.append(i)
+            size += t.numel() * t.element_size()
+            if size >= self.chunk_bytes:
+                chunks.append(cur)
+                cur, size = [], 0
+        if cur:
+            chunks.append(cur)
+        outs: List = [None] * len(host_tensors)
+        self.h2d_bytes = self.d2h_bytes = 0
+        live = []
+        for ch in chunks:
+            with torch.cuda.stream(self.s_in):
+                dev_in = [host_tensors[i].to(dev, non_blocking=True) for i in ch]
+                ev_in = torch.cuda.Event()
+                ev_in.record(self.s_in)
+            self.h2d_bytes += sum(host_tensors[i].numel() * host_tensors[i].element_size() for i in ch)
+            with torch.cuda.stream(self.s_k):
+                self.s_k.wait_event(ev_in)
+                packed = quantize_tensors_mx(dev_in, self.qmap, self.block, self.quant_max, self.pow2,
+                                             code_bits=self.code_bits)
+                ev_k = torch.cuda.Event()
+                ev_k.record(self.s_k)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_k)
+                for i, p in zip(ch, packed):
+                    if host_out is not None:
+                        hc, hs = host_out[i]
+                    else:
+                        hc = torch.empty(p.codes.shape, dtype=torch.uint8, pin_memory=True)
+                        hs = torch.empty(p.scale.shape, dtype=torch.float32, pin_memory=True)
+                    hc.copy_(p.codes, non_blocking=True)
+                    hs.copy_(p.scale, non_blocking=True)
+                    outs[i] = (hc, hs)
+                    self.d2h_bytes += hc.numel() + hs.numel() * 4
+            # tensors allocated on one stream and used on another must outlive that use
+            for t in dev_in:
+                t.record_stream(self.s_k)
+            for p in packed:
+                p.codes.record_stream(self.s_out)
+                p.scale.record_stream(self.s_out)
+            live.append((dev_in, packed))
+        self.s_in.synchronize()
+        self.s_k.synchronize()
+        self.s_out.synchronize()
+        return outs
