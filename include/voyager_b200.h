@@ -64,7 +64,9 @@ typedef struct vq_table {
     uint8_t nan_code;          /* RUNS: packed codes for NaN, +inf and -inf inputs */
     uint8_t pinf_code;
     uint8_t ninf_code;
-    uint8_t reserved[7];
+    uint8_t nan_uniform;       /* LUT16: non-zero when every NaN input pattern has the same output, which
+                                  lets the kernels use the hardware bf16 conversion (NaN -> 0x7FFF) */
+    uint8_t reserved[6];
 } vq_table;
 
 /* Where the scale (and zero point) of element i lives (upstream `expand`,

@@ -42,6 +42,22 @@ def test_fixture_bit_exact_on_cuda(case, policy):
         assert ok, f"{case['name']} [{policy}]: {msg}"
 
 
+MX_CASES = [c for c in ELEMENTWISE if c["op"] == "quantize_mx"]
+
+
+@pytest.mark.parametrize("case", MX_CASES, ids=[c["name"] for c in MX_CASES])
+def test_generic_mx_kernels_stay_bit_exact(case):
+    """The specialised fused kernel normally takes these; the generic kernels must agree too."""
+    os.environ["VOYAGER_B200_GENERIC_MX"] = "1"
+    try:
+        outs, expected = run_case(case, torch.ops.quantized_ops, device="cuda")
+        for o, e in zip(outs, expected):
+            ok, msg = same_bits(o, e)
+            assert ok, f"{case['name']}: {msg}"
+    finally:
+        del os.environ["VOYAGER_B200_GENERIC_MX"]
+
+
 @pytest.mark.parametrize("case", GEMMS, ids=[c["name"] for c in GEMMS])
 def test_gemm_fixture_within_tolerance(case):
     outs, expected = run_case(case, torch.ops.quantized_ops, device="cuda")

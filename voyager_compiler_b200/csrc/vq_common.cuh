@@ -35,6 +35,13 @@ int vq_max_smem_optin();         // max opt-in dynamic shared memory per block o
         vq_count_launch();                                                                     \
     } while (0)
 
+// Tries the compile-time specialised fused MX kernel on `items` (host array; one item is passed by
+// value, several need the device `workspace`).  Returns 1 when it launched, 0 when the arguments
+// are outside its domain (the caller then uses the generic kernels), a negative status on error.
+int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                   const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                   void* workspace, cudaStream_t st);
+
 // Division of a 31-bit index by a run-time constant: q = (umulhi(n, m) + n) >> s, valid for
 // 0 <= n < 2^31 and 1 <= d < 2^31.
 struct FastDiv {

@@ -8,6 +8,8 @@
 //
 // General path: tensor viewed as [outer, L, inner] with blocks along L; one warp per block when
 // inner == 1 (ragged or unaligned rows), one thread per (outer, block, inner) column otherwise.
+#include <cstdlib>
+
 #include "vq_common.cuh"
 #include "vq_mx_body.cuh"
 
@@ -242,6 +244,14 @@ int run_mx(const char* name, const void* in, int dtype, int64_t outer, int64_t L
 
     const bool big = n >= (1 << 21);
     const bool need_values = has_tab && (out_codes || p.dequant);
+    if (fast && has_tab && n < (1ll << 31) && !getenv("VOYAGER_B200_GENERIC_MX")) {
+        vq_mx_item item{};
+        item.in = in; item.out_scale = out_scale; item.out_codes = out_codes; item.scale_f32 = p.scale_f32;
+        item.exp_e8 = p.exp_e8; item.codes = p.codes; item.dequant = p.dequant; item.n = n;
+        int fr = vq_mx_fast_try(&item, 1, dtype, p.block, quant_max, pow2, exp, scale_table, table, p.code_bits,
+                                nullptr, st);
+        if (fr != 0) return fr < 0 ? fr : 0;
+    }
     if (fast) {
         p.group_shift = gs;
         // pieces of at most 2^30 elements, whole blocks each

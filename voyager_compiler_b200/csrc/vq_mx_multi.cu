@@ -8,7 +8,10 @@
 // from L1).  Per vector the work is the same as the single-tensor fast path: lane-group shuffle
 // reduction of |x| bit patterns, scale rule, table lookup from shared memory, packed stores.
 // HBM bound; algorithmic bytes per element: sizeof(T) read + the requested outputs.
+#include <cstdlib>
+
 #include "vq_mx_body.cuh"
+#include "vq_mx_fast.cuh"
 
 namespace {
 
@@ -79,10 +82,227 @@ __global__ void __launch_bounds__(1024, 1) mx_multi_kernel(const MultiParams mp)
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Specialised kernel (see vq_mx_fast.cuh).  One descriptor can be passed by value (`single`) so
+// that single-tensor ops need no workspace.
+struct FastParams {
+    const vq_mx_item* items;
+    const int64_t* tile_prefix;
+    int n_items;
+    int64_t n_tiles;
+    vq_mx_item single;
+    ScaleRule rule;
+    TableDev tab;
+    int group_shift;
+    int allow_refine;
+};
+
+template <typename T, int RULE, int TK, int OUT, bool SM, int U>
+__global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
+    extern __shared__ uint4 smem[];
+    FastTab ft;
+    ft.lut16 = p.tab.lut16;
+    ft.lut8 = p.tab.lut8;
+    ft.lo = p.tab.lo;
+    ft.hi = p.tab.hi;
+    ft.lo_is_zero = (p.tab.lo == 0.0f) ? 1 : 0;
+    if (SM && TK == TK_LUT) {
+        const bool wide = OUT == OUT_FLOAT;
+        const uint4* src = reinterpret_cast<const uint4*>(wide ? (const void*)p.tab.lut16 : (const void*)p.tab.lut8);
+        const int n16 = wide ? 8192 : 4096;
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) smem[i] = __ldg(src + i);
+        if (wide) ft.lut16 = reinterpret_cast<const uint16_t*>(smem);
+        else ft.lut8 = reinterpret_cast<const uint8_t*>(smem);
+        __syncthreads();
+    }
+    constexpr int N = sizeof(T) == 2 ? 8 : 4;
+    const int gs = p.group_shift;
+    const uint32_t tile_vecs = blockDim.x * U;
+    const bool refine = p.allow_refine != 0;
+
+    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
+        const T* in;
+        T* out_scale;
+        T* out_codes;
+        float* scale_f32;
+        int8_t* exp_e8;
+        uint8_t* codes8;
+        uint32_t nvec, v0;
+        if (p.n_items == 1) {
+            in = reinterpret_cast<const T*>(p.single.in);
+            out_scale = reinterpret_cast<T*>(p.single.out_scale);
+            out_codes = reinterpret_cast<T*>(p.single.out_codes);
+            scale_f32 = p.single.scale_f32;
+            exp_e8 = p.single.exp_e8;
+            codes8 = p.single.codes;
+            nvec = (uint32_t)(p.single.n / N);
+            v0 = (uint32_t)tile * tile_vecs + threadIdx.x;
+        } else {
+            int lo = 0, hi = p.n_items;
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (__ldg(p.tile_prefix + mid) <= tile) lo = mid; else hi = mid;
+            }
+            const vq_mx_item* it = p.items + lo;
+            in = reinterpret_cast<const T*>(it->in);
+            out_scale = reinterpret_cast<T*>(it->out_scale);
+            out_codes = reinterpret_cast<T*>(it->out_codes);
+            scale_f32 = it->scale_f32;
+            exp_e8 = it->exp_e8;
+            codes8 = it->codes;
+            nvec = (uint32_t)(it->n / N);
+            v0 = (uint32_t)(tile - __ldg(p.tile_prefix + lo)) * tile_vecs + threadIdx.x;
+        }
+        Raw<T> x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t vi = v0 + u * blockDim.x;
+            if (vi < nvec) x[u].load_stream(in + (size_t)vi * N);
+            else x[u].zero();
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t vi = v0 + u * blockDim.x;
+            uint32_t min_nz;
+            uint32_t m = raw_amax<T>(x[u], min_nz);
+            for (int o = 1; o < (1 << gs); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            if (vi >= nvec) continue;
+            const float s = fast_scale<T, RULE>(p.rule, m);
+            if ((vi & ((1u << gs) - 1u)) == 0) {
+                const uint32_t b = vi >> gs;
+                if (OUT == OUT_FLOAT) {
+                    store_one<T>(out_scale + b, s);
+                } else {
+                    scale_f32[b] = s;
+                    if (RULE == 1 && exp_e8) exp_e8[b] = (int8_t)scale_exponent(s);
+                }
+            }
+            fast_vector<T, TK, OUT, SM>(ft, x[u], s, min_nz, refine, (size_t)vi, out_codes, codes8);
+        }
+    }
+}
+
+template <typename T, int RULE, int TK, int OUT, bool SM>
+int launch_fast2(const FastParams& p, int threads, int blocks, size_t smem, cudaStream_t st) {
+    auto k = mx_fast2_kernel<T, RULE, TK, OUT, SM, 4>;
+    if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<blocks, threads, smem, st>>>(p);
+    VQ_LAUNCH_CHECK("mx_fast2_kernel");
+    return 0;
+}
+
+template <typename T, int RULE, int TK>
+int dispatch_out(const FastParams& p, int out, bool sm, int threads, int blocks, size_t smem, cudaStream_t st) {
+    if (TK == TK_INT) sm = false;
+    switch (out) {
+        case OUT_FLOAT:
+            return sm ? launch_fast2<T, RULE, TK, OUT_FLOAT, true>(p, threads, blocks, smem, st)
+                      : launch_fast2<T, RULE, TK, OUT_FLOAT, false>(p, threads, blocks, smem, st);
+        case OUT_PACK4:
+            return sm ? launch_fast2<T, RULE, TK, OUT_PACK4, true>(p, threads, blocks, smem, st)
+                      : launch_fast2<T, RULE, TK, OUT_PACK4, false>(p, threads, blocks, smem, st);
+        default:
+            return sm ? launch_fast2<T, RULE, TK, OUT_PACK8, true>(p, threads, blocks, smem, st)
+                      : launch_fast2<T, RULE, TK, OUT_PACK8, false>(p, threads, blocks, smem, st);
+    }
+}
+
+template <typename T>
+int dispatch_rule(const FastParams& p, int rule, int tk, int out, bool sm, int threads, int blocks, size_t smem,
+                  cudaStream_t st) {
+    if (rule == 1) {
+        return tk == TK_INT ? dispatch_out<T, 1, TK_INT>(p, out, sm, threads, blocks, smem, st)
+                            : dispatch_out<T, 1, TK_LUT>(p, out, sm, threads, blocks, smem, st);
+    }
+    return tk == TK_INT ? dispatch_out<T, 0, TK_INT>(p, out, sm, threads, blocks, smem, st)
+                        : dispatch_out<T, 0, TK_LUT>(p, out, sm, threads, blocks, smem, st);
+}
+
 constexpr int kThreads = 1024;
 constexpr int kU = 2;
 
 }  // namespace
+
+int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                   const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                   void* workspace, cudaStream_t st) {
+    if (n_items < 1 || !table || (pow2 != 0 && pow2 != 1)) return 0;
+    int tk;
+    if (table->kind == VQ_TABLE_INT) tk = TK_INT;
+    else if (table->kind == VQ_TABLE_LUT16 && table->nan_uniform && table->lut16) tk = TK_LUT;
+    else return 0;
+    if (scale_table && scale_table->kind == VQ_TABLE_RUNS) return 0;
+    const int N = dtype == VQ_F32 ? 4 : 8;
+    if (block % N) return 0;
+    const int64_t g = block / N;
+    if (g > 32 || (g & (g - 1))) return 0;
+    int gs = 0;
+    while ((1ll << gs) < g) ++gs;
+    // every item must ask for the same output set
+    int out = -1;
+    int64_t total = 0;
+    for (int i = 0; i < n_items; ++i) {
+        const vq_mx_item& it = items[i];
+        int o;
+        if (it.out_scale && it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes && !it.dequant) o = OUT_FLOAT;
+        else if (it.codes && it.scale_f32 && !it.out_scale && !it.out_codes && !it.dequant && (code_bits == 4 || code_bits == 8))
+            o = code_bits == 4 ? OUT_PACK4 : OUT_PACK8;
+        else return 0;
+        if (out >= 0 && o != out) return 0;
+        if (it.exp_e8 && !pow2) return 0;
+        if (it.n % block || it.n >= (1ll << 31) || (uintptr_t)it.in % 16 || (uintptr_t)it.out_codes % 16 ||
+            (uintptr_t)it.codes % 8 || (uintptr_t)it.scale_f32 % 4)
+            return 0;
+        out = o;
+        total += it.n;
+    }
+    if (out != OUT_FLOAT && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
+    if (out != OUT_FLOAT && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
+    if (n_items > 1 && !workspace) return 0;
+    if (total == 0) return 1;
+
+    FastParams p{};
+    p.n_items = n_items;
+    p.rule.pow2 = pow2;
+    p.rule.qmax = (float)quant_max;
+    p.rule.bump_at = exp ? exp->bump_at : nullptr;
+    p.rule.scale_of = exp ? exp->scale_of : nullptr;
+    p.rule.stab = to_dev(pow2 ? nullptr : scale_table);
+    p.rule.sres = TableRes{p.rule.stab.lut16, nullptr, nullptr, 0};
+    p.tab = to_dev(table);
+    p.group_shift = gs;
+    p.allow_refine = (p.rule.stab.kind == VQ_TABLE_NONE) ? 1 : 0;
+
+    const bool big = total >= (1ll << 22);
+    const int threads = big ? 1024 : 128;
+    const int64_t tile_elems = (int64_t)threads * 4 * N;
+    if (n_items == 1) {
+        p.single = items[0];
+        p.n_tiles = (items[0].n + tile_elems - 1) / tile_elems;
+    } else {
+        int64_t* prefix = new int64_t[(size_t)n_items + 1];
+        prefix[0] = 0;
+        for (int i = 0; i < n_items; ++i) prefix[i + 1] = prefix[i] + (items[i].n + tile_elems - 1) / tile_elems;
+        p.n_tiles = prefix[n_items];
+        p.items = reinterpret_cast<const vq_mx_item*>(workspace);
+        p.tile_prefix = reinterpret_cast<const int64_t*>((char*)workspace + (size_t)n_items * sizeof(vq_mx_item));
+        cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_mx_item), cudaMemcpyHostToDevice, st);
+        cudaError_t e2 = cudaMemcpyAsync((char*)workspace + (size_t)n_items * sizeof(vq_mx_item), prefix,
+                                         ((size_t)n_items + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st);
+        delete[] prefix;  // pageable copies are staged before cudaMemcpyAsync returns
+        if (e1 != cudaSuccess || e2 != cudaSuccess)
+            return vq_set_error(VQ_ERR_CUDA, "descriptor upload failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    }
+    const bool sm = big && tk == TK_LUT;
+    const size_t smem = sm ? (out == OUT_FLOAT ? 131072 : 65536) : 0;
+    const int sms = vq_sm_count();
+    const int64_t cap = big ? sms : (int64_t)sms * 8;
+    const int blocks = (int)(p.n_tiles < cap ? p.n_tiles : cap);
+    int rc = (dtype == VQ_F32) ? dispatch_rule<float>(p, pow2, tk, out, sm, threads, blocks, smem, st)
+                               : dispatch_rule<bf16_t>(p, pow2, tk, out, sm, threads, blocks, smem, st);
+    return rc ? rc : 1;
+}
 
 extern "C" {
 
@@ -144,6 +364,15 @@ int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_
         if (!have || (code_bits != 8 && code_bits != 4)) {
             delete[] prefix;
             return vq_set_error(VQ_ERR_INVALID, "%s: packed codes need code_bits 8 or 4 and a code table", name);
+        }
+    }
+
+    if (!getenv("VOYAGER_B200_GENERIC_MX")) {
+        int fr = vq_mx_fast_try(items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits,
+                                workspace, (cudaStream_t)stream);
+        if (fr != 0) {
+            delete[] prefix;
+            return fr < 0 ? fr : 0;
         }
     }
 
