@@ -1,11 +1,12 @@
-// Compile-time specialised per-vector body of the fused MX scale + quantize kernels.
+// Compile-time specialised per-chunk body of the fused MX scale + quantize kernels.
 //
 // The generic body (vq_mx_body.cuh) spends ~70 thread instructions per element, which makes the
-// kernel issue bound at 15 % of the HBM roofline.  This body is specialised on dtype, scale rule,
-// table kind and output set so that per element only these remain:
-//   unpack, 1-3 multiply/FMA for x / scale, half a cvt.rn.bf16x2, one shared-memory lookup,
-//   one pack op; per 16-byte vector: packed |x| maxima (max.u16x2 on bf16 pairs), the lane-group
-//   shuffle reduction and the scale rule.
+// kernel issue bound at 15 % of the HBM roofline.  Here each thread owns a 32-byte chunk (16 bf16 /
+// 8 fp32, one 256-bit load) and the code is specialised on dtype, scale rule, table kind and
+// output set, so that per element only these remain: unpack, 1-3 multiply/FMA for x / scale, one
+// cvt.rn.bf16 (pattern lands zero-extended in a register, ready to be a shared-memory offset),
+// one shared-memory lookup, one multiply-add to pack; per 32-bit word three SIMD integer ops for
+// the |x| extrema; per chunk the lane-group shuffle reduction and the scale rule.
 //
 // x / scale without an IEEE division per element:
 //   * scale is a power of two with a normal reciprocal: x * (1/scale) is the same correctly
@@ -17,7 +18,7 @@
 //     ~2^-23 error of q; rounding q to bf16 therefore equals rounding the IEEE fp32 quotient to
 //     bf16, which is what the CPU reference computes.  Used only when the scale comes straight
 //     from the block maximum (so |q| stays bounded) and the scale and every non-zero element of
-//     the vector are at least 2^-60 away from the subnormal range, so that e is computed exactly.
+//     the chunk are at least 2^-60 away from the subnormal range, so that e is computed exactly.
 //   * everything else: __fdiv_rn.
 #pragma once
 #include "vq_mx_body.cuh"
@@ -27,19 +28,30 @@ namespace {
 enum { OUT_FLOAT = 0, OUT_PACK4 = 1, OUT_PACK8 = 2 };
 enum { TK_LUT = 0, TK_INT = 1 };
 
-template <typename T>
-struct Raw {
-    uint32_t w[4];
-    __device__ __forceinline__ void load_stream(const T* p) {
-        uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
-        w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+// 32 bytes of input as raw words
+struct Chunk {
+    uint32_t w[8];
+    __device__ __forceinline__ void load(const void* p) {
+        asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                     : "l"(p));
     }
-    __device__ __forceinline__ void zero() { w[0] = w[1] = w[2] = w[3] = 0u; }
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) w[k] = 0u;
+    }
 };
 
-__device__ __forceinline__ uint32_t cvt_bf16x2(float hi, float lo) {
+__device__ __forceinline__ void store32(void* p, const uint32_t* o) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                 "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                 : "memory");
+}
+
+// bf16 pattern of v, zero-extended (NaN -> 0x7FFF)
+__device__ __forceinline__ uint32_t bf16_pattern(float v) {
     uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(0.0f), "f"(v));
     return d;
 }
 __device__ __forceinline__ float rcp_approx(float s) {
@@ -48,23 +60,36 @@ __device__ __forceinline__ float rcp_approx(float s) {
     return r;
 }
 
-// per-thread |x| maximum of one raw vector as fp32 bits (bf16: pattern << 16), plus, for bf16,
-// the smallest (|pattern| - 1) over the vector (0xFFFF for zeros) used by the safety test
+// |x| maximum of a chunk as fp32 bits.  For bf16 also whether the reciprocal path is safe for this
+// chunk: no non-zero element below 2^-60 (pattern 0x2180).
 template <typename T>
-__device__ __forceinline__ uint32_t raw_amax(const Raw<T>& x, uint32_t& min_nz);
+__device__ __forceinline__ uint32_t chunk_amax(const Chunk& x, bool& safe);
 template <>
-__device__ __forceinline__ uint32_t raw_amax<bf16_t>(const Raw<bf16_t>& x, uint32_t& min_nz) {
-    uint32_t a0 = x.w[0] & 0x7FFF7FFFu, a1 = x.w[1] & 0x7FFF7FFFu, a2 = x.w[2] & 0x7FFF7FFFu, a3 = x.w[3] & 0x7FFF7FFFu;
-    uint32_t m = __vmaxu2(__vmaxu2(a0, a1), __vmaxu2(a2, a3));
-    uint32_t t = __vminu2(__vminu2(__vsub2(a0, 0x00010001u), __vsub2(a1, 0x00010001u)),
-                          __vminu2(__vsub2(a2, 0x00010001u), __vsub2(a3, 0x00010001u)));
-    min_nz = min(t & 0xFFFFu, t >> 16);
-    return max(m & 0xFFFFu, m >> 16) << 16;
+__device__ __forceinline__ uint32_t chunk_amax<bf16_t>(const Chunk& x, bool& safe) {
+    uint32_t a[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = x.w[k] & 0x7FFF7FFFu;
+    uint32_t mx = __vmaxu2(__vmaxu2(__vmaxu2(a[0], a[1]), __vmaxu2(a[2], a[3])),
+                           __vmaxu2(__vmaxu2(a[4], a[5]), __vmaxu2(a[6], a[7])));
+    uint32_t mn = __vminu2(__vminu2(__vminu2(a[0], a[1]), __vminu2(a[2], a[3])),
+                           __vminu2(__vminu2(a[4], a[5]), __vminu2(a[6], a[7])));
+    safe = min(mn & 0xFFFFu, mn >> 16) >= 0x2180u;
+    if (!safe) {
+        // zeros are harmless: look at the smallest NON-zero magnitude (0 - 1 wraps to 0xFFFF)
+        uint32_t t = 0xFFFFFFFFu;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t = __vminu2(t, __vsub2(a[k], 0x00010001u));
+        safe = min(t & 0xFFFFu, t >> 16) >= 0x217Fu;
+    }
+    return max(mx & 0xFFFFu, mx >> 16) << 16;
 }
 template <>
-__device__ __forceinline__ uint32_t raw_amax<float>(const Raw<float>& x, uint32_t& min_nz) {
-    min_nz = 0xFFFFu;
-    return max(max(x.w[0] & 0x7FFFFFFFu, x.w[1] & 0x7FFFFFFFu), max(x.w[2] & 0x7FFFFFFFu, x.w[3] & 0x7FFFFFFFu));
+__device__ __forceinline__ uint32_t chunk_amax<float>(const Chunk& x, bool& safe) {
+    safe = false;
+    uint32_t m = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) m = max(m, x.w[k] & 0x7FFFFFFFu);
+    return m;
 }
 
 template <typename T, int RULE>
@@ -98,8 +123,7 @@ template <bool SM>
 __device__ __forceinline__ uint32_t ld_u16(const uint16_t* base, uint32_t idx) {
     if (SM) {
         uint32_t v;
-        uint32_t a = (uint32_t)__cvta_generic_to_shared(base) + idx * 2u;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"((uint32_t)__cvta_generic_to_shared(base) + idx * 2u));
         return v;
     }
     return __ldg(base + idx);
@@ -108,8 +132,7 @@ template <bool SM>
 __device__ __forceinline__ uint32_t ld_u8(const uint8_t* base, uint32_t idx) {
     if (SM) {
         uint32_t v;
-        uint32_t a = (uint32_t)__cvta_generic_to_shared(base) + idx;
-        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"((uint32_t)__cvta_generic_to_shared(base) + idx));
         return v;
     }
     return __ldg(base + idx);
@@ -127,22 +150,22 @@ __device__ __forceinline__ float int_round(const FastTab& t, float vb) {
     return (vb != vb) ? vb : q;
 }
 
-// One 16-byte vector: quantize with block scale `s`, write the outputs of kind OUT at vector
-// index `vi` of this tensor.
+// One 32-byte chunk: quantize with block scale `s`, write outputs of kind OUT at chunk index `ci`
+// of this tensor (element offset ci * N).
 template <typename T, int TK, int OUT, bool SM>
-__device__ __forceinline__ void fast_vector(const FastTab& t, const Raw<T>& x, float s, uint32_t min_nz,
-                                            bool allow_refine, size_t vi, T* out_codes, uint8_t* codes8) {
-    constexpr int N = sizeof(T) == 2 ? 8 : 4;
+__device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, float s, bool refine_ok, size_t ci,
+                                           T* out_codes, uint8_t* codes8) {
+    constexpr int N = sizeof(T) == 2 ? 16 : 8;
     float v[N];
     if (sizeof(T) == 2) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            v[2 * k] = __uint_as_float(x.w[k] << 16);
-            v[2 * k + 1] = __uint_as_float(x.w[k] & 0xFFFF0000u);
+        for (int k = 0; k < 8; ++k) {
+            v[(2 * k) % N] = __uint_as_float(x.w[k] << 16);
+            v[(2 * k + 1) % N] = __uint_as_float(x.w[k] & 0xFFFF0000u);
         }
     } else {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = __uint_as_float(x.w[k]);
+        for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(x.w[k]);
     }
     const uint32_t sb = __float_as_uint(s);
     const uint32_t ex = (sb >> 23) & 0xFFu;
@@ -150,7 +173,7 @@ __device__ __forceinline__ void fast_vector(const FastTab& t, const Raw<T>& x, f
         const float r = __uint_as_float((254u - ex) << 23);
 #pragma unroll
         for (int j = 0; j < N; ++j) v[j] = __fmul_rn(v[j], r);
-    } else if (sizeof(T) == 2 && allow_refine && (sb >> 31) == 0u && ex >= 64u && ex <= 190u && min_nz >= 0x217Fu) {
+    } else if (sizeof(T) == 2 && refine_ok && (sb >> 31) == 0u && ex >= 64u && ex <= 190u) {
         const float r = rcp_approx(s);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
@@ -162,58 +185,65 @@ __device__ __forceinline__ void fast_vector(const FastTab& t, const Raw<T>& x, f
 #pragma unroll
         for (int j = 0; j < N; ++j) v[j] = __fdiv_rn(v[j], s);
     }
-    // bf16 patterns of the quotients, two per word (NaN -> 0x7FFF; the host only selects this
-    // body for tables that give every NaN pattern the same output)
-    uint32_t p2[N / 2];
+    // bf16 pattern of every quotient (NaN -> 0x7FFF; the host only selects this body for tables
+    // that give every NaN pattern the same output)
+    uint32_t p[N];
 #pragma unroll
-    for (int k = 0; k < N / 2; ++k) p2[k] = cvt_bf16x2(v[2 * k + 1], v[2 * k]);
+    for (int j = 0; j < N; ++j) p[j] = bf16_pattern(v[j]);
 
     if (OUT == OUT_FLOAT) {
-        uint32_t o16[N];   // output bf16 patterns
+        uint32_t o[8];
+        if (sizeof(T) == 2) {
 #pragma unroll
-        for (int k = 0; k < N / 2; ++k) {
-            if (TK == TK_LUT) {
-                o16[2 * k] = ld_u16<SM>(t.lut16, p2[k] & 0xFFFFu);
-                o16[2 * k + 1] = ld_u16<SM>(t.lut16, p2[k] >> 16);
-            } else {
-                o16[2 * k] = __float_as_uint(int_round(t, __uint_as_float(p2[k] << 16))) >> 16;
-                o16[2 * k + 1] = __float_as_uint(int_round(t, __uint_as_float(p2[k] & 0xFFFF0000u))) >> 16;
+            for (int k = 0; k < 8; ++k) {
+                uint32_t a, b;
+                if (TK == TK_LUT) {
+                    a = ld_u16<SM>(t.lut16, p[(2 * k) % N]);
+                    b = ld_u16<SM>(t.lut16, p[(2 * k + 1) % N]);
+                } else {
+                    a = __float_as_uint(int_round(t, __uint_as_float(p[(2 * k) % N] << 16))) >> 16;
+                    b = __float_as_uint(int_round(t, __uint_as_float(p[(2 * k + 1) % N] << 16))) >> 16;
+                }
+                o[k] = b * 65536u + a;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (TK == TK_LUT) o[k] = ld_u16<SM>(t.lut16, p[k]) << 16;
+                else o[k] = __float_as_uint(int_round(t, __uint_as_float(p[k] << 16)));
             }
         }
-        if (sizeof(T) == 2) {
-            uint4 o;
-            o.x = o16[0] | (o16[1] << 16); o.y = o16[2] | (o16[3] << 16);
-            o.z = o16[4 % N] | (o16[5 % N] << 16); o.w = o16[6 % N] | (o16[7 % N] << 16);
-            __stcs(reinterpret_cast<uint4*>(out_codes + vi * N), o);
-        } else {
-            uint4 o = make_uint4(o16[0] << 16, o16[1] << 16, o16[2] << 16, o16[3] << 16);
-            __stcs(reinterpret_cast<uint4*>(out_codes + vi * N), o);
-        }
+        store32(out_codes + ci * N, o);
     } else {
         uint32_t c[N];
 #pragma unroll
-        for (int k = 0; k < N / 2; ++k) {
+        for (int j = 0; j < N; ++j) {
             if (TK == TK_LUT) {
-                c[2 * k] = ld_u8<SM>(t.lut8, p2[k] & 0xFFFFu);
-                c[2 * k + 1] = ld_u8<SM>(t.lut8, p2[k] >> 16);
+                c[j] = ld_u8<SM>(t.lut8, p[j]);
             } else {
-                float a = int_round(t, __uint_as_float(p2[k] << 16));
-                float b = int_round(t, __uint_as_float(p2[k] & 0xFFFF0000u));
-                c[2 * k] = (a != a) ? 0u : ((uint32_t)(int)a & 0xFFu);
-                c[2 * k + 1] = (b != b) ? 0u : ((uint32_t)(int)b & 0xFFu);
+                float a = int_round(t, __uint_as_float(p[j] << 16));
+                c[j] = (a != a) ? 0u : ((uint32_t)(int)a & (OUT == OUT_PACK4 ? 0xFu : 0xFFu));
             }
         }
         if (OUT == OUT_PACK4) {
-            uint32_t w = 0;
+            // LUT codes of a <=16-level table are < 16 already
+            uint32_t w[N / 8];
 #pragma unroll
-            for (int j = 0; j < N; ++j) w |= (c[j] & 0xFu) << (4 * j);
-            if (N == 8) __stcs(reinterpret_cast<uint32_t*>(codes8 + vi * 4), w);
-            else *reinterpret_cast<uint16_t*>(codes8 + vi * 2) = (uint16_t)w;
+            for (int g = 0; g < N / 8; ++g) {
+                uint32_t acc = c[8 * g];
+#pragma unroll
+                for (int j = 1; j < 8; ++j) acc = c[8 * g + j] * (1u << (4 * j)) + acc;
+                w[g] = acc;
+            }
+            if (N == 16) __stcs(reinterpret_cast<uint2*>(codes8 + ci * 8), make_uint2(w[0], w[(N / 8) - 1]));
+            else __stcs(reinterpret_cast<uint32_t*>(codes8 + ci * 4), w[0]);
         } else {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(codes8 + vi * N);
+            uint32_t w[N / 4];
 #pragma unroll
-            for (int k = 0; k < N / 4; ++k)
-                __stcs(dst + k, c[4 * k] | (c[4 * k + 1] << 8) | (c[4 * k + 2] << 16) | (c[4 * k + 3] << 24));
+            for (int g = 0; g < N / 4; ++g)
+                w[g] = ((c[4 * g + 3] * 256u + c[4 * g + 2]) * 256u + c[4 * g + 1]) * 256u + c[4 * g];
+            if (N == 16) __stcs(reinterpret_cast<uint4*>(codes8 + ci * 16), make_uint4(w[0], w[1], w[2 % (N / 4)], w[3 % (N / 4)]));
+            else __stcs(reinterpret_cast<uint2*>(codes8 + ci * 8), make_uint2(w[0], w[1]));
         }
     }
 }

@@ -116,9 +116,9 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
         else ft.lut8 = reinterpret_cast<const uint8_t*>(smem);
         __syncthreads();
     }
-    constexpr int N = sizeof(T) == 2 ? 8 : 4;
+    constexpr int N = sizeof(T) == 2 ? 16 : 8;   // elements per 32-byte chunk
     const int gs = p.group_shift;
-    const uint32_t tile_vecs = blockDim.x * U;
+    const uint32_t tile_chunks = blockDim.x * U;
     const bool refine = p.allow_refine != 0;
 
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
         float* scale_f32;
         int8_t* exp_e8;
         uint8_t* codes8;
-        uint32_t nvec, v0;
+        uint32_t nchunk, c0;
         if (p.n_items == 1) {
             in = reinterpret_cast<const T*>(p.single.in);
             out_scale = reinterpret_cast<T*>(p.single.out_scale);
@@ -136,8 +136,8 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             scale_f32 = p.single.scale_f32;
             exp_e8 = p.single.exp_e8;
             codes8 = p.single.codes;
-            nvec = (uint32_t)(p.single.n / N);
-            v0 = (uint32_t)tile * tile_vecs + threadIdx.x;
+            nchunk = (uint32_t)(p.single.n / N);
+            c0 = (uint32_t)tile * tile_chunks + threadIdx.x;
         } else {
             int lo = 0, hi = p.n_items;
             while (hi - lo > 1) {
@@ -151,26 +151,26 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             scale_f32 = it->scale_f32;
             exp_e8 = it->exp_e8;
             codes8 = it->codes;
-            nvec = (uint32_t)(it->n / N);
-            v0 = (uint32_t)(tile - __ldg(p.tile_prefix + lo)) * tile_vecs + threadIdx.x;
+            nchunk = (uint32_t)(it->n / N);
+            c0 = (uint32_t)(tile - __ldg(p.tile_prefix + lo)) * tile_chunks + threadIdx.x;
         }
-        Raw<T> x[U];
+        Chunk x[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t vi = v0 + u * blockDim.x;
-            if (vi < nvec) x[u].load_stream(in + (size_t)vi * N);
+            const uint32_t ci = c0 + u * blockDim.x;
+            if (ci < nchunk) x[u].load(in + (size_t)ci * N);
             else x[u].zero();
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t vi = v0 + u * blockDim.x;
-            uint32_t min_nz;
-            uint32_t m = raw_amax<T>(x[u], min_nz);
+            const uint32_t ci = c0 + u * blockDim.x;
+            bool safe;
+            uint32_t m = chunk_amax<T>(x[u], safe);
             for (int o = 1; o < (1 << gs); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-            if (vi >= nvec) continue;
+            if (ci >= nchunk) continue;
             const float s = fast_scale<T, RULE>(p.rule, m);
-            if ((vi & ((1u << gs) - 1u)) == 0) {
-                const uint32_t b = vi >> gs;
+            if ((ci & ((1u << gs) - 1u)) == 0) {
+                const uint32_t b = ci >> gs;
                 if (OUT == OUT_FLOAT) {
                     store_one<T>(out_scale + b, s);
                 } else {
@@ -178,14 +178,14 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
                     if (RULE == 1 && exp_e8) exp_e8[b] = (int8_t)scale_exponent(s);
                 }
             }
-            fast_vector<T, TK, OUT, SM>(ft, x[u], s, min_nz, refine, (size_t)vi, out_codes, codes8);
+            fast_chunk<T, TK, OUT, SM>(ft, x[u], s, refine && safe, (size_t)ci, out_codes, codes8);
         }
     }
 }
 
 template <typename T, int RULE, int TK, int OUT, bool SM>
 int launch_fast2(const FastParams& p, int threads, int blocks, size_t smem, cudaStream_t st) {
-    auto k = mx_fast2_kernel<T, RULE, TK, OUT, SM, 4>;
+    auto k = mx_fast2_kernel<T, RULE, TK, OUT, SM, 2>;
     if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<blocks, threads, smem, st>>>(p);
     VQ_LAUNCH_CHECK("mx_fast2_kernel");
@@ -233,7 +233,7 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     else if (table->kind == VQ_TABLE_LUT16 && table->nan_uniform && table->lut16) tk = TK_LUT;
     else return 0;
     if (scale_table && scale_table->kind == VQ_TABLE_RUNS) return 0;
-    const int N = dtype == VQ_F32 ? 4 : 8;
+    const int N = dtype == VQ_F32 ? 8 : 16;   // elements per 32-byte chunk
     if (block % N) return 0;
     const int64_t g = block / N;
     if (g > 32 || (g & (g - 1))) return 0;
@@ -251,8 +251,8 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
         else return 0;
         if (out >= 0 && o != out) return 0;
         if (it.exp_e8 && !pow2) return 0;
-        if (it.n % block || it.n >= (1ll << 31) || (uintptr_t)it.in % 16 || (uintptr_t)it.out_codes % 16 ||
-            (uintptr_t)it.codes % 8 || (uintptr_t)it.scale_f32 % 4)
+        if (it.n % block || it.n >= (1ll << 31) || (uintptr_t)it.in % 32 || (uintptr_t)it.out_codes % 32 ||
+            (uintptr_t)it.codes % 16 || (uintptr_t)it.scale_f32 % 4)
             return 0;
         out = o;
         total += it.n;
@@ -276,7 +276,7 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
 
     const bool big = total >= (1ll << 22);
     const int threads = big ? 1024 : 128;
-    const int64_t tile_elems = (int64_t)threads * 4 * N;
+    const int64_t tile_elems = (int64_t)threads * 2 * N;
     if (n_items == 1) {
         p.single = items[0];
         p.n_tiles = (items[0].n + tile_elems - 1) / tile_elems;
