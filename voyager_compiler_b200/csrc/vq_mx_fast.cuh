@@ -64,21 +64,36 @@ __device__ __forceinline__ float rcp_approx(float s) {
 // chunk: no non-zero element below 2^-60 (pattern 0x2180).
 template <typename T>
 __device__ __forceinline__ uint32_t chunk_amax(const Chunk& x, bool& safe);
+// max(|a|, |b|) / min(|a|, |b|) per bf16 half; the sign bit of the result is garbage (xor of the
+// input signs) and is masked off at the end.  .NaN: a NaN input gives NaN (0x7FFF), as torch.max.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t absmin_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("min.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 template <>
 __device__ __forceinline__ uint32_t chunk_amax<bf16_t>(const Chunk& x, bool& safe) {
-    uint32_t a[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) a[k] = x.w[k] & 0x7FFF7FFFu;
-    uint32_t mx = __vmaxu2(__vmaxu2(__vmaxu2(a[0], a[1]), __vmaxu2(a[2], a[3])),
-                           __vmaxu2(__vmaxu2(a[4], a[5]), __vmaxu2(a[6], a[7])));
-    uint32_t mn = __vminu2(__vminu2(__vminu2(a[0], a[1]), __vminu2(a[2], a[3])),
-                           __vminu2(__vminu2(a[4], a[5]), __vminu2(a[6], a[7])));
+    const uint32_t* w = x.w;
+    uint32_t mx = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(w[0], w[1]), absmax_bf16x2(w[2], w[3])),
+                                absmax_bf16x2(absmax_bf16x2(w[4], w[5]), absmax_bf16x2(w[6], w[7])));
+    uint32_t mn = absmin_bf16x2(absmin_bf16x2(absmin_bf16x2(w[0], w[1]), absmin_bf16x2(w[2], w[3])),
+                                absmin_bf16x2(absmin_bf16x2(w[4], w[5]), absmin_bf16x2(w[6], w[7])));
+    mx &= 0x7FFF7FFFu;
+    mn &= 0x7FFF7FFFu;
+    // smallest magnitude at least 2^-60 (pattern 0x2180): the reciprocal path is exact.  A NaN makes
+    // the minimum unreliable, but then the block scale is 1 (a power of two) and the path is unused.
     safe = min(mn & 0xFFFFu, mn >> 16) >= 0x2180u;
     if (!safe) {
         // zeros are harmless: look at the smallest NON-zero magnitude (0 - 1 wraps to 0xFFFF)
         uint32_t t = 0xFFFFFFFFu;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) t = __vminu2(t, __vsub2(a[k], 0x00010001u));
+        for (int k = 0; k < 8; ++k) t = __vminu2(t, __vsub2(w[k] & 0x7FFF7FFFu, 0x00010001u));
         safe = min(t & 0xFFFFu, t >> 16) >= 0x217Fu;
     }
     return max(mx & 0xFFFFu, mx >> 16) << 16;

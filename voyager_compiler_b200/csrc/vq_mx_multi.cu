@@ -96,6 +96,7 @@ struct FastParams {
     TableDev tab;
     int group_shift;
     int allow_refine;
+    int iters;                   // inner iterations per tile (one tensor lookup per tile)
 };
 
 template <typename T, int RULE, int TK, int OUT, bool SM, int U>
@@ -118,7 +119,8 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
     }
     constexpr int N = sizeof(T) == 2 ? 16 : 8;   // elements per 32-byte chunk
     const int gs = p.group_shift;
-    const uint32_t tile_chunks = blockDim.x * U;
+    const uint32_t sub_chunks = blockDim.x * U;               // chunks per inner iteration
+    const uint32_t tile_chunks = sub_chunks * p.iters;     // chunks per tile (one tensor lookup)
     const bool refine = p.allow_refine != 0;
 
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
@@ -154,6 +156,8 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             nchunk = (uint32_t)(it->n / N);
             c0 = (uint32_t)(tile - __ldg(p.tile_prefix + lo)) * tile_chunks + threadIdx.x;
         }
+        for (int iter = 0; iter < p.iters; ++iter, c0 += sub_chunks) {
+        if (c0 - threadIdx.x >= nchunk) break;              // uniform across the CTA
         Chunk x[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -179,6 +183,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
                 }
             }
             fast_chunk<T, TK, OUT, SM>(ft, x[u], s, refine && safe, (size_t)ci, out_codes, codes8);
+        }
         }
     }
 }
@@ -276,7 +281,12 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
 
     const bool big = total >= (1ll << 22);
     const int threads = big ? 1024 : 128;
-    const int64_t tile_elems = (int64_t)threads * 2 * N;
+    const int sms = vq_sm_count();
+    // tiles large enough to amortise the per-tile tensor lookup, small enough for >= 8 tiles per SM
+    int64_t iters = total / ((int64_t)threads * 2 * N * sms * 8);
+    iters = iters < 1 ? 1 : (iters > 8 ? 8 : iters);
+    p.iters = (int)iters;
+    const int64_t tile_elems = (int64_t)threads * 2 * N * iters;
     if (n_items == 1) {
         p.single = items[0];
         p.n_tiles = (items[0].n + tile_elems - 1) / tile_elems;
@@ -296,7 +306,6 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     }
     const bool sm = big && tk == TK_LUT;
     const size_t smem = sm ? (out == OUT_FLOAT ? 131072 : 65536) : 0;
-    const int sms = vq_sm_count();
     const int64_t cap = big ? sms : (int64_t)sms * 8;
     const int blocks = (int)(p.n_tiles < cap ? p.n_tiles : cap);
     int rc = (dtype == VQ_F32) ? dispatch_rule<float>(p, pow2, tk, out, sm, threads, blocks, smem, st)
