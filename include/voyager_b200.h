@@ -184,6 +184,24 @@ VQ_API int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype,
                                 const vq_table* table, int code_bits, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/* Y[M,N] = A[M,K] @ B[N,K]^T (+ bias[N]); A, B, bias, Y bf16, fp32 accumulation on the tensor
+ * cores, operands fetched by TMA.  K must be a multiple of 8.  `status` (device int32, may be
+ * NULL, zeroed by the caller) receives a non-zero code if a bounded wait inside the kernel ran out.
+ * This is the contraction `aten.linear` performs inside linear_mx / matmul_mx
+ * (src/voyager_compiler/ops/quantized.py:330-333, 404-406). */
+VQ_API int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int64_t M, int64_t N, int64_t K,
+                           int32_t* status, void* stream);
+
+/* Y[M,N] = (a_codes * expand(a_scale))[M,K] @ (b_codes * expand(b_scale))[N,K]^T (+ bias), all
+ * tensors bf16, scales [rows, K/block] with blocks along K; each product code*scale is rounded to
+ * bf16 once, as the bf16 tensor arithmetic of the reference does, inside the operand staging of
+ * the GEMM (no dequantised copy is written).  block must be 32 and K a multiple of 64, otherwise
+ * VQ_ERR_UNSUPPORTED.  Replaces `linear_mx`, src/voyager_compiler/ops/quantized.py:295-348
+ * (weight_layout "kc", no codebooks, no sparse side path). */
+VQ_API int vq_linear_mx(const void* a_codes, const void* a_scale, const void* b_codes, const void* b_scale,
+                        const void* bias, void* Y, int64_t M, int64_t N, int64_t K, int64_t block, int32_t* status,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

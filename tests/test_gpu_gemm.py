@@ -1,0 +1,110 @@
+"""tcgen05 GEMM: plain (TMA-fed) and fused-dequant variants against torch / the CPU oracle."""
+import os
+import sys
+
+import pytest
+import torch
+
+import voyager_compiler_b200 as vb
+from voyager_compiler_b200 import _lib, gemm_native
+from golden_util import golden_table
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import voyager_oracle as vo  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+Q = torch.ops.quantized_ops
+
+
+def _rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return ((a - b).norm() / b.norm()).item()
+
+
+def _plain(a, b, bias=None):
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    st = torch.zeros(1, dtype=torch.int32, device=a.device)
+    rc = _lib.lib.vq_gemm_bf16_tn(a.data_ptr(), b.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                  out.data_ptr(), M, N, K, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "gemm")
+    torch.cuda.synchronize()
+    assert st.item() == 0, f"kernel reported a wait that ran out: {st.item()}"
+    return out
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 768, 4096), (100, 200, 72),
+                                   (1, 8, 8), (130, 257, 136), (1024, 2816, 512)])
+def test_plain_gemm_matches_fp32_reference(M, N, K):
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    got = _plain(a, b)
+    ref = a.float() @ b.float().t()           # plain fp32 reference of the same contraction
+    assert _rel(got, ref) <= 4e-3             # bf16 output rounding only (2^-9 per element)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    got = _plain(a, b, bias)
+    assert _rel(got, ref + bias.float()) <= 4e-3
+
+
+def test_plain_gemm_exact_on_small_integers():
+    """Integer-valued operands: every product and partial sum is exact in fp32, so any wrong
+    descriptor, swizzle or accumulate flag shows up as an exact mismatch."""
+    torch.manual_seed(0)
+    a = torch.randint(-3, 4, (256, 192), device="cuda").to(torch.bfloat16)
+    b = torch.randint(-3, 4, (512, 192), device="cuda").to(torch.bfloat16)
+    got = _plain(a, b)
+    ref = (a.float() @ b.float().t()).to(torch.bfloat16)
+    assert torch.equal(got, ref)
+
+
+def _mx_operands(M, N, K, seed=4):
+    torch.manual_seed(seed)
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.02).to(torch.bfloat16)
+    q = golden_table("int8")
+    xs, xq = vo.quantize_mx(x, q, (-1,), 32, 127.0, True)
+    ws, wq = vo.quantize_mx(w, q, (-1,), 32, 127.0, True)
+    return xq, xs, wq, ws
+
+
+@pytest.mark.parametrize("mode", ["fused", "plain"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 256, 512), (300, 1000, 1024), (2048, 2816, 4096)])
+def test_linear_mx_against_oracle(mode, M, N, K):
+    xq, xs, wq, ws = _mx_operands(M, N, K)
+    want = vo.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32)
+    os.environ["VOYAGER_B200_GEMM"] = mode
+    try:
+        got = Q.linear_mx(xq.cuda(), wq.cuda(), None, input_scale=xs.cuda(), weight_scale=ws.cuda(), block_size=32)
+        torch.cuda.synchronize()
+    finally:
+        del os.environ["VOYAGER_B200_GEMM"]
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.dtype == torch.bfloat16 and got.shape == want.shape
+    assert _rel(got, want) <= 1e-2            # tolerance for the bf16 / fp32-accumulate linear
+
+
+def test_fused_equals_plain_bitwise():
+    """int8 x 2^e is exact in bf16, so the fused staging must build the very same operands as
+    the dequantize kernel; same MMA order -> identical results."""
+    xq, xs, wq, ws = _mx_operands(512, 768, 2048, seed=9)
+    outs = {}
+    for mode in ("fused", "plain"):
+        os.environ["VOYAGER_B200_GEMM"] = mode
+        try:
+            outs[mode] = Q.linear_mx(xq.cuda(), wq.cuda(), None, input_scale=xs.cuda(), weight_scale=ws.cuda(), block_size=32)
+        finally:
+            del os.environ["VOYAGER_B200_GEMM"]
+    torch.cuda.synchronize()
+    assert torch.equal(outs["fused"], outs["plain"])
+
+
+def test_fused_with_bias_and_3d_input():
+    xq, xs, wq, ws = _mx_operands(6 * 50, 320, 256, seed=11)
+    bias = torch.randn(320).to(torch.bfloat16)
+    x3, s3 = xq.reshape(6, 50, 256), xs.reshape(6, 50, 8)
+    want = vo.linear_mx(x3, wq, bias, input_scale=s3, weight_scale=ws, block_size=32)
+    got = Q.linear_mx(x3.cuda(), wq.cuda(), bias.cuda(), input_scale=s3.cuda(), weight_scale=ws.cuda(), block_size=32)
+    assert got.shape == (6, 50, 320) and _rel(got, want) <= 1e-2
+    assert gemm_native.gemm_status("cuda") == 0

@@ -1,10 +1,82 @@
-"""Binding of the tcgen05 MX GEMM kernel (filled in with the kernel)."""
+"""Binding of the tcgen05 MX GEMM kernels (``vq_linear_mx`` fused, ``vq_gemm_bf16_tn`` plain)."""
 from __future__ import annotations
+
+import os
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+
+_status: Dict[str, torch.Tensor] = {}
+
+
+def _status_tensor(device) -> torch.Tensor:
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def gemm_status(device="cuda") -> int:
+    """Non-zero when a bounded wait inside a GEMM kernel on ``device`` ran out since the last
+    call (1 producer, 2 MMA issuer, 3 epilogue).  Synchronises the device and clears the flag."""
+    t = _status_tensor(torch.device(device) if not isinstance(device, torch.device) else device)
+    v = int(t.item())
+    t.zero_()
+    return v
+
+
+def _mode() -> str:
+    return os.environ.get("VOYAGER_B200_GEMM", "fused")
+
+
+def _is_rows_by_kblocks(scale, rows, K, block) -> bool:
+    return scale is not None and scale.dtype == torch.bfloat16 and tuple(scale.shape) == (rows, K // block)
 
 
 def native_supported(a, b, bias, a_scale, b_scale, block_size, a_code, b_code, b_is_nk) -> bool:
-    return False
+    if _mode() == "cublas" or not b_is_nk:
+        return False
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or b.ndim != 2 or a.ndim < 1:
+        return False
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.ndim != 1 or bias.shape[0] != b.shape[0]):
+        return False
+    K = a.shape[-1]
+    return K == b.shape[1] and K % 8 == 0 and K > 0
 
 
 def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
-    raise NotImplementedError
+    from . import ops
+
+    K = a.shape[-1]
+    N = b.shape[0]
+    lead = a.shape[:-1]
+    M = 1
+    for d in lead:
+        M *= d
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    if M == 0 or N == 0:
+        return out.reshape(*lead, N)
+    a2 = a.reshape(M, K)
+    a_sc2 = a_scale.reshape(M, -1) if a_scale is not None and a_scale.ndim >= 2 else a_scale
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    bias_c = bias.contiguous() if bias is not None else None
+    with torch.cuda.device(a.device):
+        st = _status_tensor(a.device)
+        fused = (_mode() == "fused" and a_code is None and b_code is None and block_size == 32 and K % 64 == 0
+                 and _is_rows_by_kblocks(a_sc2, M, K, 32) and _is_rows_by_kblocks(b_scale, N, K, 32))
+        if fused:
+            ac, bc = a2.contiguous(), b.contiguous()
+            asc, bsc = a_sc2.contiguous(), b_scale.contiguous()
+            rc = _lib.lib.vq_linear_mx(ac.data_ptr(), asc.data_ptr(), bc.data_ptr(), bsc.data_ptr(),
+                                       bias_c.data_ptr() if bias_c is not None else None, out.data_ptr(), M, N, K, 32,
+                                       st.data_ptr(), stream)
+            _lib.check(rc, "linear_mx")
+        else:
+            da = ops._decode_operand("linear_mx", a2, a_code, a_sc2, block_size).contiguous()
+            db = ops._decode_operand("linear_mx", b, b_code, b_scale, block_size).contiguous()
+            rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                          out.data_ptr(), M, N, K, st.data_ptr(), stream)
+            _lib.check(rc, "linear_mx")
+    return out.reshape(*lead, N)
