@@ -293,6 +293,64 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_linear(args):
+    """cfg5: MX-quantized linear, X[8192,4096] x W[11008,4096]^T, MXINT8 block 32 (single GPU).
+    Times the quantize_mx of the activations, the fused GEMM, the plain GEMM (dequantize kernels +
+    TMA-fed GEMM) and the vendor bf16 GEMM on pre-dequantised operands for comparison."""
+    import torch
+    import voyager_compiler_b200 as vb
+    from voyager_compiler_b200 import gemm_native
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    M, N, K = args.m, 11008, 4096
+    g = torch.Generator(device=dev); g.manual_seed(4)
+    x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    Q = torch.ops.quantized_ops
+    qmap = torch.from_numpy(vb.tables.build_table("int8").view("int16").copy()).view(torch.bfloat16).to(dev)
+    ws, wq = Q.quantize_mx(w, qmap, (-1,), 32, 127.0, True)
+    xs, xq = Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True)
+    flops = 2.0 * M * N * K
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts), min(ts)
+
+    res = {}
+    sampler = ClockSampler(dev.index or 0); sampler.start()
+    for mode in ("fused", "plain"):
+        os.environ["VOYAGER_B200_GEMM"] = mode
+        med, best = timed(lambda: Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32), args.steps)
+        res[mode] = {"ms": med, "tflops": flops / med / 1e9, "best_tflops": flops / best / 1e9}
+    os.environ.pop("VOYAGER_B200_GEMM", None)
+    xd, wd = Q.dequantize(xq, xs, None, (-1,), 32), Q.dequantize(wq, ws, None, (-1,), 32)
+    med, best = timed(lambda: torch.nn.functional.linear(xd, wd), args.steps)
+    res["vendor_bf16_gemm_only"] = {"ms": med, "tflops": flops / med / 1e9, "best_tflops": flops / best / 1e9}
+    med, best = timed(lambda: Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True), args.steps)
+    res["quantize_mx_activations"] = {"ms": med, "gbs": (x.numel() * (2 + 2 + 2 / 32)) / med / 1e6}
+    med, best = timed(lambda: Q.linear_mx(Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True)[1], wq, None, input_scale=xs,
+                                          weight_scale=ws, block_size=32), args.steps)
+    res["quantize_plus_fused_linear"] = {"ms": med, "tflops": flops / med / 1e9}
+    clocks = sampler.stop()
+    peaks, kind = measured_peaks()
+    ok = gemm_native.gemm_status(dev) == 0
+    print(json.dumps({"workload": f"cfg5: MX linear M={M} N={N} K={K} MXINT8 block 32", "results": res, "clocks": clocks,
+                      "status_ok": ok, "peak_bf16_tflops": peaks.get("bf16_tflops"),
+                      "peak_bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"), "peak_kind": kind,
+                      "frac_fused_of_burst_peak": res["fused"]["tflops"] / peaks.get("bf16_tflops", 1590.0)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -301,7 +359,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="fewer than 32: reduced model for profiler captures")
     ap.add_argument("--kernel-only", action="store_true", help="device-timed part only (profiler captures)")
+    ap.add_argument("--workload", default="model", choices=["model", "linear"],
+                    help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
+    ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
     args = ap.parse_args()
+    if args.workload == "linear":
+        run_linear(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -28,7 +28,11 @@ def gemm_status(device="cuda") -> int:
 
 
 def _mode() -> str:
-    return os.environ.get("VOYAGER_B200_GEMM", "fused")
+    """``plain`` (default): operands dequantised by this package's dequantize kernel, then the
+    TMA-fed tcgen05 GEMM.  ``fused``: dequantisation inside the GEMM's operand staging (no
+    dequantised copy in HBM; slower on a one-CTA 128x256 tile because the staging warps cannot keep
+    enough loads in flight).  ``cublas``: dequantize kernel + the vendor GEMM (for A/B timing)."""
+    return os.environ.get("VOYAGER_B200_GEMM", "plain")
 
 
 def _is_rows_by_kblocks(scale, rows, K, block) -> bool:
