@@ -202,6 +202,25 @@ VQ_API int vq_linear_mx(const void* a_codes, const void* a_scale, const void* b_
                         const void* bias, void* Y, int64_t M, int64_t N, int64_t K, int64_t block, int32_t* status,
                         void* stream);
 
+/* vq_quantize_mx_multi without a caller workspace and without any allocation.  This entry point has
+ * no counterpart in the reference; it exists for callers that must not allocate device memory where
+ * they quantize (a plug-in running inside another framework's closed memory pool, a serving loop
+ * that sized all buffers at start-up, a thread that may not take the allocator lock).  The tensor
+ * descriptors are staged in a fixed array inside the library, so:
+ *   - at most vq_quantize_mx_multi_static_max_items() tensors (1024) per call; more is rejected
+ *     with VQ_ERR_INVALID;
+ *   - the first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture;
+ *   - all calls on a device share the array: calls whose GPU work can overlap (different streams,
+ *     or threads racing on one stream) overwrite each other's descriptors.  Serialise them.  Nothing
+ *     in the array has to be cleared between calls; each call rewrites what it uses.
+ * No cudaMalloc / cudaFree or other allocating routine is called; inputs and outputs are the caller's. */
+VQ_API int vq_quantize_mx_multi_static_max_items(void);
+VQ_API int vq_quantize_mx_multi_static(const vq_mx_item* items, int n_items, int dtype, int64_t block,
+                                       double quant_max, int pow2, const vq_exp_tables* exp,
+                                       const vq_table* scale_table, const vq_table* table, int code_bits,
+                                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

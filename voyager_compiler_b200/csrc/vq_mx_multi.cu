@@ -431,3 +431,50 @@ int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of vq_quantize_mx_multi.
+//
+// Some callers cannot allocate device memory at the point where they quantize: a plug-in that
+// runs inside a host framework's forward pass under a closed memory pool, a serving loop that
+// pre-sized everything at start-up, a driver thread that must not take the allocator lock.  For
+// them the descriptor workspace the multi-tensor kernel needs lives in a fixed device array inside
+// this library instead of a caller-provided buffer.  Every device that loads the library holds
+// the array (about 72 KB) until the process exits.
+#define VQ_STATIC_MAX_ITEMS 1024
+static __device__ __align__(256) unsigned char g_static_workspace[VQ_STATIC_MAX_ITEMS * sizeof(vq_mx_item) +
+                                                                  (VQ_STATIC_MAX_ITEMS + 1) * sizeof(int64_t)];
+
+namespace {
+// In host code `g_static_workspace` is only a stand-in for the device symbol; the address kernels
+// may use is looked up per device, once, with that device current.
+void* g_static_ws_ptr[64] = {};
+}  // namespace
+
+extern "C" {
+
+int vq_quantize_mx_multi_static_max_items(void) { return VQ_STATIC_MAX_ITEMS; }
+
+int vq_quantize_mx_multi_static(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max,
+                                int pow2, const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table,
+                                int code_bits, void* stream) {
+    const char* name = "vq_quantize_mx_multi_static";
+    VQ_REQUIRE(n_items >= 0, "%s: negative item count", name);
+    if (n_items > VQ_STATIC_MAX_ITEMS)
+        return vq_set_error(VQ_ERR_INVALID, "%s: %d tensors exceed the built-in workspace (at most %d per call); "
+                            "split the call or use vq_quantize_mx_multi with your own workspace", name, n_items,
+                            VQ_STATIC_MAX_ITEMS);
+    int dev = -1;
+    VQ_CUDA(cudaGetDevice(&dev));
+    VQ_REQUIRE(dev >= 0 && dev < 64, "%s: device ordinal %d is outside the supported range", name, dev);
+    if (!g_static_ws_ptr[dev]) {
+        // first call on this device: resolve the device address of the array (no allocation)
+        void* p = nullptr;
+        VQ_CUDA(cudaGetSymbolAddress(&p, g_static_workspace));
+        g_static_ws_ptr[dev] = p;
+    }
+    return vq_quantize_mx_multi(items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits,
+                                g_static_ws_ptr[dev], sizeof(g_static_workspace), stream);
+}
+
+}  // extern "C"
