@@ -345,6 +345,41 @@ def run_linear(args):
     clocks = sampler.stop()
     peaks, kind = measured_peaks()
     ok = gemm_native.gemm_status(dev) == 0
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # column-sharded linear: every rank owns a slice of W's rows, X is replicated, Y is all-gathered
+        import torch.distributed as dist
+        from voyager_compiler_b200 import parallel as par
+        dist.init_process_group("nccl", device_id=dev)
+        rank = dist.get_rank()
+        wq_r, ws_r = par.shard_weight(wq, ws, rank, world)
+
+        def timed_dist(fn, iters):
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(iters):
+                flush.zero_()
+                dist.barrier(); torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ts.append(float(t.item()))
+            return statistics.median(ts)
+
+        ms_local = timed_dist(lambda: Q.linear_mx(xq, wq_r, None, input_scale=xs, weight_scale=ws_r, block_size=32), args.steps)
+        ms_full = timed_dist(lambda: par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32), args.steps)
+        y = par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32)
+        y1 = Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32)
+        same = bool(torch.equal(y, y1))
+        res[f"column_parallel_{world}gpu"] = {"gemm_only_ms": ms_local, "gemm_only_tflops": flops / ms_local / 1e9,
+                                              "gemm_plus_allgather_ms": ms_full, "tflops": flops / ms_full / 1e9,
+                                              "shards": par.column_shards(N, world), "equals_single_gpu_result": same}
+        dist.destroy_process_group()
+        if rank != 0:
+            return
     print(json.dumps({"workload": f"cfg5: MX linear M={M} N={N} K={K} MXINT8 block 32", "results": res, "clocks": clocks,
                       "status_ok": ok, "peak_bf16_tflops": peaks.get("bf16_tflops"),
                       "peak_bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"), "peak_kind": kind,
