@@ -33,8 +33,9 @@ BLOCK = 64
 LAYER = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
 WORKLOAD = "cfg3: NF4 block-64 quantization of LLaMA-2-7B-shaped linear weights (225 bf16 tensors)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one mx_multi_kernel launch over the full
-# single-GPU workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# single-GPU workload: the 1-layer ncu capture summarised in profiles/mx_fast2_kernel_nf4_1layer.md
+# (500.5 MB) scaled by the elements processed; traffic grows in proportion to them.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 16.34e9
 
 
 def model_shapes(layers=32):
@@ -277,7 +278,7 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "mx_fast2_kernel<bf16, amax, LUT, pack4>", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * my_elems / total_elems,
                          "algorithmic_bytes_per_launch": my_elems * BYTES_PER_ELEM, "launch_ms": kernel_ms},
         }
         if world == 1:
@@ -341,7 +342,7 @@ def run_linear(args):
     res["quantize_mx_activations"] = {"ms": med, "gbs": (x.numel() * (2 + 2 + 2 / 32)) / med / 1e6}
     med, best = timed(lambda: Q.linear_mx(Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True)[1], wq, None, input_scale=xs,
                                           weight_scale=ws, block_size=32), args.steps)
-    res["quantize_plus_fused_linear"] = {"ms": med, "tflops": flops / med / 1e9}
+    res["quantize_plus_linear"] = {"ms": med, "tflops": flops / med / 1e9}
     clocks = sampler.stop()
     peaks, kind = measured_peaks()
     ok = gemm_native.gemm_status(dev) == 0
