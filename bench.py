@@ -378,6 +378,16 @@ def run_linear(args):
         res[f"column_parallel_{world}gpu"] = {"gemm_only_ms": ms_local, "gemm_only_tflops": flops / ms_local / 1e9,
                                               "gemm_plus_allgather_ms": ms_full, "tflops": flops / ms_full / 1e9,
                                               "shards": par.column_shards(N, world), "equals_single_gpu_result": same}
+        try:
+            p2p = par.P2PColumnParallelLinearMX(wq_r, ws_r, N, 32, M)
+            ms_p2p = timed_dist(lambda: p2p(xq, xs), args.steps)
+            y2 = p2p(xq, xs)
+            torch.cuda.synchronize()
+            res[f"p2p_fused_gather_{world}gpu"] = {"ms": ms_p2p, "tflops": flops / ms_p2p / 1e9,
+                                                   "equals_single_gpu_result": bool(torch.equal(y2, y1)),
+                                                   "status_ok": p2p.status() == 0}
+        except Exception as e:  # noqa: BLE001  (symmetric memory may be unavailable on a given box)
+            res[f"p2p_fused_gather_{world}gpu"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         dist.destroy_process_group()
         if rank != 0:
             return

@@ -192,6 +192,15 @@ VQ_API int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype,
 VQ_API int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int64_t M, int64_t N, int64_t K,
                            int32_t* status, void* stream);
 
+/* The same GEMM writing its [M,N] result into columns [col_offset, col_offset+N) of EVERY buffer in
+ * Ys (n_outputs <= 8 device pointers, rows ldy elements apart): a rank of a column-sharded linear
+ * passes its own output and its peers' (peer-mapped memory), so the all-gather of the reference-side
+ * composition happens as plain stores over NVLink inside the GEMM epilogue.  The caller orders the
+ * launch against the peers (a barrier before reuse of Y, another before reading it). */
+VQ_API int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bias, void* const* Ys, int n_outputs,
+                                   int64_t ldy, int64_t col_offset, int64_t M, int64_t N, int64_t K,
+                                   int32_t* status, void* stream);
+
 /* Y[M,N] = (a_codes * expand(a_scale))[M,K] @ (b_codes * expand(b_scale))[N,K]^T (+ bias), all
  * tensors bf16, scales [rows, K/block] with blocks along K; each product code*scale is rounded to
  * bf16 once, as the bf16 tensor arithmetic of the reference does, inside the operand staging of

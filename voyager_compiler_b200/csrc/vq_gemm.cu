@@ -29,8 +29,13 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int PRODUCER_WARPS_FUSED = 8;
 constexpr long long WAIT_BUDGET = 4000000000ll;   // ~2 s of SM clocks
 
+constexpr int MAX_OUTPUTS = 8;
+
 struct GemmParams {
-    uint16_t* Y;
+    uint16_t* Y[MAX_OUTPUTS];   // every output buffer receives the same tile (own memory and peers')
+    int n_outputs;
+    int64_t ldy;                // elements between rows of the output buffers
+    int64_t col_offset;         // first output column this launch owns
     const uint16_t* bias;
     int M, N, K;
     int tiles_m, tiles_n;
@@ -235,14 +240,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(hi), "f"(lo));
                     }
-                    uint16_t* dst = p.Y + (size_t)row * p.N + col0;
-                    if (col0 + 32 <= p.N && (((size_t)row * p.N + col0) & 7) == 0) {
+                    const size_t off = (size_t)row * p.ldy + p.col_offset + col0;
+                    for (int d = 0; d < p.n_outputs; ++d) {       // own buffer, then peers over NVLink
+                        uint16_t* dst = p.Y[d] + off;
+                        if (col0 + 32 <= p.N && (off & 7) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-                            dst[j] = (uint16_t)((j & 1) ? (o[j >> 1] >> 16) : (o[j >> 1] & 0xFFFFu));
+                            for (int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                                dst[j] = (uint16_t)((j & 1) ? (o[j >> 1] >> 16) : (o[j >> 1] & 0xFFFFu));
+                        }
                     }
                 }
             }
@@ -320,9 +328,19 @@ extern "C" {
 
 int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int64_t M, int64_t N, int64_t K,
                     int32_t* status, void* stream) {
-    const char* name = "vq_gemm_bf16_tn";
+    void* ys[1] = {Y};
+    return vq_gemm_bf16_tn_scatter(A, B, bias, ys, 1, N, 0, M, N, K, status, stream);
+}
+
+int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bias, void* const* Ys, int n_outputs, int64_t ldy,
+                            int64_t col_offset, int64_t M, int64_t N, int64_t K, int32_t* status, void* stream) {
+    const char* name = "vq_gemm_bf16_tn_scatter";
     VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative size", name);
     if (M == 0 || N == 0) return 0;
+    VQ_REQUIRE(Ys && n_outputs >= 1 && n_outputs <= MAX_OUTPUTS, "%s: 1..%d output buffers", name, MAX_OUTPUTS);
+    VQ_REQUIRE(ldy >= col_offset + N && col_offset >= 0, "%s: the column range does not fit the output row", name);
+    void* Y = Ys[0];
+    for (int d = 0; d < n_outputs; ++d) VQ_REQUIRE(Ys[d] != nullptr, "%s: null output buffer %d", name, d);
     VQ_REQUIRE(A && B && Y, "%s: null pointer", name);
     VQ_REQUIRE(K > 0 && K % 8 == 0, "%s: K must be a positive multiple of 8 (16-byte rows)", name);
     VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "%s: sizes must be below 2^31", name);
@@ -331,7 +349,10 @@ int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int
     if (int rc = make_map(&tmA, A, M, K, BM)) return rc;
     if (int rc = make_map(&tmB, B, N, K, BN)) return rc;
     GemmParams p{};
-    p.Y = reinterpret_cast<uint16_t*>(Y);
+    for (int d = 0; d < n_outputs; ++d) p.Y[d] = reinterpret_cast<uint16_t*>(Ys[d]);
+    p.n_outputs = n_outputs;
+    p.ldy = ldy;
+    p.col_offset = col_offset;
     p.bias = reinterpret_cast<const uint16_t*>(bias);
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.status = status;
@@ -352,7 +373,10 @@ int vq_linear_mx(const void* a_codes, const void* a_scale, const void* b_codes, 
     memset(&tmA, 0, sizeof(tmA));
     memset(&tmB, 0, sizeof(tmB));
     GemmParams p{};
-    p.Y = reinterpret_cast<uint16_t*>(Y);
+    p.Y[0] = reinterpret_cast<uint16_t*>(Y);
+    p.n_outputs = 1;
+    p.ldy = N;
+    p.col_offset = 0;
     p.bias = reinterpret_cast<const uint16_t*>(bias);
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.status = status;

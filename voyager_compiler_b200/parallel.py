@@ -77,3 +77,58 @@ def column_parallel_linear_mx(x_codes, x_scale, w_codes_shard, w_scale_shard, n_
         if b > a:
             out[:, a:b] = recv[r, :, : b - a]
     return out.reshape(*lead, n_total)
+
+
+class P2PColumnParallelLinearMX:
+    """Column-sharded ``linear_mx`` whose all-gather is fused into the GEMM epilogue: the output
+    ``[M, n_total]`` lives in peer-mapped (symmetric) memory on every rank and each rank's GEMM
+    writes its column range into its own copy and into every peer's copy with plain stores over
+    NVLink (``vq_gemm_bf16_tn_scatter``).  Two stream-ordered barriers per call order the writes
+    against the peers' reads.  The weight shard is dequantised once at construction (weights are
+    static); activations are dequantised per call by this package's dequantize kernel."""
+
+    def __init__(self, w_codes_shard, w_scale_shard, n_total: int, block_size: int, max_rows: int, group=None,
+                 bias_shard: Optional[torch.Tensor] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import ops
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.n_total, self.block, self.max_rows = n_total, block_size, max_rows
+        self.n0, self.n1 = column_shards(n_total, self.world)[self.rank]
+        if w_codes_shard.shape[0] != self.n1 - self.n0:
+            raise ValueError("weight shard does not match this rank's column range")
+        if w_codes_shard.dtype != torch.bfloat16:
+            raise NotImplementedError("the peer-to-peer linear takes bfloat16 operands")
+        self.w = ops.dequantize(w_codes_shard, w_scale_shard, None, None, block_size).contiguous()
+        self.bias = bias_shard.contiguous() if bias_shard is not None else None
+        dev = w_codes_shard.device
+        self.y = symm_mem.empty(max_rows, n_total, dtype=torch.bfloat16, device=dev)
+        self.handle = symm_mem.rendezvous(self.y, self.group)
+        ptrs = list(self.handle.buffer_ptrs)
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        import ctypes as C
+        self._ptrs = (C.c_void_p * len(order))(*[ptrs[r] for r in order])
+        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def __call__(self, x_codes, x_scale) -> torch.Tensor:
+        from . import _lib, ops
+        m = x_codes.numel() // x_codes.shape[-1]
+        if m > self.max_rows:
+            raise ValueError(f"{m} rows exceed the {self.max_rows} this object was sized for")
+        k = x_codes.shape[-1]
+        xd = ops.dequantize(x_codes.reshape(m, k), x_scale.reshape(m, -1), None, None, self.block).contiguous()
+        self.handle.barrier(channel=0)        # every rank is done reading the previous result
+        if self.n1 > self.n0:
+            rc = _lib.lib.vq_gemm_bf16_tn_scatter(
+                xd.data_ptr(), self.w.data_ptr(), self.bias.data_ptr() if self.bias is not None else None, self._ptrs,
+                self.world, self.n_total, self.n0, m, self.n1 - self.n0, k, self._status.data_ptr(),
+                torch.cuda.current_stream(xd.device).cuda_stream)
+            _lib.check(rc, "P2PColumnParallelLinearMX")
+        self.handle.barrier(channel=1)        # every rank's column range has landed everywhere
+        return self.y[:m].reshape(*x_codes.shape[:-1], self.n_total)
+
+    def status(self) -> int:
+        v = int(self._status.item())
+        self._status.zero_()
+        return v
