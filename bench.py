@@ -397,6 +397,74 @@ def run_linear(args):
                       "frac_fused_of_burst_peak": res["fused"]["tflops"] / peaks.get("bf16_tflops", 1590.0)}))
 
 
+def run_elementwise(args):
+    """cfg1 / cfg2 / cfg4-shaped element-wise measurements on one GPU (GB/s of algorithmic traffic,
+    L2 flushed between iterations)."""
+    import torch
+    import voyager_compiler_b200 as vb
+    from voyager_compiler_b200 import model_quant as mq
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    Q = torch.ops.quantized_ops
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def tab(name):
+        return torch.from_numpy(vb.tables.build_table(name).view("int16").copy()).view(torch.bfloat16).to(dev)
+
+    def timed(fn, nbytes, iters=args.steps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        med = statistics.median(ts)
+        return {"ms": med, "gbs": nbytes / med / 1e6, "best_gbs": nbytes / min(ts) / 1e6}
+
+    peaks, kind = measured_peaks()
+    res = {}
+    # cfg1: fp32 [4096,4096], outliers, MXINT8 block 32, power-of-two scales
+    g = torch.Generator(device=dev); g.manual_seed(0)
+    x = torch.randn(4096, 4096, generator=g, device=dev)
+    x[torch.rand(4096, 4096, generator=g, device=dev) < 0.001] *= 50
+    n = x.numel()
+    q8 = tab("int8")
+    s, c = Q.quantize_mx(x, q8, (-1,), 32, 127.0, True)
+    res["cfg1_quantize_mx_fp32_dropin"] = timed(lambda: Q.quantize_mx(x, q8, (-1,), 32, 127.0, True), n * (4 + 4 + 4 / 32))
+    res["cfg1_dequantize_fp32"] = timed(lambda: Q.dequantize(c, s, None, (-1,), 32), n * (4 + 4 + 4 / 32))
+    res["cfg1_quantize_mx_packed_int8_e8"] = timed(
+        lambda: mq.quantize_tensors_mx([x], q8, 32, 127.0, True, code_bits=8, want_exp=True), n * (4 + 1 + 4 / 32 + 1 / 32))
+    res["cfg1_calculate_mx_qparam"] = timed(lambda: Q.calculate_mx_qparam(x, (-1,), 32, 127.0, True), n * (4 + 4 / 32))
+    vb.set_table_policy(allow_int=False)
+    res["cfg1_quantize_mx_fp32_dropin_lut"] = timed(lambda: Q.quantize_mx(x, q8, (-1,), 32, 127.0, True), n * (4 + 4 + 4 / 32))
+    vb.set_table_policy(allow_int=True)
+    # cfg2: posit8_1 per-channel over ResNet-50-shaped conv weights (largest layer and a multi-tensor sweep)
+    qp = tab("posit8_1")
+    w = torch.randn(512, 512, 3, 3, generator=g, device=dev) * 0.02
+    sc = w.abs().amax(dim=(1, 2, 3), keepdim=True) / 4096.0
+    res["cfg2_quantize_posit8_perchannel_512x512x3x3"] = timed(lambda: Q.quantize(w, sc, None, None, None, qp), w.numel() * 8)
+    wq = Q.quantize(w, sc, None, None, None, qp)
+    res["cfg2_dequantize_perchannel_512x512x3x3"] = timed(lambda: Q.dequantize(wq, sc), w.numel() * 8)
+    big = torch.randn(25_502_912 // 4608, 4608, generator=g, device=dev) * 0.02     # all 25.5 M weights as one tensor
+    scb = big.abs().amax(dim=1, keepdim=True) / 4096.0
+    res["cfg2_quantize_posit8_perchannel_25p5M"] = timed(lambda: Q.quantize(big, scb, None, None, None, qp), big.numel() * 8)
+    # cfg4-shaped: fp32 [11008,4096] through a 16-entry codebook table, per-row scale
+    w4 = torch.randn(11008, 4096, generator=g, device=dev) * 0.02
+    cb = torch.from_numpy(vb.tables.codebook_table(sorted(torch.randn(16).mul(0.7).tolist())).view("int16").copy()).view(torch.bfloat16).to(dev)
+    s4 = w4.abs().amax(dim=1, keepdim=True)
+    res["cfg4_quantize_codebook16_perrow_11008x4096"] = timed(lambda: Q.quantize(w4, s4, None, None, None, cb), w4.numel() * 8)
+    res["vmap_fp32_posit8_11008x4096"] = timed(lambda: Q.vmap(w4, qp), w4.numel() * 8)
+    for k, v in res.items():
+        v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]
+    print(json.dumps({"workload": "element-wise configs (cfg1, cfg2, cfg4 shapes)", "results": res, "peak_hbm_gbs": peaks["hbm_gbs"],
+                      "peak_kind": kind}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -405,12 +473,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="fewer than 32: reduced model for profiler captures")
     ap.add_argument("--kernel-only", action="store_true", help="device-timed part only (profiler captures)")
-    ap.add_argument("--workload", default="model", choices=["model", "linear"],
+    ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise"],
                     help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
     ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
     args = ap.parse_args()
     if args.workload == "linear":
         run_linear(args)
+        return
+    if args.workload == "elementwise":
+        run_elementwise(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -42,6 +42,20 @@ def test_fixture_bit_exact_on_cuda(case, policy):
         assert ok, f"{case['name']} [{policy}]: {msg}"
 
 
+@pytest.mark.parametrize("case", [c for c in ELEMENTWISE if c["op"] in ("vmap", "quantize", "dequantize")],
+                         ids=[c["name"] for c in ELEMENTWISE if c["op"] in ("vmap", "quantize", "dequantize")])
+def test_generic_elementwise_kernel_stays_bit_exact(case):
+    """The specialised element-wise kernel normally takes the aligned cases; the generic one must agree."""
+    os.environ["VOYAGER_B200_GENERIC_EW"] = "1"
+    try:
+        outs, expected = run_case(case, torch.ops.quantized_ops, device="cuda")
+        for o, e in zip(outs, expected):
+            ok, msg = same_bits(o, e)
+            assert ok, f"{case['name']}: {msg}"
+    finally:
+        del os.environ["VOYAGER_B200_GENERIC_EW"]
+
+
 MX_CASES = [c for c in ELEMENTWISE if c["op"] == "quantize_mx"]
 
 

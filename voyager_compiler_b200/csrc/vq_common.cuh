@@ -42,6 +42,12 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
                    const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
                    void* workspace, cudaStream_t st);
 
+// Tries the specialised element-wise kernel (op 0 map, 1 quantize, 2 dequantize).  Returns 1 when
+// it launched, 0 when the arguments are outside its domain, a negative status on error.
+int vq_ew_fast_try(int op, const void* in, int dtype, int64_t n, const void* scale, const void* zero_point,
+                   const vq_scale_layout* layout, const vq_table* t0, const vq_table* t1, void* out, uint8_t* codes,
+                   cudaStream_t st);
+
 // Division of a 31-bit index by a run-time constant: q = (umulhi(n, m) + n) >> s, valid for
 // 0 <= n < 2^31 and 1 <= d < 2^31.
 struct FastDiv {

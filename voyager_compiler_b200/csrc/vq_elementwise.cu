@@ -5,6 +5,8 @@
 // shared memory once per CTA when the tensor is large, read through L1/L2 when it is small, and
 // replaced by arithmetic (INT) or by a run-start binary search (RUNS, <= 1 KB of shared memory)
 // when the host has proven the table equivalent.  HBM bound: 2 x sizeof(T) bytes per element.
+#include <cstdlib>
+
 #include "vq_common.cuh"
 
 namespace {
@@ -291,6 +293,10 @@ int run_ew(const void* in, int dtype, int64_t n, const void* scale, const void* 
     if (int rc = check_table(t1, name, false)) return rc;
     const size_t esz = dtype == VQ_F32 ? 4 : 2;
     const int N = dtype == VQ_F32 ? 4 : 8;
+    if (!getenv("VOYAGER_B200_GENERIC_EW")) {
+        int fr = vq_ew_fast_try(OP, in, dtype, n, scale, zp, layout, t0, t1, out, codes, (cudaStream_t)stream);
+        if (fr != 0) return fr < 0 ? fr : 0;
+    }
 
     EwParams p{};
     p.t0 = to_dev(t0);
