@@ -16,10 +16,16 @@
 // winds down (drains its copies, frees tensor memory) instead of hanging.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "vq_common.cuh"
 #include "vq_tc.cuh"
+
+// CTA-pair kernel (vq_gemm2.cu): 256 x 256 tiles on two CTAs; tensor maps with 128-row boxes
+int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
+                        int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
+                        cudaStream_t st);
 
 namespace {
 
@@ -347,6 +353,11 @@ int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bias, void
     VQ_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)B % 16 == 0 && (uintptr_t)Y % 2 == 0, "%s: operands must be 16-byte aligned", name);
     CUtensorMap tmA, tmB;
     if (int rc = make_map(&tmA, A, M, K, BM)) return rc;
+    const char* tile = getenv("VOYAGER_B200_GEMM_TILE");       // "1cta" forces the one-CTA 128x256 tile
+    if (M > 128 && !(tile && !strcmp(tile, "1cta"))) {
+        if (int rc = make_map(&tmB, B, N, K, 128)) return rc;
+        return vq_gemm_pair_launch(tmA, tmB, Ys, n_outputs, ldy, col_offset, bias, M, N, K, status, (cudaStream_t)stream);
+    }
     if (int rc = make_map(&tmB, B, N, K, BN)) return rc;
     GemmParams p{};
     for (int d = 0; d < n_outputs; ++d) p.Y[d] = reinterpret_cast<uint16_t*>(Ys[d]);

@@ -1,0 +1,219 @@
+// CTA-pair variant of the TMA-fed GEMM: two CTAs of a cluster compute one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128-column half of B
+// (32 KB per k-step instead of 48 KB), the pair's leader issues the MMAs for both, every CTA keeps
+// 128 rows x 256 columns of the accumulator (double buffered) in its tensor memory and runs its own
+// epilogue.  Per SM this writes and reads a third less shared memory per flop than the one-CTA
+// 128 x 256 tile, which is bound by the shared-memory data pipe.
+//
+// Synchronisation (all waits bounded):
+//   full[s]    leader's barrier; the leader arms it with the byte count of BOTH CTAs' tile loads,
+//              whose completions are all counted on it
+//   empty[s]   one per CTA; the leader's tcgen05.commit arrives on both once the MMAs have read stage s
+//   tfull[a]   one per CTA; commit arrives on both when accumulator a is complete
+//   tempty[a]  leader's barrier, 8 arrivals: the 4 epilogue warps of each CTA
+#include <cuda.h>
+
+#include "vq_common.cuh"
+#include "vq_tc.cuh"
+
+namespace {
+
+constexpr int PM = 128;            // rows of A per CTA (pair: 256)
+constexpr int PNH = 128;           // columns of B per CTA (pair: 256)
+constexpr int PN = 256;
+constexpr int PK = 64;
+constexpr int PSTAGES = 6;
+constexpr int PA_BYTES = PM * PK * 2, PB_BYTES = PNH * PK * 2, PSTAGE_BYTES = PA_BYTES + PB_BYTES;
+constexpr long long PWAIT = 4000000000ll;
+constexpr int P_MAX_OUT = 8;
+
+struct PairParams {
+    uint16_t* Y[P_MAX_OUT];
+    int n_outputs;
+    int64_t ldy, col_offset;
+    const uint16_t* bias;
+    int M, N, K;
+    int tiles_m, tiles_n;      // in units of 256 x 256
+    int32_t* status;
+};
+
+__device__ __forceinline__ void record_fail(int32_t* status, int code) {
+    if (status) atomicCAS(status, 0, code);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = base + PSTAGES * PSTAGE_BYTES;
+    const uint32_t FULL0 = bar_base, EMPTY0 = bar_base + 8u * PSTAGES, TFULL0 = bar_base + 16u * PSTAGES,
+                   TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int num_k = (p.K + PK - 1) / PK;
+    const int n_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) {
+            tc::mbar_init(FULL0 + 8u * s, 1);
+            tc::mbar_init(EMPTY0 + 8u * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            tc::mbar_init(TFULL0 + 8u * s, 1);
+            tc::mbar_init(TEMPTY0 + 8u * s, 8);
+        }
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&tmA);
+        tc::prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) {
+        tc::tmem_alloc_pair(SLOT, 512);
+        tc::tmem_relinquish_pair();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::cluster_sync_all();          // both CTAs' barriers are initialised before either touches the other's
+    tc::tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(SLOT));
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ tile loads (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
+                const int m0 = (tile % p.tiles_m) * 256 + (int)rank * PM;
+                const int n0 = (tile / p.tiles_m) * PN + (int)rank * PNH;
+                for (int k = 0; k < num_k; ++k) {
+                    if (!tc::mbar_wait_cluster(EMPTY0 + 8u * stage, phase ^ 1u, PWAIT)) { ok = false; break; }
+                    const uint32_t leader_full = tc::map_to_cta(FULL0 + 8u * stage, 0);
+                    if (rank == 0) tc::mbar_expect_tx(FULL0 + 8u * stage, 2 * PSTAGE_BYTES);
+                    tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES, &tmA, k * PK, m0, leader_full);
+                    tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES + PA_BYTES, &tmB, k * PK, n0, leader_full);
+                    if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) record_fail(p.status, 11);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = tc::idesc_bf16_f32(256, PN);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
+                if (!tc::mbar_wait_cluster(TEMPTY0 + 8u * acc, acc_phase ^ 1u, PWAIT)) { ok = false; break; }
+                tc::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)acc * PN;
+                for (int k = 0; k < num_k; ++k) {
+                    if (!tc::mbar_wait_cluster(FULL0 + 8u * stage, phase, PWAIT)) { ok = false; break; }
+                    tc::tc_fence_after();
+                    const uint32_t sa = base + stage * PSTAGE_BYTES, sb = sa + PA_BYTES;
+                    const uint64_t da = tc::smem_desc_k_sw128(sa), db = tc::smem_desc_k_sw128(sb);
+#pragma unroll
+                    for (int kk = 0; kk < PK / 16; ++kk)
+                        tc::mma_f16_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                    tc::mma_commit_pair(EMPTY0 + 8u * stage);
+                    if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc::mma_commit_pair(TFULL0 + 8u * acc);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) record_fail(p.status, 12);
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps per CTA)
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
+            const int m0 = (tile % p.tiles_m) * 256 + (int)rank * PM, n0 = (tile / p.tiles_m) * PN;
+            if (lane == 0) ok = tc::mbar_wait_cluster(TFULL0 + 8u * acc, acc_phase, PWAIT);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
+            tc::tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * PN;
+#pragma unroll 1
+            for (int c = 0; c < PN / 32; ++c) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(taddr + c * 32, r);
+                tc::tmem_ld_wait();
+                const int col0 = n0 + c * 32;
+                if (row < p.M && col0 < p.N) {
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float lo = __uint_as_float(r[2 * j]), hi = __uint_as_float(r[2 * j + 1]);
+                        if (p.bias) {
+                            const int cc = col0 + 2 * j;
+                            if (cc < p.N) lo = __fadd_rn(lo, __uint_as_float((uint32_t)__ldg(p.bias + cc) << 16));
+                            if (cc + 1 < p.N) hi = __fadd_rn(hi, __uint_as_float((uint32_t)__ldg(p.bias + cc + 1) << 16));
+                        }
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(hi), "f"(lo));
+                    }
+                    const size_t off = (size_t)row * p.ldy + p.col_offset + col0;
+                    for (int d = 0; d < p.n_outputs; ++d) {
+                        uint16_t* dst = p.Y[d] + off;
+                        if (col0 + 32 <= p.N && (off & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                                dst[j] = (uint16_t)((j & 1) ? (o[j >> 1] >> 16) : (o[j >> 1] & 0xFFFFu));
+                        }
+                    }
+                }
+            }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_cta(TEMPTY0 + 8u * acc, 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (!ok && lane == 0) record_fail(p.status, 13);
+    }
+
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::cluster_sync_all();          // neither CTA frees tensor memory or exits while the other may still signal it
+    if (warp == 1) {
+        tc::tc_fence_after();
+        tc::tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+// Launches the CTA-pair GEMM.  The tensor maps must have 128-row boxes for both operands.
+int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
+                        int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
+                        cudaStream_t st) {
+    PairParams p{};
+    for (int d = 0; d < n_outputs; ++d) p.Y[d] = reinterpret_cast<uint16_t*>(Ys[d]);
+    p.n_outputs = n_outputs;
+    p.ldy = ldy;
+    p.col_offset = col_offset;
+    p.bias = reinterpret_cast<const uint16_t*>(bias);
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.tiles_m = (int)((M + 255) / 256);
+    p.tiles_n = (int)((N + PN - 1) / PN);
+    p.status = status;
+    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int sms = vq_sm_count();
+    int pairs = sms / 2;
+    if (n_tiles < pairs) pairs = n_tiles;
+    const size_t smem = (size_t)PSTAGES * PSTAGE_BYTES + 256 + 1024;
+    if ((int)smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "device offers too little shared memory for the pair GEMM");
+    VQ_CUDA(cudaFuncSetAttribute(mx_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mx_gemm_pair_kernel<<<pairs * 2, 192, smem, st>>>(tmA, tmB, p);
+    VQ_LAUNCH_CHECK("mx_gemm_pair_kernel");
+    return 0;
+}
