@@ -11,6 +11,9 @@
 //   empty[s]   one per CTA; the leader's tcgen05.commit arrives on both once the MMAs have read stage s
 //   tfull[a]   one per CTA; commit arrives on both when accumulator a is complete
 //   tempty[a]  leader's barrier, 8 arrivals: the 4 epilogue warps of each CTA
+// Epilogue: each thread owns one accumulator row; it stages 128 columns of bf16 in shared memory and
+// sends them with one asynchronous bulk copy per output buffer (256 bytes each: own memory and, for
+// the column-parallel linear, every peer GPU's copy of Y over NVLink).
 #include <cuda.h>
 
 #include "vq_common.cuh"
@@ -22,8 +25,10 @@ constexpr int PM = 128;            // rows of A per CTA (pair: 256)
 constexpr int PNH = 128;           // columns of B per CTA (pair: 256)
 constexpr int PN = 256;
 constexpr int PK = 64;
-constexpr int PSTAGES = 6;
+constexpr int PSTAGES = 5;
 constexpr int PA_BYTES = PM * PK * 2, PB_BYTES = PNH * PK * 2, PSTAGE_BYTES = PA_BYTES + PB_BYTES;
+// epilogue staging: 128 rows x 128 columns of bf16, rows padded by 16 bytes against bank conflicts
+constexpr int OUT_COLS = 128, OUT_ROW_BYTES = OUT_COLS * 2 + 16, OUT_BYTES = PM * OUT_ROW_BYTES;
 constexpr long long PWAIT = 4000000000ll;
 constexpr int P_MAX_OUT = 8;
 
@@ -34,8 +39,17 @@ struct PairParams {
     const uint16_t* bias;
     int M, N, K;
     int tiles_m, tiles_n;      // in units of 256 x 256
+    int bulk_ok;               // output rows are 16-byte aligned: the epilogue may use bulk stores
     int32_t* status;
 };
+
+// shared -> global asynchronous bulk copy of `bytes` (multiple of 16) issued by one thread
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void record_fail(int32_t* status, int code) {
     if (status) atomicCAS(status, 0, code);
@@ -45,7 +59,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PairParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = base + PSTAGES * PSTAGE_BYTES;
+    const uint32_t out_base = base + PSTAGES * PSTAGE_BYTES;      // epilogue staging buffer
+    const uint32_t bar_base = out_base + OUT_BYTES;
     const uint32_t FULL0 = bar_base, EMPTY0 = bar_base + 8u * PSTAGES, TFULL0 = bar_base + 16u * PSTAGES,
                    TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u;
 
@@ -141,24 +156,45 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc::tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * PN;
+            const int rloc = q * 32 + lane;                                // row inside this CTA's 128 rows
+            const uint32_t my_row = out_base + (uint32_t)rloc * OUT_ROW_BYTES;
 #pragma unroll 1
             for (int c = 0; c < PN / 32; ++c) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(taddr + c * 32, r);
                 tc::tmem_ld_wait();
                 const int col0 = n0 + c * 32;
-                if (row < p.M && col0 < p.N) {
-                    uint32_t o[16];
+                uint32_t o[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float lo = __uint_as_float(r[2 * j]), hi = __uint_as_float(r[2 * j + 1]);
-                        if (p.bias) {
-                            const int cc = col0 + 2 * j;
-                            if (cc < p.N) lo = __fadd_rn(lo, __uint_as_float((uint32_t)__ldg(p.bias + cc) << 16));
-                            if (cc + 1 < p.N) hi = __fadd_rn(hi, __uint_as_float((uint32_t)__ldg(p.bias + cc + 1) << 16));
-                        }
-                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(hi), "f"(lo));
+                for (int j = 0; j < 16; ++j) {
+                    float lo = __uint_as_float(r[2 * j]), hi = __uint_as_float(r[2 * j + 1]);
+                    if (p.bias) {
+                        const int cc = col0 + 2 * j;
+                        if (cc < p.N) lo = __fadd_rn(lo, __uint_as_float((uint32_t)__ldg(p.bias + cc) << 16));
+                        if (cc + 1 < p.N) hi = __fadd_rn(hi, __uint_as_float((uint32_t)__ldg(p.bias + cc + 1) << 16));
                     }
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(hi), "f"(lo));
+                }
+                const int half0 = n0 + (c >> 2) * OUT_COLS;                 // first column of this 128-column half
+                const bool bulk = p.bulk_ok && half0 + OUT_COLS <= p.N;      // whole half inside the matrix
+                if (bulk) {
+                    // every thread stages only its own row and later copies only its own row, so the
+                    // only ordering needed is with its own earlier bulk reads of that row
+                    if ((c & 3) == 0) bulk_wait_read();
+                    const uint32_t dsts = my_row + (uint32_t)(c & 3) * 64u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dsts + 16u * j), "r"(o[4 * j]), "r"(o[4 * j + 1]),
+                                     "r"(o[4 * j + 2]), "r"(o[4 * j + 3]) : "memory");
+                    if ((c & 3) == 3) {
+                        tc::fence_proxy_async();
+                        if (row < p.M) {
+                            const size_t off = (size_t)row * p.ldy + p.col_offset + half0;
+                            for (int d = 0; d < p.n_outputs; ++d) bulk_store(p.Y[d] + off, my_row, OUT_COLS * 2);
+                        }
+                        bulk_commit();
+                    }
+                } else if (row < p.M && col0 < p.N) {
                     const size_t off = (size_t)row * p.ldy + p.col_offset + col0;
                     for (int d = 0; d < p.n_outputs; ++d) {
                         uint16_t* dst = p.Y[d] + off;
@@ -179,6 +215,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
         if (!ok && lane == 0) record_fail(p.status, 13);
+        bulk_wait_all();             // this thread's output copies have landed before the CTA may exit
     }
 
     tc::tc_fence_before();
@@ -206,11 +243,14 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     p.tiles_m = (int)((M + 255) / 256);
     p.tiles_n = (int)((N + PN - 1) / PN);
     p.status = status;
+    p.bulk_ok = (ldy % 8 == 0 && col_offset % 8 == 0) ? 1 : 0;
+    for (int d = 0; d < n_outputs; ++d)
+        if ((uintptr_t)Ys[d] % 16) p.bulk_ok = 0;
     const int n_tiles = p.tiles_m * p.tiles_n;
     const int sms = vq_sm_count();
     int pairs = sms / 2;
     if (n_tiles < pairs) pairs = n_tiles;
-    const size_t smem = (size_t)PSTAGES * PSTAGE_BYTES + 256 + 1024;
+    const size_t smem = (size_t)PSTAGES * PSTAGE_BYTES + OUT_BYTES + 256 + 1024;
     if ((int)smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "device offers too little shared memory for the pair GEMM");
     VQ_CUDA(cudaFuncSetAttribute(mx_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     mx_gemm_pair_kernel<<<pairs * 2, 192, smem, st>>>(tmA, tmB, p);
