@@ -311,6 +311,26 @@ def main():
            {"block_size": 32, "weight_layout": "ck"},
            qops.matmul_mx(aq, bq, input_scale=as_, weight_scale=bs_, block_size=32))
 
+    # conv2d_mx: blocks along the channel axis (ax=1 for NCHW, last axis for NHWC / HWIO)
+    xc = outliers((2, 32, 9, 9), torch.bfloat16)
+    wc = (torch.randn(24, 32, 3, 3) * 0.1).to(torch.bfloat16)
+    bc = torch.randn(24).to(torch.bfloat16)
+    xcs, xcq = qops.quantize_mx(xc, tt["int8"], (1,), 16, 127.0, True)
+    wcs, wcq = qops.quantize_mx(wc, tt["int8"], (1,), 16, 127.0, True)
+    for tag, bias_t, stride, pad in (("basic", None, [1, 1], [1, 1]), ("bias_s2", bc, [2, 2], [0, 0])):
+        R.case(f"conv_nchw_{tag}", "conv2d_mx",
+               {"input": xcq, "weight": wcq, "bias": bias_t, "input_scale": xcs, "weight_scale": wcs},
+               {"stride": stride, "padding": pad, "dilation": [1, 1], "groups": 1, "block_size": 16, "layout": "nchw"},
+               qops.conv2d_mx(xcq, wcq, bias_t, stride, pad, [1, 1], 1, input_scale=xcs, weight_scale=wcs, block_size=16))
+    xh = xc.permute(0, 2, 3, 1).contiguous()
+    wh = wc.permute(2, 3, 1, 0).contiguous()                       # HWIO
+    xhs, xhq = qops.quantize_mx(xh, tt["int8"], (-1,), 16, 127.0, True)
+    whs, whq = qops.quantize_mx(wh, tt["int8"], (2,), 16, 127.0, True)
+    R.case("conv_nhwc", "conv2d_mx", {"input": xhq, "weight": whq, "bias": bc, "input_scale": xhs, "weight_scale": whs},
+           {"stride": [1, 1], "padding": [1, 1], "dilation": [1, 1], "groups": 1, "block_size": 16, "layout": "nhwc"},
+           qops.conv2d_mx(xhq, whq, bc, [1, 1], [1, 1], [1, 1], 1, input_scale=xhs, weight_scale=whs, block_size=16,
+                          layout="nhwc"))
+
     np.savez_compressed(os.path.join(HERE, "golden_ops.npz"), **R.arrays)
     with open(os.path.join(HERE, "golden_ops.json"), "w") as f:
         json.dump({"torch": torch.__version__, "cases": R.cases}, f, indent=1)

@@ -131,6 +131,10 @@ def run_case(case, backend, device="cpu"):
                                 weight_scale=t.get("weight_scale"), block_size=p["block_size"],
                                 input_code=t.get("input_code"), weight_code=t.get("weight_code"),
                                 weight_layout=p["weight_layout"])
+    elif op == "conv2d_mx":
+        out = backend.conv2d_mx(t["input"], t["weight"], t.get("bias"), p["stride"], p["padding"], p["dilation"],
+                                p["groups"], input_scale=t.get("input_scale"), weight_scale=t.get("weight_scale"),
+                                block_size=p["block_size"], layout=p["layout"])
     else:
         raise ValueError(op)
     outs = list(out) if isinstance(out, (tuple, list)) else [out]

@@ -13,8 +13,9 @@ from golden_util import case_ids, cases, run_case, same_bits
 
 pytestmark = pytest.mark.gpu
 
-ELEMENTWISE = [c for c in cases() if c["op"] not in ("linear_mx", "matmul_mx")]
-GEMMS = [c for c in cases() if c["op"] in ("linear_mx", "matmul_mx")]
+CONTRACTIONS = ("linear_mx", "matmul_mx", "conv2d_mx")
+ELEMENTWISE = [c for c in cases() if c["op"] not in CONTRACTIONS]
+GEMMS = [c for c in cases() if c["op"] in CONTRACTIONS]
 POLICIES = {
     "default": dict(runs_max=0, allow_int=True),
     "lut": dict(runs_max=0, allow_int=False),

@@ -13,7 +13,7 @@ import voyager_oracle as vo  # noqa: E402
 
 ORACLE = types.SimpleNamespace(
     vmap=vo.lut_map, quantize=vo.quantize, dequantize=vo.dequantize, calculate_mx_qparam=vo.mx_scale,
-    quantize_mx=vo.quantize_mx, linear_mx=vo.linear_mx, matmul_mx=vo.matmul_mx)
+    quantize_mx=vo.quantize_mx, linear_mx=vo.linear_mx, matmul_mx=vo.matmul_mx, conv2d_mx=vo.conv2d_mx)
 
 BUILTIN = [n for n in golden_table_names() if not n.startswith("cb")]
 
@@ -50,7 +50,7 @@ def test_oracle_replays_upstream_case(case):
     outs, expected = run_case(case, ORACLE)
     assert len(outs) == len(expected)
     for o, e in zip(outs, expected):
-        if case["op"] in ("linear_mx", "matmul_mx"):
+        if case["op"] in ("linear_mx", "matmul_mx", "conv2d_mx"):
             # same torch CPU GEMM on the same operands: expected to be identical as well
             assert o.dtype == e.dtype and o.shape == e.shape
             rel = (o.double() - e.double()).norm() / e.double().norm()

@@ -25,7 +25,7 @@ from .qtables import exp_tables, table_handle
 
 logger = logging.getLogger(__name__)
 
-__all__ = ["vmap", "quantize", "dequantize", "calculate_mx_qparam", "quantize_mx", "linear_mx", "matmul_mx",
+__all__ = ["vmap", "quantize", "dequantize", "calculate_mx_qparam", "quantize_mx", "linear_mx", "matmul_mx", "conv2d_mx",
            "register", "SCHEMAS"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
@@ -44,6 +44,11 @@ SCHEMAS = {
     "quantize_mx": "quantize_mx(Tensor self, Tensor qmap, SymInt[] axes, int block_size, "
                    "float quant_max, bool force_scale_power_of_two=False, "
                    "Tensor scale_qmap=None, Tensor output_code=None) -> (Tensor, Tensor)",
+    "conv2d_mx": "conv2d_mx(Tensor input, Tensor weight, Tensor? bias=None, "
+                 "SymInt[2] stride=1, SymInt[2] padding=0, SymInt[2] dilation=1, "
+                 "SymInt groups=1, *, Tensor? input_scale=None, Tensor? weight_scale=None, "
+                 "int? block_size=None, Tensor? input_code=None, "
+                 'Tensor? weight_code=None, str layout="nchw") -> Tensor',
     "linear_mx": "linear_mx(Tensor input, Tensor weight, Tensor? bias=None, *, "
                  "Tensor? input_scale=None, Tensor? weight_scale=None, "
                  "int? block_size=None, Tensor? input_code=None, Tensor? weight_code=None, "
@@ -333,6 +338,28 @@ def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=No
                    b_is_nk=(weight_layout == "kc"))
 
 
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def conv2d_mx(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, *, input_scale=None,
+              weight_scale=None, block_size=None, input_code=None, weight_code=None, layout="nchw"):
+    """ops/quantized.py:239-283: operands are decoded and scaled by this package's kernels (blocks
+    along the channel axis go through the strided scale layout), the convolution itself is the
+    vendor kernel, as upstream.  ``"nhwc"``: NHWC activations, HWIO weight, NHWC result."""
+    assert layout in ("nchw", "nhwc"), layout
+    _require_cuda(input, "conv2d_mx")
+    x = _decode_operand("conv2d_mx", input, input_code, input_scale, block_size)
+    w = _decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    if layout == "nhwc":
+        x = x.permute(0, 3, 1, 2)
+        if groups == 1:
+            w = w.permute(3, 2, 0, 1)
+        return torch.ops.aten.conv2d(x, w, bias, stride, padding, dilation, groups).permute(0, 2, 3, 1)
+    return torch.ops.aten.conv2d(x, w, bias, stride, padding, dilation, groups)
+
+
 # ---------------------------------------------------------------------------------------------
 # dispatcher registration
 # ---------------------------------------------------------------------------------------------
@@ -395,6 +422,15 @@ def register() -> str:
             return torch.empty(list(torch.broadcast_shapes(a.shape[:-2], bb.shape[:-2])) + [a.shape[-2], bb.shape[-1]],
                                dtype=a.dtype, device=a.device)
 
+        def _conv_fake(x, w, b=None, stride=1, padding=0, dilation=1, groups=1, **kw):
+            xm, wm = torch.empty(x.shape, device="meta", dtype=x.dtype), torch.empty(w.shape, device="meta", dtype=w.dtype)
+            if kw.get("layout", "nchw") == "nhwc":
+                xm = xm.permute(0, 3, 1, 2)
+                wm = wm.permute(3, 2, 0, 1) if groups == 1 else wm
+            y = torch.ops.aten.conv2d(xm, wm, None, _pair(stride), _pair(padding), _pair(dilation), groups)
+            return y.permute(0, 2, 3, 1) if kw.get("layout", "nchw") == "nhwc" else y
+
+        m.impl("conv2d_mx", _conv_fake)
         m.impl("linear_mx", _lin_fake)
         m.impl("matmul_mx", _mm_fake)
         _libs.append(m)
@@ -404,6 +440,7 @@ def register() -> str:
     c.impl("dequantize", dequantize)
     c.impl("calculate_mx_qparam", calculate_mx_qparam)
     c.impl("quantize_mx", quantize_mx)
+    c.impl("conv2d_mx", conv2d_mx)
     c.impl("linear_mx", linear_mx)
     c.impl("matmul_mx", matmul_mx)
     _libs.append(c)
