@@ -1,0 +1,64 @@
+"""Drop-in behaviour next to the real upstream package (runs only where a checkout is present)."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+REF = os.environ.get("VOYAGER_REFERENCE", "/root/reference")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "src", "voyager_compiler")),
+                                reason="upstream checkout not available")
+
+
+def _run(code):
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([ROOT, os.path.join(ROOT, "tests", "golden")]))
+    r = subprocess.run([sys.executable, "-c", textwrap.dedent(code)], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    return r.stdout
+
+
+def test_impl_mode_keeps_upstream_cpu_kernels_and_op_identity():
+    out = _run("""
+        import torch
+        from _reference_import import import_reference
+        ref = import_reference()
+        op_before = torch.ops.quantized_ops.quantize_mx.default
+        import voyager_compiler_b200 as vb
+        assert vb.REGISTERED_AS == "impl", vb.REGISTERED_AS
+        assert torch.ops.quantized_ops.quantize_mx.default is op_before
+        q = ref["fake_quantize"].get_quantization_map("int8")
+        x = torch.randn(4, 64)
+        s, c = torch.ops.quantized_ops.quantize_mx(x, q, (-1,), 32, 127.0, True)     # CPU: upstream composite
+        s2, c2 = ref["ops"].quantize_mx(x, q, (-1,), 32, 127.0, True)
+        assert torch.equal(s, s2) and torch.equal(c, c2)
+        m = torch.empty(8, 64, device="meta")
+        sm, cm = torch.ops.quantized_ops.quantize_mx(m, q.to("meta"), (-1,), 32, 127.0, True)
+        assert sm.shape == (8, 2) and cm.shape == (8, 64)
+        print("ok")
+    """)
+    assert "ok" in out
+
+
+def test_patch_reference_rebinds_direct_imports_and_unpatches():
+    out = _run("""
+        import torch
+        from _reference_import import import_reference
+        ref = import_reference()
+        import voyager_compiler_b200 as vb
+        from voyager_compiler_b200 import compat
+        fq = ref["fake_quantize"]
+        orig = fq.vmap
+        done = compat.patch_reference()
+        assert "voyager_compiler.quantization.fake_quantize.vmap" in done, done
+        assert fq.vmap is not orig and fq.vmap.__wrapped_original__ is orig
+        q = fq.get_quantization_map("int8")
+        x = torch.randn(100) * 30
+        assert torch.equal(fq.vmap(x, q), orig(x, q))            # CPU tensors still use the original
+        compat.unpatch_reference()
+        assert fq.vmap is orig
+        print("ok")
+    """)
+    assert "ok" in out
