@@ -440,6 +440,18 @@ def run_elementwise(args):
     res["cfg1_quantize_mx_packed_int8_e8"] = timed(
         lambda: mq.quantize_tensors_mx([x], q8, 32, 127.0, True, code_bits=8, want_exp=True), n * (4 + 1 + 4 / 32 + 1 / 32))
     res["cfg1_calculate_mx_qparam"] = timed(lambda: Q.calculate_mx_qparam(x, (-1,), 32, 127.0, True), n * (4 + 4 / 32))
+    # the same ops on a 16x larger tensor (launch overhead amortised)
+    xl = torch.randn(16384, 16384, generator=g, device=dev)
+    nl = xl.numel()
+    sl, cl = Q.quantize_mx(xl, q8, (-1,), 32, 127.0, True)
+    res["large_quantize_mx_fp32_dropin_16384x16384"] = timed(lambda: Q.quantize_mx(xl, q8, (-1,), 32, 127.0, True), nl * (4 + 4 + 4 / 32), 5)
+    res["large_dequantize_fp32_16384x16384"] = timed(lambda: Q.dequantize(cl, sl, None, (-1,), 32), nl * (4 + 4 + 4 / 32), 5)
+    res["large_calculate_mx_qparam_16384x16384"] = timed(lambda: Q.calculate_mx_qparam(xl, (-1,), 32, 127.0, True), nl * (4 + 4 / 32), 5)
+    res["large_quantize_mx_packed_int8_e8_16384x16384"] = timed(
+        lambda: mq.quantize_tensors_mx([xl], q8, 32, 127.0, True, code_bits=8, want_exp=True), nl * (4 + 1 + 4 / 32 + 1 / 32), 5)
+    xlb = xl.to(torch.bfloat16)
+    res["large_quantize_mx_bf16_dropin_16384x16384"] = timed(lambda: Q.quantize_mx(xlb, q8, (-1,), 32, 127.0, True), nl * (2 + 2 + 2 / 32), 5)
+    del xl, sl, cl, xlb
     vb.set_table_policy(allow_int=False)
     res["cfg1_quantize_mx_fp32_dropin_lut"] = timed(lambda: Q.quantize_mx(x, q8, (-1,), 32, 127.0, True), n * (4 + 4 + 4 / 32))
     vb.set_table_policy(allow_int=True)

@@ -244,7 +244,7 @@ int run_mx(const char* name, const void* in, int dtype, int64_t outer, int64_t L
 
     const bool big = n >= (1 << 21);
     const bool need_values = has_tab && (out_codes || p.dequant);
-    if (fast && has_tab && n < (1ll << 31) && !getenv("VOYAGER_B200_GENERIC_MX")) {
+    if (fast && pow2 != 2 && n < (1ll << 31) && !getenv("VOYAGER_B200_GENERIC_MX")) {
         vq_mx_item item{};
         item.in = in; item.out_scale = out_scale; item.out_codes = out_codes; item.scale_f32 = p.scale_f32;
         item.exp_e8 = p.exp_e8; item.codes = p.codes; item.dequant = p.dequant; item.n = n;

@@ -25,7 +25,7 @@
 
 namespace {
 
-enum { OUT_FLOAT = 0, OUT_PACK4 = 1, OUT_PACK8 = 2 };
+enum { OUT_FLOAT = 0, OUT_PACK4 = 1, OUT_PACK8 = 2, OUT_SCALE = 3 };   // OUT_SCALE: block scales only
 enum { TK_LUT = 0, TK_INT = 1 };
 
 // 32 bytes of input as raw words

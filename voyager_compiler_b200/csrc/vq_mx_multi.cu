@@ -175,14 +175,15 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             const float s = fast_scale<T, RULE>(p.rule, m);
             if ((ci & ((1u << gs) - 1u)) == 0) {
                 const uint32_t b = ci >> gs;
-                if (OUT == OUT_FLOAT) {
+                if (OUT == OUT_FLOAT || OUT == OUT_SCALE) {
                     store_one<T>(out_scale + b, s);
                 } else {
                     scale_f32[b] = s;
                     if (RULE == 1 && exp_e8) exp_e8[b] = (int8_t)scale_exponent(s);
                 }
             }
-            fast_chunk<T, TK, OUT, SM>(ft, x[u], s, refine && safe, (size_t)ci, out_codes, codes8);
+            if (OUT != OUT_SCALE)
+                fast_chunk<T, TK, OUT == OUT_SCALE ? OUT_FLOAT : OUT, SM>(ft, x[u], s, refine && safe, (size_t)ci, out_codes, codes8);
         }
         }
     }
@@ -201,6 +202,8 @@ template <typename T, int RULE, int TK>
 int dispatch_out(const FastParams& p, int out, bool sm, int threads, int blocks, size_t smem, cudaStream_t st) {
     if (TK == TK_INT) sm = false;
     switch (out) {
+        case OUT_SCALE:
+            return launch_fast2<T, RULE, TK_INT, OUT_SCALE, false>(p, threads, blocks, smem, st);
         case OUT_FLOAT:
             return sm ? launch_fast2<T, RULE, TK, OUT_FLOAT, true>(p, threads, blocks, smem, st)
                       : launch_fast2<T, RULE, TK, OUT_FLOAT, false>(p, threads, blocks, smem, st);
@@ -232,9 +235,11 @@ constexpr int kU = 2;
 int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
                    const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
                    void* workspace, cudaStream_t st) {
-    if (n_items < 1 || !table || (pow2 != 0 && pow2 != 1)) return 0;
+    if (n_items < 1 || (pow2 != 0 && pow2 != 1)) return 0;
     int tk;
-    if (table->kind == VQ_TABLE_INT) tk = TK_INT;
+    const bool no_table = !table || table->kind == VQ_TABLE_NONE;
+    if (no_table) tk = TK_INT;                       // scale-only pass: no table is consulted
+    else if (table->kind == VQ_TABLE_INT) tk = TK_INT;
     else if (table->kind == VQ_TABLE_LUT16 && table->nan_uniform && table->lut16) tk = TK_LUT;
     else return 0;
     if (scale_table && scale_table->kind == VQ_TABLE_RUNS) return 0;
@@ -250,7 +255,10 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     for (int i = 0; i < n_items; ++i) {
         const vq_mx_item& it = items[i];
         int o;
-        if (it.out_scale && it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes && !it.dequant) o = OUT_FLOAT;
+        if (no_table) {
+            if (it.out_scale && !it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes && !it.dequant) o = OUT_SCALE;
+            else return 0;
+        } else if (it.out_scale && it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes && !it.dequant) o = OUT_FLOAT;
         else if (it.codes && it.scale_f32 && !it.out_scale && !it.out_codes && !it.dequant && (code_bits == 4 || code_bits == 8))
             o = code_bits == 4 ? OUT_PACK4 : OUT_PACK8;
         else return 0;
@@ -262,8 +270,8 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
         out = o;
         total += it.n;
     }
-    if (out != OUT_FLOAT && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
-    if (out != OUT_FLOAT && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
+    if (out != OUT_FLOAT && out != OUT_SCALE && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
+    if (out != OUT_FLOAT && out != OUT_SCALE && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
     if (n_items > 1 && !workspace) return 0;
     if (total == 0) return 1;
 
