@@ -41,9 +41,16 @@ def _install_torchao_stub():
     sys.modules["torchao.quantization.pt2e"] = p
 
 
+def default_reference_root():
+    """``$VOYAGER_REFERENCE``, else a ``reference`` checkout next to this repository."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    repo = os.path.dirname(os.path.dirname(here))
+    return os.environ.get("VOYAGER_REFERENCE", os.path.join(os.path.dirname(repo), "reference"))
+
+
 def import_reference(root=None):
     """Returns a dict of the upstream modules needed to generate fixtures."""
-    root = root or os.environ.get("VOYAGER_REFERENCE", "/root/reference")
+    root = root or default_reference_root()
     src = os.path.join(root, "src", "voyager_compiler")
     if not os.path.isdir(src):
         raise FileNotFoundError(f"upstream checkout not found at {root}")

@@ -1,6 +1,7 @@
 """Generate the golden fixtures in this directory by running the UPSTREAM voyager-compiler code.
 
-Run once, where an upstream checkout is available (``VOYAGER_REFERENCE`` or ``/root/reference``):
+Run once, where an upstream checkout is available (``$VOYAGER_REFERENCE``, or a ``reference``
+directory next to this repository):
 
     python tests/golden/make_golden.py
 
@@ -24,7 +25,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
-from _reference_import import import_reference  # noqa: E402
+from _reference_import import default_reference_root, import_reference  # noqa: E402
 
 TABLE_DTYPES = [
     "int8", "int4", "int6", "int2", "uint8", "uint4", "e4m3", "e5m2", "posit8_1", "posit8_0",
@@ -92,8 +93,7 @@ def main():
     # arbitrary codebooks through upstream lcq.codebook_qmap semantics.  lcq.py imports the
     # exporter stack, so its six-line function body is evaluated here from its source text.
     import ast
-    src = open(os.path.join(os.environ.get("VOYAGER_REFERENCE", "/root/reference"),
-                            "src/voyager_compiler/quantization/lcq.py")).read()
+    src = open(os.path.join(default_reference_root(), "src/voyager_compiler/quantization/lcq.py")).read()
     fn = next(n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == "codebook_qmap")
     ns = {"torch": torch}
     exec(compile(ast.Module([fn], []), "lcq_codebook_qmap", "exec"), ns)

@@ -6,8 +6,8 @@ import textwrap
 
 import pytest
 
-REF = os.environ.get("VOYAGER_REFERENCE", "/root/reference")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("VOYAGER_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "src", "voyager_compiler")),
                                 reason="upstream checkout not available")
