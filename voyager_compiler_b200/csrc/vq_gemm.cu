@@ -25,7 +25,7 @@
 // CTA-pair kernel (vq_gemm2.cu): 256 x 256 tiles on two CTAs; tensor maps with 128-row boxes
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
-                        cudaStream_t st);
+                        cudaStream_t st, const CUtensorMap* tmSA = nullptr, const CUtensorMap* tmSB = nullptr);
 
 namespace {
 
@@ -292,17 +292,18 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [rows, K] bf16 row-major tensor, tile box_rows x 64 elements, 128-byte swizzle, zero fill
-int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+// [rows, K] bf16 row-major tensor, zero fill outside; operand tiles: box_rows x 64 elements with the
+// 128-byte swizzle; scale tiles (box_cols = 16): box_rows x 16 elements, rows of 32 bytes, no swizzle
+int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows, int box_cols = BK) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return vq_set_error(VQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == BK ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return vq_set_error(VQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return 0;
 }
@@ -381,6 +382,18 @@ int vq_linear_mx(const void* a_codes, const void* a_scale, const void* b_codes, 
     VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "%s: sizes must be below 2^31", name);
     VQ_REQUIRE((uintptr_t)a_codes % 16 == 0 && (uintptr_t)b_codes % 16 == 0, "%s: code tensors must be 16-byte aligned", name);
     CUtensorMap tmA, tmB;
+    const char* tile = getenv("VOYAGER_B200_GEMM_TILE");
+    if (M > 128 && K % 256 == 0 && (uintptr_t)a_scale % 16 == 0 && (uintptr_t)b_scale % 16 == 0 &&
+        !(tile && !strcmp(tile, "1cta"))) {
+        // CTA-pair kernel: codes and block scales arrive by TMA, eight warps per CTA dequantise in place
+        CUtensorMap tmSA, tmSB;
+        if (int rc = make_map(&tmA, a_codes, M, K, 128)) return rc;
+        if (int rc = make_map(&tmB, b_codes, N, K, 128)) return rc;
+        if (int rc = make_map(&tmSA, a_scale, M, K / 32, 128, 16)) return rc;
+        if (int rc = make_map(&tmSB, b_scale, N, K / 32, 128, 16)) return rc;
+        void* ys[1] = {Y};
+        return vq_gemm_pair_launch(tmA, tmB, ys, 1, N, 0, bias, M, N, K, status, (cudaStream_t)stream, &tmSA, &tmSB);
+    }
     memset(&tmA, 0, sizeof(tmA));
     memset(&tmB, 0, sizeof(tmB));
     GemmParams p{};

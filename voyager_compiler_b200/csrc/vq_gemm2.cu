@@ -29,6 +29,9 @@ constexpr int PSTAGES = 5;
 constexpr int PA_BYTES = PM * PK * 2, PB_BYTES = PNH * PK * 2, PSTAGE_BYTES = PA_BYTES + PB_BYTES;
 // epilogue staging: 128 rows x 128 columns of bf16, rows padded by 16 bytes against bank conflicts
 constexpr int OUT_COLS = 128, OUT_ROW_BYTES = OUT_COLS * 2 + 16, OUT_BYTES = PM * OUT_ROW_BYTES;
+// fused variant: block scales arrive in groups of 8 k-steps: 128 rows x 16 scales (32 bytes per row)
+// for A and for B, double buffered
+constexpr int SC_GROUP = 8, SC_TILE = 128 * 32, SC_BUF = 2 * SC_TILE, SC_BUFS = 2;
 constexpr long long PWAIT = 4000000000ll;
 constexpr int P_MAX_OUT = 8;
 
@@ -41,6 +44,7 @@ struct PairParams {
     int tiles_m, tiles_n;      // in units of 256 x 256
     int bulk_ok;               // output rows are 16-byte aligned: the epilogue may use bulk stores
     int32_t* status;
+    int blocks_per_row;        // fused variant: the operand maps cover the CODES, two more maps the [rows, K/32] scales
 };
 
 // shared -> global asynchronous bulk copy of `bytes` (multiple of 16) issued by one thread
@@ -55,14 +59,22 @@ __device__ __forceinline__ void record_fail(int32_t* status, int code) {
     if (status) atomicCAS(status, 0, code);
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PairParams p) {
+// FUSED: the tile loads bring quantized codes; eight extra warps per CTA multiply them by their block
+// scales in place (shared memory -> registers -> shared memory, one bf16 rounding per product) before
+// the stage is handed to the MMA issuer.  Extra barrier raw[s] (per CTA): completion of the CTA's own
+// tile loads; full[s] then counts one arrival per CTA of the pair instead of bytes.
+template <bool FUSED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 448 : 192, 1)
+mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const PairParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t out_base = base + PSTAGES * PSTAGE_BYTES;      // epilogue staging buffer
+    const uint32_t sc_base = base + PSTAGES * PSTAGE_BYTES;       // fused: block-scale tiles, one pair per stage
+    const uint32_t out_base = sc_base + (FUSED ? SC_BUFS * SC_BUF : 0);   // epilogue staging buffer
     const uint32_t bar_base = out_base + OUT_BYTES;
     const uint32_t FULL0 = bar_base, EMPTY0 = bar_base + 8u * PSTAGES, TFULL0 = bar_base + 16u * PSTAGES,
-                   TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u;
+                   TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u, RAW0 = SLOT + 8u,
+                   SCF0 = RAW0 + 8u * PSTAGES, SCE0 = SCF0 + 8u * SC_BUFS;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
@@ -72,12 +84,15 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PSTAGES; ++s) {
-            tc::mbar_init(FULL0 + 8u * s, 1);
+            tc::mbar_init(FULL0 + 8u * s, FUSED ? 2 : 1);
             tc::mbar_init(EMPTY0 + 8u * s, 1);
+            tc::mbar_init(RAW0 + 8u * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(TFULL0 + 8u * s, 1);
             tc::mbar_init(TEMPTY0 + 8u * s, 8);
+            tc::mbar_init(SCF0 + 8u * s, 1);
+            tc::mbar_init(SCE0 + 8u * s, 8);
         }
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&tmA);
@@ -98,17 +113,32 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // ------------------------------------------------------------------ tile loads (both CTAs)
         if (lane == 0) {
             int stage = 0;
-            uint32_t phase = 0;
+            uint32_t phase = 0, group = 0;
             bool ok = true;
             for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
                 const int m0 = (tile % p.tiles_m) * 256 + (int)rank * PM;
                 const int n0 = (tile / p.tiles_m) * PN + (int)rank * PNH;
                 for (int k = 0; k < num_k; ++k) {
+                    if (FUSED && (k % SC_GROUP) == 0) {
+                        // block scales of the next 8 k-steps (16 per row) into the free scale buffer
+                        const uint32_t b = group & 1u, ph = (group >> 1) & 1u;
+                        if (!tc::mbar_wait(SCE0 + 8u * b, ph ^ 1u, PWAIT)) { ok = false; break; }
+                        tc::mbar_expect_tx(SCF0 + 8u * b, SC_BUF);
+                        tc::tma_load_2d(sc_base + b * SC_BUF, &tmSA, k * 2, m0, SCF0 + 8u * b);
+                        tc::tma_load_2d(sc_base + b * SC_BUF + SC_TILE, &tmSB, k * 2, n0, SCF0 + 8u * b);
+                        ++group;
+                    }
                     if (!tc::mbar_wait_cluster(EMPTY0 + 8u * stage, phase ^ 1u, PWAIT)) { ok = false; break; }
-                    const uint32_t leader_full = tc::map_to_cta(FULL0 + 8u * stage, 0);
-                    if (rank == 0) tc::mbar_expect_tx(FULL0 + 8u * stage, 2 * PSTAGE_BYTES);
-                    tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES, &tmA, k * PK, m0, leader_full);
-                    tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES + PA_BYTES, &tmB, k * PK, n0, leader_full);
+                    if (FUSED) {
+                        tc::mbar_expect_tx(RAW0 + 8u * stage, PSTAGE_BYTES);
+                        tc::tma_load_2d(base + stage * PSTAGE_BYTES, &tmA, k * PK, m0, RAW0 + 8u * stage);
+                        tc::tma_load_2d(base + stage * PSTAGE_BYTES + PA_BYTES, &tmB, k * PK, n0, RAW0 + 8u * stage);
+                    } else {
+                        const uint32_t leader_full = tc::map_to_cta(FULL0 + 8u * stage, 0);
+                        if (rank == 0) tc::mbar_expect_tx(FULL0 + 8u * stage, 2 * PSTAGE_BYTES);
+                        tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES, &tmA, k * PK, m0, leader_full);
+                        tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES + PA_BYTES, &tmB, k * PK, n0, leader_full);
+                    }
                     if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -142,6 +172,62 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if (!ok) record_fail(p.status, 12);
         }
+    } else if (FUSED && warp >= 6) {
+        // ------------------------------------------------------------------ in-place dequantisation (8 warps per CTA)
+        // 8 warps: threads 0..127 own the 128 A rows, threads 128..255 the 128 B rows of this CTA
+        const int t = (warp - 6) * 32 + lane;
+        const int r = t & 127;
+        const bool is_b = t >= 128;
+        int stage = 0;
+        uint32_t phase = 0, group = 0;
+        bool ok = true;
+        const uint32_t leader_full_base = tc::map_to_cta(FULL0, 0);
+        for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
+            for (int k = 0; k < num_k; ++k) {
+                if ((k % SC_GROUP) == 0) {                       // a new group of block scales
+                    if (lane == 0) ok = tc::mbar_wait(SCF0 + 8u * (group & 1u), (group >> 1) & 1u, PWAIT);
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    if (!ok) break;
+                }
+                if (lane == 0) ok = tc::mbar_wait(RAW0 + 8u * stage, phase, PWAIT);
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                if (!ok) break;
+                // this row's two block scales for this k-step (rows outside the matrix were zero filled)
+                uint32_t sc;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc)
+                             : "r"(sc_base + (group & 1u) * SC_BUF + (is_b ? SC_TILE : 0) + (uint32_t)r * 32u + (uint32_t)(k % SC_GROUP) * 4u));
+                const uint32_t s_lo = (sc & 0xFFFFu) * 0x00010001u, s_hi = (sc >> 16) * 0x00010001u;
+                const uint32_t row_addr = base + stage * PSTAGE_BYTES + (is_b ? PA_BYTES : 0) + (uint32_t)r * 128u;
+                uint32_t v[8][4];
+#pragma unroll
+                // logical chunk c sits at physical chunk c ^ (r & 7) (128-byte swizzle); walking the
+                // logical index keeps the 8 lanes of a quarter-warp on 8 different bank groups
+                for (int c = 0; c < 8; ++c)
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(v[c][0]), "=r"(v[c][1]), "=r"(v[c][2]), "=r"(v[c][3])
+                                 : "r"(row_addr + (uint32_t)((c ^ (r & 7)) << 4)));
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t s2 = (c >> 2) ? s_hi : s_lo;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v[c][j]) : "r"(s2));
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + (uint32_t)((c ^ (r & 7)) << 4)),
+                                 "r"(v[c][0]), "r"(v[c][1]), "r"(v[c][2]), "r"(v[c][3]) : "memory");
+                tc::fence_proxy_async();
+                // one cluster-scope arrival per CTA and k-step: the 8 warps meet on a named barrier first
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (t == 0) tc::mbar_arrive_cluster(leader_full_base + 8u * stage);
+                if ((k % SC_GROUP) == SC_GROUP - 1 || k == num_k - 1) {      // done with this scale buffer
+                    if (lane == 0) tc::mbar_arrive(SCE0 + 8u * (group & 1u));
+                    ++group;
+                }
+                if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok && lane == 0) record_fail(p.status, 14);
     } else {
         // ------------------------------------------------------------------ epilogue (4 warps per CTA)
         const int q = warp & 3;
@@ -229,10 +315,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 }  // namespace
 
-// Launches the CTA-pair GEMM.  The tensor maps must have 128-row boxes for both operands.
+// Launches the CTA-pair GEMM.  The tensor maps must have 128-row boxes for both operands.  With
+// a_scale / b_scale the maps cover code tensors and dequantisation happens inside the kernel.
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
-                        cudaStream_t st) {
+                        cudaStream_t st, const CUtensorMap* tmSA, const CUtensorMap* tmSB) {
+    const bool fused = tmSA != nullptr && tmSB != nullptr;
     PairParams p{};
     for (int d = 0; d < n_outputs; ++d) p.Y[d] = reinterpret_cast<uint16_t*>(Ys[d]);
     p.n_outputs = n_outputs;
@@ -246,14 +334,22 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     p.bulk_ok = (ldy % 8 == 0 && col_offset % 8 == 0) ? 1 : 0;
     for (int d = 0; d < n_outputs; ++d)
         if ((uintptr_t)Ys[d] % 16) p.bulk_ok = 0;
+    p.blocks_per_row = (int)(K / 32);
     const int n_tiles = p.tiles_m * p.tiles_n;
     const int sms = vq_sm_count();
     int pairs = sms / 2;
     if (n_tiles < pairs) pairs = n_tiles;
-    const size_t smem = (size_t)PSTAGES * PSTAGE_BYTES + OUT_BYTES + 256 + 1024;
+    const size_t smem = (size_t)PSTAGES * PSTAGE_BYTES + (fused ? SC_BUFS * SC_BUF : 0) + OUT_BYTES + 256 + 1024;
     if ((int)smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "device offers too little shared memory for the pair GEMM");
-    VQ_CUDA(cudaFuncSetAttribute(mx_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    mx_gemm_pair_kernel<<<pairs * 2, 192, smem, st>>>(tmA, tmB, p);
+    if (fused) {
+        auto k = mx_gemm_pair_kernel<true>;
+        VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
+    } else {
+        auto k = mx_gemm_pair_kernel<false>;
+        VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<pairs * 2, 192, smem, st>>>(tmA, tmB, tmA, tmB, p);
+    }
     VQ_LAUNCH_CHECK("mx_gemm_pair_kernel");
     return 0;
 }
