@@ -450,7 +450,13 @@ def run_elementwise(args):
         lambda: mq.quantize_tensors_mx([xl], q8, 32, 127.0, True, code_bits=8, want_exp=True), nl * (4 + 1 + 4 / 32 + 1 / 32), 5)
     xlb = xl.to(torch.bfloat16)
     res["large_quantize_mx_bf16_dropin_16384x16384"] = timed(lambda: Q.quantize_mx(xlb, q8, (-1,), 32, 127.0, True), nl * (2 + 2 + 2 / 32), 5)
-    del xl, sl, cl, xlb
+    pk = mq.quantize_tensors_mx([xl], q8, 32, 127.0, True, code_bits=8, want_exp=True)[0]
+    res["large_dequantize_packed_int8_e8_to_fp32_16384x16384"] = timed(
+        lambda: mq.dequantize_packed(pk, torch.float32, use_exponent=True), nl * (1 + 1 / 32 + 4), 5)
+    pk4 = mq.quantize_tensors_mx([xlb], tab("nf4"), 64, 1.0, code_bits=4)[0]
+    res["large_dequantize_packed_nf4_to_bf16_16384x16384"] = timed(
+        lambda: mq.dequantize_packed(pk4, torch.bfloat16), nl * (0.5 + 4 / 64 + 2), 5)
+    del xl, sl, cl, xlb, pk, pk4
     vb.set_table_policy(allow_int=False)
     res["cfg1_quantize_mx_fp32_dropin_lut"] = timed(lambda: Q.quantize_mx(x, q8, (-1,), 32, 127.0, True), n * (4 + 4 + 4 / 32))
     vb.set_table_policy(allow_int=True)

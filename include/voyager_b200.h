@@ -230,6 +230,16 @@ VQ_API int vq_quantize_mx_multi_static(const vq_mx_item* items, int n_items, int
                                        const vq_table* scale_table, const vq_table* table, int code_bits,
                                        void* stream);
 
+/* out[i] = levels[code[i]] * scale[i / block] in `dtype` (one rounding), from the packed views that
+ * vq_quantize_mx / vq_quantize_mx_multi write: 8-bit codes (one per byte) or 4-bit codes (two per
+ * byte, even element in the low nibble), and per block either an fp32 scale or an E8 exponent
+ * (scale = 2^e).  `levels`: device array of n_levels fp32 values.  block must be a multiple of 16.
+ * The decode + scale half of `linear_mx`'s operand preparation, src/voyager_compiler/ops/quantized.py:313-326,
+ * and `dequantize`, :182-227, on packed storage. */
+VQ_API int vq_dequantize_packed(const uint8_t* codes, int code_bits, const float* levels, int n_levels,
+                                const float* scale_f32, const int8_t* exp_e8, int64_t n, int64_t block, void* out,
+                                int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

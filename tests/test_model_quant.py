@@ -97,6 +97,30 @@ def test_multi_tensor_int8_pow2_fp32_with_exponents():
 
 
 @pytest.mark.gpu
+def test_dequantize_packed_matches_reference_decode():
+    torch.manual_seed(3)
+    # int8 / pow2 / fp32 and bf16 outputs, through scales and through exponents
+    x = torch.randn(96, 256)
+    x[5] = 0
+    q = golden_table("int8")
+    (p,) = mq.quantize_tensors_mx([x.cuda()], q, 32, 127.0, True, code_bits=8, want_exp=True)
+    s_ref, c_ref = vo.quantize_mx(x, q, (-1,), 32, 127.0, True)
+    want = vo.dequantize(c_ref, s_ref, None, (-1,), 32)
+    # value equality: a two's-complement byte has no -0, which the float codes keep for tiny negatives
+    assert torch.equal(mq.dequantize_packed(p).cpu(), want)
+    assert torch.equal(mq.dequantize_packed(p, use_exponent=True).cpu(), want)    # all-zero block: 0 * 2^-127 = 0
+    assert torch.equal(mq.dequantize_packed(p, torch.bfloat16).cpu(), want.to(torch.bfloat16))
+    # nf4 / 4-bit / amax scale: equals weight_code[idx] * expand(scale) of linear_mx's operand decode
+    w = (torch.randn(40, 192) * 0.02).to(torch.bfloat16)
+    tab_i, levels = index_table_of("nf4")
+    (p4,) = mq.quantize_tensors_mx([w.cuda()], golden_table("nf4"), 64, 1.0, code_bits=4)
+    s4 = vo.mx_scale(w, (-1,), 64, 1.0, False)
+    i4 = vo.quantize(w, s4, None, (-1,), 64, tab_i)
+    want4 = levels[i4.long()].to(torch.bfloat16) * vo.spread_scale(s4, w.shape, 64)
+    assert same_bits(mq.dequantize_packed(p4, torch.bfloat16), want4)[0]
+
+
+@pytest.mark.gpu
 def test_host_pipeline_round_trip():
     torch.manual_seed(5)
     host = [(torch.randn(512, 1024) * 0.02).to(torch.bfloat16).pin_memory() for _ in range(5)]

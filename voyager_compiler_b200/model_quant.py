@@ -22,7 +22,7 @@ import torch
 from . import _lib
 from .qtables import exp_tables, table_handle
 
-__all__ = ["PackedMX", "quantize_tensors_mx", "unpack_codes", "dequantize_packed_reference", "shard_plan",
+__all__ = ["PackedMX", "quantize_tensors_mx", "dequantize_packed", "unpack_codes", "dequantize_packed_reference", "shard_plan",
            "HostPipeline"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
@@ -117,6 +117,28 @@ def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant
                 0 if float_outputs else code_bits, ws.data_ptr(), ws.numel(), stream), "quantize_tensors_mx")
             del keep
     return results
+
+
+def dequantize_packed(p: PackedMX, dtype=torch.float32, use_exponent: bool = False) -> torch.Tensor:
+    """``levels[code] * scale`` with the packed-storage kernel; ``use_exponent`` takes the E8
+    exponents instead of the fp32 scales (power-of-two scales only)."""
+    if dtype not in _DT:
+        raise NotImplementedError(f"dequantize_packed: dtype {dtype}")
+    dev = p.codes.device
+    out = torch.empty(p.shape, dtype=dtype, device=dev)
+    n = out.numel()
+    if n == 0:
+        return out
+    if use_exponent and p.exp_e8 is None:
+        raise ValueError("this PackedMX carries no exponents")
+    with torch.cuda.device(dev):
+        levels = p.levels.to(dev, torch.float32).contiguous()
+        rc = _lib.lib.vq_dequantize_packed(
+            p.codes.data_ptr(), p.code_bits, levels.data_ptr(), levels.numel(),
+            None if use_exponent else p.scale.data_ptr(), p.exp_e8.data_ptr() if use_exponent else None,
+            n, p.block, out.data_ptr(), _DT[dtype], torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(rc, "dequantize_packed")
+    return out
 
 
 def unpack_codes(p: PackedMX) -> torch.Tensor:
