@@ -66,7 +66,12 @@ typedef struct vq_table {
     uint8_t ninf_code;
     uint8_t nan_uniform;       /* LUT16: non-zero when every NaN input pattern has the same output, which
                                   lets the kernels use the hardware bf16 conversion (NaN -> 0x7FFF) */
-    uint8_t reserved[6];
+    uint8_t flat_tiny;         /* LUT16: non-zero when the table is constant over the patterns 0x0000..0x0400 and
+                                  over 0x8000..0x8400 (|value| <= 2^-119), so that the rounding of a quotient
+                                  in the subnormal range cannot change the result; lets bf16 kernels divide
+                                  by multiplying with a reciprocal without scanning for tiny elements.
+                                  0 is always safe. */
+    uint8_t reserved[5];
 } vq_table;
 
 /* Where the scale (and zero point) of element i lives (upstream `expand`,

@@ -150,3 +150,34 @@ def test_exp_tables_shape_and_bounds():
     # all-zero block: amax is replaced by 2^-126 -> 2^-132 (a subnormal) in fp32, and in bf16 too
     b32, s32 = qtables.derive_exp_tables_host(torch.float32, 6)
     assert s32[149 - 126] == np.float32(2.0 ** -132)
+
+
+def test_reciprocal_quotient_rounds_like_division_for_8bit_significands():
+    """The bf16 kernels compute x / scale as x * rcp(scale) and round to bf16.  For operands with
+    8-bit significands this equals rounding the IEEE fp32 quotient, for every reciprocal within one
+    ulp of 1 / scale: checked here over all significand pairs (the argument is exponent-free)."""
+    import numpy as np
+    mx = np.arange(1, 256, dtype=np.float32)[:, None]
+    ms = np.arange(128, 256, dtype=np.float32)[None, :]
+    exact = torch.from_numpy((mx / ms).astype(np.float32)).to(torch.bfloat16)
+    r = (np.float32(1.0) / ms).astype(np.float32)
+    for cand in (r, np.nextafter(r, np.float32(0)), np.nextafter(r, np.float32(2))):
+        q = torch.from_numpy((mx * cand).astype(np.float32)).to(torch.bfloat16)
+        assert torch.equal(q.view(torch.int16), exact.view(torch.int16))
+    # distance of every quotient from the nearest bf16 rounding boundary, relative: > 2^-17
+    q64 = (mx.astype(np.float64) / ms.astype(np.float64))
+    f = q64 / 2.0 ** np.floor(np.log2(q64))              # in [1, 2)
+    t = f * 256.0                                        # boundaries are the odd integers
+    odd = 2.0 * np.floor(t / 2.0) + 1.0
+    assert (np.abs(t - odd) / t).min() > 2.0 ** -17
+
+
+def test_flat_tiny_flag_of_tables():
+    from voyager_compiler_b200 import tables
+    assert tables.analyse_table(tables.build_table("nf4")).flat_tiny
+    assert tables.analyse_table(tables.build_table("int8")).flat_tiny
+    assert tables.analyse_table(tables.build_table("posit8_1")).flat_tiny
+    # -0 maps to +0 but a tiny negative to -0: the zone is not constant, the kernels keep the scan
+    assert not tables.analyse_table(tables.build_table("fp8_e4m3")).flat_tiny
+    ident = np.arange(1 << 16, dtype=np.uint16)
+    assert not tables.analyse_table(ident).flat_tiny

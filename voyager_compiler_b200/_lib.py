@@ -25,7 +25,7 @@ class VqTable(C.Structure):
         ("run_keys", C.c_void_p), ("run_vals", C.c_void_p), ("run_codes", C.c_void_p),
         ("nan_val", C.c_uint16), ("pinf_val", C.c_uint16), ("ninf_val", C.c_uint16),
         ("nan_code", C.c_uint8), ("pinf_code", C.c_uint8), ("ninf_code", C.c_uint8),
-        ("nan_uniform", C.c_uint8), ("reserved", C.c_uint8 * 6),
+        ("nan_uniform", C.c_uint8), ("flat_tiny", C.c_uint8), ("reserved", C.c_uint8 * 5),
     ]
 
 

@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(1024, 1) ew_fast_kernel(const EwFastParams p) 
     ft.lo = p.tab.lo;
     ft.hi = p.tab.hi;
     ft.lo_is_zero = (p.tab.lo == 0.0f) ? 1 : 0;
+    ft.flat_tiny = p.tab.flat_tiny;
     if (SM && TK == TK_LUT && OP != EW_DEQUANT) {
         const uint4* src = reinterpret_cast<const uint4*>(p.tab.lut16);
         for (int i = threadIdx.x; i < 8192; i += blockDim.x) smem[i] = __ldg(src + i);
@@ -77,11 +78,10 @@ __global__ void __launch_bounds__(1024, 1) ew_fast_kernel(const EwFastParams p) 
             } else {
                 bool refine = false;
                 if (sizeof(T) == 2) {
-                    // reciprocal path only when no element is tiny and |x / s| stays far from overflow
-                    bool safe;
-                    const uint32_t am = chunk_amax<T>(x[u], safe);
-                    const int ex_a = (int)((am >> 23) & 0xFFu), ex_s = (int)((__float_as_uint(s) >> 23) & 0xFFu);
-                    refine = safe && am < 0x7F800000u && (ex_a - ex_s) < 100;
+                    // reciprocal path when the quotients stay normal: always for a table that is flat
+                    // over the tiny patterns, otherwise when no non-zero element is tiny
+                    refine = true;
+                    if (!ft.flat_tiny) chunk_amax<T>(x[u], refine, true);
                 }
                 fast_chunk<T, TK, OUT_FLOAT, SM>(ft, x[u], s, refine, (size_t)ci, out, nullptr);
             }

@@ -11,14 +11,16 @@
 // x / scale without an IEEE division per element:
 //   * scale is a power of two with a normal reciprocal: x * (1/scale) is the same correctly
 //     rounded value (exact scaling).
-//   * bf16 data, any scale: r = rcp.approx(scale), q0 = x*r, e = fma(-q0, scale, x),
-//     q = fma(e, r, q0).  Operands have 8-bit significands, so the exact quotient is either
-//     exactly representable (then q is exact: the residual e is exact and the correction lands on
-//     it) or at least 2^-17 (relative) away from every bf16 rounding boundary, far more than the
-//     ~2^-23 error of q; rounding q to bf16 therefore equals rounding the IEEE fp32 quotient to
-//     bf16, which is what the CPU reference computes.  Used only when the scale comes straight
-//     from the block maximum (so |q| stays bounded) and the scale and every non-zero element of
-//     the chunk are at least 2^-60 away from the subnormal range, so that e is computed exactly.
+//   * bf16 data, any scale: q = x * rcp.approx(scale).  Both operands have significands of at
+//     most 8 bits, x = mx * 2^a and scale = ms * 2^b with mx, ms <= 255.  A bf16 rounding boundary
+//     is an odd multiple (2k+1) >= 257 of half an ulp; mx * 2^j * 256 = (2k+1) * ms has no solution
+//     (the odd part of the right side exceeds 255), and since both sides are integers the exact
+//     quotient stays at least 1 / (256 * ms) > 2^-17 (relative) away from every boundary, the
+//     overflow boundary included.  q carries a relative error below 2^-22 (rcp.approx is within one
+//     ulp), so rounding q to bf16 equals rounding the IEEE fp32 quotient to bf16, which is what the
+//     CPU reference computes.  The argument needs q to be a normal number: the path is taken when
+//     the scale lies in [2^-63, 2^63] and either the table cannot tell apart quotients below 2^-119
+//     (`flat_tiny`) or no non-zero element of the chunk lies below 2^-60.
 //   * everything else: __fdiv_rn.
 #pragma once
 #include "vq_mx_body.cuh"
@@ -63,7 +65,7 @@ __device__ __forceinline__ float rcp_approx(float s) {
 // |x| maximum of a chunk as fp32 bits.  For bf16 also whether the reciprocal path is safe for this
 // chunk: no non-zero element below 2^-60 (pattern 0x2180).
 template <typename T>
-__device__ __forceinline__ uint32_t chunk_amax(const Chunk& x, bool& safe);
+__device__ __forceinline__ uint32_t chunk_amax(const Chunk& x, bool& safe, bool need_safe);
 // max(|a|, |b|) / min(|a|, |b|) per bf16 half; the sign bit of the result is garbage (xor of the
 // input signs) and is masked off at the end.  .NaN: a NaN input gives NaN (0x7FFF), as torch.max.
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
@@ -78,13 +80,15 @@ __device__ __forceinline__ uint32_t absmin_bf16x2(uint32_t a, uint32_t b) {
 }
 
 template <>
-__device__ __forceinline__ uint32_t chunk_amax<bf16_t>(const Chunk& x, bool& safe) {
+__device__ __forceinline__ uint32_t chunk_amax<bf16_t>(const Chunk& x, bool& safe, bool need_safe) {
     const uint32_t* w = x.w;
     uint32_t mx = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(w[0], w[1]), absmax_bf16x2(w[2], w[3])),
                                 absmax_bf16x2(absmax_bf16x2(w[4], w[5]), absmax_bf16x2(w[6], w[7])));
+    mx &= 0x7FFF7FFFu;
+    safe = true;
+    if (!need_safe) return max(mx & 0xFFFFu, mx >> 16) << 16;
     uint32_t mn = absmin_bf16x2(absmin_bf16x2(absmin_bf16x2(w[0], w[1]), absmin_bf16x2(w[2], w[3])),
                                 absmin_bf16x2(absmin_bf16x2(w[4], w[5]), absmin_bf16x2(w[6], w[7])));
-    mx &= 0x7FFF7FFFu;
     mn &= 0x7FFF7FFFu;
     // smallest magnitude at least 2^-60 (pattern 0x2180): the reciprocal path is exact.  A NaN makes
     // the minimum unreliable, but then the block scale is 1 (a power of two) and the path is unused.
@@ -99,7 +103,7 @@ __device__ __forceinline__ uint32_t chunk_amax<bf16_t>(const Chunk& x, bool& saf
     return max(mx & 0xFFFFu, mx >> 16) << 16;
 }
 template <>
-__device__ __forceinline__ uint32_t chunk_amax<float>(const Chunk& x, bool& safe) {
+__device__ __forceinline__ uint32_t chunk_amax<float>(const Chunk& x, bool& safe, bool) {
     safe = false;
     uint32_t m = 0;
 #pragma unroll
@@ -132,6 +136,7 @@ struct FastTab {
     const uint8_t* lut8;
     float lo, hi;
     int lo_is_zero;
+    int flat_tiny;           // quotients below 2^-119 all give the same output: no scan for tiny elements
 };
 
 template <bool SM>
@@ -192,9 +197,7 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
         const float r = rcp_approx(s);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
-            float q0 = __fmul_rn(v[j], r);
-            float e = __fmaf_rn(-q0, s, v[j]);
-            v[j] = __fmaf_rn(e, r, q0);
+            v[j] = __fmul_rn(v[j], r);
         }
     } else {
 #pragma unroll

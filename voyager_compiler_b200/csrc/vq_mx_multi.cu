@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
     ft.lo = p.tab.lo;
     ft.hi = p.tab.hi;
     ft.lo_is_zero = (p.tab.lo == 0.0f) ? 1 : 0;
+    ft.flat_tiny = p.tab.flat_tiny;
     if (SM && TK == TK_LUT) {
         const bool wide = OUT == OUT_FLOAT;
         const uint4* src = reinterpret_cast<const uint4*>(wide ? (const void*)p.tab.lut16 : (const void*)p.tab.lut8);
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
         for (int u = 0; u < U; ++u) {
             const uint32_t ci = c0 + u * blockDim.x;
             bool safe;
-            uint32_t m = chunk_amax<T>(x[u], safe);
+            uint32_t m = chunk_amax<T>(x[u], safe, refine && !ft.flat_tiny);
             for (int o = 1; o < (1 << gs); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
             if (ci >= nchunk) continue;
             const float s = fast_scale<T, RULE>(p.rule, m);

@@ -14,50 +14,59 @@ struct PackedParams {
     const float* scale_f32;
     const int8_t* exp_e8;
     void* out;
-    uint32_t nchunk;        // chunks of 16 elements
-    uint32_t block16;       // block size / 16
+    uint32_t nword;         // 32-bit code words: 4 elements (8-bit codes) or 8 elements (4-bit codes)
+    uint32_t block_words;   // words per block
 };
 
-template <typename T, int BITS>
+// One 32-bit code word per thread and pass, so that a warp reads 128 contiguous bytes and writes
+// 256 B - 1 KB contiguous; UNROLL independent words per thread keep enough bytes in flight.
+template <typename T, int BITS, int UNROLL>
 __global__ void __launch_bounds__(512) dequant_packed_kernel(const PackedParams p) {
+    constexpr int EPW = 32 / BITS;
     __shared__ float lv[256];
     for (int i = threadIdx.x; i < 256; i += blockDim.x) lv[i] = i < p.n_levels ? __ldg(p.levels + i) : 0.0f;
     __syncthreads();
     T* out = reinterpret_cast<T*>(p.out);
-    const uint32_t nthreads = gridDim.x * blockDim.x;
-    for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < p.nchunk; c += nthreads) {
-        uint32_t w[4];
-        if (BITS == 8) {
-            uint4 t = __ldcs(reinterpret_cast<const uint4*>(p.codes) + c);
-            w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
-        } else {
-            uint2 t = __ldcs(reinterpret_cast<const uint2*>(p.codes) + c);
-            w[0] = t.x; w[1] = t.y; w[2] = w[3] = 0;
-        }
-        const uint32_t b = c / p.block16;
-        float s;
-        if (p.scale_f32) s = __ldg(p.scale_f32 + b);
-        else {
-            const int e = __ldg(p.exp_e8 + b);
-            s = (e >= -126) ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(1u << (e + 149 < 0 ? 0 : e + 149));
-        }
-        float v[16];
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(p.codes);
+    const uint32_t span = blockDim.x * UNROLL;
+    for (uint32_t base = blockIdx.x * span + threadIdx.x; base < p.nword; base += gridDim.x * span) {
+        uint32_t w[UNROLL];
+        float s[UNROLL];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const uint32_t code = BITS == 8 ? (w[j >> 2] >> (8 * (j & 3))) & 0xFFu : (w[j >> 3] >> (4 * (j & 7))) & 0xFu;
-            v[j] = Arith<T>::rnd(__fmul_rn(lv[code], s));
+        for (int u = 0; u < UNROLL; ++u) {
+            const uint32_t c = base + u * blockDim.x;
+            if (c < p.nword) {
+                w[u] = __ldcs(words + c);
+                const uint32_t b = c / p.block_words;
+                if (p.scale_f32) s[u] = __ldg(p.scale_f32 + b);
+                else {
+                    const int e = __ldg(p.exp_e8 + b);
+                    s[u] = (e >= -126) ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(1u << (e + 149 < 0 ? 0 : e + 149));
+                }
+            }
         }
-        if (sizeof(T) == 4) {
-            float4* dst = reinterpret_cast<float4*>(out + (size_t)c * 16);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) __stcs(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-        } else {
-            uint32_t o[8];
+        for (int u = 0; u < UNROLL; ++u) {
+            const uint32_t c = base + u * blockDim.x;
+            if (c >= p.nword) break;
+            float v[EPW];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xFFFF0000u);
-            uint4* dst = reinterpret_cast<uint4*>(out + (size_t)c * 16);
-            __stcs(dst, make_uint4(o[0], o[1], o[2], o[3]));
-            __stcs(dst + 1, make_uint4(o[4], o[5], o[6], o[7]));
+            for (int j = 0; j < EPW; ++j) {
+                const uint32_t code = (w[u] >> (BITS * j)) & ((1u << BITS) - 1u);
+                v[j] = __fmul_rn(lv[code], s[u]);
+            }
+            if constexpr (sizeof(T) == 4) {
+                float4* dst = reinterpret_cast<float4*>(out + (size_t)c * EPW);
+#pragma unroll
+                for (int j = 0; j < EPW / 4; ++j) __stcs(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+            } else {
+                uint32_t o[EPW / 2];
+#pragma unroll
+                for (int j = 0; j < EPW / 2; ++j)      // one rounding of the fp32 product, two values per instruction
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(v[2 * j + 1]), "f"(v[2 * j]));
+                if constexpr (EPW == 8) __stcs(reinterpret_cast<uint4*>(out + (size_t)c * EPW), make_uint4(o[0], o[1], o[2], o[3]));
+                else __stcs(reinterpret_cast<uint2*>(out + (size_t)c * EPW), make_uint2(o[0], o[1]));
+            }
         }
     }
 }
@@ -80,19 +89,21 @@ extern "C" int vq_dequantize_packed(const uint8_t* codes, int code_bits, const f
     PackedParams p{};
     p.codes = codes; p.levels = levels; p.n_levels = n_levels;
     p.scale_f32 = scale_f32; p.exp_e8 = exp_e8; p.out = out;
-    p.nchunk = (uint32_t)(n / 16);
-    p.block16 = (uint32_t)(block / 16);
+    const int epw = 32 / code_bits;
+    p.nword = (uint32_t)(n / epw);
+    p.block_words = (uint32_t)(block / epw);
     const int sms = vq_sm_count();
     const int threads = 512;
-    int64_t want = ((int64_t)p.nchunk + threads - 1) / threads;
+    constexpr int UNROLL = 4;
+    int64_t want = ((int64_t)p.nword + threads * UNROLL - 1) / (threads * UNROLL);
     int blocks = (int)(want > (int64_t)sms * 4 ? (int64_t)sms * 4 : want);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == VQ_F32) {
-        if (code_bits == 8) dequant_packed_kernel<float, 8><<<blocks, threads, 0, st>>>(p);
-        else dequant_packed_kernel<float, 4><<<blocks, threads, 0, st>>>(p);
+        if (code_bits == 8) dequant_packed_kernel<float, 8, UNROLL><<<blocks, threads, 0, st>>>(p);
+        else dequant_packed_kernel<float, 4, UNROLL><<<blocks, threads, 0, st>>>(p);
     } else {
-        if (code_bits == 8) dequant_packed_kernel<bf16_t, 8><<<blocks, threads, 0, st>>>(p);
-        else dequant_packed_kernel<bf16_t, 4><<<blocks, threads, 0, st>>>(p);
+        if (code_bits == 8) dequant_packed_kernel<bf16_t, 8, UNROLL><<<blocks, threads, 0, st>>>(p);
+        else dequant_packed_kernel<bf16_t, 4, UNROLL><<<blocks, threads, 0, st>>>(p);
     }
     VQ_LAUNCH_CHECK("dequant_packed_kernel");
     return 0;

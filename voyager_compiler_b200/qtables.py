@@ -75,6 +75,7 @@ class TableHandle:
         self.c = _lib.VqTable()
         self.c.lut16 = self.lut16.data_ptr()
         self.c.nan_uniform = 1 if an.nan_consistent else 0
+        self.c.flat_tiny = 1 if an.flat_tiny else 0
         if an.is_int and _policy["allow_int"]:
             self.c.kind = _lib.TABLE_INT
             self.c.lo, self.c.hi = an.lo, an.hi

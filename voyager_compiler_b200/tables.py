@@ -319,6 +319,7 @@ class TableAnalysis:
     pinf_val: int                     # output pattern for +inf (entry 0x7F80)
     ninf_val: int                     # output pattern for -inf (entry 0xFF80)
     nan_consistent: bool              # every NaN input pattern maps to the same output
+    flat_tiny: bool = False           # constant over patterns 0..0x400 and over 0x8000..0x8400
 
 
 def analyse_table(lut16: np.ndarray) -> TableAnalysis:
@@ -351,7 +352,8 @@ def analyse_table(lut16: np.ndarray) -> TableAnalysis:
     else:
         n_runs = 0
     return TableAnalysis(lut16, is_int, lo, hi, n_runs, run_keys, run_vals, run_first, nan_val, int(lut16[0x7F80]),
-                         int(lut16[0xFF80]), nan_consistent)
+                         int(lut16[0xFF80]), nan_consistent,
+                         bool((canon[:0x401] == canon[0]).all() and (canon[0x8000:0x8401] == canon[0x8000]).all()))
 
 
 def code_table(lut16: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
