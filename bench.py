@@ -35,7 +35,7 @@ WORKLOAD = "cfg3: NF4 block-64 quantization of LLaMA-2-7B-shaped linear weights 
 # dram__bytes_read.sum + dram__bytes_write.sum of one mx_multi_kernel launch over the full
 # single-GPU workload: the 1-layer ncu capture summarised in profiles/mx_fast2_kernel_nf4_1layer.md
 # (500.5 MB) scaled by the elements processed; traffic grows in proportion to them.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 16.34e9
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 16.32e9
 
 
 def model_shapes(layers=32):

@@ -97,6 +97,36 @@ def test_multi_tensor_int8_pow2_fp32_with_exponents():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype,table,block,qmax,pow2,bits", [
+    (torch.bfloat16, "nf4", 64, 1.0, False, 4),
+    (torch.bfloat16, "int8", 32, 127.0, True, 8),
+    (torch.float32, "int8", 32, 127.0, True, 8),
+    (torch.float32, "int4", 128, 7.0, False, 8),
+    (torch.bfloat16, "fp8_e4m3", 16, 448.0, False, 8),
+])
+def test_large_jobs_match_the_oracle(dtype, table, block, qmax, pow2, bits):
+    """>= 2^22 elements: 1024-thread CTAs, several inner iterations per tile with the rotating
+    prefetch (ragged tails, an all-zero block, NaN and Inf included)."""
+    torch.manual_seed(4)
+    shapes = [(1024, 4096), (2049, 384), (3, 5, 128), (1, 128), (4099, 128)]
+    ws = [(torch.randn(s) * 0.02).to(dtype) for s in shapes]
+    ws[2][0, 0, :] = 0
+    ws[2][1, 1, 5] = float("nan")
+    ws[1][7, 100] = float("inf")
+    ws[4][4098, 127] = -3.0
+    tab_v = golden_table(table)
+    packed = mq.quantize_tensors_mx([w.cuda() for w in ws], tab_v, block, qmax, pow2, code_bits=bits, want_exp=pow2)
+    torch.cuda.synchronize()
+    for w, p in zip(ws, packed):
+        s_ref = vo.mx_scale(w, (-1,), block, qmax, pow2)
+        assert same_bits(p.scale, s_ref.float())[0]
+        v_ref = vo.quantize(w, s_ref, None, (-1,), block, tab_v).float()
+        got = p.levels[mq.unpack_codes(p).cpu().long().clamp(max=p.levels.numel() - 1)]
+        ok = ~torch.isnan(v_ref)
+        assert torch.equal(got[ok], v_ref[ok])
+
+
+@pytest.mark.gpu
 def test_dequantize_packed_matches_reference_decode():
     torch.manual_seed(3)
     # int8 / pow2 / fp32 and bf16 outputs, through scales and through exponents
