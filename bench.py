@@ -476,6 +476,17 @@ def run_elementwise(args):
     s4 = w4.abs().amax(dim=1, keepdim=True)
     res["cfg4_quantize_codebook16_perrow_11008x4096"] = timed(lambda: Q.quantize(w4, s4, None, None, None, cb), w4.numel() * 8)
     res["vmap_fp32_posit8_11008x4096"] = timed(lambda: Q.vmap(w4, qp), w4.numel() * 8)
+    # cfg4: per-output-channel 16-entry quantile codebooks, W[11008,4096] fp32 ~ Student-t(5) * 0.02
+    from voyager_compiler_b200 import codebook
+    torch.manual_seed(3)
+    wt = (torch.distributions.StudentT(5.0).sample((11008, 4096)) * 0.02).to(dev)
+    lv = codebook.row_quantile_levels(wt, 16)                      # the fit: torch.quantile, not timed
+    res["cfg4_row_codebook16_search_fp32_rule_11008x4096"] = timed(
+        lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=False), wt.numel() * 9 + lv.numel() * 4)
+    res["cfg4_row_codebook16_search_reference_rule_11008x4096"] = timed(
+        lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=True), wt.numel() * 9 + lv.numel() * 4)
+    res["cfg4_row_codebook16_indices_only_11008x4096"] = timed(
+        lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=False, want_values=False), wt.numel() * 5 + lv.numel() * 4)
     for k, v in res.items():
         v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]
     print(json.dumps({"workload": "element-wise configs (cfg1, cfg2, cfg4 shapes)", "results": res, "peak_hbm_gbs": peaks["hbm_gbs"],

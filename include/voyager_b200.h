@@ -245,6 +245,22 @@ VQ_API int vq_dequantize_packed(const uint8_t* codes, int code_bits, const float
                                 const float* scale_f32, const int8_t* exp_e8, int64_t n, int64_t block, void* out,
                                 int dtype, void* stream);
 
+/* Per-row codebook quantization: x is [rows, K] (dtype f32 or bf16, row-major), levels is
+ * [rows, n_levels] fp32, each row sorted ascending, n_levels <= 256.  For every element the index of
+ * the nearest level of its row goes to idx_out (uint8 [rows, K], may be NULL) and that level to
+ * deq_out (same dtype as x, may be NULL).  The rule is upstream `codebook_qmap`,
+ * src/voyager_compiler/quantization/lcq.py:270-291, applied per row: clamp to the codebook range,
+ * |x - level| in fp32, the first minimum wins, NaN -> index 0.  round_bf16 != 0 rounds the element to
+ * bf16 before the search and the returned level to bf16, which is what that table followed by `vmap`
+ * (src/voyager_compiler/ops/quantized.py:98-121) gives; round_bf16 == 0 searches the fp32 element and
+ * returns the fp32 level.  Upstream codebooks are per tensor; a per-row codebook has no upstream op.
+ * `workspace`: device scratch of vq_row_codebook_workspace(rows, n_levels) bytes, 4-byte aligned (the
+ * per-row decision thresholds are written there by a first small kernel on the same stream). */
+VQ_API size_t vq_row_codebook_workspace(int64_t rows, int n_levels);
+VQ_API int vq_row_codebook(const void* x, int dtype, int64_t rows, int64_t K, const float* levels, int n_levels,
+                           int round_bf16, uint8_t* idx_out, void* deq_out, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

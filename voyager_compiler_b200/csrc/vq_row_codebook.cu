@@ -1,0 +1,383 @@
+// Per-row codebook quantization: every row of x[rows, K] has its own sorted codebook
+// levels[row, 0..n); each element gets the index of its nearest level and, optionally, that level.
+//
+// The rule is the upstream codebook rule (quantization/lcq.py:270-291: clamp to the codebook range,
+// |x - level| in fp32, first minimum wins, NaN -> entry 0) applied per row.  With `round_bf16` the
+// element is rounded to bf16 first and the returned level is rounded to bf16, which is what the
+// upstream 65 536-entry table + `vmap` (ops/quantized.py:98-121) compute for a per-tensor codebook;
+// without it the search runs on the fp32 element and returns the fp32 level.
+//
+// fp32 rounding of a difference is monotone in the true distance, so the argmin over all levels sits
+// at one of the two neighbours of x in the sorted row, and for each adjacent pair (a, b) the set of x
+// that prefer b, { x : fl(b - x) < fl(x - a) }, is an up-set: it has a smallest member, the pair's
+// THRESHOLD.  The index of the nearest level is therefore the number of thresholds <= x, which also
+// covers the clamp (below the first threshold -> 0, above the last -> n - 1) and NaN (no comparison
+// holds -> 0).
+//   1. row_thresholds_kernel: one thread per pair finds its threshold exactly, by bisection over the
+//      ordered fp32 bit patterns between a and b (<= 32 evaluations of the predicate), into a
+//      workspace of n floats per row.  Rows whose levels are so close that rounded distances of
+//      non-neighbours can coincide (a gap below 2^-20 of the row's range, duplicates included) are
+//      flagged instead.
+//   2. row_codebook_kernel: one warp per (row, segment); thresholds and levels of the row sit in the
+//      warp's slice of shared memory; per element a branchless lower bound over the thresholds (the
+//      first two probes from registers, the rest from shared memory) and one read of the level.
+//      Flagged rows take the direct form: lower bound over the levels, the two subtractions, and a
+//      walk down to the lowest index with the same rounded distance, as argmin does.
+// HBM bound: sizeof(T) read + 1 (index) + sizeof(T) (level) written per element.
+#include <math_constants.h>
+
+#include "vq_common.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;          // per CTA
+constexpr int kMaxLevels = 256;
+constexpr int kPasses = 4;       // 16-byte loads in flight per lane
+
+struct RowCbParams {
+    const void* x;
+    const float* levels;
+    float* work;                   // [rows, n_levels]: [0] = 1 when the row is flagged, [k] = threshold of pair (k-1, k)
+    uint8_t* idx;
+    void* deq;
+    int64_t rows, K;
+    int64_t seg_len;               // elements per work item, a multiple of 128 * kPasses
+    int64_t segs_per_row, n_items;
+    int n_levels;
+    int round_bf16;
+};
+
+// ---------------------------------------------------------------------------------------------
+// order-preserving map between fp32 values and unsigned keys
+__device__ __forceinline__ uint32_t key_of(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float value_of(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+__global__ void row_thresholds_kernel(const float* __restrict__ levels, float* __restrict__ work, int64_t rows, int n) {
+    // one thread per (row, k): k = 0 classifies the row, k >= 1 bisects the threshold of pair (k-1, k)
+    const int64_t id = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= rows * n) return;
+    const int64_t row = id / n;
+    const int k = (int)(id - row * n);
+    const float* lv = levels + row * n;
+    if (k == 0) {
+        const float lo = lv[0], hi = lv[n - 1];
+        float min_gap = CUDART_INF_F;
+        for (int i = 1; i < n; ++i) min_gap = fminf(min_gap, lv[i] - lv[i - 1]);
+        // a finite, strictly increasing row whose smallest gap is well above the rounding of any distance
+        const bool clear = n == 1 || (min_gap > (hi - lo) * 9.5367431640625e-07f && (hi - lo) < CUDART_INF_F);
+        work[id] = clear ? 0.0f : 1.0f;
+        return;
+    }
+    const float a = lv[k - 1], b = lv[k];
+    float t = CUDART_NAN_F;
+    if (a < b) {
+        uint32_t klo = key_of(a), khi = key_of(b);       // the predicate is false at a, true at b
+        while (khi - klo > 1u) {
+            const uint32_t mid = klo + ((khi - klo) >> 1);
+            const float x = value_of(mid);
+            if ((b - x) < (x - a)) khi = mid; else klo = mid;
+        }
+        t = value_of(khi);
+    }
+    work[id] = t;                                       // unused when the row is flagged
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shared-memory reads by 32-bit address with a compile-time byte offset.  volatile: the slots are
+// rewritten for every row, so the reads must stay where they are written (between the warp barriers).
+template <int OFF>
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ uint32_t bf16x2_of(float hi, float lo) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// Per-warp slot.  raw: [0] = -inf, [1 .. n] = the row's levels, then +inf.  rounded: the same
+// rounded to bf16.  thr: [0 .. n-2] = thresholds of the pairs (0,1) .. (n-2,n-1), then NaN (never
+// <= x).  Byte offsets between the arrays are compile-time constants.
+template <int LOG2N>
+struct Slot {
+    static constexpr int NP = 1 << LOG2N;
+    float raw[NP + 4];
+    float rounded[NP + 4];
+    float thr[NP + 4];
+    static constexpr int kRoundedFromRaw = (NP + 4) * 4;
+    static constexpr int kRawFromThr = -2 * (NP + 4) * 4 + 4;         // thr[i] -> raw[1 + i]
+    static constexpr int kRoundedFromThr = -(NP + 4) * 4 + 4;         // thr[i] -> rounded[1 + i]
+};
+
+template <int S>
+__device__ __forceinline__ float probe(uint32_t addr) { return lds_f32<((1 << S) - 1) * 4>(addr); }
+
+// Fast form: index = number of thresholds <= x.  Four elements in lockstep.
+template <int LOG2N, bool ROUNDED_OUT>
+__device__ __forceinline__ uint32_t count4(uint32_t tbase, float tm, float tl, float th, const float* x, float* val) {
+    uint32_t off[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        // probes thr[NP/2 - 1], then thr[NP/4 - 1] or thr[3 NP/4 - 1]: the same for the whole row
+        const bool up = tm <= x[j];
+        off[j] = up ? (4u << (LOG2N - 1)) : 0u;
+        off[j] += ((up ? th : tl) <= x[j]) ? (4u << (LOG2N - 2)) : 0u;
+    }
+#pragma unroll
+    for (int s = LOG2N - 3; s >= 0; --s) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float t;
+            switch (s) {                                // the probe offset must be an immediate
+                case 5: t = probe<5>(tbase + off[j]); break;
+                case 4: t = probe<4>(tbase + off[j]); break;
+                case 3: t = probe<3>(tbase + off[j]); break;
+                case 2: t = probe<2>(tbase + off[j]); break;
+                case 1: t = probe<1>(tbase + off[j]); break;
+                default: t = probe<0>(tbase + off[j]); break;
+            }
+            off[j] += (t <= x[j]) ? (4u << s) : 0u;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        val[j] = ROUNDED_OUT ? lds_f32<Slot<LOG2N>::kRoundedFromThr>(tbase + off[j]) : lds_f32<Slot<LOG2N>::kRawFromThr>(tbase + off[j]);
+    return (off[0] >> 2) + off[1] * 64u + off[2] * 16384u + off[3] * 4194304u;
+}
+
+// Direct form for flagged rows: lower bound over the levels, two subtractions, walk down over ties.
+template <int LOG2N, bool ROUNDED_OUT>
+__device__ __forceinline__ uint32_t nearest4(uint32_t base, float lo, float hi, const float* x, float* val) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float xc = fminf(fmaxf(x[j], lo), hi);    // a NaN becomes lo and lands on entry 0
+        uint32_t addr = base;                           // ends at the first level that is not below xc
+#pragma unroll
+        for (int s = LOG2N - 1; s >= 0; --s) {
+            float t;
+            switch (s) {
+                case 7: t = probe<7>(addr); break;
+                case 6: t = probe<6>(addr); break;
+                case 5: t = probe<5>(addr); break;
+                case 4: t = probe<4>(addr); break;
+                case 3: t = probe<3>(addr); break;
+                case 2: t = probe<2>(addr); break;
+                case 1: t = probe<1>(addr); break;
+                default: t = probe<0>(addr); break;
+            }
+            addr += (t < xc) ? (4u << s) : 0u;
+        }
+        const float r = lds_f32<0>(addr);               // r >= xc > l   (l = -inf left of level 0)
+        const float l = lds_f32<-4>(addr);
+        const float dr = r - xc, dl = xc - l;
+        uint32_t a = addr;
+        if (!(dr < dl)) {                               // a tie goes to the lower index
+            a -= 4u;
+            while (a > base && (xc - lds_f32<-4>(a)) == dl) a -= 4u;
+        }
+        val[j] = ROUNDED_OUT ? lds_f32<Slot<LOG2N>::kRoundedFromRaw>(a) : lds_f32<0>(a);
+        packed |= ((a - base) >> 2) << (8 * j);
+    }
+    return packed;
+}
+
+template <typename T, int LOG2N, bool VEC>
+__global__ void __launch_bounds__(kWarps * 32) row_codebook_kernel(const RowCbParams p) {
+    constexpr int NP = 1 << LOG2N;
+    __shared__ Slot<LOG2N> slots[kWarps];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    Slot<LOG2N>& slot = slots[warp];
+    const uint32_t base = (uint32_t)__cvta_generic_to_shared(&slot.raw[1]);
+    const uint32_t tbase = (uint32_t)__cvta_generic_to_shared(&slot.thr[0]);
+    const T* x = reinterpret_cast<const T*>(p.x);
+    T* deq = reinterpret_cast<T*>(p.deq);
+    const bool rb = p.round_bf16 != 0;
+    const bool rounded_out = rb || sizeof(T) == 2;
+    const int n = p.n_levels;
+    const int64_t n_warps = (int64_t)gridDim.x * kWarps;
+    int64_t cached_row = -1;
+    float lo = 0.0f, hi = 0.0f, tm = 0.0f, tl = 0.0f, th = 0.0f;
+    bool flagged = true;
+    // Rows of up to 16 levels: lane i fetches level i, threshold i and the flag of the NEXT item's row
+    // while the current item is processed, so that the row switch costs no trip to memory.
+    constexpr bool kPrefetch = LOG2N <= 4;
+    float nv = 0.0f, nt = 0.0f, nf = 0.0f;
+    auto fetch_row = [&](int64_t row) {
+        const float* lv = p.levels + row * n;
+        const float* wk = p.work + row * n;
+        nv = lane < n ? __ldg(lv + lane) : CUDART_INF_F;
+        nt = lane + 1 < n ? __ldg(wk + lane + 1) : CUDART_NAN_F;
+        nf = __ldg(wk);
+    };
+    const int64_t first_item = (int64_t)blockIdx.x * kWarps + warp;
+    if (kPrefetch && first_item < p.n_items) fetch_row(first_item / p.segs_per_row);
+    for (int64_t item = first_item; item < p.n_items; item += n_warps) {
+        const int64_t row = item / p.segs_per_row;
+        const uint32_t k_begin = (uint32_t)((item - row * p.segs_per_row) * p.seg_len);
+        const uint32_t k_end = (uint32_t)(k_begin + p.seg_len < p.K ? k_begin + p.seg_len : p.K);
+        if (row != cached_row) {
+            __syncwarp();
+            if (kPrefetch) {
+                if (lane <= NP) {
+                    slot.raw[1 + lane] = nv;
+                    slot.rounded[1 + lane] = Arith<bf16_t>::rnd(nv);
+                    slot.thr[lane] = nt;
+                }
+                flagged = nf != 0.0f;
+            } else {
+                const float* lv = p.levels + row * n;
+                const float* wk = p.work + row * n;
+                for (int i = lane; i <= NP; i += 32) {
+                    const float v = i < n ? __ldg(lv + i) : CUDART_INF_F;
+                    slot.raw[1 + i] = v;
+                    slot.rounded[1 + i] = Arith<bf16_t>::rnd(v);
+                    slot.thr[i] = i + 1 < n ? __ldg(wk + i + 1) : CUDART_NAN_F;
+                }
+                flagged = __ldg(wk) != 0.0f;
+            }
+            if (lane == 0) { slot.raw[0] = -CUDART_INF_F; slot.rounded[0] = -CUDART_INF_F; }
+            __syncwarp();
+            lo = lds_f32<0>(base);
+            hi = lds_f32<0>(base + 4u * (uint32_t)(n - 1));
+            tm = lds_f32<(NP / 2 - 1) * 4>(tbase);
+            tl = lds_f32<(NP / 4 - 1) * 4>(tbase);
+            th = lds_f32<(NP / 2 + NP / 4 - 1) * 4>(tbase);
+            cached_row = row;
+        }
+        if (kPrefetch && item + n_warps < p.n_items) {
+            const int64_t next_row = (item + n_warps) / p.segs_per_row;
+            if (next_row != row) fetch_row(next_row);
+        }
+        const T* xr = x + row * p.K;
+        uint8_t* ir = p.idx ? p.idx + row * p.K : nullptr;
+        T* dr_ = deq ? deq + row * p.K : nullptr;
+        auto search4 = [&](const float* in, float* out) -> uint32_t {
+            if (flagged)
+                return rounded_out ? nearest4<LOG2N, true>(base, lo, hi, in, out) : nearest4<LOG2N, false>(base, lo, hi, in, out);
+            return rounded_out ? count4<LOG2N, true>(tbase, tm, tl, th, in, out) : count4<LOG2N, false>(tbase, tm, tl, th, in, out);
+        };
+        if (VEC) {
+            // four elements per lane and pass, kPasses passes in flight
+            for (uint32_t k = k_begin + lane * 4; k < k_end; k += 128 * kPasses) {
+                float v[kPasses][4];
+#pragma unroll
+                for (int h = 0; h < kPasses; ++h) {
+                    const uint32_t kk = k + 128 * h;
+                    if (kk >= k_end) break;
+                    if (sizeof(T) == 4) {
+                        const float4 a = __ldcs(reinterpret_cast<const float4*>(xr + kk));
+                        v[h][0] = a.x; v[h][1] = a.y; v[h][2] = a.z; v[h][3] = a.w;
+                    } else {
+                        const uint2 a = __ldcs(reinterpret_cast<const uint2*>(xr + kk));
+                        v[h][0] = __uint_as_float(a.x << 16); v[h][1] = __uint_as_float(a.x & 0xFFFF0000u);
+                        v[h][2] = __uint_as_float(a.y << 16); v[h][3] = __uint_as_float(a.y & 0xFFFF0000u);
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < kPasses; ++h) {
+                    const uint32_t kk = k + 128 * h;
+                    if (kk >= k_end) break;
+                    if (rb && sizeof(T) == 4) {
+                        // round the elements to bf16 (a NaN stays a NaN)
+                        const uint32_t p01 = bf16x2_of(v[h][1], v[h][0]), p23 = bf16x2_of(v[h][3], v[h][2]);
+                        v[h][0] = __uint_as_float(p01 << 16); v[h][1] = __uint_as_float(p01 & 0xFFFF0000u);
+                        v[h][2] = __uint_as_float(p23 << 16); v[h][3] = __uint_as_float(p23 & 0xFFFF0000u);
+                    }
+                    float out[4];
+                    const uint32_t packed = search4(v[h], out);
+                    if (ir) __stcs(reinterpret_cast<uint32_t*>(ir + kk), packed);
+                    if (dr_) {
+                        if (sizeof(T) == 4) {
+                            __stcs(reinterpret_cast<float4*>(dr_ + kk), make_float4(out[0], out[1], out[2], out[3]));
+                        } else {
+                            __stcs(reinterpret_cast<uint2*>(dr_ + kk), make_uint2(bf16x2_of(out[1], out[0]), bf16x2_of(out[3], out[2])));
+                        }
+                    }
+                }
+            }
+        } else {
+            for (uint32_t k = k_begin + lane; k < k_end; k += 32) {
+                float v[4], out[4];
+                if (sizeof(T) == 4) v[0] = __ldcs(reinterpret_cast<const float*>(xr) + k);
+                else v[0] = bf16_bits_to_f32(__ldcs(reinterpret_cast<const unsigned short*>(xr) + k));
+                if (rb) v[0] = Arith<bf16_t>::rnd(v[0]);
+                v[1] = v[2] = v[3] = v[0];
+                const uint32_t packed = search4(v, out);
+                if (ir) ir[k] = (uint8_t)(packed & 0xFFu);
+                if (dr_) {
+                    if (sizeof(T) == 4) reinterpret_cast<float*>(dr_)[k] = out[0];
+                    else reinterpret_cast<unsigned short*>(dr_)[k] = (unsigned short)f32_to_bf16_bits(out[0]);
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int LOG2N>
+void launch_row_codebook(const RowCbParams& p, bool vec, int blocks, cudaStream_t st) {
+    if (vec) row_codebook_kernel<T, LOG2N, true><<<blocks, kWarps * 32, 0, st>>>(p);
+    else row_codebook_kernel<T, LOG2N, false><<<blocks, kWarps * 32, 0, st>>>(p);
+}
+
+}  // namespace
+
+extern "C" size_t vq_row_codebook_workspace(int64_t rows, int n_levels) {
+    if (rows < 0 || n_levels < 1) return 0;
+    return (size_t)rows * (size_t)n_levels * sizeof(float);
+}
+
+extern "C" int vq_row_codebook(const void* x, int dtype, int64_t rows, int64_t K, const float* levels, int n_levels,
+                               int round_bf16, uint8_t* idx_out, void* deq_out, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+    const char* name = "vq_row_codebook";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(rows >= 0 && K >= 0 && K < (1ll << 31), "%s: sizes must be non-negative, K below 2^31", name);
+    VQ_REQUIRE(n_levels >= 1 && n_levels <= kMaxLevels, "%s: n_levels must be in [1, %d]", name, kMaxLevels);
+    if (rows == 0 || K == 0) return 0;
+    VQ_REQUIRE(x && levels && (idx_out || deq_out), "%s: null pointer", name);
+    VQ_REQUIRE(workspace && (uintptr_t)workspace % 4 == 0 && workspace_bytes >= vq_row_codebook_workspace(rows, n_levels),
+               "%s: workspace missing or smaller than vq_row_codebook_workspace(rows, n_levels)", name);
+    RowCbParams p{};
+    p.x = x; p.levels = levels; p.idx = idx_out; p.deq = deq_out;
+    p.work = reinterpret_cast<float*>(workspace);
+    p.rows = rows; p.K = K;
+    p.n_levels = n_levels;
+    p.round_bf16 = round_bf16 ? 1 : 0;
+    const size_t es = dtype == VQ_F32 ? 4 : 2;
+    const bool vec = K % 4 == 0 && (uintptr_t)x % (4 * es) == 0 && (uintptr_t)idx_out % 4 == 0 && (uintptr_t)deq_out % (4 * es) == 0;
+    // work items: enough of them to fill the machine eight times over, never shorter than 256 elements
+    const int sms = vq_sm_count();
+    const int64_t want_items = (int64_t)sms * 8 * kWarps * 8;
+    int64_t segs = want_items / rows;
+    if (segs < 1) segs = 1;
+    int64_t seg_len = (K + segs - 1) / segs;
+    seg_len = (seg_len + 128 * kPasses - 1) / (128 * kPasses) * (128 * kPasses);
+    p.seg_len = seg_len;
+    p.segs_per_row = (K + seg_len - 1) / seg_len;
+    p.n_items = rows * p.segs_per_row;
+    int64_t want_blocks = (p.n_items + kWarps - 1) / kWarps;
+    const int blocks = (int)(want_blocks < (int64_t)sms * 8 ? want_blocks : (int64_t)sms * 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    row_thresholds_kernel<<<(unsigned)((rows * n_levels + 255) / 256), 256, 0, st>>>(levels, p.work, rows, n_levels);
+    VQ_LAUNCH_CHECK("row_thresholds_kernel");
+    const int log2n = n_levels <= 4 ? 2 : (n_levels <= 16 ? 4 : 8);
+    if (dtype == VQ_F32) {
+        if (log2n == 2) launch_row_codebook<float, 2>(p, vec, blocks, st);
+        else if (log2n == 4) launch_row_codebook<float, 4>(p, vec, blocks, st);
+        else launch_row_codebook<float, 8>(p, vec, blocks, st);
+    } else {
+        if (log2n == 2) launch_row_codebook<bf16_t, 2>(p, vec, blocks, st);
+        else if (log2n == 4) launch_row_codebook<bf16_t, 4>(p, vec, blocks, st);
+        else launch_row_codebook<bf16_t, 8>(p, vec, blocks, st);
+    }
+    VQ_LAUNCH_CHECK("row_codebook_kernel");
+    return 0;
+}
