@@ -396,6 +396,20 @@ def run_linear(args):
                       "frac_fused_of_burst_peak": res["fused"]["tflops"] / peaks.get("bf16_tflops", 1590.0)}))
 
 
+def resnet50_weight_shapes():
+    """The 53 convolution weights and the classifier weight of the standard ResNet-50 (25 502 912 elements)."""
+    shapes = [(64, 3, 7, 7)]
+    inplanes = 64
+    for planes, blocks in ((64, 3), (128, 4), (256, 6), (512, 3)):
+        for b in range(blocks):
+            shapes += [(planes, inplanes, 1, 1), (planes, planes, 3, 3), (planes * 4, planes, 1, 1)]
+            if b == 0:
+                shapes.append((planes * 4, inplanes, 1, 1))
+            inplanes = planes * 4
+    shapes.append((1000, 2048))
+    return shapes
+
+
 def run_elementwise(args):
     """cfg1 / cfg2 / cfg4-shaped element-wise measurements on one GPU (GB/s of algorithmic traffic,
     L2 flushed between iterations)."""
@@ -476,6 +490,20 @@ def run_elementwise(args):
     s4 = w4.abs().amax(dim=1, keepdim=True)
     res["cfg4_quantize_codebook16_perrow_11008x4096"] = timed(lambda: Q.quantize(w4, s4, None, None, None, cb), w4.numel() * 8)
     res["vmap_fp32_posit8_11008x4096"] = timed(lambda: Q.vmap(w4, qp), w4.numel() * 8)
+    # cfg2 as one fused multi-tensor launch: all 54 ResNet-50 weight tensors, per-channel amax -> scale ->
+    # posit8 code byte + dequantized fp32 (read 4N, write N + 4N)
+    torch.manual_seed(1)
+    rn = []
+    for shp in resnet50_weight_shapes():
+        t = torch.empty(shp, device=dev)
+        torch.nn.init.kaiming_normal_(t, mode="fan_in")
+        rn.append(t)
+    n_rn = sum(t.numel() for t in rn)
+    plan_a = mq.ChannelQuantPlan(rn, qp, 4096.0, want_codes=True, want_dequant=True)
+    res["cfg2_fused_per_channel_posit8_54_tensors_25p5M"] = timed(plan_a.run, n_rn * 9)
+    plan_b = mq.ChannelQuantPlan(rn, qp, 4096.0, want_values=True, want_dequant=False)
+    res["cfg2_fused_per_channel_posit8_dropin_values_25p5M"] = timed(plan_b.run, n_rn * 8)
+    del rn, plan_a, plan_b
     # cfg4: per-output-channel 16-entry quantile codebooks, W[11008,4096] fp32 ~ Student-t(5) * 0.02
     from voyager_compiler_b200 import codebook
     torch.manual_seed(3)

@@ -235,6 +235,32 @@ VQ_API int vq_quantize_mx_multi_static(const vq_mx_item* items, int n_items, int
                                        const vq_table* scale_table, const vq_table* table, int code_bits,
                                        void* stream);
 
+/* One tensor of a per-channel pass, viewed as [channels, length] (a conv weight OIHW is
+ * [O, I*H*W]).  Every output may be NULL, at least one must not be.  All tensors in `dtype`. */
+typedef struct vq_channel_item {
+    const void* input;
+    int64_t channels, length;
+    const void* scale_in; /* [channels], optional: quantize with this scale instead of amax / quant_max */
+    void* amax_out;       /* [channels]: max |x| of the channel (NaN if the channel holds one) */
+    void* scale_out;      /* [channels]: amax / quant_max, 1 where amax is 0, NaN or Inf (not written with scale_in) */
+    void* values;         /* [channels, length]: qmap[bf16(x / scale)] */
+    uint8_t* codes;       /* [channels, length]: packed 8-bit code of that value */
+    void* dequant;        /* [channels, length]: values * scale */
+} vq_channel_item;
+
+/* Bytes of device workspace for these items (depends on the channel counts and lengths). */
+VQ_API size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items);
+
+/* Per-channel amax + scale + quantize (+ dequantize) over many tensors in ONE launch: what upstream
+ * computes per weight tensor with the observer's scale rule
+ * (src/voyager_compiler/quantization/fake_quantize.py:320-333: amax over all axes but the channel
+ * axis, / quant_max), `quantize` (src/voyager_compiler/ops/quantized.py:131-172) and `dequantize`
+ * (:182-227), each as separate passes.  `items` is a HOST array, copied into `workspace` (device, 16-byte
+ * aligned, vq_channel_quantize_multi_workspace(items, n_items) bytes) on `stream`.  Channel lengths
+ * below 2^22 elements. */
+VQ_API int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dtype, double quant_max,
+                                     const vq_table* table, void* workspace, size_t workspace_bytes, void* stream);
+
 /* out[i] = levels[code[i]] * scale[i / block] in `dtype` (one rounding), from the packed views that
  * vq_quantize_mx / vq_quantize_mx_multi write: 8-bit codes (one per byte) or 4-bit codes (two per
  * byte, even element in the low nibble), and per block either an fp32 scale or an E8 exponent

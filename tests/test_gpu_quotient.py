@@ -61,3 +61,29 @@ def test_block_maximum_scales_over_every_significand(flat, exponent):
     s_got, c_got = Q.quantize_mx(x.cuda(), tab.cuda(), (-1,), 64, 1.0, False)
     assert _same(s_got, s_ref)
     assert _same(c_got, c_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_per_channel_kernel_divides_like_the_cpu(dtype):
+    """The per-channel kernel divides by a corrected reciprocal (fp32-exact by Markstein's theorem).
+    Random significands against 64 scales, through a table that keeps the quotient's full bf16
+    resolution; scales given explicitly and derived from the channel maximum."""
+    from voyager_compiler_b200 import model_quant as mq
+    g = torch.Generator().manual_seed(5)
+    ch, n = 64, 1 << 18
+    bits = (torch.randint(0, 2, (ch, n), generator=g) << 31) | (torch.randint(100, 140, (ch, n), generator=g) << 23) \
+        | torch.randint(0, 1 << 23, (ch, n), generator=g)
+    x = bits.to(torch.int32).view(torch.float32)
+    x[:, :4] = torch.tensor([0.0, -0.0, 1e-30, -3e25])                 # zeros and values outside the corrected range
+    x = x.to(dtype)
+    sbits = (torch.randint(110, 130, (ch, 1), generator=g) << 23) | torch.randint(0, 1 << 23, (ch, 1), generator=g)
+    s = sbits.to(torch.int32).view(torch.float32).to(dtype)
+    s[0] = 0.25
+    s[1] = 3e-12                                                        # outside the corrected range: IEEE division
+    tab = _resolution_table(None)
+    (r,) = mq.quantize_tensors_per_channel([x.cuda()], tab, 1.0, scales=[s.cuda()], want_values=True, want_dequant=False)
+    assert _same(r.values, vo.quantize(x, s, None, None, None, tab))
+    (r2,) = mq.quantize_tensors_per_channel([x.cuda()], tab, 3.0, want_values=True, want_dequant=False)
+    s2 = vo.channel_scale(x, 3.0)
+    assert _same(r2.scale, s2)
+    assert _same(r2.values, vo.quantize(x, s2, None, None, None, tab))

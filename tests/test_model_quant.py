@@ -126,6 +126,55 @@ def test_large_jobs_match_the_oracle(dtype, table, block, qmax, pow2, bits):
         assert torch.equal(got[ok], v_ref[ok])
 
 
+def _resnet_like_shapes():
+    return [(64, 3, 7, 7), (64, 64, 1, 1), (64, 64, 3, 3), (256, 64, 1, 1), (128, 128, 3, 3), (512, 512, 3, 3),
+            (2048, 512, 1, 1), (1000, 2048)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,table,qmax", [(torch.float32, "posit8_1", 4096.0), (torch.bfloat16, "posit8_1", 4096.0),
+                                               (torch.float32, "int8", 127.0), (torch.float32, "fp8_e4m3", 448.0)])
+def test_per_channel_multi_tensor_matches_oracle(dtype, table, qmax):
+    torch.manual_seed(1)
+    ws = []
+    for s in _resnet_like_shapes():
+        w = torch.empty(s)
+        torch.nn.init.kaiming_normal_(w, mode="fan_in")
+        ws.append(w.to(dtype))
+    ws[1][3] = 0                                  # an all-zero channel: scale 1
+    ws[2][5, 0, 0, 0] = float("nan")              # NaN channel: scale 1, NaN at the element
+    ws[3][7, 1, 0, 0] = float("inf")              # Inf channel: scale 1
+    tab = golden_table(table)
+    got = mq.quantize_tensors_per_channel([w.cuda() for w in ws], tab, qmax, want_values=True, want_codes=True,
+                                          want_dequant=True, want_amax=True)
+    torch.cuda.synchronize()
+    for w, r in zip(ws, got):
+        s_ref = vo.channel_scale(w, qmax)
+        q_ref = vo.quantize(w, s_ref, None, None, None, tab)
+        d_ref = vo.dequantize(q_ref, s_ref)
+        amax = torch.amax(torch.abs(w), dim=tuple(range(1, w.ndim)), keepdim=True)
+        assert same_bits(r.scale, s_ref)[0]
+        assert same_bits(r.amax, amax)[0]
+        assert same_bits(r.values, q_ref)[0]
+        assert same_bits(r.dequant, d_ref)[0]
+        ok = ~torch.isnan(q_ref.float())
+        lv = r.levels[r.codes.cpu().long().clamp(max=r.levels.numel() - 1)]
+        assert torch.equal(lv[ok], q_ref.float()[ok])
+
+
+@pytest.mark.gpu
+def test_per_channel_with_given_scales_is_quantize_plus_dequantize():
+    torch.manual_seed(6)
+    w = torch.randn(96, 32, 3, 3)
+    s = (torch.rand(96, 1, 1, 1) + 0.1) / 100
+    s[4] = 2.0 ** -7                              # an exact-reciprocal scale
+    tab = golden_table("int8")
+    (r,) = mq.quantize_tensors_per_channel([w.cuda()], tab, 127.0, scales=[s.cuda()], want_values=True)
+    q_ref = vo.quantize(w, s, None, None, None, tab)
+    assert same_bits(r.values, q_ref)[0]
+    assert same_bits(r.dequant, vo.dequantize(q_ref, s))[0]
+
+
 @pytest.mark.gpu
 def test_dequantize_packed_matches_reference_decode():
     torch.manual_seed(3)

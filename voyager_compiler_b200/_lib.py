@@ -29,6 +29,14 @@ class VqTable(C.Structure):
     ]
 
 
+class VqChannelItem(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("channels", C.c_int64), ("length", C.c_int64), ("scale_in", C.c_void_p),
+        ("amax_out", C.c_void_p), ("scale_out", C.c_void_p), ("values", C.c_void_p), ("codes", C.c_void_p),
+        ("dequant", C.c_void_p),
+    ]
+
+
 class VqScaleLayout(C.Structure):
     _fields_ = [
         ("mode", C.c_int32), ("ndim", C.c_int32),
@@ -85,9 +93,12 @@ def _load():
         "vq_gemm_bf16_tn_scatter": [vp, vp, vp, C.POINTER(C.c_void_p), ci, i64, i64, i64, i64, i64, vp, vp],
         "vq_linear_mx": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],
         "vq_quantize_mx_multi": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp, C.c_size_t, vp],
+        "vq_channel_quantize_multi": [C.POINTER(VqChannelItem), ci, ci, dbl, T, vp, C.c_size_t, vp],
     }
     lib.vq_quantize_mx_multi_workspace.argtypes = [ci]
     lib.vq_quantize_mx_multi_workspace.restype = C.c_size_t
+    lib.vq_channel_quantize_multi_workspace.argtypes = [C.POINTER(VqChannelItem), ci]
+    lib.vq_channel_quantize_multi_workspace.restype = C.c_size_t
     lib.vq_row_codebook_workspace.argtypes = [i64, ci]
     lib.vq_row_codebook_workspace.restype = C.c_size_t
     for name, args in sigs.items():

@@ -22,7 +22,7 @@ import torch
 from . import _lib
 from .qtables import exp_tables, table_handle
 
-__all__ = ["PackedMX", "quantize_tensors_mx", "dequantize_packed", "unpack_codes", "dequantize_packed_reference", "shard_plan",
+__all__ = ["PackedMX", "quantize_tensors_mx", "ChannelQuant", "ChannelQuantPlan", "quantize_tensors_per_channel", "dequantize_packed", "unpack_codes", "dequantize_packed_reference", "shard_plan",
            "HostPipeline"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
@@ -117,6 +117,111 @@ def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant
                 0 if float_outputs else code_bits, ws.data_ptr(), ws.numel(), stream), "quantize_tensors_mx")
             del keep
     return results
+
+
+@dataclass
+class ChannelQuant:
+    """Per-channel result for one tensor (fields not asked for are ``None``).  ``scale`` and ``amax``
+    have the keepdim shape ``[C, 1, ...]`` upstream's observer produces; ``values`` is what
+    ``quantize`` returns, ``dequant`` what ``dequantize(values, scale)`` returns."""
+    scale: Optional[torch.Tensor]
+    amax: Optional[torch.Tensor]
+    values: Optional[torch.Tensor]
+    codes: Optional[torch.Tensor]
+    dequant: Optional[torch.Tensor]
+    levels: Optional[torch.Tensor] = None
+
+
+class ChannelQuantPlan:
+    """Outputs and launch descriptors of a per-channel pass, prepared once: ``run()`` is then one
+    library call per dtype (no allocation), for weights that are re-quantized every step
+    (calibration, quantization-aware training).  ``results`` holds one :class:`ChannelQuant` per
+    tensor; the tensors are read where they are at the time of ``run()``."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor], qmap, quant_max: float, *, scales=None,
+                 want_values: bool = False, want_codes: bool = False, want_dequant: bool = True,
+                 want_amax: bool = False):
+        if not tensors:
+            raise ValueError("no tensors")
+        device = tensors[0].device
+        if device.type != "cuda":
+            raise RuntimeError("quantize_tensors_per_channel: CUDA tensors only; there is no CPU path")
+        if not (want_values or want_codes or want_dequant or want_amax):
+            raise ValueError("nothing to compute")
+        self.device = device
+        self.quant_max = float(quant_max)
+        self.results: List = [None] * len(tensors)
+        self._groups = []
+        self._keep = []
+        with torch.cuda.device(device):
+            self._tab = table_handle(qmap, device)
+            if want_codes:
+                self._tab.with_codes()
+            for dt in (torch.bfloat16, torch.float32):
+                idx = [i for i, t in enumerate(tensors) if t.dtype == dt]
+                if not idx:
+                    continue
+                items = (_lib.VqChannelItem * len(idx))()
+                for k, i in enumerate(idx):
+                    t = tensors[i]
+                    if t.device != device or t.ndim < 1:
+                        raise ValueError("all tensors must live on one device and have a channel axis")
+                    if not t.is_contiguous():
+                        raise ValueError("tensors must be contiguous (the plan reads them in place)")
+                    ch = t.shape[0]
+                    kd = (ch,) + (1,) * (t.ndim - 1)
+                    r = ChannelQuant(None, None, None, None, None, self._tab.levels if want_codes else None)
+                    items[k].input = t.data_ptr()
+                    items[k].channels = ch
+                    items[k].length = t.numel() // ch if ch else 1
+                    if scales is not None:
+                        sc = scales[i].to(dt).reshape(ch).contiguous()
+                        self._keep.append(sc)
+                        items[k].scale_in = sc.data_ptr()
+                        r.scale = sc.reshape(kd)
+                    else:
+                        r.scale = torch.empty(kd, dtype=dt, device=device)
+                        items[k].scale_out = r.scale.data_ptr()
+                    if want_amax:
+                        r.amax = torch.empty(kd, dtype=dt, device=device)
+                        items[k].amax_out = r.amax.data_ptr()
+                    if want_values:
+                        r.values = torch.empty_like(t)
+                        items[k].values = r.values.data_ptr()
+                    if want_codes:
+                        r.codes = torch.empty(t.shape, dtype=torch.uint8, device=device)
+                        items[k].codes = r.codes.data_ptr()
+                    if want_dequant:
+                        r.dequant = torch.empty_like(t)
+                        items[k].dequant = r.dequant.data_ptr()
+                    self.results[i] = r
+                    self._keep.append(t)
+                need = _lib.lib.vq_channel_quantize_multi_workspace(items, len(idx))
+                ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
+                self._groups.append((items, len(idx), _DT[dt], ws))
+
+    def run(self) -> List[ChannelQuant]:
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            for items, n, dt, ws in self._groups:
+                _lib.check(_lib.lib.vq_channel_quantize_multi(items, n, dt, self.quant_max, self._tab.ptr(),
+                                                              ws.data_ptr(), ws.numel(), stream), "quantize_tensors_per_channel")
+        return self.results
+
+
+def quantize_tensors_per_channel(tensors: Sequence[torch.Tensor], qmap, quant_max: float, *, scales=None,
+                                 want_values: bool = False, want_codes: bool = False, want_dequant: bool = True,
+                                 want_amax: bool = False) -> List[ChannelQuant]:
+    """Per-output-channel (axis 0) quantization of many weight tensors in one launch per dtype:
+    ``scale = amax(|w|, all axes but 0) / quant_max`` (1 where that amax is 0, NaN or Inf; upstream
+    ``FusedAmaxObsFakeQuantize`` after its history has settled, fake_quantize.py:320-333), then
+    ``quantize(w, scale, qmap=qmap)`` and ``dequantize(q, scale)`` -- amax, divide, table lookup and
+    multiply fused, the channel read from HBM once.  ``scales``: optional list of per-channel
+    scales (observer state) to use instead of the amax rule."""
+    if not tensors:
+        return []
+    return ChannelQuantPlan([t.contiguous() for t in tensors], qmap, quant_max, scales=scales, want_values=want_values,
+                            want_codes=want_codes, want_dequant=want_dequant, want_amax=want_amax).run()
 
 
 def dequantize_packed(p: PackedMX, dtype=torch.float32, use_exponent: bool = False) -> torch.Tensor:
