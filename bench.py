@@ -515,6 +515,21 @@ def run_elementwise(args):
         lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=True), wt.numel() * 9 + lv.numel() * 4)
     res["cfg4_row_codebook16_indices_only_11008x4096"] = timed(
         lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=False, want_values=False), wt.numel() * 5 + lv.numel() * 4)
+    # observer + fake-quantize forward (calibration / QAT): activations [8192, 4096] bf16 and fp32
+    from voyager_compiler_b200 import fake_quantize as fqm
+    for dt, nm, es in ((torch.bfloat16, "bf16", 2), (torch.float32, "fp32", 4)):
+        a = torch.randn(8192, 4096, generator=g, device=dev).to(dt)
+        na = a.numel()
+        sc = (a.abs().amax() / 127.0).float()
+        res[f"fq_amax_per_tensor_{nm}_8192x4096"] = timed(lambda: fqm.amax(a), na * es)
+        res[f"fq_amax_per_channel_last_{nm}_8192x4096"] = timed(lambda: fqm.amax(a, -1), na * es)
+        res[f"fq_fake_quantize_int8_per_tensor_{nm}_8192x4096"] = timed(lambda: fqm.fake_quantize(a, sc, q8), na * 2 * es)
+        res[f"fq_mx_fake_quantize_int8_block32_{nm}_8192x4096"] = timed(
+            lambda: fqm.mx_fake_quantize(a, q8, -1, 32, 127.0, True), na * (2 * es + es / 32))
+        mod = fqm.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=16,
+                                           device=dev)
+        res[f"fq_module_forward_int8_per_tensor_{nm}_8192x4096"] = timed(lambda: mod(a), na * 3 * es)
+        del a, mod
     for k, v in res.items():
         v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]
     print(json.dumps({"workload": "element-wise configs (cfg1, cfg2, cfg4 shapes)", "results": res, "peak_hbm_gbs": peaks["hbm_gbs"],

@@ -235,6 +235,18 @@ VQ_API int vq_quantize_mx_multi_static(const vq_mx_item* items, int n_items, int
                                        const vq_table* scale_table, const vq_table* table, int code_bits,
                                        void* stream);
 
+/* out[i] = qmap[bf16(in[i] / scale)] * scale in `dtype`: quantize and dequantize in one pass, the
+ * forward of upstream `FakeQuantizeFunction`, src/voyager_compiler/quantization/fake_quantize.py:101-115
+ * (`vmap(input / scale, qmap) * scale`).  Scale placement as in vq_quantize. */
+VQ_API int vq_fake_quantize(const void* in, int dtype, int64_t n, const void* scale, const vq_scale_layout* layout,
+                            const vq_table* table, void* out, void* stream);
+
+/* out[c] = max |in[o, c, i]| over o and i, for a tensor viewed as [outer, C, inner]; fp32 output
+ * (the exact widening for bf16 data; NaN if a NaN is present).  One pass, no temporary: the
+ * observer's `torch.amax(torch.abs(x))` / per-channel amax,
+ * src/voyager_compiler/quantization/fake_quantize.py:320-325.  Per tensor: outer = C = 1. */
+VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t inner, float* out, void* stream);
+
 /* One tensor of a per-channel pass, viewed as [channels, length] (a conv weight OIHW is
  * [O, I*H*W]).  Every output may be NULL, at least one must not be.  All tensors in `dtype`. */
 typedef struct vq_channel_item {

@@ -57,8 +57,18 @@ def test_patch_reference_rebinds_direct_imports_and_unpatches():
         q = fq.get_quantization_map("int8")
         x = torch.randn(100) * 30
         assert torch.equal(fq.vmap(x, q), orig(x, q))            # CPU tensors still use the original
+        # the autograd functions: CPU tensors keep upstream's forward, module output unchanged
+        assert "voyager_compiler.quantization.fake_quantize.FakeQuantizeFunction.forward" in done, done
+        m = fq.FusedAmaxObsFakeQuantize("int8", qscheme=ref["qspec"].QScheme.PER_TENSOR_SYMMETRIC, quant_max=127.0,
+                                        amax_history_len=2)
+        xs = [torch.randn(4, 16) for _ in range(3)]
+        got = [m(v).clone() for v in xs]
         compat.unpatch_reference()
         assert fq.vmap is orig
+        assert not hasattr(fq.FakeQuantizeFunction.forward, "__wrapped_original__")
+        m2 = fq.FusedAmaxObsFakeQuantize("int8", qscheme=ref["qspec"].QScheme.PER_TENSOR_SYMMETRIC, quant_max=127.0,
+                                         amax_history_len=2)
+        assert all(torch.equal(a, m2(v)) for a, v in zip(got, xs))
         print("ok")
     """)
     assert "ok" in out

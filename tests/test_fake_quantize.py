@@ -1,0 +1,131 @@
+"""Observer + fake-quantize forward: the oracle against vectors produced by upstream's module
+(CPU), the CUDA module against both (GPU)."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from golden_util import GOLDEN, from_bits, golden_table
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import voyager_oracle as vo  # noqa: E402
+
+with open(os.path.join(GOLDEN, "golden_fake_quant.json")) as _f:
+    CASES = json.load(_f)["cases"]
+_Z = None
+
+
+def _arr(case, t, key):
+    global _Z
+    if _Z is None:
+        _Z = np.load(os.path.join(GOLDEN, "golden_fake_quant.npz"))
+    shape = case["shapes"][key][t]
+    return from_bits(_Z[f"{case['name']}/{t}/{key}"], case["tags"][key], shape)
+
+
+def _same(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return a.shape == b.shape and bool(((a == b) | (torch.isnan(a) & torch.isnan(b))).all()) and \
+        torch.equal(torch.signbit(a)[a == 0], torch.signbit(b)[b == 0])
+
+
+def _table(name):
+    try:
+        return golden_table(name)
+    except KeyError:
+        return vo.value_table(name)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_oracle_steps_like_upstream(case):
+    kw = case["kwargs"]
+    qmap = _table(kw["dtype"])
+    mx = kw["qscheme"] == "microscaling"
+    history, scale = None, torch.tensor([1.0])
+    for t in range(case["steps"]):
+        x, y_ref, s_ref = _arr(case, t, "x"), _arr(case, t, "y"), _arr(case, t, "scale")
+        if mx:
+            sq = _table(kw["scale_dtype"]) if kw.get("scale_dtype") else None
+            scale, y = vo.mx_fake_quantize(x, qmap, kw["ch_axis"], kw["block_size"], kw["quant_max"],
+                                           kw.get("force_scale_power_of_two", False), sq)
+        else:
+            cur = vo.observe_amax(x, kw.get("ch_axis") if kw["qscheme"] == "per_channel_symmetric" else None)
+            if history is None:
+                history = torch.zeros((kw["amax_history_len"],) + tuple(cur.shape))
+                scale = torch.ones(cur.shape)
+            history, scale = vo.update_amax_scale(history, scale, cur, kw["quant_max"], kw.get("force_scale_power_of_two", False))
+            y = vo.fake_quantize(x, scale, qmap)
+        assert _same(y, y_ref) and _same(scale, s_ref)
+
+
+def test_cpu_tensors_rejected():
+    from voyager_compiler_b200 import fake_quantize as fq
+    with pytest.raises(RuntimeError):
+        fq.amax(torch.zeros(4))
+    with pytest.raises(RuntimeError):
+        fq.fake_quantize(torch.zeros(4), torch.ones(1), golden_table("int8"))
+
+
+# ------------------------------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_module_steps_like_upstream(case):
+    from voyager_compiler_b200 import fake_quantize as fq
+    kw = dict(case["kwargs"])
+    m = fq.FusedAmaxObsFakeQuantize(device="cuda", **kw)
+    for t in range(case["steps"]):
+        x = _arr(case, t, "x").cuda().requires_grad_(True)
+        y = m(x)
+        assert _same(y, _arr(case, t, "y")), (case["name"], t)
+        assert _same(m.scale, _arr(case, t, "scale")), (case["name"], t)
+        y.sum().backward()
+        assert torch.equal(x.grad, torch.ones_like(x))          # straight-through estimator
+    m.disable_fake_quant()
+    x = _arr(case, 0, "x").cuda()
+    assert m(x) is x
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,ch_axis", [((4096, 1024), None), ((64, 3, 7, 7), 0), ((2, 96, 56, 56), 1), ((33, 5, 2), 1),
+                                           ((512, 768), -1), ((1000, 3), -1), ((7,), None), ((3, 70000), 0)])
+def test_amax_matches_torch(dtype, shape, ch_axis):
+    from voyager_compiler_b200 import fake_quantize as fq
+    g = torch.Generator().manual_seed(len(shape) * 7 + (ch_axis or 0))
+    x = (torch.randn(shape, generator=g) * 3).to(dtype)
+    assert _same(fq.amax(x.cuda(), ch_axis), vo.observe_amax(x, ch_axis))
+    x.view(-1)[x.numel() // 2] = float("nan")
+    assert _same(fq.amax(x.cuda(), ch_axis), vo.observe_amax(x, ch_axis))
+    x = torch.zeros(shape, dtype=dtype)
+    assert _same(fq.amax(x.cuda(), ch_axis), vo.observe_amax(x, ch_axis))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("table", ["int8", "posit8_1", "nf4", "fp8_e4m3"])
+def test_fake_quantize_matches_oracle(dtype, table):
+    from voyager_compiler_b200 import fake_quantize as fq
+    torch.manual_seed(9)
+    qmap = golden_table(table)
+    for shape, sshape in (((257, 130), ()), ((48, 16, 3, 3), (48, 1, 1, 1)), ((4, 10, 6), (1, 10, 1)), ((2048, 1024), ())):
+        x = torch.randn(shape).to(dtype)
+        x.view(-1)[1] = float("nan")
+        s = (torch.rand(sshape) + 0.05).to(torch.float32) * 0.03
+        got = fq.fake_quantize(x.cuda(), s.cuda(), qmap.cuda())
+        assert _same(got, vo.fake_quantize(x, s, qmap)), (shape, sshape)
+
+
+@pytest.mark.gpu
+def test_mx_fake_quantize_matches_oracle_large():
+    from voyager_compiler_b200 import fake_quantize as fq
+    torch.manual_seed(10)
+    x = torch.randn(512, 4096).to(torch.bfloat16)
+    x[3, :64] = 0
+    for table, qmax, pow2, block in (("int8", 127.0, True, 32), ("nf4", 1.0, False, 64)):
+        qmap = golden_table(table)
+        s, y = fq.mx_fake_quantize(x.cuda(), qmap.cuda(), -1, block, qmax, pow2)
+        s_ref, y_ref = vo.mx_fake_quantize(x, qmap, -1, block, qmax, pow2)
+        assert _same(s, s_ref) and _same(y, y_ref)

@@ -85,6 +85,8 @@ def _load():
         "vq_lut_map": [vp, ci, i64, T, vp, vp],
         "vq_quantize": [vp, ci, i64, vp, vp, L, T, vp, vp, ci, vp],
         "vq_dequantize": [vp, ci, i64, vp, vp, L, T, T, vp, vp],
+        "vq_fake_quantize": [vp, ci, i64, vp, L, T, vp, vp],
+        "vq_amax": [vp, ci, i64, i64, i64, vp, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
         "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],
         "vq_row_codebook": [vp, ci, i64, i64, vp, ci, ci, vp, vp, vp, C.c_size_t, vp],

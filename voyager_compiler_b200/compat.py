@@ -5,8 +5,10 @@
 ``ops/quantized.py`` the ops call each other as Python functions, so kernels registered on
 ``torch.ops.quantized_ops`` are not reached from the prepare-time fake-quant path.  ``patch_reference()``
 rebinds those names to wrappers that send CUDA tensors through the dispatcher (and therefore to this
-package's kernels) and everything else to the original function.  Off by default; undo with
-``unpatch_reference()``.
+package's kernels) and everything else to the original function.  The forwards of upstream's
+``FakeQuantizeFunction`` and ``MXFakeQuantizeFunction`` (quantization/fake_quantize.py:101-159) are
+rebound the same way to the fused one-pass kernels of :mod:`voyager_compiler_b200.fake_quantize`.
+Off by default; undo with ``unpatch_reference()``.
 """
 from __future__ import annotations
 
@@ -58,7 +60,37 @@ def patch_reference() -> List[str]:
             setattr(mod, n, _wrap(n, fn))
             _PATCHED.append((mod, n, fn))
             done.append(f"{modname}.{n}")
+    _patch_fake_quant_functions(done)
     return done
+
+
+def _patch_fake_quant_functions(done: List[str]) -> None:
+    mod = sys.modules.get("voyager_compiler.quantization.fake_quantize")
+    if mod is None:
+        return
+    from . import fake_quantize as ours
+
+    def wrap_forward(cls, fused):
+        original = cls.__dict__["forward"]
+        original_fn = original.__func__ if isinstance(original, staticmethod) else original
+        if hasattr(original_fn, "__wrapped_original__"):
+            return
+
+        @functools.wraps(original_fn)
+        def forward(ctx, input, *args, **kwargs):
+            if isinstance(input, torch.Tensor) and input.is_cuda and input.dtype in (torch.float32, torch.bfloat16):
+                return fused(ctx, input, *args, **kwargs)
+            return original_fn(ctx, input, *args, **kwargs)
+
+        forward.__wrapped_original__ = original_fn
+        setattr(cls, "forward", staticmethod(forward))
+        _PATCHED.append((cls, "forward", original))
+        done.append(f"voyager_compiler.quantization.fake_quantize.{cls.__name__}.forward")
+
+    if hasattr(mod, "FakeQuantizeFunction"):
+        wrap_forward(mod.FakeQuantizeFunction, ours.FakeQuantizeFunction.forward)
+    if hasattr(mod, "MXFakeQuantizeFunction"):
+        wrap_forward(mod.MXFakeQuantizeFunction, ours.MXFakeQuantizeFunction.forward)
 
 
 def unpatch_reference() -> None:

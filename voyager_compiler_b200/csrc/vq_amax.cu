@@ -1,0 +1,213 @@
+// max |x| per tensor or per channel in one pass over the data: the reduction the observer runs
+// before every fake-quantize (`torch.amax(torch.abs(x))`, per-channel `torch.amax(torch.abs(x),
+// dim=all but ch_axis)`, quantization/fake_quantize.py:320-325), which upstream computes as an abs
+// pass (a full-size temporary) followed by a reduce pass.
+//
+// The tensor is viewed as [outer, C, inner]; out[c] = max over outer and inner.  |x| is reduced as
+// an unsigned bit pattern (finite < inf < NaN, so a NaN wins as in torch.amax) and combined across
+// CTAs with atomicMax on the fp32 output, which is zeroed first on the same stream.
+//   inner >= 64: a warp per (row = outer * C + c, segment of the row), lanes stride by 16-byte vectors;
+//   inner == 1:  columns across threads, rows across the grid, one atomic per column and CTA;
+//   otherwise:   flat sweep, every lane keeps the maximum of its current channel and flushes it
+//                when the channel changes.
+// HBM bound: sizeof(T) read per element.
+#include "vq_common.cuh"
+
+namespace {
+
+struct AmaxParams {
+    const void* in;
+    uint32_t* out;          // fp32 bit patterns, [C]
+    int64_t outer, C, inner;
+    int64_t n;
+    int64_t seg_len, segs_per_row, n_items;   // row mode
+    FastDiv div_inner, div_C;                 // flat mode (n < 2^31)
+    int vec;                                  // 16-byte loads usable
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t abs16(const T* p);   // max |x| bits of the 16 bytes at p
+template <>
+__device__ __forceinline__ uint32_t abs16<float>(const float* p) {
+    const uint4 a = __ldcs(reinterpret_cast<const uint4*>(p));
+    return max(max(a.x & 0x7FFFFFFFu, a.y & 0x7FFFFFFFu), max(a.z & 0x7FFFFFFFu, a.w & 0x7FFFFFFFu));
+}
+template <>
+__device__ __forceinline__ uint32_t abs16<bf16_t>(const bf16_t* p) {
+    const uint4 a = __ldcs(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m = max(m, max((w[j] << 16) & 0x7FFFFFFFu, w[j] & 0x7FFF0000u));
+    return m;
+}
+template <typename T>
+__device__ __forceinline__ uint32_t abs1(const T* p, int64_t i);
+template <>
+__device__ __forceinline__ uint32_t abs1<float>(const float* p, int64_t i) { return __float_as_uint(p[i]) & 0x7FFFFFFFu; }
+template <>
+__device__ __forceinline__ uint32_t abs1<bf16_t>(const bf16_t* p, int64_t i) { return ((uint32_t)p[i].bits << 16) & 0x7FFFFFFFu; }
+
+// MODE 0: rows, 1: columns (inner == 1), 2: flat
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) amax_kernel(const AmaxParams p) {
+    constexpr int V = 16 / sizeof(T);
+    const T* x = reinterpret_cast<const T*>(p.in);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (MODE == 0) {
+        const int64_t n_warps = (int64_t)gridDim.x * 8;
+        int64_t cur = -1;                 // channel of the running maximum (one atomic per run of items)
+        uint32_t run = 0;
+        for (int64_t item = (int64_t)blockIdx.x * 8 + warp; item < p.n_items; item += n_warps) {
+            const int64_t row = item / p.segs_per_row;
+            const int64_t k0 = (item - row * p.segs_per_row) * p.seg_len;
+            const int64_t k1 = k0 + p.seg_len < p.inner ? k0 + p.seg_len : p.inner;
+            const T* xr = x + row * p.inner;
+            uint32_t m = 0;
+            if (p.vec) {
+                for (int64_t k = k0 + lane * V; k < k1; k += 32 * V * 4) {
+                    uint32_t t[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (k + u * 32 * V < k1) t[u] = abs16<T>(xr + k + u * 32 * V);
+                    m = max(m, max(max(t[0], t[1]), max(t[2], t[3])));
+                }
+            } else {
+                for (int64_t k = k0 + lane; k < k1; k += 32) m = max(m, abs1<T>(xr, k));
+            }
+            const int64_t c = row % p.C;
+            if (c != cur) {
+                if (cur >= 0) {
+                    run = __reduce_max_sync(0xFFFFFFFFu, run);
+                    if (lane == 0 && run) atomicMax(p.out + cur, run);
+                }
+                cur = c;
+                run = 0;
+            }
+            run = max(run, m);
+        }
+        if (cur >= 0) {
+            run = __reduce_max_sync(0xFFFFFFFFu, run);
+            if (lane == 0 && run) atomicMax(p.out + cur, run);
+        }
+    } else if (MODE == 1) {
+        // x is [outer, C]: a thread owns V consecutive columns (one 16-byte load per row) or one
+        // column; the grid splits the rows; one atomic per column and CTA
+        if (p.vec) {
+            for (int64_t c = (int64_t)threadIdx.x * V; c < p.C; c += (int64_t)blockDim.x * V) {
+                uint32_t m[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) m[j] = 0;
+                for (int64_t r = blockIdx.x; r < p.outer; r += (int64_t)gridDim.x * 4) {
+                    uint32_t w[4][4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        uint4 a = make_uint4(0, 0, 0, 0);
+                        if (r + (int64_t)u * gridDim.x < p.outer)
+                            a = __ldcs(reinterpret_cast<const uint4*>(x + (r + (int64_t)u * gridDim.x) * p.C + c));
+                        w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (sizeof(T) == 4) m[j] = max(m[j], w[u][j] & 0x7FFFFFFFu);
+                            else {
+                                m[(2 * j) % V] = max(m[(2 * j) % V], (w[u][j] << 16) & 0x7FFFFFFFu);
+                                m[(2 * j + 1) % V] = max(m[(2 * j + 1) % V], w[u][j] & 0x7FFF0000u);
+                            }
+                        }
+                }
+#pragma unroll
+                for (int j = 0; j < V; ++j)
+                    if (m[j]) atomicMax(p.out + c + j, m[j]);
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < p.C; c += blockDim.x) {
+                uint32_t m = 0;
+                for (int64_t r = blockIdx.x; r < p.outer; r += gridDim.x) m = max(m, abs1<T>(x, r * p.C + c));
+                if (m) atomicMax(p.out + c, m);
+            }
+        }
+    } else {
+        const uint32_t n = (uint32_t)p.n;
+        uint32_t cur = 0xFFFFFFFFu, m = 0;
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+            const uint32_t row = fd_div(i, p.div_inner);
+            const uint32_t c = row - fd_div(row, p.div_C) * (uint32_t)p.C;
+            if (c != cur) {
+                if (cur != 0xFFFFFFFFu && m) atomicMax(p.out + cur, m);
+                cur = c;
+                m = 0;
+            }
+            m = max(m, abs1<T>(x, i));
+        }
+        if (cur != 0xFFFFFFFFu && m) atomicMax(p.out + cur, m);
+    }
+}
+
+}  // namespace
+
+extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t inner, float* out, void* stream) {
+    const char* name = "vq_amax";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(outer >= 0 && C >= 1 && inner >= 0, "%s: bad shape", name);
+    VQ_REQUIRE(out != nullptr, "%s: null output", name);
+    cudaStream_t st = (cudaStream_t)stream;
+    VQ_CUDA(cudaMemsetAsync(out, 0, (size_t)C * sizeof(float), st));
+    const int64_t n = outer * C * inner;
+    if (n == 0) return 0;
+    VQ_REQUIRE(in != nullptr, "%s: null input", name);
+    AmaxParams p{};
+    p.in = in;
+    p.out = reinterpret_cast<uint32_t*>(out);
+    p.outer = outer; p.C = C; p.inner = inner; p.n = n;
+    const size_t es = dtype == VQ_F32 ? 4 : 2;
+    const int V = (int)(16 / es);
+    const int sms = vq_sm_count();
+    int mode, blocks;
+    if (inner >= 64 || (C == 1 && outer == 1)) {
+        mode = 0;
+        p.vec = (inner % V == 0 && (uintptr_t)in % 16 == 0) ? 1 : 0;
+        const int64_t rows = outer * C;
+        const int64_t want_items = (int64_t)sms * 8 * 8 * 4;
+        int64_t segs = want_items / rows;
+        if (segs < 1) segs = 1;
+        int64_t seg_len = (inner + segs - 1) / segs;
+        const int64_t quantum = 32 * V * 4;
+        seg_len = (seg_len + quantum - 1) / quantum * quantum;
+        p.seg_len = seg_len;
+        p.segs_per_row = (inner + seg_len - 1) / seg_len;
+        p.n_items = rows * p.segs_per_row;
+        const int64_t want = (p.n_items + 7) / 8;
+        blocks = (int)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);
+    } else if (inner == 1) {
+        mode = 1;
+        p.vec = (C % V == 0 && (uintptr_t)in % 16 == 0) ? 1 : 0;
+        // enough CTAs to cover the columns' idle threads: narrow tensors get more row splits
+        const int64_t cols_per_cta = p.vec ? 256 * V : 256;
+        const int64_t col_passes = (C + cols_per_cta - 1) / cols_per_cta;
+        // every CTA ends with one atomic per column: few CTAs, several rows in flight per thread
+        int64_t cap = (int64_t)sms * 4 / (col_passes > 4 ? 4 : col_passes);
+        if (cap < sms) cap = sms;
+        blocks = (int)(outer < cap ? outer : cap);
+    } else {
+        VQ_REQUIRE(n < (1ll << 31), "%s: tensors with 1 < inner < 64 must hold fewer than 2^31 elements", name);
+        mode = 2;
+        p.div_inner = make_fastdiv((uint32_t)inner);
+        p.div_C = make_fastdiv((uint32_t)C);
+        const int64_t want = (n + 255) / 256;
+        blocks = (int)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);
+    }
+    if (dtype == VQ_F32) {
+        if (mode == 0) amax_kernel<float, 0><<<blocks, 256, 0, st>>>(p);
+        else if (mode == 1) amax_kernel<float, 1><<<blocks, 256, 0, st>>>(p);
+        else amax_kernel<float, 2><<<blocks, 256, 0, st>>>(p);
+    } else {
+        if (mode == 0) amax_kernel<bf16_t, 0><<<blocks, 256, 0, st>>>(p);
+        else if (mode == 1) amax_kernel<bf16_t, 1><<<blocks, 256, 0, st>>>(p);
+        else amax_kernel<bf16_t, 2><<<blocks, 256, 0, st>>>(p);
+    }
+    VQ_LAUNCH_CHECK("amax_kernel");
+    return 0;
+}

@@ -11,7 +11,7 @@
 
 namespace {
 
-enum { OP_MAP = 0, OP_QUANT = 1, OP_DEQUANT = 2 };
+enum { OP_MAP = 0, OP_QUANT = 1, OP_DEQUANT = 2, OP_FAKEQ = 3 };   // FAKEQ: quantize then multiply by the scale
 
 struct EwParams {
     const void* in;
@@ -83,6 +83,9 @@ __device__ __forceinline__ float apply_one(const EwParams& p, const TableRes& r0
         Looked lk = table_lookup(p.t0, r0, f32_to_bf16_bits(q), p.out != nullptr, p.codes != nullptr);
         val = lk.val;
         code = lk.code;
+    } else if (OP == OP_FAKEQ) {
+        const float q = Arith<T>::rnd(dv(x));
+        val = Arith<T>::rnd(__fmul_rn(table_value(p.t0, r0, q, pat), s));
     } else {
         float v = x;
         if (p.t0.kind != VQ_TABLE_NONE) v = table_value(p.t0, r0, v, pat);
@@ -283,7 +286,7 @@ int launch_ew(EwParams& p, cudaStream_t stream) {
 template <int OP>
 int run_ew(const void* in, int dtype, int64_t n, const void* scale, const void* zp, const vq_scale_layout* layout,
            const vq_table* t0, const vq_table* t1, void* out, uint8_t* codes, int code_bits, void* stream) {
-    const char* name = OP == OP_MAP ? "vq_lut_map" : OP == OP_QUANT ? "vq_quantize" : "vq_dequantize";
+    const char* name = OP == OP_MAP ? "vq_lut_map" : OP == OP_QUANT ? "vq_quantize" : OP == OP_FAKEQ ? "vq_fake_quantize" : "vq_dequantize";
     VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
     VQ_REQUIRE(n >= 0, "%s: negative element count", name);
     if (n == 0) return 0;
@@ -388,6 +391,11 @@ int vq_quantize(const void* in, int dtype, int64_t n, const void* scale, const v
                 const vq_scale_layout* layout, const vq_table* table, void* out, uint8_t* out_codes, int code_bits,
                 void* stream) {
     return run_ew<OP_QUANT>(in, dtype, n, scale, zero_point, layout, table, nullptr, out, out_codes, code_bits, stream);
+}
+
+int vq_fake_quantize(const void* in, int dtype, int64_t n, const void* scale, const vq_scale_layout* layout,
+                     const vq_table* table, void* out, void* stream) {
+    return run_ew<OP_FAKEQ>(in, dtype, n, scale, nullptr, layout, table, nullptr, out, nullptr, 0, stream);
 }
 
 int vq_dequantize(const void* in, int dtype, int64_t n, const void* scale, const void* zero_point,

@@ -7,7 +7,7 @@
 
 namespace {
 
-enum { EW_MAP = 0, EW_QUANT = 1, EW_DEQUANT = 2 };
+enum { EW_MAP = 0, EW_QUANT = 1, EW_DEQUANT = 2, EW_FAKEQ = 3 };
 
 struct EwFastParams {
     const void* in;
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(1024, 1) ew_fast_kernel(const EwFastParams p) 
                     refine = true;
                     if (!ft.flat_tiny) chunk_amax<T>(x[u], refine, true);
                 }
-                fast_chunk<T, TK, OUT_FLOAT, SM>(ft, x[u], s, refine, (size_t)ci, out, nullptr);
+                fast_chunk<T, TK, OP == EW_FAKEQ ? OUT_FAKEQ : OUT_FLOAT, SM>(ft, x[u], s, refine, (size_t)ci, out, nullptr);
             }
         }
     }
@@ -109,13 +109,16 @@ int launch_op(const EwFastParams& p, int op, int tk, bool sm, int threads, int b
     if (op == EW_MAP)
         return tk == TK_INT ? launch3<T, EW_MAP, TK_INT>(p, false, threads, blocks, st)
                             : launch3<T, EW_MAP, TK_LUT>(p, sm, threads, blocks, st);
+    if (op == EW_FAKEQ)
+        return tk == TK_INT ? launch3<T, EW_FAKEQ, TK_INT>(p, false, threads, blocks, st)
+                            : launch3<T, EW_FAKEQ, TK_LUT>(p, sm, threads, blocks, st);
     return tk == TK_INT ? launch3<T, EW_QUANT, TK_INT>(p, false, threads, blocks, st)
                         : launch3<T, EW_QUANT, TK_LUT>(p, sm, threads, blocks, st);
 }
 
 }  // namespace
 
-// op: 0 map, 1 quantize, 2 dequantize (no tables).  Returns 1 when launched, 0 when not eligible.
+// op: 0 map, 1 quantize, 2 dequantize (no tables), 3 quantize then multiply by the scale.  Returns 1 when launched, 0 when not eligible.
 int vq_ew_fast_try(int op, const void* in, int dtype, int64_t n, const void* scale, const void* zero_point,
                    const vq_scale_layout* layout, const vq_table* t0, const vq_table* t1, void* out, uint8_t* codes,
                    cudaStream_t st) {

@@ -27,7 +27,8 @@
 
 namespace {
 
-enum { OUT_FLOAT = 0, OUT_PACK4 = 1, OUT_PACK8 = 2, OUT_SCALE = 3 };   // OUT_SCALE: block scales only
+enum { OUT_FLOAT = 0, OUT_PACK4 = 1, OUT_PACK8 = 2, OUT_SCALE = 3, OUT_FAKEQ = 4 };
+// OUT_SCALE: block scales only.  OUT_FAKEQ: the quantized value times the scale (quantize + dequantize).
 enum { TK_LUT = 0, TK_INT = 1 };
 
 // 32 bytes of input as raw words
@@ -209,7 +210,7 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
 #pragma unroll
     for (int j = 0; j < N; ++j) p[j] = bf16_pattern(v[j]);
 
-    if (OUT == OUT_FLOAT) {
+    if (OUT == OUT_FLOAT || OUT == OUT_FAKEQ) {
         uint32_t o[8];
         if (sizeof(T) == 2) {
 #pragma unroll
@@ -229,6 +230,16 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
             for (int k = 0; k < 8; ++k) {
                 if (TK == TK_LUT) o[k] = ld_u16<SM>(t.lut16, p[k]) << 16;
                 else o[k] = __float_as_uint(int_round(t, __uint_as_float(p[k] << 16)));
+            }
+        }
+        if (OUT == OUT_FAKEQ) {
+            if (sizeof(T) == 2) {
+                const uint32_t s2 = (__float_as_uint(s) >> 16) * 0x00010001u;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[k]) : "r"(o[k]), "r"(s2));
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = __float_as_uint(__fmul_rn(__uint_as_float(o[k]), s));
             }
         }
         store32(out_codes + ci * N, o);

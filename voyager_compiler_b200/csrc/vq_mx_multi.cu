@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
     ft.lo_is_zero = (p.tab.lo == 0.0f) ? 1 : 0;
     ft.flat_tiny = p.tab.flat_tiny;
     if (SM && TK == TK_LUT) {
-        const bool wide = OUT == OUT_FLOAT;
+        const bool wide = OUT == OUT_FLOAT || OUT == OUT_FAKEQ;
         const uint4* src = reinterpret_cast<const uint4*>(wide ? (const void*)p.tab.lut16 : (const void*)p.tab.lut8);
         const int n16 = wide ? 8192 : 4096;
         for (int i = threadIdx.x; i < n16; i += blockDim.x) smem[i] = __ldg(src + i);
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
         if (p.n_items == 1) {
             in = reinterpret_cast<const T*>(p.single.in);
             out_scale = reinterpret_cast<T*>(p.single.out_scale);
-            out_codes = reinterpret_cast<T*>(p.single.out_codes);
+            out_codes = reinterpret_cast<T*>(OUT == OUT_FAKEQ ? p.single.dequant : p.single.out_codes);
             scale_f32 = p.single.scale_f32;
             exp_e8 = p.single.exp_e8;
             codes8 = p.single.codes;
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             const vq_mx_item* it = p.items + lo;
             in = reinterpret_cast<const T*>(it->in);
             out_scale = reinterpret_cast<T*>(it->out_scale);
-            out_codes = reinterpret_cast<T*>(it->out_codes);
+            out_codes = reinterpret_cast<T*>(OUT == OUT_FAKEQ ? it->dequant : it->out_codes);
             scale_f32 = it->scale_f32;
             exp_e8 = it->exp_e8;
             codes8 = it->codes;
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             const float s = fast_scale<T, RULE>(p.rule, m);
             if ((ci & ((1u << gs) - 1u)) == 0) {
                 const uint32_t b = ci >> gs;
-                if (OUT == OUT_FLOAT || OUT == OUT_SCALE) {
+                if (OUT == OUT_FLOAT || OUT == OUT_SCALE || OUT == OUT_FAKEQ) {
                     store_one<T>(out_scale + b, s);
                 } else {
                     scale_f32[b] = s;
@@ -208,6 +208,9 @@ int dispatch_out(const FastParams& p, int out, bool sm, int threads, int blocks,
         case OUT_FLOAT:
             return sm ? launch_fast2<T, RULE, TK, OUT_FLOAT, true>(p, threads, blocks, smem, st)
                       : launch_fast2<T, RULE, TK, OUT_FLOAT, false>(p, threads, blocks, smem, st);
+        case OUT_FAKEQ:
+            return sm ? launch_fast2<T, RULE, TK, OUT_FAKEQ, true>(p, threads, blocks, smem, st)
+                      : launch_fast2<T, RULE, TK, OUT_FAKEQ, false>(p, threads, blocks, smem, st);
         case OUT_PACK4:
             return sm ? launch_fast2<T, RULE, TK, OUT_PACK4, true>(p, threads, blocks, smem, st)
                       : launch_fast2<T, RULE, TK, OUT_PACK4, false>(p, threads, blocks, smem, st);
@@ -260,19 +263,21 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
             if (it.out_scale && !it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes && !it.dequant) o = OUT_SCALE;
             else return 0;
         } else if (it.out_scale && it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes && !it.dequant) o = OUT_FLOAT;
+        else if (it.out_scale && it.dequant && !it.out_codes && !it.scale_f32 && !it.exp_e8 && !it.codes) o = OUT_FAKEQ;
         else if (it.codes && it.scale_f32 && !it.out_scale && !it.out_codes && !it.dequant && (code_bits == 4 || code_bits == 8))
             o = code_bits == 4 ? OUT_PACK4 : OUT_PACK8;
         else return 0;
         if (out >= 0 && o != out) return 0;
         if (it.exp_e8 && !pow2) return 0;
-        if (it.n % block || it.n >= (1ll << 31) || (uintptr_t)it.in % 32 || (uintptr_t)it.out_codes % 32 ||
+        if (it.n % block || it.n >= (1ll << 31) || (uintptr_t)it.in % 32 || (uintptr_t)it.out_codes % 32 || (uintptr_t)it.dequant % 32 ||
             (uintptr_t)it.codes % 16 || (uintptr_t)it.scale_f32 % 4)
             return 0;
         out = o;
         total += it.n;
     }
-    if (out != OUT_FLOAT && out != OUT_SCALE && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
-    if (out != OUT_FLOAT && out != OUT_SCALE && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
+    const bool packed_out = out == OUT_PACK4 || out == OUT_PACK8;
+    if (packed_out && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
+    if (packed_out && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
     if (n_items > 1 && !workspace) return 0;
     if (total == 0) return 1;
 
@@ -314,7 +319,7 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
             return vq_set_error(VQ_ERR_CUDA, "descriptor upload failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     }
     const bool sm = big && tk == TK_LUT;
-    const size_t smem = sm ? (out == OUT_FLOAT ? 131072 : 65536) : 0;
+    const size_t smem = sm ? ((out == OUT_FLOAT || out == OUT_FAKEQ) ? 131072 : 65536) : 0;
     const int64_t cap = big ? sms : (int64_t)sms * 8;
     const int blocks = (int)(p.n_tiles < cap ? p.n_tiles : cap);
     int rc = (dtype == VQ_F32) ? dispatch_rule<float>(p, pow2, tk, out, sm, threads, blocks, smem, st)
