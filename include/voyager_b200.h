@@ -247,6 +247,14 @@ VQ_API int vq_fake_quantize(const void* in, int dtype, int64_t n, const void* sc
  * src/voyager_compiler/quantization/fake_quantize.py:320-325.  Per tensor: outer = C = 1. */
 VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t inner, float* out, void* stream);
 
+/* The observer's state update as one launch (`_update_amax_scale`,
+ * src/voyager_compiler/quantization/fake_quantize.py:327-341): amax = max over history[history_len, channels]
+ * before amax_cur enters it; the history is rolled by -1 along its first axis and slot 0 set to
+ * amax_cur; scale = amax / quant_max, unchanged where amax is 0, NaN or Inf; pow2 != 0 rounds the
+ * scale up to a power of two (2 ** ceil(log2(scale)) in device arithmetic).  All fp32, in place. */
+VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
+                              double quant_max, int pow2, void* stream);
+
 /* One tensor of a per-channel pass, viewed as [channels, length] (a conv weight OIHW is
  * [O, I*H*W]).  Every output may be NULL, at least one must not be.  All tensors in `dtype`. */
 typedef struct vq_channel_item {

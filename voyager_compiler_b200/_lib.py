@@ -87,6 +87,7 @@ def _load():
         "vq_dequantize": [vp, ci, i64, vp, vp, L, T, T, vp, vp],
         "vq_fake_quantize": [vp, ci, i64, vp, L, T, vp, vp],
         "vq_amax": [vp, ci, i64, i64, i64, vp, vp],
+        "vq_observer_update": [vp, vp, vp, ci, i64, dbl, ci, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
         "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],
         "vq_row_codebook": [vp, ci, i64, i64, vp, ci, ci, vp, vp, vp, C.c_size_t, vp],

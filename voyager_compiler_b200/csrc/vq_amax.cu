@@ -11,6 +11,8 @@
 //   otherwise:   flat sweep, every lane keeps the maximum of its current channel and flushes it
 //                when the channel changes.
 // HBM bound: sizeof(T) read per element.
+#include <math_constants.h>
+
 #include "vq_common.cuh"
 
 namespace {
@@ -209,5 +211,51 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
         else amax_kernel<bf16_t, 2><<<blocks, 256, 0, st>>>(p);
     }
     VQ_LAUNCH_CHECK("amax_kernel");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The observer's state update, quantization/fake_quantize.py:327-341, as one small kernel:
+//   amax = max over the history (BEFORE the current maximum enters it);
+//   history <- roll(history, -1, 0); history[0] <- amax_cur;
+//   sf = amax / quant_max, keeping the previous scale where amax is 0, NaN or Inf;
+//   optionally sf <- 2 ** ceil(log2(sf)).
+// Upstream issues about a dozen tiny tensor operations for this.
+namespace {
+__global__ void observer_update_kernel(const float* __restrict__ amax_cur, float* __restrict__ history, float* __restrict__ scale,
+                                       int H, int64_t C, float qmax, int pow2) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    // torch.amax propagates NaN
+    float m = history[c];
+    bool nan = m != m;
+    for (int h = 1; h < H; ++h) {
+        const float v = history[(int64_t)h * C + c];
+        nan |= v != v;
+        m = fmaxf(m, v);
+    }
+    if (nan) m = __int_as_float(0x7FC00000);
+    // roll by -1 along the history axis, then overwrite slot 0
+    const float first = history[c];
+    for (int h = 0; h + 1 < H; ++h) history[(int64_t)h * C + c] = history[(int64_t)(h + 1) * C + c];
+    history[(int64_t)(H - 1) * C + c] = first;
+    history[c] = amax_cur[c];
+    float sf = __fdiv_rn(m, qmax);
+    const float prev = scale[c];
+    sf = (m > 0.0f) ? sf : prev;
+    sf = (fabsf(m) < CUDART_INF_F) ? sf : prev;
+    if (pow2) sf = exp2f(ceilf(log2f(sf)));
+    scale[c] = sf;
+}
+}  // namespace
+
+extern "C" int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
+                                  double quant_max, int pow2, void* stream) {
+    const char* name = "vq_observer_update";
+    VQ_REQUIRE(amax_cur && history && scale, "%s: null pointer", name);
+    VQ_REQUIRE(history_len >= 1 && channels >= 1, "%s: bad sizes", name);
+    observer_update_kernel<<<(unsigned)((channels + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+        amax_cur, history, scale, history_len, channels, (float)quant_max, pow2);
+    VQ_LAUNCH_CHECK("observer_update_kernel");
     return 0;
 }

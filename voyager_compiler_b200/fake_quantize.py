@@ -185,6 +185,7 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         # host mirrors of the two switches: reading the device buffers would synchronise every call
         self._fq_on, self._obs_on = True, self.qscheme is not None
         self._fq_host = torch.tensor([1], dtype=torch.uint8)       # what the autograd functions test
+        self._amax_cur = None                                      # fp32 scratch of the reduction
 
     # -- switches (torch.ao.quantization.FakeQuantizeBase interface)
     def enable_fake_quant(self, enabled: bool = True) -> None:
@@ -214,22 +215,27 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
     @torch.no_grad()
     def _update_amax_scale(self, x: torch.Tensor) -> None:
         """fake_quantize.py:309-341: the scale is derived from the history BEFORE the current amax
-        enters it; 0 / NaN / Inf maxima keep the previous scale."""
-        amax_cur = amax(x, self.ch_axis if self.is_per_channel else None)
+        enters it; 0 / NaN / Inf maxima keep the previous scale.  Two launches: the reduction and
+        one kernel for the whole state update."""
+        _require_cuda(x, "FusedAmaxObsFakeQuantize")
+        xc = x.contiguous()
+        if self.is_per_channel:
+            a = self.ch_axis % x.ndim
+            outer, ch, inner = math.prod(x.shape[:a]), x.shape[a], math.prod(x.shape[a + 1:])
+            shape = tuple(ch if i == a else 1 for i in range(x.ndim))
+        else:
+            outer, ch, inner, shape = 1, 1, xc.numel(), ()
         if self.amax_history.numel() == 0:
-            self.amax_history.resize_((self.amax_history_len,) + tuple(amax_cur.shape)).fill_(0.0)
-            self.scale.resize_(amax_cur.shape).fill_(1.0)
-        hist_max = torch.amax(self.amax_history, dim=0)
-        self.amax_history.copy_(torch.roll(self.amax_history, -1, 0))
-        self.amax_history[0] = amax_cur
-        # a tensor divisor: torch's CUDA division by a Python scalar multiplies by the reciprocal,
-        # which is not the IEEE quotient the CPU computes
-        sf = hist_max / torch.full((), self.quant_max, dtype=hist_max.dtype, device=hist_max.device)
-        sf = torch.where(hist_max > 0.0, sf, self.scale)
-        sf = torch.where(torch.isfinite(hist_max), sf, self.scale)
-        if self.force_scale_power_of_two:
-            sf = torch.pow(2, torch.ceil(torch.log2(sf)))
-        self.scale.copy_(sf)
+            self.amax_history.resize_((self.amax_history_len,) + shape).fill_(0.0)
+            self.scale.resize_(shape).fill_(1.0)
+        if self._amax_cur is None or self._amax_cur.numel() != ch or self._amax_cur.device != x.device:
+            self._amax_cur = torch.empty(ch, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+            _lib.check(_lib.lib.vq_amax(xc.data_ptr(), _DT[x.dtype], outer, ch, inner, self._amax_cur.data_ptr(), stream), "amax")
+            _lib.check(_lib.lib.vq_observer_update(self._amax_cur.data_ptr(), self.amax_history.data_ptr(),
+                                                   self.scale.data_ptr(), self.amax_history_len, ch, float(self.quant_max),
+                                                   1 if self.force_scale_power_of_two else 0, stream), "observer update")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.qscheme == QScheme.MICROSCALING:
