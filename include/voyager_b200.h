@@ -255,6 +255,27 @@ VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t 
 VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
                               double quant_max, int pow2, void* stream);
 
+/* `filter_outlier`, src/voyager_compiler/ops/quantized.py:565-621 (with `_pad_csr`, :538-562), over
+ * [batch, rows, cols] matrices: inlier[i] = in[i] where |in[i]| <= threshold (threshold rounded to the
+ * tensor dtype), +0 elsewhere; per matrix the non-zero outliers as a CSR in row / column order: values
+ * (tensor dtype) and int32 column indices in [batch, max_nnz] padded with 0 / -1, int32 row pointers
+ * [batch, rows + 1] starting at indptr_offset.  More than max_nnz outliers: the surplus is dropped and
+ * the row pointers are clamped, as upstream does.  `workspace`: vq_filter_outlier_workspace(batch, rows)
+ * bytes of device scratch. */
+VQ_API size_t vq_filter_outlier_workspace(int64_t batch, int64_t rows);
+VQ_API int vq_filter_outlier(const void* in, int dtype, int64_t batch, int64_t rows, int64_t cols, double threshold,
+                             int64_t max_nnz, int32_t indptr_offset, void* data, int32_t* indices, int32_t* indptr,
+                             void* inlier, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Y[b, r, :] = sum over the CSR entries (r, k, v) of matrix b of v * Bt[b, k, :], fp32 accumulation,
+ * one rounding to `dtype`: the sparse correction of `spmm_csr`, src/voyager_compiler/ops/quantized.py:786-862,
+ * with the right operand already decoded and in [K, N] order.  Row pointers may start above 0 (a
+ * slice of a longer CSR); data / indices then hold only the span they cover.  bt_batch_stride: elements
+ * between the Bt of consecutive batches, 0 when it is shared. */
+VQ_API int vq_spmm_csr(const void* data, const int32_t* indices, const int32_t* indptr, const void* Bt, int dtype,
+                       int64_t batch, int64_t rows, int64_t K, int64_t N, int64_t max_nnz, int64_t bt_batch_stride,
+                       void* Y, void* stream);
+
 /* One tensor of a per-channel pass, viewed as [channels, length] (a conv weight OIHW is
  * [O, I*H*W]).  Every output may be NULL, at least one must not be.  All tensors in `dtype`. */
 typedef struct vq_channel_item {

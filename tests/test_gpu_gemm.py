@@ -96,8 +96,17 @@ def test_fused_equals_plain_bitwise():
             outs[mode] = Q.linear_mx(xq.cuda(), wq.cuda(), None, input_scale=xs.cuda(), weight_scale=ws.cuda(), block_size=32)
         finally:
             del os.environ["VOYAGER_B200_GEMM"]
+    os.environ["VOYAGER_B200_GEMM"], os.environ["VOYAGER_B200_FUSED_STAGING"] = "fused", "regs"
+    try:            # the register-staged variant of the CTA-pair kernel (ragged last row tile included: 512 + 100 rows)
+        outs["regs"] = Q.linear_mx(xq.cuda(), wq.cuda(), None, input_scale=xs.cuda(), weight_scale=ws.cuda(), block_size=32)
+        x2, s2 = torch.cat([xq, xq[:100]]), torch.cat([xs, xs[:100]])
+        regs2 = Q.linear_mx(x2.cuda(), wq.cuda(), None, input_scale=s2.cuda(), weight_scale=ws.cuda(), block_size=32)
+    finally:
+        del os.environ["VOYAGER_B200_GEMM"], os.environ["VOYAGER_B200_FUSED_STAGING"]
     torch.cuda.synchronize()
     assert torch.equal(outs["fused"], outs["plain"])
+    assert torch.equal(outs["regs"], outs["plain"])
+    assert torch.equal(regs2[:512], outs["plain"]) and torch.equal(regs2[512:], outs["plain"][:100])
 
 
 def test_fused_with_bias_and_3d_input():

@@ -87,6 +87,8 @@ def _load():
         "vq_dequantize": [vp, ci, i64, vp, vp, L, T, T, vp, vp],
         "vq_fake_quantize": [vp, ci, i64, vp, L, T, vp, vp],
         "vq_amax": [vp, ci, i64, i64, i64, vp, vp],
+        "vq_filter_outlier": [vp, ci, i64, i64, i64, dbl, i64, C.c_int32, vp, vp, vp, vp, vp, C.c_size_t, vp],
+        "vq_spmm_csr": [vp, vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, vp, vp],
         "vq_observer_update": [vp, vp, vp, ci, i64, dbl, ci, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
         "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],
@@ -102,6 +104,8 @@ def _load():
     lib.vq_quantize_mx_multi_workspace.restype = C.c_size_t
     lib.vq_channel_quantize_multi_workspace.argtypes = [C.POINTER(VqChannelItem), ci]
     lib.vq_channel_quantize_multi_workspace.restype = C.c_size_t
+    lib.vq_filter_outlier_workspace.argtypes = [i64, i64]
+    lib.vq_filter_outlier_workspace.restype = C.c_size_t
     lib.vq_row_codebook_workspace.argtypes = [i64, ci]
     lib.vq_row_codebook_workspace.restype = C.c_size_t
     for name, args in sigs.items():

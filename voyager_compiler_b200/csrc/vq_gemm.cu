@@ -25,7 +25,8 @@
 // CTA-pair kernel (vq_gemm2.cu): 256 x 256 tiles on two CTAs; tensor maps with 128-row boxes
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
-                        cudaStream_t st, const CUtensorMap* tmSA = nullptr, const CUtensorMap* tmSB = nullptr);
+                        cudaStream_t st, const CUtensorMap* tmSA = nullptr, const CUtensorMap* tmSB = nullptr,
+                        const void* a_codes = nullptr, const void* b_codes = nullptr);
 
 namespace {
 
@@ -392,7 +393,8 @@ int vq_linear_mx(const void* a_codes, const void* a_scale, const void* b_codes, 
         if (int rc = make_map(&tmSA, a_scale, M, K / 32, 128, 16)) return rc;
         if (int rc = make_map(&tmSB, b_scale, N, K / 32, 128, 16)) return rc;
         void* ys[1] = {Y};
-        return vq_gemm_pair_launch(tmA, tmB, ys, 1, N, 0, bias, M, N, K, status, (cudaStream_t)stream, &tmSA, &tmSB);
+        return vq_gemm_pair_launch(tmA, tmB, ys, 1, N, 0, bias, M, N, K, status, (cudaStream_t)stream, &tmSA, &tmSB, a_codes,
+                                   b_codes);
     }
     memset(&tmA, 0, sizeof(tmA));
     memset(&tmB, 0, sizeof(tmB));

@@ -45,6 +45,8 @@ struct PairParams {
     int bulk_ok;               // output rows are 16-byte aligned: the epilogue may use bulk stores
     int32_t* status;
     int blocks_per_row;        // fused variant: the operand maps cover the CODES, two more maps the [rows, K/32] scales
+    const uint16_t* a_codes;   // register-staged variant: the code tensors themselves, [M, K] and [N, K]
+    const uint16_t* b_codes;
 };
 
 // shared -> global asynchronous bulk copy of `bytes` (multiple of 16) issued by one thread
@@ -63,7 +65,11 @@ __device__ __forceinline__ void record_fail(int32_t* status, int code) {
 // scales in place (shared memory -> registers -> shared memory, one bf16 rounding per product) before
 // the stage is handed to the MMA issuer.  Extra barrier raw[s] (per CTA): completion of the CTA's own
 // tile loads; full[s] then counts one arrival per CTA of the pair instead of bytes.
-template <bool FUSED>
+// FUSED == 2: the eight warps fetch the codes themselves with coalesced 16-byte global loads (one
+// k-step ahead, in registers), multiply and store straight into the swizzled operand layout: the
+// operand ring sees one write and one read per byte, as in the unfused kernel, instead of the
+// TMA write + read + write + read of the in-place variant, which is bound by the shared-memory pipe.
+template <int FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 448 : 192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const PairParams p) {
@@ -74,7 +80,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t bar_base = out_base + OUT_BYTES;
     const uint32_t FULL0 = bar_base, EMPTY0 = bar_base + 8u * PSTAGES, TFULL0 = bar_base + 16u * PSTAGES,
                    TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u, RAW0 = SLOT + 8u,
-                   SCF0 = RAW0 + 8u * PSTAGES, SCE0 = SCF0 + 8u * SC_BUFS;
+                   SCF0 = RAW0 + 8u * PSTAGES, SCE0 = SCF0 + 8u * SC_BUFS, ABORT = SCE0 + 8u * SC_BUFS;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
@@ -83,6 +89,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int n_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(ABORT), "r"(0u) : "memory");
         for (int s = 0; s < PSTAGES; ++s) {
             tc::mbar_init(FULL0 + 8u * s, FUSED ? 2 : 1);
             tc::mbar_init(EMPTY0 + 8u * s, 1);
@@ -128,8 +135,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         tc::tma_load_2d(sc_base + b * SC_BUF + SC_TILE, &tmSB, k * 2, n0, SCF0 + 8u * b);
                         ++group;
                     }
+                    if (FUSED == 2) continue;                 // the codes are fetched by the staging warps
                     if (!tc::mbar_wait_cluster(EMPTY0 + 8u * stage, phase ^ 1u, PWAIT)) { ok = false; break; }
-                    if (FUSED) {
+                    if (FUSED == 1) {
                         tc::mbar_expect_tx(RAW0 + 8u * stage, PSTAGE_BYTES);
                         tc::tma_load_2d(base + stage * PSTAGE_BYTES, &tmA, k * PK, m0, RAW0 + 8u * stage);
                         tc::tma_load_2d(base + stage * PSTAGE_BYTES + PA_BYTES, &tmB, k * PK, n0, RAW0 + 8u * stage);
@@ -172,7 +180,84 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if (!ok) record_fail(p.status, 12);
         }
-    } else if (FUSED && warp >= 6) {
+    } else if (FUSED == 2 && warp >= 6) {
+        // ------------------------------------------------------------------ register-staged dequantisation (8 warps per CTA)
+        // warps 0..3 stage the 128 A rows, warps 4..7 the 128 B rows of this CTA; one warp instruction
+        // moves 4 rows x 128 bytes: lane -> (row lane / 8, 16-byte chunk lane % 8)
+        const int t = (warp - 6) * 32 + lane;
+        const bool is_b = t >= 128;
+        const int wrow0 = ((t >> 5) & 3) * 32 + (lane >> 3);
+        const uint32_t c = (uint32_t)lane & 7u;
+        const uint16_t* gbase = is_b ? p.b_codes : p.a_codes;
+        const int nrows = is_b ? p.N : p.M;
+        const int my_tiles = pair < n_tiles ? (n_tiles - pair + npairs - 1) / npairs : 0;
+        const int total = my_tiles * num_k;                      // num_k is a multiple of 4 here
+        const uint32_t leader_full_base = tc::map_to_cta(FULL0, 0);
+        int stage = 0;
+        uint32_t phase = 0, group = 0;
+        bool ok = true;
+        auto issue = [&](uint32_t (&buf)[8][4], int step) {
+            const int tile = pair + (step / num_k) * npairs, k = step % num_k;
+            const int row0 = (is_b ? (tile / p.tiles_m) * PN + (int)rank * PNH : (tile % p.tiles_m) * 256 + (int)rank * PM) + wrow0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int row = row0 + 4 * i;
+                if (row < nrows) {
+                    const uint16_t* g = gbase + (size_t)row * p.K + (size_t)k * PK + c * 8u;
+                    asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(buf[i][0]), "=r"(buf[i][1]), "=r"(buf[i][2]), "=r"(buf[i][3]) : "l"(g));
+                } else {
+                    buf[i][0] = buf[i][1] = buf[i][2] = buf[i][3] = 0u;     // rows outside the matrix contribute zeros
+                }
+            }
+        };
+        // A wait that runs out sets the CTA's abort word; from then on the eight warps skip their waits
+        // but keep meeting on the named barrier, so that none of them is left behind at it.
+        auto process = [&](uint32_t (&buf)[8][4], int step) -> bool {
+            const int k = step % num_k;
+            bool good = true;
+            if (lane == 0) {
+                uint32_t aborted;
+                asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(aborted) : "r"(ABORT));
+                good = aborted == 0u;
+                if (good && (k % SC_GROUP) == 0) good = tc::mbar_wait(SCF0 + 8u * (group & 1u), (group >> 1) & 1u, PWAIT);
+                if (good) good = tc::mbar_wait_cluster(EMPTY0 + 8u * stage, phase ^ 1u, PWAIT);
+                if (!good) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(ABORT), "r"(1u) : "memory");
+            }
+            good = __shfl_sync(0xFFFFFFFFu, good, 0);
+            const uint32_t sc_addr = sc_base + (group & 1u) * SC_BUF + (is_b ? SC_TILE : 0) + (uint32_t)(k % SC_GROUP) * 4u + (c >> 2) * 2u;
+            const uint32_t st_addr = base + stage * PSTAGE_BYTES + (is_b ? PA_BYTES : 0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t r = (uint32_t)(wrow0 + 4 * i);
+                uint32_t sc;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(sc_addr + r * 32u));
+                const uint32_t s2 = sc * 0x00010001u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(buf[i][j]) : "r"(s2));
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(st_addr + r * 128u + ((c ^ (r & 7u)) << 4)),
+                             "r"(buf[i][0]), "r"(buf[i][1]), "r"(buf[i][2]), "r"(buf[i][3]) : "memory");
+            }
+            tc::fence_proxy_async();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (t == 0) tc::mbar_arrive_cluster(leader_full_base + 8u * stage);
+            if ((k % SC_GROUP) == SC_GROUP - 1 || k == num_k - 1) {      // done with this scale buffer
+                if (lane == 0) tc::mbar_arrive(SCE0 + 8u * (group & 1u));
+                ++group;
+            }
+            if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+            return good;
+        };
+        uint32_t b0[8][4], b1[8][4];
+        if (total > 0) issue(b0, 0);
+        for (int step = 0; step < total; step += 2) {
+            issue(b1, step + 1);
+            ok &= process(b0, step);
+            if (step + 2 < total) issue(b0, step + 2);
+            ok &= process(b1, step + 1);
+        }
+        if (!ok && lane == 0) record_fail(p.status, 15);
+    } else if (FUSED == 1 && warp >= 6) {
         // ------------------------------------------------------------------ in-place dequantisation (8 warps per CTA)
         // 8 warps: threads 0..127 own the 128 A rows, threads 128..255 the 128 B rows of this CTA
         const int t = (warp - 6) * 32 + lane;
@@ -319,8 +404,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // a_scale / b_scale the maps cover code tensors and dequantisation happens inside the kernel.
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
-                        cudaStream_t st, const CUtensorMap* tmSA, const CUtensorMap* tmSB) {
+                        cudaStream_t st, const CUtensorMap* tmSA, const CUtensorMap* tmSB, const void* a_codes,
+                        const void* b_codes) {
     const bool fused = tmSA != nullptr && tmSB != nullptr;
+    // VOYAGER_B200_FUSED_STAGING=regs selects the register-staged variant (measured slower: one k-step
+    // of global loads in flight per thread does not cover the L2 latency); default: TMA + in-place multiply
+    const char* staging = getenv("VOYAGER_B200_FUSED_STAGING");
+    const bool regs = fused && a_codes && b_codes && staging && !strcmp(staging, "regs");
     PairParams p{};
     for (int d = 0; d < n_outputs; ++d) p.Y[d] = reinterpret_cast<uint16_t*>(Ys[d]);
     p.n_outputs = n_outputs;
@@ -341,12 +431,18 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     if (n_tiles < pairs) pairs = n_tiles;
     const size_t smem = (size_t)PSTAGES * PSTAGE_BYTES + (fused ? SC_BUFS * SC_BUF : 0) + OUT_BYTES + 256 + 1024;
     if ((int)smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "device offers too little shared memory for the pair GEMM");
-    if (fused) {
-        auto k = mx_gemm_pair_kernel<true>;
+    p.a_codes = reinterpret_cast<const uint16_t*>(a_codes);
+    p.b_codes = reinterpret_cast<const uint16_t*>(b_codes);
+    if (regs) {
+        auto k = mx_gemm_pair_kernel<2>;
+        VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
+    } else if (fused) {
+        auto k = mx_gemm_pair_kernel<1>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
     } else {
-        auto k = mx_gemm_pair_kernel<false>;
+        auto k = mx_gemm_pair_kernel<0>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k<<<pairs * 2, 192, smem, st>>>(tmA, tmB, tmA, tmB, p);
     }

@@ -1,0 +1,286 @@
+// Outlier side path: split a tensor of [batch, rows, cols] matrices into inliers and a padded CSR of
+// outliers (`filter_outlier`, ops/quantized.py:565-621 with `_pad_csr`, :538-562), and the sparse
+// correction `spmm_csr` (:786-862) the MX linear adds to its dense product (:335-346).
+//
+// filter: an element is an outlier when |x| > threshold (threshold rounded to the tensor dtype, as
+// torch does for a Python scalar); the inlier tensor keeps x elsewhere and +0 at outliers; the CSR of
+// a matrix lists the non-zero outliers row by row in column order (`to_sparse_csr`), values and
+// int32 column indices padded to max_nnz with 0 / -1; when a matrix holds more than max_nnz the
+// surplus is dropped and the row pointers are clamped to max_nnz, as upstream does.
+//   1. count:  one warp per row counts its outliers;
+//   2. scan:   one CTA per matrix turns the counts into row pointers (clamped copy for the caller,
+//              unclamped copy for step 3) and writes the padding;
+//   3. fill:   one warp per row writes inliers and, by ballot + prefix count, its CSR entries.
+// Two reads and one write of the tensor; upstream makes ~6 full passes plus a sparse conversion
+// per matrix in a Python loop.
+#include <cstring>
+
+#include "vq_common.cuh"
+
+namespace {
+
+struct OutlierParams {
+    const void* in;
+    void* inlier;
+    void* data;             // [batch, max_nnz] in the tensor dtype
+    int32_t* indices;       // [batch, max_nnz]
+    int32_t* indptr;        // [batch, rows + 1], clamped
+    int32_t* offs;          // workspace [batch, rows + 1], unclamped
+    int64_t batch, rows, cols;
+    int64_t max_nnz;
+    float thr;              // already rounded to the tensor dtype
+    int32_t indptr_offset;
+};
+
+template <typename T>
+__device__ __forceinline__ float ld(const T* p, int64_t i);
+template <>
+__device__ __forceinline__ float ld<float>(const float* p, int64_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ld<bf16_t>(const bf16_t* p, int64_t i) { return bf16_bits_to_f32(p[i].bits); }
+
+__device__ __forceinline__ bool is_outlier(float x, float thr) { return fabsf(x) > thr; }   // false for NaN
+
+template <typename T>
+__global__ void __launch_bounds__(256) outlier_count_kernel(const OutlierParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t n_rows = p.batch * p.rows;
+    const T* x = reinterpret_cast<const T*>(p.in);
+    for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < n_rows; row += (int64_t)gridDim.x * 8) {
+        const T* xr = x + row * p.cols;
+        int cnt = 0;
+        for (int64_t c = lane; c < p.cols; c += 32) {
+            const float v = ld<T>(xr, c);
+            cnt += (is_outlier(v, p.thr) && v != 0.0f) ? 1 : 0;
+        }
+        cnt = __reduce_add_sync(0xFFFFFFFFu, cnt);
+        const int64_t b = row / p.rows, r = row - b * p.rows;
+        if (lane == 0) p.offs[b * (p.rows + 1) + r + 1] = cnt;
+    }
+}
+
+// one CTA (1024 threads) per matrix: inclusive scan of the row counts
+__global__ void __launch_bounds__(1024) outlier_scan_kernel(const OutlierParams p) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    const int64_t b = blockIdx.x;
+    int32_t* offs = p.offs + b * (p.rows + 1);
+    int32_t* indptr = p.indptr + b * (p.rows + 1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        carry = 0;
+        offs[0] = 0;
+        indptr[0] = p.indptr_offset;
+    }
+    __syncthreads();
+    const int64_t cap = p.max_nnz;
+    for (int64_t r0 = 0; r0 < p.rows; r0 += blockDim.x) {
+        const int64_t r = r0 + threadIdx.x;
+        int v = r < p.rows ? offs[r + 1] : 0;
+        int incl = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += t;
+            }
+            warp_sums[lane] = w;
+        }
+        __syncthreads();
+        const int total = incl + (warp ? warp_sums[warp - 1] : 0) + carry;
+        if (r < p.rows) {
+            offs[r + 1] = total;
+            indptr[r + 1] = (int32_t)(total < cap ? total : cap) + p.indptr_offset;
+        }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = total;
+        __syncthreads();
+    }
+    // padding behind the last stored entry
+    const int64_t nse = carry < cap ? carry : cap;
+    for (int64_t i = nse + threadIdx.x; i < cap; i += blockDim.x) p.indices[b * cap + i] = -1;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) outlier_fill_kernel(const OutlierParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t n_rows = p.batch * p.rows;
+    const T* x = reinterpret_cast<const T*>(p.in);
+    T* inl = reinterpret_cast<T*>(p.inlier);
+    T* data = reinterpret_cast<T*>(p.data);
+    for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < n_rows; row += (int64_t)gridDim.x * 8) {
+        const int64_t b = row / p.rows, r = row - b * p.rows;
+        const T* xr = x + row * p.cols;
+        T* ir = inl + row * p.cols;
+        int64_t pos = p.offs[b * (p.rows + 1) + r];
+        const bool any = p.offs[b * (p.rows + 1) + r + 1] != pos;      // rows without outliers: plain copy
+        for (int64_t c0 = 0; c0 < p.cols; c0 += 32) {
+            const int64_t c = c0 + lane;
+            T raw{};
+            float v = 0.0f;
+            if (c < p.cols) {
+                raw = xr[c];
+                v = ld<T>(xr, c);
+            }
+            const bool out = c < p.cols && is_outlier(v, p.thr);
+            if (c < p.cols) {
+                if (out) store_one<T>(ir + c, 0.0f);
+                else ir[c] = raw;
+            }
+            if (any) {
+                const bool keep = out && v != 0.0f;
+                const uint32_t mask = __ballot_sync(0xFFFFFFFFu, keep);
+                if (keep) {
+                    const int64_t q = pos + __popc(mask & ((1u << lane) - 1u));
+                    if (q < p.max_nnz) {
+                        data[b * p.max_nnz + q] = raw;
+                        p.indices[b * p.max_nnz + q] = (int32_t)c;
+                    }
+                }
+                pos += __popc(mask);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void outlier_pad_data_kernel(const OutlierParams p) {
+    // zero the value slots behind the last stored entry of every matrix
+    const int64_t b = blockIdx.y;
+    const int64_t total = p.offs[b * (p.rows + 1) + p.rows];
+    const int64_t nse = total < p.max_nnz ? total : p.max_nnz;
+    T* data = reinterpret_cast<T*>(p.data) + b * p.max_nnz;
+    for (int64_t i = nse + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.max_nnz; i += (int64_t)gridDim.x * blockDim.x)
+        store_one<T>(data + i, 0.0f);
+}
+
+// ---------------------------------------------------------------------------------------------
+// spmm: Y[b, r, :] = sum over the CSR entries (r, k, v) of v * Bt[b?, k, :], accumulated in fp32 and
+// rounded once to the output dtype (upstream: torch.sparse.mm in fp32, then a cast).  Bt is the
+// decoded right operand in [K, N] ("ck") order, so every entry reads one contiguous row.
+struct SpmmParams {
+    const void* data;
+    const int32_t* indices;
+    const int32_t* indptr;
+    const void* Bt;
+    void* Y;
+    int64_t batch, rows, N, K, max_nnz;
+    int64_t bt_batch_stride;      // 0 when Bt is shared by all batches
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) spmm_csr_kernel(const SpmmParams p) {
+    // one CTA per output row and 2048-column slab: thread t owns columns slab + t, + 256, ... (8 accumulators)
+    const int64_t row = blockIdx.x;
+    const int64_t b = row / p.rows, r = row - b * p.rows;
+    const int64_t n0 = (int64_t)blockIdx.y * 2048;
+    const int32_t* ip = p.indptr + b * (p.rows + 1);
+    const int32_t base = ip[0];
+    int64_t e0 = ip[r] - base, e1 = ip[r + 1] - base;
+    const T* data = reinterpret_cast<const T*>(p.data) + b * p.max_nnz;
+    const int32_t* idx = p.indices + b * p.max_nnz;
+    const T* Bt = reinterpret_cast<const T*>(p.Bt) + b * p.bt_batch_stride;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (int64_t e = e0; e < e1; ++e) {
+        const float v = ld<T>(data, e);
+        const int64_t k = idx[e];
+        const T* brow = Bt + k * p.N;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t n = n0 + threadIdx.x + 256 * j;
+            if (n < p.N) acc[j] = __fmaf_rn(v, ld<T>(brow, n), acc[j]);
+        }
+    }
+    T* y = reinterpret_cast<T*>(p.Y) + row * p.N;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int64_t n = n0 + threadIdx.x + 256 * j;
+        if (n < p.N) store_one<T>(y + n, Arith<T>::rnd(acc[j]));
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t vq_filter_outlier_workspace(int64_t batch, int64_t rows) {
+    if (batch < 0 || rows < 0) return 0;
+    return (size_t)batch * (size_t)(rows + 1) * sizeof(int32_t);
+}
+
+int vq_filter_outlier(const void* in, int dtype, int64_t batch, int64_t rows, int64_t cols, double threshold, int64_t max_nnz,
+                      int32_t indptr_offset, void* data, int32_t* indices, int32_t* indptr, void* inlier, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+    const char* name = "vq_filter_outlier";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0 && max_nnz >= 0, "%s: negative size", name);
+    VQ_REQUIRE(rows < (1ll << 31) && cols < (1ll << 31) && rows * cols < (1ll << 31), "%s: matrices must hold fewer than 2^31 elements", name);
+    if (batch == 0) return 0;
+    VQ_REQUIRE(indptr && inlier && (max_nnz == 0 || (data && indices)), "%s: null output", name);
+    VQ_REQUIRE(workspace && (uintptr_t)workspace % 4 == 0 && workspace_bytes >= vq_filter_outlier_workspace(batch, rows),
+               "%s: workspace missing or smaller than vq_filter_outlier_workspace(batch, rows)", name);
+    VQ_REQUIRE(rows * cols == 0 || in != nullptr, "%s: null input", name);
+    OutlierParams p{};
+    p.in = in; p.inlier = inlier; p.data = data; p.indices = indices; p.indptr = indptr;
+    p.offs = reinterpret_cast<int32_t*>(workspace);
+    p.batch = batch; p.rows = rows; p.cols = cols; p.max_nnz = max_nnz;
+    p.indptr_offset = indptr_offset;
+    float t = (float)threshold;
+    if (dtype == VQ_BF16) {        // float -> bf16, round to nearest even, as torch converts the scalar
+        uint32_t u;
+        memcpy(&u, &t, 4);
+        if ((u & 0x7FFFFFFFu) <= 0x7F800000u) u = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+        memcpy(&t, &u, 4);
+    }
+    p.thr = t;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int sms = vq_sm_count();
+    const int64_t n_rows = batch * rows;
+    const int64_t want = (n_rows + 7) / 8;
+    const int blocks = (int)(want < 1 ? 1 : (want < (int64_t)sms * 8 ? want : (int64_t)sms * 8));
+    if (dtype == VQ_F32) outlier_count_kernel<float><<<blocks, 256, 0, st>>>(p);
+    else outlier_count_kernel<bf16_t><<<blocks, 256, 0, st>>>(p);
+    VQ_LAUNCH_CHECK("outlier_count_kernel");
+    outlier_scan_kernel<<<(unsigned)batch, 1024, 0, st>>>(p);
+    VQ_LAUNCH_CHECK("outlier_scan_kernel");
+    if (max_nnz > 0) {
+        dim3 g((unsigned)((max_nnz + 255) / 256 < 64 ? (max_nnz + 255) / 256 : 64), (unsigned)batch);
+        if (dtype == VQ_F32) outlier_pad_data_kernel<float><<<g, 256, 0, st>>>(p);
+        else outlier_pad_data_kernel<bf16_t><<<g, 256, 0, st>>>(p);
+        VQ_LAUNCH_CHECK("outlier_pad_data_kernel");
+    }
+    if (n_rows > 0 && cols > 0) {
+        if (dtype == VQ_F32) outlier_fill_kernel<float><<<blocks, 256, 0, st>>>(p);
+        else outlier_fill_kernel<bf16_t><<<blocks, 256, 0, st>>>(p);
+        VQ_LAUNCH_CHECK("outlier_fill_kernel");
+    }
+    return 0;
+}
+
+int vq_spmm_csr(const void* data, const int32_t* indices, const int32_t* indptr, const void* Bt, int dtype, int64_t batch,
+                int64_t rows, int64_t K, int64_t N, int64_t max_nnz, int64_t bt_batch_stride, void* Y, void* stream) {
+    const char* name = "vq_spmm_csr";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(batch >= 0 && rows >= 0 && K >= 0 && N >= 0 && max_nnz >= 0, "%s: negative size", name);
+    if (batch * rows * N == 0) return 0;
+    VQ_REQUIRE(indptr && Y && (max_nnz == 0 || (data && indices && Bt)), "%s: null pointer", name);
+    VQ_REQUIRE(batch * rows < (1ll << 31), "%s: too many rows", name);
+    SpmmParams p{};
+    p.data = data; p.indices = indices; p.indptr = indptr; p.Bt = Bt; p.Y = Y;
+    p.batch = batch; p.rows = rows; p.N = N; p.K = K; p.max_nnz = max_nnz; p.bt_batch_stride = bt_batch_stride;
+    dim3 grid((unsigned)(batch * rows), (unsigned)((N + 2047) / 2048));
+    if (dtype == VQ_F32) spmm_csr_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    else spmm_csr_kernel<bf16_t><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    VQ_LAUNCH_CHECK("spmm_csr_kernel");
+    return 0;
+}
+
+}  // extern "C"

@@ -26,7 +26,7 @@ from .qtables import exp_tables, table_handle
 logger = logging.getLogger(__name__)
 
 __all__ = ["vmap", "quantize", "dequantize", "calculate_mx_qparam", "quantize_mx", "linear_mx", "matmul_mx", "conv2d_mx",
-           "register", "SCHEMAS"]
+           "filter_outlier", "quantize_mx_outlier", "slice_csr_tensor", "spmm_csr", "register", "SCHEMAS"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
 
@@ -58,6 +58,19 @@ SCHEMAS = {
                  "Tensor? weight_scale=None, int? block_size=None, Tensor? input_code=None, "
                  "Tensor? weight_code=None, Tensor? A_data=None, Tensor? A_indices=None, "
                  'Tensor? A_indptr=None, str weight_layout="ck") -> Tensor',
+    "filter_outlier": "filter_outlier(Tensor input, float threshold, float max_pct=0.01) "
+                      "-> (Tensor, Tensor, Tensor, Tensor)",
+    "quantize_mx_outlier": "quantize_mx_outlier(Tensor self, Tensor qmap, SymInt[] axes, "
+                           "int block_size, float quant_max, bool force_scale_power_of_two=False, "
+                           "Tensor scale_qmap=None, Tensor output_code=None, float? threshold=None, "
+                           "float max_pct=0.01, SymInt indptr_offset=0) "
+                           "-> (Tensor, Tensor, Tensor, Tensor, Tensor)",
+    "slice_csr_tensor": "slice_csr_tensor(Tensor data, Tensor indices, Tensor indptr, int dim=0, "
+                        "SymInt? start=None, SymInt? end=None, float size_factor=1.0) "
+                        "-> (Tensor, Tensor, Tensor)",
+    "spmm_csr": "spmm_csr(Tensor data, Tensor indices, Tensor indptr, Tensor B, "
+                "Tensor? B_scale=None, Tensor? B_code=None, int? block_size=None, "
+                'str weight_layout="kc") -> Tensor',
 }
 
 
@@ -314,16 +327,130 @@ def _decode_operand(name, t, code, scale, block_size):
     return t
 
 
+# ---------------------------------------------------------------------------------------------
+# Outlier side path
+# ---------------------------------------------------------------------------------------------
+def _filter_outlier(input: torch.Tensor, threshold: float, max_pct: float, indptr_offset: int = 0):
+    _require_cuda(input, "filter_outlier")
+    if input.dtype not in _DT:
+        raise NotImplementedError(f"filter_outlier: dtype {input.dtype} is not supported on CUDA")
+    if input.ndim < 2:
+        raise ValueError("filter_outlier: the input needs at least two dimensions")
+    x = input.contiguous()
+    batch_shape, (rows, cols) = tuple(x.shape[:-2]), x.shape[-2:]
+    batch = math.prod(batch_shape)
+    max_nnz = int(rows * cols * max_pct)
+    dev = x.device
+    data = torch.empty(batch_shape + (max_nnz,), dtype=x.dtype, device=dev)
+    indices = torch.empty(batch_shape + (max_nnz,), dtype=torch.int32, device=dev)
+    indptr = torch.empty(batch_shape + (rows + 1,), dtype=torch.int32, device=dev)
+    inlier = torch.empty_like(x)
+    if batch and rows * cols == 0:                      # empty matrices: empty CSRs
+        data.zero_()
+        indices.fill_(-1)
+        indptr.fill_(int(indptr_offset))
+    elif batch:
+        with torch.cuda.device(dev):
+            need = _lib.lib.vq_filter_outlier_workspace(batch, rows)
+            ws = torch.empty(max(need, 4), dtype=torch.uint8, device=dev)
+            _lib.check(_lib.lib.vq_filter_outlier(
+                x.data_ptr(), _DT[x.dtype], batch, rows, cols, float(threshold), max_nnz, int(indptr_offset),
+                data.data_ptr(), indices.data_ptr(), indptr.data_ptr(), inlier.data_ptr(), ws.data_ptr(), ws.numel(),
+                _stream(dev)), "filter_outlier")
+    return data, indices, indptr, inlier
+
+
+def filter_outlier(input: torch.Tensor, threshold: float, max_pct: float = 0.01):
+    """``(data, indices, indptr, inlier)``: elements with ``|x| > threshold`` leave the tensor as a
+    padded CSR per trailing matrix (ops/quantized.py:565-621)."""
+    return _filter_outlier(input, threshold, max_pct)
+
+
+def quantize_mx_outlier(input: torch.Tensor, qmap: torch.Tensor, axes: Sequence[int], block_size: int, quant_max: float,
+                        force_scale_power_of_two: bool = False, scale_qmap: Optional[torch.Tensor] = None,
+                        output_code: Optional[torch.Tensor] = None, threshold: Optional[float] = None,
+                        max_pct: float = 0.01, indptr_offset: int = 0):
+    """``(data, indices, indptr, scale, inliers)``: the outlier split followed by ``quantize_mx`` of
+    the inliers (ops/quantized.py:650-700)."""
+    data, indices, indptr, inlier = _filter_outlier(input, threshold, max_pct, indptr_offset)
+    scale, codes = quantize_mx(inlier, qmap, axes, block_size, quant_max, force_scale_power_of_two, scale_qmap)
+    return data, indices, indptr, scale, codes
+
+
+def _pad_csr(values, col_indices, crow_indices, max_nnz):
+    """ops/quantized.py:538-562 (the row pointers are clamped in place on overflow)."""
+    nse = int(crow_indices[-1].item())
+    pad = max_nnz - nse
+    if pad >= 0:
+        return torch.nn.functional.pad(values, (0, pad), value=0), torch.nn.functional.pad(col_indices, (0, pad), value=-1)
+    logger.warning("Number of outliers %d exceeds capacity %d; %d dropped.", nse, max_nnz, nse - max_nnz)
+    crow_indices.clamp_(max=max_nnz)
+    return values[:max_nnz], col_indices[:max_nnz]
+
+
+def slice_csr_tensor(data, indices, indptr, dim: int = 0, start=None, end=None, size_factor: float = 1.0):
+    """Rows or columns ``[start, end)`` of a padded CSR (ops/quantized.py:742-783).  Index bookkeeping
+    on arrays of at most max_nnz entries: done with torch operations on the tensors' device."""
+    dim = dim + 2 if dim < 0 else dim
+    if dim not in (0, 1):
+        raise ValueError(f"Cannot slice sparse CSR matrix along dim {dim}")
+    if dim == 0:
+        s0, e0 = int(indptr[start].item()), int(indptr[end].item())
+        new_indptr = indptr[start:end + 1] - s0
+        values, cols = data[s0:e0], indices[s0:e0]
+    else:
+        mask = (indices >= start) & (indices < end)
+        nse = int(indptr[-1].item())
+        per_row = torch.zeros(indptr.numel() - 1, dtype=torch.int64, device=indptr.device)
+        rows_of = torch.repeat_interleave(torch.arange(indptr.numel() - 1, device=indptr.device),
+                                          (indptr[1:] - indptr[:-1]).to(torch.int64))
+        per_row.index_add_(0, rows_of, mask[:nse].to(torch.int64))
+        new_indptr = torch.empty_like(indptr)
+        new_indptr[0] = 0
+        new_indptr[1:] = per_row.cumsum(0).to(indptr.dtype)
+        values, cols = data[mask], indices[mask] - start
+    new_data, new_indices = _pad_csr(values, cols, new_indptr, int(data.shape[0] * size_factor))
+    return new_data, new_indices, new_indptr
+
+
+def spmm_csr(data, indices, indptr, B, B_scale=None, B_code=None, block_size=None, weight_layout: str = "kc"):
+    """Sparse (padded CSR) x dense with the dense operand decoded like a ``linear_mx`` weight
+    (ops/quantized.py:786-862); fp32 accumulation, output in ``B``'s dtype."""
+    assert weight_layout in ("kc", "ck"), weight_layout
+    _require_cuda(B, "spmm_csr")
+    Bd = _decode_operand("spmm_csr", B, B_code, B_scale, block_size)
+    if Bd.dtype not in _DT:
+        raise NotImplementedError(f"spmm_csr: dtype {Bd.dtype} is not supported on CUDA")
+    if data.dtype != Bd.dtype:
+        raise NotImplementedError("spmm_csr: the sparse values and the dense operand must share a dtype")
+    Bt = (Bd.mT if weight_layout == "kc" else Bd).contiguous()           # [..., K, N]
+    batch_shape = tuple(indptr.shape[:-1])
+    batch = math.prod(batch_shape)
+    rows = indptr.shape[-1] - 1
+    K, N = Bt.shape[-2], Bt.shape[-1]
+    if Bt.ndim > 2 and math.prod(Bt.shape[:-2]) != batch:
+        raise ValueError("spmm_csr: batch dimensions of the sparse and the dense operand differ")
+    out = torch.empty(batch_shape + (rows, N), dtype=Bd.dtype, device=Bd.device)
+    if out.numel():
+        with torch.cuda.device(Bd.device):
+            _lib.check(_lib.lib.vq_spmm_csr(
+                data.contiguous().data_ptr(), indices.contiguous().data_ptr(), indptr.contiguous().data_ptr(), Bt.data_ptr(),
+                _DT[Bd.dtype], batch, rows, K, N, data.shape[-1], K * N if Bt.ndim > 2 else 0, out.data_ptr(),
+                _stream(Bd.device)), "spmm_csr")
+    return out
+
+
 def linear_mx(input, weight, bias=None, *, input_scale=None, weight_scale=None, block_size=None, input_code=None,
               weight_code=None, A_data=None, A_indices=None, A_indptr=None, weight_layout="kc"):
     """ops/quantized.py:295-348."""
     assert weight_layout in ("kc", "ck"), weight_layout
     _require_cuda(input, "linear_mx")
-    if A_data is not None:
-        raise NotImplementedError("linear_mx: the sparse outlier side path (A_data) is not implemented on CUDA")
     from .gemm import mx_gemm
-    return mx_gemm("linear_mx", input, weight, bias, input_scale, weight_scale, block_size, input_code, weight_code,
-                   b_is_nk=(weight_layout == "kc"))
+    dense = mx_gemm("linear_mx", input, weight, bias, input_scale, weight_scale, block_size, input_code, weight_code,
+                    b_is_nk=(weight_layout == "kc"))
+    if A_data is None:
+        return dense
+    return dense + spmm_csr(A_data, A_indices, A_indptr, weight, weight_scale, weight_code, block_size, weight_layout)
 
 
 def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=None, input_code=None, weight_code=None,
@@ -433,6 +560,33 @@ def register() -> str:
         m.impl("conv2d_mx", _conv_fake)
         m.impl("linear_mx", _lin_fake)
         m.impl("matmul_mx", _mm_fake)
+
+        # shapes as upstream's register_fake functions give them (ops/quantized.py:624-640, 703-732, 770-783, 865-879)
+        def _csr_fake(x, max_pct):
+            batch, (r, c) = tuple(x.shape[:-2]), x.shape[-2:]
+            nnz = int(r * c * max_pct)
+            return (x.new_empty(batch + (nnz,)), x.new_empty(batch + (nnz,), dtype=torch.int32),
+                    x.new_empty(batch + (r + 1,), dtype=torch.int32))
+
+        def _filter_fake(x, threshold, max_pct=0.01):
+            return (*_csr_fake(x, max_pct), torch.empty_like(x))
+
+        def _qmx_outlier_fake(x, q, axes, bs, qmax, p2=False, sq=None, oc=None, threshold=None, max_pct=0.01, off=0):
+            return (*_csr_fake(x, max_pct), x.new_empty(_fake_mx_shape(x, axes, bs)),
+                    torch.empty_like(x, memory_format=torch.contiguous_format))
+
+        def _slice_fake(data, indices, indptr, dim=0, start=None, end=None, size_factor=1.0):
+            ip = torch.empty_like(indptr)
+            return torch.empty_like(data), torch.empty_like(indices), (ip[start:end + 1] if dim in (0, -2) else ip)
+
+        def _spmm_fake(data, indices, indptr, B, B_scale=None, B_code=None, block_size=None, weight_layout="kc"):
+            n = B.shape[-1] if weight_layout == "ck" else B.shape[-2]
+            return data.new_empty(tuple(indptr.shape[:-1]) + (indptr.shape[-1] - 1, n))
+
+        m.impl("filter_outlier", _filter_fake)
+        m.impl("quantize_mx_outlier", _qmx_outlier_fake)
+        m.impl("slice_csr_tensor", _slice_fake)
+        m.impl("spmm_csr", _spmm_fake)
         _libs.append(m)
     c = torch.library.Library("quantized_ops", "IMPL", "CUDA")
     c.impl("vmap", vmap)
@@ -443,6 +597,10 @@ def register() -> str:
     c.impl("conv2d_mx", conv2d_mx)
     c.impl("linear_mx", linear_mx)
     c.impl("matmul_mx", matmul_mx)
+    for name, fn in (("filter_outlier", filter_outlier), ("quantize_mx_outlier", quantize_mx_outlier),
+                     ("slice_csr_tensor", slice_csr_tensor), ("spmm_csr", spmm_csr)):
+        if _op_defined(name):
+            c.impl(name, fn)
     _libs.append(c)
     _registered = mode
     logger.info("quantized_ops CUDA kernels registered (%s mode)", mode)
