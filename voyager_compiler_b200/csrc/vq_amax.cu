@@ -34,14 +34,17 @@ __device__ __forceinline__ uint32_t abs16<float>(const float* p) {
     const uint4 a = __ldcs(reinterpret_cast<const uint4*>(p));
     return max(max(a.x & 0x7FFFFFFFu, a.y & 0x7FFFFFFFu), max(a.z & 0x7FFFFFFFu, a.w & 0x7FFFFFFFu));
 }
+// max(|a|, |b|) per bf16 half; NaN wins; the sign bit of the result is the xor of the input signs
+__device__ __forceinline__ uint32_t absmax2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 template <>
 __device__ __forceinline__ uint32_t abs16<bf16_t>(const bf16_t* p) {
     const uint4 a = __ldcs(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-    uint32_t m = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) m = max(m, max((w[j] << 16) & 0x7FFFFFFFu, w[j] & 0x7FFF0000u));
-    return m;
+    const uint32_t m2 = absmax2(absmax2(a.x, a.y), absmax2(a.z, a.w));       // two packed maxima
+    return max((m2 << 16) & 0x7FFFFFFFu, m2 & 0x7FFF0000u);
 }
 template <typename T>
 __device__ __forceinline__ uint32_t abs1(const T* p, int64_t i);
