@@ -141,6 +141,24 @@ def test_kernel_quantize_mx_outlier_spmm_and_linear():
 
 
 @pytest.mark.gpu
+def test_matmul_mx_with_sparse_correction_batched():
+    """Attention-like batched operands: right operand [K, N] with blocks along -2 ("ck")."""
+    from voyager_compiler_b200 import ops
+    torch.manual_seed(8)
+    q = golden_table("int8")
+    A = torch.randn(2, 3, 16, 64)
+    A[torch.rand(2, 3, 16, 64) < 0.02] *= 30
+    A = A.to(torch.bfloat16)
+    B = torch.randn(2, 3, 64, 24).to(torch.bfloat16)
+    d, i, p, s, c = vo.quantize_mx_outlier(A, q, (-1,), 32, 127.0, True, None, 8.0, 0.1, 0)
+    bs, bq = vo.quantize_mx(B, q, (-2,), 32, 127.0, True)
+    want = vo.matmul_mx(c, bq, input_scale=s, weight_scale=bs, block_size=32) + vo.spmm_csr(d, i, p, bq, bs, None, 32, "ck")
+    got = ops.matmul_mx(c.cuda(), bq.cuda(), input_scale=s.cuda(), weight_scale=bs.cuda(), block_size=32,
+                        A_data=d.cuda(), A_indices=i.cuda(), A_indptr=p.cuda())
+    assert _rel(got, want) < 1e-2
+
+
+@pytest.mark.gpu
 def test_spmm_batched_and_ck_layout_against_oracle():
     from voyager_compiler_b200 import ops
     torch.manual_seed(3)

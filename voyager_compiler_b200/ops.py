@@ -458,11 +458,12 @@ def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=No
     """ops/quantized.py:371-421."""
     assert weight_layout in ("kc", "ck"), weight_layout
     _require_cuda(self, "matmul_mx")
-    if A_data is not None:
-        raise NotImplementedError("matmul_mx: the sparse outlier side path (A_data) is not implemented on CUDA")
     from .gemm import mx_gemm
-    return mx_gemm("matmul_mx", self, other, None, input_scale, weight_scale, block_size, input_code, weight_code,
-                   b_is_nk=(weight_layout == "kc"))
+    dense = mx_gemm("matmul_mx", self, other, None, input_scale, weight_scale, block_size, input_code, weight_code,
+                    b_is_nk=(weight_layout == "kc"))
+    if A_data is None:
+        return dense
+    return dense + spmm_csr(A_data, A_indices, A_indptr, other, weight_scale, weight_code, block_size, weight_layout)
 
 
 def _pair(v):
