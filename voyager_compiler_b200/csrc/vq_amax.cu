@@ -25,6 +25,7 @@ struct AmaxParams {
     int64_t seg_len, segs_per_row, n_items;   // row mode
     FastDiv div_inner, div_C;                 // flat mode (n < 2^31)
     int vec;                                  // 16-byte loads usable
+    int smem_cols;                            // column mode: per-CTA maxima staged in shared memory
 };
 
 template <typename T>
@@ -55,7 +56,7 @@ __device__ __forceinline__ uint32_t abs1<bf16_t>(const bf16_t* p, int64_t i) { r
 
 // MODE 0: rows, 1: columns (inner == 1), 2: flat
 template <typename T, int MODE>
-__global__ void __launch_bounds__(256) amax_kernel(const AmaxParams p) {
+__global__ void __launch_bounds__(MODE == 1 ? 1024 : 256) amax_kernel(const AmaxParams p) {
     constexpr int V = 16 / sizeof(T);
     const T* x = reinterpret_cast<const T*>(p.in);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -96,36 +97,60 @@ __global__ void __launch_bounds__(256) amax_kernel(const AmaxParams p) {
             if (lane == 0 && run) atomicMax(p.out + cur, run);
         }
     } else if (MODE == 1) {
-        // x is [outer, C]: a thread owns V consecutive columns (one 16-byte load per row) or one
-        // column; the grid splits the rows; one atomic per column and CTA
+        // x is [outer, C]: a thread owns V consecutive columns (one 16-byte load per row) of a row
+        // lane, or one column; the grid splits the rows.  The row lanes of a CTA meet in shared
+        // memory, then one atomic per column and CTA goes to the result (the atomics, not the reads,
+        // are what limits this mode, hence few and large CTAs).
+        extern __shared__ uint32_t col_max[];
         if (p.vec) {
-            for (int64_t c = (int64_t)threadIdx.x * V; c < p.C; c += (int64_t)blockDim.x * V) {
-                uint32_t m[V];
+            const int64_t G = p.C / V;                                   // column groups
+            const bool staged = p.smem_cols != 0;
+            if (staged) {
+                for (int64_t c = threadIdx.x; c < p.C; c += blockDim.x) col_max[c] = 0u;
+                __syncthreads();
+            }
+            const int64_t lanes = G >= blockDim.x ? 1 : blockDim.x / G;   // row lanes of this CTA
+            const int64_t lane_id = G >= blockDim.x ? 0 : threadIdx.x / G;
+            const int64_t g0 = G >= blockDim.x ? threadIdx.x : threadIdx.x % G;
+            if (lane_id < lanes) {
+                for (int64_t gcol = g0; gcol < G; gcol += blockDim.x) {
+                    const int64_t c = gcol * V;
+                    uint32_t m[V];
 #pragma unroll
-                for (int j = 0; j < V; ++j) m[j] = 0;
-                for (int64_t r = blockIdx.x; r < p.outer; r += (int64_t)gridDim.x * 4) {
-                    uint32_t w[4][4];
+                    for (int j = 0; j < V; ++j) m[j] = 0;
+                    constexpr int R = 4;          // rows in flight per thread
+                    const int64_t rstep = (int64_t)gridDim.x * lanes;
+                    for (int64_t r = (int64_t)blockIdx.x * lanes + lane_id; r < p.outer; r += rstep * R) {
+                        uint32_t w[R][4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        uint4 a = make_uint4(0, 0, 0, 0);
-                        if (r + (int64_t)u * gridDim.x < p.outer)
-                            a = __ldcs(reinterpret_cast<const uint4*>(x + (r + (int64_t)u * gridDim.x) * p.C + c));
-                        w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
+                        for (int u = 0; u < R; ++u) {
+                            uint4 a = make_uint4(0, 0, 0, 0);
+                            if (r + u * rstep < p.outer) a = __ldcs(reinterpret_cast<const uint4*>(x + (r + u * rstep) * p.C + c));
+                            w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
+                        }
+#pragma unroll
+                        for (int u = 0; u < R; ++u)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (sizeof(T) == 4) m[j] = max(m[j], w[u][j] & 0x7FFFFFFFu);
+                                else {
+                                    m[(2 * j) % V] = max(m[(2 * j) % V], (w[u][j] << 16) & 0x7FFFFFFFu);
+                                    m[(2 * j + 1) % V] = max(m[(2 * j + 1) % V], w[u][j] & 0x7FFF0000u);
+                                }
+                            }
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (sizeof(T) == 4) m[j] = max(m[j], w[u][j] & 0x7FFFFFFFu);
-                            else {
-                                m[(2 * j) % V] = max(m[(2 * j) % V], (w[u][j] << 16) & 0x7FFFFFFFu);
-                                m[(2 * j + 1) % V] = max(m[(2 * j + 1) % V], w[u][j] & 0x7FFF0000u);
-                            }
+                    for (int j = 0; j < V; ++j)
+                        if (m[j]) {
+                            if (staged) atomicMax(col_max + c + j, m[j]);
+                            else atomicMax(p.out + c + j, m[j]);
                         }
                 }
-#pragma unroll
-                for (int j = 0; j < V; ++j)
-                    if (m[j]) atomicMax(p.out + c + j, m[j]);
+            }
+            if (staged) {
+                __syncthreads();
+                for (int64_t c = threadIdx.x; c < p.C; c += blockDim.x)
+                    if (col_max[c]) atomicMax(p.out + c, col_max[c]);
             }
         } else {
             for (int64_t c = threadIdx.x; c < p.C; c += blockDim.x) {
@@ -170,7 +195,8 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
     const size_t es = dtype == VQ_F32 ? 4 : 2;
     const int V = (int)(16 / es);
     const int sms = vq_sm_count();
-    int mode, blocks;
+    int mode, blocks, threads = 256;
+    size_t smem = 0;
     if (inner >= 64 || (C == 1 && outer == 1)) {
         mode = 0;
         p.vec = (inner % V == 0 && (uintptr_t)in % 16 == 0) ? 1 : 0;
@@ -189,12 +215,10 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
     } else if (inner == 1) {
         mode = 1;
         p.vec = (C % V == 0 && (uintptr_t)in % 16 == 0) ? 1 : 0;
-        // enough CTAs to cover the columns' idle threads: narrow tensors get more row splits
-        const int64_t cols_per_cta = p.vec ? 256 * V : 256;
-        const int64_t col_passes = (C + cols_per_cta - 1) / cols_per_cta;
-        // every CTA ends with one atomic per column: few CTAs, several rows in flight per thread
-        int64_t cap = (int64_t)sms * 4 / (col_passes > 4 ? 4 : col_passes);
-        if (cap < sms) cap = sms;
+        p.smem_cols = (p.vec && C * 4 <= 48 * 1024) ? 1 : 0;
+        threads = p.vec ? 1024 : 256;
+        smem = p.smem_cols ? (size_t)C * 4 : 0;
+        const int64_t cap = p.vec ? sms : (int64_t)sms * 4;
         blocks = (int)(outer < cap ? outer : cap);
     } else {
         VQ_REQUIRE(n < (1ll << 31), "%s: tensors with 1 < inner < 64 must hold fewer than 2^31 elements", name);
@@ -206,11 +230,11 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
     }
     if (dtype == VQ_F32) {
         if (mode == 0) amax_kernel<float, 0><<<blocks, 256, 0, st>>>(p);
-        else if (mode == 1) amax_kernel<float, 1><<<blocks, 256, 0, st>>>(p);
+        else if (mode == 1) amax_kernel<float, 1><<<blocks, threads, smem, st>>>(p);
         else amax_kernel<float, 2><<<blocks, 256, 0, st>>>(p);
     } else {
         if (mode == 0) amax_kernel<bf16_t, 0><<<blocks, 256, 0, st>>>(p);
-        else if (mode == 1) amax_kernel<bf16_t, 1><<<blocks, 256, 0, st>>>(p);
+        else if (mode == 1) amax_kernel<bf16_t, 1><<<blocks, threads, smem, st>>>(p);
         else amax_kernel<bf16_t, 2><<<blocks, 256, 0, st>>>(p);
     }
     VQ_LAUNCH_CHECK("amax_kernel");

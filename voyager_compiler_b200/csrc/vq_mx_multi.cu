@@ -92,6 +92,10 @@ struct FastParams {
     int n_items;
     int64_t n_tiles;
     vq_mx_item single;
+    // up to kInlineItems descriptors travel in the kernel parameters (constant bank): no upload
+    vq_mx_item inl[28];
+    int64_t inl_prefix[29];
+    int n_inline;
     ScaleRule rule;
     TableDev tab;
     int group_shift;
@@ -100,7 +104,7 @@ struct FastParams {
 };
 
 template <typename T, int RULE, int TK, int OUT, bool SM, int U>
-__global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
+__global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant__ FastParams p) {
     extern __shared__ uint4 smem[];
     FastTab ft;
     ft.lut16 = p.tab.lut16;
@@ -141,6 +145,21 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const FastParams p) {
             codes8 = p.single.codes;
             nchunk = (uint32_t)(p.single.n / N);
             c0 = (uint32_t)tile * tile_chunks + threadIdx.x;
+        } else if (p.n_inline) {
+            int lo = 0, hi = p.n_items;
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (p.inl_prefix[mid] <= tile) lo = mid; else hi = mid;
+            }
+            const vq_mx_item& it = p.inl[lo];
+            in = reinterpret_cast<const T*>(it.in);
+            out_scale = reinterpret_cast<T*>(it.out_scale);
+            out_codes = reinterpret_cast<T*>(OUT == OUT_FAKEQ ? it.dequant : it.out_codes);
+            scale_f32 = it.scale_f32;
+            exp_e8 = it.exp_e8;
+            codes8 = it.codes;
+            nchunk = (uint32_t)(it.n / N);
+            c0 = (uint32_t)(tile - p.inl_prefix[lo]) * tile_chunks + threadIdx.x;
         } else {
             int lo = 0, hi = p.n_items;
             while (hi - lo > 1) {
@@ -278,7 +297,7 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     const bool packed_out = out == OUT_PACK4 || out == OUT_PACK8;
     if (packed_out && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
     if (packed_out && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
-    if (n_items > 1 && !workspace) return 0;
+    if (n_items > 28 && !workspace) return 0;
     if (total == 0) return 1;
 
     FastParams p{};
@@ -304,6 +323,14 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     if (n_items == 1) {
         p.single = items[0];
         p.n_tiles = (items[0].n + tile_elems - 1) / tile_elems;
+    } else if (n_items <= (int)(sizeof(p.inl) / sizeof(p.inl[0]))) {
+        p.n_inline = n_items;
+        p.inl_prefix[0] = 0;
+        for (int i = 0; i < n_items; ++i) {
+            p.inl[i] = items[i];
+            p.inl_prefix[i + 1] = p.inl_prefix[i] + (items[i].n + tile_elems - 1) / tile_elems;
+        }
+        p.n_tiles = p.inl_prefix[n_items];
     } else {
         int64_t* prefix = new int64_t[(size_t)n_items + 1];
         prefix[0] = 0;
