@@ -342,6 +342,15 @@ def run_linear(args):
     med, best = timed(lambda: Q.linear_mx(Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True)[1], wq, None, input_scale=xs,
                                           weight_scale=ws, block_size=32), args.steps)
     res["quantize_plus_linear"] = {"ms": med, "tflops": flops / med / 1e9}
+    # packed operands: int8 bytes + bf16 scales, conversion inside the GEMM's operand staging
+    from voyager_compiler_b200 import model_quant as mq
+    (px,) = mq.quantize_tensors_mx([x], qmap, 32, 127.0, True, code_bits=8)
+    (pw,) = mq.quantize_tensors_mx([w], qmap, 32, 127.0, True, code_bits=8)
+    med, best = timed(lambda: gemm_native.linear_mx_packed(px, pw), args.steps)
+    res["packed_int8_fused"] = {"ms": med, "tflops": flops / med / 1e9, "best_tflops": flops / best / 1e9}
+    med, best = timed(lambda: gemm_native.linear_mx_packed(
+        mq.quantize_tensors_mx([x], qmap, 32, 127.0, True, code_bits=8)[0], pw), args.steps)
+    res["quantize_packed_plus_packed_linear"] = {"ms": med, "tflops": flops / med / 1e9}
     clocks = sampler.stop()
     peaks, kind = measured_peaks()
     ok = gemm_native.gemm_status(dev) == 0

@@ -255,6 +255,17 @@ VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t 
 VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
                               double quant_max, int pow2, void* stream);
 
+/* vq_linear_mx on PACKED operands: a_codes [M,K] and b_codes [N,K] hold one int8 code per byte (as
+ * vq_quantize_mx / vq_quantize_mx_multi write them with code_bits 8 for an integer table), a_scale /
+ * b_scale are bf16 [rows, K/32].  Codes and scales arrive by TMA; the conversion int8 -> bf16(code *
+ * scale) happens inside the operand staging of the CTA-pair kernel, so the operands cost one byte per
+ * element of HBM and L2 traffic.  Same product as vq_linear_mx / `linear_mx`
+ * (src/voyager_compiler/ops/quantized.py:295-348) on the float codes.  Needs block 32, K a multiple of
+ * 256 and M > 128 (VQ_ERR_UNSUPPORTED otherwise). */
+VQ_API int vq_linear_mx_packed(const int8_t* a_codes, const void* a_scale, const int8_t* b_codes, const void* b_scale,
+                               const void* bias, void* Y, int64_t M, int64_t N, int64_t K, int64_t block,
+                               int32_t* status, void* stream);
+
 /* `filter_outlier`, src/voyager_compiler/ops/quantized.py:565-621 (with `_pad_csr`, :538-562), over
  * [batch, rows, cols] matrices: inlier[i] = in[i] where |in[i]| <= threshold (threshold rounded to the
  * tensor dtype), +0 elsewhere; per matrix the non-zero outliers as a CSR in row / column order: values

@@ -117,3 +117,26 @@ def test_fused_with_bias_and_3d_input():
     got = Q.linear_mx(x3.cuda(), wq.cuda(), bias.cuda(), input_scale=s3.cuda(), weight_scale=ws.cuda(), block_size=32)
     assert got.shape == (6, 50, 320) and _rel(got, want) <= 1e-2
     assert gemm_native.gemm_status("cuda") == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 2304, 4096), (512, 768, 2048), (612, 300, 512), (8192, 1024, 256), (64, 256, 512), (300, 256, 320)])
+def test_packed_operands_equal_the_float_code_path_bitwise(M, N, K):
+    """int8 bytes + bf16 scales through the packed GEMM (conversion inside the operand staging) against
+    the float-code linear_mx: int8 x 2^e is exact in bf16 and the MMA order is the same."""
+    from voyager_compiler_b200 import gemm_native, model_quant as mq
+    from golden_util import golden_table
+    torch.manual_seed(M + N + K)
+    q = golden_table("int8")
+    x = torch.randn(M, K).to(torch.bfloat16)
+    x[0, :32] = 0
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N).to(torch.bfloat16)
+    (px,) = mq.quantize_tensors_mx([x.cuda()], q, 32, 127.0, True, code_bits=8)
+    (pw,) = mq.quantize_tensors_mx([w.cuda()], q, 32, 127.0, True, code_bits=8)
+    got = gemm_native.linear_mx_packed(px, pw, bias.cuda())
+    xs, xq = Q.quantize_mx(x.cuda(), q.cuda(), (-1,), 32, 127.0, True)
+    ws, wq = Q.quantize_mx(w.cuda(), q.cuda(), (-1,), 32, 127.0, True)
+    want = Q.linear_mx(xq, wq, bias.cuda(), input_scale=xs, weight_scale=ws, block_size=32)
+    torch.cuda.synchronize()
+    assert gemm_native.gemm_status() == 0
+    assert torch.equal(got, want)

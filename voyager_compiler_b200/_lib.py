@@ -97,6 +97,7 @@ def _load():
         "vq_gemm_bf16_tn": [vp, vp, vp, vp, i64, i64, i64, vp, vp],
         "vq_gemm_bf16_tn_scatter": [vp, vp, vp, C.POINTER(C.c_void_p), ci, i64, i64, i64, i64, i64, vp, vp],
         "vq_linear_mx": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],
+        "vq_linear_mx_packed": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],
         "vq_quantize_mx_multi": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp, C.c_size_t, vp],
         "vq_channel_quantize_multi": [C.POINTER(VqChannelItem), ci, ci, dbl, T, vp, C.c_size_t, vp],
     }

@@ -26,7 +26,7 @@
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
                         cudaStream_t st, const CUtensorMap* tmSA = nullptr, const CUtensorMap* tmSB = nullptr,
-                        const void* a_codes = nullptr, const void* b_codes = nullptr);
+                        const void* a_codes = nullptr, const void* b_codes = nullptr, bool packed_codes = false);
 
 namespace {
 
@@ -309,6 +309,21 @@ int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box
     return 0;
 }
 
+// [rows, K] tensor of bytes (packed int8 codes), zero fill outside; tiles of box_rows x 64 bytes, no swizzle
+int make_map_u8(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return vq_set_error(VQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return vq_set_error(VQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
 int launch_gemm(bool fused, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t st) {
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
@@ -412,6 +427,28 @@ int vq_linear_mx(const void* a_codes, const void* a_scale, const void* b_codes, 
     p.b_scale = reinterpret_cast<const uint16_t*>(b_scale);
     p.blocks_per_row = (int)(K / 32);
     return launch_gemm(true, tmA, tmB, p, (cudaStream_t)stream);
+}
+
+int vq_linear_mx_packed(const int8_t* a_codes, const void* a_scale, const int8_t* b_codes, const void* b_scale,
+                        const void* bias, void* Y, int64_t M, int64_t N, int64_t K, int64_t block, int32_t* status,
+                        void* stream) {
+    const char* name = "vq_linear_mx_packed";
+    VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative size", name);
+    if (M == 0 || N == 0) return 0;
+    VQ_REQUIRE(a_codes && a_scale && b_codes && b_scale && Y, "%s: null pointer", name);
+    if (block != 32 || K % 256 != 0 || K <= 0 || M <= 128)
+        return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: needs block 32 along K, K a multiple of 256 and more than 128 rows", name);
+    VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "%s: sizes must be below 2^31", name);
+    VQ_REQUIRE((uintptr_t)a_codes % 16 == 0 && (uintptr_t)b_codes % 16 == 0 && (uintptr_t)a_scale % 16 == 0 &&
+                   (uintptr_t)b_scale % 16 == 0, "%s: code and scale tensors must be 16-byte aligned", name);
+    CUtensorMap tmA, tmB, tmSA, tmSB;
+    if (int rc = make_map_u8(&tmA, a_codes, M, K, 128)) return rc;
+    if (int rc = make_map_u8(&tmB, b_codes, N, K, 128)) return rc;
+    if (int rc = make_map(&tmSA, a_scale, M, K / 32, 128, 16)) return rc;
+    if (int rc = make_map(&tmSB, b_scale, N, K / 32, 128, 16)) return rc;
+    void* ys[1] = {Y};
+    return vq_gemm_pair_launch(tmA, tmB, ys, 1, N, 0, bias, M, N, K, status, (cudaStream_t)stream, &tmSA, &tmSB, nullptr, nullptr,
+                               true);
 }
 
 }  // extern "C"

@@ -69,6 +69,12 @@ __device__ __forceinline__ void record_fail(int32_t* status, int code) {
 // k-step ahead, in registers), multiply and store straight into the swizzled operand layout: the
 // operand ring sees one write and one read per byte, as in the unfused kernel, instead of the
 // TMA write + read + write + read of the in-place variant, which is bound by the shared-memory pipe.
+// FUSED == 3: the codes are PACKED int8 (one byte per element).  TMA brings 128 x 64-byte tiles into a
+// raw ring of 4 stages; the eight warps turn every byte into bf16(code * scale) with a sign-extending
+// byte permute, an integer add that plants the value in the significand of 1.5 * 2^23, and one fma
+// against the block scale (exact), and write the 128-byte-swizzled operand ring (3 stages).  Per
+// k-step and CTA the shared memory sees 16 KB + 16 KB + 32 KB + 32 KB instead of 4 x 32 KB, and HBM /
+// L2 half the operand bytes.
 template <int FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 448 : 192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -80,8 +86,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t bar_base = out_base + OUT_BYTES;
     const uint32_t FULL0 = bar_base, EMPTY0 = bar_base + 8u * PSTAGES, TFULL0 = bar_base + 16u * PSTAGES,
                    TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u, RAW0 = SLOT + 8u,
-                   SCF0 = RAW0 + 8u * PSTAGES, SCE0 = SCF0 + 8u * SC_BUFS, ABORT = SCE0 + 8u * SC_BUFS;
+                   SCF0 = RAW0 + 8u * PSTAGES, SCE0 = SCF0 + 8u * SC_BUFS, ABORT = SCE0 + 8u * SC_BUFS,
+                   RAWE0 = ABORT + 8u;       // packed variant: "raw stage free" barriers
 
+    constexpr int OST = FUSED == 3 ? 3 : PSTAGES;            // operand ring stages
+    constexpr int RST = 4;                                   // packed variant: raw ring stages (16 KB each)
+    constexpr uint32_t RAW_TILE = 128u * 64u, RAW_STAGE = 2u * RAW_TILE;
+    const uint32_t raw_base = base + OST * PSTAGE_BYTES;     // 3 x 32 KB + 4 x 16 KB = the 5 x 32 KB of the other variants
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
@@ -94,6 +105,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc::mbar_init(FULL0 + 8u * s, FUSED ? 2 : 1);
             tc::mbar_init(EMPTY0 + 8u * s, 1);
             tc::mbar_init(RAW0 + 8u * s, 1);
+            tc::mbar_init(RAWE0 + 8u * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(TFULL0 + 8u * s, 1);
@@ -119,8 +131,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 0) {
         // ------------------------------------------------------------------ tile loads (both CTAs)
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0, group = 0;
+            int stage = 0, rs = 0;
+            uint32_t phase = 0, group = 0, rphase = 0;
             bool ok = true;
             for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
                 const int m0 = (tile % p.tiles_m) * 256 + (int)rank * PM;
@@ -136,6 +148,14 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         ++group;
                     }
                     if (FUSED == 2) continue;                 // the codes are fetched by the staging warps
+                    if (FUSED == 3) {                         // packed codes into the raw ring
+                        if (!tc::mbar_wait(RAWE0 + 8u * rs, rphase ^ 1u, PWAIT)) { ok = false; break; }
+                        tc::mbar_expect_tx(RAW0 + 8u * rs, RAW_STAGE);
+                        tc::tma_load_2d(raw_base + rs * RAW_STAGE, &tmA, k * PK, m0, RAW0 + 8u * rs);
+                        tc::tma_load_2d(raw_base + rs * RAW_STAGE + RAW_TILE, &tmB, k * PK, n0, RAW0 + 8u * rs);
+                        if (++rs == RST) { rs = 0; rphase ^= 1u; }
+                        continue;
+                    }
                     if (!tc::mbar_wait_cluster(EMPTY0 + 8u * stage, phase ^ 1u, PWAIT)) { ok = false; break; }
                     if (FUSED == 1) {
                         tc::mbar_expect_tx(RAW0 + 8u * stage, PSTAGE_BYTES);
@@ -147,7 +167,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES, &tmA, k * PK, m0, leader_full);
                         tc::tma_load_2d_pair(base + stage * PSTAGE_BYTES + PA_BYTES, &tmB, k * PK, n0, leader_full);
                     }
-                    if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+                    if (++stage == OST) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) record_fail(p.status, 11);
@@ -172,7 +192,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int kk = 0; kk < PK / 16; ++kk)
                         tc::mma_f16_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (k | kk) != 0 ? 1u : 0u);
                     tc::mma_commit_pair(EMPTY0 + 8u * stage);
-                    if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+                    if (++stage == OST) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 tc::mma_commit_pair(TFULL0 + 8u * acc);
@@ -180,6 +200,76 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if (!ok) record_fail(p.status, 12);
         }
+    } else if (FUSED == 3 && warp >= 6) {
+        // ------------------------------------------------------------------ packed int8 codes -> bf16 operands (8 warps per CTA)
+        // warps 0..3 convert the 128 A rows, warps 4..7 the 128 B rows; one warp instruction covers
+        // 4 rows: lane -> (row lane / 8, 8-element chunk lane % 8): 8 raw bytes in, 16 operand bytes out
+        const int t = (warp - 6) * 32 + lane;
+        const bool is_b = t >= 128;
+        const int wrow0 = ((t >> 5) & 3) * 32 + (lane >> 3);
+        const uint32_t c = (uint32_t)lane & 7u;
+        const uint32_t leader_full_base = tc::map_to_cta(FULL0, 0);
+        int stage = 0, rs = 0;
+        uint32_t phase = 0, rphase = 0, group = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles; tile += npairs) {
+            for (int k = 0; k < num_k; ++k) {
+                bool good = true;
+                if (lane == 0) {
+                    uint32_t aborted;
+                    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(aborted) : "r"(ABORT));
+                    good = aborted == 0u;
+                    if (good && (k % SC_GROUP) == 0) good = tc::mbar_wait(SCF0 + 8u * (group & 1u), (group >> 1) & 1u, PWAIT);
+                    if (good) good = tc::mbar_wait(RAW0 + 8u * rs, rphase, PWAIT);
+                    if (good) good = tc::mbar_wait_cluster(EMPTY0 + 8u * stage, phase ^ 1u, PWAIT);
+                    if (!good) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(ABORT), "r"(1u) : "memory");
+                }
+                good = __shfl_sync(0xFFFFFFFFu, good, 0);
+                ok &= good;
+                const uint32_t sc_addr = sc_base + (group & 1u) * SC_BUF + (is_b ? SC_TILE : 0) + (uint32_t)(k % SC_GROUP) * 4u + (c >> 2) * 2u;
+                const uint32_t in_addr = raw_base + rs * RAW_STAGE + (is_b ? RAW_TILE : 0) + c * 8u;
+                const uint32_t st_addr = base + stage * PSTAGE_BYTES + (is_b ? PA_BYTES : 0);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t r = (uint32_t)(wrow0 + 4 * i);
+                    uint32_t w0, w1, sc;
+                    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(in_addr + r * 64u));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(sc_addr + r * 32u));
+                    const float sf = __uint_as_float(sc << 16);
+                    const float c0 = __fmul_rn(-12582912.0f, sf);          // exact: 1.5 * 2^23 times an 8-bit significand
+                    uint32_t o[4];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t w = h ? w1 : w0;
+                        float f[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // sign-extend byte j, plant it in the significand of 1.5 * 2^23: the float 12582912 + v
+                            uint32_t v;
+                            asm("prmt.b32 %0, %1, %1, %2;" : "=r"(v) : "r"(w), "r"((uint32_t)(((j | 8) * 0x1110) | j)));
+                            f[j] = __fmaf_rn(__uint_as_float(v + 0x4B400000u), sf, c0);     // = v * sf, exact
+                        }
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[2 * h]) : "f"(f[1]), "f"(f[0]));
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[2 * h + 1]) : "f"(f[3]), "f"(f[2]));
+                    }
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(st_addr + r * 128u + ((c ^ (r & 7u)) << 4)),
+                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                }
+                tc::fence_proxy_async();
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (t == 0) {
+                    tc::mbar_arrive_cluster(leader_full_base + 8u * stage);
+                    tc::mbar_arrive(RAWE0 + 8u * rs);
+                }
+                if ((k % SC_GROUP) == SC_GROUP - 1 || k == num_k - 1) {      // done with this scale buffer
+                    if (lane == 0) tc::mbar_arrive(SCE0 + 8u * (group & 1u));
+                    ++group;
+                }
+                if (++stage == OST) { stage = 0; phase ^= 1u; }
+                if (++rs == RST) { rs = 0; rphase ^= 1u; }
+            }
+        }
+        if (!ok && lane == 0) record_fail(p.status, 16);
     } else if (FUSED == 2 && warp >= 6) {
         // ------------------------------------------------------------------ register-staged dequantisation (8 warps per CTA)
         // warps 0..3 stage the 128 A rows, warps 4..7 the 128 B rows of this CTA; one warp instruction
@@ -259,56 +349,67 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!ok && lane == 0) record_fail(p.status, 15);
     } else if (FUSED == 1 && warp >= 6) {
         // ------------------------------------------------------------------ in-place dequantisation (8 warps per CTA)
-        // 8 warps: threads 0..127 own the 128 A rows, threads 128..255 the 128 B rows of this CTA
+        // Two groups of four warps take alternate k-steps, so that two stages are being rewritten at a
+        // time: in group g (the steps with k % 2 == g) thread r owns row r of the A tile and row r of
+        // the B tile of this CTA.
         const int t = (warp - 6) * 32 + lane;
-        const int r = t & 127;
-        const bool is_b = t >= 128;
+        const int g = t >> 7, r = t & 127;
         int stage = 0;
         uint32_t phase = 0, group = 0;
         bool ok = true;
         const uint32_t leader_full_base = tc::map_to_cta(FULL0, 0);
-        for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
+        for (int tile = pair; tile < n_tiles; tile += npairs) {
             for (int k = 0; k < num_k; ++k) {
-                if ((k % SC_GROUP) == 0) {                       // a new group of block scales
-                    if (lane == 0) ok = tc::mbar_wait(SCF0 + 8u * (group & 1u), (group >> 1) & 1u, PWAIT);
-                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                    if (!ok) break;
+                const int group_end = ((k / SC_GROUP) + 1) * SC_GROUP < num_k ? ((k / SC_GROUP) + 1) * SC_GROUP : num_k;
+                if ((k & 1) == g) {
+                    bool good = true;
+                    if (lane == 0) {
+                        uint32_t aborted;
+                        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(aborted) : "r"(ABORT));
+                        good = aborted == 0u;
+                        // the first step this group sees of a scale group waits for the scales
+                        if (good && (k % SC_GROUP) == g) good = tc::mbar_wait(SCF0 + 8u * (group & 1u), (group >> 1) & 1u, PWAIT);
+                        if (good) good = tc::mbar_wait(RAW0 + 8u * stage, phase, PWAIT);
+                        if (!good) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(ABORT), "r"(1u) : "memory");
+                    }
+                    good = __shfl_sync(0xFFFFFFFFu, good, 0);
+                    ok &= good;
+#pragma unroll
+                    for (int op = 0; op < 2; ++op) {                 // this row of the A tile, then of the B tile
+                        // the row's two block scales for this k-step (rows outside the matrix were zero filled)
+                        uint32_t sc;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc)
+                                     : "r"(sc_base + (group & 1u) * SC_BUF + (op ? SC_TILE : 0) + (uint32_t)r * 32u + (uint32_t)(k % SC_GROUP) * 4u));
+                        const uint32_t s_lo = (sc & 0xFFFFu) * 0x00010001u, s_hi = (sc >> 16) * 0x00010001u;
+                        const uint32_t row_addr = base + stage * PSTAGE_BYTES + (op ? PA_BYTES : 0) + (uint32_t)r * 128u;
+                        uint32_t v[8][4];
+                        // logical chunk c sits at physical chunk c ^ (r & 7) (128-byte swizzle); walking the
+                        // logical index keeps the 8 lanes of a quarter-warp on 8 different bank groups
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(v[c][0]), "=r"(v[c][1]), "=r"(v[c][2]), "=r"(v[c][3])
+                                         : "r"(row_addr + (uint32_t)((c ^ (r & 7)) << 4)));
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const uint32_t s2 = (c >> 2) ? s_hi : s_lo;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v[c][j]) : "r"(s2));
+                        }
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + (uint32_t)((c ^ (r & 7)) << 4)),
+                                         "r"(v[c][0]), "r"(v[c][1]), "r"(v[c][2]), "r"(v[c][3]) : "memory");
+                    }
+                    tc::fence_proxy_async();
+                    // one cluster-scope arrival per CTA and k-step: the group's warps meet on a named barrier first
+                    if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                    else asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (r == 0) tc::mbar_arrive_cluster(leader_full_base + 8u * stage);
+                    // this warp's last step inside the scale group: release the scale buffer
+                    if (k + 2 >= group_end && lane == 0) tc::mbar_arrive(SCE0 + 8u * (group & 1u));
                 }
-                if (lane == 0) ok = tc::mbar_wait(RAW0 + 8u * stage, phase, PWAIT);
-                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                if (!ok) break;
-                // this row's two block scales for this k-step (rows outside the matrix were zero filled)
-                uint32_t sc;
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc)
-                             : "r"(sc_base + (group & 1u) * SC_BUF + (is_b ? SC_TILE : 0) + (uint32_t)r * 32u + (uint32_t)(k % SC_GROUP) * 4u));
-                const uint32_t s_lo = (sc & 0xFFFFu) * 0x00010001u, s_hi = (sc >> 16) * 0x00010001u;
-                const uint32_t row_addr = base + stage * PSTAGE_BYTES + (is_b ? PA_BYTES : 0) + (uint32_t)r * 128u;
-                uint32_t v[8][4];
-#pragma unroll
-                // logical chunk c sits at physical chunk c ^ (r & 7) (128-byte swizzle); walking the
-                // logical index keeps the 8 lanes of a quarter-warp on 8 different bank groups
-                for (int c = 0; c < 8; ++c)
-                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(v[c][0]), "=r"(v[c][1]), "=r"(v[c][2]), "=r"(v[c][3])
-                                 : "r"(row_addr + (uint32_t)((c ^ (r & 7)) << 4)));
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint32_t s2 = (c >> 2) ? s_hi : s_lo;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v[c][j]) : "r"(s2));
-                }
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + (uint32_t)((c ^ (r & 7)) << 4)),
-                                 "r"(v[c][0]), "r"(v[c][1]), "r"(v[c][2]), "r"(v[c][3]) : "memory");
-                tc::fence_proxy_async();
-                // one cluster-scope arrival per CTA and k-step: the 8 warps meet on a named barrier first
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (t == 0) tc::mbar_arrive_cluster(leader_full_base + 8u * stage);
-                if ((k % SC_GROUP) == SC_GROUP - 1 || k == num_k - 1) {      // done with this scale buffer
-                    if (lane == 0) tc::mbar_arrive(SCE0 + 8u * (group & 1u));
-                    ++group;
-                }
+                if (k + 1 == group_end) ++group;
                 if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
             }
         }
@@ -405,7 +506,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
                         cudaStream_t st, const CUtensorMap* tmSA, const CUtensorMap* tmSB, const void* a_codes,
-                        const void* b_codes) {
+                        const void* b_codes, bool packed_codes) {
     const bool fused = tmSA != nullptr && tmSB != nullptr;
     // VOYAGER_B200_FUSED_STAGING=regs selects the register-staged variant (measured slower: one k-step
     // of global loads in flight per thread does not cover the L2 latency); default: TMA + in-place multiply
@@ -433,7 +534,11 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     if ((int)smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "device offers too little shared memory for the pair GEMM");
     p.a_codes = reinterpret_cast<const uint16_t*>(a_codes);
     p.b_codes = reinterpret_cast<const uint16_t*>(b_codes);
-    if (regs) {
+    if (fused && packed_codes) {
+        auto k = mx_gemm_pair_kernel<3>;
+        VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
+    } else if (regs) {
         auto k = mx_gemm_pair_kernel<2>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);

@@ -84,3 +84,49 @@ def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
                                           out.data_ptr(), M, N, K, st.data_ptr(), stream)
             _lib.check(rc, "linear_mx")
     return out.reshape(*lead, N)
+
+
+def linear_mx_packed(x, w, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``deq(x) @ deq(w).T (+ bias)`` in bf16 for two :class:`~voyager_compiler_b200.model_quant.PackedMX`
+    operands with 8-bit integer codes and blocks of 32 along the last axis (``quantize_tensors_mx(...,
+    code_bits=8)`` through an integer table): the GEMM reads the packed bytes and converts inside its
+    operand staging.  Shapes the packed kernel does not take (M <= 128, K not a multiple of 256) are
+    dequantised by ``dequantize_packed`` and multiplied by the TMA-fed GEMM."""
+    from . import model_quant as mq
+
+    for t, nm in ((x, "x"), (w, "w")):
+        if t.code_bits != 8 or t.block != 32:
+            raise NotImplementedError(f"linear_mx_packed: {nm} needs 8-bit codes and blocks of 32")
+        lv = t.levels
+        if lv.numel() != 256 or float(lv[1]) != 1.0 or float(lv[255]) != -1.0:
+            raise NotImplementedError(f"linear_mx_packed: {nm} must hold two's-complement integer codes")
+    K = x.shape[-1]
+    if len(w.shape) != 2 or w.shape[1] != K:
+        raise ValueError("linear_mx_packed: w must be [N, K] with the K of x")
+    N = w.shape[0]
+    lead = tuple(x.shape[:-1])
+    M = 1
+    for d in lead:
+        M *= d
+    dev = x.codes.device
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    if M == 0 or N == 0:
+        return out.reshape(*lead, N)
+    bias_c = bias.to(torch.bfloat16).contiguous() if bias is not None else None
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        st = _status_tensor(dev)
+        if M > 128 and K % 256 == 0:
+            xs = x.scale.to(torch.bfloat16).reshape(M, K // 32).contiguous()
+            ws = w.scale.to(torch.bfloat16).reshape(N, K // 32).contiguous()
+            rc = _lib.lib.vq_linear_mx_packed(x.codes.data_ptr(), xs.data_ptr(), w.codes.data_ptr(), ws.data_ptr(),
+                                              bias_c.data_ptr() if bias_c is not None else None, out.data_ptr(), M, N, K, 32,
+                                              st.data_ptr(), stream)
+            _lib.check(rc, "linear_mx_packed")
+        else:
+            da = mq.dequantize_packed(x, torch.bfloat16).reshape(M, K)
+            db = mq.dequantize_packed(w, torch.bfloat16)
+            rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                          out.data_ptr(), M, N, K, st.data_ptr(), stream)
+            _lib.check(rc, "linear_mx_packed")
+    return out.reshape(*lead, N)
