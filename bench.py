@@ -351,6 +351,19 @@ def run_linear(args):
     med, best = timed(lambda: gemm_native.linear_mx_packed(
         mq.quantize_tensors_mx([x], qmap, 32, 127.0, True, code_bits=8)[0], pw), args.steps)
     res["quantize_packed_plus_packed_linear"] = {"ms": med, "tflops": flops / med / 1e9}
+    # outlier side path: 0.1 % of the activations x 50, split off above a threshold, sparse correction added
+    xo = x.clone()
+    xo[torch.rand(M, K, generator=g, device=dev) < 0.001] *= 50
+    thr = 8.0
+    med, best = timed(lambda: Q.quantize_mx_outlier(xo, qmap, (-1,), 32, 127.0, True, None, None, thr, 0.01, 0), args.steps)
+    res["quantize_mx_outlier"] = {"ms": med, "gbs": (xo.numel() * (2 + 2 + 2 + 2 / 32)) / med / 1e6}
+    od, oi, op_, os_, oc = Q.quantize_mx_outlier(xo, qmap, (-1,), 32, 127.0, True, None, None, thr, 0.01, 0)
+    nnz = int(op_[-1].item())
+    med, best = timed(lambda: Q.spmm_csr(od, oi, op_, wq, ws, None, 32, "kc"), args.steps)
+    res["spmm_csr"] = {"ms": med, "nnz": nnz}
+    med, best = timed(lambda: Q.linear_mx(oc, wq, None, input_scale=os_, weight_scale=ws, block_size=32, A_data=od,
+                                          A_indices=oi, A_indptr=op_), args.steps)
+    res["linear_mx_with_outliers"] = {"ms": med, "tflops": flops / med / 1e9, "nnz": nnz}
     clocks = sampler.stop()
     peaks, kind = measured_peaks()
     ok = gemm_native.gemm_status(dev) == 0

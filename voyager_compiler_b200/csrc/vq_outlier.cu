@@ -30,6 +30,34 @@ struct OutlierParams {
     int64_t max_nnz;
     float thr;              // already rounded to the tensor dtype
     int32_t indptr_offset;
+    int vec;                // rows start 16-byte aligned and hold a multiple of 16 bytes
+};
+
+// 16 bytes of a row as fp32 values
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* v, uint4& raw) {
+        raw = __ldcs(reinterpret_cast<const uint4*>(p));
+        v[0] = __uint_as_float(raw.x); v[1] = __uint_as_float(raw.y); v[2] = __uint_as_float(raw.z); v[3] = __uint_as_float(raw.w);
+    }
+    static __device__ __forceinline__ void zero(uint4& raw, int j) { (&raw.x)[j] = 0u; }
+};
+template <>
+struct Vec16<bf16_t> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16_t* p, float* v, uint4& raw) {
+        raw = __ldcs(reinterpret_cast<const uint4*>(p));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+    }
+    static __device__ __forceinline__ void zero(uint4& raw, int j) { (&raw.x)[j >> 1] &= (j & 1) ? 0x0000FFFFu : 0xFFFF0000u; }
 };
 
 template <typename T>
@@ -49,6 +77,16 @@ __global__ void __launch_bounds__(256) outlier_count_kernel(const OutlierParams 
     for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < n_rows; row += (int64_t)gridDim.x * 8) {
         const T* xr = x + row * p.cols;
         int cnt = 0;
+        if (p.vec) {
+            constexpr int V = Vec16<T>::N;
+            for (int64_t c = (int64_t)lane * V; c < p.cols; c += 32 * V) {
+                float v[V];
+                uint4 raw;
+                Vec16<T>::load(xr + c, v, raw);
+#pragma unroll
+                for (int j = 0; j < V; ++j) cnt += (is_outlier(v[j], p.thr) && v[j] != 0.0f) ? 1 : 0;
+            }
+        } else
         for (int64_t c = lane; c < p.cols; c += 32) {
             const float v = ld<T>(xr, c);
             cnt += (is_outlier(v, p.thr) && v != 0.0f) ? 1 : 0;
@@ -120,6 +158,49 @@ __global__ void __launch_bounds__(256) outlier_fill_kernel(const OutlierParams p
         T* ir = inl + row * p.cols;
         int64_t pos = p.offs[b * (p.rows + 1) + r];
         const bool any = p.offs[b * (p.rows + 1) + r + 1] != pos;      // rows without outliers: plain copy
+        if (p.vec) {
+            // 16 bytes per lane and step: V consecutive elements; CSR order = lane order, then element order
+            constexpr int V = Vec16<T>::N;
+            for (int64_t c0 = 0; c0 < p.cols; c0 += 32 * V) {
+                const int64_t c = c0 + (int64_t)lane * V;
+                float v[V];
+                uint4 raw = make_uint4(0, 0, 0, 0);
+                const bool in = c < p.cols;
+                if (in) Vec16<T>::load(xr + c, v, raw);
+                uint4 keep_raw = raw;
+                int n = 0;
+                uint32_t out_mask = 0;
+                if (in) {
+#pragma unroll
+                    for (int j = 0; j < V; ++j)
+                        if (is_outlier(v[j], p.thr)) {
+                            Vec16<T>::zero(keep_raw, j);
+                            if (v[j] != 0.0f) { out_mask |= 1u << j; ++n; }
+                        }
+                    __stcs(reinterpret_cast<uint4*>(ir + c), keep_raw);
+                }
+                if (any) {
+                    // exclusive prefix of n over the lanes
+                    int incl = n;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    int64_t q = pos + incl - n;
+                    for (int j = 0; j < V; ++j)
+                        if (out_mask & (1u << j)) {
+                            if (q < p.max_nnz) {
+                                data[b * p.max_nnz + q] = xr[c + j];
+                                p.indices[b * p.max_nnz + q] = (int32_t)(c + j);
+                            }
+                            ++q;
+                        }
+                    pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
+                }
+            }
+            continue;
+        }
         for (int64_t c0 = 0; c0 < p.cols; c0 += 32) {
             const int64_t c = c0 + lane;
             T raw{};
@@ -241,6 +322,8 @@ int vq_filter_outlier(const void* in, int dtype, int64_t batch, int64_t rows, in
         memcpy(&t, &u, 4);
     }
     p.thr = t;
+    const size_t es = dtype == VQ_F32 ? 4 : 2;
+    p.vec = ((cols * es) % 16 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)inlier % 16 == 0) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
     const int sms = vq_sm_count();
     const int64_t n_rows = batch * rows;
