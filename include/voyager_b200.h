@@ -282,10 +282,11 @@ VQ_API int vq_filter_outlier(const void* in, int dtype, int64_t batch, int64_t r
  * one rounding to `dtype`: the sparse correction of `spmm_csr`, src/voyager_compiler/ops/quantized.py:786-862,
  * with the right operand already decoded and in [K, N] order.  Row pointers may start above 0 (a
  * slice of a longer CSR); data / indices then hold only the span they cover.  bt_batch_stride: elements
- * between the Bt of consecutive batches, 0 when it is shared. */
+ * between the Bt of consecutive batches, 0 when it is shared.  addend (optional, [batch, rows, N], may
+ * alias Y): Y = addend + product, the product rounded to `dtype` first, as `dense_out + spmm_out` does. */
 VQ_API int vq_spmm_csr(const void* data, const int32_t* indices, const int32_t* indptr, const void* Bt, int dtype,
                        int64_t batch, int64_t rows, int64_t K, int64_t N, int64_t max_nnz, int64_t bt_batch_stride,
-                       void* Y, void* stream);
+                       const void* addend, void* Y, void* stream);
 
 /* One tensor of a per-channel pass, viewed as [channels, length] (a conv weight OIHW is
  * [O, I*H*W]).  Every output may be NULL, at least one must not be.  All tensors in `dtype`. */

@@ -88,7 +88,7 @@ def _load():
         "vq_fake_quantize": [vp, ci, i64, vp, L, T, vp, vp],
         "vq_amax": [vp, ci, i64, i64, i64, vp, vp],
         "vq_filter_outlier": [vp, ci, i64, i64, i64, dbl, i64, C.c_int32, vp, vp, vp, vp, vp, C.c_size_t, vp],
-        "vq_spmm_csr": [vp, vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, vp, vp],
+        "vq_spmm_csr": [vp, vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, vp, vp, vp],
         "vq_observer_update": [vp, vp, vp, ci, i64, dbl, ci, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
         "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],

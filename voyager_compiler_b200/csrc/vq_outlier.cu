@@ -250,41 +250,100 @@ struct SpmmParams {
     const int32_t* indices;
     const int32_t* indptr;
     const void* Bt;
+    const void* addend;           // optional [batch, rows, N]: Y = addend + round(product), the linear's dense part
     void* Y;
     int64_t batch, rows, N, K, max_nnz;
     int64_t bt_batch_stride;      // 0 when Bt is shared by all batches
 };
 
+// eight consecutive elements of a row as fp32
 template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* v);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16_t>(const bf16_t* p, float* v) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float* v);     // v already rounded to T
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<bf16_t>(bf16_t* p, const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xFFFF0000u);
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One CTA per output row and 2048-column slab.  VEC: thread t owns the 8 consecutive columns
+// slab + 8 t (16- or 32-byte accesses); otherwise columns slab + t, + 256, ...
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) spmm_csr_kernel(const SpmmParams p) {
-    // one CTA per output row and 2048-column slab: thread t owns columns slab + t, + 256, ... (8 accumulators)
     const int64_t row = blockIdx.x;
     const int64_t b = row / p.rows, r = row - b * p.rows;
     const int64_t n0 = (int64_t)blockIdx.y * 2048;
     const int32_t* ip = p.indptr + b * (p.rows + 1);
     const int32_t base = ip[0];
-    int64_t e0 = ip[r] - base, e1 = ip[r + 1] - base;
+    const int64_t e0 = ip[r] - base, e1 = ip[r + 1] - base;
     const T* data = reinterpret_cast<const T*>(p.data) + b * p.max_nnz;
     const int32_t* idx = p.indices + b * p.max_nnz;
     const T* Bt = reinterpret_cast<const T*>(p.Bt) + b * p.bt_batch_stride;
+    T* y = reinterpret_cast<T*>(p.Y) + row * p.N;
+    const T* add = p.addend ? reinterpret_cast<const T*>(p.addend) + row * p.N : nullptr;
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    if (VEC) {
+        const int64_t n = n0 + (int64_t)threadIdx.x * 8;
+        if (n >= p.N) return;
+        for (int64_t e = e0; e < e1; ++e) {
+            const float v = ld<T>(data, e);
+            float w[8];
+            load8<T>(Bt + (int64_t)idx[e] * p.N + n, w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(v, w[j], acc[j]);
+        }
+        float o[8], a[8];
+        if (add) load8<T>(add + n, a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j] = Arith<T>::rnd(acc[j]);                              // the product, rounded to the output dtype ...
+            if (add) o[j] = Arith<T>::rnd(__fadd_rn(a[j], o[j]));      // ... then added to the dense part in that dtype
+        }
+        store8<T>(y + n, o);
+        return;
+    }
     for (int64_t e = e0; e < e1; ++e) {
         const float v = ld<T>(data, e);
-        const int64_t k = idx[e];
-        const T* brow = Bt + k * p.N;
+        const T* brow = Bt + (int64_t)idx[e] * p.N;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int64_t n = n0 + threadIdx.x + 256 * j;
             if (n < p.N) acc[j] = __fmaf_rn(v, ld<T>(brow, n), acc[j]);
         }
     }
-    T* y = reinterpret_cast<T*>(p.Y) + row * p.N;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int64_t n = n0 + threadIdx.x + 256 * j;
-        if (n < p.N) store_one<T>(y + n, Arith<T>::rnd(acc[j]));
+        if (n < p.N) {
+            float v = Arith<T>::rnd(acc[j]);
+            if (add) v = Arith<T>::rnd(__fadd_rn(ld<T>(add, n), v));
+            store_one<T>(y + n, v);
+        }
     }
 }
 
@@ -349,7 +408,8 @@ int vq_filter_outlier(const void* in, int dtype, int64_t batch, int64_t rows, in
 }
 
 int vq_spmm_csr(const void* data, const int32_t* indices, const int32_t* indptr, const void* Bt, int dtype, int64_t batch,
-                int64_t rows, int64_t K, int64_t N, int64_t max_nnz, int64_t bt_batch_stride, void* Y, void* stream) {
+                int64_t rows, int64_t K, int64_t N, int64_t max_nnz, int64_t bt_batch_stride, const void* addend, void* Y,
+                void* stream) {
     const char* name = "vq_spmm_csr";
     VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
     VQ_REQUIRE(batch >= 0 && rows >= 0 && K >= 0 && N >= 0 && max_nnz >= 0, "%s: negative size", name);
@@ -357,11 +417,20 @@ int vq_spmm_csr(const void* data, const int32_t* indices, const int32_t* indptr,
     VQ_REQUIRE(indptr && Y && (max_nnz == 0 || (data && indices && Bt)), "%s: null pointer", name);
     VQ_REQUIRE(batch * rows < (1ll << 31), "%s: too many rows", name);
     SpmmParams p{};
-    p.data = data; p.indices = indices; p.indptr = indptr; p.Bt = Bt; p.Y = Y;
+    p.data = data; p.indices = indices; p.indptr = indptr; p.Bt = Bt; p.Y = Y; p.addend = addend;
     p.batch = batch; p.rows = rows; p.N = N; p.K = K; p.max_nnz = max_nnz; p.bt_batch_stride = bt_batch_stride;
     dim3 grid((unsigned)(batch * rows), (unsigned)((N + 2047) / 2048));
-    if (dtype == VQ_F32) spmm_csr_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
-    else spmm_csr_kernel<bf16_t><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    const size_t es = dtype == VQ_F32 ? 4 : 2;
+    const bool vec = N % 8 == 0 && (uintptr_t)Bt % 16 == 0 && (uintptr_t)Y % 16 == 0 && (uintptr_t)addend % 16 == 0 &&
+                     (bt_batch_stride * es) % 16 == 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == VQ_F32) {
+        if (vec) spmm_csr_kernel<float, true><<<grid, 256, 0, st>>>(p);
+        else spmm_csr_kernel<float, false><<<grid, 256, 0, st>>>(p);
+    } else {
+        if (vec) spmm_csr_kernel<bf16_t, true><<<grid, 256, 0, st>>>(p);
+        else spmm_csr_kernel<bf16_t, false><<<grid, 256, 0, st>>>(p);
+    }
     VQ_LAUNCH_CHECK("spmm_csr_kernel");
     return 0;
 }

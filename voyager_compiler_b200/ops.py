@@ -413,29 +413,59 @@ def slice_csr_tensor(data, indices, indptr, dim: int = 0, start=None, end=None, 
     return new_data, new_indices, new_indptr
 
 
+_kn_cache: "dict" = {}
+
+
+def _decoded_kn(B, B_scale, B_code, block_size, weight_layout):
+    """The decoded dense operand of ``spmm_csr`` in [..., K, N] order.  A weight is static, so the
+    last few results are kept, keyed by the identity and version counters of the tensors involved
+    (weak references: an entry dies with its weight)."""
+    import weakref
+    parts = [t for t in (B, B_scale, B_code) if t is not None]
+    key = (tuple((t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in parts), block_size, weight_layout)
+    hit = _kn_cache.get(key)
+    if hit is not None and all(r() is t for r, t in zip(hit[0], parts)):
+        return hit[1]
+    Bd = _decode_operand("spmm_csr", B, B_code, B_scale, block_size)
+    Bt = (Bd.mT if weight_layout == "kc" else Bd).contiguous()
+    if len(_kn_cache) >= 8:
+        _kn_cache.pop(next(iter(_kn_cache)))
+    _kn_cache[key] = ([weakref.ref(t) for t in parts], Bt)
+    return Bt
+
+
 def spmm_csr(data, indices, indptr, B, B_scale=None, B_code=None, block_size=None, weight_layout: str = "kc"):
     """Sparse (padded CSR) x dense with the dense operand decoded like a ``linear_mx`` weight
     (ops/quantized.py:786-862); fp32 accumulation, output in ``B``'s dtype."""
+    return _spmm_csr(data, indices, indptr, B, B_scale, B_code, block_size, weight_layout, None)
+
+
+def _spmm_csr(data, indices, indptr, B, B_scale, B_code, block_size, weight_layout, addend):
+    """``spmm_csr``; with ``addend`` (the dense product, overwritten) the sum ``addend + spmm`` in one pass."""
     assert weight_layout in ("kc", "ck"), weight_layout
     _require_cuda(B, "spmm_csr")
-    Bd = _decode_operand("spmm_csr", B, B_code, B_scale, block_size)
-    if Bd.dtype not in _DT:
-        raise NotImplementedError(f"spmm_csr: dtype {Bd.dtype} is not supported on CUDA")
-    if data.dtype != Bd.dtype:
+    Bt = _decoded_kn(B, B_scale, B_code, block_size, weight_layout)      # [..., K, N]
+    if Bt.dtype not in _DT:
+        raise NotImplementedError(f"spmm_csr: dtype {Bt.dtype} is not supported on CUDA")
+    if data.dtype != Bt.dtype:
         raise NotImplementedError("spmm_csr: the sparse values and the dense operand must share a dtype")
-    Bt = (Bd.mT if weight_layout == "kc" else Bd).contiguous()           # [..., K, N]
+    Bd = Bt
     batch_shape = tuple(indptr.shape[:-1])
     batch = math.prod(batch_shape)
     rows = indptr.shape[-1] - 1
     K, N = Bt.shape[-2], Bt.shape[-1]
     if Bt.ndim > 2 and math.prod(Bt.shape[:-2]) != batch:
         raise ValueError("spmm_csr: batch dimensions of the sparse and the dense operand differ")
-    out = torch.empty(batch_shape + (rows, N), dtype=Bd.dtype, device=Bd.device)
+    if addend is not None and (addend.dtype != Bd.dtype or tuple(addend.shape) != batch_shape + (rows, N)
+                               or not addend.is_contiguous()):
+        return addend + _spmm_csr(data, indices, indptr, B, B_scale, B_code, block_size, weight_layout, None)
+    out = addend if addend is not None else torch.empty(batch_shape + (rows, N), dtype=Bd.dtype, device=Bd.device)
     if out.numel():
         with torch.cuda.device(Bd.device):
             _lib.check(_lib.lib.vq_spmm_csr(
                 data.contiguous().data_ptr(), indices.contiguous().data_ptr(), indptr.contiguous().data_ptr(), Bt.data_ptr(),
-                _DT[Bd.dtype], batch, rows, K, N, data.shape[-1], K * N if Bt.ndim > 2 else 0, out.data_ptr(),
+                _DT[Bd.dtype], batch, rows, K, N, data.shape[-1], K * N if Bt.ndim > 2 else 0,
+                addend.data_ptr() if addend is not None else None, out.data_ptr(),
                 _stream(Bd.device)), "spmm_csr")
     return out
 
@@ -450,7 +480,7 @@ def linear_mx(input, weight, bias=None, *, input_scale=None, weight_scale=None, 
                     b_is_nk=(weight_layout == "kc"))
     if A_data is None:
         return dense
-    return dense + spmm_csr(A_data, A_indices, A_indptr, weight, weight_scale, weight_code, block_size, weight_layout)
+    return _spmm_csr(A_data, A_indices, A_indptr, weight, weight_scale, weight_code, block_size, weight_layout, dense)
 
 
 def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=None, input_code=None, weight_code=None,
@@ -463,7 +493,7 @@ def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=No
                     b_is_nk=(weight_layout == "kc"))
     if A_data is None:
         return dense
-    return dense + spmm_csr(A_data, A_indices, A_indptr, other, weight_scale, weight_code, block_size, weight_layout)
+    return _spmm_csr(A_data, A_indices, A_indptr, other, weight_scale, weight_code, block_size, weight_layout, dense)
 
 
 def _pair(v):
