@@ -93,8 +93,8 @@ struct FastParams {
     int64_t n_tiles;
     vq_mx_item single;
     // up to kInlineItems descriptors travel in the kernel parameters (constant bank): no upload
-    vq_mx_item inl[28];
-    int64_t inl_prefix[29];
+    vq_mx_item inl[32];
+    int64_t inl_prefix[33];
     int n_inline;
     ScaleRule rule;
     TableDev tab;
@@ -297,7 +297,7 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     const bool packed_out = out == OUT_PACK4 || out == OUT_PACK8;
     if (packed_out && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
     if (packed_out && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
-    if (n_items > 28 && !workspace) return 0;
+    if (n_items > 32 && !workspace) return 0;
     if (total == 0) return 1;
 
     FastParams p{};

@@ -83,32 +83,53 @@ def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant
             exp = exp_tables(dt, quant_max, device) if force_scale_power_of_two else None
             items = (_lib.VqMxItem * len(idx))()
             keep = []
-            for k, i in enumerate(idx):
+            for i in idx:
                 t = tensors[i]
                 if t.device != device:
                     raise ValueError("all tensors must live on one device")
                 if t.ndim < 1 or t.shape[-1] % block:
                     raise NotImplementedError(
                         f"tensor {i}: last dimension {tuple(t.shape)} must be a multiple of the block ({block})")
-                x = t.contiguous()
-                nblk_shape = tuple(t.shape[:-1]) + (t.shape[-1] // block,)
-                items[k].input = x.data_ptr()
-                items[k].n = x.numel()
-                if float_outputs:
-                    sc = torch.empty(nblk_shape, dtype=dt, device=device)
+            if float_outputs:
+                for k, i in enumerate(idx):
+                    t = tensors[i]
+                    x = t.contiguous()
+                    sc = torch.empty(tuple(t.shape[:-1]) + (t.shape[-1] // block,), dtype=dt, device=device)
                     cd = torch.empty_like(x)
+                    items[k].input, items[k].n = x.data_ptr(), x.numel()
                     items[k].out_scale, items[k].out_codes = sc.data_ptr(), cd.data_ptr()
                     results[i] = (sc, cd)
-                else:
-                    sc = torch.empty(nblk_shape, dtype=torch.float32, device=device)
-                    per_byte = 8 // code_bits
-                    cd = torch.empty(tuple(t.shape[:-1]) + (t.shape[-1] // per_byte,), dtype=torch.uint8, device=device)
-                    ex = torch.empty(nblk_shape, dtype=torch.int8, device=device) if want_exp else None
-                    items[k].scale_f32, items[k].codes = sc.data_ptr(), cd.data_ptr()
-                    if ex is not None:
-                        items[k].exp_e8 = ex.data_ptr()
+                    keep.append(x)
+            else:
+                # one allocation per output kind for the whole group; the per-tensor results are views
+                # (16-byte aligned segments), which keeps the host cost of a call low for many tensors
+                per_byte = 8 // code_bits
+                nel = [tensors[i].numel() for i in idx]
+                cbytes = [(n // per_byte + 15) // 16 * 16 for n in nel]
+                nblk = [n // block for n in nel]
+                codes_all = torch.empty(sum(cbytes), dtype=torch.uint8, device=device)
+                scale_all = torch.empty(sum(nblk), dtype=torch.float32, device=device)
+                exp_all = torch.empty(sum(nblk), dtype=torch.int8, device=device) if want_exp else None
+                cviews, sviews = codes_all.split(cbytes), scale_all.split(nblk)
+                eviews = exp_all.split(nblk) if want_exp else None
+                cbase, sbase = codes_all.data_ptr(), scale_all.data_ptr()
+                ebase = exp_all.data_ptr() if want_exp else 0
+                coff = soff = 0
+                for k, i in enumerate(idx):
+                    t = tensors[i]
+                    x = t.contiguous()
+                    lead = tuple(t.shape[:-1])
+                    items[k].input, items[k].n = x.data_ptr(), nel[k]
+                    items[k].scale_f32, items[k].codes = sbase + 4 * soff, cbase + coff
+                    if want_exp:
+                        items[k].exp_e8 = ebase + soff
+                    cd = cviews[k][:nel[k] // per_byte].view(lead + (t.shape[-1] // per_byte,))
+                    sc = sviews[k].view(lead + (t.shape[-1] // block,))
+                    ex = eviews[k].view(lead + (t.shape[-1] // block,)) if want_exp else None
                     results[i] = PackedMX(cd, sc, tuple(t.shape), block, code_bits, tab.levels, ex)
-                keep.append(x)
+                    coff += cbytes[k]
+                    soff += nblk[k]
+                    keep.append(x)
             need = _lib.lib.vq_quantize_mx_multi_workspace(len(idx))
             ws = _workspace(device, need)
             _lib.check(_lib.lib.vq_quantize_mx_multi(
