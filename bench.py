@@ -530,7 +530,10 @@ def run_elementwise(args):
     from voyager_compiler_b200 import codebook
     torch.manual_seed(3)
     wt = (torch.distributions.StudentT(5.0).sample((11008, 4096)) * 0.02).to(dev)
-    lv = codebook.row_quantile_levels(wt, 16)                      # the fit: torch.quantile, not timed
+    lv = codebook.row_quantile_levels(wt, 16)
+    res["cfg4_row_quantile_fit16_11008x4096"] = timed(lambda: codebook.row_quantile_levels(wt, 16), wt.numel() * 4 + lv.numel() * 4)
+    qq = (2 * torch.arange(16, device=dev, dtype=torch.float32) + 1) / 32
+    res["cfg4_torch_quantile_fit16_11008x4096_for_scale"] = timed(lambda: torch.quantile(wt, qq, dim=-1), wt.numel() * 4 + lv.numel() * 4)
     res["cfg4_row_codebook16_search_fp32_rule_11008x4096"] = timed(
         lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=False), wt.numel() * 9 + lv.numel() * 4)
     res["cfg4_row_codebook16_search_reference_rule_11008x4096"] = timed(

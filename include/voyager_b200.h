@@ -336,6 +336,12 @@ VQ_API int vq_dequantize_packed(const uint8_t* codes, int code_bits, const float
  * `workspace`: device scratch of vq_row_codebook_workspace(rows, n_levels) bytes, 4-byte aligned (the
  * per-row decision thresholds are written there by a first small kernel on the same stream). */
 VQ_API size_t vq_row_codebook_workspace(int64_t rows, int n_levels);
+
+/* The fit of those codebooks: out[row, k] (fp32 [rows, n_levels]) = quantile of row `row` of x [rows, K] at
+ * (2k + 1) / (2 n_levels), linear interpolation, evaluated in fp32 exactly as torch.quantile does on the
+ * CPU; a row holding a NaN gives NaN.  K from 1 to 8192 (VQ_ERR_UNSUPPORTED otherwise).  No upstream
+ * counterpart (upstream codebooks are fitted per tensor by quantization/lcq.py). */
+VQ_API int vq_row_quantile(const void* x, int dtype, int64_t rows, int64_t K, int n_levels, float* out, void* stream);
 VQ_API int vq_row_codebook(const void* x, int dtype, int64_t rows, int64_t K, const float* levels, int n_levels,
                            int round_bf16, uint8_t* idx_out, void* deq_out, void* workspace, size_t workspace_bytes,
                            void* stream);

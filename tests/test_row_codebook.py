@@ -107,6 +107,25 @@ def test_full_size_properties_student_t_11008x4096():
     assert float((counts - 1 / 16).abs().max()) < 0.01         # quantile codebook: equal occupancy
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,K,n", [(64, 4096, 16), (300, 1000, 16), (17, 37, 7), (5, 8192, 256), (9, 1, 4), (33, 2, 3), (12, 129, 16)])
+def test_quantile_fit_matches_torch_cpu(dtype, rows, K, n):
+    from voyager_compiler_b200 import codebook
+    g = torch.Generator().manual_seed(rows * 7 + K)
+    x = (torch.randn(rows, K, generator=g) * torch.exp(torch.randn(rows, 1, generator=g) * 3)).to(dtype)
+    if K > 4:
+        x[1, :3] = x[1, 3]                                   # repeated values
+    q = (2 * torch.arange(n, dtype=torch.float32) + 1) / (2 * n)
+    want = torch.quantile(x.float(), q, dim=-1).t().contiguous()
+    got = codebook.row_quantile_levels(x.cuda(), n).cpu()
+    assert torch.equal(got, want)
+    if rows > 2 and K > 2:
+        x[2, K // 2] = float("nan")
+        got = codebook.row_quantile_levels(x.cuda(), n).cpu()
+        assert bool(torch.isnan(got[2]).all()) and torch.equal(got[:2], want[:2])
+
+
 def test_cpu_tensors_rejected():
     from voyager_compiler_b200 import codebook
     with pytest.raises(RuntimeError):

@@ -20,8 +20,22 @@ _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
 
 def row_quantile_levels(x: torch.Tensor, n_levels: int = 16) -> torch.Tensor:
     """Codebook of every row: its quantiles at (2k+1) / (2 n_levels), k = 0..n_levels-1, linear
-    interpolation (``torch.quantile``).  fp32 ``[rows, n_levels]``, ascending.  A torch call on the
-    tensor's device: the fit is not part of the quantize kernel."""
+    interpolation, fp32 ``[rows, n_levels]``, ascending; bit-identical to
+    ``torch.quantile(x.float(), q, dim=-1).T`` evaluated on the CPU.  Rows of up to 8192 elements
+    are sorted in shared memory by ``vq_row_quantile``; longer rows go through ``torch.quantile`` on
+    the device."""
+    if x.device.type != "cuda":
+        raise RuntimeError("row_quantile_levels: CUDA tensors only; there is no CPU path")
+    if x.ndim != 2:
+        raise ValueError("x must be [rows, K]")
+    rows, K = x.shape
+    if x.dtype in _DT and 1 <= K <= 8192 and 1 <= n_levels <= 256:
+        xc = x.contiguous()
+        out = torch.empty(rows, n_levels, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib.vq_row_quantile(xc.data_ptr(), _DT[x.dtype], rows, K, n_levels, out.data_ptr(),
+                                                torch.cuda.current_stream(x.device).cuda_stream), "row_quantile_levels")
+        return out
     q = (2 * torch.arange(n_levels, device=x.device, dtype=torch.float32) + 1) / (2 * n_levels)
     return torch.quantile(x.float(), q, dim=-1).t().contiguous()
 

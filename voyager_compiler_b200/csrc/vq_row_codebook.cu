@@ -329,6 +329,98 @@ void launch_row_codebook(const RowCbParams& p, bool vec, int blocks, cudaStream_
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// The fit of the per-row codebooks: out[row, k] = quantile of the row at q_k = (2k + 1) / (2n),
+// linear interpolation, exactly as torch.quantile evaluates it on the CPU in fp32:
+//   rank = q * (K - 1) (fp32), lo = floor(rank), w = rank - lo, a = sorted[lo], b = sorted[ceil(rank)],
+//   w < 0.5 ? fma(w, b - a, a) : fma(-(b - a), 1 - w, b);  a row holding a NaN gives NaN.
+// One CTA per row: the row is sorted in shared memory as order-preserving integer keys (bitonic
+// network over the next power of two, padded with the largest key), then n threads interpolate.
+namespace {
+
+constexpr int kQuantThreads = 512;
+
+template <typename T>
+__device__ __forceinline__ float load_elem(const T* p);
+template <>
+__device__ __forceinline__ float load_elem<float>(const float* p) { return __ldcs(p); }
+template <>
+__device__ __forceinline__ float load_elem<bf16_t>(const bf16_t* p) {
+    return bf16_bits_to_f32(__ldcs(reinterpret_cast<const unsigned short*>(p)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) row_quantile_kernel(const void* __restrict__ xin, float* __restrict__ out,
+                                                                      int64_t rows, int K, int P, int n) {
+    extern __shared__ uint32_t keys[];
+    __shared__ int has_nan;
+    const T* x = reinterpret_cast<const T*>(xin);
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        if (threadIdx.x == 0) has_nan = 0;
+        __syncthreads();
+        const T* xr = x + row * K;
+        bool nan = false;
+        for (int i = threadIdx.x; i < P; i += blockDim.x) {
+            uint32_t k = 0xFFFFFFFFu;
+            if (i < K) {
+                const float v = load_elem<T>(xr + i);
+                nan |= v != v;
+                k = key_of(v);
+            }
+            keys[i] = k;
+        }
+        if (nan) has_nan = 1;
+        __syncthreads();
+        for (int size = 2; size <= P; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int t = threadIdx.x; t < (P >> 1); t += blockDim.x) {
+                    const int i = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));     // lower index of the pair
+                    const int j = i + stride;
+                    const bool up = (i & size) == 0;
+                    const uint32_t a = keys[i], b = keys[j];
+                    if ((a > b) == up) { keys[i] = b; keys[j] = a; }
+                }
+                __syncthreads();
+            }
+        }
+        for (int k = threadIdx.x; k < n; k += blockDim.x) {
+            const float q = __fdiv_rn((float)(2 * k + 1), (float)(2 * n));
+            const float rank = __fmul_rn(q, (float)(K - 1));
+            const float lo = floorf(rank);
+            const float w = __fsub_rn(rank, lo);
+            const float a = value_of(keys[(int)lo]), b = value_of(keys[(int)ceilf(rank)]);
+            const float d = __fsub_rn(b, a);
+            float v = (w < 0.5f) ? __fmaf_rn(w, d, a) : __fmaf_rn(-d, __fsub_rn(1.0f, w), b);
+            if (has_nan) v = CUDART_NAN_F;
+            out[row * n + k] = v;
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+extern "C" int vq_row_quantile(const void* x, int dtype, int64_t rows, int64_t K, int n_levels, float* out, void* stream) {
+    const char* name = "vq_row_quantile";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(rows >= 0 && n_levels >= 1 && n_levels <= kMaxLevels, "%s: bad sizes", name);
+    if (K < 1 || K > 8192) return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: rows of 1 to 8192 elements", name);
+    if (rows == 0) return 0;
+    VQ_REQUIRE(x && out, "%s: null pointer", name);
+    int P = 1;
+    while (P < K) P <<= 1;
+    if (P < 2) P = 2;
+    const int sms = vq_sm_count();
+    const size_t smem = (size_t)P * 4;
+    const int per_sm = smem > 16 * 1024 ? 4 : 4;
+    const int blocks = (int)(rows < (int64_t)sms * per_sm ? rows : (int64_t)sms * per_sm);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == VQ_F32) row_quantile_kernel<float><<<blocks, kQuantThreads, smem, st>>>(x, out, rows, (int)K, P, n_levels);
+    else row_quantile_kernel<bf16_t><<<blocks, kQuantThreads, smem, st>>>(x, out, rows, (int)K, P, n_levels);
+    VQ_LAUNCH_CHECK("row_quantile_kernel");
+    return 0;
+}
+
 extern "C" size_t vq_row_codebook_workspace(int64_t rows, int n_levels) {
     if (rows < 0 || n_levels < 1) return 0;
     return (size_t)rows * (size_t)n_levels * sizeof(float);
