@@ -109,13 +109,25 @@ def test_full_size_properties_student_t_11008x4096():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,K,n", [(64, 4096, 16), (300, 1000, 16), (17, 37, 7), (5, 8192, 256), (9, 1, 4), (33, 2, 3), (12, 129, 16)])
+@pytest.mark.parametrize("rows,K,n", [(64, 4096, 16), (300, 1000, 16), (17, 37, 7), (5, 8192, 256), (9, 1, 4), (33, 2, 3), (12, 129, 16),
+                                      (40, 8192, 16), (50, 2048, 8), (30, 1024, 16), (20, 5000, 3), (600, 4096, 16)])
 def test_quantile_fit_matches_torch_cpu(dtype, rows, K, n):
     from voyager_compiler_b200 import codebook
     g = torch.Generator().manual_seed(rows * 7 + K)
     x = (torch.randn(rows, K, generator=g) * torch.exp(torch.randn(rows, 1, generator=g) * 3)).to(dtype)
     if K > 4:
         x[1, :3] = x[1, 3]                                   # repeated values
+    if rows > 12 and K > 16:                                 # rows the binned selection cannot split, and ones it barely can
+        x[3] = 0.375
+        x[4, 0] = 1e30
+        x[5, 7] = float("inf")
+        x[6, 9] = float("-inf")
+        x[7] = (x[7].float() * 4).round().to(dtype)
+        x[8, :2] = torch.tensor([-3e38, 3e38]).to(dtype)
+        x[9] = x[9].abs()
+        x[10, 5] = 1e-3 * float(x[10].float().abs().max()) + 100 * float(x[10].float().abs().max())
+        x[11, ::2] = 0.0
+        x[11, 1::4] = -0.0
     q = (2 * torch.arange(n, dtype=torch.float32) + 1) / (2 * n)
     want = torch.quantile(x.float(), q, dim=-1).t().contiguous()
     got = codebook.row_quantile_levels(x.cuda(), n).cpu()

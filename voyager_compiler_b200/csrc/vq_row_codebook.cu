@@ -349,53 +349,297 @@ __device__ __forceinline__ float load_elem<bf16_t>(const bf16_t* p) {
     return bf16_bits_to_f32(__ldcs(reinterpret_cast<const unsigned short*>(p)));
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kQuantThreads) row_quantile_kernel(const void* __restrict__ xin, float* __restrict__ out,
-                                                                      int64_t rows, int K, int P, int n) {
-    extern __shared__ uint32_t keys[];
-    __shared__ int has_nan;
-    const T* x = reinterpret_cast<const T*>(xin);
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        if (threadIdx.x == 0) has_nan = 0;
-        __syncthreads();
-        const T* xr = x + row * K;
-        bool nan = false;
-        for (int i = threadIdx.x; i < P; i += blockDim.x) {
-            uint32_t k = 0xFFFFFFFFu;
-            if (i < K) {
-                const float v = load_elem<T>(xr + i);
-                nan |= v != v;
-                k = key_of(v);
+// Shared-memory position of sort index i: index bits 5..9 are folded onto the bank bits, so that both the
+// unit-stride accesses of the wide windows and the stride-8 accesses of the lowest window spread over all banks.
+__device__ __forceinline__ int sort_slot(int i) { return i ^ ((i >> 5) & 31); }
+
+// One compare-exchange stage of the bitonic network on the eight keys a thread holds: pairs differ in bit SB of
+// the register index; the direction of a pair is ascending where bit `mbit` of its sort index is clear.
+template <int SB>
+__device__ __forceinline__ void sort_stage(uint32_t (&v)[8], bool base_up, int jm) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (j & (1 << SB)) continue;
+        const int j2 = j | (1 << SB);
+        const bool up = base_up && ((j & jm) == 0);
+        const uint32_t lo = min(v[j], v[j2]), hi = max(v[j], v[j2]);
+        v[j] = up ? lo : hi;
+        v[j2] = up ? hi : lo;
+    }
+}
+
+// Stages (m, s) for m = m_lo..m_hi, s = min(s_hi, m - 1) down to s_lo of the network over P = 2^p keys, all of
+// whose stride bits lie in the window b..b+2: each thread takes the eight keys that differ in those three index
+// bits, runs the stages in registers and puts the keys back.  Ends with a CTA barrier.
+__device__ __forceinline__ void sort_phase(uint32_t* keys, int P, int p, int b, int m_lo, int m_hi, int s_hi, int s_lo) {
+    for (int g = threadIdx.x; g < (P >> 3); g += blockDim.x) {
+        int base;
+        if (b == 3 && p >= 10) base = (g & 7) | (((g >> 3) & 3) << 8) | (((g >> 5) & 3) << 6) | ((g >> 7) << 10);
+        else base = (g & ((1 << b) - 1)) | ((g >> b) << (b + 3));
+        uint32_t v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = keys[sort_slot(base | (j << b))];
+        for (int m = m_lo; m <= m_hi; ++m) {
+            const int mbit = 1 << m;
+            const bool base_up = (base & mbit) == 0;
+            const int jm = (mbit >> b) & 7;                      // the direction bit, when it lies inside the window
+            for (int s = min(s_hi, m - 1); s >= s_lo; --s) {
+                const int sb = s - b;
+                if (sb == 0) sort_stage<0>(v, base_up, jm);
+                else if (sb == 1) sort_stage<1>(v, base_up, jm);
+                else sort_stage<2>(v, base_up, jm);
             }
-            keys[i] = k;
         }
-        if (nan) has_nan = 1;
-        __syncthreads();
-        for (int size = 2; size <= P; size <<= 1) {
-            for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                for (int t = threadIdx.x; t < (P >> 1); t += blockDim.x) {
-                    const int i = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));     // lower index of the pair
-                    const int j = i + stride;
-                    const bool up = (i & size) == 0;
-                    const uint32_t a = keys[i], b = keys[j];
-                    if ((a > b) == up) { keys[i] = b; keys[j] = a; }
-                }
-                __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) keys[sort_slot(base | (j << b))] = v[j];
+    }
+    __syncthreads();
+}
+
+// Selection without sorting, for the usual case of a few levels over a long row: the row's values are counted
+// into kSelBins equal-width bins between its minimum and maximum (a weakly monotone map, so the bins are ordered
+// groups), a prefix sum over the counts names the bin and the rank inside it of every wanted order statistic,
+// the members of those few bins are collected, and each statistic is picked from its bin by counting.  Rows the
+// bins cannot split (an infinite or empty range, more than kSelCap members in a wanted bin) are sorted instead.
+constexpr int kSelBins = 4096;
+constexpr int kSelSlots = 32;                                    // order statistics per row: 2 per level
+constexpr int kSelCap = kSelBins / kSelSlots;                    // members kept per wanted bin (lists reuse the counters)
+constexpr int kSelMinK = 1024;
+static_assert(kSelBins == 8 * 512, "the prefix sums give every one of the 512 threads eight bins");
+
+__device__ __forceinline__ int sel_bin(float v, float mn, float inv) {
+    return min(__float2int_rz(__fmul_rn(__fsub_rn(v, mn), inv)), kSelBins - 1);
+}
+
+__device__ __forceinline__ float quantile_rank(int k, int n, int K) {
+    const float q = __fdiv_rn((float)(2 * k + 1), (float)(2 * n));
+    return __fmul_rn(q, (float)(K - 1));
+}
+
+// torch.quantile's linear interpolation between the order statistics a (at floor(rank)) and b (at ceil(rank))
+__device__ __forceinline__ float quantile_lerp(float a, float b, float rank) {
+    const float w = __fsub_rn(rank, floorf(rank));
+    const float d = __fsub_rn(b, a);
+    return (w < 0.5f) ? __fmaf_rn(w, d, a) : __fmaf_rn(-d, __fsub_rn(1.0f, w), b);
+}
+
+struct SelShared {
+    int has_nan, give_up;
+    uint32_t kmin, kmax;
+    uint32_t warp_tot[kQuantThreads / 32];
+    int t_bin[kSelSlots], t_local[kSelSlots], cnt[kSelSlots];
+    uint32_t sel[kSelSlots];
+};
+
+// The selection for one row whose elements the CTA's kQuantThreads threads hold in registers (element
+// j * kQuantThreads + thread in v[j]).  True when out[0..n) was written; false when the row has to be sorted.
+// Every thread of the CTA returns the same answer.  hist: kSelBins zeroed counters; slot_of_bin: kSelBins bytes
+// of 0xFF (left so); sh.cnt zeroed, sh.kmin / sh.kmax the extreme keys of the row.
+template <int EPT>
+__device__ __forceinline__ bool select_row(const float (&v)[EPT], int K, int n, float* __restrict__ out, uint32_t* hist,
+                                           uint8_t* slot_of_bin, SelShared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kWarpsQ = kQuantThreads / 32, kPerWarp = kSelBins / kWarpsQ;
+    const float mn = value_of(sh.kmin), range = __fsub_rn(value_of(sh.kmax), mn);
+    const float inv = __fdiv_rn((float)(kSelBins - 1), range);
+    if (!(range > 0.0f && range < CUDART_INF_F && inv < CUDART_INF_F)) return false;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j)
+        if (j * kQuantThreads + (int)threadIdx.x < K) atomicAdd(&hist[sel_bin(v[j], mn, inv)], 1u);
+    __syncthreads();
+    {   // inclusive prefix sums of the counters, restarting at every warp's run of kPerWarp bins; eight bins a thread
+        uint4* h4 = reinterpret_cast<uint4*>(hist) + 2 * threadIdx.x;
+        uint4 a = h4[0], b = h4[1];
+        a.y += a.x; a.z += a.y; a.w += a.z;
+        b.x += a.w; b.y += b.x; b.z += b.y; b.w += b.z;
+        uint32_t incl = b.w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const uint32_t excl = incl - b.w;
+        a.x += excl; a.y += excl; a.z += excl; a.w += excl;
+        b.x += excl; b.y += excl; b.z += excl; b.w += excl;
+        h4[0] = a; h4[1] = b;
+        if (lane == 31) sh.warp_tot[warp] = incl;
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * n) {                                   // the bin of every wanted order statistic, and its rank there
+        const int t = threadIdx.x;
+        const float rank = quantile_rank(t >> 1, n, K);
+        uint32_t r = (uint32_t)((t & 1) ? ceilf(rank) : floorf(rank));
+        int w = 0;
+        while (w < kWarpsQ - 1 && r >= sh.warp_tot[w]) { r -= sh.warp_tot[w]; ++w; }
+        int a = w * kPerWarp, b = a + kPerWarp - 1;              // first bin of the run whose prefix sum exceeds r
+        while (a < b) {
+            const int mid = (a + b) >> 1;
+            if (hist[mid] > r) b = mid; else a = mid + 1;
+        }
+        const uint32_t before = a == w * kPerWarp ? 0u : hist[a - 1];
+        if (hist[a] - before > (uint32_t)kSelCap) sh.give_up = 1;
+        sh.t_bin[t] = a;
+        sh.t_local[t] = (int)(r - before);
+        slot_of_bin[a] = (uint8_t)t;                             // statistics sharing a bin share one list: any writer wins
+    }
+    __syncthreads();
+    const bool ok = !sh.give_up;
+    if (ok) {
+        uint32_t* lists = hist;                                  // the counters are not needed any more
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            if (j * kQuantThreads + (int)threadIdx.x < K) {
+                const int s = slot_of_bin[sel_bin(v[j], mn, inv)];
+                if (s != 0xFF) lists[s * kSelCap + atomicAdd(&sh.cnt[s], 1)] = key_of(v[j]);
             }
+        }
+        __syncthreads();
+        for (int t = warp; t < 2 * n; t += kWarpsQ) {
+            const int s = slot_of_bin[sh.t_bin[t]], c = sh.cnt[s], want = sh.t_local[t];
+            for (int e = lane; e < c; e += 32) {
+                const uint32_t ke = lists[s * kSelCap + e];
+                int less = 0, leq = 0;
+                for (int f = 0; f < c; ++f) {
+                    const uint32_t kf = lists[s * kSelCap + f];
+                    less += kf < ke;
+                    leq += kf <= ke;
+                }
+                if (less <= want && want < leq) sh.sel[t] = ke;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < n) {
+            const int k = threadIdx.x;
+            out[k] = quantile_lerp(value_of(sh.sel[2 * k]), value_of(sh.sel[2 * k + 1]), quantile_rank(k, n, K));
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * n) slot_of_bin[sh.t_bin[threadIdx.x]] = 0xFF;
+    return ok;
+}
+
+// EPT > 0: kQuantThreads threads, EPT * kQuantThreads == P, rows selected from registers where that works.
+// EPT == 0: every row sorted.
+template <typename T, int EPT>
+__global__ void __launch_bounds__(kQuantThreads, EPT >= 16 ? 2 : 3)
+row_quantile_kernel(const void* __restrict__ xin, float* __restrict__ out, int64_t rows, int K, int P, int p, int n) {
+    extern __shared__ uint4 smem_q[];                            // [P] keys | [kSelBins] counters / lists | [kSelBins] bytes
+    uint32_t* keys = reinterpret_cast<uint32_t*>(smem_q);
+    uint32_t* hist = keys + P;
+    uint8_t* slot_of_bin = reinterpret_cast<uint8_t*>(hist + kSelBins);
+    __shared__ SelShared sh;
+    const T* x = reinterpret_cast<const T*>(xin);
+    if (EPT > 0) {
+        for (int i = threadIdx.x; i < kSelBins / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(slot_of_bin)[i] = 0xFFFFFFFFu;
+    }
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * K;
+        if (threadIdx.x == 0) { sh.has_nan = 0; sh.give_up = 0; sh.kmin = 0xFFFFFFFFu; sh.kmax = 0u; }
+        bool nan = false;
+        if constexpr (EPT > 0) {
+            float v[EPT];
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                const int i = j * kQuantThreads + threadIdx.x;
+                v[j] = i < K ? load_elem<T>(xr + i) : CUDART_INF_F;
+            }
+            reinterpret_cast<uint4*>(hist)[2 * threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(hist)[2 * threadIdx.x + 1] = make_uint4(0u, 0u, 0u, 0u);
+            if (threadIdx.x < kSelSlots) sh.cnt[threadIdx.x] = 0;
+            float lo_v = CUDART_INF_F, hi_v = -CUDART_INF_F;
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                if (j * kQuantThreads + (int)threadIdx.x < K) {
+                    nan |= v[j] != v[j];
+                    lo_v = fminf(lo_v, v[j]);
+                    hi_v = fmaxf(hi_v, v[j]);
+                }
+            }
+            __syncthreads();                                     // the flags and extremes are reset
+            const uint32_t lo_k = __reduce_min_sync(0xFFFFFFFFu, key_of(lo_v));
+            const uint32_t hi_k = __reduce_max_sync(0xFFFFFFFFu, key_of(hi_v));
+            if ((threadIdx.x & 31) == 0) { atomicMin(&sh.kmin, lo_k); atomicMax(&sh.kmax, hi_k); }
+            if (nan) sh.has_nan = 1;
+            __syncthreads();
+            bool done = false;
+            if (sh.has_nan) {                                    // torch.quantile: a NaN anywhere in the row
+                for (int k = threadIdx.x; k < n; k += blockDim.x) out[row * n + k] = CUDART_NAN_F;
+                done = true;
+            } else {
+                done = select_row<EPT>(v, K, n, out + row * n, hist, slot_of_bin, sh);
+            }
+            if (done) {
+                __syncthreads();
+                continue;
+            }
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                const int i = j * kQuantThreads + threadIdx.x;
+                keys[sort_slot(i)] = i < K ? key_of(v[j]) : 0xFFFFFFFFu;
+            }
+            __syncthreads();
+        } else {
+            __syncthreads();
+            for (int i = threadIdx.x; i < P; i += blockDim.x) {
+                uint32_t k = 0xFFFFFFFFu;
+                if (i < K) {
+                    const float v = load_elem<T>(xr + i);
+                    nan |= v != v;
+                    k = key_of(v);
+                }
+                keys[sort_slot(i)] = k;
+            }
+            if (nan) sh.has_nan = 1;
+            __syncthreads();
+            if (sh.has_nan) {
+                for (int k = threadIdx.x; k < n; k += blockDim.x) out[row * n + k] = CUDART_NAN_F;
+                __syncthreads();
+                continue;
+            }
+        }
+        // bitonic network, three stride bits per pass over shared memory: merges of 2, 4 and 8 keys in one
+        // pass, then every larger merge from its widest strides down
+        sort_phase(keys, P, p, 0, 1, 3, 2, 0);
+        for (int m = 4; m <= p; ++m) {
+            for (int lo = (m - 1) / 3 * 3; lo >= 0; lo -= 3)
+                sort_phase(keys, P, p, min(lo, p - 3), m, m, min(lo + 2, m - 1), lo);
         }
         for (int k = threadIdx.x; k < n; k += blockDim.x) {
-            const float q = __fdiv_rn((float)(2 * k + 1), (float)(2 * n));
-            const float rank = __fmul_rn(q, (float)(K - 1));
-            const float lo = floorf(rank);
-            const float w = __fsub_rn(rank, lo);
-            const float a = value_of(keys[(int)lo]), b = value_of(keys[(int)ceilf(rank)]);
-            const float d = __fsub_rn(b, a);
-            float v = (w < 0.5f) ? __fmaf_rn(w, d, a) : __fmaf_rn(-d, __fsub_rn(1.0f, w), b);
-            if (has_nan) v = CUDART_NAN_F;
-            out[row * n + k] = v;
+            const float rank = quantile_rank(k, n, K);
+            out[row * n + k] = quantile_lerp(value_of(keys[sort_slot((int)floorf(rank))]),
+                                             value_of(keys[sort_slot((int)ceilf(rank))]), rank);
         }
         __syncthreads();
     }
+}
+
+template <typename T, int EPT>
+int launch_row_quantile(const void* x, float* out, int64_t rows, int K, int P, int p, int n, int threads, cudaStream_t st) {
+    const size_t smem = (size_t)P * 4 + (EPT > 0 ? (size_t)kSelBins * 5 : 0);
+    const int per_sm = EPT >= 16 ? 2 : (EPT > 0 ? 3 : (2048 / threads < 16 ? 2048 / threads : 16));
+    const int64_t cap = (int64_t)vq_sm_count() * per_sm;
+    const int blocks = (int)(rows < cap ? rows : cap);
+    if (smem > 48 * 1024)
+        VQ_CUDA(cudaFuncSetAttribute(row_quantile_kernel<T, EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    row_quantile_kernel<T, EPT><<<blocks, threads, smem, st>>>(x, out, rows, K, P, p, n);
+    VQ_LAUNCH_CHECK("row_quantile_kernel");
+    return 0;
+}
+
+template <typename T>
+int dispatch_row_quantile(const void* x, float* out, int64_t rows, int K, int n, cudaStream_t st) {
+    int P = 8, p = 3;                                            // keys padded to a power of two, eight at least
+    while (P < K) { P <<= 1; ++p; }
+    if (K >= kSelMinK && 2 * n <= kSelSlots) {
+        switch (P / kQuantThreads) {
+            case 2: return launch_row_quantile<T, 2>(x, out, rows, K, P, p, n, kQuantThreads, st);
+            case 4: return launch_row_quantile<T, 4>(x, out, rows, K, P, p, n, kQuantThreads, st);
+            case 8: return launch_row_quantile<T, 8>(x, out, rows, K, P, p, n, kQuantThreads, st);
+            default: return launch_row_quantile<T, 16>(x, out, rows, K, P, p, n, kQuantThreads, st);
+        }
+    }
+    const int threads = P / 8 < 32 ? 32 : (P / 8 > kQuantThreads ? kQuantThreads : P / 8);
+    return launch_row_quantile<T, 0>(x, out, rows, K, P, p, n, threads, st);
 }
 
 }  // namespace
@@ -407,18 +651,8 @@ extern "C" int vq_row_quantile(const void* x, int dtype, int64_t rows, int64_t K
     if (K < 1 || K > 8192) return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: rows of 1 to 8192 elements", name);
     if (rows == 0) return 0;
     VQ_REQUIRE(x && out, "%s: null pointer", name);
-    int P = 1;
-    while (P < K) P <<= 1;
-    if (P < 2) P = 2;
-    const int sms = vq_sm_count();
-    const size_t smem = (size_t)P * 4;
-    const int per_sm = smem > 16 * 1024 ? 4 : 4;
-    const int blocks = (int)(rows < (int64_t)sms * per_sm ? rows : (int64_t)sms * per_sm);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == VQ_F32) row_quantile_kernel<float><<<blocks, kQuantThreads, smem, st>>>(x, out, rows, (int)K, P, n_levels);
-    else row_quantile_kernel<bf16_t><<<blocks, kQuantThreads, smem, st>>>(x, out, rows, (int)K, P, n_levels);
-    VQ_LAUNCH_CHECK("row_quantile_kernel");
-    return 0;
+    if (dtype == VQ_F32) return dispatch_row_quantile<float>(x, out, rows, (int)K, n_levels, (cudaStream_t)stream);
+    return dispatch_row_quantile<bf16_t>(x, out, rows, (int)K, n_levels, (cudaStream_t)stream);
 }
 
 extern "C" size_t vq_row_codebook_workspace(int64_t rows, int n_levels) {
