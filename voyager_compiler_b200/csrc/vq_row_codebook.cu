@@ -465,22 +465,32 @@ __device__ __forceinline__ bool select_row(const float (&v)[EPT], int K, int n, 
         if (lane == 31) sh.warp_tot[warp] = incl;
     }
     __syncthreads();
-    if (threadIdx.x < 2 * n) {                                   // the bin of every wanted order statistic, and its rank there
-        const int t = threadIdx.x;
+    {   // the bin of every wanted order statistic and its rank there: sixteen lanes search for one statistic,
+        // over the warps' totals, then the sixteen 16-bin groups of that warp's run, then the group's bins
+        const int t = threadIdx.x >> 4, l = threadIdx.x & 15;
+        const unsigned half = 0xFFFFu << (lane & 16);
         const float rank = quantile_rank(t >> 1, n, K);
         uint32_t r = (uint32_t)((t & 1) ? ceilf(rank) : floorf(rank));
-        int w = 0;
-        while (w < kWarpsQ - 1 && r >= sh.warp_tot[w]) { r -= sh.warp_tot[w]; ++w; }
-        int a = w * kPerWarp, b = a + kPerWarp - 1;              // first bin of the run whose prefix sum exceeds r
-        while (a < b) {
-            const int mid = (a + b) >> 1;
-            if (hist[mid] > r) b = mid; else a = mid + 1;
+        const uint32_t tot = sh.warp_tot[l];
+        uint32_t cum = tot;
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, cum, o, 16);
+            if (l >= o) cum += up;
         }
-        const uint32_t before = a == w * kPerWarp ? 0u : hist[a - 1];
-        if (hist[a] - before > (uint32_t)kSelCap) sh.give_up = 1;
-        sh.t_bin[t] = a;
-        sh.t_local[t] = (int)(r - before);
-        slot_of_bin[a] = (uint8_t)t;                             // statistics sharing a bin share one list: any writer wins
+        const int w = min(__popc(__ballot_sync(0xFFFFFFFFu, cum <= r) & half), kWarpsQ - 1);
+        r -= __shfl_sync(0xFFFFFFFFu, cum - tot, w, 16);         // ranks before the run of warp w
+        const int run = w * kPerWarp;
+        const int grp = min(__popc(__ballot_sync(0xFFFFFFFFu, hist[run + l * 16 + 15] <= r) & half), 15);
+        const uint32_t mine = hist[run + grp * 16 + l];
+        const int a = run + grp * 16 + min(__popc(__ballot_sync(0xFFFFFFFFu, mine <= r) & half), 15);
+        if (l == 0 && t < 2 * n) {
+            const uint32_t before = a == run ? 0u : hist[a - 1];
+            if (hist[a] - before > (uint32_t)kSelCap) sh.give_up = 1;
+            sh.t_bin[t] = a;
+            sh.t_local[t] = (int)(r - before);
+            slot_of_bin[a] = (uint8_t)t;                         // statistics sharing a bin share one list: any writer wins
+        }
     }
     __syncthreads();
     const bool ok = !sh.give_up;
@@ -494,17 +504,21 @@ __device__ __forceinline__ bool select_row(const float (&v)[EPT], int K, int n, 
             }
         }
         __syncthreads();
-        for (int t = warp; t < 2 * n; t += kWarpsQ) {
-            const int s = slot_of_bin[sh.t_bin[t]], c = sh.cnt[s], want = sh.t_local[t];
-            for (int e = lane; e < c; e += 32) {
-                const uint32_t ke = lists[s * kSelCap + e];
-                int less = 0, leq = 0;
-                for (int f = 0; f < c; ++f) {
-                    const uint32_t kf = lists[s * kSelCap + f];
-                    less += kf < ke;
-                    leq += kf <= ke;
+        {   // sixteen lanes per statistic: a lane takes members of the bin and counts the keys below and up to its own
+            const int t = threadIdx.x >> 4;
+            if (t < 2 * n) {
+                const int s = slot_of_bin[sh.t_bin[t]], c = sh.cnt[s], want = sh.t_local[t];
+                const uint32_t* list = lists + s * kSelCap;
+                for (int e = threadIdx.x & 15; e < c; e += 16) {
+                    const uint32_t ke = list[e];
+                    int less = 0, leq = 0;
+                    for (int f = 0; f < c; ++f) {
+                        const uint32_t kf = list[f];
+                        less += kf < ke;
+                        leq += kf <= ke;
+                    }
+                    if (less <= want && want < leq) sh.sel[t] = ke;
                 }
-                if (less <= want && want < leq) sh.sel[t] = ke;
             }
         }
         __syncthreads();
