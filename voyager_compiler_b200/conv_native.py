@@ -1,0 +1,94 @@
+"""``conv2d_mx`` on this library's tensor-core GEMM (src/voyager_compiler/ops/quantized.py:239-283).
+
+The convolution is the TN contraction ``patches[M, K] @ weight[O, K]^T``: ``M = N * Ho * Wo`` output
+positions, ``K = kh * kw * C`` ordered (kh, kw, c).  ``vq_conv_patches`` builds the patch matrix from the
+decoded activation (NCHW or NHWC, by strides); a 1x1, stride-1, unpadded NHWC convolution needs no patch
+matrix at all.  The decoded weight is kept as ``[O, K]`` (zero-padded to a multiple of 8 columns) for as
+long as the weight tensor lives, since a weight is static.  bf16, ``groups == 1``; everything else stays on
+the vendor convolution (``supported`` says which).
+"""
+from __future__ import annotations
+
+import os
+import weakref
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .gemm_native import _status_tensor
+
+_weight_cache: dict = {}
+
+
+def supported(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], groups: int) -> bool:
+    if os.environ.get("VOYAGER_B200_CONV", "native") == "vendor":
+        return False
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or groups != 1 or x.ndim != 4 or w.ndim != 4:
+        return False
+    return bias is None or (bias.dtype == torch.bfloat16 and bias.ndim == 1)
+
+
+def _weight_matrix(weight, weight_scale, weight_code, block_size, layout) -> torch.Tensor:
+    """Decoded weight as ``[O, ceil8(kh * kw * I)]`` with columns ordered (kh, kw, i), cached per weight."""
+    from . import ops
+    parts = [t for t in (weight, weight_scale, weight_code) if t is not None]
+    key = (tuple((t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in parts), block_size, layout)
+    hit = _weight_cache.get(key)
+    if hit is not None and all(r() is t for r, t in zip(hit[0], parts)):
+        return hit[1]
+    wd = ops._decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
+    wm = wd.permute(0, 2, 3, 1) if layout == "nchw" else wd.permute(3, 0, 1, 2)       # OIHW / HWIO -> O, kh, kw, I
+    O = wm.shape[0]
+    wm = wm.reshape(O, -1)
+    K = wm.shape[1]
+    Kp = (K + 7) // 8 * 8
+    if Kp != K:
+        wm = torch.nn.functional.pad(wm, (0, Kp - K))
+    wm = wm.contiguous()
+    if len(_weight_cache) >= 64:
+        _weight_cache.pop(next(iter(_weight_cache)))
+    _weight_cache[key] = ([weakref.ref(t) for t in parts], wm)
+    return wm
+
+
+def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout) -> torch.Tensor:
+    """``x``: the decoded activation (bf16, NCHW or NHWC as ``layout`` says, any strides).  Returns the result in
+    the layout's logical shape; for ``"nchw"`` its memory is channels-last (the GEMM writes [N*Ho*Wo, O])."""
+    wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)
+    if layout == "nchw":
+        N, C, H, W = x.shape
+        sn, sc, sh, sw = x.stride()
+        kh, kw = weight.shape[2], weight.shape[3]
+    else:
+        N, H, W, C = x.shape
+        sn, sh, sw, sc = x.stride()
+        kh, kw = weight.shape[0], weight.shape[1]
+    O, Kp = wm.shape
+    K = kh * kw * C
+    if (K + 7) // 8 * 8 != Kp:
+        raise ValueError("conv2d_mx: the channel counts of input and weight differ")
+    Ho = (H + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    Wo = (W + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    if Ho <= 0 or Wo <= 0:
+        raise RuntimeError("conv2d_mx: the kernel window is larger than the padded input")
+    M = N * Ho * Wo
+    dev = x.device
+    out = torch.empty((M, O), dtype=torch.bfloat16, device=dev)
+    if M and O:
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            pointwise = (kh == 1 and kw == 1 and tuple(stride) == (1, 1) and tuple(padding) == (0, 0) and K == Kp
+                         and sc == 1 and sw == C and sh == W * C and sn == H * W * C and x.data_ptr() % 16 == 0)
+            if pointwise:
+                a = x
+            else:
+                a = torch.empty((M, Kp), dtype=torch.bfloat16, device=dev)
+                _lib.check(_lib.lib.vq_conv_patches(
+                    x.data_ptr(), _lib.VQ_BF16, N, H, W, C, sn, sh, sw, sc, kh, kw, stride[0], stride[1], padding[0], padding[1],
+                    dilation[0], dilation[1], a.data_ptr(), Kp, stream), "conv2d_mx")
+            bias_c = bias.contiguous() if bias is not None else None
+            _lib.check(_lib.lib.vq_gemm_bf16_tn(a.data_ptr(), wm.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                                out.data_ptr(), M, O, Kp, _status_tensor(dev).data_ptr(), stream), "conv2d_mx")
+    y = out.view(N, Ho, Wo, O)
+    return y.permute(0, 3, 1, 2) if layout == "nchw" else y

@@ -503,13 +503,18 @@ def _pair(v):
 def conv2d_mx(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, *, input_scale=None,
               weight_scale=None, block_size=None, input_code=None, weight_code=None, layout="nchw"):
     """ops/quantized.py:239-283: operands are decoded and scaled by this package's kernels (blocks
-    along the channel axis go through the strided scale layout), the convolution itself is the
-    vendor kernel, as upstream.  ``"nhwc"``: NHWC activations, HWIO weight, NHWC result."""
+    along the channel axis go through the strided scale layout).  bf16 convolutions with one group run as
+    patch matrix + this library's tensor-core GEMM (``conv_native``; an ``"nchw"`` result then comes back
+    with channels-last strides); other dtypes and grouped convolutions use the vendor kernel, as upstream.
+    ``"nhwc"``: NHWC activations, HWIO weight, NHWC result."""
     assert layout in ("nchw", "nhwc"), layout
     _require_cuda(input, "conv2d_mx")
+    from . import conv_native
     x = _decode_operand("conv2d_mx", input, input_code, input_scale, block_size)
-    w = _decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    if conv_native.supported(x, weight, bias, groups) and (padding[0] >= 0 and padding[1] >= 0):
+        return conv_native.conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout)
+    w = _decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
     if layout == "nhwc":
         x = x.permute(0, 3, 1, 2)
         if groups == 1:
