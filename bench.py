@@ -364,6 +364,35 @@ def run_linear(args):
     med, best = timed(lambda: Q.linear_mx(oc, wq, None, input_scale=os_, weight_scale=ws, block_size=32, A_data=od,
                                           A_indices=oi, A_indptr=op_), args.steps)
     res["linear_mx_with_outliers"] = {"ms": med, "tflops": flops / med / 1e9, "nnz": nnz}
+    # conv2d_mx: ResNet-50-shaped bf16 convolutions, batch 32, MXINT8 codes with block 32 along the channels
+    # (plain bf16 for the 3-channel stem); the library's patch matrix + GEMM against the vendor convolution
+    # on the same decoded operands
+    conv_shapes = [("stem_7x7s2_3to64_224", 3, 224, 64, 7, 2, 3), ("l1_3x3_64to64_56", 64, 56, 64, 3, 1, 1),
+                   ("l1_1x1_64to256_56", 64, 56, 256, 1, 1, 0), ("l2_3x3_128to128_28", 128, 28, 128, 3, 1, 1),
+                   ("l3_3x3_256to256_14", 256, 14, 256, 3, 1, 1), ("l4_1x1_1024to2048_s2_14", 1024, 14, 2048, 1, 2, 0),
+                   ("l4_3x3_512to512_7", 512, 7, 512, 3, 1, 1)]
+    for name, C, HW, O, k, s_, p_ in conv_shapes:
+        for layout in ("nhwc", "nchw"):
+            xc = torch.randn(32, C, HW, HW, generator=g, device=dev).bfloat16()
+            wc = (torch.randn(O, C, k, k, generator=g, device=dev) * 0.05).bfloat16()
+            if layout == "nhwc":
+                xc, wc = xc.permute(0, 2, 3, 1).contiguous(), wc.permute(2, 3, 1, 0).contiguous()
+            kw = {}
+            if C % 32 == 0:
+                ax_x, ax_w = ((3,), (2,)) if layout == "nhwc" else ((1,), (1,))
+                xs_c, xc = Q.quantize_mx(xc, qmap, ax_x, 32, 127.0, True)
+                ws_c, wc = Q.quantize_mx(wc, qmap, ax_w, 32, 127.0, True)
+                kw = dict(input_scale=xs_c, weight_scale=ws_c, block_size=32)
+            Ho = (HW + 2 * p_ - k) // s_ + 1
+            cflops = 2.0 * 32 * Ho * Ho * O * C * k * k
+            call = lambda: Q.conv2d_mx(xc, wc, None, (s_, s_), (p_, p_), (1, 1), 1, layout=layout, **kw)
+            os.environ["VOYAGER_B200_CONV"] = "native"
+            med_n, _ = timed(call, args.steps)
+            os.environ["VOYAGER_B200_CONV"] = "vendor"
+            med_v, _ = timed(call, args.steps)
+            os.environ["VOYAGER_B200_CONV"] = "native"
+            res[f"conv2d_mx_{name}_{layout}"] = {"ms": med_n, "tflops": cflops / med_n / 1e9, "vendor_ms": med_v,
+                                                 "vendor_tflops": cflops / med_v / 1e9}
     clocks = sampler.stop()
     peaks, kind = measured_peaks()
     ok = gemm_native.gemm_status(dev) == 0

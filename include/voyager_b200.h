@@ -210,12 +210,16 @@ VQ_API int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bia
  * out[(n, ho, wo), (i, j, c)] = x[n, ho*stride_h - pad_h + i*dil_h, wo*stride_w - pad_w + j*dil_w, c], zero
  * outside the image; out is [N*Ho*Wo, ldk] in x's dtype (VQ_F32 or VQ_BF16), ldk >= kh*kw*C, the columns from
  * kh*kw*C on are zero-filled; Ho = (H + 2 pad_h - dil_h (kh-1) - 1) / stride_h + 1, Wo alike.  x is addressed
- * by the element strides sn, sh, sw, sc (NCHW: sc = H*W, sw = 1; NHWC: sc = 1).  The weight goes against it
- * as [O, ldk] with the same (i, j, c) column order.  Serves `conv2d_mx`,
+ * by the element strides sn, sh, sw, sc (NCHW: sc = H*W, sw = 1; NHWC: sc = 1).  With `scale` (same dtype, may
+ * be NULL) every element is multiplied by scale[n*ssn + h*ssh + w*ssw + (c / block)*ssc] and rounded once in
+ * that dtype: `dequantize` of an MX activation with blocks along the channels
+ * (src/voyager_compiler/ops/quantized.py:182-227, 267-271) fused into the copy.  The weight goes against the
+ * result as [O, ldk] with the same (i, j, c) column order.  Serves `conv2d_mx`,
  * src/voyager_compiler/ops/quantized.py:239-283 (upstream calls aten.conv2d on the decoded operands). */
 VQ_API int vq_conv_patches(const void* x, int dtype, int64_t N, int64_t H, int64_t W, int64_t C, int64_t sn, int64_t sh,
                            int64_t sw, int64_t sc, int kh, int kw, int stride_h, int stride_w, int pad_h, int pad_w,
-                           int dil_h, int dil_w, void* out, int64_t ldk, void* stream);
+                           int dil_h, int dil_w, const void* scale, int64_t block, int64_t ssn, int64_t ssh, int64_t ssw,
+                           int64_t ssc, void* out, int64_t ldk, void* stream);
 
 /* Y[M,N] = (a_codes * expand(a_scale))[M,K] @ (b_codes * expand(b_scale))[N,K]^T (+ bias), all
  * tensors bf16, scales [rows, K/block] with blocks along K; each product code*scale is rounded to

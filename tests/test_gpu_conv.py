@@ -62,14 +62,15 @@ def test_conv2d_mx_matches_oracle(shape, layout):
 
 
 @pytest.mark.parametrize("layout", ["nchw", "nhwc"])
-def test_conv2d_mx_with_block_scales(layout):
+@pytest.mark.parametrize("C,k,s,p", [(64, 3, 1, 1), (48, 1, 1, 0), (96, 1, 2, 0), (40, 3, 2, 1), (20, 3, 1, 1)])
+def test_conv2d_mx_with_block_scales(layout, C, k, s, p):
     """Codes and power-of-two block scales along the channel axis, as the MX flow annotates convolutions
     (quantization/quantize_pt2e.py:111-113): axis 1 of NCHW tensors, the last axis of NHWC activations."""
     from golden_util import golden_table
     g = torch.Generator().manual_seed(5)
-    N, C, H, W, O = 2, 64, 10, 10, 96
+    N, H, W, O = 2, 10, 10, 96
     x = torch.randn(N, C, H, W, generator=g).bfloat16()
-    w = (torch.randn(O, C, 3, 3, generator=g) * 0.05).bfloat16()
+    w = (torch.randn(O, C, k, k, generator=g) * 0.05).bfloat16()
     q = golden_table("int8")
     if layout == "nhwc":
         x, w = x.permute(0, 2, 3, 1).contiguous(), w.permute(2, 3, 1, 0).contiguous()
@@ -78,18 +79,18 @@ def test_conv2d_mx_with_block_scales(layout):
         ax_x, ax_w = (1,), (1,)
     xs, xq = vo.quantize_mx(x, q, ax_x, 32, 127.0, True)
     ws, wq = vo.quantize_mx(w, q, ax_w, 32, 127.0, True)
-    want = vo.conv2d_mx(xq.float(), wq.float(), None, 1, 1, 1, 1, input_scale=xs.float(), weight_scale=ws.float(), block_size=32,
+    want = vo.conv2d_mx(xq.float(), wq.float(), None, s, p, 1, 1, input_scale=xs.float(), weight_scale=ws.float(), block_size=32,
                         layout=layout)
-    got = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq.cuda(), None, (1, 1), (1, 1), (1, 1), 1, input_scale=xs.cuda(), weight_scale=ws.cuda(),
+    got = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq.cuda(), None, (s, s), (p, p), (1, 1), 1, input_scale=xs.cuda(), weight_scale=ws.cuda(),
                                             block_size=32, layout=layout)
     rel = (got.float().cpu().double() - want.double()).norm() / want.double().norm()
     assert rel <= 1e-2, rel
     # the cached weight matrix must follow an in-place change of the weight
     wq2 = wq.cuda()
-    a = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq2, None, (1, 1), (1, 1), (1, 1), 1, input_scale=xs.cuda(), weight_scale=ws.cuda(),
+    a = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq2, None, (s, s), (p, p), (1, 1), 1, input_scale=xs.cuda(), weight_scale=ws.cuda(),
                                           block_size=32, layout=layout)
     wq2.mul_(2)
-    b = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq2, None, (1, 1), (1, 1), (1, 1), 1, input_scale=xs.cuda(), weight_scale=ws.cuda(),
+    b = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq2, None, (s, s), (p, p), (1, 1), 1, input_scale=xs.cuda(), weight_scale=ws.cuda(),
                                           block_size=32, layout=layout)
     assert torch.allclose(b.float(), 2 * a.float(), rtol=2e-2, atol=1e-2)
 
@@ -127,7 +128,7 @@ def test_patch_matrix_bit_exact(shape, channels_last, dtype):
     sn, sc, sh, sw = xd.stride()
     out = torch.full((N * L, ldk), 7.0, dtype=dtype, device="cuda")
     _lib.check(_lib.lib.vq_conv_patches(xd.data_ptr(), _lib.VQ_BF16 if dtype == torch.bfloat16 else _lib.VQ_F32, N, H, W, C,
-                                        sn, sh, sw, sc, kh, kw, st[0], st[1], pd[0], pd[1], dl[0], dl[1], out.data_ptr(), ldk,
+                                        sn, sh, sw, sc, kh, kw, st[0], st[1], pd[0], pd[1], dl[0], dl[1], None, 0, 0, 0, 0, 0, out.data_ptr(), ldk,
                                         torch.cuda.current_stream().cuda_stream), "patches")
     got = out.cpu()
     assert torch.equal(got[:, :K], want)
@@ -137,7 +138,7 @@ def test_patch_matrix_bit_exact(shape, channels_last, dtype):
 def test_patch_matrix_rejects_bad_arguments():
     x = torch.zeros(1, 4, 4, 8, dtype=torch.bfloat16, device="cuda")
     out = torch.zeros(16, 8, dtype=torch.bfloat16, device="cuda")
-    rc = _lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, 1, 4, 4, 8, 128, 32, 8, 1, 7, 7, 1, 1, 0, 0, 1, 1, out.data_ptr(), 392, None)
+    rc = _lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, 1, 4, 4, 8, 128, 32, 8, 1, 7, 7, 1, 1, 0, 0, 1, 1, None, 0, 0, 0, 0, 0, out.data_ptr(), 392, None)
     assert rc < 0                                                  # window larger than the image
-    rc = _lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, 1, 4, 4, 8, 128, 32, 8, 1, 1, 1, 1, 1, 0, 0, 1, 1, out.data_ptr(), 4, None)
+    rc = _lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, 1, 4, 4, 8, 128, 32, 8, 1, 1, 1, 1, 1, 0, 0, 1, 1, None, 0, 0, 0, 0, 0, out.data_ptr(), 4, None)
     assert rc < 0                                                  # ldk below kh * kw * C

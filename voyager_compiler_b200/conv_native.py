@@ -2,8 +2,8 @@
 
 The convolution is the TN contraction ``patches[M, K] @ weight[O, K]^T``: ``M = N * Ho * Wo`` output
 positions, ``K = kh * kw * C`` ordered (kh, kw, c).  ``vq_conv_patches`` builds the patch matrix from the
-decoded activation (NCHW or NHWC, by strides); a 1x1, stride-1, unpadded NHWC convolution needs no patch
-matrix at all.  The decoded weight is kept as ``[O, K]`` (zero-padded to a multiple of 8 columns) for as
+decoded activation; an NCHW activation is first made channels-last by the same entry point (its 1x1 patch
+matrix, a tiled transposition), and a 1x1, stride-1, unpadded convolution needs no patch matrix beyond that.  The decoded weight is kept as ``[O, K]`` (zero-padded to a multiple of 8 columns) for as
 long as the weight tensor lives, since a weight is static.  bf16, ``groups == 1``; everything else stays on
 the vendor convolution (``supported`` says which).
 """
@@ -52,18 +52,40 @@ def _weight_matrix(weight, weight_scale, weight_code, block_size, layout) -> tor
     return wm
 
 
-def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout) -> torch.Tensor:
-    """``x``: the decoded activation (bf16, NCHW or NHWC as ``layout`` says, any strides).  Returns the result in
-    the layout's logical shape; for ``"nchw"`` its memory is channels-last (the GEMM writes [N*Ho*Wo, O])."""
+def fusable_scale(x: torch.Tensor, scale: Optional[torch.Tensor], block_size, layout) -> bool:
+    """True when ``scale`` holds one value per block of channels at every pixel of ``x`` (the layout
+    ``quantize_mx`` along the channel axis produces), which the patch kernels multiply in on the way."""
+    if scale is None or block_size is None or scale.dtype != x.dtype or scale.ndim != 4 or x.ndim != 4:
+        return False
+    ch = 1 if layout == "nchw" else 3
+    want = list(x.shape)
+    want[ch] = -(-x.shape[ch] // block_size)
+    return list(scale.shape) == want
+
+
+def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout,
+              x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x``: the activation (bf16, NCHW or NHWC as ``layout`` says, any strides), decoded, or still to be
+    multiplied by ``x_scale`` (see :func:`fusable_scale`).  Returns the result in the layout's logical shape;
+    for ``"nchw"`` its memory is channels-last (the GEMM writes [N*Ho*Wo, O])."""
     wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)
+    sc_args = (None, 0, 0, 0, 0, 0)
     if layout == "nchw":
         N, C, H, W = x.shape
         sn, sc, sh, sw = x.stride()
         kh, kw = weight.shape[2], weight.shape[3]
+        if x_scale is not None:
+            x_scale = x_scale.contiguous()
+            ssn, ssc, ssh, ssw = x_scale.stride()
+            sc_args = (x_scale.data_ptr(), block_size, ssn, ssh, ssw, ssc)
     else:
         N, H, W, C = x.shape
         sn, sh, sw, sc = x.stride()
         kh, kw = weight.shape[0], weight.shape[1]
+        if x_scale is not None:
+            x_scale = x_scale.contiguous()
+            ssn, ssh, ssw, ssc = x_scale.stride()
+            sc_args = (x_scale.data_ptr(), block_size, ssn, ssh, ssw, ssc)
     O, Kp = wm.shape
     K = kh * kw * C
     if (K + 7) // 8 * 8 != Kp:
@@ -78,15 +100,31 @@ def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_c
     if M and O:
         stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
+            if sc != 1 and C >= 8:
+                # channels strided (NCHW): one tiled pass makes the activation channels-last (its 1x1 patch
+                # matrix), so that the patch rows below are copied in 16-byte pieces
+                # (scaled on the way when the scale was not applied yet); image rows that follow one another in
+                # memory are handed over as one long row
+                xt = torch.empty((N, H, W, C), dtype=torch.bfloat16, device=dev)
+                flat = sh == W * sw and (sc_args[0] is None or sc_args[3] == W * sc_args[4])
+                h_, w_, sh_ = (1, H * W, H * W * sw) if flat else (H, W, sh)
+                ssh_ = (H * W * sc_args[4] if flat else sc_args[3])
+                _lib.check(_lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, N, h_, w_, C, sn, sh_, sw, sc, 1, 1, 1, 1, 0, 0, 1, 1,
+                                                    sc_args[0], sc_args[1], sc_args[2], ssh_, sc_args[4], sc_args[5],
+                                                    xt.data_ptr(), C, stream), "conv2d_mx")
+                x = xt
+                sn, sh, sw, sc = x.stride()
+                sc_args = (None, 0, 0, 0, 0, 0)
             pointwise = (kh == 1 and kw == 1 and tuple(stride) == (1, 1) and tuple(padding) == (0, 0) and K == Kp
-                         and sc == 1 and sw == C and sh == W * C and sn == H * W * C and x.data_ptr() % 16 == 0)
+                         and sc == 1 and sw == C and sh == W * C and sn == H * W * C and x.data_ptr() % 16 == 0
+                         and sc_args[0] is None)
             if pointwise:
                 a = x
             else:
                 a = torch.empty((M, Kp), dtype=torch.bfloat16, device=dev)
                 _lib.check(_lib.lib.vq_conv_patches(
                     x.data_ptr(), _lib.VQ_BF16, N, H, W, C, sn, sh, sw, sc, kh, kw, stride[0], stride[1], padding[0], padding[1],
-                    dilation[0], dilation[1], a.data_ptr(), Kp, stream), "conv2d_mx")
+                    dilation[0], dilation[1], *sc_args, a.data_ptr(), Kp, stream), "conv2d_mx")
             bias_c = bias.contiguous() if bias is not None else None
             _lib.check(_lib.lib.vq_gemm_bf16_tn(a.data_ptr(), wm.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
                                                 out.data_ptr(), M, O, Kp, _status_tensor(dev).data_ptr(), stream), "conv2d_mx")

@@ -28,6 +28,8 @@ struct EwParams {
     FastDiv divK, divB;
     int ndim;
     int64_t size[6], div[6], stride[6];
+    int small;          // STRIDED: n below 2^31, the 32-bit dividers below apply
+    FastDiv fsize[6], fdiv[6];
     TableDev t0, t1;
     int smem_lut;       // 0: none, 1: t0's LUT16 staged in shared memory, 2: t1's
 };
@@ -99,6 +101,15 @@ __device__ __forceinline__ float apply_one(const EwParams& p, const TableRes& r0
 
 __device__ __forceinline__ int64_t strided_index(const EwParams& p, int64_t i) {
     int64_t idx = 0;
+    if (p.small) {
+        uint32_t r = (uint32_t)i;
+        for (int d = p.ndim - 1; d > 0; --d) {
+            const uint32_t q = fd_div(r, p.fsize[d]);
+            idx += (int64_t)fd_div(r - q * p.fsize[d].d, p.fdiv[d]) * p.stride[d];
+            r = q;
+        }
+        return idx + (int64_t)fd_div(r, p.fdiv[0]) * p.stride[0];
+    }
     for (int d = p.ndim - 1; d >= 0; --d) {
         int64_t c = i % p.size[d];
         i /= p.size[d];
@@ -332,13 +343,33 @@ int run_ew(const void* in, int dtype, int64_t n, const void* scale, const void* 
     } else if (p.smode == VQ_SCALE_STRIDED) {
         VQ_REQUIRE(layout->ndim >= 1 && layout->ndim <= 6, "%s: STRIDED layout needs 1..6 dims", name);
         int64_t tot = 1;
-        p.ndim = layout->ndim;
-        for (int d = 0; d < p.ndim; ++d) {
+        p.ndim = 0;
+        for (int d = 0; d < layout->ndim; ++d) {
             VQ_REQUIRE(layout->size[d] > 0 && layout->div[d] > 0, "%s: bad STRIDED dim %d", name, d);
-            p.size[d] = layout->size[d]; p.div[d] = layout->div[d]; p.stride[d] = layout->stride[d];
             tot *= layout->size[d];
+            const int64_t sz = layout->size[d], dv = layout->div[d] > sz ? sz : layout->div[d];
+            const int64_t sd = dv >= sz ? 0 : layout->stride[d];          // one block over the whole dim: a broadcast
+            const int last = p.ndim - 1;
+            // adjacent dims fold into one when the scale index is linear over the pair: both broadcast, or both
+            // undivided with the outer stride equal to the inner extent
+            if (last >= 0 && ((p.stride[last] == 0 && sd == 0) ||
+                              (p.div[last] == 1 && dv == 1 && sd != 0 && p.stride[last] == sd * sz))) {
+                p.size[last] *= sz;
+                if (sd == 0) p.div[last] = p.size[last];
+                else p.stride[last] = sd;
+                continue;
+            }
+            p.size[p.ndim] = sz; p.div[p.ndim] = sd == 0 ? sz : dv; p.stride[p.ndim] = sd;
+            ++p.ndim;
         }
         VQ_REQUIRE(tot == n, "%s: STRIDED sizes do not multiply to n", name);
+        p.small = n < (1ll << 31) ? 1 : 0;
+        if (p.small) {
+            for (int d = 0; d < p.ndim; ++d) {
+                p.fsize[d] = make_fastdiv((uint32_t)p.size[d]);
+                p.fdiv[d] = make_fastdiv((uint32_t)p.div[d]);
+            }
+        }
         aligned = false;  // scalar path
     }
     if (codes && code_bits == 4)

@@ -510,9 +510,14 @@ def conv2d_mx(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=
     assert layout in ("nchw", "nhwc"), layout
     _require_cuda(input, "conv2d_mx")
     from . import conv_native
-    x = _decode_operand("conv2d_mx", input, input_code, input_scale, block_size)
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
-    if conv_native.supported(x, weight, bias, groups) and (padding[0] >= 0 and padding[1] >= 0):
+    native = conv_native.supported(input, weight, bias, groups) and padding[0] >= 0 and padding[1] >= 0
+    if native and input_code is None and conv_native.fusable_scale(input, input_scale, block_size, layout):
+        # the activation's block scales are multiplied in by the patch kernels: no decoded copy of the input
+        return conv_native.conv2d_mx(input, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size,
+                                     layout, x_scale=input_scale)
+    x = _decode_operand("conv2d_mx", input, input_code, input_scale, block_size)
+    if native:
         return conv_native.conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout)
     w = _decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
     if layout == "nhwc":
