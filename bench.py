@@ -393,6 +393,21 @@ def run_linear(args):
             os.environ["VOYAGER_B200_CONV"] = "native"
             res[f"conv2d_mx_{name}_{layout}"] = {"ms": med_n, "tflops": cflops / med_n / 1e9, "vendor_ms": med_v,
                                                  "vendor_tflops": cflops / med_v / 1e9}
+    # GPTQ compensation of one [4096, 4096] weight on the NF4 / block-64 grid (Hessian of 8192 synthetic tokens):
+    # the column walk alone (64 block launches + 63 trailing updates) and the whole entry point
+    import types
+    from voyager_compiler_b200 import gptq as gq, qtables
+    wg = torch.randn(4096, 4096, generator=g, device=dev) * 0.02
+    xg = torch.randn(8192, 4096, generator=g, device=dev) * (0.2 + 2 * torch.rand(4096, generator=g, device=dev))
+    hg = xg.t() @ xg
+    nf4 = qtables.table_handle("nf4", dev).lut16.view(torch.bfloat16)
+    fake = types.SimpleNamespace(qmap=nf4, scale_qmap=None, quant_max=1.0, block_size=64, ch_axis=-1)
+    hinv_g = gq.hessian_inverse_chol(hg.clone(), 8192, 0.01)
+    sal_g = hg.diagonal().clone()
+    med, best = timed(lambda: gq.walk(wg, hinv_g, sal_g, nf4, None, 1.0, 64, False), max(3, args.steps // 4))
+    res["gptq_walk_4096x4096_nf4_b64"] = {"ms": med, "best_ms": best, "columns_per_s": 4096 / med * 1e3}
+    med, best = timed(lambda: gq.compensate_weight(wg, hg, 8192, fake, 0.01), max(3, args.steps // 4))
+    res["gptq_compensate_weight_4096x4096_nf4_b64"] = {"ms": med, "best_ms": best}
     clocks = sampler.stop()
     peaks, kind = measured_peaks()
     ok = gemm_native.gemm_status(dev) == 0

@@ -206,6 +206,21 @@ VQ_API int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bia
                                    int64_t ldy, int64_t col_offset, int64_t M, int64_t N, int64_t K,
                                    int32_t* status, void* stream);
 
+/* One microscaling block of the GPTQ column walk, all rows at once
+ * (src/voyager_compiler/quantization/gptq.py:238-259 with block_scale, :79-137): for every row r of
+ * work[rows, ld] (fp32) the scale s_r = where(t > 0, t, 1) with t = scale_table(amax_r / quant_max) over the
+ * columns start..start+bw, floored at 1e-12 (with `shrink`: the factor of {1, .93, .86, .79, .72} times that, taken
+ * through scale_table, whose salience-weighted squared error is lowest); then column by column
+ * q = table(bf16(w / s_r)) * s_r -> out[r, col], delta = (w - q) / max(hinv[col, col], 1e-12) -> deltas[r, col - start]
+ * (deltas is [rows, bw]), and w[later columns of the block] -= delta * hinv[col, later].  work is only read: the
+ * caller applies work[:, start+bw:] -= deltas @ hinv[start:start+bw, start+bw:].  hinv is the upper Cholesky factor of
+ * the inverse Hessian, [K, ldh] fp32; salience [K] = diag(H), needed with `shrink`; scale_out [rows] may be NULL;
+ * bw <= 64.  Every step is the fp32 operation upstream's tensor expression performs, in its order. */
+VQ_API int vq_gptq_block(const float* work, int64_t ld, int64_t rows, int64_t start, int bw, const float* hinv, int64_t ldh,
+                         const float* salience, int shrink, double quant_max, const vq_table* table,
+                         const vq_table* scale_table, float* out, int64_t ldo, float* deltas, float* scale_out,
+                         void* stream);
+
 /* Patch matrix of a 2-D convolution (groups = 1), so that conv2d_mx becomes the contraction above:
  * out[(n, ho, wo), (i, j, c)] = x[n, ho*stride_h - pad_h + i*dil_h, wo*stride_w - pad_w + j*dil_w, c], zero
  * outside the image; out is [N*Ho*Wo, ldk] in x's dtype (VQ_F32 or VQ_BF16), ldk >= kh*kw*C, the columns from

@@ -7,7 +7,8 @@
 rebinds those names to wrappers that send CUDA tensors through the dispatcher (and therefore to this
 package's kernels) and everything else to the original function.  The forwards of upstream's
 ``FakeQuantizeFunction`` and ``MXFakeQuantizeFunction`` (quantization/fake_quantize.py:101-159) are
-rebound the same way to the fused one-pass kernels of :mod:`voyager_compiler_b200.fake_quantize`.
+rebound the same way to the fused one-pass kernels of :mod:`voyager_compiler_b200.fake_quantize`, and
+``compensate_weight`` of ``quantization/gptq.py`` to :mod:`voyager_compiler_b200.gptq`.
 Off by default; undo with ``unpatch_reference()``.
 """
 from __future__ import annotations
@@ -61,7 +62,31 @@ def patch_reference() -> List[str]:
             _PATCHED.append((mod, n, fn))
             done.append(f"{modname}.{n}")
     _patch_fake_quant_functions(done)
+    _patch_gptq(done)
     return done
+
+
+def _patch_gptq(done: List[str]) -> None:
+    """``compensate_weight`` of upstream's GPTQ driver (quantization/gptq.py:184-270) -> the block-per-launch
+    walk of :mod:`voyager_compiler_b200.gptq` for CUDA weights with blocks of up to 64 input channels."""
+    mod = sys.modules.get("voyager_compiler.quantization.gptq")
+    if mod is None or not hasattr(mod, "compensate_weight"):
+        return
+    original = mod.compensate_weight
+    if hasattr(original, "__wrapped_original__"):
+        return
+    from . import gptq as ours
+
+    @functools.wraps(original)
+    def compensate_weight(weight, hessian, tokens, fake_quant, *args, **kwargs):
+        if isinstance(weight, torch.Tensor) and weight.is_cuda and weight.dim() == 2 and fake_quant.block_size <= 64:
+            return ours.compensate_weight(weight, hessian, tokens, fake_quant, *args, **kwargs)
+        return original(weight, hessian, tokens, fake_quant, *args, **kwargs)
+
+    compensate_weight.__wrapped_original__ = original
+    mod.compensate_weight = compensate_weight
+    _PATCHED.append((mod, "compensate_weight", original))
+    done.append("voyager_compiler.quantization.gptq.compensate_weight")
 
 
 def _patch_fake_quant_functions(done: List[str]) -> None:
