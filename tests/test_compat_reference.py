@@ -72,3 +72,34 @@ def test_patch_reference_rebinds_direct_imports_and_unpatches():
         print("ok")
     """)
     assert "ok" in out
+
+
+def test_patch_reference_rebinds_gptq_compensation():
+    out = _run("""
+        import types
+        import torch
+        import transformers                      # before the torchao stand-in of the import helper
+        from transformers import PreTrainedModel
+        from _reference_import import import_reference
+        ref = import_reference()
+        import importlib
+        g = importlib.import_module("voyager_compiler.quantization.gptq")
+        import voyager_compiler_b200 as vb
+        from voyager_compiler_b200 import compat
+        orig = g.compensate_weight
+        done = compat.patch_reference()
+        assert "voyager_compiler.quantization.gptq.compensate_weight" in done, done
+        assert g.compensate_weight.__wrapped_original__ is orig
+        torch.manual_seed(0)
+        w = torch.randn(8, 64) * 0.1
+        x = torch.randn(200, 64)
+        fake = types.SimpleNamespace(qmap=ref["fake_quantize"].get_quantization_map("int4"), scale_qmap=None, quant_max=7.0,
+                                     block_size=32, ch_axis=-1)
+        a = g.compensate_weight(w, x.t() @ x, 200, fake, 0.01)            # CPU tensors: upstream's own walk
+        b = orig(w, x.t() @ x, 200, fake, 0.01)
+        assert torch.equal(a, b)
+        compat.unpatch_reference()
+        assert g.compensate_weight is orig
+        print("ok")
+    """)
+    assert "ok" in out
