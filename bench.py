@@ -584,6 +584,27 @@ def run_elementwise(args):
         lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=True), wt.numel() * 9 + lv.numel() * 4)
     res["cfg4_row_codebook16_indices_only_11008x4096"] = timed(
         lambda: codebook.row_codebook_quantize(wt, lv, reference_rule=False, want_values=False), wt.numel() * 5 + lv.numel() * 4)
+    # statistics pass of the learned-codebook fit over the same weight: unit scale per block of 64, 4001 bins,
+    # three fp64 moments, every element weighted by the energy of its input channel
+    from voyager_compiler_b200 import lcq
+    hist = lcq.Histogram(-7.0, 7.0)
+    energy = torch.rand(4096, generator=g, device=dev) + 0.1
+    res["lcq_accumulate_fp32_11008x4096_b64_energy"] = timed(lambda: hist.accumulate(wt, 64, 7.0, energy), wt.numel() * 4)
+    res["lcq_accumulate_fp32_11008x4096_b64_flat"] = timed(lambda: hist.accumulate(wt, 64, 7.0, None), wt.numel() * 4)
+    # the same statistics through torch's own operators on this GPU (upstream's formulation), for scale
+    t_edges = torch.linspace(-7.5, 7.5, 4002, device=dev, dtype=torch.float32)
+    t_m = [torch.zeros(4001, dtype=torch.float64, device=dev) for _ in range(3)]
+
+    def torch_stats():
+        flat = wt.reshape(-1, 64)
+        v = (flat / (flat.abs().amax(-1, keepdim=True).clamp_min(1e-12) / 7.0)).reshape(-1)
+        idx = (torch.bucketize(v, t_edges, right=True) - 1).clamp_(0, 4000)
+        vd, wd = v.double(), energy.repeat(v.numel() // 4096).double()
+        t_m[0].index_add_(0, idx, wd)
+        t_m[1].index_add_(0, idx, wd * vd)
+        t_m[2].index_add_(0, idx, wd * vd * vd)
+    res["lcq_torch_operators_fp32_11008x4096_b64_energy_for_scale"] = timed(torch_stats, wt.numel() * 4, iters=3)
+    del t_m, t_edges
     # observer + fake-quantize forward (calibration / QAT): activations [8192, 4096] bf16 and fp32
     from voyager_compiler_b200 import fake_quantize as fqm
     for dt, nm, es in ((torch.bfloat16, "bf16", 2), (torch.float32, "fp32", 4)):

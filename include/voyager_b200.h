@@ -206,6 +206,18 @@ VQ_API int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bia
                                    int64_t ldy, int64_t col_offset, int64_t M, int64_t N, int64_t K,
                                    int32_t* status, void* stream);
 
+/* Statistics pass of the learned-codebook fit (src/voyager_compiler/quantization/lcq.py: unit_scale :136-150,
+ * Histogram.add :75-105, _accumulate :601-626).  x holds n elements (VQ_F32 or VQ_BF16, widened to fp32);
+ * with block > 0 every run of `block` elements is divided by max(amax, 1e-12) / quant_max first, with block == 0
+ * the values are taken as they are.  Value v goes to bin clamp(#{edges <= v} - 1, 0, bins - 1) over the bins + 1
+ * ascending fp32 `edges` (device) and adds w, w * v and w * v * v, in fp64, to weight / total / square (device,
+ * [bins] each, accumulated in place); w = 1 when n_weights == 0, else weights[i % n_weights] for element i (the
+ * energy of its channel, channels last).  Sums are formed in an order the scheduler decides; fp64 keeps that
+ * below what can move a fitted level, as upstream notes for its own GPU path. */
+VQ_API int vq_lcq_accumulate(const void* x, int dtype, int64_t n, int64_t block, double quant_max, const float* weights,
+                             int64_t n_weights, const float* edges, int bins, double* weight, double* total,
+                             double* square, void* stream);
+
 /* One microscaling block of the GPTQ column walk, all rows at once
  * (src/voyager_compiler/quantization/gptq.py:238-259 with block_scale, :79-137): for every row r of
  * work[rows, ld] (fp32) the scale s_r = where(t > 0, t, 1) with t = scale_table(amax_r / quant_max) over the

@@ -103,3 +103,31 @@ def test_patch_reference_rebinds_gptq_compensation():
         print("ok")
     """)
     assert "ok" in out
+
+
+def test_patch_reference_rebinds_lcq_accumulation():
+    out = _run("""
+        import types
+        import torch
+        import transformers                      # before the torchao stand-in of the import helper
+        from transformers import PreTrainedModel
+        from _reference_import import import_reference
+        import_reference()
+        import importlib
+        lcq = importlib.import_module("voyager_compiler.quantization.lcq")
+        import voyager_compiler_b200 as vb
+        from voyager_compiler_b200 import compat
+        orig = lcq._accumulate
+        done = compat.patch_reference()
+        assert "voyager_compiler.quantization.lcq._accumulate" in done, done
+        module = types.SimpleNamespace(ch_axis=-1, block_size=32, quant_max=7.0)
+        x = torch.randn(6, 64)
+        a, b = lcq.Histogram(-7.0, 7.0), lcq.Histogram(-7.0, 7.0)
+        lcq._accumulate(x, module, None, a)                 # CPU tensors: upstream's own pass
+        orig(x, module, None, b)
+        assert torch.equal(a.weight, b.weight) and torch.equal(a.square, b.square)
+        compat.unpatch_reference()
+        assert lcq._accumulate is orig
+        print("ok")
+    """)
+    assert "ok" in out

@@ -1,0 +1,102 @@
+"""LCQ statistics pass (quantization/lcq.py: unit_scale, Histogram.add, _accumulate): the oracle against
+vectors upstream produced (CPU), the fused CUDA pass against the oracle (GPU)."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from golden_util import GOLDEN
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import voyager_oracle as vo  # noqa: E402
+
+_Z = None
+
+
+def _z():
+    global _Z
+    if _Z is None:
+        _Z = np.load(os.path.join(GOLDEN, "golden_lcq.npz"))
+    return _Z
+
+
+CASES = json.loads(bytes(_z()["cases"]).decode())
+
+
+def _inputs(case):
+    n = case["name"]
+    dt = torch.bfloat16 if case["dtype"] == "bfloat16" else torch.float32
+    xs = [torch.from_numpy(_z()[f"{n}/x{i}"].copy()).view(dt).reshape(s) for i, s in enumerate(case["shapes"])]
+    energy = torch.from_numpy(_z()[f"{n}/energy"].copy()).view(torch.float32) if case["energy"] else None
+    return xs, energy
+
+
+def _dense(case, key):
+    n = case["name"]
+    m = torch.zeros(case["bins"], dtype=torch.float64)
+    m[torch.from_numpy(_z()[f"{n}/{key}_idx"].astype(np.int64))] = torch.from_numpy(_z()[f"{n}/{key}_val"].copy())
+    return m
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_oracle_matches_upstream(case):
+    torch.set_num_threads(1)
+    xs, energy = _inputs(case)
+    assert torch.equal(vo.lcq_edges(case["quant_min"], case["quant_max"], case["bins"]).view(torch.int32),
+                       torch.from_numpy(_z()[f"{case['name']}/edges"].copy()))
+    m = None
+    for x in xs:
+        m = vo.lcq_accumulate(m, x, case["block"], case["quant_max"], case["quant_min"], energy, case["bins"])
+    for got, key in zip(m, ("weight", "total", "square")):
+        assert torch.equal(got, _dense(case, key)), key
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_cuda_pass_matches_upstream(case):
+    """Bins are exact (the same fp32 quotient against the same boundaries): with unit weights the weight
+    moment is a count and must be equal; the fp64 sums depend on the order of addition only in their last bits."""
+    from voyager_compiler_b200 import lcq
+    xs, energy = _inputs(case)
+    h = lcq.Histogram(case["quant_min"], case["quant_max"], case["bins"])
+    for x in xs:
+        h.accumulate(x.cuda(), case["block"], case["quant_max"], energy.cuda() if energy is not None else None)
+    want = [_dense(case, k) for k in ("weight", "total", "square")]
+    got = [h.weight.cpu(), h.total.cpu(), h.square.cpu()]
+    assert torch.equal(got[0] != 0, want[0] != 0)                  # the same bins are hit
+    if not case["energy"]:
+        assert torch.equal(got[0], want[0])
+    for g, w in zip(got, want):
+        assert torch.allclose(g, w, rtol=1e-12, atol=1e-9 * float(w.abs().max()))
+    cw, ct, cs = h.cumulative()
+    assert cw.shape == (case["bins"] + 1,) and cw[0] == 0 and abs(cw[-1] - float(want[0].sum())) <= 1e-9 * float(want[0].sum())
+
+
+@pytest.mark.gpu
+def test_add_of_normalised_values_and_large_input():
+    from voyager_compiler_b200 import lcq
+    g = torch.Generator().manual_seed(3)
+    v = (torch.randn(1 << 20, generator=g) * 3).clamp_(-9, 9)
+    v[:7] = torch.tensor([-7.5, 7.5, -7.4999995, 7.4999995, 0.0, float("inf"), -float("inf")])
+    w = torch.rand(1 << 20, generator=g)
+    want = vo.lcq_histogram_add(None, v, w, -7.0, 7.0)
+    h = lcq.Histogram(-7.0, 7.0)
+    h.add(v.cuda(), w.cuda())
+    assert torch.equal(h.weight.cpu() != 0, want[0] != 0)
+    for gq, wq in zip((h.weight, h.total, h.square), want):
+        fin = torch.isfinite(wq)
+        assert torch.equal(torch.isfinite(gq.cpu()), fin)
+        assert torch.allclose(gq.cpu()[fin], wq[fin], rtol=1e-11, atol=1e-9)
+    ones = lcq.Histogram(-7.0, 7.0)
+    ones.add(v.cuda(), torch.ones((), device="cuda"))
+    cnt = vo.lcq_histogram_add(None, v, torch.ones(()), -7.0, 7.0)[0]
+    assert torch.equal(ones.weight.cpu(), cnt)                     # counts are exact in any order
+
+
+def test_cpu_tensors_rejected():
+    from voyager_compiler_b200 import lcq
+    with pytest.raises(RuntimeError):
+        lcq.Histogram(-7.0, 7.0).add(torch.zeros(8), torch.ones(8))

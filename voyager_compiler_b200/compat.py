@@ -8,7 +8,8 @@ rebinds those names to wrappers that send CUDA tensors through the dispatcher (a
 package's kernels) and everything else to the original function.  The forwards of upstream's
 ``FakeQuantizeFunction`` and ``MXFakeQuantizeFunction`` (quantization/fake_quantize.py:101-159) are
 rebound the same way to the fused one-pass kernels of :mod:`voyager_compiler_b200.fake_quantize`, and
-``compensate_weight`` of ``quantization/gptq.py`` to :mod:`voyager_compiler_b200.gptq`.
+``compensate_weight`` of ``quantization/gptq.py`` to :mod:`voyager_compiler_b200.gptq`, ``_accumulate`` of
+``quantization/lcq.py`` to :mod:`voyager_compiler_b200.lcq`.
 Off by default; undo with ``unpatch_reference()``.
 """
 from __future__ import annotations
@@ -63,7 +64,39 @@ def patch_reference() -> List[str]:
             done.append(f"{modname}.{n}")
     _patch_fake_quant_functions(done)
     _patch_gptq(done)
+    _patch_lcq(done)
     return done
+
+
+def _patch_lcq(done: List[str]) -> None:
+    """``_accumulate`` of upstream's codebook fit (quantization/lcq.py:601-626: unit scale, weights, three
+    ``index_add_``) -> one launch of :func:`voyager_compiler_b200.lcq.accumulate_moments` for CUDA tensors whose
+    blocks run along the last axis."""
+    mod = sys.modules.get("voyager_compiler.quantization.lcq")
+    if mod is None or not hasattr(mod, "_accumulate"):
+        return
+    original = mod._accumulate
+    if hasattr(original, "__wrapped_original__"):
+        return
+    from . import lcq as ours
+
+    @functools.wraps(original)
+    def _accumulate(tensor, module, energy, histogram):
+        axis = module.ch_axis[0] if isinstance(module.ch_axis, (tuple, list)) else module.ch_axis
+        fused = (isinstance(tensor, torch.Tensor) and tensor.is_cuda and axis in (-1, tensor.dim() - 1)
+                 and tensor.shape[-1] % module.block_size == 0 and tensor.numel() >= module.block_size)
+        if not fused:
+            return original(tensor, module, energy, histogram)
+        if histogram.weight is None:
+            histogram.weight, histogram.total, histogram.square = (
+                torch.zeros(histogram.bins, dtype=torch.float64, device=tensor.device) for _ in range(3))
+        ours.accumulate_moments(histogram.weight, histogram.total, histogram.square, histogram.quant_min, histogram.quant_max,
+                                tensor.detach(), module.block_size, module.quant_max, energy)
+
+    _accumulate.__wrapped_original__ = original
+    mod._accumulate = _accumulate
+    _PATCHED.append((mod, "_accumulate", original))
+    done.append("voyager_compiler.quantization.lcq._accumulate")
 
 
 def _patch_gptq(done: List[str]) -> None:

@@ -1,0 +1,129 @@
+// Statistics pass of the learned-codebook fit (upstream: src/voyager_compiler/quantization/lcq.py, unit_scale
+// :136-150, Histogram.add :75-105, _accumulate :601-626): every element is divided by its block's scale
+// (max(amax, 1e-12) / quant_max), binned between fp32 boundaries and adds its weight, weight * v and weight * v^2
+// to three fp64 arrays.  Upstream does this with a dozen full-size tensor passes (abs, amax, divide, bucketize,
+// three widenings, three index_add_); here one kernel reads the tensor once from HBM (the second sweep of a
+// block comes from L1) and keeps the three arrays of a CTA in shared memory until it is done.
+#include "vq_common.cuh"
+
+namespace {
+
+constexpr int kLcqThreads = 256;
+constexpr float kLcqEps = 1e-12f;                                // lcq.py:34, as fp32
+
+struct LcqParams {
+    const void* x;
+    int64_t n;
+    int64_t block;               // 0: the values are already normalised
+    float qmax;
+    const float* weights;
+    int64_t n_weights;           // 0: every weight is 1; otherwise element i takes weights[i % n_weights]
+    const float* edges;          // bins + 1 ascending boundaries
+    int bins;
+    double* weight;
+    double* total;
+    double* square;
+};
+
+// Number of boundaries <= v (torch.bucketize(..., right=True)), as a bin index clamped to [0, bins - 1]: a guess
+// from the (nearly uniform) spacing, then a walk to the exact place against the boundaries themselves.
+__device__ __forceinline__ int bin_of(const float* edges, int n_edges, float v, float inv_step) {
+    const int last = n_edges - 2;
+    int b = min(max(__float2int_rd((v - edges[0]) * inv_step), 0), last);        // NaN -> 0
+    while (b > 0 && edges[b] > v) --b;
+    while (b < last && edges[b + 1] <= v) ++b;
+    return b;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLcqThreads) lcq_accumulate_kernel(const __grid_constant__ LcqParams p) {
+    extern __shared__ double sm_moments[];                       // [3][bins] doubles, then bins + 1 floats
+    double* sw = sm_moments;
+    double* st = sw + p.bins;
+    double* ss = st + p.bins;
+    float* edges = reinterpret_cast<float*>(ss + p.bins);
+    for (int i = threadIdx.x; i < 3 * p.bins; i += blockDim.x) sm_moments[i] = 0.0;
+    for (int i = threadIdx.x; i <= p.bins; i += blockDim.x) edges[i] = p.edges[i];
+    __syncthreads();
+    const T* x = reinterpret_cast<const T*>(p.x);
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
+    const float inv_step = (float)p.bins / (edges[p.bins] - edges[0]);
+    auto add = [&](float v, float w) {
+        const int b = bin_of(edges, p.bins + 1, v, inv_step);
+        const double dv = (double)v, dw = (double)w;
+        atomicAdd(&sw[b], dw);
+        atomicAdd(&st[b], dw * dv);
+        atomicAdd(&ss[b], dw * dv * dv);
+    };
+    const bool small = p.n < (1ll << 31);
+    if (p.block == 0) {
+        for (int64_t i = tid; i < p.n; i += nthreads) {
+            float w = 1.0f;
+            if (p.n_weights == 1) w = p.weights[0];
+            else if (p.n_weights) w = p.weights[small ? (int64_t)((uint32_t)i % (uint32_t)p.n_weights) : i % p.n_weights];
+            add(load_one<T>(x + i), w);
+        }
+    } else {
+        const int64_t nblk = p.n / p.block;
+        for (int64_t b = tid; b < nblk; b += nthreads) {
+            const T* xb = x + b * p.block;
+            float amax = 0.0f;
+            for (int64_t j = 0; j < p.block; ++j) amax = fmaxf(amax, fabsf(load_one<T>(xb + j)));
+            const float scale = __fdiv_rn(fmaxf(amax, kLcqEps), p.qmax);
+            int64_t c = p.n_weights > 1 ? (b * p.block) % p.n_weights : 0;       // channel of the block's first element
+            for (int64_t j = 0; j < p.block; ++j) {
+                float w = 1.0f;
+                if (p.n_weights) w = p.weights[c];
+                if (p.n_weights > 1 && ++c == p.n_weights) c = 0;
+                add(__fdiv_rn(load_one<T>(xb + j), scale), w);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.bins; i += blockDim.x) {
+        if (sw[i] != 0.0 || st[i] != 0.0 || ss[i] != 0.0) {
+            atomicAdd(p.weight + i, sw[i]);
+            atomicAdd(p.total + i, st[i]);
+            atomicAdd(p.square + i, ss[i]);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int vq_lcq_accumulate(const void* x, int dtype, int64_t n, int64_t block, double quant_max, const float* weights,
+                                 int64_t n_weights, const float* edges, int bins, double* weight, double* total,
+                                 double* square, void* stream) {
+    const char* name = "vq_lcq_accumulate";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(n >= 0 && block >= 0 && bins >= 1 && n_weights >= 0, "%s: bad sizes", name);
+    VQ_REQUIRE(block == 0 || n % block == 0, "%s: the element count must be a whole number of blocks", name);
+    VQ_REQUIRE(block == 0 || quant_max > 0, "%s: quant_max must be positive", name);
+    if (n == 0) return 0;
+    VQ_REQUIRE(x && edges && weight && total && square && (n_weights == 0 || weights), "%s: null pointer", name);
+    const size_t smem = (size_t)bins * 3 * sizeof(double) + ((size_t)bins + 1) * sizeof(float);
+    if ((int)smem > vq_max_smem_optin())
+        return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: %d bins do not fit the shared memory of a CTA", name, bins);
+    LcqParams p{};
+    p.x = x; p.n = n; p.block = block; p.qmax = (float)quant_max;
+    p.weights = weights; p.n_weights = n_weights; p.edges = edges; p.bins = bins;
+    p.weight = weight; p.total = total; p.square = square;
+    const int64_t items = block ? n / block : n;
+    const int sms = vq_sm_count();
+    const int per_sm = smem > 100 * 1024 ? 2 : 4;
+    int64_t want = (items + kLcqThreads - 1) / kLcqThreads;
+    // a CTA pays for clearing and flushing its arrays: at least a few thousand items each
+    const int64_t by_work = (items + 4095) / 4096;
+    if (want > by_work) want = by_work;
+    const int blocks = (int)(want < 1 ? 1 : (want > (int64_t)sms * per_sm ? (int64_t)sms * per_sm : want));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == VQ_F32) {
+        VQ_CUDA(cudaFuncSetAttribute(lcq_accumulate_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        lcq_accumulate_kernel<float><<<blocks, kLcqThreads, smem, st>>>(p);
+    } else {
+        VQ_CUDA(cudaFuncSetAttribute(lcq_accumulate_kernel<bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        lcq_accumulate_kernel<bf16_t><<<blocks, kLcqThreads, smem, st>>>(p);
+    }
+    VQ_LAUNCH_CHECK("lcq_accumulate_kernel");
+    return 0;
+}
