@@ -371,6 +371,7 @@ def run_linear(args):
                    ("l1_1x1_64to256_56", 64, 56, 256, 1, 1, 0), ("l2_3x3_128to128_28", 128, 28, 128, 3, 1, 1),
                    ("l3_3x3_256to256_14", 256, 14, 256, 3, 1, 1), ("l4_1x1_1024to2048_s2_14", 1024, 14, 2048, 1, 2, 0),
                    ("l4_3x3_512to512_7", 512, 7, 512, 3, 1, 1)]
+    from voyager_compiler_b200 import conv_native
     for name, C, HW, O, k, s_, p_ in conv_shapes:
         for layout in ("nhwc", "nchw"):
             xc = torch.randn(32, C, HW, HW, generator=g, device=dev).bfloat16()
@@ -388,10 +389,15 @@ def run_linear(args):
             call = lambda: Q.conv2d_mx(xc, wc, None, (s_, s_), (p_, p_), (1, 1), 1, layout=layout, **kw)
             os.environ["VOYAGER_B200_CONV"] = "native"
             med_n, _ = timed(call, args.steps)
+
+            def call_cold():                     # the [O, K] weight matrix rebuilt on every call, as the vendor arm decodes it
+                conv_native._weight_cache.clear()
+                return call()
+            med_c, _ = timed(call_cold, args.steps)
             os.environ["VOYAGER_B200_CONV"] = "vendor"
             med_v, _ = timed(call, args.steps)
             os.environ["VOYAGER_B200_CONV"] = "native"
-            res[f"conv2d_mx_{name}_{layout}"] = {"ms": med_n, "tflops": cflops / med_n / 1e9, "vendor_ms": med_v,
+            res[f"conv2d_mx_{name}_{layout}"] = {"ms": med_n, "tflops": cflops / med_n / 1e9, "ms_weight_not_cached": med_c, "vendor_ms": med_v,
                                                  "vendor_tflops": cflops / med_v / 1e9}
     # GPTQ compensation of one [4096, 4096] weight on the NF4 / block-64 grid (Hessian of 8192 synthetic tokens):
     # the column walk alone (64 block launches + 63 trailing updates) and the whole entry point

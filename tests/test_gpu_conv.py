@@ -95,6 +95,28 @@ def test_conv2d_mx_with_block_scales(layout, C, k, s, p):
     assert torch.allclose(b.float(), 2 * a.float(), rtol=2e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("I,k,scaled", [(64, 3, True), (64, 3, False), (96, 1, True), (40, 3, False), (32, 7, True)])
+def test_weight_matrix_one_pass_equals_decode_and_permute(layout, I, k, scaled):
+    """The [O, K] weight written by one launch of the patch kernel equals dequantize + permute + pad, bit for bit."""
+    from voyager_compiler_b200 import conv_native, ops
+    g = torch.Generator().manual_seed(9)
+    O = 72
+    w = (torch.randn(O, I, k, k, generator=g) * 0.05).bfloat16()
+    ws = None
+    if scaled:
+        ws = torch.exp2(torch.randint(-9, -3, (O, -(-I // 32), k, k), generator=g).float()).bfloat16()
+    if layout == "nhwc":
+        w = w.permute(2, 3, 1, 0).contiguous()
+        ws = None if ws is None else ws.permute(2, 3, 1, 0).contiguous()
+    w, ws = w.cuda(), None if ws is None else ws.cuda()
+    got = conv_native._weight_matrix_one_pass(w, ws, None, 32 if scaled else None, layout)
+    assert got is not None
+    wd = ops._decode_operand("conv2d_mx", w, None, ws, 32 if scaled else None)
+    want = (wd.permute(0, 2, 3, 1) if layout == "nchw" else wd.permute(3, 0, 1, 2)).reshape(O, -1)
+    assert torch.equal(got[:, :want.shape[1]].view(torch.int16), want.contiguous().view(torch.int16))
+
+
 def test_vendor_switch_and_other_dtypes_agree(monkeypatch):
     x, w, b, st, pd, dl = _case(SHAPES[1], 3)
     a = torch.ops.quantized_ops.conv2d_mx(x.cuda(), w.cuda(), b.cuda(), st, pd, dl, 1)

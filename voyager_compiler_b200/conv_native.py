@@ -29,6 +29,53 @@ def supported(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], gr
     return bias is None or (bias.dtype == torch.bfloat16 and bias.ndim == 1)
 
 
+def _weight_matrix_one_pass(weight, weight_scale, weight_code, block_size, layout) -> Optional[torch.Tensor]:
+    """The [O, K] weight by one launch of the patch kernel (a transposition with the block scales multiplied
+    in), for plain or MX-scaled weights without a codebook; None when that form does not apply."""
+    if weight_code is not None or not weight.is_contiguous() or weight.data_ptr() % 16:
+        return None
+    dev = weight.device
+    if layout == "nchw":
+        O, I, kh, kw = weight.shape
+        K = kh * kw * I
+        if I % 8 or I < 8:                                        # rows of [O * kh * kw, I] must need no padding
+            return None
+        sc_args = (None, 0, 0, 0, 0, 0)
+        if weight_scale is not None:
+            if not fusable_scale(weight, weight_scale, block_size, "nchw"):
+                return None
+            ws = weight_scale.contiguous()
+            nb = ws.shape[1]
+            sc_args = (ws.data_ptr(), block_size, nb * kh * kw, kw, 1, kh * kw)     # n, h, w, channel block
+        wm = torch.empty((O, K), dtype=torch.bfloat16, device=dev)
+        # the weight as O "images" of kh x kw pixels (handed over as one row) with I channels: its 1x1 patch matrix
+        args = (weight.data_ptr(), _lib.VQ_BF16, O, 1, kh * kw, I, I * kh * kw, kh * kw, 1, kh * kw, 1, 1, 1, 1, 0, 0, 1, 1)
+        ldk = I
+        if sc_args[0] is not None:
+            sc_args = (sc_args[0], sc_args[1], sc_args[2], kh * kw, 1, sc_args[5])
+    else:
+        kh, kw, I, O = weight.shape
+        K = kh * kw * I
+        if K < 8:
+            return None
+        sc_args = (None, 0, 0, 0, 0, 0)
+        if weight_scale is not None:
+            want = [kh, kw, -(-I // block_size), O] if block_size else None
+            if weight_scale.dtype != weight.dtype or list(weight_scale.shape) != want or I % block_size:
+                return None
+            ws = weight_scale.contiguous()
+            sc_args = (ws.data_ptr(), block_size, 0, 0, 1, O)
+        Kp = (K + 7) // 8 * 8
+        wm = torch.empty((O, Kp), dtype=torch.bfloat16, device=dev)
+        # the weight as one image row of O pixels with K strided channels: its 1x1 patch matrix is the transpose
+        args = (weight.data_ptr(), _lib.VQ_BF16, 1, 1, O, K, K * O, K * O, 1, O, 1, 1, 1, 1, 0, 0, 1, 1)
+        ldk = Kp
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.vq_conv_patches(*args, *sc_args, wm.data_ptr(), ldk, torch.cuda.current_stream(dev).cuda_stream),
+                   "conv2d_mx")
+    return wm
+
+
 def _weight_matrix(weight, weight_scale, weight_code, block_size, layout) -> torch.Tensor:
     """Decoded weight as ``[O, ceil8(kh * kw * I)]`` with columns ordered (kh, kw, i), cached per weight."""
     from . import ops
@@ -37,15 +84,17 @@ def _weight_matrix(weight, weight_scale, weight_code, block_size, layout) -> tor
     hit = _weight_cache.get(key)
     if hit is not None and all(r() is t for r, t in zip(hit[0], parts)):
         return hit[1]
-    wd = ops._decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
-    wm = wd.permute(0, 2, 3, 1) if layout == "nchw" else wd.permute(3, 0, 1, 2)       # OIHW / HWIO -> O, kh, kw, I
-    O = wm.shape[0]
-    wm = wm.reshape(O, -1)
-    K = wm.shape[1]
-    Kp = (K + 7) // 8 * 8
-    if Kp != K:
-        wm = torch.nn.functional.pad(wm, (0, Kp - K))
-    wm = wm.contiguous()
+    wm = _weight_matrix_one_pass(weight, weight_scale, weight_code, block_size, layout)
+    if wm is None:
+        wd = ops._decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
+        wm = wd.permute(0, 2, 3, 1) if layout == "nchw" else wd.permute(3, 0, 1, 2)       # OIHW / HWIO -> O, kh, kw, I
+        O = wm.shape[0]
+        wm = wm.reshape(O, -1)
+        K = wm.shape[1]
+        Kp = (K + 7) // 8 * 8
+        if Kp != K:
+            wm = torch.nn.functional.pad(wm, (0, Kp - K))
+        wm = wm.contiguous()
     if len(_weight_cache) >= 64:
         _weight_cache.pop(next(iter(_weight_cache)))
     _weight_cache[key] = ([weakref.ref(t) for t in parts], wm)
