@@ -342,6 +342,10 @@ def run_linear(args):
     med, best = timed(lambda: Q.linear_mx(Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True)[1], wq, None, input_scale=xs,
                                           weight_scale=ws, block_size=32), args.steps)
     res["quantize_plus_linear"] = {"ms": med, "tflops": flops / med / 1e9}
+    # the same value with the activation's codes * scale written straight into the GEMM operand (one pass over x)
+    med, best = timed(lambda: gemm_native.linear_mx_dynamic(x, wq, None, qmap=qmap, weight_scale=ws, block_size=32, quant_max=127.0),
+                      args.steps)
+    res["quantize_plus_linear_one_pass_activation"] = {"ms": med, "tflops": flops / med / 1e9, "best_tflops": flops / best / 1e9}
     # packed operands: int8 bytes + bf16 scales, conversion inside the GEMM's operand staging
     from voyager_compiler_b200 import model_quant as mq
     (px,) = mq.quantize_tensors_mx([x], qmap, 32, 127.0, True, code_bits=8)

@@ -140,3 +140,28 @@ def test_packed_operands_equal_the_float_code_path_bitwise(M, N, K):
     torch.cuda.synchronize()
     assert gemm_native.gemm_status() == 0
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("table,qmax,pow2", [("int8", 127.0, True), ("int8", 127.0, False), ("fp8_e4m3", 448.0, True)])
+@pytest.mark.parametrize("shape,N", [((300, 256), 520), ((2, 65, 136), 96), ((1, 64), 8)])
+def test_linear_mx_dynamic_equals_quantize_mx_then_linear_mx(table, qmax, pow2, shape, N):
+    """Activation quantized on the fly inside one pass == the quantize_mx + linear_mx node pair, bit for bit,
+    and both within the linear's tolerance of the CPU oracle."""
+    g = torch.Generator().manual_seed(sum(shape) + N)
+    K = shape[-1]
+    x = torch.randn(*shape, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, generator=g).bfloat16()
+    q = golden_table(table)
+    ws, wq = vo.quantize_mx(w, q, (-1,), 32, qmax, pow2)
+    xs, xq = vo.quantize_mx(x, q, (-1,), 32, qmax, pow2)
+    want = vo.linear_mx(xq, wq, bias, input_scale=xs, weight_scale=ws, block_size=32)
+    qc, wqc, wsc, bc, xc = q.cuda(), wq.cuda(), ws.cuda(), bias.cuda(), x.cuda()
+    s2, q2 = Q.quantize_mx(xc, qc, (-1,), 32, qmax, pow2)
+    two_ops = Q.linear_mx(q2, wqc, bc, input_scale=s2, weight_scale=wsc, block_size=32)
+    got = gemm_native.linear_mx_dynamic(xc, wqc, bc, qmap=qc, weight_scale=wsc, block_size=32, quant_max=qmax,
+                                        force_scale_power_of_two=pow2)
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.shape == two_ops.shape == want.shape
+    assert torch.equal(got.view(torch.int16), two_ops.view(torch.int16))
+    assert _rel(got.float(), want.float()) <= 1e-2

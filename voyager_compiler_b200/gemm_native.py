@@ -86,6 +86,43 @@ def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
     return out.reshape(*lead, N)
 
 
+def linear_mx_dynamic(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, qmap: torch.Tensor,
+                      weight_scale: Optional[torch.Tensor] = None, block_size: int = 32, quant_max: float = 127.0,
+                      force_scale_power_of_two: bool = True, scale_qmap: Optional[torch.Tensor] = None,
+                      weight_code: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``linear_mx`` on an activation that is quantized on the fly: the value of
+
+        s, q = quantize_mx(x, qmap, (-1,), block_size, quant_max, force_scale_power_of_two, scale_qmap)
+        linear_mx(q, weight, bias, input_scale=s, weight_scale=weight_scale, block_size=block_size, weight_code=weight_code)
+
+    (the node pair the converter emits for a dynamically quantized linear, ops/quantized.py:502-529 and :286-348)
+    without the round trip of codes and scales through HBM: one pass writes ``codes * scale`` of the
+    activation straight into the GEMM's left operand (the MX fake-quantize form of the quantize kernel), the
+    weight is decoded as ``linear_mx`` decodes it, then the tcgen05 GEMM runs.  Bit-identical to the two ops.
+    bf16 ``x`` of shape [..., K] and ``weight`` [N, K] with K a multiple of 8."""
+    from . import fake_quantize, ops
+
+    if x.device.type != "cuda":
+        raise RuntimeError("linear_mx_dynamic: CUDA tensors only; there is no CPU path")
+    if not native_supported(x, weight, bias, None, weight_scale, block_size, None, weight_code, True):
+        raise NotImplementedError("linear_mx_dynamic: bf16 activation [..., K] and weight [N, K] with K a multiple of 8")
+    K, N = x.shape[-1], weight.shape[0]
+    lead = x.shape[:-1]
+    M = x.numel() // K if K else 0
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if M == 0 or N == 0:
+        return out.reshape(*lead, N)
+    _, da = fake_quantize.mx_fake_quantize(x.reshape(M, K), qmap, -1, block_size, quant_max, force_scale_power_of_two, scale_qmap)
+    bias_c = bias.contiguous() if bias is not None else None
+    with torch.cuda.device(x.device):
+        db = ops._decode_operand("linear_mx", weight, weight_code, weight_scale, block_size).contiguous()
+        rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                      out.data_ptr(), M, N, K, _status_tensor(x.device).data_ptr(),
+                                      torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check(rc, "linear_mx_dynamic")
+    return out.reshape(*lead, N)
+
+
 def linear_mx_packed(x, w, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``deq(x) @ deq(w).T (+ bias)`` in bf16 for two :class:`~voyager_compiler_b200.model_quant.PackedMX`
     operands with 8-bit integer codes and blocks of 32 along the last axis (``quantize_tensors_mx(...,
