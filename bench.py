@@ -629,7 +629,17 @@ def run_elementwise(args):
         mod = fqm.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=16,
                                            device=dev)
         res[f"fq_module_forward_int8_per_tensor_{nm}_8192x4096"] = timed(lambda: mod(a), na * 3 * es)
-        del a, mod
+        # the observer's optional steps: exponent histogram (one read), outlier split (read + write) and merge (2 reads + write)
+        hist = torch.zeros(254, device=dev)
+        thr = torch.tensor([3.0], device=dev)
+        res[f"fq_exponent_histogram_{nm}_8192x4096"] = timed(lambda: fqm.exponent_histogram(a, hist), na * es)
+        res[f"fq_outlier_split_{nm}_8192x4096"] = timed(lambda: fqm.outlier_split(a, thr), na * 2 * es)
+        inl, _ = fqm.outlier_split(a, thr)
+        res[f"fq_outlier_merge_{nm}_8192x4096"] = timed(lambda: fqm.outlier_merge(a, inl, thr), na * 3 * es)
+        mod2 = fqm.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=16,
+                                            device=dev, record_histogram=True, outlier_threshold=3.0)
+        res[f"fq_module_forward_histogram_outliers_{nm}_8192x4096"] = timed(lambda: mod2(a), na * 9 * es)
+        del a, mod, mod2, inl
     for k, v in res.items():
         v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]
     print(json.dumps({"workload": "element-wise configs (cfg1, cfg2, cfg4 shapes)", "results": res, "peak_hbm_gbs": peaks["hbm_gbs"],

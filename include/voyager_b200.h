@@ -297,6 +297,26 @@ VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t 
 VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
                               double quant_max, int pow2, void* stream);
 
+/* histogram[b] += number of elements of `in` with floor(log2(|x| as fp32)) == b - 126, b = 0..253, as one fp32
+ * addition per bin: the observer's exponent histogram, `histogram += torch.histc(floor(log2(|x|)), 254, min=-126,
+ * max=127)`, src/voyager_compiler/quantization/fake_quantize.py:369-371.  Zeros, subnormals, infinities and NaNs are
+ * not counted.  `exp` holds the fp32 thresholds (bump_at) of the shared-exponent rule; `workspace` is 2032 bytes of
+ * device scratch, 8-byte aligned. */
+VQ_API int vq_exp_histogram(const void* in, int dtype, int64_t n, const vq_exp_tables* exp, float* histogram, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* inliers[i] = |in[i]| >= t ? 0 : in[i], with t = *threshold (device, fp32) rounded to the dtype of `in`;
+ * *n_outliers (device) receives the number of elements set to zero.  The observer's outlier removal before
+ * quantization, `x.masked_fill(x.abs() >= outlier_threshold, 0.0)`,
+ * src/voyager_compiler/quantization/fake_quantize.py:388-394. */
+VQ_API int vq_outlier_split(const void* in, int dtype, int64_t n, const float* threshold, void* inliers,
+                            unsigned long long* n_outliers, void* stream);
+
+/* out[i] = |in[i]| >= t ? in[i] : quantized[i]: the outliers come back after the quantizer ran on the inliers
+ * (`torch.where(skip, orig_x, x)`, src/voyager_compiler/quantization/fake_quantize.py:428-430). */
+VQ_API int vq_outlier_merge(const void* in, const void* quantized, int dtype, int64_t n, const float* threshold, void* out,
+                            void* stream);
+
 /* vq_linear_mx on PACKED operands: a_codes [M,K] and b_codes [N,K] hold one int8 code per byte (as
  * vq_quantize_mx / vq_quantize_mx_multi write them with code_bits 8 for an integer table), a_scale /
  * b_scale are bf16 [rows, K/32].  Codes and scales arrive by TMA; the conversion int8 -> bf16(code *

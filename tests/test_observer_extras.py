@@ -1,0 +1,141 @@
+"""The observer's optional steps (quantization/fake_quantize.py:368-432): exponent histogram and outlier
+filtering.  The oracle against vectors produced by upstream's module (CPU); the CUDA module and kernels
+against the vectors and the oracle (GPU)."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from golden_util import GOLDEN, from_bits, golden_table
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import voyager_oracle as vo  # noqa: E402
+
+with open(os.path.join(GOLDEN, "golden_observer_extras.json")) as _f:
+    CASES = json.load(_f)["cases"]
+_Z = None
+
+
+def _arr(case, t, key):
+    global _Z
+    if _Z is None:
+        _Z = np.load(os.path.join(GOLDEN, "golden_observer_extras.npz"))
+    return from_bits(_Z[f"{case['name']}/{t}/{key}"], case["tags"][key], case["shapes"][key][t])
+
+
+def _same(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return a.shape == b.shape and bool(((a == b) | (torch.isnan(a) & torch.isnan(b))).all()) and \
+        torch.equal(torch.signbit(a)[a == 0], torch.signbit(b)[b == 0])
+
+
+def _table(name):
+    try:
+        return golden_table(name)
+    except KeyError:
+        return vo.value_table(name)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_oracle_steps_like_upstream(case):
+    kw = case["kwargs"]
+    qmap = _table(kw["dtype"])
+    mx = kw["qscheme"] == "microscaling"
+    history, scale, hist, thr_state, max_pct = None, torch.tensor([1.0]), torch.zeros(254), None, 0.0
+    for t in range(case["steps"]):
+        x = _arr(case, t, "x")
+        if kw.get("record_histogram"):
+            hist = hist + vo.exponent_histogram(x)
+            assert torch.equal(hist, _arr(case, t, "histogram"))
+        thr = kw.get("outlier_threshold")
+        if kw.get("outlier_pct") is not None:
+            thr_state = vo.outlier_threshold_ema(thr_state, vo.outlier_threshold_topk(x, kw["outlier_pct"]),
+                                                 kw.get("outlier_ema_decay", 0.9))
+            assert _same(thr_state, _arr(case, t, "outlier_threshold"))
+            thr = thr_state
+        skip, xin = None, x
+        if thr is not None:
+            skip, xin = vo.outlier_split(x, thr)
+            max_pct = max(max_pct, skip.sum().item() / x.numel())
+            assert max_pct == case["max_outlier_pct"][t]
+        if mx:
+            scale, y = vo.mx_fake_quantize(xin, qmap, kw["ch_axis"], kw["block_size"], kw["quant_max"],
+                                           kw.get("force_scale_power_of_two", False), None)
+        else:
+            cur = vo.observe_amax(xin, kw.get("ch_axis") if kw["qscheme"] == "per_channel_symmetric" else None)
+            if history is None:
+                history = torch.zeros((kw["amax_history_len"],) + tuple(cur.shape))
+                scale = torch.ones(cur.shape)
+            history, scale = vo.update_amax_scale(history, scale, cur, kw["quant_max"], False)
+            y = vo.fake_quantize(xin, scale, qmap)
+        if skip is not None:
+            y = vo.outlier_merge(skip, x, y)
+        assert _same(y, _arr(case, t, "y")) and _same(scale, _arr(case, t, "scale"))
+
+
+# ------------------------------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_module_steps_like_upstream(case):
+    from voyager_compiler_b200 import fake_quantize as fq
+    m = fq.FusedAmaxObsFakeQuantize(device="cuda", **dict(case["kwargs"]))
+    for t in range(case["steps"]):
+        x = _arr(case, t, "x").cuda().requires_grad_(True)
+        y = m(x)
+        assert _same(y, _arr(case, t, "y")), (case["name"], t)
+        assert _same(m.scale, _arr(case, t, "scale")), (case["name"], t)
+        if case["kwargs"].get("record_histogram"):
+            assert torch.equal(m.histogram.cpu(), _arr(case, t, "histogram")), (case["name"], t)
+        if case["kwargs"].get("outlier_pct") is not None:
+            assert _same(m.outlier_threshold, _arr(case, t, "outlier_threshold")), (case["name"], t)
+        if case["kwargs"].get("outlier_pct") is not None or case["kwargs"].get("outlier_threshold") is not None:
+            assert m.max_outlier_pct == case["max_outlier_pct"][t], (case["name"], t)
+        y.sum().backward()
+        assert torch.equal(x.grad, torch.ones_like(x))          # straight-through estimator
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [1, 31, 4099, 1 << 20, (1 << 22) + 5])
+def test_exponent_histogram_matches_oracle(dtype, n):
+    from voyager_compiler_b200 import fake_quantize as fq
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g) * torch.exp2(torch.randint(-140, 130, (n,), generator=g).float())
+    k = min(n, 2000)
+    e = torch.randint(-126, 128, (k,), generator=g)
+    edge = (torch.exp2(e.float()).view(torch.int32) - torch.randint(0, 50, (k,), generator=g).int()).view(torch.float32)
+    x[:k] = edge
+    if n > 8:
+        x[-8:] = torch.tensor([0.0, -0.0, float("inf"), -float("inf"), 1e-40, float("nan"), 1.17549421e-38, -3.4e38])
+    x = x.to(dtype)
+    xs = x[~torch.isnan(x)]                                     # NaNs are not counted on the device; torch's histc on them is not pinned
+    hist = torch.full((254,), 3.0, device="cuda")
+    fq.exponent_histogram(x.cuda(), hist)
+    assert torch.equal(hist.cpu(), 3.0 + vo.exponent_histogram(xs))
+    off = x[1:]                                                 # a pointer that is not 16-byte aligned
+    hist2 = torch.zeros(254, device="cuda")
+    fq.exponent_histogram(x.cuda()[1:], hist2)
+    assert torch.equal(hist2.cpu(), vo.exponent_histogram(off[~torch.isnan(off)]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,thr", [(5, 0.7), (4099, 1.003), (1 << 20, 2.5), ((1 << 21) + 3, 0.0)])
+def test_outlier_split_and_merge_match_oracle(dtype, n, thr):
+    from voyager_compiler_b200 import fake_quantize as fq
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g).to(dtype)
+    x[n // 2] = float("nan")
+    x[0] = thr                                                  # |x| == threshold (after rounding to the dtype) is an outlier
+    t_dev = torch.tensor([thr], dtype=torch.float32, device="cuda")
+    skip, want = vo.outlier_split(x, thr)
+    got, count = fq.outlier_split(x.cuda(), t_dev)
+    assert _same(got, want) and int(count.item()) == int(skip.sum().item())
+    q = (x.float() * 0.5).to(dtype)
+    assert _same(fq.outlier_merge(x.cuda(), q.cuda(), t_dev), vo.outlier_merge(skip, x, q))
+    got1, count1 = fq.outlier_split(x.cuda()[1:], t_dev)        # unaligned start
+    skip1, want1 = vo.outlier_split(x[1:], thr)
+    assert _same(got1, want1) and int(count1.item()) == int(skip1.sum().item())

@@ -90,6 +90,9 @@ def _load():
         "vq_filter_outlier": [vp, ci, i64, i64, i64, dbl, i64, C.c_int32, vp, vp, vp, vp, vp, C.c_size_t, vp],
         "vq_spmm_csr": [vp, vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, vp, vp, vp],
         "vq_observer_update": [vp, vp, vp, ci, i64, dbl, ci, vp],
+        "vq_exp_histogram": [vp, ci, i64, E, vp, vp, C.c_size_t, vp],
+        "vq_outlier_split": [vp, ci, i64, vp, vp, vp, vp],
+        "vq_outlier_merge": [vp, vp, ci, i64, vp, vp, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],
         "vq_quantize_mx": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, T, vp, vp, X, vp],
         "vq_row_codebook": [vp, ci, i64, i64, vp, ci, ci, vp, vp, vp, C.c_size_t, vp],

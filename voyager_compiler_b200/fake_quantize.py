@@ -11,8 +11,11 @@ module of upstream, src/voyager_compiler/quantization/fake_quantize.py.
   (``qmap``, ``scale_qmap``, ``amax_history``, ``scale``, ``fake_quant_enabled``,
   ``observer_enabled``) and forward semantics (:216-432); the backward is the straight-through
   estimator.  The amax history is a handful of numbers and is updated with torch operations on the
-  device, in upstream's order.  Outlier filtering, the exponent histogram and the group-wise
-  affine scheme are not provided and raise ``NotImplementedError``.
+  device, in upstream's order.  ``record_histogram`` (:369-371) is one counting kernel
+  (:func:`exponent_histogram`); outlier filtering (:373-394, :428-430) is a split kernel before and a merge
+  kernel after the quantizer (:func:`outlier_split`, :func:`outlier_merge`), the top-k threshold and its
+  moving average being torch operations on the device.  The group-wise affine scheme is not provided and
+  raises ``NotImplementedError``.
 
 CUDA tensors only; there is no CPU path.
 """
@@ -30,7 +33,7 @@ from . import _lib, ops, tables
 from .qtables import table_handle
 
 __all__ = ["QScheme", "amax", "fake_quantize", "mx_fake_quantize", "FakeQuantizeFunction", "MXFakeQuantizeFunction",
-           "FusedAmaxObsFakeQuantize", "quantization_map"]
+           "FusedAmaxObsFakeQuantize", "quantization_map", "exponent_histogram", "outlier_split", "outlier_merge"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
 
@@ -118,6 +121,75 @@ def mx_fake_quantize(x: torch.Tensor, qmap: torch.Tensor, axes: Union[int, Seque
     return sf, out
 
 
+_hist_scratch = {}
+
+
+def exponent_histogram(x: torch.Tensor, histogram: torch.Tensor) -> torch.Tensor:
+    """``histogram += torch.histc(floor(log2(|x|.float())), 254, min=-126, max=127)`` in place
+    (fake_quantize.py:369-371): one counting pass over ``x`` (``vq_exp_histogram``) instead of abs, cast, log2,
+    floor and histc passes.  ``histogram``: fp32 [254] on the device of ``x``.  Counts are exact; a bin that
+    receives more than 2^24 elements in one call is added as the rounded fp32 count."""
+    from .qtables import exp_tables
+    _require_cuda(x, "exponent_histogram")
+    if histogram.dtype != torch.float32 or histogram.numel() != 254 or not histogram.is_contiguous() or histogram.device != x.device:
+        raise ValueError("exponent_histogram: the histogram is a contiguous fp32 tensor of 254 bins on the device of x")
+    xc = x.contiguous()
+    if xc.numel():
+        with torch.cuda.device(x.device):
+            ws = _hist_scratch.get(x.device)
+            if ws is None:
+                ws = _hist_scratch[x.device] = torch.empty(256, dtype=torch.int64, device=x.device)
+            et = exp_tables(torch.float32, 1.0, x.device)         # log2 is taken in fp32 whatever the dtype of x
+            _lib.check(_lib.lib.vq_exp_histogram(xc.data_ptr(), _DT[x.dtype], xc.numel(), et.ptr(), histogram.data_ptr(),
+                                                 ws.data_ptr(), ws.numel() * 8, torch.cuda.current_stream(x.device).cuda_stream),
+                       "exponent_histogram")
+    return histogram
+
+
+def outlier_split(x: torch.Tensor, threshold: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(x.masked_fill(x.abs() >= threshold, 0.0), number of outliers)`` in one pass (fake_quantize.py:388-394).
+    ``threshold``: one fp32 value on the device; it is rounded to the dtype of ``x`` for the comparison, as torch
+    promotes a scalar.  The count is an int64 tensor on the device (no synchronisation)."""
+    _require_cuda(x, "outlier_split")
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    count = torch.empty(1, dtype=torch.int64, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib.vq_outlier_split(xc.data_ptr(), _DT[x.dtype], xc.numel(), threshold.data_ptr(), out.data_ptr(),
+                                             count.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream), "outlier_split")
+    return out, count
+
+
+def outlier_merge(x: torch.Tensor, quantized: torch.Tensor, threshold: torch.Tensor) -> torch.Tensor:
+    """``torch.where(x.abs() >= threshold, x, quantized)`` in one pass (fake_quantize.py:428-430)."""
+    _require_cuda(x, "outlier_merge")
+    xc, qc = x.contiguous(), quantized.contiguous()
+    if qc.dtype != xc.dtype or qc.shape != xc.shape:
+        raise ValueError("outlier_merge: the quantized tensor has the shape and dtype of x")
+    out = torch.empty_like(xc)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib.vq_outlier_merge(xc.data_ptr(), qc.data_ptr(), _DT[x.dtype], xc.numel(), threshold.data_ptr(),
+                                             out.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream), "outlier_merge")
+    return out
+
+
+class _OutlierBypass(torch.autograd.Function):
+    """Quantizer on the inliers, outliers passed through (fake_quantize.py:388-394, 396-430).  Upstream's graph
+    (masked_fill, straight-through quantizer, where) has the identity as its gradient."""
+
+    @staticmethod
+    def forward(ctx, x, module):
+        with torch.no_grad():
+            thr = module._threshold_tensor(x.device)
+            inliers, count = outlier_split(x, thr)
+            module._note_outliers(count, x.numel())
+            return outlier_merge(x, module._quantize(inliers), thr)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output, None
+
+
 class FakeQuantizeFunction(torch.autograd.Function):
     """fake_quantize.py:101-120."""
 
@@ -158,8 +230,7 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
                  record_histogram: bool = False, outlier_threshold: Optional[float] = None,
                  outlier_pct: Optional[float] = None, device: Optional[torch.device] = None, **kwargs) -> None:
         super().__init__()
-        if record_histogram or outlier_threshold is not None or outlier_pct is not None:
-            raise NotImplementedError("FusedAmaxObsFakeQuantize: histogram recording and outlier filtering are not provided")
+        assert outlier_pct is None or outlier_threshold is None, "Only one of outlier_pct and outlier_threshold can be set."
         self.dtype = dtype
         self.qscheme = _scheme(qscheme)
         if self.qscheme == QScheme.GROUP_WISE_AFFINE:
@@ -171,6 +242,8 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         self.block_size = block_size
         self.scale_dtype = scale_dtype
         self.force_scale_power_of_two = force_scale_power_of_two
+        self.record_histogram = record_histogram
+        self.outlier_pct = outlier_pct
         kw = {"device": device, "dtype": torch.float}
         self.register_buffer("fake_quant_enabled", torch.tensor([1], dtype=torch.uint8, device=device))
         self.register_buffer("observer_enabled", torch.tensor([1], dtype=torch.uint8, device=device))
@@ -180,6 +253,16 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         self.register_buffer("amax_history", torch.tensor([], **kw))
         self.register_buffer("scale", torch.tensor([1.0], **kw))
         self.register_buffer("zero_point", torch.tensor([1.0], **kw))
+        if record_histogram:
+            self.register_buffer("histogram", torch.zeros(254, **kw), persistent=False)
+        if outlier_pct is not None:
+            self.outlier_ema_decay = kwargs.get("outlier_ema_decay", 0.9)
+            self.register_buffer("outlier_threshold", torch.tensor([], **kw))
+        else:
+            self.outlier_threshold = outlier_threshold
+        self._thr_dev = None                                       # device copy of a fixed threshold
+        self._max_outlier_frac = 0.0
+        self._pending_counts = []                                  # (device counter, numel) of forwards not folded in yet
         self.observer_enabled[0] = 1 if self.qscheme is not None else 0
         self.is_per_channel = self.qscheme == QScheme.PER_CHANNEL_SYMMETRIC
         # host mirrors of the two switches: reading the device buffers would synchronise every call
@@ -237,7 +320,51 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
                                                    self.scale.data_ptr(), self.amax_history_len, ch, float(self.quant_max),
                                                    1 if self.force_scale_power_of_two else 0, stream), "observer update")
 
+    # -- outlier filtering (fake_quantize.py:373-394)
+    @property
+    def max_outlier_pct(self) -> float:
+        """Largest fraction of elements bypassed in one forward so far.  The counts stay on the device until this
+        is read (upstream synchronises on every forward, fake_quantize.py:392-394)."""
+        for count, numel in self._pending_counts:
+            self._max_outlier_frac = max(self._max_outlier_frac, int(count.item()) / max(numel, 1))
+        self._pending_counts.clear()
+        return self._max_outlier_frac
+
+    def _threshold_tensor(self, device) -> torch.Tensor:
+        if isinstance(self.outlier_threshold, torch.Tensor):
+            return self.outlier_threshold
+        if self._thr_dev is None or self._thr_dev.device != device:
+            self._thr_dev = torch.tensor([float(self.outlier_threshold)], dtype=torch.float32, device=device)
+        return self._thr_dev
+
+    def _note_outliers(self, count: torch.Tensor, numel: int) -> None:
+        self._pending_counts.append((count, numel))
+        if len(self._pending_counts) >= 256:          # bounded: fold (and synchronise) now and then
+            _ = self.max_outlier_pct
+
+    @torch.no_grad()
+    def _update_outlier_threshold(self, x: torch.Tensor) -> None:
+        """The k-th largest magnitude (k = ceil(outlier_pct * numel)) and its moving average: an order statistic
+        and two scalar operations, torch calls on the device in upstream's order."""
+        flat = x.abs().flatten()
+        k = max(1, math.ceil(self.outlier_pct * flat.numel()))
+        threshold = torch.topk(flat, k, largest=True, sorted=False).values.min()
+        if self.outlier_threshold.numel() == 0:
+            self.outlier_threshold.resize_as_(threshold)
+            self.outlier_threshold.copy_(threshold)
+        else:
+            self.outlier_threshold.mul_(self.outlier_ema_decay).add_(threshold * (1.0 - self.outlier_ema_decay))
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.record_histogram:
+            exponent_histogram(x.detach(), self.histogram)
+        if self.outlier_pct is not None and self._obs_on:
+            self._update_outlier_threshold(x.detach())
+        if self.outlier_threshold is None:
+            return self._quantize(x)
+        return _OutlierBypass.apply(x, self)
+
+    def _quantize(self, x: torch.Tensor) -> torch.Tensor:
         if self.qscheme == QScheme.MICROSCALING:
             if not self._fq_on:
                 return x
