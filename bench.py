@@ -143,6 +143,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers: the CPU arm is to use every host thread it can
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if torch.get_num_threads() < cores:
+        torch.set_num_threads(cores)
     torch.manual_seed(2)
     sample_shapes = LAYER                         # one transformer layer: 7 tensors
     ws = [(torch.randn(s) * 0.02).to(torch.bfloat16) for s in sample_shapes]
