@@ -643,6 +643,9 @@ def run_elementwise(args):
         mod2 = fqm.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=16,
                                             device=dev, record_histogram=True, outlier_threshold=3.0)
         res[f"fq_module_forward_histogram_outliers_{nm}_8192x4096"] = timed(lambda: mod2(a), na * 9 * es)
+        # group-wise affine fake-quantize (uint4, blocks of 128 along the last axis): read + write, two numbers per block
+        res[f"fq_group_affine_uint4_block128_{nm}_8192x4096"] = timed(
+            lambda: fqm.group_affine_fake_quantize(a, -1, 128, 0.0, 15.0), na * (2 * es + 2 * es / 128))
         del a, mod, mod2, inl
     for k, v in res.items():
         v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]

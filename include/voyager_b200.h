@@ -297,6 +297,18 @@ VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t 
 VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
                               double quant_max, int pow2, void* stream);
 
+/* Group-wise affine fake-quantize of a tensor viewed as [rows, K] with blocks of `block` elements along K (the last
+ * block of a row may be short; its zero padding takes part in the extrema as upstream pads it):
+ *   sf = (max - min) / (quant_max - quant_min), 1 where that is not positive;  zp = -min / sf + quant_min;
+ *   both optionally mapped through `scale_table` (65 536 bf16 patterns on the device, or NULL);
+ *   out = (clamp(round_half_even(in / sf + zp), quant_min, quant_max) - zp) * sf,
+ * every step rounded to `dtype`.  out_scale / out_zero_point: [rows, ceil(K / block)] in `dtype`.
+ * Replaces `GroupWiseAffineFakeQuantFunction.forward`,
+ * src/voyager_compiler/quantization/fake_quantize.py:160-207. */
+VQ_API int vq_group_affine_fake_quantize(const void* in, int dtype, int64_t rows, int64_t K, int64_t block, double quant_min,
+                                         double quant_max, const uint16_t* scale_table, void* out_scale, void* out_zero_point,
+                                         void* out, void* stream);
+
 /* histogram[b] += number of elements of `in` with floor(log2(|x| as fp32)) == b - 126, b = 0..253, as one fp32
  * addition per bin: the observer's exponent histogram, `histogram += torch.histc(floor(log2(|x|)), 254, min=-126,
  * max=127)`, src/voyager_compiler/quantization/fake_quantize.py:369-371.  Zeros, subnormals, infinities and NaNs are

@@ -51,6 +51,8 @@ def main():
             rec = [("x", x), ("y", y), ("scale", m.scale.detach().clone())]
             if kw.get("record_histogram"):
                 rec.append(("histogram", m.histogram.detach().clone()))
+            if kw.get("qscheme") == Q.GROUP_WISE_AFFINE:
+                rec.append(("zero_point", m.zero_point.detach().clone()))
             if isinstance(m.outlier_threshold, torch.Tensor):
                 rec.append(("outlier_threshold", m.outlier_threshold.detach().clone()))
             for key, val in rec:
@@ -75,6 +77,22 @@ def main():
     run("outlier_fixed_hist_bf16", lambda t: torch.randn(9, 130, generator=g) * 3.0, torch.bfloat16, 2,
         dtype="posit8_1", qscheme=Q.PER_TENSOR_SYMMETRIC, quant_max=4096.0, amax_history_len=3, outlier_threshold=4.3,
         record_histogram=True)
+    def affine_input(shape, t):
+        x = torch.randn(shape, generator=g) * (1.0 + t) + 0.3 * t
+        x.view(-1)[:shape[-1] if len(shape) > 1 else 4] = 0.0          # a block without range
+        if t == 1:
+            x.view(-1)[-1] = float("nan")
+        return x
+
+    run("gwa_uint4_f32", lambda t: affine_input((6, 96), t), torch.float32, 2,
+        dtype="int4", qscheme=Q.GROUP_WISE_AFFINE, quant_min=0.0, quant_max=15.0, ch_axis=-1, block_size=32)
+    run("gwa_int8_ragged_bf16", lambda t: affine_input((5, 72), t), torch.bfloat16, 2,
+        dtype="int8", qscheme=Q.GROUP_WISE_AFFINE, quant_min=-128.0, quant_max=127.0, ch_axis=-1, block_size=32)
+    run("gwa_uint8_axis0_scale_e5m3_f32", lambda t: affine_input((64, 7), t), torch.float32, 2,
+        dtype="int8", qscheme=Q.GROUP_WISE_AFFINE, quant_min=0.0, quant_max=255.0, ch_axis=0, block_size=16,
+        scale_dtype="fp8_e5m3")
+    run("gwa_int4_block8_bf16", lambda t: affine_input((3, 4, 40), t), torch.bfloat16, 2,
+        dtype="int4", qscheme=Q.GROUP_WISE_AFFINE, quant_min=-8.0, quant_max=7.0, ch_axis=2, block_size=8)
     np.savez_compressed(os.path.join(HERE, "golden_observer_extras.npz"), **arrays)
     with open(os.path.join(HERE, "golden_observer_extras.json"), "w") as f:
         json.dump({"torch": torch.__version__, "cases": cases}, f, indent=1)

@@ -61,7 +61,11 @@ def test_oracle_steps_like_upstream(case):
             skip, xin = vo.outlier_split(x, thr)
             max_pct = max(max_pct, skip.sum().item() / x.numel())
             assert max_pct == case["max_outlier_pct"][t]
-        if mx:
+        if kw["qscheme"] == "group_wise_affine":
+            sq = _table(kw["scale_dtype"]) if kw.get("scale_dtype") else None
+            scale, zp, y = vo.group_affine_fake_quantize(xin, kw["ch_axis"], kw["block_size"], kw["quant_min"], kw["quant_max"], sq)
+            assert _same(zp, _arr(case, t, "zero_point"))
+        elif mx:
             scale, y = vo.mx_fake_quantize(xin, qmap, kw["ch_axis"], kw["block_size"], kw["quant_max"],
                                            kw.get("force_scale_power_of_two", False), None)
         else:
@@ -87,6 +91,9 @@ def test_module_steps_like_upstream(case):
         y = m(x)
         assert _same(y, _arr(case, t, "y")), (case["name"], t)
         assert _same(m.scale, _arr(case, t, "scale")), (case["name"], t)
+        if case["kwargs"]["qscheme"] == "group_wise_affine":
+            assert _same(m.zero_point, _arr(case, t, "zero_point")), (case["name"], t)
+            assert all(_same(a, b) for a, b in zip(m.calculate_qparams(), (m.scale, m.zero_point)))
         if case["kwargs"].get("record_histogram"):
             assert torch.equal(m.histogram.cpu(), _arr(case, t, "histogram")), (case["name"], t)
         if case["kwargs"].get("outlier_pct") is not None:
@@ -139,3 +146,20 @@ def test_outlier_split_and_merge_match_oracle(dtype, n, thr):
     got1, count1 = fq.outlier_split(x.cuda()[1:], t_dev)        # unaligned start
     skip1, want1 = vo.outlier_split(x[1:], thr)
     assert _same(got1, want1) and int(count1.item()) == int(skip1.sum().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,axis,block,qmin,qmax", [((512, 4096), -1, 32, 0.0, 15.0), ((300, 1000), 1, 128, -128.0, 127.0),
+                                                       ((64, 96, 5), 1, 32, 0.0, 255.0), ((7, 50), -1, 16, -8.0, 7.0),
+                                                       ((33, 257), -1, 64, 0.0, 3.0), ((4, 8), 0, 32, -128.0, 127.0)])
+def test_group_affine_fake_quantize_matches_oracle(dtype, shape, axis, block, qmin, qmax):
+    from voyager_compiler_b200 import fake_quantize as fq
+    g = torch.Generator().manual_seed(sum(shape) + block)
+    x = (torch.randn(shape, generator=g) * 2 + 0.5).to(dtype)
+    x.view(-1)[5] = float("nan")
+    x.view(-1)[-3:] = 0.0
+    for sq in (None, _table("fp8_e5m3")):
+        sf, zp, y = fq.group_affine_fake_quantize(x.cuda(), axis, block, qmin, qmax, None if sq is None else sq.cuda())
+        sf_ref, zp_ref, y_ref = vo.group_affine_fake_quantize(x, axis, block, qmin, qmax, sq)
+        assert _same(sf, sf_ref) and _same(zp, zp_ref) and _same(y, y_ref)

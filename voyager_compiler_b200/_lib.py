@@ -91,6 +91,7 @@ def _load():
         "vq_spmm_csr": [vp, vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, vp, vp, vp],
         "vq_observer_update": [vp, vp, vp, ci, i64, dbl, ci, vp],
         "vq_exp_histogram": [vp, ci, i64, E, vp, vp, C.c_size_t, vp],
+        "vq_group_affine_fake_quantize": [vp, ci, i64, i64, i64, dbl, dbl, vp, vp, vp, vp, vp],
         "vq_outlier_split": [vp, ci, i64, vp, vp, vp, vp],
         "vq_outlier_merge": [vp, vp, ci, i64, vp, vp, vp],
         "vq_mx_scale": [vp, ci, i64, i64, i64, i64, dbl, ci, E, T, vp, vp],

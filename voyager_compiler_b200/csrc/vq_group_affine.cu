@@ -1,0 +1,167 @@
+// Group-wise affine fake-quantize: GroupWiseAffineFakeQuantFunction.forward,
+// src/voyager_compiler/quantization/fake_quantize.py:160-207, for blocks along the last (contiguous) axis.
+//
+//   min, max over each block (the zero padding of a ragged last block takes part, mx_utils.py:81-101;
+//   a NaN in the block makes both NaN, as torch.amin / torch.amax do)
+//   sf = (max - min) / (quant_max - quant_min);  sf = sf > 0 ? sf : 1
+//   zp = -min / sf + quant_min;  optionally both through the scale table (vmap)
+//   q  = clamp(round_half_even(x / sf + zp), quant_min, quant_max);  out = (q - zp) * sf
+//
+// Every operation is the IEEE operation upstream's expression performs, rounded to the tensor dtype after
+// each step for bf16.  One launch: a group of G lanes takes a block, sweeps it once for the extrema and once
+// (from L1/L2) for the values; HBM sees sizeof(T) read + sizeof(T) written per element plus two numbers per block.
+#include "vq_common.cuh"
+
+namespace {
+
+struct GroupAffineParams {
+    const void* in;
+    void* out;
+    void* scale;
+    void* zero_point;
+    const uint16_t* table;     // optional 65 536-entry bf16 table for scale and zero point
+    int64_t rows, K, n_blocks; // n_blocks = rows * blocks_per_row
+    int block, blocks_per_row;
+    int lanes;                 // lanes per block: a power of two <= 32
+    int vec;                   // 16-byte accesses
+    float qmin, qmax, qrange;  // qrange = float(quant_max - quant_min)
+};
+
+// Rounding to the tensor dtype after every operation; bf16 by the hardware conversion (round to nearest even; a NaN
+// stays a NaN, whose payload nothing downstream reads).
+template <typename T>
+__device__ __forceinline__ float rnd(float v);
+template <>
+__device__ __forceinline__ float rnd<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float rnd<bf16_t>(float v) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(0.0f), "f"(v));
+    return __uint_as_float(d << 16);
+}
+
+template <typename T>
+__device__ __forceinline__ float through_table(const uint16_t* table, float v) {
+    return table ? bf16_bits_to_f32(__ldg(table + f32_to_bf16_bits(v))) : v;
+}
+
+template <typename T>
+__device__ __forceinline__ float fake_quant_one(float x, float sf, float zp, float lo, float hi) {
+    float t = rnd<T>(__fdiv_rn(x, sf));
+    t = rnd<T>(__fadd_rn(t, zp));
+    float r = rintf(t);
+    r = (r < lo) ? lo : r;             // comparisons keep a NaN, as torch.clamp does
+    r = (r > hi) ? hi : r;
+    return rnd<T>(__fmul_rn(rnd<T>(__fsub_rn(r, zp)), sf));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) group_affine_kernel(const GroupAffineParams p) {
+    constexpr int V = Vec<T>::N;
+    const T* x = reinterpret_cast<const T*>(p.in);
+    T* out = reinterpret_cast<T*>(p.out);
+    const int G = p.lanes;
+    const int lane = threadIdx.x & 31, sub = lane & (G - 1);
+    const uint32_t gmask = (G == 32) ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+    const int64_t groups = ((int64_t)gridDim.x * blockDim.x) / G;
+    const int64_t rounds = (p.n_blocks + groups - 1) / groups;
+    const int64_t g0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const float lo = rnd<T>(p.qmin), hi = rnd<T>(p.qmax);      // clamp bounds in the tensor dtype
+    for (int64_t r = 0; r < rounds; ++r) {               // all lanes of a warp stay in the loop together
+        const int64_t b = g0 + r * groups;
+        const bool live = b < p.n_blocks;
+        const int64_t row = live ? b / p.blocks_per_row : 0;
+        const int kb = live ? (int)(b - row * p.blocks_per_row) : 0;
+        const int64_t base = row * p.K + (int64_t)kb * p.block;
+        const int len = live ? (int)min((int64_t)p.block, p.K - (int64_t)kb * p.block) : 0;
+        float mn = __uint_as_float(0x7F800000u), mx = __uint_as_float(0xFF800000u);
+        bool nan = false;
+        if (p.vec) {
+#pragma unroll 4
+            for (int c = sub * V; c < len; c += G * V) {
+                Vec<T> v;
+                v.load(x + base + c);
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    nan |= v.v[j] != v.v[j];
+                    mn = fminf(mn, v.v[j]);
+                    mx = fmaxf(mx, v.v[j]);
+                }
+            }
+        } else {
+            for (int c = sub; c < len; c += G) {
+                const float e = load_one<T>(x + base + c);
+                nan |= e != e;
+                mn = fminf(mn, e);
+                mx = fmaxf(mx, e);
+            }
+        }
+        if (len < p.block) {               // zero padding of a ragged block
+            mn = fminf(mn, 0.0f);
+            mx = fmaxf(mx, 0.0f);
+        }
+        for (int o = G >> 1; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(gmask, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, o));
+            nan |= (__shfl_xor_sync(gmask, nan ? 1 : 0, o) != 0);
+        }
+        if (nan) mn = mx = __uint_as_float(0x7FC00000u);
+        // -0 and +0 compare equal in fminf/fmaxf, and only enter the results through max - min and -min / sf,
+        // where the sign of a zero extremum cannot change a finite non-zero outcome; a zero range gives sf = 1.
+        float sf = rnd<T>(__fdiv_rn(rnd<T>(__fsub_rn(mx, mn)), p.qrange));
+        sf = (sf > 0.0f) ? sf : 1.0f;
+        float zp = rnd<T>(__fadd_rn(rnd<T>(__fdiv_rn(-mn, sf)), p.qmin));
+        sf = through_table<T>(p.table, sf);
+        zp = through_table<T>(p.table, zp);
+        if (live && sub == 0) {
+            store_one<T>(reinterpret_cast<T*>(p.scale) + b, sf);
+            store_one<T>(reinterpret_cast<T*>(p.zero_point) + b, zp);
+        }
+        if (p.vec) {
+#pragma unroll 4
+            for (int c = sub * V; c < len; c += G * V) {
+                Vec<T> v;
+                v.load(x + base + c);
+#pragma unroll
+                for (int j = 0; j < V; ++j) v.v[j] = fake_quant_one<T>(v.v[j], sf, zp, lo, hi);
+                v.store(out + base + c);
+            }
+        } else {
+            for (int c = sub; c < len; c += G) store_one<T>(out + base + c, fake_quant_one<T>(load_one<T>(x + base + c), sf, zp, lo, hi));
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int vq_group_affine_fake_quantize(const void* in, int dtype, int64_t rows, int64_t K, int64_t block, double quant_min,
+                                             double quant_max, const uint16_t* scale_table, void* out_scale, void* out_zero_point,
+                                             void* out, void* stream) {
+    const char* name = "vq_group_affine_fake_quantize";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(rows >= 0 && K >= 0 && block >= 1 && block < (1ll << 30), "%s: bad shape or block size", name);
+    VQ_REQUIRE(quant_max > quant_min, "%s: quant_max must exceed quant_min", name);
+    if (rows == 0 || K == 0) return 0;
+    VQ_REQUIRE(in && out && out_scale && out_zero_point, "%s: null tensor", name);
+    GroupAffineParams p{};
+    p.in = in; p.out = out; p.scale = out_scale; p.zero_point = out_zero_point; p.table = scale_table;
+    p.rows = rows; p.K = K;
+    p.block = (int)block;
+    p.blocks_per_row = (int)((K + block - 1) / block);
+    p.n_blocks = rows * p.blocks_per_row;
+    p.qmin = (float)quant_min; p.qmax = (float)quant_max; p.qrange = (float)(quant_max - quant_min);
+    const int V = dtype == VQ_F32 ? 4 : 8;
+    p.vec = (K % V == 0 && block % V == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0) ? 1 : 0;
+    const int64_t chunks = p.vec ? (block + V - 1) / V : block;
+    int lanes = 1;
+    while (lanes * 2 <= 32 && lanes * 2 * 4 <= chunks) lanes *= 2;      // about four 16-byte pieces per lane: loads in flight
+    p.lanes = lanes;
+    const int threads = 256;
+    const int64_t want = (p.n_blocks * lanes + threads - 1) / threads;
+    const int64_t cap = (int64_t)vq_sm_count() * 8;
+    const int blocks = (int)(want < cap ? want : cap);
+    if (dtype == VQ_F32) group_affine_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    else group_affine_kernel<bf16_t><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    VQ_LAUNCH_CHECK("group_affine_kernel");
+    return 0;
+}

@@ -14,8 +14,9 @@ module of upstream, src/voyager_compiler/quantization/fake_quantize.py.
   device, in upstream's order.  ``record_histogram`` (:369-371) is one counting kernel
   (:func:`exponent_histogram`); outlier filtering (:373-394, :428-430) is a split kernel before and a merge
   kernel after the quantizer (:func:`outlier_split`, :func:`outlier_merge`), the top-k threshold and its
-  moving average being torch operations on the device.  The group-wise affine scheme is not provided and
-  raises ``NotImplementedError``.
+  moving average being torch operations on the device.
+* :func:`group_affine_fake_quantize` -- per-block min / max, scale, zero point, round, clamp and dequantize in one
+  launch (``vq_group_affine_fake_quantize``; ``GroupWiseAffineFakeQuantFunction.forward``, :160-207).
 
 CUDA tensors only; there is no CPU path.
 """
@@ -33,7 +34,8 @@ from . import _lib, ops, tables
 from .qtables import table_handle
 
 __all__ = ["QScheme", "amax", "fake_quantize", "mx_fake_quantize", "FakeQuantizeFunction", "MXFakeQuantizeFunction",
-           "FusedAmaxObsFakeQuantize", "quantization_map", "exponent_histogram", "outlier_split", "outlier_merge"]
+           "FusedAmaxObsFakeQuantize", "quantization_map", "exponent_histogram", "outlier_split", "outlier_merge", "group_affine_fake_quantize",
+           "GroupWiseAffineFakeQuantFunction"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
 
@@ -190,6 +192,55 @@ class _OutlierBypass(torch.autograd.Function):
         return grad_output, None
 
 
+def group_affine_fake_quantize(x: torch.Tensor, axes: Union[int, Sequence[int]], block_size: int, quant_min: float,
+                               quant_max: float, scale_qmap: Optional[torch.Tensor] = None
+                               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(scale, zero_point, (clamp(round(x / scale + zero_point), quant_min, quant_max) - zero_point) * scale)`` with
+    ``scale = (max - min) / (quant_max - quant_min)`` (1 where not positive) and ``zero_point = -min / scale +
+    quant_min`` per block of ``block_size`` elements along one axis (fake_quantize.py:160-207).  An axis other than
+    the last one is moved there for the launch and back."""
+    assert block_size > 0
+    _require_cuda(x, "group_affine_fake_quantize")
+    ax = ops._norm_axes(axes, x.ndim)
+    if len(ax) != 1:
+        raise NotImplementedError("group_affine_fake_quantize: blocks along exactly one axis")
+    a = ax[0]
+    xl = x.movedim(a, -1).contiguous()
+    K = xl.shape[-1]
+    rows = xl.numel() // K if K else 0
+    nb = -(-K // block_size)
+    out = torch.empty_like(xl)
+    sf = torch.empty(xl.shape[:-1] + (nb,), dtype=x.dtype, device=x.device)
+    zp = torch.empty_like(sf)
+    if xl.numel():
+        with torch.cuda.device(x.device):
+            tab = table_handle(scale_qmap, x.device) if scale_qmap is not None else None
+            _lib.check(_lib.lib.vq_group_affine_fake_quantize(
+                xl.data_ptr(), _DT[x.dtype], rows, K, block_size, float(quant_min), float(quant_max),
+                tab.lut16.data_ptr() if tab is not None else None, sf.data_ptr(), zp.data_ptr(), out.data_ptr(),
+                torch.cuda.current_stream(x.device).cuda_stream), "group_affine_fake_quantize")
+    if a != x.ndim - 1:
+        out, sf, zp = out.movedim(-1, a).contiguous(), sf.movedim(-1, a).contiguous(), zp.movedim(-1, a).contiguous()
+    return sf, zp, out
+
+
+class GroupWiseAffineFakeQuantFunction(torch.autograd.Function):
+    """fake_quantize.py:160-214; ``scale`` and ``zero_point`` are resized and overwritten with the block values."""
+
+    @staticmethod
+    def forward(ctx, input, fake_quant_enabled, scale, zero_point, axes, block_size, quant_min, quant_max, scale_qmap=None):
+        if fake_quant_enabled[0] == 0:
+            return input
+        sf, zp, out = group_affine_fake_quantize(input, axes, block_size, quant_min, quant_max, scale_qmap)
+        scale.resize_(sf.shape).copy_(sf)
+        zero_point.resize_(zp.shape).copy_(zp)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return (grad_output,) + (None,) * 8
+
+
 class FakeQuantizeFunction(torch.autograd.Function):
     """fake_quantize.py:101-120."""
 
@@ -222,7 +273,7 @@ class MXFakeQuantizeFunction(torch.autograd.Function):
 
 
 class FusedAmaxObsFakeQuantize(torch.nn.Module):
-    """fake_quantize.py:216-432 for the symmetric per-tensor, per-channel and microscaling schemes."""
+    """fake_quantize.py:216-432: the symmetric per-tensor, per-channel, microscaling and group-wise affine schemes."""
 
     def __init__(self, dtype: str, qscheme=None, quant_min: Optional[float] = None, quant_max: Optional[float] = None,
                  amax_history_len: Optional[int] = None, ch_axis: Optional[int] = None, block_size: Optional[int] = None,
@@ -233,8 +284,6 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         assert outlier_pct is None or outlier_threshold is None, "Only one of outlier_pct and outlier_threshold can be set."
         self.dtype = dtype
         self.qscheme = _scheme(qscheme)
-        if self.qscheme == QScheme.GROUP_WISE_AFFINE:
-            raise NotImplementedError("FusedAmaxObsFakeQuantize: the group-wise affine scheme is not provided")
         self.quant_min = quant_min
         self.quant_max = quant_max
         self.amax_history_len = amax_history_len
@@ -287,6 +336,8 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         self.enable_observer(False)
 
     def calculate_qparams(self):
+        if self.qscheme == QScheme.GROUP_WISE_AFFINE:
+            return self.scale, self.zero_point
         return self.scale
 
     def extra_repr(self) -> str:
@@ -371,6 +422,11 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
             return MXFakeQuantizeFunction.apply(x, self._fq_host, self.scale, self.qmap, self.ch_axis,
                                                 self.block_size, self.quant_max, self.force_scale_power_of_two,
                                                 self.scale_qmap)
+        if self.qscheme == QScheme.GROUP_WISE_AFFINE:
+            if not self._fq_on:
+                return x
+            return GroupWiseAffineFakeQuantFunction.apply(x, self._fq_host, self.scale, self.zero_point, self.ch_axis,
+                                                          self.block_size, self.quant_min, self.quant_max, self.scale_qmap)
         if self._obs_on:
             self._update_amax_scale(x.detach())
         if not self._fq_on:
