@@ -59,6 +59,10 @@ def test_patch_reference_rebinds_direct_imports_and_unpatches():
         assert torch.equal(fq.vmap(x, q), orig(x, q))            # CPU tensors still use the original
         # the autograd functions: CPU tensors keep upstream's forward, module output unchanged
         assert "voyager_compiler.quantization.fake_quantize.FakeQuantizeFunction.forward" in done, done
+        assert "voyager_compiler.quantization.fake_quantize.GroupWiseAffineFakeQuantFunction.forward" in done, done
+        ga = fq.FusedAmaxObsFakeQuantize("int8", qscheme=ref["qspec"].QScheme.GROUP_WISE_AFFINE, quant_min=0.0, quant_max=15.0,
+                                         ch_axis=-1, block_size=8)
+        assert ga(torch.randn(3, 16)).shape == (3, 16) and ga.scale.shape == (3, 2)     # CPU: upstream's own forward
         m = fq.FusedAmaxObsFakeQuantize("int8", qscheme=ref["qspec"].QScheme.PER_TENSOR_SYMMETRIC, quant_max=127.0,
                                         amax_history_len=2)
         xs = [torch.randn(4, 16) for _ in range(3)]

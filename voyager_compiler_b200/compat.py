@@ -6,7 +6,8 @@
 ``torch.ops.quantized_ops`` are not reached from the prepare-time fake-quant path.  ``patch_reference()``
 rebinds those names to wrappers that send CUDA tensors through the dispatcher (and therefore to this
 package's kernels) and everything else to the original function.  The forwards of upstream's
-``FakeQuantizeFunction`` and ``MXFakeQuantizeFunction`` (quantization/fake_quantize.py:101-159) are
+``FakeQuantizeFunction``, ``MXFakeQuantizeFunction`` and ``GroupWiseAffineFakeQuantFunction``
+(quantization/fake_quantize.py:101-214) are
 rebound the same way to the fused one-pass kernels of :mod:`voyager_compiler_b200.fake_quantize`, and
 ``compensate_weight`` of ``quantization/gptq.py`` to :mod:`voyager_compiler_b200.gptq`, ``_accumulate`` of
 ``quantization/lcq.py`` to :mod:`voyager_compiler_b200.lcq`.
@@ -149,6 +150,13 @@ def _patch_fake_quant_functions(done: List[str]) -> None:
         wrap_forward(mod.FakeQuantizeFunction, ours.FakeQuantizeFunction.forward)
     if hasattr(mod, "MXFakeQuantizeFunction"):
         wrap_forward(mod.MXFakeQuantizeFunction, ours.MXFakeQuantizeFunction.forward)
+    if hasattr(mod, "GroupWiseAffineFakeQuantFunction"):
+        def group_affine(ctx, input, fake_quant_enabled, scale, zero_point, axes, *rest, **kw):
+            one_axis = isinstance(axes, int) or len(axes) == 1
+            target = ours.GroupWiseAffineFakeQuantFunction.forward if one_axis else \
+                mod.GroupWiseAffineFakeQuantFunction.forward.__wrapped_original__       # several block axes: upstream's own ops
+            return target(ctx, input, fake_quant_enabled, scale, zero_point, axes, *rest, **kw)
+        wrap_forward(mod.GroupWiseAffineFakeQuantFunction, group_affine)
 
 
 def unpatch_reference() -> None:
