@@ -123,9 +123,6 @@ def mx_fake_quantize(x: torch.Tensor, qmap: torch.Tensor, axes: Union[int, Seque
     return sf, out
 
 
-_hist_scratch = {}
-
-
 def exponent_histogram(x: torch.Tensor, histogram: torch.Tensor) -> torch.Tensor:
     """``histogram += torch.histc(floor(log2(|x|.float())), 254, min=-126, max=127)`` in place
     (fake_quantize.py:369-371): one counting pass over ``x`` (``vq_exp_histogram``) instead of abs, cast, log2,
@@ -138,9 +135,7 @@ def exponent_histogram(x: torch.Tensor, histogram: torch.Tensor) -> torch.Tensor
     xc = x.contiguous()
     if xc.numel():
         with torch.cuda.device(x.device):
-            ws = _hist_scratch.get(x.device)
-            if ws is None:
-                ws = _hist_scratch[x.device] = torch.empty(256, dtype=torch.int64, device=x.device)
+            ws = torch.empty(256, dtype=torch.int64, device=x.device)     # per call: safe with several streams
             et = exp_tables(torch.float32, 1.0, x.device)         # log2 is taken in fp32 whatever the dtype of x
             _lib.check(_lib.lib.vq_exp_histogram(xc.data_ptr(), _DT[x.dtype], xc.numel(), et.ptr(), histogram.data_ptr(),
                                                  ws.data_ptr(), ws.numel() * 8, torch.cuda.current_stream(x.device).cuda_stream),
