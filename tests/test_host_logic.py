@@ -181,3 +181,39 @@ def test_flat_tiny_flag_of_tables():
     assert not tables.analyse_table(tables.build_table("fp8_e4m3")).flat_tiny
     ident = np.arange(1 << 16, dtype=np.uint16)
     assert not tables.analyse_table(ident).flat_tiny
+
+
+def test_observer_entry_points_reject_bad_arguments_before_any_launch():
+    """Argument checks of the observer kernels' C ABI: an invalid dtype or size is refused with a message and a
+    negative status, before the device is touched (so this runs without a GPU)."""
+    lib = _lib.lib
+    lib.vq_last_error.restype = __import__("ctypes").c_char_p
+    assert lib.vq_exp_histogram(None, 7, 16, None, None, None, 0, None) < 0
+    assert b"dtype" in lib.vq_last_error()
+    assert lib.vq_exp_histogram(None, _lib.VQ_F32, -1, None, None, None, 0, None) < 0
+    assert lib.vq_outlier_split(None, 7, 16, None, None, None, None) < 0
+    assert lib.vq_outlier_split(None, _lib.VQ_BF16, 16, None, None, None, None) < 0           # null threshold / counter
+    assert lib.vq_outlier_merge(None, None, 9, 4, None, None, None) < 0
+    assert lib.vq_outlier_merge(None, None, _lib.VQ_F32, -4, None, None, None) < 0
+    assert lib.vq_group_affine_fake_quantize(None, 7, 2, 64, 32, 0.0, 15.0, None, None, None, None, None) < 0
+    assert lib.vq_group_affine_fake_quantize(None, _lib.VQ_F32, 2, 64, 0, 0.0, 15.0, None, None, None, None, None) < 0
+    assert lib.vq_group_affine_fake_quantize(None, _lib.VQ_F32, 2, 64, 32, 15.0, 15.0, None, None, None, None, None) < 0
+    assert b"quant_max" in lib.vq_last_error()
+    # empty inputs are a no-op
+    assert lib.vq_group_affine_fake_quantize(None, _lib.VQ_F32, 0, 64, 32, 0.0, 15.0, None, None, None, None, None) == 0
+    assert lib.vq_outlier_merge(None, None, _lib.VQ_F32, 0, torch.zeros(1).data_ptr(), None, None) == 0
+
+
+def test_module_accepts_every_upstream_scheme_and_option():
+    """Constructor parity with fake_quantize.py:216-307: no scheme or option is refused any more (construction needs no GPU)."""
+    from voyager_compiler_b200 import fake_quantize as fq
+    m = fq.FusedAmaxObsFakeQuantize("int8", qscheme="group_wise_affine", quant_min=0.0, quant_max=255.0, ch_axis=-1, block_size=32)
+    assert isinstance(m.calculate_qparams(), tuple) and len(m.calculate_qparams()) == 2
+    m = fq.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=4,
+                                    record_histogram=True, outlier_pct=0.01, outlier_ema_decay=0.5)
+    assert m.histogram.shape == (254,) and m.outlier_threshold.numel() == 0 and m.outlier_ema_decay == 0.5
+    assert m.max_outlier_pct == 0.0
+    m = fq.FusedAmaxObsFakeQuantize("int8", qscheme="microscaling", quant_max=127.0, ch_axis=-1, block_size=32, outlier_threshold=6.0)
+    assert m.outlier_threshold == 6.0
+    with pytest.raises(AssertionError):
+        fq.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, outlier_pct=0.1, outlier_threshold=1.0)
