@@ -32,9 +32,8 @@ BYTES_PER_ELEM = 2.0 + 0.5 + 4.0 / 64.0
 BLOCK = 64
 LAYER = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
 WORKLOAD = "cfg3: NF4 block-64 quantization of LLaMA-2-7B-shaped linear weights (225 bf16 tensors)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one mx_multi_kernel launch over the full
-# single-GPU workload: the 1-layer ncu capture summarised in profiles/mx_fast2_kernel_nf4_1layer.md
-# (500.5 MB) scaled by the elements processed; traffic grows in proportion to them.
+# DRAM bytes (read + write) one launch of the headline kernel moves over the full single-GPU
+# workload, from a profiler capture of a one-layer launch scaled by the elements processed.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 16.32e9
 
 
@@ -137,6 +136,29 @@ def cpu_time_oracle(tensors_cpu, repeats=1):
     return best, torch.get_num_threads()
 
 
+def parity_sample(tensors, results, qmap, max_tensors=4, max_rows=1024):
+    """Compares up to ``max_tensors`` packed results (first ``max_rows`` rows each; rows are
+    independent) with the CPU oracle.  Returns (elements checked, mismatching codes + scales)."""
+    import numpy as np
+    import torch
+    vo = oracle_module()
+    tab = torch.from_numpy(qmap.view(np.int16).copy()).view(torch.bfloat16)
+    idx_tab, _, _ = vo.index_table(tab)
+    n = len(tensors)
+    pick = sorted({0, n // 3, (2 * n) // 3, n - 1})[:max_tensors]
+    checked = bad = 0
+    for i in pick:
+        rows = min(max_rows, tensors[i].shape[0])
+        w = tensors[i][:rows].cpu()
+        s_ref = vo.mx_scale(w, (-1,), BLOCK, 1.0, False).float()
+        c_ref = vo.quantize(w, s_ref.to(w.dtype), None, (-1,), BLOCK, idx_tab).to(torch.uint8)
+        codes = results[i].codes[:rows].cpu()
+        got = torch.stack([codes & 0xF, codes >> 4], dim=-1).reshape(w.shape)
+        bad += int((got != c_ref).sum()) + int((results[i].scale[:rows].cpu().view(torch.int32) != s_ref.view(torch.int32)).sum())
+        checked += w.numel()
+    return checked, bad
+
+
 def run_reference(args):
     """CPU arm: rank 0 alone times the oracle port on a bounded sample per step."""
     import torch
@@ -190,8 +212,8 @@ def run_ours(args):
 
     shapes = model_shapes(args.layers)
     sizes = [r * c for r, c in shapes]
-    plan = mq.shard_plan(sizes, [r for r, _ in shapes], world)[rank]
-    tensors = [make_tensor(i, shapes[i], dev, (b, e)) for i, b, e in plan]
+    shard = mq.shard_plan(sizes, [r for r, _ in shapes], world)[rank]
+    tensors = [make_tensor(i, shapes[i], dev, (b, e)) for i, b, e in shard]
     my_elems = sum(t.numel() for t in tensors)
     total_elems = sum(sizes)
     qmap = vb.tables.build_table("nf4")
@@ -201,39 +223,58 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step():
-        return mq.quantize_tensors_mx(tensors, qmap, BLOCK, 1.0, False, code_bits=4)
+    # the pass is prepared once (outputs, descriptors, launch shape); a step is then one library
+    # call = one kernel launch over every tensor of this rank
+    plan = mq.MXQuantPlan(tensors, qmap, BLOCK, 1.0, False, code_bits=4)
+    step = plan.run
 
     for _ in range(max(args.warmup, 3)):
-        out = step()
-    del out
+        step()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = vb._lib.launch_count()
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    enqueue_s = 0.0
     evs[0].record()
     for k in range(args.steps):
-        out = step()
+        h0 = time.perf_counter()
+        step()
+        enqueue_s += time.perf_counter() - h0
         evs[k + 1].record()
-        del out
     barrier()
     launches = vb._lib.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     total_ms = evs[0].elapsed_time(evs[-1])
     per_step = [evs[k].elapsed_time(evs[k + 1]) for k in range(args.steps)]
-    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    # per rank: mean device time of a step (one launch) and mean host time spent queueing it
+    mine = torch.tensor([total_ms, statistics.mean(per_step), enqueue_s / args.steps * 1e3, float(my_elems)],
+                        device=dev, dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+    else:
+        every = [mine]
+    every = [e.tolist() for e in every]
+    total_ms = max(e[0] for e in every)
     ms_per_step = total_ms / args.steps
     value = total_elems * BYTES_PER_ELEM / (ms_per_step * 1e-3) / 1e9
+
+    # parity of what was just timed: a few of this rank's outputs against the CPU oracle
+    checked, mismatches = parity_sample(tensors, plan.results, qmap)
+    par = torch.tensor([checked, mismatches], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(par, op=dist.ReduceOp.SUM)
+    checked, mismatches = int(par[0].item()), int(par[1].item())
+    plan.close()
+    del plan
 
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"kernel_only": True, "layers": args.layers, "ms_per_step": ms_per_step, "value": value,
-                              "unit": "GB/s", "gpu_launches": int(launches)}))
+                              "unit": "GB/s", "gpu_launches": int(launches), "parity_checked": checked,
+                              "mismatches": mismatches, "kernel_ms": [e[1] for e in every]}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -267,8 +308,10 @@ def run_ours(args):
 
     if rank == 0:
         peaks, peak_kind = measured_peaks()
-        kernel_ms = statistics.mean(per_step)  # one mx_multi_kernel launch per step on this rank
-        achieved = my_elems * BYTES_PER_ELEM / (kernel_ms * 1e-3) / 1e9
+        # one launch per step and rank: the roofline entry describes the SLOWEST rank's launch
+        slow = max(range(world), key=lambda r: every[r][1])
+        kernel_ms, slow_elems = every[slow][1], every[slow][3]
+        achieved = slow_elems * BYTES_PER_ELEM / (kernel_ms * 1e-3) / 1e9
         line = {
             "metric": "nf4_whole_model_quantize_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -282,8 +325,10 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "mx_fast2_kernel<bf16, amax, LUT, pack4>", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * my_elems / total_elems,
-                         "algorithmic_bytes_per_launch": my_elems * BYTES_PER_ELEM, "launch_ms": kernel_ms},
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * slow_elems / total_elems,
+                         "algorithmic_bytes_per_launch": slow_elems * BYTES_PER_ELEM, "launch_ms": kernel_ms, "rank": slow},
+            "kernel_ms": [e[1] for e in every], "enqueue_ms": [e[2] for e in every],
+            "parity_checked": checked, "mismatches": mismatches,
         }
         if world == 1:
             # the pinned host copies of the e2e leg are the very tensors the GPU quantized

@@ -189,6 +189,22 @@ VQ_API int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype,
                                 const vq_table* table, int code_bits, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/* vq_quantize_mx_multi prepared once and run many times (weights re-quantized every calibration or
+ * training step; a sharded whole-model pass that repeats): create checks the arguments, picks the
+ * kernel and its launch shape and puts the descriptors into `workspace` (same size rule as above;
+ * the stream is synchronised once so the descriptors have landed); run is then a single kernel
+ * launch on any stream of the same device, with no host work that grows with the tensor count and
+ * no copy.  The tensors are read and written where the items pointed at creation time; the tables,
+ * the exponent tables and the workspace must stay alive and untouched for the life of the plan.
+ * Same upstream counterpart as vq_quantize_mx_multi. */
+typedef struct vq_mx_plan vq_mx_plan;
+VQ_API int vq_mx_plan_create(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max,
+                             int pow2, const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table,
+                             int code_bits, void* workspace, size_t workspace_bytes, void* stream,
+                             vq_mx_plan** plan_out);
+VQ_API int vq_mx_plan_run(const vq_mx_plan* plan, void* stream);
+VQ_API void vq_mx_plan_destroy(vq_mx_plan* plan);
+
 /* Y[M,N] = A[M,K] @ B[N,K]^T (+ bias[N]); A, B, bias, Y bf16, fp32 accumulation on the tensor
  * cores, operands fetched by TMA.  K must be a multiple of 8.  `status` (device int32, may be
  * NULL, zeroed by the caller) receives a non-zero code if a bounded wait inside the kernel ran out.

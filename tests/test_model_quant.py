@@ -209,3 +209,98 @@ def test_host_pipeline_round_trip():
     for (hc, hs), p in zip(outs, direct):
         assert torch.equal(hc, p.codes.cpu()) and torch.equal(hs, p.scale.cpu())
     assert pipe.h2d_bytes == sum(h.numel() * 2 for h in host) and pipe.d2h_bytes > 0
+
+
+def test_chunk_plan_keeps_order_and_covers_everything():
+    sizes = [5, 1, 9, 2, 2, 7, 1]
+    plan = mq.HostPipeline.chunk_plan(sizes, 8)
+    assert [i for ch in plan for i in ch] == list(range(len(sizes)))
+    assert all(sum(sizes[i] for i in ch[:-1]) < 8 for ch in plan)     # a chunk closes as soon as it reaches the size
+    assert mq.HostPipeline.chunk_plan([], 8) == []
+    assert mq.HostPipeline.chunk_plan([100], 8) == [[0]]
+
+
+_MANY = [(64, 256), (3, 64), (129, 1024), (1, 4096), (17, 128), (256, 512), (33, 192)]
+
+
+def _many_tensors(count, seed, dtype=torch.bfloat16, scale=0.02):
+    """``count`` tensors of mixed sizes (last dims multiples of 128), with an all-zero block, a NaN
+    and an Inf planted in three of them."""
+    g = torch.Generator().manual_seed(seed)
+    ws = [(torch.randn(_MANY[i % len(_MANY)], generator=g) * scale).to(dtype) for i in range(count)]
+    ws[1][0, :64] = 0
+    ws[4][3, 70] = float("nan")
+    ws[count - 1].view(-1)[5] = float("inf")
+    return ws
+
+
+def _check_packed_against_oracle(ws, packed, table, block, qmax, pow2):
+    tab_v = golden_table(table)
+    for k, (w, p) in enumerate(zip(ws, packed)):
+        s_ref = vo.mx_scale(w, (-1,), block, qmax, pow2)
+        assert same_bits(p.scale, s_ref.float())[0], f"tensor {k}: scales differ"
+        v_ref = vo.quantize(w, s_ref, None, (-1,), block, tab_v).float()
+        got = p.levels[mq.unpack_codes(p).cpu().long().clamp(max=p.levels.numel() - 1)]
+        ok = ~torch.isnan(v_ref)
+        assert torch.equal(got[ok], v_ref[ok]), f"tensor {k}: codes differ"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("count", [33, 40, 225])
+@pytest.mark.parametrize("generic", [False, True])
+def test_more_than_32_tensors_take_the_uploaded_descriptors(count, generic, monkeypatch):
+    """Above 32 tensors the descriptors and running tile counts travel through the device
+    workspace (40 tensors: small CTAs; 225: 1024-thread CTAs with the table staged in shared
+    memory, the shape of the whole-model pass); ``generic`` forces the unspecialised kernel, which
+    always reads the workspace.  Every tensor is compared with the CPU oracle bit for bit."""
+    if generic:
+        monkeypatch.setenv("VOYAGER_B200_GENERIC_MX", "1")
+    ws = _many_tensors(count, 100 + count)
+    packed = mq.quantize_tensors_mx([w.cuda() for w in ws], golden_table("nf4"), 64, 1.0, code_bits=4)
+    torch.cuda.synchronize()
+    _check_packed_against_oracle(ws, packed, "nf4", 64, 1.0, False)
+
+
+@pytest.mark.gpu
+def test_more_than_32_tensors_float_outputs_and_int8_pow2():
+    ws = _many_tensors(45, 7, torch.float32, 1.0)
+    q = golden_table("int8")
+    outs = mq.quantize_tensors_mx([w.cuda() for w in ws], q, 32, 127.0, True, float_outputs=True)
+    torch.cuda.synchronize()
+    for k, (w, (s, c)) in enumerate(zip(ws, outs)):
+        s_ref, c_ref = vo.quantize_mx(w, q, (-1,), 32, 127.0, True)
+        assert same_bits(s, s_ref)[0] and same_bits(c, c_ref)[0], k
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("count", [1, 7, 40, 225])
+def test_plan_runs_match_the_oracle_and_follow_new_data(count):
+    """A prepared pass: one, a few (descriptors in the kernel parameters) and many tensors
+    (descriptors uploaded once at creation).  The second run reads the tensors' new contents."""
+    ws = _many_tensors(max(count, 5), 300 + count)[:count] if count < 5 else _many_tensors(count, 300 + count)
+    dev = [w.cuda() for w in ws]
+    plan = mq.MXQuantPlan(dev, golden_table("nf4"), 64, 1.0, code_bits=4)
+    side = torch.cuda.Stream()
+    plan.run()
+    torch.cuda.synchronize()
+    _check_packed_against_oracle(ws, plan.results, "nf4", 64, 1.0, False)
+    ws2 = [(w.float() * 1.7 + 0.003).to(torch.bfloat16) for w in ws]
+    for d, w in zip(dev, ws2):
+        d.copy_(w)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):                     # any stream of the device will do
+        plan.run()
+    torch.cuda.synchronize()
+    _check_packed_against_oracle(ws2, plan.results, "nf4", 64, 1.0, False)
+    plan.close()
+
+
+@pytest.mark.gpu
+def test_plan_rejects_what_it_cannot_read_in_place():
+    x = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    with pytest.raises(ValueError):
+        mq.MXQuantPlan([x.t()], golden_table("nf4"), 64, 1.0)
+    with pytest.raises(NotImplementedError):
+        mq.MXQuantPlan([x[:, :100].contiguous()], golden_table("nf4"), 64, 1.0)
+    with pytest.raises(ValueError):
+        mq.MXQuantPlan([], golden_table("nf4"), 64, 1.0)

@@ -109,7 +109,15 @@ def _load():
         "vq_linear_mx_packed": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],
         "vq_quantize_mx_multi": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp, C.c_size_t, vp],
         "vq_channel_quantize_multi": [C.POINTER(VqChannelItem), ci, ci, dbl, T, vp, C.c_size_t, vp],
+        "vq_quantize_mx_multi_static": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp],
+        "vq_mx_plan_create": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp, C.c_size_t, vp,
+                              C.POINTER(C.c_void_p)],
+        "vq_mx_plan_run": [vp, vp],
     }
+    lib.vq_mx_plan_destroy.argtypes = [vp]
+    lib.vq_mx_plan_destroy.restype = None
+    lib.vq_quantize_mx_multi_static_max_items.argtypes = []
+    lib.vq_quantize_mx_multi_static_max_items.restype = C.c_int
     lib.vq_quantize_mx_multi_workspace.argtypes = [ci]
     lib.vq_quantize_mx_multi_workspace.restype = C.c_size_t
     lib.vq_channel_quantize_multi_workspace.argtypes = [C.POINTER(VqChannelItem), ci]

@@ -9,6 +9,8 @@
 // reduction of |x| bit patterns, scale rule, table lookup from shared memory, packed stores.
 // HBM bound; algorithmic bytes per element: sizeof(T) read + the requested outputs.
 #include <cstdlib>
+#include <new>
+#include <vector>
 
 #include "vq_mx_body.cuh"
 #include "vq_mx_fast.cuh"
@@ -93,7 +95,7 @@ struct FastParams {
     int64_t n_tiles;
     vq_mx_item single;
     // up to kInlineItems descriptors travel in the kernel parameters (constant bank): no upload
-    vq_mx_item inl[32];
+    vq_mx_item inl[32];      // kInlineItems
     int64_t inl_prefix[33];
     int n_inline;
     ScaleRule rule;
@@ -252,12 +254,24 @@ int dispatch_rule(const FastParams& p, int rule, int tk, int out, bool sm, int t
 
 constexpr int kThreads = 1024;
 constexpr int kU = 2;
+constexpr int kInlineItems = 32;
 
-}  // namespace
+// Everything a launch of the specialised kernel needs, decided once from the host descriptors.
+struct FastLaunch {
+    FastParams p;
+    int dtype = 0, pow2 = 0, tk = 0, out = 0;
+    bool sm = false;
+    int threads = 0, blocks = 0;
+    size_t smem = 0;
+    bool empty = false;             // no element to process: nothing is launched
+    bool upload = false;            // descriptors + running tile counts go to the device workspace
+    std::vector<int64_t> prefix;    // running tile counts (upload only)
+};
 
-int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
-                   const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
-                   void* workspace, cudaStream_t st) {
+// 1: `L` describes the launch; 0: the arguments are outside the specialised kernel's domain.
+int fast_prepare(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                 const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                 void* workspace, FastLaunch& L) {
     if (n_items < 1 || (pow2 != 0 && pow2 != 1)) return 0;
     int tk;
     const bool no_table = !table || table->kind == VQ_TABLE_NONE;
@@ -297,10 +311,19 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     const bool packed_out = out == OUT_PACK4 || out == OUT_PACK8;
     if (packed_out && tk == TK_LUT && (!table->lut8 || (uintptr_t)table->lut8 % 16)) return 0;
     if (packed_out && tk == TK_INT && (table->lo < -128.0f || table->hi > 255.0f)) return 0;
-    if (n_items > 32 && !workspace) return 0;
-    if (total == 0) return 1;
+    if (n_items > kInlineItems && !workspace) return 0;
+    L = FastLaunch{};
+    L.dtype = dtype;
+    L.pow2 = pow2;
+    L.tk = tk;
+    L.out = out;
+    if (total == 0) {
+        L.empty = true;
+        return 1;
+    }
 
-    FastParams p{};
+    FastParams& p = L.p;
+    p = FastParams{};
     p.n_items = n_items;
     p.rule.pow2 = pow2;
     p.rule.qmax = (float)quant_max;
@@ -323,7 +346,7 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
     if (n_items == 1) {
         p.single = items[0];
         p.n_tiles = (items[0].n + tile_elems - 1) / tile_elems;
-    } else if (n_items <= (int)(sizeof(p.inl) / sizeof(p.inl[0]))) {
+    } else if (n_items <= kInlineItems) {
         p.n_inline = n_items;
         p.inl_prefix[0] = 0;
         for (int i = 0; i < n_items; ++i) {
@@ -332,41 +355,77 @@ int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t bloc
         }
         p.n_tiles = p.inl_prefix[n_items];
     } else {
-        int64_t* prefix = new int64_t[(size_t)n_items + 1];
-        prefix[0] = 0;
-        for (int i = 0; i < n_items; ++i) prefix[i + 1] = prefix[i] + (items[i].n + tile_elems - 1) / tile_elems;
-        p.n_tiles = prefix[n_items];
+        L.upload = true;
+        L.prefix.resize((size_t)n_items + 1);
+        L.prefix[0] = 0;
+        for (int i = 0; i < n_items; ++i) L.prefix[i + 1] = L.prefix[i] + (items[i].n + tile_elems - 1) / tile_elems;
+        p.n_tiles = L.prefix[n_items];
         p.items = reinterpret_cast<const vq_mx_item*>(workspace);
         p.tile_prefix = reinterpret_cast<const int64_t*>((char*)workspace + (size_t)n_items * sizeof(vq_mx_item));
-        cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_mx_item), cudaMemcpyHostToDevice, st);
-        cudaError_t e2 = cudaMemcpyAsync((char*)workspace + (size_t)n_items * sizeof(vq_mx_item), prefix,
-                                         ((size_t)n_items + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st);
-        delete[] prefix;  // pageable copies are staged before cudaMemcpyAsync returns
-        if (e1 != cudaSuccess || e2 != cudaSuccess)
-            return vq_set_error(VQ_ERR_CUDA, "descriptor upload failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     }
-    const bool sm = big && tk == TK_LUT;
-    const size_t smem = sm ? ((out == OUT_FLOAT || out == OUT_FAKEQ) ? 131072 : 65536) : 0;
+    L.sm = big && tk == TK_LUT;
+    L.smem = L.sm ? ((out == OUT_FLOAT || out == OUT_FAKEQ) ? 131072 : 65536) : 0;
     const int64_t cap = big ? sms : (int64_t)sms * 8;
-    const int blocks = (int)(p.n_tiles < cap ? p.n_tiles : cap);
-    int rc = (dtype == VQ_F32) ? dispatch_rule<float>(p, pow2, tk, out, sm, threads, blocks, smem, st)
-                               : dispatch_rule<bf16_t>(p, pow2, tk, out, sm, threads, blocks, smem, st);
-    return rc ? rc : 1;
+    L.threads = threads;
+    L.blocks = (int)(p.n_tiles < cap ? p.n_tiles : cap);
+    return 1;
 }
 
-extern "C" {
-
-size_t vq_quantize_mx_multi_workspace(int n_items) {
-    if (n_items < 0) return 0;
-    return (size_t)n_items * sizeof(vq_mx_item) + ((size_t)n_items + 1) * sizeof(int64_t);
+// Descriptors and running tile counts -> device workspace (pageable sources are staged before
+// cudaMemcpyAsync returns, so the host arrays may be released right after).
+int upload_descriptors(const vq_mx_item* items, const int64_t* prefix, int n_items, void* workspace, cudaStream_t st) {
+    cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_mx_item), cudaMemcpyHostToDevice, st);
+    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + (size_t)n_items * sizeof(vq_mx_item), prefix,
+                                     ((size_t)n_items + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st);
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+        return vq_set_error(VQ_ERR_CUDA, "descriptor upload failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    return 0;
 }
 
-int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
-                         const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
-                         void* workspace, size_t workspace_bytes, void* stream) {
-    const char* name = "vq_quantize_mx_multi";
-    VQ_REQUIRE(n_items >= 0, "%s: negative item count", name);
-    if (n_items == 0) return 0;
+int fast_launch(const FastLaunch& L, cudaStream_t st) {
+    if (L.empty) return 0;
+    return (L.dtype == VQ_F32) ? dispatch_rule<float>(L.p, L.pow2, L.tk, L.out, L.sm, L.threads, L.blocks, L.smem, st)
+                               : dispatch_rule<bf16_t>(L.p, L.pow2, L.tk, L.out, L.sm, L.threads, L.blocks, L.smem, st);
+}
+
+// The generic multi-tensor kernel: always reads its descriptors from the workspace.
+struct GenericLaunch {
+    MultiParams mp;
+    int dtype = 0;
+    int blocks = 0;
+    size_t smem = 0;
+    std::vector<int64_t> prefix;
+};
+
+int generic_launch(const GenericLaunch& G, cudaStream_t st) {
+    if (G.mp.n_tiles == 0) return 0;
+    if (G.dtype == VQ_F32) {
+        auto k = mx_multi_kernel<float, kU>;
+        if (G.smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G.smem));
+        k<<<G.blocks, kThreads, G.smem, st>>>(G.mp);
+    } else {
+        auto k = mx_multi_kernel<bf16_t, kU>;
+        if (G.smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G.smem));
+        k<<<G.blocks, kThreads, G.smem, st>>>(G.mp);
+    }
+    VQ_LAUNCH_CHECK("mx_multi_kernel");
+    return 0;
+}
+
+// A prepared multi-tensor pass: which kernel, its parameters, whether descriptors must be uploaded.
+struct MultiLaunch {
+    bool fast = false;
+    FastLaunch f;
+    GenericLaunch g;
+    bool needs_upload() const { return fast ? f.upload : true; }
+    const int64_t* prefix() const { return fast ? f.prefix.data() : g.prefix.data(); }
+    int launch(cudaStream_t st) const { return fast ? fast_launch(f, st) : generic_launch(g, st); }
+};
+
+// Argument checks + launch set-up shared by vq_quantize_mx_multi and the plan.  0 on success.
+int multi_prepare(const char* name, const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max,
+                  int pow2, const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                  void* workspace, size_t workspace_bytes, MultiLaunch& M) {
     VQ_REQUIRE(items != nullptr, "%s: null item array", name);
     VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
     VQ_REQUIRE(pow2 == 0 || pow2 == 1, "%s: scale rule must be 0 (amax/qmax) or 1 (power of two)", name);
@@ -385,7 +444,7 @@ int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_
 
     bool any_codes8 = false, any_values = false;
     const int64_t tile_elems = (int64_t)kThreads * kU * N;
-    int64_t* prefix = new int64_t[(size_t)n_items + 1];
+    std::vector<int64_t> prefix((size_t)n_items + 1);
     prefix[0] = 0;
     int64_t total = 0;
     for (int i = 0; i < n_items; ++i) {
@@ -394,16 +453,11 @@ int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_
         bool ok = it.in && it.n >= 0 && it.n % block == 0 && it.n < (1ll << 31) && al(it.in, 16) && al(it.out_codes, 16) &&
                   al(it.dequant, 16) && al(it.codes, 8) && al(it.scale_f32, 4) &&
                   (it.out_scale || it.out_codes || it.scale_f32 || it.exp_e8 || it.codes || it.dequant);
-        if (!ok) {
-            delete[] prefix;
+        if (!ok)
             return vq_set_error(VQ_ERR_INVALID,
                                 "%s: item %d needs a 16-byte aligned input, n a multiple of the block below 2^31, "
                                 "aligned outputs and at least one output", name, i);
-        }
-        if (it.exp_e8 && !pow2) {
-            delete[] prefix;
-            return vq_set_error(VQ_ERR_INVALID, "%s: item %d: exp_e8 needs power-of-two scales", name, i);
-        }
+        if (it.exp_e8 && !pow2) return vq_set_error(VQ_ERR_INVALID, "%s: item %d: exp_e8 needs power-of-two scales", name, i);
         any_codes8 |= it.codes != nullptr;
         any_values |= it.out_codes != nullptr || it.dequant != nullptr;
         prefix[i + 1] = prefix[i] + (it.n + tile_elems - 1) / tile_elems;
@@ -411,22 +465,19 @@ int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_
     }
     if (any_codes8) {
         bool have = table->kind == VQ_TABLE_INT || table->lut8 || (table->kind == VQ_TABLE_RUNS && table->run_codes);
-        if (!have || (code_bits != 8 && code_bits != 4)) {
-            delete[] prefix;
+        if (!have || (code_bits != 8 && code_bits != 4))
             return vq_set_error(VQ_ERR_INVALID, "%s: packed codes need code_bits 8 or 4 and a code table", name);
-        }
     }
 
-    if (!getenv("VOYAGER_B200_GENERIC_MX")) {
-        int fr = vq_mx_fast_try(items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits,
-                                workspace, (cudaStream_t)stream);
-        if (fr != 0) {
-            delete[] prefix;
-            return fr < 0 ? fr : 0;
-        }
+    if (!getenv("VOYAGER_B200_GENERIC_MX") &&
+        fast_prepare(items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits, workspace, M.f)) {
+        M.fast = true;
+        return 0;
     }
-
-    MultiParams mp{};
+    M.fast = false;
+    GenericLaunch& G = M.g;
+    MultiParams& mp = G.mp;
+    mp = MultiParams{};
     mp.items = reinterpret_cast<const vq_mx_item*>(workspace);
     mp.tile_prefix = reinterpret_cast<const int64_t*>((char*)workspace + (size_t)n_items * sizeof(vq_mx_item));
     mp.n_items = n_items;
@@ -446,30 +497,93 @@ int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_
     size_t smem = (mp.common.smem_lut16 ? 131072 : 0) + (mp.common.smem_lut8 ? 65536 : 0) +
                   (table->kind == VQ_TABLE_RUNS ? 5 * VQ_MAX_RUNS : 0);
     if ((int)smem > vq_max_smem_optin()) { mp.common.smem_lut8 = 0; smem -= 65536; }
-
-    cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_mx_item), cudaMemcpyHostToDevice, st);
-    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + (size_t)n_items * sizeof(vq_mx_item), prefix,
-                                     ((size_t)n_items + 1) * sizeof(int64_t), cudaMemcpyHostToDevice, st);
-    const int64_t n_tiles = prefix[n_items];
-    delete[] prefix;  // pageable copies are staged before cudaMemcpyAsync returns
-    if (e1 != cudaSuccess || e2 != cudaSuccess)
-        return vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload failed: %s", name, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
-    if (n_tiles == 0) return 0;
+    G.smem = smem;
+    G.dtype = dtype;
     const int sms = vq_sm_count();
-    int blocks = (int)(n_tiles < sms ? n_tiles : sms);
-    if (dtype == VQ_F32) {
-        auto k = mx_multi_kernel<float, kU>;
-        if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<blocks, kThreads, smem, st>>>(mp);
-    } else {
-        auto k = mx_multi_kernel<bf16_t, kU>;
-        if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<blocks, kThreads, smem, st>>>(mp);
-    }
-    VQ_LAUNCH_CHECK("mx_multi_kernel");
+    G.blocks = (int)(mp.n_tiles < sms ? mp.n_tiles : sms);
+    G.prefix = std::move(prefix);
     return 0;
 }
+
+}  // namespace
+
+int vq_mx_fast_try(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                   const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                   void* workspace, cudaStream_t st) {
+    FastLaunch L;
+    if (!fast_prepare(items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits, workspace, L)) return 0;
+    if (L.upload) {
+        int rc = upload_descriptors(items, L.prefix.data(), n_items, workspace, st);
+        if (rc) return rc;
+    }
+    int rc = fast_launch(L, st);
+    return rc ? rc : 1;
+}
+
+// A prepared pass (see vq_mx_plan_create).
+struct vq_mx_plan {
+    MultiLaunch m;
+    int device = -1;
+};
+
+extern "C" {
+
+size_t vq_quantize_mx_multi_workspace(int n_items) {
+    if (n_items < 0) return 0;
+    return (size_t)n_items * sizeof(vq_mx_item) + ((size_t)n_items + 1) * sizeof(int64_t);
+}
+
+int vq_quantize_mx_multi(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                         const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+    const char* name = "vq_quantize_mx_multi";
+    VQ_REQUIRE(n_items >= 0, "%s: negative item count", name);
+    if (n_items == 0) return 0;
+    MultiLaunch M;
+    int rc = multi_prepare(name, items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits,
+                           workspace, workspace_bytes, M);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M.needs_upload()) {
+        rc = upload_descriptors(items, M.prefix(), n_items, workspace, st);
+        if (rc) return rc;
+    }
+    return M.launch(st);
+}
+
+int vq_mx_plan_create(const vq_mx_item* items, int n_items, int dtype, int64_t block, double quant_max, int pow2,
+                      const vq_exp_tables* exp, const vq_table* scale_table, const vq_table* table, int code_bits,
+                      void* workspace, size_t workspace_bytes, void* stream, vq_mx_plan** plan_out) {
+    const char* name = "vq_mx_plan_create";
+    VQ_REQUIRE(plan_out != nullptr, "%s: null plan pointer", name);
+    *plan_out = nullptr;
+    VQ_REQUIRE(n_items >= 1, "%s: a plan needs at least one tensor", name);
+    vq_mx_plan* plan = new (std::nothrow) vq_mx_plan();
+    VQ_REQUIRE(plan != nullptr, "%s: out of host memory", name);
+    int rc = multi_prepare(name, items, n_items, dtype, block, quant_max, pow2, exp, scale_table, table, code_bits,
+                           workspace, workspace_bytes, plan->m);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!rc && plan->m.needs_upload()) {
+        rc = upload_descriptors(items, plan->m.prefix(), n_items, workspace, st);
+        // run() may be queued on any stream afterwards: the descriptors must have landed by then
+        if (!rc && cudaStreamSynchronize(st) != cudaSuccess)
+            rc = vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload did not complete", name);
+    }
+    if (!rc && cudaGetDevice(&plan->device) != cudaSuccess) rc = vq_set_error(VQ_ERR_CUDA, "%s: cudaGetDevice failed", name);
+    if (rc) {
+        delete plan;
+        return rc;
+    }
+    *plan_out = plan;
+    return 0;
+}
+
+int vq_mx_plan_run(const vq_mx_plan* plan, void* stream) {
+    VQ_REQUIRE(plan != nullptr, "vq_mx_plan_run: null plan");
+    return plan->m.launch((cudaStream_t)stream);
+}
+
+void vq_mx_plan_destroy(vq_mx_plan* plan) { delete plan; }
 
 }  // extern "C"
 

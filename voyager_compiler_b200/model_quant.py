@@ -22,7 +22,7 @@ import torch
 from . import _lib
 from .qtables import exp_tables, table_handle
 
-__all__ = ["PackedMX", "quantize_tensors_mx", "ChannelQuant", "ChannelQuantPlan", "quantize_tensors_per_channel", "dequantize_packed", "unpack_codes", "dequantize_packed_reference", "shard_plan",
+__all__ = ["PackedMX", "quantize_tensors_mx", "MXQuantPlan", "ChannelQuant", "ChannelQuantPlan", "quantize_tensors_per_channel", "dequantize_packed", "unpack_codes", "dequantize_packed_reference", "shard_plan",
            "HostPipeline"]
 
 _DT = {torch.float32: _lib.VQ_F32, torch.bfloat16: _lib.VQ_BF16}
@@ -52,6 +52,84 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+def _check_block_multiple(tensors, idx, device, block):
+    for i in idx:
+        t = tensors[i]
+        if t.device != device:
+            raise ValueError("all tensors must live on one device")
+        if t.ndim < 1 or t.shape[-1] % block:
+            raise NotImplementedError(
+                f"tensor {i}: last dimension {tuple(t.shape)} must be a multiple of the block ({block})")
+
+
+def _build_items(tensors, idx, dt, device, block, code_bits, float_outputs, want_exp, levels, results, in_place=False):
+    """Descriptors and freshly allocated outputs for the tensors ``idx`` (all of dtype ``dt``).
+    Fills ``results`` and returns ``(items, inputs kept alive)``.  ``in_place``: the tensors are read
+    where they are (they must be contiguous) instead of through ``.contiguous()`` copies."""
+    items = (_lib.VqMxItem * len(idx))()
+    keep = []
+
+    def source(i):
+        t = tensors[i]
+        if in_place and not t.is_contiguous():
+            raise ValueError(f"tensor {i} must be contiguous (the plan reads it in place)")
+        return t.contiguous()
+
+    if float_outputs:
+        for k, i in enumerate(idx):
+            t = tensors[i]
+            x = source(i)
+            sc = torch.empty(tuple(t.shape[:-1]) + (t.shape[-1] // block,), dtype=dt, device=device)
+            cd = torch.empty_like(x)
+            items[k].input, items[k].n = x.data_ptr(), x.numel()
+            items[k].out_scale, items[k].out_codes = sc.data_ptr(), cd.data_ptr()
+            results[i] = (sc, cd)
+            keep.append(x)
+        return items, keep
+    # one allocation per output kind for the whole group; the per-tensor results are views
+    # (16-byte aligned segments), which keeps the host cost of a call low for many tensors
+    per_byte = 8 // code_bits
+    nel = [tensors[i].numel() for i in idx]
+    cbytes = [(n // per_byte + 15) // 16 * 16 for n in nel]
+    nblk = [n // block for n in nel]
+    codes_all = torch.empty(sum(cbytes), dtype=torch.uint8, device=device)
+    scale_all = torch.empty(sum(nblk), dtype=torch.float32, device=device)
+    exp_all = torch.empty(sum(nblk), dtype=torch.int8, device=device) if want_exp else None
+    cviews, sviews = codes_all.split(cbytes), scale_all.split(nblk)
+    eviews = exp_all.split(nblk) if want_exp else None
+    cbase, sbase = codes_all.data_ptr(), scale_all.data_ptr()
+    ebase = exp_all.data_ptr() if want_exp else 0
+    coff = soff = 0
+    for k, i in enumerate(idx):
+        t = tensors[i]
+        x = source(i)
+        lead = tuple(t.shape[:-1])
+        items[k].input, items[k].n = x.data_ptr(), nel[k]
+        items[k].scale_f32, items[k].codes = sbase + 4 * soff, cbase + coff
+        if want_exp:
+            items[k].exp_e8 = ebase + soff
+        cd = cviews[k][:nel[k] // per_byte].view(lead + (t.shape[-1] // per_byte,))
+        sc = sviews[k].view(lead + (t.shape[-1] // block,))
+        ex = eviews[k].view(lead + (t.shape[-1] // block,)) if want_exp else None
+        results[i] = PackedMX(cd, sc, tuple(t.shape), block, code_bits, levels, ex)
+        coff += cbytes[k]
+        soff += nblk[k]
+        keep.append(x)
+    return items, keep
+
+
+def _tables_for(qmap, scale_qmap, device, float_outputs, code_bits):
+    tab = table_handle(qmap, device)
+    if not float_outputs:
+        if code_bits not in (4, 8):
+            raise ValueError("code_bits must be 4 or 8")
+        tab.with_codes()
+        if code_bits == 4 and tab.levels.numel() > 16:
+            raise ValueError(f"table has {tab.levels.numel()} levels; 4-bit codes hold 16")
+    stab = table_handle(scale_qmap, device, allow_runs=False) if scale_qmap is not None else None
+    return tab, stab
+
+
 def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant_max: float,
                         force_scale_power_of_two: bool = False, scale_qmap=None, code_bits: Optional[int] = 4,
                         float_outputs: bool = False, want_exp: bool = False):
@@ -67,69 +145,16 @@ def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant
         raise RuntimeError("quantize_tensors_mx: CUDA tensors only; there is no CPU path")
     results: List = [None] * len(tensors)
     with torch.cuda.device(device):
-        tab = table_handle(qmap, device)
-        if not float_outputs:
-            if code_bits not in (4, 8):
-                raise ValueError("code_bits must be 4 or 8")
-            tab.with_codes()
-            if code_bits == 4 and tab.levels.numel() > 16:
-                raise ValueError(f"table has {tab.levels.numel()} levels; 4-bit codes hold 16")
-        stab = table_handle(scale_qmap, device, allow_runs=False) if scale_qmap is not None else None
+        tab, stab = _tables_for(qmap, scale_qmap, device, float_outputs, code_bits)
         stream = torch.cuda.current_stream(device).cuda_stream
         for dt in (torch.bfloat16, torch.float32):
             idx = [i for i, t in enumerate(tensors) if t.dtype == dt]
             if not idx:
                 continue
             exp = exp_tables(dt, quant_max, device) if force_scale_power_of_two else None
-            items = (_lib.VqMxItem * len(idx))()
-            keep = []
-            for i in idx:
-                t = tensors[i]
-                if t.device != device:
-                    raise ValueError("all tensors must live on one device")
-                if t.ndim < 1 or t.shape[-1] % block:
-                    raise NotImplementedError(
-                        f"tensor {i}: last dimension {tuple(t.shape)} must be a multiple of the block ({block})")
-            if float_outputs:
-                for k, i in enumerate(idx):
-                    t = tensors[i]
-                    x = t.contiguous()
-                    sc = torch.empty(tuple(t.shape[:-1]) + (t.shape[-1] // block,), dtype=dt, device=device)
-                    cd = torch.empty_like(x)
-                    items[k].input, items[k].n = x.data_ptr(), x.numel()
-                    items[k].out_scale, items[k].out_codes = sc.data_ptr(), cd.data_ptr()
-                    results[i] = (sc, cd)
-                    keep.append(x)
-            else:
-                # one allocation per output kind for the whole group; the per-tensor results are views
-                # (16-byte aligned segments), which keeps the host cost of a call low for many tensors
-                per_byte = 8 // code_bits
-                nel = [tensors[i].numel() for i in idx]
-                cbytes = [(n // per_byte + 15) // 16 * 16 for n in nel]
-                nblk = [n // block for n in nel]
-                codes_all = torch.empty(sum(cbytes), dtype=torch.uint8, device=device)
-                scale_all = torch.empty(sum(nblk), dtype=torch.float32, device=device)
-                exp_all = torch.empty(sum(nblk), dtype=torch.int8, device=device) if want_exp else None
-                cviews, sviews = codes_all.split(cbytes), scale_all.split(nblk)
-                eviews = exp_all.split(nblk) if want_exp else None
-                cbase, sbase = codes_all.data_ptr(), scale_all.data_ptr()
-                ebase = exp_all.data_ptr() if want_exp else 0
-                coff = soff = 0
-                for k, i in enumerate(idx):
-                    t = tensors[i]
-                    x = t.contiguous()
-                    lead = tuple(t.shape[:-1])
-                    items[k].input, items[k].n = x.data_ptr(), nel[k]
-                    items[k].scale_f32, items[k].codes = sbase + 4 * soff, cbase + coff
-                    if want_exp:
-                        items[k].exp_e8 = ebase + soff
-                    cd = cviews[k][:nel[k] // per_byte].view(lead + (t.shape[-1] // per_byte,))
-                    sc = sviews[k].view(lead + (t.shape[-1] // block,))
-                    ex = eviews[k].view(lead + (t.shape[-1] // block,)) if want_exp else None
-                    results[i] = PackedMX(cd, sc, tuple(t.shape), block, code_bits, tab.levels, ex)
-                    coff += cbytes[k]
-                    soff += nblk[k]
-                    keep.append(x)
+            _check_block_multiple(tensors, idx, device, block)
+            items, keep = _build_items(tensors, idx, dt, device, block, code_bits, float_outputs, want_exp,
+                                       None if float_outputs else tab.levels, results)
             need = _lib.lib.vq_quantize_mx_multi_workspace(len(idx))
             ws = _workspace(device, need)
             _lib.check(_lib.lib.vq_quantize_mx_multi(
@@ -138,6 +163,70 @@ def quantize_tensors_mx(tensors: Sequence[torch.Tensor], qmap, block: int, quant
                 0 if float_outputs else code_bits, ws.data_ptr(), ws.numel(), stream), "quantize_tensors_mx")
             del keep
     return results
+
+
+class MXQuantPlan:
+    """:func:`quantize_tensors_mx` prepared once: outputs, descriptors, tables and the launch shape
+    are fixed at construction, so :meth:`run` is one library call -- one kernel launch -- per dtype
+    with no allocation, no descriptor copy and no Python work that grows with the tensor count.
+    For passes that repeat over the same parameters (weights re-quantized every calibration or
+    training step, the shards of a whole-model pass).  The tensors are read where they are when
+    ``run()`` executes, so they must be contiguous and stay alive; ``results`` (one
+    :class:`PackedMX`, or one ``(scale, codes)`` pair with ``float_outputs``, per tensor) is
+    overwritten by every run."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor], qmap, block: int, quant_max: float,
+                 force_scale_power_of_two: bool = False, scale_qmap=None, code_bits: Optional[int] = 4,
+                 float_outputs: bool = False, want_exp: bool = False):
+        if not tensors:
+            raise ValueError("no tensors")
+        device = tensors[0].device
+        if device.type != "cuda":
+            raise RuntimeError("MXQuantPlan: CUDA tensors only; there is no CPU path")
+        self.device = device
+        self.results: List = [None] * len(tensors)
+        self._plans: List[C.c_void_p] = []
+        self._keep = []
+        with torch.cuda.device(device):
+            self._tab, self._stab = _tables_for(qmap, scale_qmap, device, float_outputs, code_bits)
+            stream = torch.cuda.current_stream(device).cuda_stream
+            for dt in (torch.bfloat16, torch.float32):
+                idx = [i for i, t in enumerate(tensors) if t.dtype == dt]
+                if not idx:
+                    continue
+                exp = exp_tables(dt, quant_max, device) if force_scale_power_of_two else None
+                _check_block_multiple(tensors, idx, device, block)
+                items, keep = _build_items(tensors, idx, dt, device, block, code_bits, float_outputs, want_exp,
+                                           None if float_outputs else self._tab.levels, self.results, in_place=True)
+                ws = torch.empty(max(_lib.lib.vq_quantize_mx_multi_workspace(len(idx)), 16), dtype=torch.uint8, device=device)
+                handle = C.c_void_p()
+                _lib.check(_lib.lib.vq_mx_plan_create(
+                    items, len(idx), _DT[dt], block, float(quant_max), 1 if force_scale_power_of_two else 0,
+                    exp.ptr() if exp is not None else None, self._stab.ptr() if self._stab is not None else None,
+                    self._tab.ptr(), 0 if float_outputs else code_bits, ws.data_ptr(), ws.numel(), stream,
+                    C.byref(handle)), "MXQuantPlan")
+                self._plans.append(handle)
+                self._keep.append((keep, ws, exp))
+
+    def run(self) -> List:
+        """Queue the pass on the current stream of the plan's device; returns ``results``."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        run, check = _lib.lib.vq_mx_plan_run, _lib.check
+        with torch.cuda.device(self.device):
+            for h in self._plans:
+                check(run(h, stream), "MXQuantPlan.run")
+        return self.results
+
+    def close(self) -> None:
+        for h in self._plans:
+            _lib.lib.vq_mx_plan_destroy(h)
+        self._plans = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass
 
 
 @dataclass
@@ -323,8 +412,9 @@ class HostPipeline:
     chunk by chunk, so the transfers overlap the kernel."""
 
     def __init__(self, device, qmap, block: int, quant_max: float, force_scale_power_of_two: bool = False,
-                 code_bits: int = 4, chunk_bytes: int = 1 << 30):
+                 code_bits: int = 4, chunk_bytes: int = 1 << 30, chunks_in_flight: int = 3):
         self.device = torch.device(device)
+        self.chunks_in_flight = max(1, int(chunks_in_flight))
         self.qmap, self.block, self.quant_max = qmap, block, quant_max
         self.pow2, self.code_bits, self.chunk_bytes = force_scale_power_of_two, code_bits, chunk_bytes
         self.s_in = torch.cuda.Stream(self.device)
@@ -333,23 +423,33 @@ class HostPipeline:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
-    def run(self, host_tensors: Sequence[torch.Tensor], host_out: Optional[List[Tuple[torch.Tensor, torch.Tensor]]] = None):
-        """Returns ``[(codes_host, scale_host), ...]``; ``host_out`` supplies preallocated pinned
-        destinations.  Synchronises the three streams before returning."""
-        dev = self.device
+    @staticmethod
+    def chunk_plan(nbytes: Sequence[int], chunk_bytes: int) -> List[List[int]]:
+        """Consecutive tensors grouped until a group reaches ``chunk_bytes``; every index once, in order."""
         chunks, cur, size = [], [], 0
-        for i, t in enumerate(host_tensors):
+        for i, n in enumerate(nbytes):
             cur.append(i)
-            size += t.numel() * t.element_size()
-            if size >= self.chunk_bytes:
+            size += n
+            if size >= chunk_bytes:
                 chunks.append(cur)
                 cur, size = [], 0
         if cur:
             chunks.append(cur)
+        return chunks
+
+    def run(self, host_tensors: Sequence[torch.Tensor], host_out: Optional[List[Tuple[torch.Tensor, torch.Tensor]]] = None):
+        """Returns ``[(codes_host, scale_host), ...]``; ``host_out`` supplies preallocated pinned
+        destinations.  Synchronises the three streams before returning.  At most
+        ``chunks_in_flight`` chunks (inputs + packed results) are resident on the device at a time:
+        the host waits for the oldest chunk's copy-out before it queues another one."""
+        dev = self.device
+        chunks = self.chunk_plan([t.numel() * t.element_size() for t in host_tensors], self.chunk_bytes)
         outs: List = [None] * len(host_tensors)
         self.h2d_bytes = self.d2h_bytes = 0
-        live = []
+        in_flight: List = []
         for ch in chunks:
+            if len(in_flight) >= self.chunks_in_flight:
+                in_flight.pop(0).synchronize()
             with torch.cuda.stream(self.s_in):
                 dev_in = [host_tensors[i].to(dev, non_blocking=True) for i in ch]
                 ev_in = torch.cuda.Event()
@@ -379,7 +479,10 @@ class HostPipeline:
             for p in packed:
                 p.codes.record_stream(self.s_out)
                 p.scale.record_stream(self.s_out)
-            live.append((dev_in, packed))
+            ev_out = torch.cuda.Event()
+            ev_out.record(self.s_out)
+            in_flight.append(ev_out)
+            del dev_in, packed
         self.s_in.synchronize()
         self.s_k.synchronize()
         self.s_out.synchronize()
