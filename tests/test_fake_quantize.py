@@ -69,6 +69,61 @@ def test_cpu_tensors_rejected():
         fq.fake_quantize(torch.zeros(4), torch.ones(1), golden_table("int8"))
 
 
+def test_module_on_another_device_than_its_input_is_refused_on_the_host():
+    """A module built without ``device=`` keeps its buffers on the CPU; handing their addresses to a
+    kernel together with a device input would read the wrong memory.  The check is a Python
+    exception before any launch (a ``meta`` input stands in for a device one here)."""
+    from voyager_compiler_b200 import fake_quantize as fq
+    x = torch.empty(4, 64, device="meta")
+    for kw in (dict(qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=4),
+               dict(qscheme="per_channel_symmetric", quant_max=127.0, amax_history_len=4, ch_axis=0),
+               dict(qscheme="microscaling", quant_max=127.0, ch_axis=-1, block_size=32),
+               dict(qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=4, outlier_threshold=3.0),
+               dict(qscheme="per_tensor_symmetric", quant_max=127.0, amax_history_len=4, outlier_pct=0.01)):
+        m = fq.FusedAmaxObsFakeQuantize("int8", **kw)
+        with pytest.raises(RuntimeError, match="same device"):
+            m(x)
+    with pytest.raises(RuntimeError, match="same device"):
+        fq.outlier_split(x, torch.tensor([3.0]))
+    with pytest.raises(RuntimeError, match="same device"):
+        fq.outlier_merge(x, x, torch.tensor([3.0]))
+    with pytest.raises(ValueError):
+        fq.outlier_split(x, torch.tensor([3.0], dtype=torch.float64))
+    with pytest.raises(ValueError):
+        fq.outlier_split(x, 3.0)
+
+
+def test_state_dict_round_trip_resizes_buffers_and_refreshes_the_switches():
+    """fake_quantize.py:434-463: a checkpoint saved after calibration loads into a fresh module, and
+    the switches it carries (or that are written into the buffers directly) reach the host mirrors
+    the forward reads."""
+    from voyager_compiler_b200 import fake_quantize as fq
+    kw = dict(qscheme="per_channel_symmetric", quant_max=127.0, amax_history_len=4, ch_axis=0)
+    a = fq.FusedAmaxObsFakeQuantize("int8", **kw)
+    a.amax_history.resize_(4, 6, 1).copy_(torch.arange(24.0).reshape(4, 6, 1))      # as after a forward on [6, k]
+    a.scale.resize_(6, 1).copy_(torch.arange(6.0).reshape(6, 1) + 0.5)
+    a.observer_enabled[0] = 0                                                          # written in place, not via the method
+    a._refresh_switches()
+    assert a._obs_on is False and a._fq_on is True
+    sd = a.state_dict()
+    assert set(sd) >= {"scale", "amax_history", "fake_quant_enabled", "observer_enabled", "zero_point"}
+    b = fq.FusedAmaxObsFakeQuantize("int8", **kw)
+    assert b._obs_on is True
+    b.load_state_dict(sd)
+    assert torch.equal(b.amax_history, a.amax_history) and torch.equal(b.scale, a.scale)
+    assert b._obs_on is False and b._fq_on is True and int(b._fq_host[0]) == 1
+    b.fake_quant_enabled[0] = 0
+    b._refresh_switches()
+    assert b._fq_on is False and int(b._fq_host[0]) == 0
+    b.enable_fake_quant()
+    b.enable_observer()
+    assert b._fq_on and b._obs_on and int(b.observer_enabled[0]) == 1
+    # strict loading still reports what is missing
+    c = fq.FusedAmaxObsFakeQuantize("int8", **kw)
+    with pytest.raises(RuntimeError, match="amax_history"):
+        c.load_state_dict({k: v for k, v in sd.items() if k != "amax_history"})
+
+
 # ------------------------------------------------------------------------------------------ GPU
 @pytest.mark.gpu
 @pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
@@ -129,3 +184,35 @@ def test_mx_fake_quantize_matches_oracle_large():
         s, y = fq.mx_fake_quantize(x.cuda(), qmap.cuda(), -1, block, qmax, pow2)
         s_ref, y_ref = vo.mx_fake_quantize(x, qmap, -1, block, qmax, pow2)
         assert _same(s, s_ref) and _same(y, y_ref)
+
+
+@pytest.mark.gpu
+def test_per_channel_observer_refuses_a_new_channel_count_and_loads_a_checkpoint():
+    from voyager_compiler_b200 import fake_quantize as fq
+    kw = dict(qscheme="per_channel_symmetric", quant_max=127.0, amax_history_len=4, ch_axis=0)
+    m = fq.FusedAmaxObsFakeQuantize("int8", device="cuda", **kw)
+    torch.manual_seed(0)
+    x = torch.randn(6, 40, device="cuda")
+    y1 = m(x)
+    with pytest.raises(RuntimeError, match="observer state"):
+        m(torch.randn(9, 40, device="cuda"))                   # larger count: would index past the history
+    with pytest.raises(RuntimeError, match="observer state"):
+        m(torch.randn(3, 40, device="cuda"))
+    y2 = m(x)                                                   # the module is still usable
+    # save -> load into a fresh module -> same next step, observer switch included
+    n = fq.FusedAmaxObsFakeQuantize("int8", device="cuda", **kw)
+    n.load_state_dict(m.state_dict())
+    assert torch.equal(n.scale, m.scale) and torch.equal(n.amax_history, m.amax_history)
+    assert torch.equal(n(x), m(x))
+    m.observer_enabled[0] = 0                                   # in-place write: the mirror follows
+    before = m.amax_history.clone()
+    m(x * 3)
+    assert torch.equal(m.amax_history, before)
+    n.load_state_dict(m.state_dict())
+    n(x * 3)
+    assert torch.equal(n.amax_history, before)
+    # a module left on the CPU refuses a device input instead of handing host addresses to a kernel
+    cpu_mod = fq.FusedAmaxObsFakeQuantize("int8", **kw)
+    with pytest.raises(RuntimeError, match="same device"):
+        cpu_mod(x)
+    del y1, y2

@@ -165,3 +165,26 @@ def test_linear_mx_dynamic_equals_quantize_mx_then_linear_mx(table, qmax, pow2, 
     assert got.shape == two_ops.shape == want.shape
     assert torch.equal(got.view(torch.int16), two_ops.view(torch.int16))
     assert _rel(got.float(), want.float()) <= 1e-2
+
+
+@pytest.mark.gpu
+def test_status_word_is_one_per_device_however_the_device_is_named(monkeypatch):
+    """``cuda``, ``cuda:0`` and a ``torch.device`` name the same word, so a wait that ran out is
+    seen by whoever asks; with VOYAGER_B200_GEMM_CHECK=1 the next native GEMM call raises."""
+    from voyager_compiler_b200 import _lib, gemm_native
+    torch.cuda.set_device(0)
+    word = gemm_native._status_tensor(torch.device("cuda:0"))
+    assert gemm_native._status_tensor("cuda") is word and gemm_native._status_tensor(torch.device("cuda")) is word
+    word.fill_(3)                                   # what the epilogue role writes when its wait runs out
+    assert gemm_native.gemm_status("cuda") == 3
+    assert gemm_native.gemm_status("cuda:0") == 0   # read once, cleared
+    with pytest.raises(ValueError):
+        gemm_native.gemm_status("cpu")
+    monkeypatch.setenv("VOYAGER_B200_GEMM_CHECK", "1")
+    a = torch.randn(256, 64, device="cuda").bfloat16()
+    b = torch.randn(256, 64, device="cuda").bfloat16()
+    y = gemm_native.native_mx_gemm(a, b, None, None, None, None, None, None)
+    assert y.shape == (256, 256)
+    word.fill_(2)
+    with pytest.raises(_lib.VoyagerB200Error, match="bounded wait"):
+        gemm_native.native_mx_gemm(a, b, None, None, None, None, None, None)

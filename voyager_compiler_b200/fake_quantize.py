@@ -68,6 +68,23 @@ def _require_cuda(x: torch.Tensor, what: str) -> None:
         raise NotImplementedError(f"{what}: dtype {x.dtype} is not supported")
 
 
+def _require_same_device(x: torch.Tensor, what: str, **named: Optional[torch.Tensor]) -> None:
+    """The kernels take raw addresses: a tensor on another device (a module built without
+    ``device=`` and never moved keeps its buffers on the CPU) must be refused on the host, as torch
+    refuses mixed devices, before an address of the wrong memory reaches a launch."""
+    for name, t in named.items():
+        if t is not None and t.device != x.device:
+            raise RuntimeError(f"{what}: Expected all tensors to be on the same device, but {name} is on {t.device} "
+                               f"and the input on {x.device} (move the module with .to(device))")
+
+
+def _threshold_arg(x: torch.Tensor, threshold: torch.Tensor, what: str) -> torch.Tensor:
+    if not isinstance(threshold, torch.Tensor) or threshold.numel() != 1 or threshold.dtype != torch.float32:
+        raise ValueError(f"{what}: the threshold is one fp32 value in a tensor")
+    _require_same_device(x, what, threshold=threshold)
+    return threshold.contiguous()
+
+
 def amax(x: torch.Tensor, ch_axis: Optional[int] = None) -> torch.Tensor:
     """``torch.amax(torch.abs(x))`` (0-d) or, with ``ch_axis``, the maximum over every other axis
     with ``keepdim=True``; in ``x.dtype``."""
@@ -90,6 +107,7 @@ def fake_quantize(x: torch.Tensor, scale: torch.Tensor, qmap: torch.Tensor) -> t
     """``vmap(x / scale, qmap) * scale`` with ``scale`` cast to ``x.dtype`` and broadcast against
     ``x`` (a scalar or a keepdim per-channel tensor)."""
     _require_cuda(x, "fake_quantize")
+    _require_same_device(x, "fake_quantize", scale=scale, qmap=qmap)
     xc = x.contiguous()
     s = scale.to(device=x.device, dtype=x.dtype).contiguous()
     out = torch.empty_like(xc)
@@ -147,6 +165,7 @@ def outlier_split(x: torch.Tensor, threshold: torch.Tensor) -> Tuple[torch.Tenso
     """``(x.masked_fill(x.abs() >= threshold, 0.0), number of outliers)`` in one pass (fake_quantize.py:388-394).
     ``threshold``: one fp32 value on the device; it is rounded to the dtype of ``x`` for the comparison, as torch
     promotes a scalar.  The count is an int64 tensor on the device (no synchronisation)."""
+    threshold = _threshold_arg(x, threshold, "outlier_split")
     _require_cuda(x, "outlier_split")
     xc = x.contiguous()
     out = torch.empty_like(xc)
@@ -159,6 +178,8 @@ def outlier_split(x: torch.Tensor, threshold: torch.Tensor) -> Tuple[torch.Tenso
 
 def outlier_merge(x: torch.Tensor, quantized: torch.Tensor, threshold: torch.Tensor) -> torch.Tensor:
     """``torch.where(x.abs() >= threshold, x, quantized)`` in one pass (fake_quantize.py:428-430)."""
+    threshold = _threshold_arg(x, threshold, "outlier_merge")
+    _require_same_device(x, "outlier_merge", quantized=quantized)
     _require_cuda(x, "outlier_merge")
     xc, qc = x.contiguous(), quantized.contiguous()
     if qc.dtype != xc.dtype or qc.shape != xc.shape:
@@ -313,12 +334,46 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         self._fq_on, self._obs_on = True, self.qscheme is not None
         self._fq_host = torch.tensor([1], dtype=torch.uint8)       # what the autograd functions test
         self._amax_cur = None                                      # fp32 scratch of the reduction
+        self._note_switch_versions()
+
+    # The mirrors follow the buffers: a switch written in place (``m.observer_enabled[0] = 0``) or
+    # loaded from a checkpoint bumps the buffer's version counter, which costs nothing to compare;
+    # only then is the buffer read back (one synchronisation).
+    def _note_switch_versions(self) -> None:
+        self._switch_versions = (self.fake_quant_enabled._version, self.observer_enabled._version,
+                                 id(self.fake_quant_enabled), id(self.observer_enabled))
+
+    def _refresh_switches(self) -> None:
+        now = (self.fake_quant_enabled._version, self.observer_enabled._version,
+               id(self.fake_quant_enabled), id(self.observer_enabled))
+        if now != self._switch_versions:
+            self._fq_on = bool(int(self.fake_quant_enabled[0].item()))
+            self._obs_on = bool(int(self.observer_enabled[0].item()))
+            self._fq_host[0] = 1 if self._fq_on else 0
+            self._switch_versions = now
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        """fake_quantize.py:434-463: ``scale`` and ``amax_history`` start empty / one-element and take
+        their shape on the first forward, so a checkpoint saved after calibration is loaded by resizing
+        them first (``zero_point`` and a learned ``outlier_threshold`` likewise); then the switches'
+        host mirrors are refreshed from what was loaded."""
+        for name in ("scale", "amax_history", "zero_point", "outlier_threshold"):
+            key = prefix + name
+            buf = getattr(self, name, None)
+            if key in state_dict and isinstance(buf, torch.Tensor):
+                buf.resize_(state_dict[key].shape)
+            elif strict and name in ("scale", "amax_history"):
+                missing_keys.append(key)
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+        self._switch_versions = None
+        self._refresh_switches()
 
     # -- switches (torch.ao.quantization.FakeQuantizeBase interface)
     def enable_fake_quant(self, enabled: bool = True) -> None:
         self.fake_quant_enabled[0] = 1 if enabled else 0
         self._fq_on = bool(enabled)
         self._fq_host[0] = 1 if enabled else 0
+        self._note_switch_versions()
 
     def disable_fake_quant(self) -> None:
         self.enable_fake_quant(False)
@@ -326,6 +381,7 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
     def enable_observer(self, enabled: bool = True) -> None:
         self.observer_enabled[0] = 1 if enabled else 0
         self._obs_on = bool(enabled)
+        self._note_switch_versions()
 
     def disable_observer(self) -> None:
         self.enable_observer(False)
@@ -347,6 +403,7 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         enters it; 0 / NaN / Inf maxima keep the previous scale.  Two launches: the reduction and
         one kernel for the whole state update."""
         _require_cuda(x, "FusedAmaxObsFakeQuantize")
+        _require_same_device(x, "FusedAmaxObsFakeQuantize", amax_history=self.amax_history, scale=self.scale)
         xc = x.contiguous()
         if self.is_per_channel:
             a = self.ch_axis % x.ndim
@@ -357,6 +414,15 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         if self.amax_history.numel() == 0:
             self.amax_history.resize_((self.amax_history_len,) + shape).fill_(0.0)
             self.scale.resize_(shape).fill_(1.0)
+        elif tuple(self.amax_history.shape) != (self.amax_history_len,) + shape or tuple(self.scale.shape) != shape:
+            # the state was sized by an earlier input (or a checkpoint): the update kernel indexes it
+            # with this input's channel count, so a different count must stop here, as the broadcast
+            # of upstream's tensor expression does
+            raise RuntimeError(f"FusedAmaxObsFakeQuantize: the observer state has shape {tuple(self.amax_history.shape)} "
+                               f"(scale {tuple(self.scale.shape)}), this input needs {(self.amax_history_len,) + shape}")
+        if not (self.amax_history.is_contiguous() and self.scale.is_contiguous()
+                and self.amax_history.dtype == torch.float32 and self.scale.dtype == torch.float32):
+            raise RuntimeError("FusedAmaxObsFakeQuantize: amax_history and scale must be contiguous fp32 buffers")
         if self._amax_cur is None or self._amax_cur.numel() != ch or self._amax_cur.device != x.device:
             self._amax_cur = torch.empty(ch, dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
@@ -402,6 +468,9 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
             self.outlier_threshold.mul_(self.outlier_ema_decay).add_(threshold * (1.0 - self.outlier_ema_decay))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        self._refresh_switches()
+        _require_same_device(x, "FusedAmaxObsFakeQuantize", qmap=self.qmap, scale=self.scale,
+                             fake_quant_enabled=self.fake_quant_enabled)
         if self.record_histogram:
             exponent_histogram(x.detach(), self.histogram)
         if self.outlier_pct is not None and self._obs_on:

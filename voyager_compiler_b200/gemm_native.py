@@ -11,20 +11,39 @@ from . import _lib
 _status: Dict[str, torch.Tensor] = {}
 
 
+def _device_key(device) -> torch.device:
+    """``cuda`` without an index means the current device: one status word per physical device,
+    whichever way the caller names it."""
+    d = torch.device(device)
+    if d.type != "cuda":
+        raise ValueError(f"the GEMM status word lives on a CUDA device, not on {d}")
+    return torch.device("cuda", torch.cuda.current_device() if d.index is None else d.index)
+
+
 def _status_tensor(device) -> torch.Tensor:
-    key = str(device)
+    key = str(_device_key(device))
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
     return _status[key]
 
 
 def gemm_status(device="cuda") -> int:
     """Non-zero when a bounded wait inside a GEMM kernel on ``device`` ran out since the last
-    call (1 producer, 2 MMA issuer, 3 epilogue).  Synchronises the device and clears the flag."""
-    t = _status_tensor(torch.device(device) if not isinstance(device, torch.device) else device)
+    call (1 producer, 2 MMA issuer, 3 epilogue): the result of that GEMM is then not to be used.
+    Synchronises the device and clears the flag.  The ops do not poll it (that would synchronise
+    every call); callers check it at a point where they synchronise anyway, or set
+    ``VOYAGER_B200_GEMM_CHECK=1`` to have every native GEMM call check it and raise."""
+    t = _status_tensor(device)
     v = int(t.item())
     t.zero_()
     return v
+
+
+def _debug_check(device, what: str) -> None:
+    if os.environ.get("VOYAGER_B200_GEMM_CHECK") == "1":
+        v = gemm_status(device)
+        if v:
+            raise _lib.VoyagerB200Error(f"{what}: a bounded wait inside the GEMM kernel ran out (role {v}); the result is invalid")
 
 
 def _mode() -> str:
@@ -83,6 +102,7 @@ def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
             rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
                                           out.data_ptr(), M, N, K, st.data_ptr(), stream)
             _lib.check(rc, "linear_mx")
+    _debug_check(a.device, "linear_mx")
     return out.reshape(*lead, N)
 
 
@@ -120,6 +140,7 @@ def linear_mx_dynamic(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torc
                                       out.data_ptr(), M, N, K, _status_tensor(x.device).data_ptr(),
                                       torch.cuda.current_stream(x.device).cuda_stream)
         _lib.check(rc, "linear_mx_dynamic")
+    _debug_check(x.device, "linear_mx_dynamic")
     return out.reshape(*lead, N)
 
 
