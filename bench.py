@@ -159,6 +159,260 @@ def parity_sample(tensors, results, qmap, max_tensors=4, max_rows=1024):
     return checked, bad
 
 
+def _timed_flushed(torch, fn, iters, flush):
+    """Median and best milliseconds of ``fn`` (CUDA events on the current stream), three warm-up
+    calls, the L2 overwritten before every timed call."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts), min(ts)
+
+
+def _bits_differ(torch, got, want):
+    """Number of elements whose values differ (NaN == NaN, -0 != +0)."""
+    a, b = got.detach().cpu().contiguous(), want.detach().cpu().contiguous()
+    if a.shape != b.shape or a.dtype != b.dtype:
+        return max(a.numel(), b.numel())
+    it = {1: torch.uint8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[a.element_size()]
+    ai, bi = a.view(it), b.view(it)
+    if a.is_floating_point():
+        both_nan = torch.isnan(a) & torch.isnan(b)
+        return int(((ai != bi) & ~both_nan).sum())
+    return int((ai != bi).sum())
+
+
+def run_extras(dev, iters=20):
+    """The other configurations of the baseline on one GPU, each timed (CUDA events, L2 flushed
+    between iterations) and compared with the CPU oracle on the same tensors: cfg1 (MXINT8 block 32
+    of fp32 [4096, 4096] with outliers), cfg2 (posit8 per output channel over the 54 ResNet-50-shaped
+    weights, one fused launch), cfg4 (per-row 16-level quantile codebooks of a Student-t weight),
+    cfg5 (MX linear 8192 x 11008 x 4096), and the reference's composite of torch operators run on
+    this GPU for the headline sample.  GB/s are algorithmic bytes / time; ``frac`` is of the measured peak."""
+    import numpy as np
+    import torch
+    import voyager_compiler_b200 as vb
+    from voyager_compiler_b200 import codebook, gemm_native, model_quant as mq
+
+    vo = oracle_module()
+    Q = torch.ops.quantized_ops
+    peaks, kind = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {"peak_kind": kind, "l2": "256 MB written between timed iterations"}
+
+    def tab(name):
+        return torch.from_numpy(vb.tables.build_table(name).view(np.int16).copy()).view(torch.bfloat16)
+
+    def hbm(name, fn, nbytes, mismatches=None, **more):
+        med, best = _timed_flushed(torch, fn, iters, flush)
+        gbs = nbytes / med / 1e6
+        out[name] = {"ms": med, "value": gbs, "unit": "GB/s", "best": nbytes / best / 1e6, "algorithmic_bytes": int(nbytes),
+                     "frac": gbs / peaks["hbm_gbs"], **({"mismatches": mismatches} if mismatches is not None else {}), **more}
+
+    # ---- cfg1
+    torch.manual_seed(0)
+    x1 = torch.randn(4096, 4096)
+    x1[torch.rand_like(x1) < 0.001] *= 50
+    q8 = tab("int8")
+    s_ref, c_ref = vo.quantize_mx(x1, q8, (-1,), 32, 127.0, True)
+    d_ref = vo.dequantize(c_ref, s_ref, None, (-1,), 32)
+    xg, q8g = x1.to(dev), q8.to(dev)
+    n = x1.numel()
+    s, c = Q.quantize_mx(xg, q8g, (-1,), 32, 127.0, True)
+    d = Q.dequantize(c, s, None, (-1,), 32)
+    hbm("cfg1_quantize_mx_fp32", lambda: Q.quantize_mx(xg, q8g, (-1,), 32, 127.0, True), n * (4 + 4 + 4 / 32),
+        _bits_differ(torch, s, s_ref) + _bits_differ(torch, c, c_ref))
+    hbm("cfg1_dequantize_fp32", lambda: Q.dequantize(c, s, None, (-1,), 32), n * (4 + 4 + 4 / 32), _bits_differ(torch, d, d_ref))
+    sq = Q.calculate_mx_qparam(xg, (-1,), 32, 127.0, True)
+    hbm("cfg1_calculate_mx_qparam_fp32", lambda: Q.calculate_mx_qparam(xg, (-1,), 32, 127.0, True), n * (4 + 4 / 32),
+        _bits_differ(torch, sq, s_ref))
+    plan1 = mq.MXQuantPlan([xg], q8, 32, 127.0, True, code_bits=8, want_exp=True)
+    (p1,) = plan1.run()
+    torch.cuda.synchronize()
+    bad = _bits_differ(torch, p1.scale, s_ref) + int((p1.codes.cpu().view(torch.int8).float() != c_ref).sum()) + \
+        int((p1.exp_e8.cpu() != torch.log2(s_ref).clamp(-127, 127).to(torch.int8)).sum())
+    hbm("cfg1_packed_int8_codes_e8_exponents", plan1.run, n * (4 + 1 + 4 / 32 + 1 / 32), bad)
+    dp = mq.dequantize_packed(p1, torch.float32, use_exponent=True)
+    hbm("cfg1_dequantize_packed_int8_e8_to_fp32", lambda: mq.dequantize_packed(p1, torch.float32, use_exponent=True),
+        n * (1 + 1 / 32 + 4), int((dp.cpu() != d_ref).sum()))
+    plan1.close()
+    del xg, s, c, d, sq, p1, dp, plan1
+
+    # ---- cfg2
+    torch.manual_seed(1)
+    rn = []
+    for shp in resnet50_weight_shapes():
+        t = torch.empty(shp)
+        torch.nn.init.kaiming_normal_(t, mode="fan_in")
+        rn.append(t)
+    qp = tab("posit8_1")
+    rg = [t.to(dev) for t in rn]
+    n2 = sum(t.numel() for t in rn)
+    plan2 = mq.ChannelQuantPlan(rg, qp, 4096.0, want_codes=True, want_dequant=True, want_values=True)
+    res2 = plan2.run()
+    torch.cuda.synchronize()
+    bad = 0
+    for w, r in zip(rn, res2):
+        sc = vo.channel_scale(w, 4096.0)
+        qv = vo.quantize(w, sc, None, None, None, qp)
+        bad += _bits_differ(torch, r.scale, sc) + _bits_differ(torch, r.values, qv) + _bits_differ(torch, r.dequant, vo.dequantize(qv, sc))
+        ok = ~torch.isnan(qv)
+        bad += int((r.levels[r.codes.cpu().long().clamp(max=r.levels.numel() - 1)][ok] != qv.float()[ok]).sum())
+    del plan2, res2
+    plan2 = mq.ChannelQuantPlan(rg, qp, 4096.0, want_codes=True, want_dequant=True)
+    hbm("cfg2_posit8_per_channel_54_tensors_codes_and_dequant", plan2.run, n2 * 9, bad, launches_per_pass=1)
+    plan2b = mq.ChannelQuantPlan(rg, qp, 4096.0, want_values=True, want_dequant=False)
+    hbm("cfg2_posit8_per_channel_54_tensors_values", plan2b.run, n2 * 8)
+    del plan2, plan2b, rg, rn
+
+    # ---- cfg4
+    torch.manual_seed(3)
+    w4 = torch.distributions.StudentT(5.0).sample((11008, 4096)) * 0.02
+    w4g = w4.to(dev)
+    lv = codebook.row_quantile_levels(w4g, 16)
+    rows = 256
+    qq = (2 * torch.arange(16, dtype=torch.float32) + 1) / 32
+    lv_ref = torch.quantile(w4[:rows], qq, dim=-1).t().contiguous()
+    bad_fit = int((lv[:rows].cpu() != lv_ref).sum())
+    n4 = w4.numel()
+    hbm("cfg4_row_quantile_fit16", lambda: codebook.row_quantile_levels(w4g, 16), n4 * 4 + lv.numel() * 4, bad_fit,
+        rows_checked=rows)
+    for rule, nm in ((True, "reference_rule"), (False, "fp32_rule")):
+        idx, val = codebook.row_codebook_quantize(w4g, lv, reference_rule=rule)
+        i_ref, v_ref = vo.row_codebook(w4[:rows], lv[:rows].cpu(), reference_rule=rule)
+        bad = int((idx[:rows].cpu() != i_ref).sum()) + _bits_differ(torch, val[:rows], v_ref)
+        hbm(f"cfg4_row_codebook16_search_{nm}", lambda: codebook.row_codebook_quantize(w4g, lv, reference_rule=rule),
+            n4 * 9 + lv.numel() * 4, bad, rows_checked=rows)
+    del w4g, w4, idx, val, lv
+
+    # ---- cfg5
+    torch.manual_seed(4)
+    M, N, K = 8192, 11008, 4096
+    x5 = torch.randn(M, K).bfloat16()
+    w5 = (torch.randn(N, K) * 0.02).bfloat16()
+    xg, wg = x5.to(dev), w5.to(dev)
+    ws, wq = Q.quantize_mx(wg, q8g, (-1,), 32, 127.0, True)
+    xs, xq = Q.quantize_mx(xg, q8g, (-1,), 32, 127.0, True)
+    xs_ref, xq_ref = vo.quantize_mx(x5[:512], q8, (-1,), 32, 127.0, True)
+    bad_q = _bits_differ(torch, xs[:512], xs_ref) + _bits_differ(torch, xq[:512], xq_ref)
+    y_ref = vo.linear_mx(xq.cpu(), wq.cpu(), None, input_scale=xs.cpu(), weight_scale=ws.cpu(), block_size=32).double()
+    flops = 2.0 * M * N * K
+
+    def tc(name, fn, **more):
+        y = fn()
+        torch.cuda.synchronize()
+        rel = float(((y.cpu().double() - y_ref).norm() / y_ref.norm()).item())
+        med, best = _timed_flushed(torch, fn, iters, flush)
+        out[name] = {"ms": med, "value": flops / med / 1e9, "unit": "TFLOP/s", "best": flops / best / 1e9, "flops": flops,
+                     "frac": flops / med / 1e9 / peaks["bf16_tflops"], "frac_of_sustained": flops / med / 1e9 / peaks["bf16_tflops_sustained"],
+                     "rel_frobenius_error_vs_oracle": rel, "tolerance": 1e-2, "within_tolerance": rel <= 1e-2, **more}
+
+    tc("cfg5_linear_mx", lambda: Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32))
+    os.environ["VOYAGER_B200_GEMM"] = "fused"
+    tc("cfg5_linear_mx_fused_staging", lambda: Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32))
+    os.environ.pop("VOYAGER_B200_GEMM", None)
+    tc("cfg5_quantize_mx_plus_linear_mx", lambda: Q.linear_mx(Q.quantize_mx(xg, q8g, (-1,), 32, 127.0, True)[1], wq, None,
+                                                              input_scale=xs, weight_scale=ws, block_size=32),
+       activation_quantize_mismatches=bad_q, rows_checked=512)
+    tc("cfg5_linear_mx_dynamic_one_pass_activation",
+       lambda: gemm_native.linear_mx_dynamic(xg, wq, None, qmap=q8g, weight_scale=ws, block_size=32, quant_max=127.0))
+    out["cfg5_status_ok"] = gemm_native.gemm_status(dev) == 0
+    del xg, wg, xq, wq, xs, ws
+
+    # ---- the reference's composite of torch operators on this GPU (one layer of the headline workload)
+    nf4 = vo.value_table("nf4")
+    idx_tab = vo.index_table(nf4)[0].to(dev)
+    sample = [make_tensor(i, shp, dev) for i, shp in enumerate(LAYER)]
+    ns = sum(t.numel() for t in sample)
+
+    def composite():
+        for w in sample:
+            sc = vo.mx_scale(w, (-1,), BLOCK, 1.0, False)
+            vo.quantize(w, sc, None, (-1,), BLOCK, idx_tab)
+    med, best = _timed_flushed(torch, composite, 5, flush)
+    out["composite_on_gpu"] = {"ms": med, "value": ns * BYTES_PER_ELEM / med / 1e6, "unit": "GB/s",
+                               "sample": f"one layer: {len(sample)} of 225 tensors, {ns} elements",
+                               "what": "calculate_mx_qparam + quantize as chains of torch operators on CUDA tensors (the device-agnostic upstream formulation)"}
+    return out
+
+
+def run_extras_multi(dev, world, rank, iters=10):
+    """cfg5 sharded by output columns over the ranks (every rank calls this): the local GEMM alone,
+    GEMM + NCCL all-gather, and the GEMM whose epilogue stores its columns into every rank's copy of
+    Y over NVLink.  Times are CUDA events, max over ranks; results are compared with the one-GPU op."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import voyager_compiler_b200 as vb
+    from voyager_compiler_b200 import parallel as par
+
+    Q = torch.ops.quantized_ops
+    peaks, _ = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    M, N, K = 8192, 11008, 4096
+    g = torch.Generator(device=dev); g.manual_seed(4)
+    x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    q8 = torch.from_numpy(vb.tables.build_table("int8").view(np.int16).copy()).view(torch.bfloat16).to(dev)
+    ws, wq = Q.quantize_mx(w, q8, (-1,), 32, 127.0, True)
+    xs, xq = Q.quantize_mx(x, q8, (-1,), 32, 127.0, True)
+    wq_r, ws_r = par.shard_weight(wq, ws, rank, world)
+    y1 = Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32)
+    flops = 2.0 * M * N * K
+    out = {"shards": par.column_shards(N, world)}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            dist.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts.append(float(t.item()))
+        return statistics.median(ts)
+
+    def entry(ms, same=None):
+        e = {"ms": ms, "value": flops / ms / 1e9, "unit": "TFLOP/s (whole job)", "frac_of_n_gpu_peak": flops / ms / 1e9 / (peaks["bf16_tflops"] * world)}
+        if same is not None:
+            e["equals_single_gpu_result"] = same
+        return e
+
+    out["cfg5_single_gpu_linear_mx"] = entry(timed(lambda: Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32)))
+    out["cfg5_column_shard_gemm_only"] = entry(timed(lambda: Q.linear_mx(xq, wq_r, None, input_scale=xs, weight_scale=ws_r, block_size=32)))
+    y = par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32)
+    out["cfg5_column_parallel_nccl_all_gather"] = entry(timed(lambda: par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32)),
+                                                        bool(torch.equal(y, y1)))
+    ok = torch.ones(1, device=dev)
+    p2p = None
+    try:
+        p2p = par.P2PColumnParallelLinearMX(wq_r, ws_r, N, 32, M)
+    except Exception as e:  # noqa: BLE001  (peer-mapped memory may be unavailable on a given box)
+        ok.zero_()
+        out["cfg5_column_parallel_peer_store_epilogue"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)         # every rank takes the same branch
+    if bool(ok.item()):
+        y2 = p2p(xq, xs)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(y2, y1))
+        e = entry(timed(lambda: p2p(xq, xs)), same)
+        e["status_ok"] = p2p.status() == 0
+        out["cfg5_column_parallel_peer_store_epilogue"] = e
+    elif "cfg5_column_parallel_peer_store_epilogue" not in out:
+        out["cfg5_column_parallel_peer_store_epilogue"] = {"unavailable": "another rank could not map peer memory"}
+    return out
+
+
 def run_reference(args):
     """CPU arm: rank 0 alone times the oracle port on a bounded sample per step."""
     import torch
@@ -337,6 +591,22 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": n * BYTES_PER_ELEM / secs / 1e9, "unit": "GB/s", "cores": cores,
                                     "kind": "port", "seconds": secs,
                                     "sample": f"all {len(host)} tensors of the workload once ({n} elements)"}
+    extra = None
+    if not args.no_extras:
+        if world > 1:
+            extra = run_extras_multi(dev, world, rank)
+        elif rank == 0:
+            del host, host_out
+            torch.cuda.empty_cache()
+            try:
+                extra = run_extras(dev)
+            except Exception as e:  # noqa: BLE001  (the headline line is still to be printed)
+                import traceback
+                traceback.print_exc()
+                extra = {"error": f"{type(e).__name__}: {e}"[:300]}
+    if rank == 0:
+        if extra is not None:
+            line["extra"] = extra
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -706,6 +976,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="fewer than 32: reduced model for profiler captures")
     ap.add_argument("--kernel-only", action="store_true", help="device-timed part only (profiler captures)")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only (skip the other configurations)")
     ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise"],
                     help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
     ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
