@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define VQ_ABI_VERSION 1
+#define VQ_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define VQ_API __attribute__((visibility("default")))
@@ -72,6 +72,11 @@ typedef struct vq_table {
                                   by multiplying with a reciprocal without scanning for tiny elements.
                                   0 is always safe. */
     uint8_t reserved[5];
+    const float* levels2;      /* optional, with lut8: device pointer, 512 fp32 entries: the output value of packed
+                                  code c for an input pattern without the sign bit at [c], with it at [256 + c].
+                                  Only set when lut16[p] == levels2[lut8[p] + 256 * (p >> 15)] holds for every
+                                  pattern p (the host checks it): the value then follows from the code and the
+                                  input's sign, and kernels need the 64 KB code table alone in shared memory. */
 } vq_table;
 
 /* Where the scale (and zero point) of element i lives (upstream `expand`,
@@ -212,6 +217,22 @@ VQ_API void vq_mx_plan_destroy(vq_mx_plan* plan);
  * (src/voyager_compiler/ops/quantized.py:330-333, 404-406). */
 VQ_API int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int64_t M, int64_t N, int64_t K,
                            int32_t* status, void* stream);
+
+/* out[b, n, k] = bf16(in[b, k, n] * scale[b, k / block, n]) for bf16 tensors: `in` [batch, K, N], `scale`
+ * [batch, scale_rows, N] with scale_rows >= ceil(K / block) (NULL: a plain transposition), `out` [batch, N, K].
+ * K, N and block even.  Decodes the right operand of `matmul_mx` (blocks along dim -2) or a "ck" linear
+ * weight, src/voyager_compiler/ops/quantized.py:330-333, 389-406, straight into the K-major order the GEMM reads. */
+VQ_API int vq_dequantize_transpose(const void* in, const void* scale, int64_t batch, int64_t K, int64_t N, int64_t block,
+                                   int64_t scale_rows, void* out, void* stream);
+
+/* `batch` independent products Y[b] = A[b] @ B[b]^T with A [batch, M, K], B [batch, N, K] and Y [batch, M, N],
+ * all contiguous bf16; a_shared / b_shared != 0: that operand is a single [M, K] / [N, K] matrix used by every
+ * batch.  One persistent launch walks the output tiles of all batches.  This is the contraction
+ * `aten.matmul` performs inside matmul_mx on batched (attention) operands,
+ * src/voyager_compiler/ops/quantized.py:404-406, once the right operand is in [N, K] order
+ * (vq_dequantize_transpose). */
+VQ_API int vq_gemm_bf16_tn_batched(const void* A, const void* B, void* Y, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                   int a_shared, int b_shared, int32_t* status, void* stream);
 
 /* The same GEMM writing its [M,N] result into columns [col_offset, col_offset+N) of EVERY buffer in
  * Ys (n_outputs <= 8 device pointers, rows ldy elements apart): a rank of a column-sharded linear
@@ -403,6 +424,24 @@ VQ_API size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, 
  * below 2^22 elements. */
 VQ_API int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dtype, double quant_max,
                                      const vq_table* table, void* workspace, size_t workspace_bytes, void* stream);
+
+/* vq_channel_quantize_multi prepared once and run many times (weights re-quantized every calibration or
+ * training step): create checks the arguments, cuts the tensors into batches, picks the kernel and puts
+ * the descriptors into `workspace` (the stream is synchronised once); run is then a single kernel launch
+ * on any stream of the same device, with no host work and no copy.  Tensors are read and written where the
+ * items pointed at creation time; the table and the workspace must stay alive and untouched for the life of
+ * the plan.  Same upstream counterpart as vq_channel_quantize_multi. */
+typedef struct vq_channel_plan vq_channel_plan;
+VQ_API int vq_channel_plan_create(const vq_channel_item* items, int n_items, int dtype, double quant_max,
+                                  const vq_table* table, void* workspace, size_t workspace_bytes, void* stream,
+                                  vq_channel_plan** plan_out);
+VQ_API int vq_channel_plan_run(const vq_channel_plan* plan, void* stream);
+VQ_API void vq_channel_plan_destroy(vq_channel_plan* plan);
+
+/* Non-zero when a bounded wait inside the pipelined per-channel kernel ran out on the current device since
+ * the last call (21: the producer waited for a free stage, 22: a consumer group waited for its batch);
+ * the outputs of that launch are then incomplete.  Synchronises the device; clears the word. */
+VQ_API int vq_channel_status(void);
 
 /* out[i] = levels[code[i]] * scale[i / block] in `dtype` (one rounding), from the packed views that
  * vq_quantize_mx / vq_quantize_mx_multi write: 8-bit codes (one per byte) or 4-bit codes (two per

@@ -188,3 +188,97 @@ def test_status_word_is_one_per_device_however_the_device_is_named(monkeypatch):
     word.fill_(2)
     with pytest.raises(_lib.VoyagerB200Error, match="bounded wait"):
         gemm_native.native_mx_gemm(a, b, None, None, None, None, None, None)
+
+
+def _no_vendor_gemm(monkeypatch):
+    """The contraction must run on this library's kernel: any route into the vendor GEMM fails the test."""
+    def boom(*a, **k):
+        raise AssertionError("the vendor GEMM was called")
+    monkeypatch.setattr(torch, "matmul", boom)
+    monkeypatch.setattr(torch.nn.functional, "linear", boom)
+
+
+def _mx_pair(a_shape, b_shape, seed, b_axis):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(*a_shape, generator=g).to(torch.bfloat16)
+    b = (torch.randn(*b_shape, generator=g) * 0.05).to(torch.bfloat16)
+    q = golden_table("int8")
+    sa, qa = vo.quantize_mx(a, q, (-1,), 32, 127.0, True)
+    sb, qb = vo.quantize_mx(b, q, (b_axis,), 32, 127.0, True)
+    return qa, sa, qb, sb
+
+
+@pytest.mark.parametrize("a_shape,b_shape", [
+    ((2, 3, 256, 64), (2, 3, 64, 256)),        # attention scores: Q [B,H,S,D] x K^T [B,H,D,S]
+    ((2, 3, 256, 256), (2, 3, 256, 64)),       # attention output: P [B,H,S,S] x V [B,H,S,D]
+    ((4, 1, 128), (4, 128, 320)),              # decode step: one query row per batch (one-CTA tile)
+    ((5, 200, 96), (5, 96, 130)),              # ragged: tiles reach into the next batch and are masked
+    ((3, 300, 64), (64, 512)),                 # right operand shared by all batches
+    ((300, 64), (64, 512)),
+])
+def test_matmul_mx_runs_on_the_native_gemm(a_shape, b_shape, monkeypatch):
+    """``matmul_mx`` with the right operand in [.., K, N] order and block scales along K (ops/quantized.py:363-432):
+    decode + transpose kernel, then the tcgen05 GEMM over all batches in one launch."""
+    qa, sa, qb, sb = _mx_pair(a_shape, b_shape, sum(a_shape) + sum(b_shape), -2)
+    want = vo.matmul_mx(qa, qb, input_scale=sa, weight_scale=sb, block_size=32)
+    before = _lib.launch_count()
+    _no_vendor_gemm(monkeypatch)
+    got = Q.matmul_mx(qa.cuda(), qb.cuda(), input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32)
+    torch.cuda.synchronize()
+    monkeypatch.undo()
+    assert _lib.launch_count() >= before + 3          # decode of a, decode + transpose of b, the GEMM
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    assert _rel(got, want) <= 1e-2
+
+
+def test_matmul_mx_kc_layout_batched_and_plain_operands(monkeypatch):
+    """Batched right operand already in [.., N, K] order (weight_layout="kc"), and operands without scales."""
+    qa, sa, qb, sb = _mx_pair((2, 2, 160, 64), (2, 2, 288, 64), 5, -1)
+    want = vo.matmul_mx(qa, qb, input_scale=sa, weight_scale=sb, block_size=32, weight_layout="kc")
+    g = torch.Generator().manual_seed(6)
+    a = torch.randn(3, 40, 72, generator=g).bfloat16()
+    b = torch.randn(3, 72, 50, generator=g).bfloat16()
+    want2 = vo.matmul_mx(a, b)
+    _no_vendor_gemm(monkeypatch)
+    got = Q.matmul_mx(qa.cuda(), qb.cuda(), input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32, weight_layout="kc")
+    got2 = Q.matmul_mx(a.cuda(), b.cuda())
+    torch.cuda.synchronize()
+    monkeypatch.undo()
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.shape == want.shape and _rel(got, want) <= 1e-2
+    assert got2.shape == want2.shape and _rel(got2, want2) <= 1e-2
+
+
+def test_linear_mx_ck_weight_runs_on_the_native_gemm(monkeypatch):
+    """``linear_mx(..., weight_layout="ck")``: the weight is stored [K, N] with block scales along K
+    (ops/quantized.py:330-333); bias and a 3-D activation included; a codebook on the weight."""
+    qa, sa, qb, sb = _mx_pair((4, 75, 128), (128, 384), 21, -2)
+    bias = torch.randn(384).to(torch.bfloat16)
+    want = vo.linear_mx(qa, qb, bias, input_scale=sa, weight_scale=sb, block_size=32, weight_layout="ck")
+    code = torch.linspace(-1, 1, 16).to(torch.bfloat16)
+    idx = torch.randint(0, 16, (128, 384)).to(torch.bfloat16)
+    want_c = vo.linear_mx(qa, idx, None, input_scale=sa, weight_scale=sb, block_size=32, weight_code=code, weight_layout="ck")
+    _no_vendor_gemm(monkeypatch)
+    dev = [t.cuda() for t in (qa, sa, qb, sb, bias, idx, code)]
+    got = Q.linear_mx(dev[0], dev[2], dev[4], input_scale=dev[1], weight_scale=dev[3], block_size=32, weight_layout="ck")
+    again = Q.linear_mx(dev[0], dev[2], dev[4], input_scale=dev[1], weight_scale=dev[3], block_size=32, weight_layout="ck")
+    got_c = Q.linear_mx(dev[0], dev[5], None, input_scale=dev[1], weight_scale=dev[3], block_size=32, weight_code=dev[6],
+                        weight_layout="ck")
+    torch.cuda.synchronize()
+    monkeypatch.undo()
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.shape == want.shape == (4, 75, 384) and _rel(got, want) <= 1e-2
+    assert torch.equal(got, again)                    # second call: the decoded weight comes from the cache
+    assert _rel(got_c, want_c) <= 1e-2
+
+
+def test_dequantize_transpose_equals_dequantize_then_transpose():
+    g = torch.Generator().manual_seed(8)
+    for batch, K, N in ((1, 64, 64), (3, 96, 130), (2, 200, 66), (1, 4096, 1024)):
+        x = torch.randn(batch, K, N, generator=g).bfloat16().cuda()
+        s = (torch.rand(batch, -(-K // 32), N, generator=g) + 0.5).bfloat16().cuda()
+        want = Q.dequantize(x, s, None, (-2,), 32).transpose(-1, -2).contiguous()
+        got = gemm_native._decode_transposed("test", x, None, s, 32)
+        assert torch.equal(got, want), (batch, K, N)
+        assert torch.equal(gemm_native._decode_transposed("test", x, None, None, None), x.transpose(-1, -2).contiguous())

@@ -304,3 +304,63 @@ def test_plan_rejects_what_it_cannot_read_in_place():
         mq.MXQuantPlan([x[:, :100].contiguous()], golden_table("nf4"), 64, 1.0)
     with pytest.raises(ValueError):
         mq.MXQuantPlan([], golden_table("nf4"), 64, 1.0)
+
+
+def _check_channel_results(ws, got, tab, qmax, scales=None):
+    for k, (w, r) in enumerate(zip(ws, got)):
+        s_ref = vo.channel_scale(w, qmax) if scales is None else scales[k].to(w.dtype)
+        q_ref = vo.quantize(w, s_ref, None, None, None, tab)
+        assert same_bits(r.scale, s_ref)[0], k
+        assert same_bits(r.values, q_ref)[0], k
+        assert same_bits(r.dequant, vo.dequantize(q_ref, s_ref))[0], k
+        ok = ~torch.isnan(q_ref.float())
+        lv = r.levels[r.codes.cpu().long().clamp(max=r.levels.numel() - 1)]
+        assert torch.equal(lv[ok], q_ref.float()[ok]), k
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["pipe", "sweep"])
+@pytest.mark.parametrize("dtype,table,qmax", [(torch.float32, "posit8_1", 4096.0), (torch.bfloat16, "posit8_1", 4096.0),
+                                               (torch.float32, "int8", 127.0), (torch.bfloat16, "fp8_e4m3", 448.0)])
+def test_per_channel_kernels_on_awkward_shapes(kernel, dtype, table, qmax, monkeypatch):
+    """The bulk-copy pipeline and the two-sweep kernel on the same awkward set: channel lengths that
+    are no multiple of 4 (vectors straddle channels), many short channels per batch, a channel as long
+    as a batch, a tensor that starts off a 16-byte boundary, tiny and huge magnitudes (the checked
+    division), NaN / Inf / all-zero channels; more than 2^21 elements in total so the staged tables
+    are used.  The plan runs twice (second run on changed data)."""
+    monkeypatch.setenv("VOYAGER_B200_CHANNEL_KERNEL", kernel)
+    g = torch.Generator().manual_seed(17)
+    shapes = [(64, 3, 7, 7), (300, 37), (1024, 64), (96, 7168 // 4, 4), (40, 2304), (2000, 1000), (5, 6), (128, 3, 3, 3)]
+    ws = [(torch.randn(s, generator=g) * 0.05).to(dtype) for s in shapes]
+    ws[1][3] = 0
+    ws[2][5, 7] = float("nan")
+    ws[2][6, 1] = float("inf")
+    ws[4][2] *= 1e-30                               # quotients of tiny values: the corrected reciprocal is not used
+    ws[4][3] *= 1e20
+    ws[5][7, :5] = torch.tensor([1e-38, -1e-39, 3e-41, 0.0, -0.0]).to(dtype)
+    tab = golden_table(table)
+    dev = [w.cuda() for w in ws]
+    pad = torch.zeros(40 * 2304 + 1, dtype=dtype, device="cuda")          # tensor 4 one element off the allocation start
+    pad[1:].copy_(dev[4].reshape(-1))
+    dev[4] = pad[1:].view(40, 2304)
+    plan = mq.ChannelQuantPlan(dev, tab, qmax, want_values=True, want_codes=True, want_dequant=True)
+    _check_channel_results(ws, plan.run(), tab, qmax)
+    ws2 = [(w.float() * 1.3).to(dtype) for w in ws]
+    for d, w in zip(dev, ws2):
+        d.copy_(w)
+    _check_channel_results(ws2, plan.run(), tab, qmax)
+    assert _status() == 0
+    # caller-supplied scales (observer state): the checked division, batch by batch
+    scales = [(torch.rand(w.shape[0], *([1] * (w.ndim - 1)), generator=g) + 0.1) / 50 for w in ws2]
+    got = mq.quantize_tensors_per_channel(dev, tab, qmax, scales=[s.cuda() for s in scales], want_values=True, want_codes=True)
+    _check_channel_results(ws2, got, tab, qmax, scales)
+    # a channel longer than a batch of the pipeline: the call falls back to the two-sweep kernel
+    big = (torch.randn(300, 9000, generator=g) * 0.05).to(dtype)
+    (r,) = mq.quantize_tensors_per_channel([big.cuda()], tab, qmax, want_values=True, want_codes=True)
+    _check_channel_results([big], [r], tab, qmax)
+    plan.close()
+
+
+def _status():
+    from voyager_compiler_b200 import _lib
+    return _lib.lib.vq_channel_status()

@@ -10,7 +10,7 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libvoyager_b200.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 VQ_F32, VQ_BF16 = 0, 1
 TABLE_NONE, TABLE_LUT16, TABLE_INT, TABLE_RUNS = 0, 1, 2, 3
@@ -26,6 +26,7 @@ class VqTable(C.Structure):
         ("nan_val", C.c_uint16), ("pinf_val", C.c_uint16), ("ninf_val", C.c_uint16),
         ("nan_code", C.c_uint8), ("pinf_code", C.c_uint8), ("ninf_code", C.c_uint8),
         ("nan_uniform", C.c_uint8), ("flat_tiny", C.c_uint8), ("reserved", C.c_uint8 * 5),
+        ("levels2", C.c_void_p),
     ]
 
 
@@ -104,6 +105,8 @@ def _load():
                             vp, i64, i64, i64, i64, i64, vp, i64, vp],
         "vq_dequantize_packed": [vp, ci, vp, ci, vp, vp, i64, i64, vp, ci, vp],
         "vq_gemm_bf16_tn": [vp, vp, vp, vp, i64, i64, i64, vp, vp],
+        "vq_gemm_bf16_tn_batched": [vp, vp, vp, i64, i64, i64, i64, ci, ci, vp, vp],
+        "vq_dequantize_transpose": [vp, vp, i64, i64, i64, i64, i64, vp, vp],
         "vq_gemm_bf16_tn_scatter": [vp, vp, vp, C.POINTER(C.c_void_p), ci, i64, i64, i64, i64, i64, vp, vp],
         "vq_linear_mx": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],
         "vq_linear_mx_packed": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],
@@ -113,7 +116,12 @@ def _load():
         "vq_mx_plan_create": [C.POINTER(VqMxItem), ci, ci, i64, dbl, ci, E, T, T, ci, vp, C.c_size_t, vp,
                               C.POINTER(C.c_void_p)],
         "vq_mx_plan_run": [vp, vp],
+        "vq_channel_plan_create": [C.POINTER(VqChannelItem), ci, ci, dbl, T, vp, C.c_size_t, vp, C.POINTER(C.c_void_p)],
+        "vq_channel_plan_run": [vp, vp],
+        "vq_channel_status": [],
     }
+    lib.vq_channel_plan_destroy.argtypes = [vp]
+    lib.vq_channel_plan_destroy.restype = None
     lib.vq_mx_plan_destroy.argtypes = [vp]
     lib.vq_mx_plan_destroy.restype = None
     lib.vq_quantize_mx_multi_static_max_items.argtypes = []

@@ -10,9 +10,16 @@
 // values * scale (`dequantize`, ops/quantized.py:182-227).  Upstream runs amax, divide, expand,
 // quantize and dequantize as separate full passes per tensor.
 // HBM bound: sizeof(T) read per element + the requested outputs.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
 #include "vq_mx_body.cuh"
 #include "vq_mx_fast.cuh"
 #include "vq_divide.cuh"
+#include "vq_tc.cuh"
 
 namespace {
 
@@ -78,7 +85,8 @@ __device__ __forceinline__ void quantize_one(const TableDev& tab, const TableRes
 struct ChanBatch {
     int item, c0, nc;
     FastDiv len;            // flat index -> channel
-    int pad[2];
+    int vec;                // pipelined kernel: the batch starts and ends on 16-byte boundaries of aligned tensors
+    int pad;
 };
 constexpr int kBatchElems = 16384;
 constexpr int kGroupThreads = 256;
@@ -290,35 +298,423 @@ __global__ void __launch_bounds__(1024) channel_quant_kernel(const BatchParams p
     }
 }
 
-// batches of one item
-inline int64_t batches_of(const vq_channel_item& it) {
-    if (it.channels <= 0) return 0;
-    int64_t per = kBatchElems / it.length;
+// ---------------------------------------------------------------------------------------------
+constexpr int kSmemItems = 96;         // tensor descriptors a CTA of the pipelined kernel keeps in shared memory
+constexpr int kSmemBatches = 64;       // batch descriptors it keeps there
+
+// 16 bytes of a batch held in registers between the |x| reduction and the quantization
+template <typename T>
+struct RawVec;
+template <>
+struct RawVec<float> {
+    float4 r;
+    __device__ __forceinline__ void load(const float* p) { r = __ldcs(reinterpret_cast<const float4*>(p)); }
+    __device__ __forceinline__ void load_shared(const float* p) { r = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void zero() { r = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void get(float* v) const { v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w; }
+    __device__ __forceinline__ void set(int k, float f) { (&r.x)[k] = f; }
+};
+template <>
+struct RawVec<bf16_t> {
+    uint2 r;
+    __device__ __forceinline__ void load(const bf16_t* p) { r = __ldcs(reinterpret_cast<const uint2*>(p)); }
+    __device__ __forceinline__ void load_shared(const bf16_t* p) { r = *reinterpret_cast<const uint2*>(p); }
+    __device__ __forceinline__ void zero() { r = make_uint2(0u, 0u); }
+    __device__ __forceinline__ void get(float* v) const {
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+    }
+    __device__ __forceinline__ void set(int k, float f) {
+        uint32_t& w = (k < 2) ? r.x : r.y;
+        const uint32_t h = __float_as_uint(f) >> 16;
+        w = (k & 1) ? ((w & 0x0000FFFFu) | (h << 16)) : ((w & 0xFFFF0000u) | h);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Pipelined variant: batches arrive in shared memory by asynchronous bulk copies.
+//
+// Warp 0 is the producer: one thread walks this CTA's batches and, for each, waits for a free
+// stage of a PIPE_STAGES-deep ring and issues ONE cp.async.bulk of the whole batch (up to 32 KB)
+// whose completion is counted on the stage's mbarrier.  PIPE_GROUPS consumer groups of PIPE_GT threads
+// take the batches in turn: wait for the stage, read it into registers (8 x 16 bytes per thread),
+// release the stage at once, reduce |x| per channel, derive the scales, quantize from registers
+// and store.  Global loads therefore never stall a compute warp and up to PIPE_STAGES batches
+// per SM are in flight whatever the consumers are doing.
+//
+// The table costs 64 KB + 2 KB of shared memory instead of 192 KB: the packed code comes from the
+// code table, the value from `levels2[code + 256 * sign of the input]` (see vq_table), which the
+// host only provides when that is the same function as the full value table.  INT tables use
+// arithmetic and no table at all.  Batches that bulk copies cannot take (channel length not a
+// multiple of 4 elements / 16 bytes, unaligned tensors) are read by the consumers themselves.
+// Every wait is bounded; a wait that runs out sets g_channel_status and winds the CTA down.
+constexpr int PIPE_GROUPS = 3;
+constexpr int PIPE_GT = 224;                                   // threads per consumer group: 3 x 7 + 1 warps leave 80 registers per thread
+constexpr int PIPE_STAGES = 4;
+constexpr int PIPE_VECS = 8;                                   // 16-byte vectors per consumer thread
+constexpr int PIPE_BATCH = PIPE_GT * PIPE_VECS * 4;            // 7168 elements
+constexpr int PIPE_THREADS = 32 + PIPE_GROUPS * PIPE_GT;
+constexpr long long PIPE_WAIT = 4000000000ll;                  // ~2 s of SM clocks
+
+__device__ int g_channel_status = 0;
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+struct PipeShared {
+    ChanShared ch[PIPE_GROUPS];
+    int ok[PIPE_GROUPS];
+};
+
+template <typename T, int TK>
+__global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const BatchParams p, const int n_items) {
+    extern __shared__ uint4 smem[];
+    // layout: [code table 64 KB (TK_LUT)] [levels2 2 KB (TK_LUT)] [ring] [PipeShared] [items] [barriers]
+    constexpr uint32_t TAB_BYTES = TK == TK_LUT ? 65536u + 2048u : 0u;
+    constexpr uint32_t STAGE_BYTES = PIPE_BATCH * sizeof(T);
+    uint8_t* base = reinterpret_cast<uint8_t*>(smem);
+    const uint8_t* s_codes = base;
+    const float* s_lv2 = reinterpret_cast<const float*>(base + 65536);
+    uint8_t* ring = base + TAB_BYTES;
+    PipeShared& ps = *reinterpret_cast<PipeShared*>(ring + PIPE_STAGES * STAGE_BYTES);
+    vq_channel_item* sitems = reinterpret_cast<vq_channel_item*>(reinterpret_cast<uint8_t*>(&ps) + ((sizeof(PipeShared) + 15) / 16) * 16);
+    ChanBatch* sbatches = reinterpret_cast<ChanBatch*>(sitems + kSmemItems);       // this CTA's first kSmemBatches batches
+    const uint32_t bar0 = tc::smem_u32(sbatches + kSmemBatches);
+    const uint32_t FULL0 = bar0, EMPTY0 = bar0 + 8u * PIPE_STAGES;
+    // Prologue: barriers first, then the tables are fetched by two bulk copies (no thread waits for
+    // them until its first lookup) while all threads gather the descriptors; the producer starts
+    // loading batches as soon as the descriptors are in place.
+    const uint32_t TABLE_BAR = EMPTY0 + 8u * PIPE_STAGES;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PIPE_STAGES; ++s) {
+            tc::mbar_init(FULL0 + 8u * s, 1);
+            tc::mbar_init(EMPTY0 + 8u * s, 1);
+        }
+        tc::mbar_init(TABLE_BAR, 1);
+        tc::fence_barrier_init();
+        if (TK == TK_LUT) {
+            tc::mbar_expect_tx(TABLE_BAR, 65536u + 2048u);
+            bulk_load(tc::smem_u32(base), p.common.tab.lut8, 65536u, TABLE_BAR);
+            bulk_load(tc::smem_u32(base + 65536), p.common.tab.levels2, 2048u, TABLE_BAR);
+        }
+    }
+    const bool items_staged = n_items <= kSmemItems;
+    if (items_staged) {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.items);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(sitems);
+        for (int i = threadIdx.x; i < n_items * (int)(sizeof(vq_channel_item) / 4); i += blockDim.x) dst[i] = src[i];
+    }
+    {
+        // descriptors of the batches this CTA will walk (batch blockIdx.x + i * gridDim.x at slot i)
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.batches);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(sbatches);
+        constexpr int W = sizeof(ChanBatch) / 4;
+        for (int t = threadIdx.x; t < kSmemBatches * W; t += blockDim.x) {
+            const int64_t b = blockIdx.x + (int64_t)(t / W) * gridDim.x;
+            if (b < p.n_batches) dst[t] = __ldg(src + b * W + t % W);
+        }
+    }
+    __syncthreads();
+    const float lo = p.common.tab.lo, hi = p.common.tab.hi;
+    const bool lo_is_zero = lo == 0.0f;
+
+    if (threadIdx.x < 32) {
+        // ------------------------------------------------------------------ producer
+        if (threadIdx.x == 0) {
+            bool ok = true;
+            int i = 0;
+            for (int b = blockIdx.x; b < p.n_batches && ok; b += gridDim.x, ++i) {
+                const int s = i % PIPE_STAGES;
+                const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
+                if (i >= PIPE_STAGES && !tc::mbar_wait(EMPTY0 + 8u * s, ph ^ 1u, PIPE_WAIT)) { ok = false; break; }
+                const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
+                const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
+                const uint32_t L = (uint32_t)it.length;
+                if (bt.vec) {
+                    const uint32_t bytes = (uint32_t)bt.nc * L * (uint32_t)sizeof(T);
+                    tc::mbar_expect_tx(FULL0 + 8u * s, bytes);
+                    bulk_load(tc::smem_u32(ring + s * STAGE_BYTES), reinterpret_cast<const T*>(it.input) + (int64_t)bt.c0 * L,
+                              bytes, FULL0 + 8u * s);
+                } else {
+                    tc::mbar_arrive(FULL0 + 8u * s);          // the consumers read this batch themselves
+                }
+            }
+            if (!ok) atomicCAS(&g_channel_status, 0, 21);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    constexpr int GT = PIPE_GT;
+    const int ct = threadIdx.x - 32;
+    const int group = ct / GT, tid = ct % GT;
+    ChanShared& sh = ps.ch[group];
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp_e0 = (uint32_t)(tid & ~31) * 4u;
+    auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(GT) : "memory"); };
+    bool tables_ready = TK != TK_LUT;
+    int i = group;
+    for (int b = blockIdx.x + group * gridDim.x; b < p.n_batches; b += PIPE_GROUPS * gridDim.x, i += PIPE_GROUPS) {
+        const int s = i % PIPE_STAGES;
+        const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
+        const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
+        const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
+        const uint32_t L = (uint32_t)it.length;
+        const uint32_t n = (uint32_t)bt.nc * L;
+        const int64_t off = (int64_t)bt.c0 * L;
+        const T* x = reinterpret_cast<const T*>(it.input) + off;
+        const bool vec = bt.vec != 0;
+        const bool ragged = (L & 3u) != 0u;                  // a 4-element vector may straddle two channels
+        const bool need_amax = !it.scale_in || it.amax_out;
+        for (int c = tid; c < bt.nc; c += GT) {
+            sh.amax[c] = 0u;
+            sh.minnz[c] = 0xFFFFFFFFu;
+        }
+        if (tid == 0) {
+            sh.slow = need_amax ? 0 : 1;
+            bool ok = tc::mbar_wait(FULL0 + 8u * s, ph, PIPE_WAIT);
+            if (ok && !tables_ready) ok = tc::mbar_wait(TABLE_BAR, 0u, PIPE_WAIT);      // the bulk copies of the tables have landed
+            ps.ok[group] = ok ? 1 : 0;
+        }
+        tables_ready = true;
+        group_sync();
+        if (!ps.ok[group]) {
+            if (tid == 0) atomicCAS(&g_channel_status, 0, 22);
+            break;
+        }
+        // Batches whose channel length is a multiple of 4 elements go through registers and give their
+        // stage back at once.  "Ragged" ones (a 16-byte vector may straddle two channels; e.g. the 7x7x3
+        // stem) are rare: they stay in the stage and are walked by rolled loops, element by element.
+        const bool in_regs = vec && !ragged;
+        const T* st = reinterpret_cast<const T*>(ring + s * STAGE_BYTES);
+        RawVec<T> raw[PIPE_VECS];
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < PIPE_VECS; ++j) {
+                const uint32_t e = (uint32_t)(j * GT + tid) * 4u;
+                if (e < n) raw[j].load_shared(st + e);
+                else raw[j].zero();
+            }
+        }
+        if (!(vec && ragged)) {
+            group_sync();                                    // every thread has its copy: the stage is free
+            if (tid == 0) tc::mbar_arrive(EMPTY0 + 8u * s);
+        }
+        const T* xs = (vec && ragged) ? st : x;              // where the rolled loops read the batch
+
+        if (need_amax && in_regs) {
+            uint32_t cur = 0xFFFFFFFFu, m = 0u, mn = 0xFFFFFFFFu;
+            auto flush = [&]() {
+                if (cur != 0xFFFFFFFFu) {
+                    const uint32_t wm = __reduce_max_sync(0xFFFFFFFFu, m), wn = __reduce_min_sync(0xFFFFFFFFu, mn);
+                    if (lane == 0) {
+                        atomicMax(&sh.amax[cur], wm);
+                        atomicMin(&sh.minnz[cur], wn);
+                    }
+                }
+                cur = 0xFFFFFFFFu; m = 0u; mn = 0xFFFFFFFFu;
+            };
+#pragma unroll
+            for (int j = 0; j < PIPE_VECS; ++j) {
+                const uint32_t first = (uint32_t)(j * GT) * 4u + warp_e0;          // warp uniform
+                if (first >= n) continue;
+                float v[4];
+                raw[j].get(v);
+                const uint32_t e = (uint32_t)(j * GT + tid) * 4u;
+                const uint32_t a0 = abs_bits(v[0]), a1 = abs_bits(v[1]), a2 = abs_bits(v[2]), a3 = abs_bits(v[3]);
+                const uint32_t m4 = max(max(a0, a1), max(a2, a3));
+                const uint32_t n4 = min(min(a0 - 1u, a1 - 1u), min(a2 - 1u, a3 - 1u));   // a zero wraps to the top and drops out
+                const uint32_t last = min(first + 127u, n - 1u);
+                const uint32_t c_first = fd_div(first, bt.len), c_last = fd_div(last, bt.len);
+                if (c_first == c_last) {
+                    if (c_first != cur) {
+                        flush();
+                        cur = c_first;
+                    }
+                    if (e < n) {
+                        m = max(m, m4);
+                        mn = min(mn, n4);
+                    }
+                } else {
+                    flush();
+                    if (e < n) {
+                        const uint32_t ch = fd_div(e, bt.len);
+                        atomicMax(&sh.amax[ch], m4);
+                        atomicMin(&sh.minnz[ch], n4);
+                    }
+                }
+            }
+            flush();
+        } else if (need_amax) {
+            // consecutive lanes take consecutive elements: a warp usually sits in one channel
+            for (uint32_t e0 = (uint32_t)(tid & ~31); e0 < n; e0 += GT) {
+                const uint32_t e = e0 + lane;
+                uint32_t a = 0u, an = 0xFFFFFFFFu, ch = 0u;
+                if (e < n) {
+                    a = abs_bits(elem_f32<T>(xs, e));
+                    an = a - 1u;
+                    ch = fd_div(e, bt.len);
+                }
+                const uint32_t c_first = fd_div(e0, bt.len), c_last = fd_div(min(e0 + 31u, n - 1u), bt.len);
+                if (c_first == c_last) {
+                    const uint32_t wm = __reduce_max_sync(0xFFFFFFFFu, a), wn = __reduce_min_sync(0xFFFFFFFFu, an);
+                    if (lane == 0) {
+                        atomicMax(&sh.amax[c_first], wm);
+                        atomicMin(&sh.minnz[c_first], wn);
+                    }
+                } else if (e < n) {
+                    atomicMax(&sh.amax[ch], a);
+                    atomicMin(&sh.minnz[ch], an);
+                }
+            }
+        }
+        if (need_amax) group_sync();
+        for (int c = tid; c < bt.nc; c += GT) {
+            const int64_t cg = bt.c0 + c;
+            float sc;
+            if (need_amax) {
+                const uint32_t mb = sh.amax[c];
+                const float amax = __uint_as_float(mb);
+                sc = (mb != 0u && mb < 0x7F800000u) ? Arith<T>::rnd(__fdiv_rn(amax, p.qmax)) : 1.0f;
+                if (it.amax_out) store_one<T>(reinterpret_cast<T*>(it.amax_out) + cg, amax);
+                if (it.scale_out && !it.scale_in) store_one<T>(reinterpret_cast<T*>(it.scale_out) + cg, sc);
+            }
+            if (it.scale_in) sc = elem_f32<T>(reinterpret_cast<const T*>(it.scale_in), cg);
+            const DivPlan d = plan_division(sc);
+            const uint32_t sb = __float_as_uint(sc), ex = (sb >> 23) & 0xFFu;
+            const bool in_range = d.kind != 0 && (sb >> 31) == 0u && ex >= 97u && ex <= 157u && need_amax &&
+                                  sh.amax[c] < 0x5E000000u && sh.minnz[c] >= 0x0D800000u - 1u;
+            if (!in_range) sh.slow = 1;
+            sh.s[c] = sc;
+            sh.y[c] = d.y;
+            sh.kind[c] = d.kind;
+        }
+        group_sync();
+        const bool want_val = it.values != nullptr || it.dequant != nullptr;
+        const bool want_code = it.codes != nullptr;
+        if (want_val || want_code) {
+            T* values = reinterpret_cast<T*>(it.values) + (it.values ? off : 0);
+            T* dequant = reinterpret_cast<T*>(it.dequant) + (it.dequant ? off : 0);
+            uint8_t* codes = it.codes + (it.codes ? off : 0);
+            // value and code of the bf16 pattern `pat` of a quotient whose dividend was `xv`
+            auto lookup = [&](uint32_t pat, float& val, uint32_t& code) {
+                if (TK == TK_LUT) {
+                    code = s_codes[pat];
+                    val = s_lv2[code + ((pat >> 15) << 8)];
+                } else {
+                    const float vb = __uint_as_float(pat << 16);
+                    float q = rintf(vb);
+                    if (lo_is_zero) {
+                        q = (q < lo) ? lo : q;
+                        q = (q > hi) ? hi : q;
+                    } else {
+                        q = fminf(fmaxf(q, lo), hi);
+                    }
+                    val = (vb != vb) ? vb : q;
+                    code = (vb != vb) ? 0u : ((uint32_t)(int)q & 0xFFu);
+                }
+            };
+            if (in_regs && sh.slow == 0) {
+#pragma unroll
+                for (int j = 0; j < PIPE_VECS; ++j) {
+                    const uint32_t e = (uint32_t)(j * GT + tid) * 4u;
+                    if (e >= n) continue;
+                    float v[4];
+                    raw[j].get(v);
+                    const uint32_t ch = fd_div(e, bt.len);
+                    const float sc = sh.s[ch], y = sh.y[ch];
+                    float q[4], d[4];
+                    uint32_t packed = 0;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float xv = v[k];
+                        const float q0 = __fmul_rn(xv, y);
+                        const float qq = __fmaf_rn(__fmaf_rn(-sc, q0, xv), y, q0);
+                        const uint32_t pat = bf16_pattern(
+                            __uint_as_float((__float_as_uint(qq) & 0x7FFFFFFFu) | (__float_as_uint(xv) & 0x80000000u)));
+                        uint32_t code;
+                        lookup(pat, q[k], code);
+                        packed |= code << (8 * k);
+                        d[k] = Arith<T>::rnd(__fmul_rn(q[k], sc));
+                    }
+                    if (it.values) store4<T>(values + e, q);
+                    if (it.dequant) store4<T>(dequant + e, d);
+                    if (want_code) __stcs(reinterpret_cast<uint32_t*>(codes + e), packed);
+                }
+            } else {
+#pragma unroll 1
+                for (uint32_t e = tid; e < n; e += GT) {
+                    const uint32_t ch = fd_div(e, bt.len);
+                    DivPlan dv;
+                    dv.s = sh.s[ch];
+                    dv.y = sh.y[ch];
+                    dv.kind = sh.kind[ch];
+                    float q;
+                    uint32_t code;
+                    lookup(bf16_pattern(divide(dv, elem_f32<T>(xs, e))), q, code);
+                    if (it.values) store_one<T>(values + e, q);
+                    if (it.dequant) store_one<T>(dequant + e, Arith<T>::rnd(__fmul_rn(q, dv.s)));
+                    if (want_code) codes[e] = (uint8_t)code;
+                }
+            }
+        }
+        group_sync();
+        if (vec && ragged && tid == 0) tc::mbar_arrive(EMPTY0 + 8u * s);
+    }
+}
+
+// channels per batch / batches of one item, for batches of about `batch_elems` elements
+inline int64_t channels_per_batch(const vq_channel_item& it, int64_t batch_elems, int vec_elems = 1) {
+    int64_t per = batch_elems / it.length;
     per = per < 1 ? 1 : (per > kBatchMaxChannels ? kBatchMaxChannels : per);
+    if (vec_elems > 1 && it.length % vec_elems) {
+        // channel length no multiple of a 16-byte vector: a multiple of q channels is
+        int64_t g = it.length, b = vec_elems;
+        while (b) { const int64_t t = g % b; g = b; b = t; }
+        const int64_t q = vec_elems / g;
+        if (per >= q) per = per / q * q;
+    }
+    return per;
+}
+// 1 when the batch [c0, c0 + nc) of `it` can be moved and processed in 16-byte vectors
+inline int batch_vec(const vq_channel_item& it, int64_t c0, int64_t nc, int dtype) {
+    const int64_t ve = dtype == VQ_F32 ? 4 : 8;
+    const bool aligned = ((uintptr_t)it.input & 15) == 0 && ((uintptr_t)it.values & 15) == 0 && ((uintptr_t)it.dequant & 15) == 0 &&
+                         ((uintptr_t)it.codes & 3) == 0;
+    return aligned && (c0 * it.length) % ve == 0 && (nc * it.length) % ve == 0;
+}
+inline int64_t batches_of(const vq_channel_item& it, int64_t batch_elems, int vec_elems = 1) {
+    if (it.channels <= 0) return 0;
+    const int64_t per = channels_per_batch(it, batch_elems, vec_elems);
     return (it.channels + per - 1) / per;
 }
+constexpr int64_t kSmallestBatch = 7168;    // the workspace is sized for the finest split any kernel uses
 
 }  // namespace
+extern "C" size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items);
+namespace {
 
-extern "C" {
+// Everything a launch needs, decided once from the host descriptors.
+struct ChanLaunch {
+    BatchParams p{};
+    int kernel = 0;                 // 0 two sweeps, 2 pipelined
+    int dtype = 0, mode = 0, n_items = 0;
+    bool lut_tab = false;
+    int threads = 0, blocks = 0;
+    size_t smem = 0, items_bytes = 0;
+    std::vector<ChanBatch> batches; // host copy until it has been uploaded
+};
 
-size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items) {
-    if (n_items < 0 || !items) return 0;
-    int64_t nb = 0;
-    for (int i = 0; i < n_items; ++i) nb += (items[i].length >= 1) ? batches_of(items[i]) : 0;
-    return (size_t)n_items * sizeof(vq_channel_item) + (size_t)nb * sizeof(ChanBatch) + 64;
-}
-
-int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dtype, double quant_max, const vq_table* table,
-                              void* workspace, size_t workspace_bytes, void* stream) {
-    const char* name = "vq_channel_quantize_multi";
-    VQ_REQUIRE(n_items >= 0, "%s: negative item count", name);
-    if (n_items == 0) return 0;
+// Argument checks, kernel choice, batch list.  0 on success; L.p.n_batches == 0: nothing to do.
+int channel_prepare(const char* name, const vq_channel_item* items, int n_items, int dtype, double quant_max, const vq_table* table,
+                    void* workspace, size_t workspace_bytes, ChanLaunch& L) {
     VQ_REQUIRE(items != nullptr, "%s: null item array", name);
     VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
     VQ_REQUIRE(quant_max > 0.0, "%s: quant_max must be positive", name);
     bool any_table_out = false, any_codes = false;
-    int64_t total = 0, n_batches = 0;
+    int64_t total = 0, longest = 0;
     for (int i = 0; i < n_items; ++i) {
         const vq_channel_item& it = items[i];
         const bool ok = it.input && it.channels >= 0 && it.channels < (1ll << 31) && it.length >= 1 &&
@@ -327,39 +723,18 @@ int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dty
         any_table_out |= it.values || it.codes || it.dequant;
         any_codes |= it.codes != nullptr;
         total += it.channels * it.length;
-        n_batches += batches_of(it);
+        if (it.channels > 0 && it.length > longest) longest = it.length;
     }
     VQ_REQUIRE(!any_table_out || (table && table->kind != VQ_TABLE_NONE), "%s: quantized outputs need a table", name);
     if (any_codes) {
         const bool have = table->kind == VQ_TABLE_INT || table->lut8 || (table->kind == VQ_TABLE_RUNS && table->run_codes);
         VQ_REQUIRE(have, "%s: packed codes need a code table", name);
     }
-    VQ_REQUIRE(n_batches < (1ll << 31), "%s: too many channels", name);
     VQ_REQUIRE(workspace && (uintptr_t)workspace % 16 == 0 && workspace_bytes >= vq_channel_quantize_multi_workspace(items, n_items),
                "%s: workspace missing, unaligned or smaller than vq_channel_quantize_multi_workspace(items, n_items)", name);
-    if (n_batches == 0) return 0;
 
-    const size_t items_bytes = ((size_t)n_items * sizeof(vq_channel_item) + 31) / 32 * 32;
-    ChanBatch* hb = new ChanBatch[(size_t)n_batches];
-    int64_t k = 0;
-    for (int i = 0; i < n_items; ++i) {
-        const vq_channel_item& it = items[i];
-        if (it.channels <= 0) continue;
-        int64_t per = kBatchElems / it.length;
-        per = per < 1 ? 1 : (per > kBatchMaxChannels ? kBatchMaxChannels : per);
-        const FastDiv fdv = make_fastdiv((uint32_t)it.length);
-        for (int64_t c0 = 0; c0 < it.channels; c0 += per, ++k) {
-            hb[k].item = i;
-            hb[k].c0 = (int)c0;
-            hb[k].nc = (int)(it.channels - c0 < per ? it.channels - c0 : per);
-            hb[k].len = fdv;
-            hb[k].pad[0] = hb[k].pad[1] = 0;
-        }
-    }
-    BatchParams p{};
-    p.items = reinterpret_cast<const vq_channel_item*>(workspace);
-    p.batches = reinterpret_cast<const ChanBatch*>((char*)workspace + items_bytes);
-    p.n_batches = (int)n_batches;
+    BatchParams& p = L.p;
+    p = BatchParams{};
     p.qmax = (float)quant_max;
     p.common.tab = to_dev(table);
     const bool lut = table && table->kind == VQ_TABLE_LUT16;
@@ -368,25 +743,124 @@ int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dty
     p.common.smem_lut8 = (big && lut && any_codes && table->lut8) ? 1 : 0;
     p.table_bytes = (p.common.smem_lut16 ? 131072 : 0) + (p.common.smem_lut8 ? 65536 : 0) +
                     ((table && table->kind == VQ_TABLE_RUNS) ? ((5 * VQ_MAX_RUNS + 15) / 16 * 16) : 0);
-    const size_t smem = (size_t)p.table_bytes + 4 * sizeof(ChanShared);
     const bool direct = lut && table->nan_uniform && (!any_codes || table->lut8);
     const bool staged = direct && p.common.smem_lut16 && (!any_codes || p.common.smem_lut8);
     const int mode = staged ? 2 : (direct ? 1 : 0);
+    // Kernel choice (VOYAGER_B200_CHANNEL_KERNEL=sweep forces the second one, for measurements):
+    //   pipe   bulk-copy pipeline; needs every channel to fit a batch and either an INT table or a code
+    //          table whose values follow from (code, input sign);
+    //   sweep  two sweeps per batch, any table, any channel length.
+    const char* want_kernel = getenv("VOYAGER_B200_CHANNEL_KERNEL");
+    const bool pipe_table = table && ((table->kind == VQ_TABLE_INT && table->lo >= -128.0f && table->hi <= 255.0f) ||
+                                      (table->kind == VQ_TABLE_LUT16 && table->nan_uniform && table->lut8 && table->levels2 &&
+                                       (uintptr_t)table->lut8 % 16 == 0 && (uintptr_t)table->levels2 % 16 == 0));
+    bool use_pipe = big && (pipe_table || !any_table_out) && longest <= PIPE_BATCH;
+    if (want_kernel && !strcmp(want_kernel, "sweep")) use_pipe = false;
+    const int64_t batch_elems = use_pipe ? PIPE_BATCH : kBatchElems;
 
-    cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_channel_item), cudaMemcpyHostToDevice, st);
-    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + items_bytes, hb, (size_t)n_batches * sizeof(ChanBatch),
-                                     cudaMemcpyHostToDevice, st);
-    delete[] hb;   // pageable copies are staged before cudaMemcpyAsync returns
-    if (e1 != cudaSuccess || e2 != cudaSuccess)
-        return vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload failed: %s", name, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    const int vec_elems = use_pipe ? (dtype == VQ_F32 ? 4 : 8) : 1;
+    // Batches of the pipelined kernel that cannot go through registers (channel length no multiple of 4
+    // elements, unaligned tensors) cost several times more per element: they are cut eight times smaller
+    // so that no single one unbalances the CTAs.
+    auto item_batch = [&](const vq_channel_item& it) -> int64_t {
+        if (!use_pipe) return batch_elems;
+        const bool lean = it.length % 4 == 0 && batch_vec(it, 0, 4, dtype);
+        return lean ? batch_elems : batch_elems / 8;
+    };
+    int64_t n_batches = 0;
+    for (int i = 0; i < n_items; ++i) n_batches += batches_of(items[i], item_batch(items[i]), vec_elems);
+    VQ_REQUIRE(n_batches < (1ll << 31), "%s: too many channels", name);
+    L.dtype = dtype;
+    L.n_items = n_items;
+    L.mode = mode;
+    if (n_batches == 0) return 0;
+
+    const size_t items_bytes = ((size_t)n_items * sizeof(vq_channel_item) + 31) / 32 * 32;
+    L.items_bytes = items_bytes;
+    L.batches.resize((size_t)n_batches);
+    ChanBatch* hb = L.batches.data();
+    int64_t k = 0;
+    for (int i = 0; i < n_items; ++i) {
+        const vq_channel_item& it = items[i];
+        if (it.channels <= 0) continue;
+        const int64_t per = channels_per_batch(it, item_batch(it), vec_elems);
+        const FastDiv fdv = make_fastdiv((uint32_t)it.length);
+        for (int64_t c0 = 0; c0 < it.channels; c0 += per, ++k) {
+            hb[k].item = i;
+            hb[k].c0 = (int)c0;
+            hb[k].nc = (int)(it.channels - c0 < per ? it.channels - c0 : per);
+            hb[k].len = fdv;
+            hb[k].vec = batch_vec(it, hb[k].c0, hb[k].nc, dtype);
+            hb[k].pad = 0;
+        }
+    }
+    if (use_pipe) {
+        // CTA c walks batches c, c + grid, c + 2 grid, ...: with the list ordered by estimated cost every
+        // CTA receives one batch of each cost tier
+        auto cost = [&](const ChanBatch& b) -> int64_t {
+            const vq_channel_item& it = items[b.item];
+            const int64_t n = (int64_t)b.nc * it.length;
+            const int64_t per_elem = !b.vec ? 10 : (it.length % 4 ? 6 : 1);
+            return n * per_elem + 64 * (int64_t)b.nc;
+        };
+        std::stable_sort(hb, hb + n_batches, [&](const ChanBatch& a, const ChanBatch& b) { return cost(a) > cost(b); });
+    }
+    p.items = reinterpret_cast<const vq_channel_item*>(workspace);
+    p.batches = reinterpret_cast<const ChanBatch*>((char*)workspace + items_bytes);
+    p.n_batches = (int)n_batches;
 
     const int sms = vq_sm_count();
-    // tables in shared memory leave room for one CTA per SM: make it a full one
-    const int threads = smem > 100 * 1024 ? 1024 : 512;
-    const int per_sm = smem > 100 * 1024 ? 1 : 2;
-    const int64_t want = (n_batches * kGroupThreads + threads - 1) / threads;
-    const int blocks = (int)(want < (int64_t)sms * per_sm ? want : (int64_t)sms * per_sm);
+    if (use_pipe) {
+        L.kernel = 2;
+        L.lut_tab = any_table_out && table->kind == VQ_TABLE_LUT16;     // no quantized output: no table is staged
+        const size_t esize = dtype == VQ_F32 ? 4 : 2;
+        L.smem = (L.lut_tab ? 65536 + 2048 : 0) + (size_t)PIPE_STAGES * PIPE_BATCH * esize + ((sizeof(PipeShared) + 15) / 16) * 16 +
+                 kSmemItems * sizeof(vq_channel_item) + kSmemBatches * sizeof(ChanBatch) + 16 * PIPE_STAGES + 16;
+        if ((int)L.smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: device offers too little shared memory", name);
+        L.threads = PIPE_THREADS;
+        L.blocks = (int)(n_batches < sms ? n_batches : sms);
+    } else {
+        L.kernel = 0;
+        L.smem = (size_t)p.table_bytes + 4 * sizeof(ChanShared);
+        // tables in shared memory leave room for one CTA per SM: make it a full one
+        L.threads = L.smem > 100 * 1024 ? 1024 : 512;
+        const int per_sm = L.smem > 100 * 1024 ? 1 : 2;
+        const int64_t want = (n_batches * kGroupThreads + L.threads - 1) / L.threads;
+        L.blocks = (int)(want < (int64_t)sms * per_sm ? want : (int64_t)sms * per_sm);
+    }
+    return 0;
+}
+
+// Descriptors -> device workspace (pageable sources are staged before cudaMemcpyAsync returns).
+int channel_upload(const char* name, const ChanLaunch& L, const vq_channel_item* items, int n_items, void* workspace, cudaStream_t st) {
+    cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_channel_item), cudaMemcpyHostToDevice, st);
+    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + L.items_bytes, L.batches.data(), L.batches.size() * sizeof(ChanBatch),
+                                     cudaMemcpyHostToDevice, st);
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+        return vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload failed: %s", name, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    return 0;
+}
+
+int channel_launch(const ChanLaunch& L, cudaStream_t st) {
+    const BatchParams& p = L.p;
+    const int dtype = L.dtype, mode = L.mode, blocks = L.blocks, threads = L.threads, n_items = L.n_items;
+    const size_t smem = L.smem;
+    if (L.kernel == 2) {
+#define VQ_CHP_LAUNCH(T, K)                                                                                           \
+    do {                                                                                                              \
+        auto kern = channel_pipe_kernel<T, K>;                                                                        \
+        VQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                  \
+        kern<<<blocks, threads, smem, st>>>(p, n_items);                                                              \
+    } while (0)
+        if (dtype == VQ_F32) {
+            if (L.lut_tab) VQ_CHP_LAUNCH(float, TK_LUT); else VQ_CHP_LAUNCH(float, TK_INT);
+        } else {
+            if (L.lut_tab) VQ_CHP_LAUNCH(bf16_t, TK_LUT); else VQ_CHP_LAUNCH(bf16_t, TK_INT);
+        }
+#undef VQ_CHP_LAUNCH
+        VQ_LAUNCH_CHECK("channel_pipe_kernel");
+        return 0;
+    }
 #define VQ_CH_LAUNCH(T, D)                                                                                            \
     do {                                                                                                              \
         auto kern = channel_quant_kernel<T, D>;                                                                       \
@@ -402,5 +876,77 @@ int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dty
     VQ_LAUNCH_CHECK("channel_quant_kernel");
     return 0;
 }
+
+}  // namespace
+
+// A prepared per-channel pass (see vq_channel_plan_create).
+struct vq_channel_plan {
+    ChanLaunch l;
+};
+
+extern "C" {
+
+int vq_channel_status(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_channel_status, sizeof(int)) != cudaSuccess) return VQ_ERR_CUDA;
+    if (v) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_channel_status, &zero, sizeof(int));
+    }
+    return v;
+}
+
+size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items) {
+    if (n_items < 0 || !items) return 0;
+    int64_t nb = 0;
+    for (int i = 0; i < n_items; ++i) nb += (items[i].length >= 1) ? batches_of(items[i], kSmallestBatch / 8, 8) : 0;
+    return (size_t)n_items * sizeof(vq_channel_item) + (size_t)nb * sizeof(ChanBatch) + 64;
+}
+
+int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dtype, double quant_max, const vq_table* table,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    const char* name = "vq_channel_quantize_multi";
+    VQ_REQUIRE(n_items >= 0, "%s: negative item count", name);
+    if (n_items == 0) return 0;
+    ChanLaunch L;
+    int rc = channel_prepare(name, items, n_items, dtype, quant_max, table, workspace, workspace_bytes, L);
+    if (rc || L.p.n_batches == 0) return rc;
+    rc = channel_upload(name, L, items, n_items, workspace, (cudaStream_t)stream);
+    if (rc) return rc;
+    return channel_launch(L, (cudaStream_t)stream);
+}
+
+int vq_channel_plan_create(const vq_channel_item* items, int n_items, int dtype, double quant_max, const vq_table* table,
+                           void* workspace, size_t workspace_bytes, void* stream, vq_channel_plan** plan_out) {
+    const char* name = "vq_channel_plan_create";
+    VQ_REQUIRE(plan_out != nullptr, "%s: null plan pointer", name);
+    *plan_out = nullptr;
+    VQ_REQUIRE(n_items >= 1, "%s: a plan needs at least one tensor", name);
+    vq_channel_plan* plan = new (std::nothrow) vq_channel_plan();
+    VQ_REQUIRE(plan != nullptr, "%s: out of host memory", name);
+    int rc = channel_prepare(name, items, n_items, dtype, quant_max, table, workspace, workspace_bytes, plan->l);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!rc && plan->l.p.n_batches > 0) {
+        rc = channel_upload(name, plan->l, items, n_items, workspace, st);
+        // run() may be queued on any stream afterwards: the descriptors must have landed by then
+        if (!rc && cudaStreamSynchronize(st) != cudaSuccess) rc = vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload did not complete", name);
+    }
+    if (rc) {
+        delete plan;
+        return rc;
+    }
+    plan->l.batches.clear();
+    plan->l.batches.shrink_to_fit();
+    *plan_out = plan;
+    return 0;
+}
+
+int vq_channel_plan_run(const vq_channel_plan* plan, void* stream) {
+    VQ_REQUIRE(plan != nullptr, "vq_channel_plan_run: null plan");
+    if (plan->l.p.n_batches == 0) return 0;
+    return channel_launch(plan->l, (cudaStream_t)stream);
+}
+
+void vq_channel_plan_destroy(vq_channel_plan* plan) { delete plan; }
 
 }  // extern "C"

@@ -81,6 +81,7 @@ struct TableDev {
     uint16_t nan_val, pinf_val, ninf_val;
     uint8_t nan_code, pinf_code, ninf_code;
     uint8_t flat_tiny;
+    const float* levels2;
 };
 
 #define VQ_MAX_RUNS 512
@@ -103,6 +104,7 @@ inline TableDev to_dev(const vq_table* t) {
     d.nan_code = t->nan_code;
     d.pinf_code = t->pinf_code;
     d.ninf_code = t->ninf_code;
+    d.levels2 = t->levels2;
     d.flat_tiny = (t->kind == VQ_TABLE_INT) ? (t->lo <= 0.0f && t->hi >= 0.0f) : t->flat_tiny;
     return d;
 }

@@ -38,7 +38,6 @@ __global__ void __launch_bounds__(1024, 1) ew_fast_kernel(const EwFastParams p) 
     if (SM && TK == TK_LUT && OP != EW_DEQUANT) {
         const uint4* src = reinterpret_cast<const uint4*>(p.tab.lut16);
         for (int i = threadIdx.x; i < 8192; i += blockDim.x) smem[i] = __ldg(src + i);
-        ft.lut16 = reinterpret_cast<const uint16_t*>(smem);
         __syncthreads();
     }
     constexpr int N = sizeof(T) == 2 ? 16 : 8;
@@ -74,7 +73,7 @@ __global__ void __launch_bounds__(1024, 1) ew_fast_kernel(const EwFastParams p) 
                 }
                 store32(out + (size_t)ci * N, o);
             } else if (OP == EW_MAP) {
-                fast_chunk<T, TK, OUT_FLOAT, SM>(ft, x[u], 1.0f, false, (size_t)ci, out, nullptr);
+                fast_chunk<T, TK, OUT_FLOAT, SM>(ft, smem, x[u], 1.0f, false, (size_t)ci, out, nullptr);
             } else {
                 bool refine = false;
                 if (sizeof(T) == 2) {
@@ -83,7 +82,7 @@ __global__ void __launch_bounds__(1024, 1) ew_fast_kernel(const EwFastParams p) 
                     refine = true;
                     if (!ft.flat_tiny) chunk_amax<T>(x[u], refine, true);
                 }
-                fast_chunk<T, TK, OP == EW_FAKEQ ? OUT_FAKEQ : OUT_FLOAT, SM>(ft, x[u], s, refine, (size_t)ci, out, nullptr);
+                fast_chunk<T, TK, OP == EW_FAKEQ ? OUT_FAKEQ : OUT_FLOAT, SM>(ft, smem, x[u], s, refine, (size_t)ci, out, nullptr);
             }
         }
     }

@@ -26,7 +26,8 @@
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
                         cudaStream_t st, const CUtensorMap* tmSA = nullptr, const CUtensorMap* tmSB = nullptr,
-                        const void* a_codes = nullptr, const void* b_codes = nullptr, bool packed_codes = false);
+                        const void* a_codes = nullptr, const void* b_codes = nullptr, bool packed_codes = false, int batch = 1,
+                        int64_t a_batch_rows = 0, int64_t b_batch_rows = 0, int64_t y_batch_stride = 0);
 
 namespace {
 
@@ -46,6 +47,14 @@ struct GemmParams {
     const uint16_t* bias;
     int M, N, K;
     int tiles_m, tiles_n;
+    // Batched product (plain variant): `batch` independent M x N x K problems.  A and B are addressed
+    // through 2-D maps over the flattened [batch * rows, K] operands, batch b starting a_batch_rows /
+    // b_batch_rows rows further down (0: the operand is shared by all batches); a tile that reaches past
+    // the end of its batch reads rows of the next one, whose products land in rows / columns the
+    // epilogue masks.  Output b starts y_batch_stride elements after output b - 1.
+    int batch;
+    int a_batch_rows, b_batch_rows;
+    int64_t y_batch_stride;
     int32_t* status;
     // fused variant
     const uint16_t* a_codes;
@@ -86,7 +95,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mma_warp = NPROD, epi_warp0 = NPROD + 1;
     const int num_k = (p.K + BK - 1) / BK;
-    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+    const int n_tiles = tiles_per_batch * p.batch;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -121,7 +131,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!FUSED) {
             if (lane == 0) {
                 for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                    const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+                    const int bi = tile / tiles_per_batch, rem = tile - bi * tiles_per_batch;
+                    const int m0 = bi * p.a_batch_rows + (rem % p.tiles_m) * BM, n0 = bi * p.b_batch_rows + (rem / p.tiles_m) * BN;
                     for (int k = 0; k < num_k; ++k) {
                         if (!tc::mbar_wait(EMPTY0 + 8u * stage, phase ^ 1u, WAIT_BUDGET)) { ok = false; break; }
                         tc::mbar_expect_tx(FULL0 + 8u * stage, STAGE_BYTES);
@@ -222,7 +233,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+            const int bi = tile / tiles_per_batch, rem = tile - bi * tiles_per_batch;
+            const int m0 = (rem % p.tiles_m) * BM, n0 = (rem / p.tiles_m) * BN;
             if (lane == 0) ok = tc::mbar_wait(TFULL0 + 8u * acc, acc_phase, WAIT_BUDGET);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
@@ -247,7 +259,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(hi), "f"(lo));
                     }
-                    const size_t off = (size_t)row * p.ldy + p.col_offset + col0;
+                    const size_t off = (size_t)bi * p.y_batch_stride + (size_t)row * p.ldy + p.col_offset + col0;
                     for (int d = 0; d < p.n_outputs; ++d) {       // own buffer, then peers over NVLink
                         uint16_t* dst = p.Y[d] + off;
                         if (col0 + 32 <= p.N && (off & 7) == 0) {
@@ -327,7 +339,8 @@ int make_map_u8(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int 
 int launch_gemm(bool fused, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t st) {
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
-    const int n_tiles = p.tiles_m * p.tiles_n;
+    if (p.batch < 1) p.batch = 1;
+    const int n_tiles = p.tiles_m * p.tiles_n * p.batch;
     const int sms = vq_sm_count();
     const int grid = n_tiles < sms ? n_tiles : sms;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 256 + 1024;
@@ -353,6 +366,41 @@ int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int
                     int32_t* status, void* stream) {
     void* ys[1] = {Y};
     return vq_gemm_bf16_tn_scatter(A, B, bias, ys, 1, N, 0, M, N, K, status, stream);
+}
+
+int vq_gemm_bf16_tn_batched(const void* A, const void* B, void* Y, int64_t batch, int64_t M, int64_t N, int64_t K,
+                            int a_shared, int b_shared, int32_t* status, void* stream) {
+    const char* name = "vq_gemm_bf16_tn_batched";
+    VQ_REQUIRE(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "%s: negative size", name);
+    if (batch == 0 || M == 0 || N == 0) return 0;
+    VQ_REQUIRE(A && B && Y, "%s: null pointer", name);
+    VQ_REQUIRE(K > 0 && K % 8 == 0, "%s: K must be a positive multiple of 8 (16-byte rows)", name);
+    VQ_REQUIRE(batch * M < (1ll << 31) && batch * N < (1ll << 31) && K < (1ll << 31), "%s: batch * rows must be below 2^31", name);
+    VQ_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)B % 16 == 0 && (uintptr_t)Y % 2 == 0, "%s: operands must be 16-byte aligned", name);
+    const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+    VQ_REQUIRE(tiles * batch < (1ll << 31), "%s: too many output tiles", name);
+    const int64_t rowsA = a_shared ? M : batch * M, rowsB = b_shared ? N : batch * N;
+    CUtensorMap tmA, tmB;
+    if (int rc = make_map(&tmA, A, rowsA, K, BM)) return rc;
+    void* ys[1] = {Y};
+    const char* tile = getenv("VOYAGER_B200_GEMM_TILE");
+    if (M > 128 && !(tile && !strcmp(tile, "1cta"))) {
+        if (int rc = make_map(&tmB, B, rowsB, K, 128)) return rc;
+        return vq_gemm_pair_launch(tmA, tmB, ys, 1, N, 0, nullptr, M, N, K, status, (cudaStream_t)stream, nullptr, nullptr, nullptr,
+                                   nullptr, false, (int)batch, a_shared ? 0 : M, b_shared ? 0 : N, M * N);
+    }
+    if (int rc = make_map(&tmB, B, rowsB, K, BN)) return rc;
+    GemmParams p{};
+    p.Y[0] = reinterpret_cast<uint16_t*>(Y);
+    p.n_outputs = 1;
+    p.ldy = N;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.batch = (int)batch;
+    p.a_batch_rows = a_shared ? 0 : (int)M;
+    p.b_batch_rows = b_shared ? 0 : (int)N;
+    p.y_batch_stride = M * N;
+    p.status = status;
+    return launch_gemm(false, tmA, tmB, p, (cudaStream_t)stream);
 }
 
 int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bias, void* const* Ys, int n_outputs, int64_t ldy,

@@ -42,6 +42,9 @@ struct PairParams {
     const uint16_t* bias;
     int M, N, K;
     int tiles_m, tiles_n;      // in units of 256 x 256
+    int batch;                 // plain variant: independent problems over flattened [batch * rows, K] operands
+    int a_batch_rows, b_batch_rows;   // rows between consecutive batches of A / B (0: shared operand)
+    int64_t y_batch_stride;    // elements between consecutive outputs
     int bulk_ok;               // output rows are 16-byte aligned: the epilogue may use bulk stores
     int32_t* status;
     int blocks_per_row;        // fused variant: the operand maps cover the CODES, two more maps the [rows, K/32] scales
@@ -97,7 +100,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int num_k = (p.K + PK - 1) / PK;
-    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+    const int n_tiles = tiles_per_batch * p.batch;
 
     if (threadIdx.x == 0) {
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(ABORT), "r"(0u) : "memory");
@@ -135,8 +139,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t phase = 0, group = 0, rphase = 0;
             bool ok = true;
             for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
-                const int m0 = (tile % p.tiles_m) * 256 + (int)rank * PM;
-                const int n0 = (tile / p.tiles_m) * PN + (int)rank * PNH;
+                const int bi = tile / tiles_per_batch, rem = tile - bi * tiles_per_batch;
+                const int m0 = bi * p.a_batch_rows + (rem % p.tiles_m) * 256 + (int)rank * PM;
+                const int n0 = bi * p.b_batch_rows + (rem / p.tiles_m) * PN + (int)rank * PNH;
                 for (int k = 0; k < num_k; ++k) {
                     if (FUSED && (k % SC_GROUP) == 0) {
                         // block scales of the next 8 k-steps (16 per row) into the free scale buffer
@@ -421,7 +426,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int tile = pair; tile < n_tiles && ok; tile += npairs) {
-            const int m0 = (tile % p.tiles_m) * 256 + (int)rank * PM, n0 = (tile / p.tiles_m) * PN;
+            const int bi = tile / tiles_per_batch, rem = tile - bi * tiles_per_batch;
+            const int m0 = (rem % p.tiles_m) * 256 + (int)rank * PM, n0 = (rem / p.tiles_m) * PN;
+            const size_t ybase = (size_t)bi * p.y_batch_stride;
             if (lane == 0) ok = tc::mbar_wait_cluster(TFULL0 + 8u * acc, acc_phase, PWAIT);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
@@ -461,13 +468,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if ((c & 3) == 3) {
                         tc::fence_proxy_async();
                         if (row < p.M) {
-                            const size_t off = (size_t)row * p.ldy + p.col_offset + half0;
+                            const size_t off = ybase + (size_t)row * p.ldy + p.col_offset + half0;
                             for (int d = 0; d < p.n_outputs; ++d) bulk_store(p.Y[d] + off, my_row, OUT_COLS * 2);
                         }
                         bulk_commit();
                     }
                 } else if (row < p.M && col0 < p.N) {
-                    const size_t off = (size_t)row * p.ldy + p.col_offset + col0;
+                    const size_t off = ybase + (size_t)row * p.ldy + p.col_offset + col0;
                     for (int d = 0; d < p.n_outputs; ++d) {
                         uint16_t* dst = p.Y[d] + off;
                         if (col0 + 32 <= p.N && (off & 7) == 0) {
@@ -506,7 +513,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* const* Ys, int n_outputs, int64_t ldy,
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
                         cudaStream_t st, const CUtensorMap* tmSA, const CUtensorMap* tmSB, const void* a_codes,
-                        const void* b_codes, bool packed_codes) {
+                        const void* b_codes, bool packed_codes, int batch, int64_t a_batch_rows, int64_t b_batch_rows,
+                        int64_t y_batch_stride) {
     const bool fused = tmSA != nullptr && tmSB != nullptr;
     // VOYAGER_B200_FUSED_STAGING=regs selects the register-staged variant (measured slower: one k-step
     // of global loads in flight per thread does not cover the L2 latency); default: TMA + in-place multiply
@@ -521,12 +529,16 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.tiles_m = (int)((M + 255) / 256);
     p.tiles_n = (int)((N + PN - 1) / PN);
+    p.batch = batch;
+    p.a_batch_rows = (int)a_batch_rows;
+    p.b_batch_rows = (int)b_batch_rows;
+    p.y_batch_stride = y_batch_stride;
     p.status = status;
-    p.bulk_ok = (ldy % 8 == 0 && col_offset % 8 == 0) ? 1 : 0;
+    p.bulk_ok = (ldy % 8 == 0 && col_offset % 8 == 0 && y_batch_stride % 8 == 0) ? 1 : 0;
     for (int d = 0; d < n_outputs; ++d)
         if ((uintptr_t)Ys[d] % 16) p.bulk_ok = 0;
     p.blocks_per_row = (int)(K / 32);
-    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int n_tiles = p.tiles_m * p.tiles_n * batch;
     const int sms = vq_sm_count();
     int pairs = sms / 2;
     if (n_tiles < pairs) pairs = n_tiles;

@@ -63,6 +63,13 @@ __device__ __forceinline__ float rcp_approx(float s) {
     return r;
 }
 
+// {a, b} *= r as one packed fp32x2 multiply (two correctly rounded IEEE products, one issue slot).
+__device__ __forceinline__ void mul2(float& a, float& b, float r) {
+    asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %2};\n\tmul.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+        : "+f"(a), "+f"(b)
+        : "f"(r));
+}
+
 // |x| maximum of a chunk as fp32 bits.  For bf16 also whether the reciprocal path is safe for this
 // chunk: no non-zero element below 2^-60 (pattern 0x2180).
 template <typename T>
@@ -158,6 +165,17 @@ __device__ __forceinline__ uint32_t ld_u8(const uint8_t* base, uint32_t idx) {
     }
     return __ldg(base + idx);
 }
+// The same reads for a table that sits at the very start of the kernel's dynamic shared memory:
+// `stab` is that array itself, so the compiler addresses the table as symbol + index and the byte
+// offset of the table costs no instruction.
+template <bool SM>
+__device__ __forceinline__ uint32_t tab_u16(const uint16_t* stab, const uint16_t* gtab, uint32_t idx) {
+    return SM ? (uint32_t)stab[idx] : (uint32_t)__ldg(gtab + idx);
+}
+template <bool SM>
+__device__ __forceinline__ uint32_t tab_u8(const uint8_t* stab, const uint8_t* gtab, uint32_t idx) {
+    return SM ? (uint32_t)stab[idx] : (uint32_t)__ldg(gtab + idx);
+}
 
 // clamp(rint(v)) of a bf16-representable value, NaN kept, -0 kept when lo == 0
 __device__ __forceinline__ float int_round(const FastTab& t, float vb) {
@@ -174,8 +192,10 @@ __device__ __forceinline__ float int_round(const FastTab& t, float vb) {
 // One 32-byte chunk: quantize with block scale `s`, write outputs of kind OUT at chunk index `ci`
 // of this tensor (element offset ci * N).
 template <typename T, int TK, int OUT, bool SM>
-__device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, float s, bool refine_ok, size_t ci,
+__device__ __forceinline__ void fast_chunk(const FastTab& t, const void* stab, const Chunk& x, float s, bool refine_ok, size_t ci,
                                            T* out_codes, uint8_t* codes8) {
+    const uint16_t* s16 = reinterpret_cast<const uint16_t*>(stab);
+    const uint8_t* s8 = reinterpret_cast<const uint8_t*>(stab);
     constexpr int N = sizeof(T) == 2 ? 16 : 8;
     float v[N];
     if (sizeof(T) == 2) {
@@ -193,13 +213,11 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
     if ((sb & 0x807FFFFFu) == 0u && ex >= 2u && ex <= 252u) {
         const float r = __uint_as_float((254u - ex) << 23);
 #pragma unroll
-        for (int j = 0; j < N; ++j) v[j] = __fmul_rn(v[j], r);
+        for (int j = 0; j < N; j += 2) mul2(v[j], v[j + 1], r);
     } else if (sizeof(T) == 2 && refine_ok && (sb >> 31) == 0u && ex >= 64u && ex <= 190u) {
         const float r = rcp_approx(s);
 #pragma unroll
-        for (int j = 0; j < N; ++j) {
-            v[j] = __fmul_rn(v[j], r);
-        }
+        for (int j = 0; j < N; j += 2) mul2(v[j], v[j + 1], r);
     } else {
 #pragma unroll
         for (int j = 0; j < N; ++j) v[j] = __fdiv_rn(v[j], s);
@@ -217,8 +235,8 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
             for (int k = 0; k < 8; ++k) {
                 uint32_t a, b;
                 if (TK == TK_LUT) {
-                    a = ld_u16<SM>(t.lut16, p[(2 * k) % N]);
-                    b = ld_u16<SM>(t.lut16, p[(2 * k + 1) % N]);
+                    a = tab_u16<SM>(s16, t.lut16, p[(2 * k) % N]);
+                    b = tab_u16<SM>(s16, t.lut16, p[(2 * k + 1) % N]);
                 } else {
                     a = __float_as_uint(int_round(t, __uint_as_float(p[(2 * k) % N] << 16))) >> 16;
                     b = __float_as_uint(int_round(t, __uint_as_float(p[(2 * k + 1) % N] << 16))) >> 16;
@@ -228,7 +246,7 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
         } else {
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                if (TK == TK_LUT) o[k] = ld_u16<SM>(t.lut16, p[k]) << 16;
+                if (TK == TK_LUT) o[k] = tab_u16<SM>(s16, t.lut16, p[k]) << 16;
                 else o[k] = __float_as_uint(int_round(t, __uint_as_float(p[k] << 16)));
             }
         }
@@ -248,7 +266,7 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const Chunk& x, flo
 #pragma unroll
         for (int j = 0; j < N; ++j) {
             if (TK == TK_LUT) {
-                c[j] = ld_u8<SM>(t.lut8, p[j]);
+                c[j] = tab_u8<SM>(s8, t.lut8, p[j]);
             } else {
                 float a = int_round(t, __uint_as_float(p[j] << 16));
                 c[j] = (a != a) ? 0u : ((uint32_t)(int)a & (OUT == OUT_PACK4 ? 0xFu : 0xFFu));

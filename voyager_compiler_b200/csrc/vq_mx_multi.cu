@@ -105,7 +105,9 @@ struct FastParams {
     int iters;                   // inner iterations per tile (one tensor lookup per tile)
 };
 
-template <typename T, int RULE, int TK, int OUT, bool SM, int U>
+// GS > 0: the number of lanes per block is 2^GS, known at compile time (the usual block sizes);
+// GS == 0: taken from the parameters.
+template <typename T, int RULE, int TK, int OUT, bool SM, int U, int GS>
 __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant__ FastParams p) {
     extern __shared__ uint4 smem[];
     FastTab ft;
@@ -116,16 +118,15 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant
     ft.lo_is_zero = (p.tab.lo == 0.0f) ? 1 : 0;
     ft.flat_tiny = p.tab.flat_tiny;
     if (SM && TK == TK_LUT) {
+        // the table (values or packed codes, whichever this output set reads) sits at offset 0
         const bool wide = OUT == OUT_FLOAT || OUT == OUT_FAKEQ;
         const uint4* src = reinterpret_cast<const uint4*>(wide ? (const void*)p.tab.lut16 : (const void*)p.tab.lut8);
         const int n16 = wide ? 8192 : 4096;
         for (int i = threadIdx.x; i < n16; i += blockDim.x) smem[i] = __ldg(src + i);
-        if (wide) ft.lut16 = reinterpret_cast<const uint16_t*>(smem);
-        else ft.lut8 = reinterpret_cast<const uint8_t*>(smem);
         __syncthreads();
     }
     constexpr int N = sizeof(T) == 2 ? 16 : 8;   // elements per 32-byte chunk
-    const int gs = p.group_shift;
+    const int gs = GS > 0 ? GS : p.group_shift;
     const uint32_t sub_chunks = blockDim.x * U;               // chunks per inner iteration
     const uint32_t tile_chunks = sub_chunks * p.iters;     // chunks per tile (one tensor lookup)
     const bool refine = p.allow_refine != 0;
@@ -192,7 +193,12 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant
             const uint32_t ci = c0 + u * blockDim.x;
             bool safe;
             uint32_t m = chunk_amax<T>(x[u], safe, refine && !ft.flat_tiny);
-            for (int o = 1; o < (1 << gs); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            if (GS > 0) {
+#pragma unroll
+                for (int o = 1; o < (1 << GS); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            } else {
+                for (int o = 1; o < (1 << gs); o <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            }
             if (ci >= nchunk) continue;
             const float s = fast_scale<T, RULE>(p.rule, m);
             if ((ci & ((1u << gs) - 1u)) == 0) {
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant
                 }
             }
             if (OUT != OUT_SCALE)
-                fast_chunk<T, TK, OUT == OUT_SCALE ? OUT_FLOAT : OUT, SM>(ft, x[u], s, refine && safe, (size_t)ci, out_codes, codes8);
+                fast_chunk<T, TK, OUT == OUT_SCALE ? OUT_FLOAT : OUT, SM>(ft, smem, x[u], s, refine && safe, (size_t)ci, out_codes, codes8);
         }
         }
     }
@@ -213,7 +219,10 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant
 
 template <typename T, int RULE, int TK, int OUT, bool SM>
 int launch_fast2(const FastParams& p, int threads, int blocks, size_t smem, cudaStream_t st) {
-    auto k = mx_fast2_kernel<T, RULE, TK, OUT, SM, 2>;
+    // blocks of 2 or 4 chunks (32 / 64 elements) have the lane-group reduction unrolled
+    auto k = p.group_shift == 1   ? mx_fast2_kernel<T, RULE, TK, OUT, SM, 2, 1>
+             : p.group_shift == 2 ? mx_fast2_kernel<T, RULE, TK, OUT, SM, 2, 2>
+                                  : mx_fast2_kernel<T, RULE, TK, OUT, SM, 2, 0>;
     if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<blocks, threads, smem, st>>>(p);
     VQ_LAUNCH_CHECK("mx_fast2_kernel");

@@ -106,6 +106,126 @@ def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
     return out.reshape(*lead, N)
 
 
+def native_kn_supported(a, b, bias) -> bool:
+    """Right operand in ``[.., K, N]`` order (``matmul_mx``, ``"ck"`` weights): bf16, K a multiple of 8, N even,
+    and batch dimensions that are either equal on both sides or absent on the right."""
+    if _mode() == "cublas":
+        return False
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.ndim < 2 or b.ndim < 2:
+        return False
+    K, N = b.shape[-2], b.shape[-1]
+    if a.shape[-1] != K or K % 8 or K == 0 or N % 2:
+        return False
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.ndim != 1 or bias.shape[0] != N):
+        return False
+    if b.ndim == 2 or all(d == 1 for d in b.shape[:-2]):
+        return True
+    return tuple(a.shape[:-2]) == tuple(b.shape[:-2])
+
+
+_kn_weights: Dict[tuple, tuple] = {}
+
+
+def _decode_transposed(name, b, b_code, b_scale, block_size):
+    """``[batch, N, K]`` bf16: ``deq(b)`` of a ``[batch, K, N]`` operand, transposed by the decode kernel."""
+    from . import ops
+
+    K, N = b.shape[-2], b.shape[-1]
+    batch = b.numel() // (K * N) if K * N else 0
+    x = b.contiguous()
+    if b_code is not None:
+        x = ops._decode_operand(name, x, b_code, None, None)
+    sc, rows = None, 0
+    if b_scale is not None:
+        want = tuple(b.shape[:-2]) + (-(-K // block_size) if block_size else 0, N)
+        if block_size and block_size % 2 == 0 and b_scale.dtype == torch.bfloat16 and tuple(b_scale.shape) == want:
+            sc, rows = b_scale.contiguous(), want[-2]
+        else:                                                        # any other scale placement: the general decode first
+            x = ops.dequantize(x, b_scale, None, None, block_size)
+    out = torch.empty((batch, N, K), dtype=torch.bfloat16, device=b.device)
+    if out.numel():
+        with torch.cuda.device(b.device):
+            rc = _lib.lib.vq_dequantize_transpose(x.data_ptr(), sc.data_ptr() if sc is not None else None, batch, K, N,
+                                                  block_size or 0, rows, out.data_ptr(),
+                                                  torch.cuda.current_stream(b.device).cuda_stream)
+            _lib.check(rc, name)
+    return out
+
+
+def native_batched_nk_supported(a, b) -> bool:
+    """``matmul_mx(..., weight_layout="kc")`` on batched operands: right operand ``[.., N, K]`` with the batch
+    dimensions of the left one."""
+    if _mode() == "cublas" or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.ndim < 3 or b.ndim < 3:
+        return False
+    K = a.shape[-1]
+    return K == b.shape[-1] and K % 8 == 0 and K > 0 and tuple(a.shape[:-2]) == tuple(b.shape[:-2])
+
+
+def native_mx_gemm_batched_nk(name, a, b, a_scale, b_scale, block_size, a_code, b_code):
+    from . import ops
+
+    K, M, N = a.shape[-1], a.shape[-2], b.shape[-2]
+    da = ops._decode_operand(name, a, a_code, a_scale, block_size).contiguous()
+    db = ops._decode_operand(name, b, b_code, b_scale, block_size).contiguous()
+    out = torch.empty(tuple(a.shape[:-1]) + (N,), dtype=torch.bfloat16, device=a.device)
+    batch = out.numel() // (M * N) if M * N else 0
+    if out.numel():
+        with torch.cuda.device(a.device):
+            rc = _lib.lib.vq_gemm_bf16_tn_batched(da.data_ptr(), db.data_ptr(), out.data_ptr(), batch, M, N, K, 0, 0,
+                                                  _status_tensor(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
+            _lib.check(rc, name)
+        _debug_check(a.device, name)
+    return out
+
+
+def native_mx_gemm_kn(name, a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
+    """``deq(a) @ deq(b)`` with ``b`` in ``[.., K, N]`` order on the tcgen05 GEMM: ``b`` is decoded into
+    ``[batch, N, K]`` by one kernel, ``a`` by the dequantize kernel, and one persistent launch walks
+    the output tiles of all batches.  A 2-D ``b`` (a ``"ck"`` weight) is shared by every row of ``a``;
+    its decoded form is kept between calls, keyed by the identity and version of its tensors."""
+    import weakref
+    from . import ops
+
+    K, N = b.shape[-2], b.shape[-1]
+    shared_b = b.ndim == 2 or all(d == 1 for d in b.shape[:-2])
+    lead = tuple(a.shape[:-1])
+    if shared_b:
+        parts = [t for t in (b, b_scale, b_code) if t is not None]
+        key = tuple((id(t), t._version, t.data_ptr()) for t in parts) + (block_size,)
+        hit = _kn_weights.get(key)
+        if hit is not None and all(r() is t for r, t in zip(hit[0], parts)):
+            bt = hit[1]
+        else:
+            bt = _decode_transposed(name, b.reshape(K, N), b_code, b_scale.reshape(-1, N) if b_scale is not None and b_scale.ndim >= 2 else b_scale,
+                                    block_size)
+            if len(_kn_weights) >= 8:
+                _kn_weights.pop(next(iter(_kn_weights)))
+            _kn_weights[key] = ([weakref.ref(t) for t in parts], bt)
+        batch, M = 1, a.numel() // K
+    else:
+        bt = _decode_transposed(name, b, b_code, b_scale, block_size)
+        batch, M = bt.shape[0], a.shape[-2]
+    da = ops._decode_operand(name, a, a_code, a_scale, block_size).contiguous()
+    out = torch.empty(lead + (N,), dtype=torch.bfloat16, device=a.device)
+    if out.numel() == 0:
+        return out
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    with torch.cuda.device(a.device):
+        st = _status_tensor(a.device)
+        if batch == 1:
+            bias_c = bias.contiguous() if bias is not None else None
+            rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), bt.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                          out.data_ptr(), M, N, K, st.data_ptr(), stream)
+        else:
+            rc = _lib.lib.vq_gemm_bf16_tn_batched(da.data_ptr(), bt.data_ptr(), out.data_ptr(), batch, M, N, K, 0, 0,
+                                                  st.data_ptr(), stream)
+        _lib.check(rc, name)
+    _debug_check(a.device, name)
+    if batch > 1 and bias is not None:
+        out = out + bias
+    return out
+
+
 def linear_mx_dynamic(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, qmap: torch.Tensor,
                       weight_scale: Optional[torch.Tensor] = None, block_size: int = 32, quant_max: float = 127.0,
                       force_scale_power_of_two: bool = True, scale_qmap: Optional[torch.Tensor] = None,

@@ -265,8 +265,11 @@ class ChannelQuantPlan:
         self._keep = []
         with torch.cuda.device(device):
             self._tab = table_handle(qmap, device)
-            if want_codes:
-                self._tab.with_codes()
+            try:
+                self._tab.with_codes()          # code table + levels by (code, sign): the pipelined kernel's tables
+            except ValueError:
+                if want_codes:
+                    raise
             for dt in (torch.bfloat16, torch.float32):
                 idx = [i for i, t in enumerate(tensors) if t.dtype == dt]
                 if not idx:
@@ -308,15 +311,31 @@ class ChannelQuantPlan:
                     self._keep.append(t)
                 need = _lib.lib.vq_channel_quantize_multi_workspace(items, len(idx))
                 ws = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
-                self._groups.append((items, len(idx), _DT[dt], ws))
+                handle = C.c_void_p()
+                _lib.check(_lib.lib.vq_channel_plan_create(items, len(idx), _DT[dt], self.quant_max, self._tab.ptr(),
+                                                           ws.data_ptr(), ws.numel(),
+                                                           torch.cuda.current_stream(device).cuda_stream, C.byref(handle)),
+                           "quantize_tensors_per_channel")
+                self._groups.append((handle, ws))
 
     def run(self) -> List[ChannelQuant]:
+        """One kernel launch per dtype on the current stream (descriptors were uploaded at construction)."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         with torch.cuda.device(self.device):
-            stream = torch.cuda.current_stream(self.device).cuda_stream
-            for items, n, dt, ws in self._groups:
-                _lib.check(_lib.lib.vq_channel_quantize_multi(items, n, dt, self.quant_max, self._tab.ptr(),
-                                                              ws.data_ptr(), ws.numel(), stream), "quantize_tensors_per_channel")
+            for handle, _ in self._groups:
+                _lib.check(_lib.lib.vq_channel_plan_run(handle, stream), "quantize_tensors_per_channel")
         return self.results
+
+    def close(self) -> None:
+        for handle, _ in self._groups:
+            _lib.lib.vq_channel_plan_destroy(handle)
+        self._groups = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass
 
 
 def quantize_tensors_per_channel(tensors: Sequence[torch.Tensor], qmap, quant_max: float, *, scales=None,

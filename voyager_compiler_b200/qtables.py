@@ -107,6 +107,10 @@ class TableHandle:
             self._lut8 = torch.from_numpy(codes.copy()).to(self.device)
             if self.c.kind != _lib.TABLE_INT:
                 self.c.lut8 = self._lut8.data_ptr()
+                lv2 = tables.levels_by_code_and_sign(an.lut16, codes)
+                if lv2 is not None:
+                    self._levels2 = torch.from_numpy(lv2).to(self.device)
+                    self.c.levels2 = self._levels2.data_ptr()
             if self.c.kind == _lib.TABLE_RUNS:
                 rc = codes[an.run_first]
                 self._run_codes = torch.from_numpy(np.ascontiguousarray(rc)).to(self.device)

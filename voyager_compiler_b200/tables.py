@@ -383,3 +383,18 @@ def code_table(lut16: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
         codes = np.searchsorted(levels, np.where(nan, levels[0], vals)).astype(np.int64)
         codes = np.where(nan, levels.size if levels.size < 256 else 0, codes)
     return codes.astype(np.uint8), levels
+
+
+def levels_by_code_and_sign(lut16: np.ndarray, codes: np.ndarray) -> Optional[np.ndarray]:
+    """fp32[512]: the table's output for packed code ``c`` and an input without / with the sign bit
+    at ``[c]`` / ``[256 + c]``, when the output is a function of (code, input sign) alone -- i.e.
+    ``lut16[p] == out[codes[p] + 256 * (p >> 15)]`` for every pattern ``p`` (signed zeros and NaN
+    payloads compared by bits).  ``None`` when it is not (e.g. 256 levels plus a NaN output that had to
+    share a code)."""
+    lut16 = np.ascontiguousarray(lut16, dtype=np.uint16)
+    idx = codes.astype(np.int64) + 256 * (np.arange(1 << 16) >> 15)
+    out = np.zeros(512, dtype=np.uint16)
+    out[idx] = lut16                      # any representative; checked below
+    if not np.array_equal(out[idx], lut16):
+        return None
+    return bf16_bits_to_f32(out).astype(np.float32)
