@@ -119,8 +119,14 @@ __device__ __forceinline__ uint32_t chunk_amax<float>(const Chunk& x, bool& safe
     return m;
 }
 
+// RULE 0: amax / quant_max (optionally through a scale table); 1: power of two; 2: quant_max is 1 and
+// there is no scale table, so the scale is the block maximum itself (1 where that is 0 or NaN).
 template <typename T, int RULE>
 __device__ __forceinline__ float fast_scale(const ScaleRule& r, uint32_t amax_bits) {
+    if (RULE == 2) {
+        const float a = __uint_as_float(amax_bits);
+        return (a > 0.0f) ? a : 1.0f;                   // NaN compares false
+    }
     if (amax_bits > 0x7F800000u) return 1.0f;
     if (RULE == 1) {
         if (amax_bits == 0x7F800000u) return __uint_as_float(0x7F800000u);
@@ -210,12 +216,15 @@ __device__ __forceinline__ void fast_chunk(const FastTab& t, const void* stab, c
     }
     const uint32_t sb = __float_as_uint(s);
     const uint32_t ex = (sb >> 23) & 0xFFu;
-    if ((sb & 0x807FFFFFu) == 0u && ex >= 2u && ex <= 252u) {
-        const float r = __uint_as_float((254u - ex) << 23);
+    // bf16 data, positive scale in [2^-63, 2^63], no tiny element: one reciprocal multiply (see the
+    // header; a power-of-two scale is just a special case of it).  sb - 2^-63 < 2^63 - 2^-63 as
+    // unsigned integers is that range test (a negative scale wraps to the top).
+    if (sizeof(T) == 2 && refine_ok && sb - 0x20000000u < 0x3F800000u) {
+        const float r = rcp_approx(s);
 #pragma unroll
         for (int j = 0; j < N; j += 2) mul2(v[j], v[j + 1], r);
-    } else if (sizeof(T) == 2 && refine_ok && (sb >> 31) == 0u && ex >= 64u && ex <= 190u) {
-        const float r = rcp_approx(s);
+    } else if ((sb & 0x807FFFFFu) == 0u && ex >= 2u && ex <= 252u) {
+        const float r = __uint_as_float((254u - ex) << 23);
 #pragma unroll
         for (int j = 0; j < N; j += 2) mul2(v[j], v[j + 1], r);
     } else {

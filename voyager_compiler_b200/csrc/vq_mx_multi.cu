@@ -257,6 +257,10 @@ int dispatch_rule(const FastParams& p, int rule, int tk, int out, bool sm, int t
         return tk == TK_INT ? dispatch_out<T, 1, TK_INT>(p, out, sm, threads, blocks, smem, st)
                             : dispatch_out<T, 1, TK_LUT>(p, out, sm, threads, blocks, smem, st);
     }
+    if (p.rule.qmax == 1.0f && p.rule.stab.kind == VQ_TABLE_NONE) {      // the scale is the block maximum itself
+        return tk == TK_INT ? dispatch_out<T, 2, TK_INT>(p, out, sm, threads, blocks, smem, st)
+                            : dispatch_out<T, 2, TK_LUT>(p, out, sm, threads, blocks, smem, st);
+    }
     return tk == TK_INT ? dispatch_out<T, 0, TK_INT>(p, out, sm, threads, blocks, smem, st)
                         : dispatch_out<T, 0, TK_LUT>(p, out, sm, threads, blocks, smem, st);
 }

@@ -42,6 +42,15 @@ class PackedMX:
     levels: torch.Tensor
     exp_e8: Optional[torch.Tensor] = None
 
+    def levels_on(self, device) -> torch.Tensor:
+        """fp32 levels on ``device`` (copied once per device and kept)."""
+        cache = self.__dict__.setdefault("_levels_dev", {})
+        key = str(device)
+        t = cache.get(key)
+        if t is None:
+            t = cache[key] = self.levels.to(device, torch.float32).contiguous()
+        return t
+
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (str(device), torch.cuda.current_stream(device).cuda_stream)
@@ -366,7 +375,7 @@ def dequantize_packed(p: PackedMX, dtype=torch.float32, use_exponent: bool = Fal
     if use_exponent and p.exp_e8 is None:
         raise ValueError("this PackedMX carries no exponents")
     with torch.cuda.device(dev):
-        levels = p.levels.to(dev, torch.float32).contiguous()
+        levels = p.levels_on(dev)
         rc = _lib.lib.vq_dequantize_packed(
             p.codes.data_ptr(), p.code_bits, levels.data_ptr(), levels.numel(),
             None if use_exponent else p.scale.data_ptr(), p.exp_e8.data_ptr() if use_exponent else None,
