@@ -145,3 +145,35 @@ def test_converted_graph_runs_on_cuda_like_upstream_on_cpu(case):
     fake = _tensor(case, "fake_quant_out").double()
     rel = ((out.double().cpu() - fake).norm() / fake.norm()).item()
     assert rel <= 2e-2, rel
+
+
+def test_fuse_dynamic_linear_rewrites_only_the_matching_node_groups():
+    """Graph surgery is host work: the pass is checked on the stored graphs without running them."""
+    from voyager_compiler_b200 import compat, gemm_native
+    want = {"linear_int8_int8_bf16": 1, "linear_int8_nf4_codebook_bf16": 1, "linear_fp8_int8_f32_3d": 1,
+            "linear_int8_outliers_bf16": 0, "matmul_int8_int8_bf16": 0}
+    for case in CASES:
+        gm = _rebuild(case, "cpu")
+        assert compat.fuse_dynamic_linear(gm) == want[case["name"]], case["name"]
+        targets = [n.target for n in gm.graph.nodes if n.op == "call_function"]
+        if want[case["name"]]:
+            assert targets == [gemm_native.linear_mx_dynamic]
+            (n,) = [n for n in gm.graph.nodes if n.op == "call_function"]
+            assert n.kwargs["block_size"] == 32 and n.kwargs["force_scale_power_of_two"] is True
+        assert compat.fuse_dynamic_linear(gm) == 0                  # idempotent
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [c for c in CASES if c["name"] in ("linear_int8_int8_bf16", "linear_int8_nf4_codebook_bf16")],
+                         ids=lambda c: c["name"])
+def test_fused_dynamic_linear_equals_the_two_node_form_bitwise(case):
+    import voyager_compiler_b200  # noqa: F401
+    from voyager_compiler_b200 import compat
+    x = _tensor(case, "x").cuda()
+    plain = _rebuild(case, "cuda")
+    want = plain(x)
+    fused = _rebuild(case, "cuda")
+    assert compat.fuse_dynamic_linear(fused) == 1
+    got = fused(x)
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))

@@ -163,3 +163,65 @@ def unpatch_reference() -> None:
     while _PATCHED:
         mod, n, fn = _PATCHED.pop()
         setattr(mod, n, fn)
+
+
+# ---------------------------------------------------------------------------------------------
+def fuse_dynamic_linear(gm: "torch.fx.GraphModule") -> int:
+    """Graph pass over a converted model: the node group the converter emits for a dynamically
+    quantized linear (quantization/quantize_pt2e.py:431-712),
+
+        q = quantized_ops.quantize_mx(x, qmap, (-1,), block, quant_max, pow2, scale_qmap, None)
+        s, c = q[0], q[1]
+        y = quantized_ops.linear_mx(c, w, bias, input_scale=s, weight_scale=ws, block_size=block, ...)
+
+    becomes one call of :func:`voyager_compiler_b200.gemm_native.linear_mx_dynamic` when nothing else
+    reads the codes or the scale: the activation's ``codes * scale`` are then written straight into the
+    GEMM's left operand by one pass instead of travelling through HBM as two tensors and back.  The
+    result is bit-identical.  Nodes that do not match (other block axes, a codebook on the activation,
+    the sparse outlier side path, a ``"ck"`` weight) are left as they are.  Returns the number of
+    fused linears; the module is recompiled when that is not zero."""
+    import operator
+
+    from .gemm_native import linear_mx_dynamic
+
+    Q = torch.ops.quantized_ops
+    fused = 0
+    for lin in list(gm.graph.nodes):
+        if lin.op != "call_function" or lin.target is not Q.linear_mx.default:
+            continue
+        kw = dict(lin.kwargs)
+        codes, scale = lin.args[0], kw.get("input_scale")
+        if not (isinstance(codes, torch.fx.Node) and isinstance(scale, torch.fx.Node)):
+            continue
+        if codes.target is not operator.getitem or scale.target is not operator.getitem:
+            continue
+        q = codes.args[0]
+        if q is not scale.args[0] or codes.args[1] != 1 or scale.args[1] != 0:
+            continue
+        if not (isinstance(q, torch.fx.Node) and q.op == "call_function" and q.target is Q.quantize_mx.default):
+            continue
+        if set(codes.users) != {lin} or set(scale.users) != {lin} or set(q.users) != {codes, scale}:
+            continue
+        qa = list(q.args) + [None] * (8 - len(q.args))
+        x, qmap, axes, block, qmax, pow2, scale_qmap, out_code = qa[:8]
+        pow2 = q.kwargs.get("force_scale_power_of_two", pow2 if pow2 is not None else False)
+        scale_qmap = q.kwargs.get("scale_qmap", scale_qmap)
+        axes = tuple(axes) if isinstance(axes, (list, tuple)) else (axes,)
+        if axes != (-1,) or kw.get("block_size") != block or kw.get("input_code") is not None:
+            continue
+        if any(kw.get(k) is not None for k in ("A_data", "A_indices", "A_indptr")) or kw.get("weight_layout", "kc") != "kc":
+            continue
+        bias = lin.args[2] if len(lin.args) > 2 else None
+        with gm.graph.inserting_before(lin):
+            new = gm.graph.call_function(linear_mx_dynamic, (x, lin.args[1], bias), {
+                "qmap": qmap, "weight_scale": kw.get("weight_scale"), "block_size": block, "quant_max": qmax,
+                "force_scale_power_of_two": bool(pow2), "scale_qmap": scale_qmap, "weight_code": kw.get("weight_code")})
+        new.meta = dict(lin.meta)
+        lin.replace_all_uses_with(new)
+        for dead in (lin, codes, scale, q):
+            gm.graph.erase_node(dead)
+        fused += 1
+    if fused:
+        gm.graph.lint()
+        gm.recompile()
+    return fused

@@ -69,6 +69,42 @@ def native_supported(a, b, bias, a_scale, b_scale, block_size, a_code, b_code, b
     return K == b.shape[1] and K % 8 == 0 and K > 0
 
 
+_decoded_weights: Dict[tuple, tuple] = {}
+
+
+def _weight_cache_entries() -> int:
+    """How many decoded weights are kept between calls (``VOYAGER_B200_WEIGHT_CACHE``, default 8; 0 disables)."""
+    try:
+        return max(0, int(os.environ.get("VOYAGER_B200_WEIGHT_CACHE", "8")))
+    except ValueError:
+        return 8
+
+
+def _decoded_weight(name, b, b_code, b_scale, block_size):
+    """``deq(b)`` of a 2-D ``[N, K]`` linear weight.  Weights are static buffers of the converted graph, so
+    the last few decoded copies are kept, keyed by the identity, address and version counter of the tensors
+    involved (weak references: an entry is never used for another tensor that reuses the address; an
+    in-place update of the weight bumps its version and misses)."""
+    import weakref
+    from . import ops
+
+    limit = _weight_cache_entries()
+    if b_scale is None and b_code is None:
+        return b.contiguous()
+    if limit == 0:
+        return ops._decode_operand(name, b, b_code, b_scale, block_size).contiguous()
+    parts = [t for t in (b, b_scale, b_code) if t is not None]
+    key = tuple((id(t), t.data_ptr(), t._version) for t in parts) + (block_size,)
+    hit = _decoded_weights.get(key)
+    if hit is not None and all(r() is t for r, t in zip(hit[0], parts)):
+        return hit[1]
+    db = ops._decode_operand(name, b, b_code, b_scale, block_size).contiguous()
+    while len(_decoded_weights) >= limit:
+        _decoded_weights.pop(next(iter(_decoded_weights)))
+    _decoded_weights[key] = ([weakref.ref(t) for t in parts], db)
+    return db
+
+
 def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
     from . import ops
 
@@ -98,7 +134,7 @@ def native_mx_gemm(a, b, bias, a_scale, b_scale, block_size, a_code, b_code):
             _lib.check(rc, "linear_mx")
         else:
             da = ops._decode_operand("linear_mx", a2, a_code, a_sc2, block_size).contiguous()
-            db = ops._decode_operand("linear_mx", b, b_code, b_scale, block_size).contiguous()
+            db = _decoded_weight("linear_mx", b, b_code, b_scale, block_size)
             rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
                                           out.data_ptr(), M, N, K, st.data_ptr(), stream)
             _lib.check(rc, "linear_mx")
@@ -239,13 +275,17 @@ def linear_mx_dynamic(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torc
     without the round trip of codes and scales through HBM: one pass writes ``codes * scale`` of the
     activation straight into the GEMM's left operand (the MX fake-quantize form of the quantize kernel), the
     weight is decoded as ``linear_mx`` decodes it, then the tcgen05 GEMM runs.  Bit-identical to the two ops.
-    bf16 ``x`` of shape [..., K] and ``weight`` [N, K] with K a multiple of 8."""
+    The one-pass form takes bf16 ``x`` of shape [..., K] and ``weight`` [N, K] with K a multiple of 8;
+    anything else runs as the two ops."""
     from . import fake_quantize, ops
 
     if x.device.type != "cuda":
         raise RuntimeError("linear_mx_dynamic: CUDA tensors only; there is no CPU path")
     if not native_supported(x, weight, bias, None, weight_scale, block_size, None, weight_code, True):
-        raise NotImplementedError("linear_mx_dynamic: bf16 activation [..., K] and weight [N, K] with K a multiple of 8")
+        # shapes / dtypes the one-pass form does not take (fp32 operands, K not a multiple of 8): the two ops
+        s, q = ops.quantize_mx(x, qmap, (-1,), block_size, quant_max, force_scale_power_of_two, scale_qmap)
+        return ops.linear_mx(q, weight, bias, input_scale=s, weight_scale=weight_scale, block_size=block_size,
+                             weight_code=weight_code)
     K, N = x.shape[-1], weight.shape[0]
     lead = x.shape[:-1]
     M = x.numel() // K if K else 0
@@ -255,7 +295,7 @@ def linear_mx_dynamic(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torc
     _, da = fake_quantize.mx_fake_quantize(x.reshape(M, K), qmap, -1, block_size, quant_max, force_scale_power_of_two, scale_qmap)
     bias_c = bias.contiguous() if bias is not None else None
     with torch.cuda.device(x.device):
-        db = ops._decode_operand("linear_mx", weight, weight_code, weight_scale, block_size).contiguous()
+        db = _decoded_weight("linear_mx", weight, weight_code, weight_scale, block_size)
         rc = _lib.lib.vq_gemm_bf16_tn(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
                                       out.data_ptr(), M, N, K, _status_tensor(x.device).data_ptr(),
                                       torch.cuda.current_stream(x.device).cuda_stream)
