@@ -390,9 +390,10 @@ def run_extras_multi(dev, world, rank, iters=10):
 
     out["cfg5_single_gpu_linear_mx"] = entry(timed(lambda: Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32)))
     out["cfg5_column_shard_gemm_only"] = entry(timed(lambda: Q.linear_mx(xq, wq_r, None, input_scale=xs, weight_scale=ws_r, block_size=32)))
-    y = par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32)
-    out["cfg5_column_parallel_nccl_all_gather"] = entry(timed(lambda: par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32)),
-                                                        bool(torch.equal(y, y1)))
+    lin = par.ColumnParallelLinearMX(wq_r, ws_r, N, 32)          # all-gather in pieces, overlapped with the next piece's GEMM
+    y = lin(xq, xs)
+    out["cfg5_column_parallel_nccl_all_gather"] = entry(timed(lambda: lin(xq, xs)), bool(torch.equal(y, y1)))
+    out["cfg5_column_parallel_nccl_all_gather"]["pieces"] = len(lin.pieces)
     ok = torch.ones(1, device=dev)
     p2p = None
     try:

@@ -399,6 +399,17 @@ VQ_API int vq_spmm_csr(const void* data, const int32_t* indices, const int32_t* 
                        int64_t batch, int64_t rows, int64_t K, int64_t N, int64_t max_nnz, int64_t bt_batch_stride,
                        const void* addend, void* Y, void* stream);
 
+/* `slice_csr_tensor`, src/voyager_compiler/ops/quantized.py:745-788, without its three host read-backs: rows
+ * (dim 0) or columns (dim 1) [start, end) of a padded CSR (`data` / `indices` of max_nnz entries, int32 `indptr`
+ * of rows + 1 entries).  Outputs: `cap` entries (upstream: int(max_nnz * size_factor)) padded with 0 / -1, and the
+ * row pointers of the slice (dim 0: end - start + 1 entries rebased to 0; dim 1: rows + 1 entries, column indices
+ * rebased to `start`); when more entries survive than fit, the surplus is dropped and the row pointers are clamped
+ * to `cap`, as upstream's _pad_csr does.  dim 1 needs vq_slice_csr_workspace(rows) bytes of device scratch. */
+VQ_API size_t vq_slice_csr_workspace(int64_t rows);
+VQ_API int vq_slice_csr(const void* data, const int32_t* indices, const int32_t* indptr, int dtype, int64_t rows,
+                        int64_t max_nnz, int dim, int64_t start, int64_t end, int64_t cap, void* out_data,
+                        int32_t* out_indices, int32_t* out_indptr, void* workspace, size_t workspace_bytes, void* stream);
+
 /* One tensor of a per-channel pass, viewed as [channels, length] (a conv weight OIHW is
  * [O, I*H*W]).  Every output may be NULL, at least one must not be.  All tensors in `dtype`. */
 typedef struct vq_channel_item {

@@ -69,6 +69,10 @@ def _worker(rank, world, port, ret):
         got = par.column_parallel_linear_mx(xq, xs, wq_r, ws_r, N, 32, bias_shard=bias[n0:n1], gemm=vo.linear_mx)
         want = vo.linear_mx(xq, wq, bias, input_scale=xs, weight_scale=wsc, block_size=32)
         assert got.shape == want.shape and torch.equal(got, want)
+        # the prepared form, exchanged in two pieces (512 + 88 columns on rank 0's side, 88 + 0 on rank 1's)
+        lin = par.ColumnParallelLinearMX(wq_r, ws_r, N, 32, bias_shard=bias[n0:n1], gemm=vo.linear_mx, chunks=2)
+        assert len(lin.pieces) == 2
+        assert torch.equal(lin(xq, xs), want) and torch.equal(lin(xq, xs), want)
         ret[rank] = "ok"
     except Exception as e:  # noqa: BLE001
         import traceback

@@ -92,10 +92,9 @@ def test_oracle_quantize_mx_outlier_spmm_and_linear_match_upstream():
 
 
 @pytest.mark.parametrize("dim,a,b", [(0, 4, 20), (1, 32, 96)])
-def test_slice_csr_matches_upstream(dim, a, b):
-    from voyager_compiler_b200 import ops
+def test_oracle_slice_csr_matches_upstream(dim, a, b):
     L = _lin()
-    sd, si, sp = ops.slice_csr_tensor(L["data"], L["indices"], L["indptr"].clone(), dim, a, b, 1.0)
+    sd, si, sp = vo.slice_csr_tensor(L["data"], L["indices"], L["indptr"].clone(), dim, a, b, 1.0)
     assert same(sd, ft(f"slice{dim}/data", "bf16")) and torch.equal(si.to(torch.int32), it(f"slice{dim}/indices").to(torch.int32))
     assert torch.equal(sp.to(torch.int32), it(f"slice{dim}/indptr").to(torch.int32))
 
@@ -171,3 +170,36 @@ def test_spmm_batched_and_ck_layout_against_oracle():
     Bs = torch.randn(70, 96)                                    # "kc": [N, K] shared by the batches
     got = ops.spmm_csr(d.cuda(), i.cuda(), p.cuda(), Bs.cuda(), None, None, None, "kc")
     assert _rel(got, vo.spmm_csr(d, i, p, Bs, None, None, None, "kc")) < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,a,b", [(0, 4, 20), (1, 32, 96)])
+def test_kernel_slice_csr_matches_upstream(dim, a, b):
+    """The device-side slice (no host read-back) against upstream's vectors, op function and dispatcher."""
+    from voyager_compiler_b200 import ops
+    L = _lin()
+    args = (L["data"].cuda(), L["indices"].cuda(), L["indptr"].cuda())
+    for fn in (ops.slice_csr_tensor, torch.ops.quantized_ops.slice_csr_tensor):
+        sd, si, sp = fn(*args, dim, a, b, 1.0)
+        assert same(sd, ft(f"slice{dim}/data", "bf16")) and torch.equal(si.cpu(), it(f"slice{dim}/indices").to(torch.int32))
+        assert torch.equal(sp.cpu(), it(f"slice{dim}/indptr").to(torch.int32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols,pct,factor", [(64, 128, 0.05, 1.0), (300, 77, 0.2, 0.5), (1, 40, 0.5, 1.0), (2000, 64, 0.02, 0.25),
+                                                  (17, 5000, 0.01, 2.0)])
+def test_kernel_slice_csr_matches_oracle(dtype, rows, cols, pct, factor):
+    """Random padded CSRs: empty rows, slices that keep nothing, and capacities smaller than what survives
+    (surplus dropped, row pointers clamped)."""
+    from voyager_compiler_b200 import ops
+    g = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=g).to(dtype)
+    x[rows // 2] = 0
+    d, i, p, _ = vo.filter_outlier(x, 1.0, pct)
+    for dim, a, b in ((0, 0, rows), (0, rows // 3, rows // 3), (0, rows // 4, rows - rows // 5), (1, 0, cols), (1, cols // 3, cols // 2),
+                      (1, cols - 1, cols), (-1, 3, 4)):
+        want = vo.slice_csr_tensor(d, i, p.clone(), dim, a, b, factor)
+        got = ops.slice_csr_tensor(d.cuda(), i.cuda(), p.cuda(), dim, a, b, factor)
+        assert same(got[0], want[0]), (dim, a, b)
+        assert torch.equal(got[1].cpu(), want[1].to(torch.int32)) and torch.equal(got[2].cpu(), want[2].to(torch.int32)), (dim, a, b)

@@ -105,6 +105,7 @@ def _load():
                             vp, i64, i64, i64, i64, i64, vp, i64, vp],
         "vq_dequantize_packed": [vp, ci, vp, ci, vp, vp, i64, i64, vp, ci, vp],
         "vq_gemm_bf16_tn": [vp, vp, vp, vp, i64, i64, i64, vp, vp],
+        "vq_slice_csr": [vp, vp, vp, ci, i64, i64, ci, i64, i64, i64, vp, vp, vp, vp, C.c_size_t, vp],
         "vq_gemm_bf16_tn_batched": [vp, vp, vp, i64, i64, i64, i64, ci, ci, vp, vp],
         "vq_dequantize_transpose": [vp, vp, i64, i64, i64, i64, i64, vp, vp],
         "vq_gemm_bf16_tn_scatter": [vp, vp, vp, C.POINTER(C.c_void_p), ci, i64, i64, i64, i64, i64, vp, vp],
@@ -132,6 +133,8 @@ def _load():
     lib.vq_channel_quantize_multi_workspace.restype = C.c_size_t
     lib.vq_filter_outlier_workspace.argtypes = [i64, i64]
     lib.vq_filter_outlier_workspace.restype = C.c_size_t
+    lib.vq_slice_csr_workspace.argtypes = [i64]
+    lib.vq_slice_csr_workspace.restype = C.c_size_t
     lib.vq_row_codebook_workspace.argtypes = [i64, ci]
     lib.vq_row_codebook_workspace.restype = C.c_size_t
     for name, args in sigs.items():

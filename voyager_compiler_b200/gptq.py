@@ -22,18 +22,22 @@ from .qtables import table_handle
 EPS = 1e-12                                      # quantization/lcq.py:34
 
 
+DAMPING_STEPS = (1.0, 10.0, 100.0, 1000.0, 10000.0)      # multiples of the requested damping that are tried in turn
+
+
 def hessian_inverse_chol(hessian: torch.Tensor, tokens: int, damping: float) -> torch.Tensor:
-    """Upper Cholesky factor of ``inv(H / tokens + damping * mean(diag) * I)``; the damping is raised tenfold,
-    up to 10^4 times, while the factorisation fails (gptq.py:30-70)."""
-    h = hessian / max(tokens, 1)
-    damp = damping * h.diagonal().mean().clamp_min(EPS)
-    applied = 0
-    for mult in (1, 10, 100, 1000, 10000):
-        h.diagonal().add_((mult - applied) * damp)
-        applied = mult
-        low, info = torch.linalg.cholesky_ex(h)
-        if int(info.item()) == 0:
-            return torch.linalg.cholesky(torch.cholesky_inverse(low), upper=True)
+    """Upper Cholesky factor ``U`` of ``inv(H / tokens + lambda * I)`` with ``lambda = damping * mean(diag)``
+    (what gptq.py:30-70 computes): the factorisation is attempted with ``lambda`` times 1, 10, ..., 10^4
+    until it succeeds; ``LinAlgError`` when even the strongest damping leaves the matrix indefinite.  The
+    factorisations are torch's (cuSOLVER) on the device of ``hessian``."""
+    mean_h = hessian / max(tokens, 1)
+    unit = damping * mean_h.diagonal().mean().clamp_min(EPS)
+    eye_diag = torch.ones_like(mean_h.diagonal())
+    for step in DAMPING_STEPS:
+        trial = mean_h + torch.diag_embed(eye_diag * (step * unit))
+        lower, failed = torch.linalg.cholesky_ex(trial)
+        if not bool(failed.any()):
+            return torch.linalg.cholesky(torch.cholesky_inverse(lower), upper=True)
     raise torch.linalg.LinAlgError("Hessian not positive-definite")
 
 
@@ -97,22 +101,20 @@ def walk(weight: torch.Tensor, hinv_chol: torch.Tensor, salience: Optional[torch
 def compensate_weight(weight, hessian, tokens, fake_quant, damping, act_order=True, within_block=True, shrink=False):
     """The GPTQ-compensated reconstruction of ``weight`` ``[out, in]`` on the grid ``fake_quant`` deploys
     (its ``qmap``, ``scale_qmap``, ``quant_max``, ``block_size`` and ``ch_axis``); same arguments and result as
-    upstream's ``compensate_weight`` (gptq.py:184-270)."""
-    block_size = fake_quant.block_size
-    axis = fake_quant.ch_axis
-    axis = axis[0] if isinstance(axis, (tuple, list)) else axis
-    if axis not in (-1, weight.dim() - 1):
-        raise ValueError(f"weight blocks run along axis {axis}, but the compensation walks the input channels of a "
+    upstream's ``compensate_weight`` (gptq.py:184-270).  Steps: walking order of the input channels (most salient
+    blocks first), the damped inverse factor in that order, the kernel's column walk, the columns put back."""
+    axes = fake_quant.ch_axis
+    block_axis = axes[0] if isinstance(axes, (tuple, list)) else axes
+    if block_axis % weight.dim() != weight.dim() - 1:
+        raise ValueError(f"weight blocks run along axis {block_axis}, but the compensation walks the input channels of a "
                          f"{tuple(weight.shape)} weight")
-    perm = salience_order(hessian, weight.shape[1], within_block, block_size) if act_order else None
-    if perm is not None:
-        hessian = hessian[perm][:, perm]
-        weight = weight[:, perm]
-    salience = hessian.diagonal().clone()
-    hinv = hessian_inverse_chol(hessian, tokens, damping)
-    out = walk(weight, hinv, salience, fake_quant.qmap, fake_quant.scale_qmap, fake_quant.quant_max, block_size, shrink)
-    if perm is None:
+    order = salience_order(hessian, weight.shape[1], within_block, fake_quant.block_size) if act_order else None
+    w_walk, h_walk = (weight, hessian) if order is None else (weight.index_select(1, order), hessian.index_select(0, order).index_select(1, order))
+    hinv = hessian_inverse_chol(h_walk, tokens, damping)
+    out = walk(w_walk, hinv, h_walk.diagonal().clone(), fake_quant.qmap, fake_quant.scale_qmap, fake_quant.quant_max,
+               fake_quant.block_size, shrink)
+    if order is None:
         return out
-    restored = torch.empty_like(out)
-    restored[:, perm] = out
-    return restored
+    back = torch.empty_like(order)
+    back[order] = torch.arange(order.numel(), device=order.device)
+    return out.index_select(1, back)

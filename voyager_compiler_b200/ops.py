@@ -377,39 +377,34 @@ def quantize_mx_outlier(input: torch.Tensor, qmap: torch.Tensor, axes: Sequence[
     return data, indices, indptr, scale, codes
 
 
-def _pad_csr(values, col_indices, crow_indices, max_nnz):
-    """ops/quantized.py:538-562 (the row pointers are clamped in place on overflow)."""
-    nse = int(crow_indices[-1].item())
-    pad = max_nnz - nse
-    if pad >= 0:
-        return torch.nn.functional.pad(values, (0, pad), value=0), torch.nn.functional.pad(col_indices, (0, pad), value=-1)
-    logger.warning("Number of outliers %d exceeds capacity %d; %d dropped.", nse, max_nnz, nse - max_nnz)
-    crow_indices.clamp_(max=max_nnz)
-    return values[:max_nnz], col_indices[:max_nnz]
-
-
 def slice_csr_tensor(data, indices, indptr, dim: int = 0, start=None, end=None, size_factor: float = 1.0):
-    """Rows or columns ``[start, end)`` of a padded CSR (ops/quantized.py:742-783).  Index bookkeeping
-    on arrays of at most max_nnz entries: done with torch operations on the tensors' device."""
+    """Rows (``dim`` 0) or columns (``dim`` 1) ``[start, end)`` of a padded CSR (ops/quantized.py:745-788) as one
+    to three kernel launches of ``vq_slice_csr``: nothing is read back to the host, so the call does not
+    synchronise.  The outputs hold ``int(data.shape[0] * size_factor)`` entries padded with 0 / -1; entries beyond
+    that capacity are dropped and the row pointers clamped, as upstream does (its warning about dropped entries
+    would need the count on the host and is not issued)."""
+    _require_cuda(data, "slice_csr_tensor")
     dim = dim + 2 if dim < 0 else dim
     if dim not in (0, 1):
         raise ValueError(f"Cannot slice sparse CSR matrix along dim {dim}")
-    if dim == 0:
-        s0, e0 = int(indptr[start].item()), int(indptr[end].item())
-        new_indptr = indptr[start:end + 1] - s0
-        values, cols = data[s0:e0], indices[s0:e0]
-    else:
-        mask = (indices >= start) & (indices < end)
-        nse = int(indptr[-1].item())
-        per_row = torch.zeros(indptr.numel() - 1, dtype=torch.int64, device=indptr.device)
-        rows_of = torch.repeat_interleave(torch.arange(indptr.numel() - 1, device=indptr.device),
-                                          (indptr[1:] - indptr[:-1]).to(torch.int64))
-        per_row.index_add_(0, rows_of, mask[:nse].to(torch.int64))
-        new_indptr = torch.empty_like(indptr)
-        new_indptr[0] = 0
-        new_indptr[1:] = per_row.cumsum(0).to(indptr.dtype)
-        values, cols = data[mask], indices[mask] - start
-    new_data, new_indices = _pad_csr(values, cols, new_indptr, int(data.shape[0] * size_factor))
+    if data.dtype not in _DT:
+        raise NotImplementedError(f"slice_csr_tensor: dtype {data.dtype} is not supported on CUDA")
+    if data.ndim != 1 or indices.ndim != 1 or indptr.ndim != 1 or indices.dtype != torch.int32 or indptr.dtype != torch.int32:
+        raise NotImplementedError("slice_csr_tensor: one padded CSR (1-D data / int32 indices / int32 indptr) per call")
+    rows = indptr.numel() - 1
+    start = 0 if start is None else int(start)
+    end = (rows if dim == 0 else (1 << 31) - 1) if end is None else int(end)
+    cap = int(data.shape[0] * size_factor)
+    d, ix, ip = data.contiguous(), indices.contiguous(), indptr.contiguous()
+    new_data = torch.empty(cap, dtype=data.dtype, device=data.device)
+    new_indices = torch.empty(cap, dtype=torch.int32, device=data.device)
+    new_indptr = torch.empty(end - start + 1 if dim == 0 else rows + 1, dtype=torch.int32, device=data.device)
+    with torch.cuda.device(data.device):
+        ws = torch.empty(max(_lib.lib.vq_slice_csr_workspace(rows), 4), dtype=torch.uint8, device=data.device) if dim == 1 else None
+        _lib.check(_lib.lib.vq_slice_csr(d.data_ptr(), ix.data_ptr(), ip.data_ptr(), _DT[data.dtype], rows, d.numel(), dim, start, end,
+                                         cap, new_data.data_ptr(), new_indices.data_ptr(), new_indptr.data_ptr(),
+                                         ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                         _stream(data.device)), "slice_csr_tensor")
     return new_data, new_indices, new_indptr
 
 

@@ -14,7 +14,7 @@ from typing import Callable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["column_shards", "shard_weight", "column_parallel_linear_mx"]
+__all__ = ["column_shards", "shard_weight", "column_parallel_linear_mx", "ColumnParallelLinearMX", "P2PColumnParallelLinearMX"]
 
 TILE_N = 256
 
@@ -41,42 +41,86 @@ def shard_weight(w_codes: torch.Tensor, w_scale: torch.Tensor, rank: int, world_
     return w_codes[n0:n1].contiguous(), w_scale[n0:n1].contiguous()
 
 
+class ColumnParallelLinearMX:
+    """``linear_mx`` with the weight sharded by output columns over ``group`` and the result exchanged with
+    NCCL all-gathers, prepared once per weight shard.  The shard's columns are cut into ``chunks`` pieces
+    (multiples of the GEMM's 256-wide tile): while the GEMM of piece ``c + 1`` runs on the caller's stream,
+    piece ``c`` is gathered and copied into place on a side stream, so that only the last piece's exchange is
+    exposed.  Returns the full ``[..., n_total]`` result on every rank.  ``gemm`` defaults to
+    ``torch.ops.quantized_ops.linear_mx`` (tests on CPU pass a stand-in so the exchange logic runs under gloo)."""
+
+    def __init__(self, w_codes_shard, w_scale_shard, n_total: int, block_size: int, group=None,
+                 bias_shard: Optional[torch.Tensor] = None, gemm: Optional[Callable] = None, chunks: Optional[int] = None):
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n_total, self.block = n_total, block_size
+        self.shards = column_shards(n_total, self.world)
+        n0, n1 = self.shards[self.rank]
+        if w_codes_shard.shape[0] != n1 - n0:
+            raise ValueError(f"rank {self.rank} holds {w_codes_shard.shape[0]} weight rows, its shard is {n1 - n0}")
+        self.gemm = gemm if gemm is not None else torch.ops.quantized_ops.linear_mx
+        self.width = max(b - a for a, b in self.shards)                 # equal-sized exchange buffers
+        tiles = -(-self.width // TILE_N)
+        if chunks is None:
+            chunks = min(4, tiles) if w_codes_shard.is_cuda and self.world > 1 else 1
+        chunks = max(1, min(int(chunks), tiles))
+        per = -(-tiles // chunks) * TILE_N
+        # piece c covers shard-local columns [c * per, (c + 1) * per); the views are kept so that the decoded
+        # copies of the weight pieces are found again on the next call
+        self.pieces = []
+        for c0 in range(0, self.width, per):
+            c1 = min(c0 + per, self.width)
+            lo, hi = min(c0, n1 - n0), min(c1, n1 - n0)
+            self.pieces.append((c0, c1, w_codes_shard[lo:hi], w_scale_shard[lo:hi] if w_scale_shard is not None else None,
+                                bias_shard[lo:hi] if bias_shard is not None else None))
+        self._side = torch.cuda.Stream(w_codes_shard.device) if w_codes_shard.is_cuda and self.world > 1 else None
+
+    def __call__(self, x_codes, x_scale) -> torch.Tensor:
+        lead = x_codes.shape[:-1]
+        m = 1
+        for d in lead:
+            m *= d
+        out = torch.empty((m, self.n_total), dtype=x_codes.dtype, device=x_codes.device)
+        main = torch.cuda.current_stream(x_codes.device) if self._side is not None else None
+        for c0, c1, wq, ws, bias in self.pieces:
+            w = c1 - c0
+            if wq.shape[0]:
+                y = self.gemm(x_codes, wq, bias, input_scale=x_scale, weight_scale=ws, block_size=self.block).reshape(m, wq.shape[0])
+            else:
+                y = x_codes.new_empty((m, 0))
+            if self.world == 1:
+                out[:, c0:c0 + y.shape[1]] = y
+                continue
+            send = y if y.shape[1] == w else torch.nn.functional.pad(y, (0, w - y.shape[1]))
+            recv = torch.empty((self.world, m, w), dtype=send.dtype, device=send.device)
+            if self._side is not None:
+                ready = torch.cuda.Event()
+                ready.record(main)
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(ready)
+                    self._exchange(send.contiguous(), recv, out, c0, w)
+                send.record_stream(self._side)
+                recv.record_stream(self._side)
+            else:
+                self._exchange(send.contiguous(), recv, out, c0, w)
+        if self._side is not None:
+            main.wait_stream(self._side)
+        return out.reshape(*lead, self.n_total)
+
+    def _exchange(self, send, recv, out, c0, w):
+        dist.all_gather_into_tensor(recv.view(self.world * recv.shape[1], w), send, group=self.group)
+        for r, (a, b) in enumerate(self.shards):
+            lo, hi = min(a + c0, b), min(a + c0 + w, b)
+            if hi > lo:
+                out[:, lo:hi] = recv[r, :, : hi - lo]
+
+
 def column_parallel_linear_mx(x_codes, x_scale, w_codes_shard, w_scale_shard, n_total: int, block_size: int,
                               group=None, bias_shard: Optional[torch.Tensor] = None,
-                              gemm: Optional[Callable] = None) -> torch.Tensor:
-    """``linear_mx`` with the weight sharded by output columns over ``group``.  Returns the full
-    ``[..., n_total]`` result on every rank.  ``gemm`` defaults to ``torch.ops.quantized_ops.linear_mx``
-    (tests on CPU pass a stand-in so that the exchange logic runs under gloo)."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    shards = column_shards(n_total, world)
-    n0, n1 = shards[rank]
-    if w_codes_shard.shape[0] != n1 - n0:
-        raise ValueError(f"rank {rank} holds {w_codes_shard.shape[0]} weight rows, its shard is {n1 - n0}")
-    if gemm is None:
-        gemm = torch.ops.quantized_ops.linear_mx
-    lead = x_codes.shape[:-1]
-    m = 1
-    for d in lead:
-        m *= d
-    if n1 > n0:
-        y_local = gemm(x_codes, w_codes_shard, bias_shard, input_scale=x_scale, weight_scale=w_scale_shard,
-                       block_size=block_size).reshape(m, n1 - n0)
-    else:
-        y_local = x_codes.new_empty((m, 0))
-    if world == 1:
-        return y_local.reshape(*lead, n_total)
-    # equal-sized exchange buffers: shards differ by at most one tile
-    width = max(b - a for a, b in shards)
-    send = y_local if y_local.shape[1] == width else torch.nn.functional.pad(y_local, (0, width - y_local.shape[1]))
-    recv = torch.empty((world * m, width), dtype=send.dtype, device=send.device)
-    dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
-    recv = recv.view(world, m, width)
-    out = torch.empty((m, n_total), dtype=send.dtype, device=send.device)
-    for r, (a, b) in enumerate(shards):
-        if b > a:
-            out[:, a:b] = recv[r, :, : b - a]
-    return out.reshape(*lead, n_total)
+                              gemm: Optional[Callable] = None, chunks: Optional[int] = None) -> torch.Tensor:
+    """One call of :class:`ColumnParallelLinearMX` (which is the form to keep when the same weight shard is
+    used again: it reuses the decoded weight pieces and its side stream)."""
+    return ColumnParallelLinearMX(w_codes_shard, w_scale_shard, n_total, block_size, group, bias_shard, gemm, chunks)(x_codes, x_scale)
 
 
 class P2PColumnParallelLinearMX:
@@ -106,7 +150,9 @@ class P2PColumnParallelLinearMX:
         self.y = symm_mem.empty(max_rows, n_total, dtype=torch.bfloat16, device=dev)
         self.handle = symm_mem.rendezvous(self.y, self.group)
         ptrs = list(self.handle.buffer_ptrs)
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        # own copy first, then the peers starting with the next rank: at any moment the ranks write to
+        # different destinations instead of all starting on rank 0's memory
+        order = [(self.rank + d) % self.world for d in range(self.world)]
         import ctypes as C
         self._ptrs = (C.c_void_p * len(order))(*[ptrs[r] for r in order])
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
