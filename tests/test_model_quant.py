@@ -364,3 +364,30 @@ def test_per_channel_kernels_on_awkward_shapes(kernel, dtype, table, qmax, monke
 def _status():
     from voyager_compiler_b200 import _lib
     return _lib.lib.vq_channel_status()
+
+
+@pytest.mark.gpu
+def test_pipeline_wait_that_runs_out_is_reported_and_the_context_stays_usable(monkeypatch):
+    """The bounded waits of the bulk-copy pipeline: with one batch left out by the producer (a test hook)
+    and a budget of about a millisecond, the consumers of that batch give up, the kernel records it and
+    returns in order; the next, untouched launch on the same context is correct again."""
+    from voyager_compiler_b200 import _lib
+    torch.manual_seed(3)
+    ws = [torch.randn(512, 4608) * 0.05, torch.randn(1024, 1024) * 0.05]
+    dev = [w.cuda() for w in ws]
+    tab = golden_table("posit8_1")
+    assert _lib.lib.vq_channel_status() == 0
+    monkeypatch.setenv("VOYAGER_B200_CHANNEL_SKIP_BATCH", "7")
+    monkeypatch.setenv("VOYAGER_B200_CHANNEL_WAIT_CYCLES", "2000000")
+    broken = mq.ChannelQuantPlan(dev, tab, 4096.0, want_values=True, want_codes=True, want_dequant=True)
+    broken.run()
+    torch.cuda.synchronize()                                   # returns: nothing hangs
+    assert _lib.lib.vq_channel_status() in (21, 22)            # producer or consumer side, whichever gave up first
+    assert _lib.lib.vq_channel_status() == 0                   # read once, cleared
+    broken.close()
+    monkeypatch.delenv("VOYAGER_B200_CHANNEL_SKIP_BATCH")
+    monkeypatch.delenv("VOYAGER_B200_CHANNEL_WAIT_CYCLES")
+    plan = mq.ChannelQuantPlan(dev, tab, 4096.0, want_values=True, want_codes=True, want_dequant=True)
+    _check_channel_results(ws, plan.run(), tab, 4096.0)
+    assert _lib.lib.vq_channel_status() == 0
+    plan.close()

@@ -99,6 +99,8 @@ struct BatchParams {
     float qmax;
     MxParams common;                  // table + shared-memory staging flags only
     int table_bytes;                  // shared memory taken by the staged tables
+    long long wait_budget;            // pipelined kernel: clock cycles a wait may take before it gives up
+    int skip_batch;                   // pipelined kernel, tests only: the producer leaves this batch out (-1: none)
 };
 
 struct ChanShared {
@@ -335,7 +337,7 @@ struct RawVec<bf16_t> {
 // Pipelined variant: batches arrive in shared memory by asynchronous bulk copies.
 //
 // Warp 0 is the producer: one thread walks this CTA's batches and, for each, waits for a free
-// stage of a PIPE_STAGES-deep ring and issues ONE cp.async.bulk of the whole batch (up to 32 KB)
+// stage of a PIPE_STAGES-deep ring and issues ONE cp.async.bulk of the whole batch (up to 28 KB)
 // whose completion is counted on the stage's mbarrier.  PIPE_GROUPS consumer groups of PIPE_GT threads
 // take the batches in turn: wait for the stage, read it into registers (8 x 16 bytes per thread),
 // release the stage at once, reduce |x| per channel, derive the scales, quantize from registers
@@ -350,11 +352,17 @@ struct RawVec<bf16_t> {
 // Every wait is bounded; a wait that runs out sets g_channel_status and winds the CTA down.
 constexpr int PIPE_GROUPS = 3;
 constexpr int PIPE_GT = 224;                                   // threads per consumer group: 3 x 7 + 1 warps leave 80 registers per thread
-constexpr int PIPE_STAGES = 4;
+constexpr int PIPE_STAGES = 3;                                 // a multiple of PIPE_GROUPS: see below
 constexpr int PIPE_VECS = 8;                                   // 16-byte vectors per consumer thread
 constexpr int PIPE_BATCH = PIPE_GT * PIPE_VECS * 4;            // 7168 elements
 constexpr int PIPE_THREADS = 32 + PIPE_GROUPS * PIPE_GT;
 constexpr long long PIPE_WAIT = 4000000000ll;                  // ~2 s of SM clocks
+// Batch i of a CTA uses stage i % PIPE_STAGES and consumer group i % PIPE_GROUPS.  With the stage count a
+// multiple of the group count a stage always belongs to the same group, so that group sees every phase of
+// the stage's barriers in order; a parity wait is only meaningful for a waiter that has seen the phase before
+// (a group meeting a stage for the first time in its SECOND use would find "parity 1 not pending" and read
+// the stage before the first copy into it has landed).
+static_assert(PIPE_STAGES % PIPE_GROUPS == 0, "every stage must belong to one consumer group");
 
 __device__ int g_channel_status = 0;
 
@@ -428,7 +436,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             for (int b = blockIdx.x; b < p.n_batches && ok; b += gridDim.x, ++i) {
                 const int s = i % PIPE_STAGES;
                 const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
-                if (i >= PIPE_STAGES && !tc::mbar_wait(EMPTY0 + 8u * s, ph ^ 1u, PIPE_WAIT)) { ok = false; break; }
+                if (i >= PIPE_STAGES && !tc::mbar_wait(EMPTY0 + 8u * s, ph ^ 1u, p.wait_budget)) { ok = false; break; }
+                if (b == p.skip_batch) continue;              // test hook: this batch's consumers will see their wait run out
                 const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
                 const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
                 const uint32_t L = (uint32_t)it.length;
@@ -474,8 +483,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         }
         if (tid == 0) {
             sh.slow = need_amax ? 0 : 1;
-            bool ok = tc::mbar_wait(FULL0 + 8u * s, ph, PIPE_WAIT);
-            if (ok && !tables_ready) ok = tc::mbar_wait(TABLE_BAR, 0u, PIPE_WAIT);      // the bulk copies of the tables have landed
+            bool ok = tc::mbar_wait(FULL0 + 8u * s, ph, p.wait_budget);
+            if (ok && !tables_ready) ok = tc::mbar_wait(TABLE_BAR, 0u, p.wait_budget);      // the bulk copies of the tables have landed
             ps.ok[group] = ok ? 1 : 0;
         }
         tables_ready = true;
@@ -736,6 +745,16 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
     BatchParams& p = L.p;
     p = BatchParams{};
     p.qmax = (float)quant_max;
+    p.wait_budget = PIPE_WAIT;
+    p.skip_batch = -1;
+    // Test hooks of the bounded waits: VOYAGER_B200_CHANNEL_WAIT_CYCLES shortens the budget and
+    // VOYAGER_B200_CHANNEL_SKIP_BATCH makes the producer leave one batch out, so that a wait runs out, the
+    // kernel records it (vq_channel_status) and winds down.  Read when a launch is prepared.
+    if (const char* e = getenv("VOYAGER_B200_CHANNEL_WAIT_CYCLES")) {
+        const long long v = atoll(e);
+        if (v > 0) p.wait_budget = v;
+    }
+    if (const char* e = getenv("VOYAGER_B200_CHANNEL_SKIP_BATCH")) p.skip_batch = atoi(e);
     p.common.tab = to_dev(table);
     const bool lut = table && table->kind == VQ_TABLE_LUT16;
     const bool big = total >= (1 << 21);
