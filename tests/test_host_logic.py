@@ -217,3 +217,16 @@ def test_module_accepts_every_upstream_scheme_and_option():
     assert m.outlier_threshold == 6.0
     with pytest.raises(AssertionError):
         fq.FusedAmaxObsFakeQuantize("int8", qscheme="per_tensor_symmetric", quant_max=127.0, outlier_pct=0.1, outlier_threshold=1.0)
+
+
+def test_nvtx_wrapper_is_only_installed_on_request(monkeypatch):
+    from voyager_compiler_b200 import ops
+
+    def op(x, y=1):
+        """doc"""
+        return x + y
+    monkeypatch.delenv("VOYAGER_B200_NVTX", raising=False)
+    assert ops._traced("vmap", op) is op                      # default: the function itself, no wrapper
+    monkeypatch.setenv("VOYAGER_B200_NVTX", "1")
+    wrapped = ops._traced("vmap", op)
+    assert wrapped is not op and wrapped.__doc__ == "doc" and wrapped.__wrapped__ is op

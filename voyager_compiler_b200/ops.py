@@ -553,6 +553,27 @@ def _fake_mx_shape(x, axes, block_size):
     return shape
 
 
+def _traced(name: str, fn):
+    """With ``VOYAGER_B200_NVTX=1`` every dispatcher call of an op runs inside an NVTX range named
+    ``quantized_ops::<op>``, so a timeline shows which kernels belong to which graph node; otherwise ``fn``
+    itself is registered (no wrapper, no cost)."""
+    import os
+    if os.environ.get("VOYAGER_B200_NVTX") != "1":
+        return fn
+    import functools
+    label = f"quantized_ops::{name}"
+
+    @functools.wraps(fn)
+    def ranged(*args, **kwargs):
+        torch.cuda.nvtx.range_push(label)
+        try:
+            return fn(*args, **kwargs)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    return ranged
+
+
 def register() -> str:
     """Attach the CUDA kernels to ``torch.ops.quantized_ops``.  Returns ``"impl"`` when the upstream
     library definition was found (kernels added to it) or ``"def"`` when this package had to define
@@ -625,18 +646,14 @@ def register() -> str:
         m.impl("spmm_csr", _spmm_fake)
         _libs.append(m)
     c = torch.library.Library("quantized_ops", "IMPL", "CUDA")
-    c.impl("vmap", vmap)
-    c.impl("quantize", quantize)
-    c.impl("dequantize", dequantize)
-    c.impl("calculate_mx_qparam", calculate_mx_qparam)
-    c.impl("quantize_mx", quantize_mx)
-    c.impl("conv2d_mx", conv2d_mx)
-    c.impl("linear_mx", linear_mx)
-    c.impl("matmul_mx", matmul_mx)
+    for name, fn in (("vmap", vmap), ("quantize", quantize), ("dequantize", dequantize),
+                     ("calculate_mx_qparam", calculate_mx_qparam), ("quantize_mx", quantize_mx), ("conv2d_mx", conv2d_mx),
+                     ("linear_mx", linear_mx), ("matmul_mx", matmul_mx)):
+        c.impl(name, _traced(name, fn))
     for name, fn in (("filter_outlier", filter_outlier), ("quantize_mx_outlier", quantize_mx_outlier),
                      ("slice_csr_tensor", slice_csr_tensor), ("spmm_csr", spmm_csr)):
         if _op_defined(name):
-            c.impl(name, fn)
+            c.impl(name, _traced(name, fn))
     _libs.append(c)
     _registered = mode
     logger.info("quantized_ops CUDA kernels registered (%s mode)", mode)

@@ -43,10 +43,11 @@ def shard_weight(w_codes: torch.Tensor, w_scale: torch.Tensor, rank: int, world_
 
 class ColumnParallelLinearMX:
     """``linear_mx`` with the weight sharded by output columns over ``group`` and the result exchanged with
-    NCCL all-gathers, prepared once per weight shard.  The shard's columns are cut into ``chunks`` pieces
-    (multiples of the GEMM's 256-wide tile): while the GEMM of piece ``c + 1`` runs on the caller's stream,
-    piece ``c`` is gathered and copied into place on a side stream, so that only the last piece's exchange is
-    exposed.  Returns the full ``[..., n_total]`` result on every rank.  ``gemm`` defaults to
+    NCCL all-gathers, prepared once per weight shard (the decoded weight pieces are found again on the next
+    call).  With ``chunks`` > 1 the shard's columns are cut into that many pieces (multiples of the GEMM's
+    256-wide tile): while the GEMM of piece ``c + 1`` runs on the caller's stream, piece ``c`` is gathered and
+    copied into place on a side stream.  This is the library-collective form of the exchange;
+    :class:`P2PColumnParallelLinearMX`, which stores from the GEMM epilogue into the peers' memory, is the fast one.  Returns the full ``[..., n_total]`` result on every rank.  ``gemm`` defaults to
     ``torch.ops.quantized_ops.linear_mx`` (tests on CPU pass a stand-in so the exchange logic runs under gloo)."""
 
     def __init__(self, w_codes_shard, w_scale_shard, n_total: int, block_size: int, group=None,
@@ -62,7 +63,10 @@ class ColumnParallelLinearMX:
         self.width = max(b - a for a, b in self.shards)                 # equal-sized exchange buffers
         tiles = -(-self.width // TILE_N)
         if chunks is None:
-            chunks = min(4, tiles) if w_codes_shard.is_cuda and self.world > 1 else 1
+            # one piece: measured on 4 x B200 the cfg5 linear takes 0.84 ms in one piece and 1.08 ms in four --
+            # every piece adds a GEMM, a collective and a copy per rank to the launch queue, and at these sizes
+            # (11 MB per piece and rank) the host cannot queue them as fast as the GPU retires them
+            chunks = 1
         chunks = max(1, min(int(chunks), tiles))
         per = -(-tiles // chunks) * TILE_N
         # piece c covers shard-local columns [c * per, (c + 1) * per); the views are kept so that the decoded
