@@ -105,7 +105,9 @@ struct FastParams {
     int iters;                   // inner iterations per tile (one tensor lookup per tile)
 };
 
-constexpr int kFastU = 2;    // 32-byte chunks a thread has in flight per inner iteration
+// 32-byte chunks a thread has in flight per inner iteration: two when the chunk is quantized (registers), four
+// for the scale-only pass, which keeps nothing but the block maxima
+__host__ __device__ constexpr int fast_u(int out) { return out == OUT_SCALE ? 4 : 2; }
 
 // GS > 0: the number of lanes per block is 2^GS, known at compile time (the usual block sizes);
 // GS == 0: taken from the parameters.
@@ -222,9 +224,9 @@ __global__ void __launch_bounds__(1024, 1) mx_fast2_kernel(const __grid_constant
 template <typename T, int RULE, int TK, int OUT, bool SM>
 int launch_fast2(const FastParams& p, int threads, int blocks, size_t smem, cudaStream_t st) {
     // blocks of 2 or 4 chunks (32 / 64 elements) have the lane-group reduction unrolled
-    auto k = p.group_shift == 1   ? mx_fast2_kernel<T, RULE, TK, OUT, SM, kFastU, 1>
-             : p.group_shift == 2 ? mx_fast2_kernel<T, RULE, TK, OUT, SM, kFastU, 2>
-                                  : mx_fast2_kernel<T, RULE, TK, OUT, SM, kFastU, 0>;
+    auto k = p.group_shift == 1   ? mx_fast2_kernel<T, RULE, TK, OUT, SM, fast_u(OUT), 1>
+             : p.group_shift == 2 ? mx_fast2_kernel<T, RULE, TK, OUT, SM, fast_u(OUT), 2>
+                                  : mx_fast2_kernel<T, RULE, TK, OUT, SM, fast_u(OUT), 0>;
     if (smem > 48 * 1024) VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<blocks, threads, smem, st>>>(p);
     VQ_LAUNCH_CHECK("mx_fast2_kernel");
@@ -354,10 +356,11 @@ int fast_prepare(const vq_mx_item* items, int n_items, int dtype, int64_t block,
     const int threads = big ? 1024 : 128;
     const int sms = vq_sm_count();
     // tiles large enough to amortise the per-tile tensor lookup, small enough for >= 8 tiles per SM
-    int64_t iters = total / ((int64_t)threads * kFastU * N * sms * 8);
+    const int U = fast_u(out);
+    int64_t iters = total / ((int64_t)threads * U * N * sms * 8);
     iters = iters < 1 ? 1 : (iters > 8 ? 8 : iters);
     p.iters = (int)iters;
-    const int64_t tile_elems = (int64_t)threads * kFastU * N * iters;
+    const int64_t tile_elems = (int64_t)threads * U * N * iters;
     if (n_items == 1) {
         p.single = items[0];
         p.n_tiles = (items[0].n + tile_elems - 1) / tile_elems;
