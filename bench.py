@@ -806,6 +806,45 @@ def resnet50_weight_shapes():
     return shapes
 
 
+def run_channel(args):
+    """cfg2 alone: the 54 ResNet-50-shaped weight tensors, posit8_1 per output channel (scale = channel
+    maximum / 4096), code byte + dequantized fp32 from one prepared launch; ``--steps`` timed launches with
+    256 MB written in between.  Small enough for a full profiler capture of the kernel."""
+    import torch
+    import voyager_compiler_b200 as vb
+    from voyager_compiler_b200 import model_quant as mq
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    qp = torch.from_numpy(vb.tables.build_table("posit8_1").view("int16").copy()).view(torch.bfloat16).to(dev)
+    torch.manual_seed(1)
+    ws = []
+    for shp in resnet50_weight_shapes():
+        t = torch.empty(shp, device=dev)
+        torch.nn.init.kaiming_normal_(t, mode="fan_in")
+        ws.append(t)
+    n = sum(t.numel() for t in ws)
+    plan = mq.ChannelQuantPlan(ws, qp, 4096.0, want_codes=True, want_dequant=True)
+    for _ in range(max(args.warmup, 1)):
+        plan.run()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); plan.run(); e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    peaks, kind = measured_peaks()
+    med = statistics.median(ts)
+    print(json.dumps({"workload": "cfg2: posit8_1 per output channel, 54 ResNet-50-shaped tensors, codes + dequantized fp32",
+                      "elements": n, "bytes_per_launch": n * 9, "us_per_launch": med * 1e3, "gbs": n * 9 / med / 1e6,
+                      "frac_of_measured_hbm_peak": n * 9 / med / 1e6 / peaks["hbm_gbs"], "peak_kind": kind,
+                      "steps": args.steps, "channel_status": vb._lib.lib.vq_channel_status()}))
+    plan.close()
+
+
 def run_elementwise(args):
     """cfg1 / cfg2 / cfg4-shaped element-wise measurements on one GPU (GB/s of algorithmic traffic,
     L2 flushed between iterations)."""
@@ -978,7 +1017,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="fewer than 32: reduced model for profiler captures")
     ap.add_argument("--kernel-only", action="store_true", help="device-timed part only (profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (skip the other configurations)")
-    ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise"],
+    ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise", "channel"],
                     help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
     ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
     args = ap.parse_args()
@@ -987,6 +1026,9 @@ def main():
         return
     if args.workload == "elementwise":
         run_elementwise(args)
+        return
+    if args.workload == "channel":
+        run_channel(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -86,7 +86,7 @@ struct ChanBatch {
     int item, c0, nc;
     FastDiv len;            // flat index -> channel
     int vec;                // pipelined kernel: the batch starts and ends on 16-byte boundaries of aligned tensors
-    int pad;
+    int fast;               // pipelined kernel: vec, and the channel length is a multiple of 128 elements
 };
 constexpr int kBatchElems = 16384;
 constexpr int kGroupThreads = 256;
@@ -372,7 +372,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
 }
 
 struct PipeShared {
-    ChanShared ch[PIPE_GROUPS];
+    ChanShared ch[PIPE_GROUPS][2];
     int ok[PIPE_GROUPS];
 };
 
@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
     if (threadIdx.x == 0) {
         for (int s = 0; s < PIPE_STAGES; ++s) {
             tc::mbar_init(FULL0 + 8u * s, 1);
-            tc::mbar_init(EMPTY0 + 8u * s, 1);
+            tc::mbar_init(EMPTY0 + 8u * s, PIPE_GT / 32);     // one arrival per consumer warp of the owning group
         }
         tc::mbar_init(TABLE_BAR, 1);
         tc::fence_barrier_init();
@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             for (int b = blockIdx.x; b < p.n_batches && ok; b += gridDim.x, ++i) {
                 const int s = i % PIPE_STAGES;
                 const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
-                if (i >= PIPE_STAGES && !tc::mbar_wait(EMPTY0 + 8u * s, ph ^ 1u, p.wait_budget)) { ok = false; break; }
+                if (i >= PIPE_STAGES && !tc::mbar_wait_relaxed(EMPTY0 + 8u * s, ph ^ 1u, p.wait_budget)) { ok = false; break; }
                 if (b == p.skip_batch) continue;              // test hook: this batch's consumers will see their wait run out
                 const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
                 const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
@@ -457,10 +457,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
 
     // ---------------------------------------------------------------------- consumers
     constexpr int GT = PIPE_GT;
+    constexpr int GW = GT / 32;
     const int ct = threadIdx.x - 32;
     const int group = ct / GT, tid = ct % GT;
-    ChanShared& sh = ps.ch[group];
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = tid >> 5;
     const uint32_t warp_e0 = (uint32_t)(tid & ~31) * 4u;
     auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(GT) : "memory"); };
     bool tables_ready = TK != TK_LUT;
@@ -468,6 +468,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
     for (int b = blockIdx.x + group * gridDim.x; b < p.n_batches; b += PIPE_GROUPS * gridDim.x, i += PIPE_GROUPS) {
         const int s = i % PIPE_STAGES;
         const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
+        // The per-channel scratch alternates between two copies: a thread may enter the next batch (and clear
+        // that batch's copy) while slower threads of the group still read this batch's scales; the barriers
+        // inside the next batch keep it from going two batches ahead.
+        ChanShared& sh = ps.ch[group][(i / PIPE_GROUPS) & 1];
         const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
         const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
         const uint32_t L = (uint32_t)it.length;
@@ -476,6 +480,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         const T* x = reinterpret_cast<const T*>(it.input) + off;
         const bool vec = bt.vec != 0;
         const bool ragged = (L & 3u) != 0u;                  // a 4-element vector may straddle two channels
+        const bool fast = bt.fast != 0;                      // vec and every 128-element run inside one channel
         const bool need_amax = !it.scale_in || it.amax_out;
         for (int c = tid; c < bt.nc; c += GT) {
             sh.amax[c] = 0u;
@@ -483,8 +488,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         }
         if (tid == 0) {
             sh.slow = need_amax ? 0 : 1;
-            bool ok = tc::mbar_wait(FULL0 + 8u * s, ph, p.wait_budget);
-            if (ok && !tables_ready) ok = tc::mbar_wait(TABLE_BAR, 0u, p.wait_budget);      // the bulk copies of the tables have landed
+            bool ok = tc::mbar_wait_relaxed(FULL0 + 8u * s, ph, p.wait_budget);
+            if (ok && !tables_ready) ok = tc::mbar_wait_relaxed(TABLE_BAR, 0u, p.wait_budget);   // the bulk copies of the tables have landed
             ps.ok[group] = ok ? 1 : 0;
         }
         tables_ready = true;
@@ -493,27 +498,73 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             if (tid == 0) atomicCAS(&g_channel_status, 0, 22);
             break;
         }
-        // Batches whose channel length is a multiple of 4 elements go through registers and give their
-        // stage back at once.  "Ragged" ones (a 16-byte vector may straddle two channels; e.g. the 7x7x3
-        // stem) are rare: they stay in the stage and are walked by rolled loops, element by element.
-        const bool in_regs = vec && !ragged;
+        // every consumer warp gives the stage back once per batch (the barrier counts GW arrivals)
+        auto release_stage = [&]() {
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(EMPTY0 + 8u * s);
+        };
+        // Three ways through a batch:
+        //   fast     channel length a multiple of 128 elements: every warp takes one contiguous run of the batch in
+        //            128-element pieces, each inside one channel, so the channel bookkeeping is one comparison per piece;
+        //   in_regs  channel length a multiple of 4: registers too, pieces strided over the group, the channel of a
+        //            piece found by division and pieces that straddle channels reduced element-wise;
+        //   rolled   anything else (a vector may straddle two channels, e.g. a 7x7x3 stem; unaligned tensors): the
+        //            batch stays in the stage (or in global memory) and is walked element by element.
+        // The first two copy the batch to registers and give the stage back at once.
+        const bool in_regs = vec && !ragged && !fast;
         const T* st = reinterpret_cast<const T*>(ring + s * STAGE_BYTES);
         RawVec<T> raw[PIPE_VECS];
-        if (in_regs) {
+        // fast: this warp's run is pieces [qc, qc + cnt) of the batch
+        const uint32_t pieces = n >> 7, per = (pieces + GW - 1) / GW, qc = (uint32_t)warp * per;
+        const int cnt = (fast && qc < pieces) ? (int)min(per, pieces - qc) : 0;
+        const uint32_t e_w = qc << 7;
+        if (fast) {
+#pragma unroll
+            for (int j = 0; j < PIPE_VECS; ++j)
+                if (j < cnt) raw[j].load_shared(st + e_w + (uint32_t)(j << 7) + (uint32_t)lane * 4u);
+            release_stage();
+        } else if (in_regs) {
 #pragma unroll
             for (int j = 0; j < PIPE_VECS; ++j) {
                 const uint32_t e = (uint32_t)(j * GT + tid) * 4u;
                 if (e < n) raw[j].load_shared(st + e);
                 else raw[j].zero();
             }
-        }
-        if (!(vec && ragged)) {
-            group_sync();                                    // every thread has its copy: the stage is free
-            if (tid == 0) tc::mbar_arrive(EMPTY0 + 8u * s);
+            release_stage();
+        } else if (!vec) {
+            release_stage();                                 // nothing was copied: the rolled loops read global memory
         }
         const T* xs = (vec && ragged) ? st : x;              // where the rolled loops read the batch
 
-        if (need_amax && in_regs) {
+        if (need_amax && fast) {
+            if (cnt > 0) {
+                uint32_t cur = fd_div(e_w, bt.len), next = (cur + 1u) * L, m = 0u, mn = 0xFFFFFFFFu;
+                auto flush = [&]() {
+                    const uint32_t wm = __reduce_max_sync(0xFFFFFFFFu, m), wn = __reduce_min_sync(0xFFFFFFFFu, mn);
+                    if (lane == 0) {
+                        atomicMax(&sh.amax[cur], wm);
+                        atomicMin(&sh.minnz[cur], wn);
+                    }
+                };
+#pragma unroll
+                for (int j = 0; j < PIPE_VECS; ++j) {
+                    if (j >= cnt) break;
+                    if (e_w + (uint32_t)(j << 7) >= next) {   // warp uniform
+                        flush();
+                        ++cur;
+                        next += L;
+                        m = 0u;
+                        mn = 0xFFFFFFFFu;
+                    }
+                    float v[4];
+                    raw[j].get(v);
+                    const uint32_t a0 = abs_bits(v[0]), a1 = abs_bits(v[1]), a2 = abs_bits(v[2]), a3 = abs_bits(v[3]);
+                    m = max(max(m, a0), max(a1, max(a2, a3)));
+                    mn = min(min(mn, a0 - 1u), min(a1 - 1u, min(a2 - 1u, a3 - 1u)));   // a zero wraps to the top and drops out
+                }
+                flush();
+            }
+        } else if (need_amax && in_regs) {
             uint32_t cur = 0xFFFFFFFFu, m = 0u, mn = 0xFFFFFFFFu;
             auto flush = [&]() {
                 if (cur != 0xFFFFFFFFu) {
@@ -534,7 +585,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                 const uint32_t e = (uint32_t)(j * GT + tid) * 4u;
                 const uint32_t a0 = abs_bits(v[0]), a1 = abs_bits(v[1]), a2 = abs_bits(v[2]), a3 = abs_bits(v[3]);
                 const uint32_t m4 = max(max(a0, a1), max(a2, a3));
-                const uint32_t n4 = min(min(a0 - 1u, a1 - 1u), min(a2 - 1u, a3 - 1u));   // a zero wraps to the top and drops out
+                const uint32_t n4 = min(min(a0 - 1u, a1 - 1u), min(a2 - 1u, a3 - 1u));
                 const uint32_t last = min(first + 127u, n - 1u);
                 const uint32_t c_first = fd_div(first, bt.len), c_last = fd_div(last, bt.len);
                 if (c_first == c_last) {
@@ -607,6 +658,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             T* values = reinterpret_cast<T*>(it.values) + (it.values ? off : 0);
             T* dequant = reinterpret_cast<T*>(it.dequant) + (it.dequant ? off : 0);
             uint8_t* codes = it.codes + (it.codes ? off : 0);
+            const bool st_values = it.values != nullptr, st_dequant = it.dequant != nullptr;
             // value and code of the bf16 pattern `pat` of a quotient whose dividend was `xv`
             auto lookup = [&](uint32_t pat, float& val, uint32_t& code) {
                 if (TK == TK_LUT) {
@@ -625,31 +677,68 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                     code = (vb != vb) ? 0u : ((uint32_t)(int)q & 0xFFu);
                 }
             };
-            if (in_regs && sh.slow == 0) {
+            // Four elements of one channel whose quotients are in the range of the corrected-reciprocal division
+            // (q = x y, q += (x - s q) y: the correctly rounded x / s), two elements per packed fp32 instruction.
+            auto quantize4 = [&](const float* v, float sc, float y, float* q, float* d, uint32_t& packed) {
+                float t[4], r[4];
+                t[0] = v[0]; t[1] = v[1]; t[2] = v[2]; t[3] = v[3];
+                mul2(t[0], t[1], y);
+                mul2(t[2], t[3], y);
+                fma2(r[0], r[1], t[0], t[1], -sc, v[0], v[1]);
+                fma2(r[2], r[3], t[2], t[3], -sc, v[2], v[3]);
+                fma2(t[0], t[1], r[0], r[1], y, t[0], t[1]);
+                fma2(t[2], t[3], r[2], r[3], y, t[2], t[3]);
+                packed = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t pat = bf16_pattern(
+                        __uint_as_float((__float_as_uint(t[k]) & 0x7FFFFFFFu) | (__float_as_uint(v[k]) & 0x80000000u)));
+                    uint32_t code;
+                    lookup(pat, q[k], code);
+                    packed |= code << (8 * k);
+                    d[k] = q[k];
+                }
+                mul2(d[0], d[1], sc);
+                mul2(d[2], d[3], sc);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) d[k] = Arith<T>::rnd(d[k]);
+            };
+            if (fast && sh.slow == 0) {
+                if (cnt > 0) {
+                    uint32_t cur = fd_div(e_w, bt.len), next = (cur + 1u) * L;
+                    float sc = sh.s[cur], y = sh.y[cur];
+#pragma unroll
+                    for (int j = 0; j < PIPE_VECS; ++j) {
+                        if (j >= cnt) break;
+                        const uint32_t e0 = e_w + (uint32_t)(j << 7);
+                        if (e0 >= next) {                     // warp uniform
+                            ++cur;
+                            next += L;
+                            sc = sh.s[cur];
+                            y = sh.y[cur];
+                        }
+                        const uint32_t e = e0 + (uint32_t)lane * 4u;
+                        float v[4], q[4], d[4];
+                        uint32_t packed;
+                        raw[j].get(v);
+                        quantize4(v, sc, y, q, d, packed);
+                        if (st_values) store4<T>(values + e, q);
+                        if (st_dequant) store4<T>(dequant + e, d);
+                        if (want_code) __stcs(reinterpret_cast<uint32_t*>(codes + e), packed);
+                    }
+                }
+            } else if (in_regs && sh.slow == 0) {
 #pragma unroll
                 for (int j = 0; j < PIPE_VECS; ++j) {
                     const uint32_t e = (uint32_t)(j * GT + tid) * 4u;
                     if (e >= n) continue;
-                    float v[4];
-                    raw[j].get(v);
                     const uint32_t ch = fd_div(e, bt.len);
-                    const float sc = sh.s[ch], y = sh.y[ch];
-                    float q[4], d[4];
-                    uint32_t packed = 0;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float xv = v[k];
-                        const float q0 = __fmul_rn(xv, y);
-                        const float qq = __fmaf_rn(__fmaf_rn(-sc, q0, xv), y, q0);
-                        const uint32_t pat = bf16_pattern(
-                            __uint_as_float((__float_as_uint(qq) & 0x7FFFFFFFu) | (__float_as_uint(xv) & 0x80000000u)));
-                        uint32_t code;
-                        lookup(pat, q[k], code);
-                        packed |= code << (8 * k);
-                        d[k] = Arith<T>::rnd(__fmul_rn(q[k], sc));
-                    }
-                    if (it.values) store4<T>(values + e, q);
-                    if (it.dequant) store4<T>(dequant + e, d);
+                    float v[4], q[4], d[4];
+                    uint32_t packed;
+                    raw[j].get(v);
+                    quantize4(v, sh.s[ch], sh.y[ch], q, d, packed);
+                    if (st_values) store4<T>(values + e, q);
+                    if (st_dequant) store4<T>(dequant + e, d);
                     if (want_code) __stcs(reinterpret_cast<uint32_t*>(codes + e), packed);
                 }
             } else {
@@ -669,8 +758,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                 }
             }
         }
-        group_sync();
-        if (vec && ragged && tid == 0) tc::mbar_arrive(EMPTY0 + 8u * s);
+        if (vec && ragged) release_stage();                  // the rolled loops read the stage until here
     }
 }
 
@@ -810,7 +898,7 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
             hb[k].nc = (int)(it.channels - c0 < per ? it.channels - c0 : per);
             hb[k].len = fdv;
             hb[k].vec = batch_vec(it, hb[k].c0, hb[k].nc, dtype);
-            hb[k].pad = 0;
+            hb[k].fast = (use_pipe && hb[k].vec && it.length % 128 == 0) ? 1 : 0;
         }
     }
     if (use_pipe) {

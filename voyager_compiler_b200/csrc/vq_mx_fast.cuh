@@ -69,6 +69,13 @@ __device__ __forceinline__ void mul2(float& a, float& b, float r) {
         : "+f"(a), "+f"(b)
         : "f"(r));
 }
+// {d0, d1} = {a0, a1} * b + {c0, c1}: two fused multiply-adds, each rounded once, one issue slot.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c0, float c1) {
+    asm("{\n\t.reg .b64 a, b, c;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tmov.b64 c, {%5, %6};\n\t"
+        "fma.rn.f32x2 a, a, b, c;\n\tmov.b64 {%0, %1}, a;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c0), "f"(c1));
+}
 
 // |x| maximum of a chunk as fp32 bits.  For bf16 also whether the reciprocal path is safe for this
 // chunk: no non-zero element below 2^-60 (pattern 0x2180).

@@ -46,6 +46,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
     }
     return true;
 }
+// The same for waits that may last microseconds: the polling thread sleeps between polls and leaves the
+// issue slots to warps that have work.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, long long budget) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > budget) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
 
 // 2-D TMA tile load global -> shared, completion counted in bytes on `bar`.  c0 is the innermost
 // (contiguous) coordinate in elements.
