@@ -11,6 +11,7 @@
 // quantize and dequantize as separate full passes per tensor.
 // HBM bound: sizeof(T) read per element + the requested outputs.
 #include <algorithm>
+#include <type_traits>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -350,11 +351,11 @@ struct RawVec<bf16_t> {
 // arithmetic and no table at all.  Batches that bulk copies cannot take (channel length not a
 // multiple of 4 elements / 16 bytes, unaligned tensors) are read by the consumers themselves.
 // Every wait is bounded; a wait that runs out sets g_channel_status and winds the CTA down.
-constexpr int PIPE_GROUPS = 3;
-constexpr int PIPE_GT = 224;                                   // threads per consumer group: 3 x 7 + 1 warps leave 80 registers per thread
-constexpr int PIPE_STAGES = 3;                                 // a multiple of PIPE_GROUPS: see below
+constexpr int PIPE_GROUPS = 4;
+constexpr int PIPE_GT = 192;                                   // threads per consumer group: 4 x 6 + 1 warps leave 80 registers per thread
+constexpr int PIPE_STAGES = 4;                                 // a multiple of PIPE_GROUPS: see below
 constexpr int PIPE_VECS = 8;                                   // 16-byte vectors per consumer thread
-constexpr int PIPE_BATCH = PIPE_GT * PIPE_VECS * 4;            // 7168 elements
+constexpr int PIPE_BATCH = PIPE_GT * PIPE_VECS * 4;            // 6144 elements
 constexpr int PIPE_THREADS = 32 + PIPE_GROUPS * PIPE_GT;
 constexpr long long PIPE_WAIT = 4000000000ll;                  // ~2 s of SM clocks
 // Batch i of a CTA uses stage i % PIPE_STAGES and consumer group i % PIPE_GROUPS.  With the stage count a
@@ -370,6 +371,42 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+
+// value and code of the bf16 pattern `pat` of a quotient: from the code table and the level table in shared
+// memory (TK_LUT), or by rounding and clamping (TK_INT)
+template <int TK>
+__device__ __forceinline__ void pipe_lookup(const uint8_t* s_codes, const float* s_lv2, float lo, float hi, uint32_t pat,
+                                            float& val, uint32_t& code) {
+    if (TK == TK_LUT) {
+        code = s_codes[pat];
+        val = s_lv2[code + ((pat >> 15) << 8)];
+    } else {
+        const float vb = __uint_as_float(pat << 16);
+        float q = rintf(vb);
+        if (lo == 0.0f) {
+            q = (q < lo) ? lo : q;
+            q = (q > hi) ? hi : q;
+        } else {
+            q = fminf(fmaxf(q, lo), hi);
+        }
+        val = (vb != vb) ? vb : q;
+        code = (vb != vb) ? 0u : ((uint32_t)(int)q & 0xFFu);
+    }
+}
+// F(integral constant j) for j = CNT - 1 down to 0, CNT <= PIPE_VECS known at run time: one jump, then straight-line code
+#define VQ_PIECES_DOWN(CNT, F)                                   \
+    switch (CNT) {                                               \
+        case 8: F(std::integral_constant<int, 7>{}); [[fallthrough]]; \
+        case 7: F(std::integral_constant<int, 6>{}); [[fallthrough]]; \
+        case 6: F(std::integral_constant<int, 5>{}); [[fallthrough]]; \
+        case 5: F(std::integral_constant<int, 4>{}); [[fallthrough]]; \
+        case 4: F(std::integral_constant<int, 3>{}); [[fallthrough]]; \
+        case 3: F(std::integral_constant<int, 2>{}); [[fallthrough]]; \
+        case 2: F(std::integral_constant<int, 1>{}); [[fallthrough]]; \
+        case 1: F(std::integral_constant<int, 0>{}); [[fallthrough]]; \
+        default: break;                                          \
+    }
+static_assert(PIPE_VECS == 8, "VQ_PIECES_DOWN lists eight pieces");
 
 struct PipeShared {
     ChanShared ch[PIPE_GROUPS][2];
@@ -426,7 +463,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
     }
     __syncthreads();
     const float lo = p.common.tab.lo, hi = p.common.tab.hi;
-    const bool lo_is_zero = lo == 0.0f;
 
     if (threadIdx.x < 32) {
         // ------------------------------------------------------------------ producer
@@ -438,8 +474,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                 const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
                 if (i >= PIPE_STAGES && !tc::mbar_wait_relaxed(EMPTY0 + 8u * s, ph ^ 1u, p.wait_budget)) { ok = false; break; }
                 if (b == p.skip_batch) continue;              // test hook: this batch's consumers will see their wait run out
-                const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
-                const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
+                const ChanBatch& bt = *(i < kSmemBatches ? static_cast<const ChanBatch*>(sbatches + i) : p.batches + b);
+                const vq_channel_item& it = *(items_staged ? static_cast<const vq_channel_item*>(sitems + bt.item) : p.items + bt.item);
                 const uint32_t L = (uint32_t)it.length;
                 if (bt.vec) {
                     const uint32_t bytes = (uint32_t)bt.nc * L * (uint32_t)sizeof(T);
@@ -472,8 +508,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         // that batch's copy) while slower threads of the group still read this batch's scales; the barriers
         // inside the next batch keep it from going two batches ahead.
         ChanShared& sh = ps.ch[group][(i / PIPE_GROUPS) & 1];
-        const ChanBatch bt = i < kSmemBatches ? sbatches[i] : p.batches[b];
-        const vq_channel_item it = items_staged ? sitems[bt.item] : p.items[bt.item];
+        // descriptors through one pointer each: a select between a shared-memory and a global copy would load both,
+        // and the global load would sit at the head of every batch
+        const ChanBatch& bt = *(i < kSmemBatches ? static_cast<const ChanBatch*>(sbatches + i) : p.batches + b);
+        const vq_channel_item& it = *(items_staged ? static_cast<const vq_channel_item*>(sitems + bt.item) : p.items + bt.item);
         const uint32_t L = (uint32_t)it.length;
         const uint32_t n = (uint32_t)bt.nc * L;
         const int64_t off = (int64_t)bt.c0 * L;
@@ -538,7 +576,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
 
         if (need_amax && fast) {
             if (cnt > 0) {
-                uint32_t cur = fd_div(e_w, bt.len), next = (cur + 1u) * L, m = 0u, mn = 0xFFFFFFFFu;
+                // last piece first: one jump into straight-line code instead of a test per piece
+                uint32_t cur = fd_div(e_w + ((uint32_t)(cnt - 1) << 7), bt.len), floor_ = cur * L, m = 0u, mn = 0xFFFFFFFFu;
                 auto flush = [&]() {
                     const uint32_t wm = __reduce_max_sync(0xFFFFFFFFu, m), wn = __reduce_min_sync(0xFFFFFFFFu, mn);
                     if (lane == 0) {
@@ -546,13 +585,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                         atomicMin(&sh.minnz[cur], wn);
                     }
                 };
-#pragma unroll
-                for (int j = 0; j < PIPE_VECS; ++j) {
-                    if (j >= cnt) break;
-                    if (e_w + (uint32_t)(j << 7) >= next) {   // warp uniform
+                auto piece = [&](auto jc) {
+                    constexpr int j = decltype(jc)::value;
+                    if (e_w + (uint32_t)(j << 7) < floor_) {  // warp uniform: the run has left the channel
                         flush();
-                        ++cur;
-                        next += L;
+                        --cur;
+                        floor_ -= L;
                         m = 0u;
                         mn = 0xFFFFFFFFu;
                     }
@@ -561,7 +599,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                     const uint32_t a0 = abs_bits(v[0]), a1 = abs_bits(v[1]), a2 = abs_bits(v[2]), a3 = abs_bits(v[3]);
                     m = max(max(m, a0), max(a1, max(a2, a3)));
                     mn = min(min(mn, a0 - 1u), min(a1 - 1u, min(a2 - 1u, a3 - 1u)));   // a zero wraps to the top and drops out
-                }
+                };
+                VQ_PIECES_DOWN(cnt, piece);
                 flush();
             }
         } else if (need_amax && in_regs) {
@@ -631,6 +670,40 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             }
         }
         if (need_amax) group_sync();
+        const bool want_val = it.values != nullptr || it.dequant != nullptr;
+        const bool want_code = it.codes != nullptr;
+        T* values = reinterpret_cast<T*>(it.values) + (it.values ? off : 0);
+        T* dequant = reinterpret_cast<T*>(it.dequant) + (it.dequant ? off : 0);
+        uint8_t* codes = it.codes + (it.codes ? off : 0);
+        const bool st_values = it.values != nullptr, st_dequant = it.dequant != nullptr;
+        // value and code of the bf16 pattern `pat` of a quotient whose dividend was `xv`
+        auto lookup = [&](uint32_t pat, float& val, uint32_t& code) { pipe_lookup<TK>(s_codes, s_lv2, lo, hi, pat, val, code); };
+        // Four elements of one channel whose quotients are in the range of the corrected-reciprocal division
+        // (q = x y, q += (x - s q) y: the correctly rounded x / s), two elements per packed fp32 instruction.
+        auto quantize4 = [&](const float* v, float sc, float y, float* q, float* d, uint32_t& packed) {
+            float t[4], r[4];
+            t[0] = v[0]; t[1] = v[1]; t[2] = v[2]; t[3] = v[3];
+            mul2(t[0], t[1], y);
+            mul2(t[2], t[3], y);
+            fma2(r[0], r[1], t[0], t[1], -sc, v[0], v[1]);
+            fma2(r[2], r[3], t[2], t[3], -sc, v[2], v[3]);
+            fma2(t[0], t[1], r[0], r[1], y, t[0], t[1]);
+            fma2(t[2], t[3], r[2], r[3], y, t[2], t[3]);
+            packed = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t pat = bf16_pattern(
+                    __uint_as_float((__float_as_uint(t[k]) & 0x7FFFFFFFu) | (__float_as_uint(v[k]) & 0x80000000u)));
+                uint32_t code;
+                lookup(pat, q[k], code);
+                packed |= code << (8 * k);
+                d[k] = q[k];
+            }
+            mul2(d[0], d[1], sc);
+            mul2(d[2], d[3], sc);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) d[k] = Arith<T>::rnd(d[k]);
+        };
         for (int c = tid; c < bt.nc; c += GT) {
             const int64_t cg = bt.c0 + c;
             float sc;
@@ -652,68 +725,17 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             sh.kind[c] = d.kind;
         }
         group_sync();
-        const bool want_val = it.values != nullptr || it.dequant != nullptr;
-        const bool want_code = it.codes != nullptr;
         if (want_val || want_code) {
-            T* values = reinterpret_cast<T*>(it.values) + (it.values ? off : 0);
-            T* dequant = reinterpret_cast<T*>(it.dequant) + (it.dequant ? off : 0);
-            uint8_t* codes = it.codes + (it.codes ? off : 0);
-            const bool st_values = it.values != nullptr, st_dequant = it.dequant != nullptr;
-            // value and code of the bf16 pattern `pat` of a quotient whose dividend was `xv`
-            auto lookup = [&](uint32_t pat, float& val, uint32_t& code) {
-                if (TK == TK_LUT) {
-                    code = s_codes[pat];
-                    val = s_lv2[code + ((pat >> 15) << 8)];
-                } else {
-                    const float vb = __uint_as_float(pat << 16);
-                    float q = rintf(vb);
-                    if (lo_is_zero) {
-                        q = (q < lo) ? lo : q;
-                        q = (q > hi) ? hi : q;
-                    } else {
-                        q = fminf(fmaxf(q, lo), hi);
-                    }
-                    val = (vb != vb) ? vb : q;
-                    code = (vb != vb) ? 0u : ((uint32_t)(int)q & 0xFFu);
-                }
-            };
-            // Four elements of one channel whose quotients are in the range of the corrected-reciprocal division
-            // (q = x y, q += (x - s q) y: the correctly rounded x / s), two elements per packed fp32 instruction.
-            auto quantize4 = [&](const float* v, float sc, float y, float* q, float* d, uint32_t& packed) {
-                float t[4], r[4];
-                t[0] = v[0]; t[1] = v[1]; t[2] = v[2]; t[3] = v[3];
-                mul2(t[0], t[1], y);
-                mul2(t[2], t[3], y);
-                fma2(r[0], r[1], t[0], t[1], -sc, v[0], v[1]);
-                fma2(r[2], r[3], t[2], t[3], -sc, v[2], v[3]);
-                fma2(t[0], t[1], r[0], r[1], y, t[0], t[1]);
-                fma2(t[2], t[3], r[2], r[3], y, t[2], t[3]);
-                packed = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t pat = bf16_pattern(
-                        __uint_as_float((__float_as_uint(t[k]) & 0x7FFFFFFFu) | (__float_as_uint(v[k]) & 0x80000000u)));
-                    uint32_t code;
-                    lookup(pat, q[k], code);
-                    packed |= code << (8 * k);
-                    d[k] = q[k];
-                }
-                mul2(d[0], d[1], sc);
-                mul2(d[2], d[3], sc);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) d[k] = Arith<T>::rnd(d[k]);
-            };
             if (fast && sh.slow == 0) {
                 if (cnt > 0) {
-                    uint32_t cur = fd_div(e_w, bt.len), next = (cur + 1u) * L;
+                    uint32_t cur = fd_div(e_w + ((uint32_t)(cnt - 1) << 7), bt.len), floor_ = cur * L;
                     float sc = sh.s[cur], y = sh.y[cur];
-#pragma unroll
-                    for (int j = 0; j < PIPE_VECS; ++j) {
-                        if (j >= cnt) break;
+                    auto piece = [&](auto jc) {
+                        constexpr int j = decltype(jc)::value;
                         const uint32_t e0 = e_w + (uint32_t)(j << 7);
-                        if (e0 >= next) {                     // warp uniform
-                            ++cur;
-                            next += L;
+                        if (e0 < floor_) {                    // warp uniform
+                            --cur;
+                            floor_ -= L;
                             sc = sh.s[cur];
                             y = sh.y[cur];
                         }
@@ -725,7 +747,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
                         if (st_values) store4<T>(values + e, q);
                         if (st_dequant) store4<T>(dequant + e, d);
                         if (want_code) __stcs(reinterpret_cast<uint32_t*>(codes + e), packed);
-                    }
+                    };
+                    VQ_PIECES_DOWN(cnt, piece);
                 }
             } else if (in_regs && sh.slow == 0) {
 #pragma unroll
@@ -787,7 +810,7 @@ inline int64_t batches_of(const vq_channel_item& it, int64_t batch_elems, int ve
     const int64_t per = channels_per_batch(it, batch_elems, vec_elems);
     return (it.channels + per - 1) / per;
 }
-constexpr int64_t kSmallestBatch = 7168;    // the workspace is sized for the finest split any kernel uses
+constexpr int64_t kSmallestBatch = PIPE_BATCH;    // the workspace is sized for the finest split any kernel uses
 
 }  // namespace
 extern "C" size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items);
