@@ -12,6 +12,7 @@
 // HBM bound: sizeof(T) read per element + the requested outputs.
 #include <algorithm>
 #include <type_traits>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -98,6 +99,7 @@ struct BatchParams {
     const ChanBatch* batches;         // device
     int n_batches;
     float qmax;
+    float inv_qmax;                   // 1 / qmax when that is exact (qmax a power of two), else 0
     MxParams common;                  // table + shared-memory staging flags only
     int table_bytes;                  // shared memory taken by the staged tables
     long long wait_budget;            // pipelined kernel: clock cycles a wait may take before it gives up
@@ -411,6 +413,7 @@ static_assert(PIPE_VECS == 8, "VQ_PIECES_DOWN lists eight pieces");
 struct PipeShared {
     ChanShared ch[PIPE_GROUPS][2];
     int ok[PIPE_GROUPS];
+    int tables_ok[PIPE_GROUPS];
 };
 
 template <typename T, int TK>
@@ -469,21 +472,46 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         if (threadIdx.x == 0) {
             bool ok = true;
             int i = 0;
-            for (int b = blockIdx.x; b < p.n_batches && ok; b += gridDim.x, ++i) {
-                const int s = i % PIPE_STAGES;
-                const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
-                if (i >= PIPE_STAGES && !tc::mbar_wait_relaxed(EMPTY0 + 8u * s, ph ^ 1u, p.wait_budget)) { ok = false; break; }
-                if (b == p.skip_batch) continue;              // test hook: this batch's consumers will see their wait run out
-                const ChanBatch& bt = *(i < kSmemBatches ? static_cast<const ChanBatch*>(sbatches + i) : p.batches + b);
-                const vq_channel_item& it = *(items_staged ? static_cast<const vq_channel_item*>(sitems + bt.item) : p.items + bt.item);
-                const uint32_t L = (uint32_t)it.length;
-                if (bt.vec) {
-                    const uint32_t bytes = (uint32_t)bt.nc * L * (uint32_t)sizeof(T);
-                    tc::mbar_expect_tx(FULL0 + 8u * s, bytes);
-                    bulk_load(tc::smem_u32(ring + s * STAGE_BYTES), reinterpret_cast<const T*>(it.input) + (int64_t)bt.c0 * L,
-                              bytes, FULL0 + 8u * s);
+            // Every consumer group has its own sequence of batches (group g: this CTA's batches g, g + G, ...) and
+            // its own stage.  The producer serves whichever group has given its stage back, not the groups in turn:
+            // a group that is ahead of the others gets its next batch at once.
+            int k[PIPE_GROUPS];                               // batches of group g loaded so far
+            int left = 0;
+#pragma unroll
+            for (int g = 0; g < PIPE_GROUPS; ++g) k[g] = 0;
+            for (int b = blockIdx.x; b < p.n_batches; b += gridDim.x) ++left;
+            long long idle_since = clock64();
+            while (left > 0 && ok) {
+                bool progress = false;
+#pragma unroll
+                for (int g = 0; g < PIPE_GROUPS; ++g) {
+                    const int i = g + k[g] * PIPE_GROUPS;
+                    const int64_t b = blockIdx.x + (int64_t)i * gridDim.x;
+                    if (b >= p.n_batches) continue;
+                    const int s = i % PIPE_STAGES;
+                    const uint32_t ph = (uint32_t)(i / PIPE_STAGES) & 1u;
+                    if (i >= PIPE_STAGES && !tc::mbar_try_wait(EMPTY0 + 8u * s, ph ^ 1u)) continue;
+                    ++k[g];
+                    --left;
+                    progress = true;
+                    if (b == p.skip_batch) continue;          // test hook: this batch's consumers will see their wait run out
+                    const ChanBatch& bt = *(i < kSmemBatches ? static_cast<const ChanBatch*>(sbatches + i) : p.batches + b);
+                    const vq_channel_item& it = *(items_staged ? static_cast<const vq_channel_item*>(sitems + bt.item) : p.items + bt.item);
+                    const uint32_t L = (uint32_t)it.length;
+                    if (bt.vec) {
+                        const uint32_t bytes = (uint32_t)bt.nc * L * (uint32_t)sizeof(T);
+                        tc::mbar_expect_tx(FULL0 + 8u * s, bytes);
+                        bulk_load(tc::smem_u32(ring + s * STAGE_BYTES), reinterpret_cast<const T*>(it.input) + (int64_t)bt.c0 * L,
+                                  bytes, FULL0 + 8u * s);
+                    } else {
+                        tc::mbar_arrive(FULL0 + 8u * s);      // the consumers read this batch themselves
+                    }
+                }
+                if (progress) {
+                    idle_since = clock64();
                 } else {
-                    tc::mbar_arrive(FULL0 + 8u * s);          // the consumers read this batch themselves
+                    if (clock64() - idle_since > p.wait_budget) ok = false;
+                    __nanosleep(64);
                 }
             }
             if (!ok) atomicCAS(&g_channel_status, 0, 21);
@@ -526,11 +554,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         }
         if (tid == 0) {
             sh.slow = need_amax ? 0 : 1;
-            bool ok = tc::mbar_wait_relaxed(FULL0 + 8u * s, ph, p.wait_budget);
-            if (ok && !tables_ready) ok = tc::mbar_wait_relaxed(TABLE_BAR, 0u, p.wait_budget);   // the bulk copies of the tables have landed
-            ps.ok[group] = ok ? 1 : 0;
+            ps.ok[group] = tc::mbar_wait_relaxed(FULL0 + 8u * s, ph, p.wait_budget) ? 1 : 0;
         }
-        tables_ready = true;
         group_sync();
         if (!ps.ok[group]) {
             if (tid == 0) atomicCAS(&g_channel_status, 0, 22);
@@ -710,7 +735,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             if (need_amax) {
                 const uint32_t mb = sh.amax[c];
                 const float amax = __uint_as_float(mb);
-                sc = (mb != 0u && mb < 0x7F800000u) ? Arith<T>::rnd(__fdiv_rn(amax, p.qmax)) : 1.0f;
+                // amax / qmax; a multiplication gives the same correctly rounded number when qmax is a power of two
+                const float ratio = p.inv_qmax != 0.0f ? __fmul_rn(amax, p.inv_qmax) : __fdiv_rn(amax, p.qmax);
+                sc = (mb != 0u && mb < 0x7F800000u) ? Arith<T>::rnd(ratio) : 1.0f;
                 if (it.amax_out) store_one<T>(reinterpret_cast<T*>(it.amax_out) + cg, amax);
                 if (it.scale_out && !it.scale_in) store_one<T>(reinterpret_cast<T*>(it.scale_out) + cg, sc);
             }
@@ -724,7 +751,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
             sh.y[c] = d.y;
             sh.kind[c] = d.kind;
         }
+        // the tables are first needed here: their bulk copies had the first batch's reduction to land
+        if (!tables_ready && tid == 0) ps.tables_ok[group] = tc::mbar_wait_relaxed(TABLE_BAR, 0u, p.wait_budget) ? 1 : 0;
         group_sync();
+        if (!tables_ready && !ps.tables_ok[group]) {
+            if (tid == 0) atomicCAS(&g_channel_status, 0, 23);
+            break;
+        }
+        tables_ready = true;
         if (want_val || want_code) {
             if (fast && sh.slow == 0) {
                 if (cnt > 0) {
@@ -856,6 +890,11 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
     BatchParams& p = L.p;
     p = BatchParams{};
     p.qmax = (float)quant_max;
+    {
+        int ex = 0;
+        const float mant = frexpf(p.qmax, &ex);
+        p.inv_qmax = (mant == 0.5f && ex > -100 && ex < 100) ? 1.0f / p.qmax : 0.0f;
+    }
     p.wait_budget = PIPE_WAIT;
     p.skip_batch = -1;
     // Test hooks of the bounded waits: VOYAGER_B200_CHANNEL_WAIT_CYCLES shortens the budget and
