@@ -285,6 +285,26 @@ VQ_API int vq_conv_patches(const void* x, int dtype, int64_t N, int64_t H, int64
                            int dil_h, int dil_w, const void* scale, int64_t block, int64_t ssn, int64_t ssh, int64_t ssw,
                            int64_t ssc, void* out, int64_t ldk, void* stream);
 
+/* 2-D convolution as an implicit GEMM on the tensor cores (no patch matrix is written):
+ *   y[(n, ho, wo), o] = bias[o] + sum over (i, j, c) of
+ *       x[n, ho*stride_h - pad_h + i*dil_h, wo*stride_w - pad_w + j*dil_w, g*Cg + c] * wmat[o, (i*kw + j)*Cp + c]
+ * for the outputs o of group g (Cg = C / groups input channels, O / groups outputs per group), zero outside the
+ * image; fp32 accumulation, one rounding to bf16.  x: bf16, channels contiguous, pixels addressed by the element
+ * strides sn, sh, sw; with `x_scale` (bf16, may be NULL) every element is first multiplied by
+ * x_scale[n*ssn + h*ssh + w*ssw + channel / block] and rounded to bf16 once (`dequantize` of an MX activation with
+ * blocks along the channels, src/voyager_compiler/ops/quantized.py:182-227, fused into the operand staging).  wmat:
+ * the decoded bf16 weight as [O, vq_conv2d_weight_columns(Cg, kh, kw)], every tap's channels zero-padded to
+ * Cp = 64 * ceil(Cg / 64).  y: [N*Ho*Wo, O] bf16 (NHWC), Ho = (H + 2 pad_h - dil_h (kh-1) - 1) / stride_h + 1, Wo
+ * alike; bias bf16 [O] or NULL.  Needs Cg, sn, sh, sw multiples of 8, 16-byte aligned x, wmat, y and a block that
+ * is a power of two >= 8 (VQ_ERR_UNSUPPORTED otherwise: use vq_conv_patches + vq_gemm_bf16_tn).  `status` as in
+ * vq_gemm_bf16_tn (codes 11..14 name the warp role whose bounded wait ran out).  Serves `conv2d_mx`,
+ * src/voyager_compiler/ops/quantized.py:239-283 (upstream calls aten.conv2d on the decoded operands), groups included. */
+VQ_API int64_t vq_conv2d_weight_columns(int64_t channels_per_group, int kh, int kw);
+VQ_API int vq_conv2d_bf16(const void* x, int64_t N, int64_t H, int64_t W, int64_t C, int64_t sn, int64_t sh, int64_t sw,
+                          const void* x_scale, int64_t block, int64_t ssn, int64_t ssh, int64_t ssw, const void* wmat,
+                          int64_t O, int kh, int kw, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
+                          int dil_w, int groups, const void* bias, void* y, int32_t* status, void* stream);
+
 /* Y[M,N] = (a_codes * expand(a_scale))[M,K] @ (b_codes * expand(b_scale))[N,K]^T (+ bias), all
  * tensors bf16, scales [rows, K/block] with blocks along K; each product code*scale is rounded to
  * bf16 once, as the bf16 tensor arithmetic of the reference does, inside the operand staging of

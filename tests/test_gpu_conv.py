@@ -1,6 +1,7 @@
-"""conv2d_mx on the library's own GEMM (patch matrix + tcgen05 contraction) against the CPU oracle
-(oracle/voyager_oracle.py: conv2d_mx, following ops/quantized.py:239-283), and the patch matrix itself
-against torch's unfold, bit for bit."""
+"""conv2d_mx on the library's own tensor-core kernels (implicit GEMM, or patch matrix + contraction for the
+channel counts the implicit form does not take) against the CPU oracle (oracle/voyager_oracle.py: conv2d_mx,
+following ops/quantized.py:239-283), grouped convolutions included, and the patch matrix itself against
+torch's unfold, bit for bit."""
 import os
 import sys
 
@@ -115,6 +116,90 @@ def test_weight_matrix_one_pass_equals_decode_and_permute(layout, I, k, scaled):
     wd = ops._decode_operand("conv2d_mx", w, None, ws, 32 if scaled else None)
     want = (wd.permute(0, 2, 3, 1) if layout == "nchw" else wd.permute(3, 0, 1, 2)).reshape(O, -1)
     assert torch.equal(got[:, :want.shape[1]].view(torch.int16), want.contiguous().view(torch.int16))
+
+
+# (N, C, H, W, O, k, stride, padding, groups): tile widths 64 / 128 / 256, partial tiles in every direction,
+# several tiles per CTA, channel counts below and above one 64-channel step
+BIG = [
+    (4, 64, 28, 28, 320, 3, 1, 1, 1),             # 128-wide tiles, the last one partial
+    (8, 64, 56, 56, 512, 3, 1, 1, 1),             # 256-wide tiles, more tiles than SMs
+    (2, 96, 17, 19, 64, 3, 2, 1, 1),              # 64-wide tile; 96 channels = one and a half steps per tap
+    (2, 200, 9, 9, 136, 1, 1, 0, 1),              # pointwise through the gather; 200 = 3 steps + 8 channels
+    (2, 64, 12, 12, 96, 3, 1, 1, 2),              # two groups of 32 -> 48
+    (3, 128, 10, 10, 128, 3, 1, 1, 8),            # eight groups of 16 -> 16
+    (2, 48, 14, 14, 48, 5, 2, 2, 6),              # six groups of 8 -> 8
+    (1, 512, 7, 7, 512, 3, 1, 1, 1),              # deep K (72 steps), few pixels
+]
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("shape", BIG, ids=[str(i) for i in range(len(BIG))])
+def test_implicit_gemm_convolution_matches_oracle(shape, layout, monkeypatch):
+    N, C, H, W, O, k, st, pd, groups = shape
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(N, C, H, W, generator=g).bfloat16()
+    w = (torch.randn(O, C // groups, k, k, generator=g) * 0.05).bfloat16()
+    b = torch.randn(O, generator=g).bfloat16()
+    if layout == "nhwc":
+        x = x.permute(0, 2, 3, 1).contiguous()
+        if groups == 1:                                          # a grouped convolution keeps its weight OIHW
+            w = w.permute(2, 3, 1, 0).contiguous()
+    want = vo.conv2d_mx(x.float(), w.float(), b.float(), st, pd, 1, groups, layout=layout)
+    before = _lib.launch_count()
+    got = torch.ops.quantized_ops.conv2d_mx(x.cuda(), w.cuda(), b.cuda(), (st, st), (pd, pd), (1, 1), groups, layout=layout)
+    torch.cuda.synchronize()
+    launches = _lib.launch_count() - before
+    assert launches >= 1
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == tuple(want.shape)
+    rel = (got.float().cpu().double() - want.double()).norm() / want.double().norm()
+    assert rel <= 1e-2, rel
+    from voyager_compiler_b200.gemm_native import gemm_status
+    assert gemm_status("cuda") == 0
+    if groups == 1:
+        # the explicit form (patch matrix in memory) computes the same sums in the same order
+        monkeypatch.setenv("VOYAGER_B200_CONV", "patches")
+        ref = torch.ops.quantized_ops.conv2d_mx(x.cuda(), w.cuda(), b.cuda(), (st, st), (pd, pd), (1, 1), groups, layout=layout)
+        rel2 = (got.float() - ref.float()).norm() / ref.float().norm()
+        assert rel2 <= 1e-3, rel2
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("C,O,groups,k", [(64, 64, 2, 3), (128, 96, 4, 1), (64, 128, 1, 3)])
+def test_implicit_gemm_convolution_with_block_scales_and_groups(layout, C, O, groups, k):
+    """MX activations and weights (codes + power-of-two scales per 32 channels... 16 where a group is narrower), the
+    activation's scales multiplied in by the gather warps."""
+    from golden_util import golden_table
+    g = torch.Generator().manual_seed(17)
+    N, H, W = 2, 11, 13
+    bs = min(32, C // groups)
+    x = torch.randn(N, C, H, W, generator=g).bfloat16()
+    w = (torch.randn(O, C // groups, k, k, generator=g) * 0.05).bfloat16()
+    q = golden_table("int8")
+    w_hwio = layout == "nhwc" and groups == 1
+    if layout == "nhwc":
+        x = x.permute(0, 2, 3, 1).contiguous()
+    if w_hwio:
+        w = w.permute(2, 3, 1, 0).contiguous()
+    xs, xq = vo.quantize_mx(x, q, (3,) if layout == "nhwc" else (1,), bs, 127.0, True)
+    ws, wq = vo.quantize_mx(w, q, (2,) if w_hwio else (1,), bs, 127.0, True)
+    p = k // 2
+    want = vo.conv2d_mx(xq.float(), wq.float(), None, 1, p, 1, groups, input_scale=xs.float(), weight_scale=ws.float(),
+                        block_size=bs, layout=layout)
+    got = torch.ops.quantized_ops.conv2d_mx(xq.cuda(), wq.cuda(), None, (1, 1), (p, p), (1, 1), groups, input_scale=xs.cuda(),
+                                            weight_scale=ws.cuda(), block_size=bs, layout=layout)
+    rel = (got.float().cpu().double() - want.double()).norm() / want.double().norm()
+    assert rel <= 1e-2, rel
+
+
+def test_grouped_convolution_with_narrow_groups_uses_the_vendor_kernel():
+    """Depthwise and other groups narrower than 8 channels are not taken by the tensor-core kernels."""
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 16, 9, 9, generator=g).bfloat16()
+    w = (torch.randn(16, 1, 3, 3, generator=g) * 0.1).bfloat16()
+    want = vo.conv2d_mx(x.float(), w.float(), None, 1, 1, 1, 16)
+    got = torch.ops.quantized_ops.conv2d_mx(x.cuda(), w.cuda(), None, (1, 1), (1, 1), (1, 1), 16)
+    rel = (got.float().cpu().double() - want.double()).norm() / want.double().norm()
+    assert rel <= 1e-2, rel
 
 
 def test_vendor_switch_and_other_dtypes_agree(monkeypatch):

@@ -103,6 +103,8 @@ def _load():
         "vq_gptq_block": [vp, i64, i64, i64, ci, vp, i64, vp, ci, C.c_double, vp, vp, vp, i64, vp, vp, vp],
         "vq_conv_patches": [vp, ci, i64, i64, i64, i64, i64, i64, i64, i64, ci, ci, ci, ci, ci, ci, ci, ci,
                             vp, i64, i64, i64, i64, i64, vp, i64, vp],
+        "vq_conv2d_bf16": [vp, i64, i64, i64, i64, i64, i64, i64, vp, i64, i64, i64, i64, vp, i64, ci, ci, ci, ci, ci, ci, ci,
+                           ci, ci, vp, vp, vp, vp],
         "vq_dequantize_packed": [vp, ci, vp, ci, vp, vp, i64, i64, vp, ci, vp],
         "vq_gemm_bf16_tn": [vp, vp, vp, vp, i64, i64, i64, vp, vp],
         "vq_slice_csr": [vp, vp, vp, ci, i64, i64, ci, i64, i64, i64, vp, vp, vp, vp, C.c_size_t, vp],
@@ -135,6 +137,8 @@ def _load():
     lib.vq_filter_outlier_workspace.restype = C.c_size_t
     lib.vq_slice_csr_workspace.argtypes = [i64]
     lib.vq_slice_csr_workspace.restype = C.c_size_t
+    lib.vq_conv2d_weight_columns.argtypes = [i64, ci, ci]
+    lib.vq_conv2d_weight_columns.restype = i64
     lib.vq_row_codebook_workspace.argtypes = [i64, ci]
     lib.vq_row_codebook_workspace.restype = C.c_size_t
     for name, args in sigs.items():

@@ -1,11 +1,18 @@
-"""``conv2d_mx`` on this library's tensor-core GEMM (src/voyager_compiler/ops/quantized.py:239-283).
+"""``conv2d_mx`` on this library's tensor cores (src/voyager_compiler/ops/quantized.py:239-283).
 
 The convolution is the TN contraction ``patches[M, K] @ weight[O, K]^T``: ``M = N * Ho * Wo`` output
-positions, ``K = kh * kw * C`` ordered (kh, kw, c).  ``vq_conv_patches`` builds the patch matrix from the
-decoded activation; an NCHW activation is first made channels-last by the same entry point (its 1x1 patch
-matrix, a tiled transposition), and a 1x1, stride-1, unpadded convolution needs no patch matrix beyond that.  The decoded weight is kept as ``[O, K]`` (zero-padded to a multiple of 8 columns) for as
-long as the weight tensor lives, since a weight is static.  bf16, ``groups == 1``; everything else stays on
-the vendor convolution (``supported`` says which).
+positions, ``K = kh * kw * C`` ordered (kh, kw, c).  Two forms:
+
+* implicit (``vq_conv2d_bf16``): the GEMM kernel's own warps gather the patches from the channels-last
+  activation while they stage the operand tiles, so no patch matrix exists in memory; the activation's block
+  scales are multiplied in on the way; grouped convolutions run as one launch over (group, tile).  Needs the
+  channels per group to be a multiple of 8.
+* explicit (``vq_conv_patches`` + ``vq_gemm_bf16_tn``): the patch matrix is written once; used for the channel
+  counts the implicit form does not take (a 3-channel stem), ``groups == 1`` only.
+
+An NCHW activation is first made channels-last by ``vq_conv_patches`` (its 1x1 patch matrix, a tiled
+transposition with the scaling fused).  The decoded weight matrix is kept for as long as the weight tensor
+lives, since a weight is static.  bf16; other dtypes stay on the vendor convolution (``supported`` says which).
 """
 from __future__ import annotations
 
@@ -21,10 +28,25 @@ from .gemm_native import _status_tensor
 _weight_cache: dict = {}
 
 
-def supported(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], groups: int) -> bool:
+def weight_layout(layout: str, groups: int) -> str:
+    """``"nhwc"`` weights are HWIO, except that a grouped convolution keeps its weight OIHW (ops/layout.py:152-175)."""
+    return "nchw" if (layout == "nchw" or groups != 1) else "nhwc"
+
+
+def implicit_ok(channels: int, groups: int) -> bool:
+    """The implicit-GEMM kernel takes the convolution (``VOYAGER_B200_CONV=patches`` forces the explicit form)."""
+    return os.environ.get("VOYAGER_B200_CONV", "native") != "patches" and groups >= 1 and channels % groups == 0 \
+        and (channels // groups) % 8 == 0
+
+
+def supported(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], groups: int, layout: str = "nchw") -> bool:
     if os.environ.get("VOYAGER_B200_CONV", "native") == "vendor":
         return False
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or groups != 1 or x.ndim != 4 or w.ndim != 4:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.ndim != 4 or w.ndim != 4 or groups < 1:
+        return False
+    channels = x.shape[1] if layout == "nchw" else x.shape[3]
+    outputs = w.shape[0] if weight_layout(layout, groups) == "nchw" else w.shape[3]
+    if groups != 1 and not (implicit_ok(channels, groups) and outputs % groups == 0):
         return False
     return bias is None or (bias.dtype == torch.bfloat16 and bias.ndim == 1)
 
@@ -101,6 +123,31 @@ def _weight_matrix(weight, weight_scale, weight_code, block_size, layout) -> tor
     return wm
 
 
+def _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, groups) -> torch.Tensor:
+    """The decoded weight for the implicit kernel: ``[O, kh * kw * Cp]`` with every tap's ``Cg`` channels padded with
+    zeros to ``Cp = 64 * ceil(Cg / 64)``, cached per weight."""
+    parts = [t for t in (weight, weight_scale, weight_code) if t is not None]
+    key = (tuple((t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in parts), block_size, layout, "taps", groups)
+    hit = _weight_cache.get(key)
+    if hit is not None and all(r() is t for r, t in zip(hit[0], parts)):
+        return hit[1]
+    layout = weight_layout(layout, groups)
+    if layout == "nchw":
+        O, Cg, kh, kw = weight.shape
+    else:
+        kh, kw, Cg, O = weight.shape
+    wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)[:, :kh * kw * Cg]
+    cols = _lib.lib.vq_conv2d_weight_columns(Cg, kh, kw)
+    cp = cols // (kh * kw)
+    if cp != Cg:
+        wm = torch.nn.functional.pad(wm.reshape(O, kh * kw, Cg), (0, cp - Cg)).reshape(O, cols)
+    wm = wm.contiguous()
+    if len(_weight_cache) >= 64:
+        _weight_cache.pop(next(iter(_weight_cache)))
+    _weight_cache[key] = ([weakref.ref(t) for t in parts], wm)
+    return wm
+
+
 def fusable_scale(x: torch.Tensor, scale: Optional[torch.Tensor], block_size, layout) -> bool:
     """True when ``scale`` holds one value per block of channels at every pixel of ``x`` (the layout
     ``quantize_mx`` along the channel axis produces), which the patch kernels multiply in on the way."""
@@ -112,11 +159,77 @@ def fusable_scale(x: torch.Tensor, scale: Optional[torch.Tensor], block_size, la
     return list(scale.shape) == want
 
 
+def _conv2d_implicit(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout, x_scale,
+                     groups) -> Optional[torch.Tensor]:
+    """The implicit-GEMM form; ``None`` when the activation's strides or the block size rule it out."""
+    if layout == "nchw":
+        N, C, H, W = x.shape
+        sn, sc, sh, sw = x.stride()
+    else:
+        N, H, W, C = x.shape
+        sn, sh, sw, sc = x.stride()
+    if weight_layout(layout, groups) == "nchw":
+        O, kh, kw = weight.shape[0], weight.shape[2], weight.shape[3]
+    else:
+        kh, kw, O = weight.shape[0], weight.shape[1], weight.shape[3]
+    dev = x.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    sc_args = (None, 0, 0, 0, 0)
+    if x_scale is not None:
+        if block_size < 8 or block_size & (block_size - 1):
+            return None
+        x_scale = x_scale.contiguous()
+        if layout == "nchw":
+            ssn, ssc, ssh, ssw = x_scale.stride()
+        else:
+            ssn, ssh, ssw, ssc = x_scale.stride()
+    with torch.cuda.device(dev):
+        if sc != 1:
+            # channels strided (NCHW): one tiled pass makes the activation channels-last, scaled on the way
+            xt = torch.empty((N, H, W, C), dtype=torch.bfloat16, device=dev)
+            pre = (None, 0, 0, 0, 0, 0) if x_scale is None else (x_scale.data_ptr(), block_size, ssn, ssh, ssw, ssc)
+            flat = sh == W * sw and (pre[0] is None or pre[3] == W * pre[4])
+            h_, w_, sh_ = (1, H * W, H * W * sw) if flat else (H, W, sh)
+            ssh_ = (H * W * pre[4] if flat else pre[3])
+            _lib.check(_lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, N, h_, w_, C, sn, sh_, sw, sc, 1, 1, 1, 1, 0, 0, 1, 1,
+                                                pre[0], pre[1], pre[2], ssh_, pre[4], pre[5], xt.data_ptr(), C, stream), "conv2d_mx")
+            x = xt
+            sn, sh, sw, sc = H * W * C, W * C, C, 1
+        elif x_scale is not None:
+            if ssc != 1:
+                return None
+            sc_args = (x_scale.data_ptr(), block_size, ssn, ssh, ssw)
+        if sn % 8 or sh % 8 or sw % 8 or x.data_ptr() % 16:
+            return None
+        wm = _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, groups)
+        Ho = (H + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+        Wo = (W + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+        if Ho <= 0 or Wo <= 0:
+            raise RuntimeError("conv2d_mx: the kernel window is larger than the padded input")
+        out = torch.empty((N * Ho * Wo, O), dtype=torch.bfloat16, device=dev)
+        bias_c = bias.contiguous() if bias is not None else None
+        _lib.check(_lib.lib.vq_conv2d_bf16(
+            x.data_ptr(), N, H, W, C, sn, sh, sw, *sc_args, wm.data_ptr(), O, kh, kw, stride[0], stride[1], padding[0], padding[1],
+            dilation[0], dilation[1], groups, bias_c.data_ptr() if bias_c is not None else None, out.data_ptr(),
+            _status_tensor(dev).data_ptr(), stream), "conv2d_mx")
+    y = out.view(N, Ho, Wo, O)
+    return y.permute(0, 3, 1, 2) if layout == "nchw" else y
+
+
 def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout,
-              x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+              x_scale: Optional[torch.Tensor] = None, groups: int = 1) -> torch.Tensor:
     """``x``: the activation (bf16, NCHW or NHWC as ``layout`` says, any strides), decoded, or still to be
     multiplied by ``x_scale`` (see :func:`fusable_scale`).  Returns the result in the layout's logical shape;
-    for ``"nchw"`` its memory is channels-last (the GEMM writes [N*Ho*Wo, O])."""
+    for ``"nchw"`` its memory is channels-last (the kernels write [N*Ho*Wo, O])."""
+    channels = x.shape[1] if layout == "nchw" else x.shape[3]
+    if implicit_ok(channels, groups):
+        y = _conv2d_implicit(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout, x_scale,
+                             groups)
+        if y is not None:
+            return y
+    if groups != 1:
+        raise NotImplementedError("conv2d_mx: grouped convolutions need channels per group in multiples of 8 and "
+                                  "16-byte aligned pixels")
     wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)
     sc_args = (None, 0, 0, 0, 0, 0)
     if layout == "nchw":

@@ -360,6 +360,11 @@ int launch_gemm(bool fused, const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
 
 }  // namespace
 
+// for the convolution kernel (vq_conv_gemm.cu): operand map with the 128-byte swizzle over a [rows, K] bf16 matrix
+int vq_make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+    return make_map(map, ptr, rows, K, box_rows);
+}
+
 extern "C" {
 
 int vq_gemm_bf16_tn(const void* A, const void* B, const void* bias, void* Y, int64_t M, int64_t N, int64_t K,

@@ -498,22 +498,23 @@ def _pair(v):
 def conv2d_mx(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, *, input_scale=None,
               weight_scale=None, block_size=None, input_code=None, weight_code=None, layout="nchw"):
     """ops/quantized.py:239-283: operands are decoded and scaled by this package's kernels (blocks
-    along the channel axis go through the strided scale layout).  bf16 convolutions with one group run as
-    patch matrix + this library's tensor-core GEMM (``conv_native``; an ``"nchw"`` result then comes back
-    with channels-last strides); other dtypes and grouped convolutions use the vendor kernel, as upstream.
+    along the channel axis go through the strided scale layout).  bf16 convolutions run on this library's
+    tensor-core kernels (``conv_native``: implicit GEMM, grouped included, or patch matrix + GEMM; an ``"nchw"``
+    result then comes back with channels-last strides); other dtypes use the vendor kernel, as upstream.
     ``"nhwc"``: NHWC activations, HWIO weight, NHWC result."""
     assert layout in ("nchw", "nhwc"), layout
     _require_cuda(input, "conv2d_mx")
     from . import conv_native
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
-    native = conv_native.supported(input, weight, bias, groups) and padding[0] >= 0 and padding[1] >= 0
+    native = conv_native.supported(input, weight, bias, groups, layout) and padding[0] >= 0 and padding[1] >= 0
     if native and input_code is None and conv_native.fusable_scale(input, input_scale, block_size, layout):
-        # the activation's block scales are multiplied in by the patch kernels: no decoded copy of the input
+        # the activation's block scales are multiplied in while the operand tiles are staged: no decoded copy of the input
         return conv_native.conv2d_mx(input, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size,
-                                     layout, x_scale=input_scale)
+                                     layout, x_scale=input_scale, groups=groups)
     x = _decode_operand("conv2d_mx", input, input_code, input_scale, block_size)
     if native:
-        return conv_native.conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout)
+        return conv_native.conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout,
+                                     groups=groups)
     w = _decode_operand("conv2d_mx", weight, weight_code, weight_scale, block_size)
     if layout == "nhwc":
         x = x.permute(0, 3, 1, 2)
