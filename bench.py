@@ -613,6 +613,91 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def conv_cases(res, timed, Q, qmap, g, dev, steps):
+    """conv2d_mx: ResNet-50-shaped bf16 convolutions, batch 32, MXINT8 codes with block 32 along the channels
+    (plain bf16 for the 3-channel stem).  Per case: the library's default form (implicit GEMM where the
+    channel count allows, else patch matrix + GEMM), the patch-matrix form forced, the default with the decoded
+    weight matrix rebuilt on every call, and the vendor convolution on the same operands decoded by this
+    library's kernels.  Two grouped cases (ResNeXt-style 32 groups) close the list."""
+    import torch
+    from voyager_compiler_b200 import conv_native
+    conv_shapes = [("stem_7x7s2_3to64_224", 3, 224, 64, 7, 2, 3, 1), ("l1_3x3_64to64_56", 64, 56, 64, 3, 1, 1, 1),
+                   ("l1_1x1_64to256_56", 64, 56, 256, 1, 1, 0, 1), ("l2_3x3_128to128_28", 128, 28, 128, 3, 1, 1, 1),
+                   ("l3_3x3_256to256_14", 256, 14, 256, 3, 1, 1, 1), ("l4_1x1_1024to2048_s2_14", 1024, 14, 2048, 1, 2, 0, 1),
+                   ("l4_3x3_512to512_7", 512, 7, 512, 3, 1, 1, 1),
+                   ("resnext_3x3_256to256_g32_56", 256, 56, 256, 3, 1, 1, 32), ("resnext_3x3_1024to1024_g32_14", 1024, 14, 1024, 3, 1, 1, 32)]
+    for name, C, HW, O, k, s_, p_, groups in conv_shapes:
+        for layout in ("nhwc", "nchw"):
+            xc = torch.randn(32, C, HW, HW, generator=g, device=dev).bfloat16()
+            wc = (torch.randn(O, C // groups, k, k, generator=g, device=dev) * 0.05).bfloat16()
+            w_hwio = layout == "nhwc" and groups == 1
+            if layout == "nhwc":
+                xc = xc.permute(0, 2, 3, 1).contiguous()
+            if w_hwio:
+                wc = wc.permute(2, 3, 1, 0).contiguous()
+            kw = {}
+            bs = min(32, C // groups)
+            if C % 32 == 0 and bs >= 8:
+                ax_x, ax_w = ((3,) if layout == "nhwc" else (1,)), ((2,) if w_hwio else (1,))
+                xs_c, xc = Q.quantize_mx(xc, qmap, ax_x, bs, 127.0, True)
+                ws_c, wc = Q.quantize_mx(wc, qmap, ax_w, bs, 127.0, True)
+                kw = dict(input_scale=xs_c, weight_scale=ws_c, block_size=bs)
+            Ho = (HW + 2 * p_ - k) // s_ + 1
+            cflops = 2.0 * 32 * Ho * Ho * O * (C // groups) * k * k
+            call = lambda: Q.conv2d_mx(xc, wc, None, (s_, s_), (p_, p_), (1, 1), groups, layout=layout, **kw)
+            os.environ["VOYAGER_B200_CONV"] = "native"
+            med_n, _ = timed(call, steps)
+
+            def call_cold():                     # the weight matrix rebuilt on every call, as the vendor arm decodes it
+                conv_native._weight_cache.clear()
+                return call()
+            med_c, _ = timed(call_cold, steps)
+            entry = {"ms": med_n, "tflops": cflops / med_n / 1e9, "ms_weight_not_cached": med_c,
+                     "form": "implicit" if conv_native.implicit_ok(C, groups) else "patches"}
+            if groups == 1:
+                os.environ["VOYAGER_B200_CONV"] = "patches"
+                entry["patches_ms"], _ = timed(call, steps)
+            os.environ["VOYAGER_B200_CONV"] = "vendor"
+            med_v, _ = timed(call, steps)
+            os.environ["VOYAGER_B200_CONV"] = "native"
+            entry.update(vendor_ms=med_v, vendor_tflops=cflops / med_v / 1e9)
+            res[f"conv2d_mx_{name}_{layout}"] = entry
+
+
+def run_conv(args):
+    """The conv2d_mx cases alone (see conv_cases): one JSON line."""
+    import torch
+    import voyager_compiler_b200 as vb
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev); g.manual_seed(4)
+    Q = torch.ops.quantized_ops
+    qmap = torch.from_numpy(vb.tables.build_table("int8").view("int16").copy()).view(torch.bfloat16).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts), min(ts)
+
+    res = {}
+    sampler = ClockSampler(dev.index or 0); sampler.start()
+    conv_cases(res, timed, Q, qmap, g, dev, args.steps)
+    clocks = sampler.stop()
+    from voyager_compiler_b200.gemm_native import gemm_status
+    print(json.dumps({"workload": "conv2d_mx, ResNet-50 / ResNeXt-shaped layers, batch 32, bf16 MXINT8 block 32", "results": res,
+                      "gemm_status": gemm_status(dev), "clocks": clocks}))
+
+
 def run_linear(args):
     """cfg5: MX-quantized linear, X[8192,4096] x W[11008,4096]^T, MXINT8 block 32 (single GPU).
     Times the quantize_mx of the activations, the fused GEMM, the plain GEMM (dequantize kernels +
@@ -688,41 +773,7 @@ def run_linear(args):
     med, best = timed(lambda: Q.linear_mx(oc, wq, None, input_scale=os_, weight_scale=ws, block_size=32, A_data=od,
                                           A_indices=oi, A_indptr=op_), args.steps)
     res["linear_mx_with_outliers"] = {"ms": med, "tflops": flops / med / 1e9, "nnz": nnz}
-    # conv2d_mx: ResNet-50-shaped bf16 convolutions, batch 32, MXINT8 codes with block 32 along the channels
-    # (plain bf16 for the 3-channel stem); the library's patch matrix + GEMM against the vendor convolution
-    # on the same decoded operands
-    conv_shapes = [("stem_7x7s2_3to64_224", 3, 224, 64, 7, 2, 3), ("l1_3x3_64to64_56", 64, 56, 64, 3, 1, 1),
-                   ("l1_1x1_64to256_56", 64, 56, 256, 1, 1, 0), ("l2_3x3_128to128_28", 128, 28, 128, 3, 1, 1),
-                   ("l3_3x3_256to256_14", 256, 14, 256, 3, 1, 1), ("l4_1x1_1024to2048_s2_14", 1024, 14, 2048, 1, 2, 0),
-                   ("l4_3x3_512to512_7", 512, 7, 512, 3, 1, 1)]
-    from voyager_compiler_b200 import conv_native
-    for name, C, HW, O, k, s_, p_ in conv_shapes:
-        for layout in ("nhwc", "nchw"):
-            xc = torch.randn(32, C, HW, HW, generator=g, device=dev).bfloat16()
-            wc = (torch.randn(O, C, k, k, generator=g, device=dev) * 0.05).bfloat16()
-            if layout == "nhwc":
-                xc, wc = xc.permute(0, 2, 3, 1).contiguous(), wc.permute(2, 3, 1, 0).contiguous()
-            kw = {}
-            if C % 32 == 0:
-                ax_x, ax_w = ((3,), (2,)) if layout == "nhwc" else ((1,), (1,))
-                xs_c, xc = Q.quantize_mx(xc, qmap, ax_x, 32, 127.0, True)
-                ws_c, wc = Q.quantize_mx(wc, qmap, ax_w, 32, 127.0, True)
-                kw = dict(input_scale=xs_c, weight_scale=ws_c, block_size=32)
-            Ho = (HW + 2 * p_ - k) // s_ + 1
-            cflops = 2.0 * 32 * Ho * Ho * O * C * k * k
-            call = lambda: Q.conv2d_mx(xc, wc, None, (s_, s_), (p_, p_), (1, 1), 1, layout=layout, **kw)
-            os.environ["VOYAGER_B200_CONV"] = "native"
-            med_n, _ = timed(call, args.steps)
-
-            def call_cold():                     # the [O, K] weight matrix rebuilt on every call, as the vendor arm decodes it
-                conv_native._weight_cache.clear()
-                return call()
-            med_c, _ = timed(call_cold, args.steps)
-            os.environ["VOYAGER_B200_CONV"] = "vendor"
-            med_v, _ = timed(call, args.steps)
-            os.environ["VOYAGER_B200_CONV"] = "native"
-            res[f"conv2d_mx_{name}_{layout}"] = {"ms": med_n, "tflops": cflops / med_n / 1e9, "ms_weight_not_cached": med_c, "vendor_ms": med_v,
-                                                 "vendor_tflops": cflops / med_v / 1e9}
+    conv_cases(res, timed, Q, qmap, g, dev, args.steps)
     # GPTQ compensation of one [4096, 4096] weight on the NF4 / block-64 grid (Hessian of 8192 synthetic tokens):
     # the column walk alone (64 block launches + 63 trailing updates) and the whole entry point
     import types
@@ -1017,7 +1068,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="fewer than 32: reduced model for profiler captures")
     ap.add_argument("--kernel-only", action="store_true", help="device-timed part only (profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (skip the other configurations)")
-    ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise", "channel"],
+    ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise", "channel", "conv"],
                     help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
     ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
     args = ap.parse_args()
@@ -1029,6 +1080,9 @@ def main():
         return
     if args.workload == "channel":
         run_channel(args)
+        return
+    if args.workload == "conv":
+        run_conv(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -123,9 +123,23 @@ def _weight_matrix(weight, weight_scale, weight_code, block_size, layout) -> tor
     return wm
 
 
-def _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, groups) -> torch.Tensor:
-    """The decoded weight for the implicit kernel: ``[O, kh * kw * Cp]`` with every tap's ``Cg`` channels padded with
-    zeros to ``Cp = 64 * ceil(Cg / 64)``, cached per weight."""
+def _merged_groups(groups: int, cg: int) -> int:
+    """How many neighbouring groups the implicit kernel treats as one: a k-step is 64 channels of one tap, so groups
+    narrower than that are merged (their weights become block-diagonal) until a step is full."""
+    sg = 1
+    while cg * sg * 2 <= 64 and groups % (sg * 2) == 0:
+        sg *= 2
+    return sg
+
+
+def _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, groups):
+    """The decoded weight for the implicit kernel and the group count to run it with.
+
+    ``[O, kh * kw * Cp]``: every tap's channels padded with zeros to ``Cp``, a multiple of 64.  Groups narrower than
+    64 channels are merged ``sg`` at a time: the kernel then sees ``groups / sg`` groups of ``sg * Cg`` channels whose
+    weight is block-diagonal (output ``o`` of original group ``g`` has its ``Cg`` weights at channel offset
+    ``(g % sg) * Cg`` and zeros elsewhere), so that a 64-channel step of the contraction is not mostly padding.
+    Cached per weight."""
     parts = [t for t in (weight, weight_scale, weight_code) if t is not None]
     key = (tuple((t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in parts), block_size, layout, "taps", groups)
     hit = _weight_cache.get(key)
@@ -136,16 +150,23 @@ def _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, g
         O, Cg, kh, kw = weight.shape
     else:
         kh, kw, Cg, O = weight.shape
-    wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)[:, :kh * kw * Cg]
-    cols = _lib.lib.vq_conv2d_weight_columns(Cg, kh, kw)
+    wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)[:, :kh * kw * Cg].reshape(O, kh * kw, Cg)
+    sg = _merged_groups(groups, Cg) if groups > 1 else 1
+    if sg > 1:
+        wide = torch.zeros((O, kh * kw, sg, Cg), dtype=wm.dtype, device=wm.device)
+        rows = torch.arange(O, device=wm.device)
+        wide[rows, :, (rows // (O // groups)) % sg, :] = wm
+        wm = wide.reshape(O, kh * kw, sg * Cg)
+    cg = sg * Cg
+    cols = _lib.lib.vq_conv2d_weight_columns(cg, kh, kw)
     cp = cols // (kh * kw)
-    if cp != Cg:
-        wm = torch.nn.functional.pad(wm.reshape(O, kh * kw, Cg), (0, cp - Cg)).reshape(O, cols)
-    wm = wm.contiguous()
+    if cp != cg:
+        wm = torch.nn.functional.pad(wm, (0, cp - cg))
+    wm = wm.reshape(O, cols).contiguous()
     if len(_weight_cache) >= 64:
         _weight_cache.pop(next(iter(_weight_cache)))
-    _weight_cache[key] = ([weakref.ref(t) for t in parts], wm)
-    return wm
+    _weight_cache[key] = ([weakref.ref(t) for t in parts], (wm, groups // sg))
+    return wm, groups // sg
 
 
 def fusable_scale(x: torch.Tensor, scale: Optional[torch.Tensor], block_size, layout) -> bool:
@@ -201,7 +222,7 @@ def _conv2d_implicit(x, weight, bias, stride, padding, dilation, weight_scale, w
             sc_args = (x_scale.data_ptr(), block_size, ssn, ssh, ssw)
         if sn % 8 or sh % 8 or sw % 8 or x.data_ptr() % 16:
             return None
-        wm = _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, groups)
+        wm, run_groups = _weight_matrix_taps(weight, weight_scale, weight_code, block_size, layout, groups)
         Ho = (H + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
         Wo = (W + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
         if Ho <= 0 or Wo <= 0:
@@ -210,7 +231,7 @@ def _conv2d_implicit(x, weight, bias, stride, padding, dilation, weight_scale, w
         bias_c = bias.contiguous() if bias is not None else None
         _lib.check(_lib.lib.vq_conv2d_bf16(
             x.data_ptr(), N, H, W, C, sn, sh, sw, *sc_args, wm.data_ptr(), O, kh, kw, stride[0], stride[1], padding[0], padding[1],
-            dilation[0], dilation[1], groups, bias_c.data_ptr() if bias_c is not None else None, out.data_ptr(),
+            dilation[0], dilation[1], run_groups, bias_c.data_ptr() if bias_c is not None else None, out.data_ptr(),
             _status_tensor(dev).data_ptr(), stream), "conv2d_mx")
     y = out.view(N, Ho, Wo, O)
     return y.permute(0, 3, 1, 2) if layout == "nchw" else y

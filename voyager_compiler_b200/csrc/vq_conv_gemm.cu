@@ -8,17 +8,19 @@
 // decoded [O, kh * kw * Cp] matrix with every tap's channels padded to Cp = 64 * ceil(Cg / 64) (zeros).
 //
 // One persistent CTA per SM, output tile 128 pixels x BN channels, K step = 64 channels of one tap:
-//   8 gather warps   each thread owns 4 (pixel, 16-byte chunk) slots of the 128 x 64 A tile: it finds the
-//                    pixel's window position once per tile, then per k-step loads its chunks straight from
-//                    the activation (zero outside the image or past the last channel), multiplies the
-//                    block scale in (one bf16 rounding per product, as `codes * scale` in bf16 gives) and
-//                    stores them in the 128-byte-swizzled K-major layout the MMA reads; loads run one
-//                    k-step ahead of the stores;
+//   16 gather warps  in 4 sets, set s staging the k-steps s, s + 4, ... into stage s of the ring.  Each thread of a
+//                    set owns 8 (pixel, 16-byte chunk) slots of the 128 x 64 A tile: it finds the pixels' window
+//                    positions once per tile, then per k-step loads its chunks straight from the activation
+//                    (zero outside the image or past the last channel), multiplies the block scale in (one bf16
+//                    rounding per product, as `codes * scale` in bf16 gives) and stores them in the
+//                    128-byte-swizzled K-major layout the MMA reads.  The proxy fence between the stores and
+//                    the hand-over waits for the thread's loads, so a set has one step in flight: the four
+//                    sets give the pipeline its depth;
 //   1 weight warp    one thread issues the TMA tile load of the BN x 64 weight tile of the k-step;
 //   1 MMA warp       one thread issues tcgen05.mma (bf16 x bf16 -> fp32) into a double-buffered accumulator
 //                    in tensor memory and commits to mbarriers;
 //   4 epilogue warps tcgen05.ld, bias, rounding to bf16, stores of [M, O] rows.
-// full[s] counts the 8 gather warps and the weight thread's expect_tx; every wait is bounded and a wait
+// full[s] counts the 4 warps of set s and the weight thread's expect_tx; every wait is bounded and a wait
 // that runs out records a code in `status` and winds the CTA down.
 #include <cuda.h>
 
@@ -34,9 +36,10 @@ int vq_make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t
 namespace {
 
 constexpr int CM = 128, CK = 64;
-constexpr int CSTAGES = 4;
-constexpr int GATHER_WARPS = 8, GATHER_THREADS = GATHER_WARPS * 32;
-constexpr int SLOTS = CM * 8 / GATHER_THREADS;            // 4 chunks per gather thread per k-step
+constexpr int NSETS = 4, SET_WARPS = 4, SET_THREADS = SET_WARPS * 32;   // gather warps: NSETS sets, one per ring stage
+constexpr int CSTAGES = NSETS;
+constexpr int GATHER_WARPS = NSETS * SET_WARPS;
+constexpr int SLOTS = CM * 8 / SET_THREADS;               // 8 chunks per gather thread per k-step
 constexpr int CONV_THREADS = (GATHER_WARPS + 2 + 4) * 32;
 constexpr long long CWAIT = 4000000000ll;                 // ~2 s of SM clocks
 
@@ -89,7 +92,7 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_gemm_kernel(const __grid
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < CSTAGES; ++s) {
-            tc::mbar_init(FULL0 + 8u * s, GATHER_WARPS + 1);
+            tc::mbar_init(FULL0 + 8u * s, SET_WARPS + 1);
             tc::mbar_init(EMPTY0 + 8u * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -111,84 +114,76 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_gemm_kernel(const __grid
 
     if (warp < GATHER_WARPS) {
         // ------------------------------------------------------------------ activation gather
-        const int t = warp * 32 + lane;
+        // Set s (SET_WARPS warps) stages the k-steps s, s + NSETS, ... of every tile, always into stage s of the
+        // ring.  A step is: issue the loads, wait for the stage, store, proxy fence, arrive.  The fence waits for
+        // the thread's own loads, so a set has one step in flight; the NSETS sets overlap theirs.
+        const int set = warp / SET_WARPS;
+        const int t = (warp - set * SET_WARPS) * 32 + lane;    // thread of the set
         const int ch = t & 7;                                  // this thread's 16-byte chunk of the 128-byte rows
-        int stage = 0;
+        const int stage = set;
         uint32_t phase = 0;
         bool ok = true;
+        int kbase = 0;                                         // k-steps of earlier tiles, modulo NSETS
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const int g = tile / tiles_per_group, rem = tile - g * tiles_per_group;
             const int m0 = (rem % p.tiles_m) * CM;
-            // window origin of this thread's four pixels
-            int64_t pix_off[SLOTS], sc_off[SLOTS];
-            int hi0[SLOTS], wi0[SLOTS];
+            // window origin of this thread's pixels (32-bit element offsets: the host checks the sizes)
+            int pix_off[SLOTS], sc_off[SLOTS], hw0[SLOTS];
 #pragma unroll
             for (int j = 0; j < SLOTS; ++j) {
-                const int r = j * (GATHER_THREADS / 8) + (t >> 3);
+                const int r = j * (SET_THREADS / 8) + (t >> 3);
                 const uint32_t m = (uint32_t)(m0 + r);
                 if (m < (uint32_t)p.M) {
                     const uint32_t n = fd_div(m, p.div_howo), hw = m - n * (uint32_t)p.HoWo;
                     const uint32_t ho = fd_div(hw, p.div_wo), wo = hw - ho * (uint32_t)p.Wo;
-                    hi0[j] = (int)ho * p.stride_h - p.pad_h;
-                    wi0[j] = (int)wo * p.stride_w - p.pad_w;
-                    pix_off[j] = (int64_t)n * p.sn + (int64_t)hi0[j] * p.sh + (int64_t)wi0[j] * p.sw + (int64_t)g * p.Cg;
-                    sc_off[j] = (int64_t)n * p.ssn + (int64_t)hi0[j] * p.ssh + (int64_t)wi0[j] * p.ssw;
+                    const int hi0 = (int)ho * p.stride_h - p.pad_h, wi0 = (int)wo * p.stride_w - p.pad_w;
+                    hw0[j] = (hi0 << 16) | (wi0 & 0xFFFF);
+                    pix_off[j] = (int)((int64_t)n * p.sn + (int64_t)hi0 * p.sh + (int64_t)wi0 * p.sw + (int64_t)g * p.Cg);
+                    sc_off[j] = (int)((int64_t)n * p.ssn + (int64_t)hi0 * p.ssh + (int64_t)wi0 * p.ssw);
                 } else {
-                    hi0[j] = -0x40000000;                      // no tap brings this row inside the image
-                    wi0[j] = 0;
+                    hw0[j] = (int)0xC0000000;                  // row -16384: no tap brings it inside the image
                     pix_off[j] = 0;
                     sc_off[j] = 0;
                 }
             }
-            uint4 cur[SLOTS], nxt[SLOTS];
-            uint32_t cur_s[SLOTS], nxt_s[SLOTS];
-            int ti = 0, tj = 0, cb = 0;                        // tap and channel step of the k-step being LOADED
-            auto load_step = [&](uint4* c, uint32_t* s2) {
+            // first k-step of this tile that belongs to the set: global step numbers kbase + k are dealt round robin
+            int k = (set - kbase + NSETS) % NSETS;
+            kbase = (kbase + p.num_k) % NSETS;
+            for (; k < p.num_k; k += NSETS) {
+                const int tap = k / p.cblocks, cb = k - tap * p.cblocks;
+                const int ti = tap / p.kw, tj = tap - ti * p.kw;
                 const int dh = ti * p.dil_h, dw = tj * p.dil_w;
                 const int cch = cb * CK + ch * 8;              // first channel of this thread's chunk within the group
-                const int64_t tap_off = (int64_t)dh * p.sh + (int64_t)dw * p.sw + cch;
-                const int64_t tap_soff = (int64_t)dh * p.ssh + (int64_t)dw * p.ssw;
+                const int tap_off = dh * (int)p.sh + dw * (int)p.sw + cch;
+                const int tap_soff = dh * (int)p.ssh + dw * (int)p.ssw + ((g * p.Cg + cch) >> p.block_shift);
+                uint4 c[SLOTS];
+                uint32_t s2[SLOTS];
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j) {
-                    const bool in = (uint32_t)(hi0[j] + dh) < (uint32_t)p.H && (uint32_t)(wi0[j] + dw) < (uint32_t)p.W && cch < p.Cg;
+                    const int hi = (hw0[j] >> 16) + dh, wi = (int)(int16_t)(hw0[j] & 0xFFFF) + dw;
+                    const bool in = (uint32_t)hi < (uint32_t)p.H && (uint32_t)wi < (uint32_t)p.W && cch < p.Cg;
                     if (in) {
-                        c[j] = __ldg(reinterpret_cast<const uint4*>(p.x + pix_off[j] + tap_off));
-                        s2[j] = p.xs ? (uint32_t)__ldg(p.xs + sc_off[j] + tap_soff + ((g * p.Cg + cch) >> p.block_shift)) * 0x00010001u : 0u;
+                        c[j] = __ldg(reinterpret_cast<const uint4*>(p.x + (pix_off[j] + tap_off)));
+                        s2[j] = p.xs ? (uint32_t)__ldg(p.xs + (sc_off[j] + tap_soff)) * 0x00010001u : 0u;
                     } else {
                         c[j] = make_uint4(0u, 0u, 0u, 0u);
                         s2[j] = 0u;
                     }
                 }
-                if (++cb == p.cblocks) {
-                    cb = 0;
-                    if (++tj == p.kw) {
-                        tj = 0;
-                        ++ti;
-                    }
-                }
-            };
-            load_step(cur, cur_s);
-            for (int k = 0; k < p.num_k; ++k) {
-                if (k + 1 < p.num_k) load_step(nxt, nxt_s);   // in flight while this step is stored
                 if (lane == 0) ok = tc::mbar_wait(EMPTY0 + 8u * stage, phase ^ 1u, CWAIT);
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
                 uint8_t* st = smem + stage * STAGE_BYTES;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j) {
-                    const int r = j * (GATHER_THREADS / 8) + (t >> 3);
-                    const uint4 v = p.xs ? mul_chunk(cur[j], cur_s[j]) : cur[j];
+                    const int r = j * (SET_THREADS / 8) + (t >> 3);
+                    const uint4 v = p.xs ? mul_chunk(c[j], s2[j]) : c[j];
                     *reinterpret_cast<uint4*>(st + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
                 }
                 tc::fence_proxy_async();                      // generic-proxy stores -> visible to the MMA
                 __syncwarp();
                 if (lane == 0) tc::mbar_arrive(FULL0 + 8u * stage);
-                if (++stage == CSTAGES) { stage = 0; phase ^= 1u; }
-#pragma unroll
-                for (int j = 0; j < SLOTS; ++j) {
-                    cur[j] = nxt[j];
-                    cur_s[j] = nxt_s[j];
-                }
+                phase ^= 1u;
             }
         }
         if (!ok && lane == 0) conv_fail(p.status, 11);
@@ -343,6 +338,15 @@ int vq_conv2d_bf16(const void* x, int64_t N, int64_t H, int64_t W, int64_t C, in
     if (Cg % 8 != 0 || sn % 8 || sh % 8 || sw % 8 || (uintptr_t)x % 16 || (uintptr_t)wmat % 16 || (uintptr_t)y % 16)
         return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: channels per group, pixel strides (multiples of 8) and 16-byte alignment", name);
     VQ_REQUIRE(M < (1ll << 31) && O < (1ll << 31) && H < (1 << 24) && W < (1 << 24), "%s: sizes must be below 2^31", name);
+    if (H + pad_h + (int64_t)dil_h * kh >= 16384 || W + pad_w + (int64_t)dil_w * kw >= 16384)
+        return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: images of up to 16383 pixels a side", name);
+    {
+        // the gather addresses the activation (and its scales) by 32-bit element offsets
+        const int64_t reach = (N - 1) * sn + (H - 1 + pad_h) * sh + (W - 1 + pad_w) * sw + C;
+        const int64_t sreach = x_scale ? (N - 1) * ssn + (H - 1 + pad_h) * ssh + (W - 1 + pad_w) * ssw + C : 0;
+        if (reach >= (1ll << 31) || sreach >= (1ll << 31) || sn < 0 || sh < 0 || sw < 0 || ssn < 0 || ssh < 0 || ssw < 0)
+            return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: the activation must span fewer than 2^31 elements, strides non-negative", name);
+    }
     int block_shift = 0;
     if (x_scale) {
         while ((1ll << block_shift) < block) ++block_shift;
