@@ -613,7 +613,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def conv_cases(res, timed, Q, qmap, g, dev, steps):
+def conv_cases(res, timed, Q, qmap, g, dev, steps, only=None):
     """conv2d_mx: ResNet-50-shaped bf16 convolutions, batch 32, MXINT8 codes with block 32 along the channels
     (plain bf16 for the 3-channel stem).  Per case: the library's default form (implicit GEMM where the
     channel count allows, else patch matrix + GEMM), the patch-matrix form forced, the default with the decoded
@@ -628,6 +628,8 @@ def conv_cases(res, timed, Q, qmap, g, dev, steps):
                    ("resnext_3x3_256to256_g32_56", 256, 56, 256, 3, 1, 1, 32), ("resnext_3x3_1024to1024_g32_14", 1024, 14, 1024, 3, 1, 1, 32)]
     for name, C, HW, O, k, s_, p_, groups in conv_shapes:
         for layout in ("nhwc", "nchw"):
+            if only and only not in f"{name}_{layout}":
+                continue
             xc = torch.randn(32, C, HW, HW, generator=g, device=dev).bfloat16()
             wc = (torch.randn(O, C // groups, k, k, generator=g, device=dev) * 0.05).bfloat16()
             w_hwio = layout == "nhwc" and groups == 1
@@ -691,7 +693,7 @@ def run_conv(args):
 
     res = {}
     sampler = ClockSampler(dev.index or 0); sampler.start()
-    conv_cases(res, timed, Q, qmap, g, dev, args.steps)
+    conv_cases(res, timed, Q, qmap, g, dev, args.steps, args.only)
     clocks = sampler.stop()
     from voyager_compiler_b200.gemm_native import gemm_status
     print(json.dumps({"workload": "conv2d_mx, ResNet-50 / ResNeXt-shaped layers, batch 32, bf16 MXINT8 block 32", "results": res,
@@ -1070,6 +1072,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (skip the other configurations)")
     ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise", "channel", "conv"],
                     help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
+    ap.add_argument("--only", default=None, help="--workload conv: run the cases whose name contains this text")
     ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
     args = ap.parse_args()
     if args.workload == "linear":

@@ -124,6 +124,11 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_gemm_kernel(const __grid
         uint32_t phase = 0;
         bool ok = true;
         int kbase = 0;                                         // k-steps of earlier tiles, modulo NSETS
+        // the numbers every step uses, in registers
+        const uint16_t* const x = p.x;
+        const uint16_t* const xs = p.xs;
+        const int H = p.H, W = p.W, sh = (int)p.sh, sw = (int)p.sw, ssh = (int)p.ssh, ssw = (int)p.ssw, dil_h = p.dil_h,
+                  dil_w = p.dil_w, cblocks = p.cblocks, kw = p.kw, Cg = p.Cg, num_k = p.num_k, block_shift = p.block_shift;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const int g = tile / tiles_per_group, rem = tile - g * tiles_per_group;
             const int m0 = (rem % p.tiles_m) * CM;
@@ -148,36 +153,46 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_gemm_kernel(const __grid
             }
             // first k-step of this tile that belongs to the set: global step numbers kbase + k are dealt round robin
             int k = (set - kbase + NSETS) % NSETS;
-            kbase = (kbase + p.num_k) % NSETS;
-            for (; k < p.num_k; k += NSETS) {
-                const int tap = k / p.cblocks, cb = k - tap * p.cblocks;
-                const int ti = tap / p.kw, tj = tap - ti * p.kw;
-                const int dh = ti * p.dil_h, dw = tj * p.dil_w;
+            kbase = (kbase + num_k) % NSETS;
+            int tap = k / cblocks, cb = k - tap * cblocks;     // once per tile; afterwards the counters advance by NSETS steps
+            int ti = tap / kw, tj = tap - ti * kw;
+            for (; k < num_k; k += NSETS) {
+                const int dh = ti * dil_h, dw = tj * dil_w;
                 const int cch = cb * CK + ch * 8;              // first channel of this thread's chunk within the group
-                const int tap_off = dh * (int)p.sh + dw * (int)p.sw + cch;
-                const int tap_soff = dh * (int)p.ssh + dw * (int)p.ssw + ((g * p.Cg + cch) >> p.block_shift);
+                const int tap_off = dh * sh + dw * sw + cch;
+                const int tap_soff = dh * ssh + dw * ssw + ((g * Cg + cch) >> block_shift);
+                const bool c_in = cch < Cg;
+                // Loads first, nothing that consumes them: the SM issues in order, so an instruction that needs a
+                // loaded value (a select against zero, the widening of a scale) would hold back the loads behind
+                // it.  Chunks outside the image are loaded from offset 0 and zeroed when they are stored.
                 uint4 c[SLOTS];
-                uint32_t s2[SLOTS];
+                uint32_t sraw[SLOTS];
+                uint32_t valid = 0u;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j) {
                     const int hi = (hw0[j] >> 16) + dh, wi = (int)(int16_t)(hw0[j] & 0xFFFF) + dw;
-                    const bool in = (uint32_t)hi < (uint32_t)p.H && (uint32_t)wi < (uint32_t)p.W && cch < p.Cg;
-                    if (in) {
-                        c[j] = __ldg(reinterpret_cast<const uint4*>(p.x + (pix_off[j] + tap_off)));
-                        s2[j] = p.xs ? (uint32_t)__ldg(p.xs + (sc_off[j] + tap_soff)) * 0x00010001u : 0u;
-                    } else {
-                        c[j] = make_uint4(0u, 0u, 0u, 0u);
-                        s2[j] = 0u;
+                    const bool in = (uint32_t)hi < (uint32_t)H && (uint32_t)wi < (uint32_t)W && c_in;
+                    valid |= (in ? 1u : 0u) << j;
+                    c[j] = __ldg(reinterpret_cast<const uint4*>(x + (in ? pix_off[j] + tap_off : 0)));
+                    sraw[j] = xs ? (uint32_t)__ldg(xs + (in ? sc_off[j] + tap_soff : 0)) : 0u;
+                }
+                cb += NSETS;
+                while (cb >= cblocks) {
+                    cb -= cblocks;
+                    if (++tj == kw) {
+                        tj = 0;
+                        ++ti;
                     }
                 }
-                if (lane == 0) ok = tc::mbar_wait(EMPTY0 + 8u * stage, phase ^ 1u, CWAIT);
+                if (lane == 0) ok = tc::mbar_wait_relaxed(EMPTY0 + 8u * stage, phase ^ 1u, CWAIT);
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
                 uint8_t* st = smem + stage * STAGE_BYTES;
 #pragma unroll
                 for (int j = 0; j < SLOTS; ++j) {
                     const int r = j * (SET_THREADS / 8) + (t >> 3);
-                    const uint4 v = p.xs ? mul_chunk(c[j], s2[j]) : c[j];
+                    uint4 v = xs ? mul_chunk(c[j], sraw[j] * 0x00010001u) : c[j];
+                    if (!((valid >> j) & 1u)) v = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(st + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
                 }
                 tc::fence_proxy_async();                      // generic-proxy stores -> visible to the MMA
@@ -197,7 +212,7 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_gemm_kernel(const __grid
                 const int g = tile / tiles_per_group, rem = tile - g * tiles_per_group;
                 const int row0 = g * p.Og + (rem / p.tiles_m) * BN;
                 for (int k = 0; k < p.num_k; ++k) {
-                    if (!tc::mbar_wait(EMPTY0 + 8u * stage, phase ^ 1u, CWAIT)) { ok = false; break; }
+                    if (!tc::mbar_wait_relaxed(EMPTY0 + 8u * stage, phase ^ 1u, CWAIT)) { ok = false; break; }
                     tc::mbar_expect_tx(FULL0 + 8u * stage, B_BYTES);
                     tc::tma_load_2d(base + stage * STAGE_BYTES + A_BYTES, &tmW, k * CK, row0, FULL0 + 8u * stage);
                     if (++stage == CSTAGES) { stage = 0; phase ^= 1u; }
@@ -245,7 +260,7 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_gemm_kernel(const __grid
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const int g = tile / tiles_per_group, rem = tile - g * tiles_per_group;
             const int m0 = (rem % p.tiles_m) * CM, n0 = (rem / p.tiles_m) * BN;
-            if (lane == 0) ok = tc::mbar_wait(TFULL0 + 8u * acc, acc_phase, CWAIT);
+            if (lane == 0) ok = tc::mbar_wait_relaxed(TFULL0 + 8u * acc, acc_phase, CWAIT);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
             tc::tc_fence_after();
