@@ -234,6 +234,15 @@ VQ_API int vq_dequantize_transpose(const void* in, const void* scale, int64_t ba
 VQ_API int vq_gemm_bf16_tn_batched(const void* A, const void* B, void* Y, int64_t batch, int64_t M, int64_t N, int64_t K,
                                    int a_shared, int b_shared, int32_t* status, void* stream);
 
+/* The fp32 form of the contraction above on the tensor cores: Y[b][M,N] = A[b][M,K] @ B[b][N,K]^T (+ bias, batch 1
+ * only), all tensors fp32 row-major; the tensor cores read the operands as tf32 (the low 13 bits of every operand
+ * are ignored: exact for decoded MX operands -- codes of up to 11 significant bits times a power-of-two scale --
+ * and 2^-11 relative otherwise) and accumulate in fp32.  K a multiple of 4, operands 16-byte aligned; a_shared /
+ * b_shared as in vq_gemm_bf16_tn_batched.  Serves `linear_mx` / `matmul_mx` / `conv2d_mx` on fp32 operands,
+ * src/voyager_compiler/ops/quantized.py:239-432 (upstream calls the fp32 F.linear / matmul / conv2d there). */
+VQ_API int vq_gemm_f32_tn_batched(const void* A, const void* B, const void* bias, void* Y, int64_t batch, int64_t M,
+                                  int64_t N, int64_t K, int a_shared, int b_shared, int32_t* status, void* stream);
+
 /* The same GEMM writing its [M,N] result into columns [col_offset, col_offset+N) of EVERY buffer in
  * Ys (n_outputs <= 8 device pointers, rows ldy elements apart): a rank of a column-sharded linear
  * passes its own output and its peers' (peer-mapped memory), so the all-gather of the reference-side

@@ -202,6 +202,30 @@ def test_grouped_convolution_with_narrow_groups_uses_the_vendor_kernel():
     assert rel <= 1e-2, rel
 
 
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("shape", SHAPES, ids=[str(i) for i in range(len(SHAPES))])
+def test_fp32_convolution_runs_on_the_tensor_cores_as_tf32(shape, layout, monkeypatch):
+    """fp32 operands: patch matrix + the tf32 contraction (the low 13 bits of every operand are ignored), fp32
+    result; no vendor convolution."""
+    x, w, b, st, pd, dl = _case(shape, 13)
+    x, w, b = x.float() + 0.001 * torch.randn(x.shape), w.float() * 1.003, b.float()      # not bf16-representable
+    if layout == "nhwc":
+        x, w = x.permute(0, 2, 3, 1).contiguous(), w.permute(2, 3, 1, 0).contiguous()
+    want = vo.conv2d_mx(x, w, b, st, pd, dl, 1, layout=layout)
+
+    def boom(*a, **k):
+        raise AssertionError("the vendor convolution was called")
+    monkeypatch.setattr(torch.ops.aten, "conv2d", boom)
+    got = torch.ops.quantized_ops.conv2d_mx(x.cuda(), w.cuda(), b.cuda(), st, pd, dl, 1, layout=layout)
+    torch.cuda.synchronize()
+    monkeypatch.undo()
+    assert got.dtype == torch.float32 and tuple(got.shape) == tuple(want.shape)
+    rel = (got.cpu().double() - want.double()).norm() / want.double().norm()
+    assert rel <= 2e-3, rel
+    from voyager_compiler_b200.gemm_native import gemm_status
+    assert gemm_status("cuda") == 0
+
+
 def test_vendor_switch_and_other_dtypes_agree(monkeypatch):
     x, w, b, st, pd, dl = _case(SHAPES[1], 3)
     a = torch.ops.quantized_ops.conv2d_mx(x.cuda(), w.cuda(), b.cuda(), st, pd, dl, 1)
@@ -210,7 +234,7 @@ def test_vendor_switch_and_other_dtypes_agree(monkeypatch):
     rel = (a.float() - v.float()).norm() / v.float().norm()
     assert rel <= 1e-2, rel
     monkeypatch.delenv("VOYAGER_B200_CONV")
-    f = torch.ops.quantized_ops.conv2d_mx(x.float().cuda(), w.float().cuda(), b.float().cuda(), st, pd, dl, 1)   # fp32: vendor kernel
+    f = torch.ops.quantized_ops.conv2d_mx(x.float().cuda(), w.float().cuda(), b.float().cuda(), st, pd, dl, 1)   # fp32: tf32 contraction
     assert f.dtype == torch.float32
     rel = (a.float() - f).norm() / f.norm()
     assert rel <= 1e-2, rel

@@ -282,3 +282,55 @@ def test_dequantize_transpose_equals_dequantize_then_transpose():
         got = gemm_native._decode_transposed("test", x, None, s, 32)
         assert torch.equal(got, want), (batch, K, N)
         assert torch.equal(gemm_native._decode_transposed("test", x, None, None, None), x.transpose(-1, -2).contiguous())
+
+
+def _mx_pair_f32(a_shape, b_shape, seed, b_axis, pow2=True):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(*a_shape, generator=g)
+    b = torch.randn(*b_shape, generator=g) * 0.05
+    q = golden_table("int8")
+    sa, qa = vo.quantize_mx(a, q, (-1,), 32, 127.0, pow2)
+    sb, qb = vo.quantize_mx(b, q, (b_axis,), 32, 127.0, pow2)
+    return qa, sa, qb, sb
+
+
+@pytest.mark.parametrize("pow2,tol", [(True, 1e-5), (False, 2e-3)])
+@pytest.mark.parametrize("a_shape,N", [((300, 256), 200), ((2, 70, 132), 520), ((64,), 96)])
+def test_fp32_linear_mx_runs_on_the_tensor_cores_as_tf32(a_shape, N, pow2, tol, monkeypatch):
+    """fp32 operands (ops/quantized.py:295-348 on fp32 tensors): decoded by this library, contracted as tf32 with
+    fp32 accumulation.  Codes times power-of-two scales are exact in tf32, so only the summation order differs
+    from the fp32 oracle; arbitrary fp32 scales lose the low 13 bits of every decoded operand."""
+    K = a_shape[-1]
+    qa, sa, qb, sb = _mx_pair_f32(a_shape, (N, K), 40 + N, -1, pow2)
+    bias = torch.randn(N)
+    want = vo.linear_mx(qa, qb, bias, input_scale=sa, weight_scale=sb, block_size=32)
+    before = _lib.launch_count()
+    _no_vendor_gemm(monkeypatch)
+    got = Q.linear_mx(qa.cuda(), qb.cuda(), bias.cuda(), input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32)
+    torch.cuda.synchronize()
+    monkeypatch.undo()
+    assert _lib.launch_count() >= before + 2
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.dtype == torch.float32 and got.shape == want.shape
+    assert _rel(got, want) <= tol
+
+
+@pytest.mark.parametrize("a_shape,b_shape", [((2, 3, 130, 64), (2, 3, 64, 200)), ((3, 90, 64), (64, 300)), ((150, 96), (96, 72))])
+def test_fp32_matmul_mx_runs_on_the_tensor_cores_as_tf32(a_shape, b_shape, monkeypatch):
+    qa, sa, qb, sb = _mx_pair_f32(a_shape, b_shape, 77, -2)
+    want = vo.matmul_mx(qa, qb, input_scale=sa, weight_scale=sb, block_size=32)
+    _no_vendor_gemm(monkeypatch)
+    got = Q.matmul_mx(qa.cuda(), qb.cuda(), input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32)
+    torch.cuda.synchronize()
+    monkeypatch.undo()
+    assert gemm_native.gemm_status("cuda") == 0
+    assert got.dtype == torch.float32 and got.shape == want.shape
+    assert _rel(got, want) <= 1e-5
+
+
+def test_fp32_vendor_switch(monkeypatch):
+    qa, sa, qb, sb = _mx_pair_f32((64, 128), (96, 128), 3, -1)
+    a = Q.linear_mx(qa.cuda(), qb.cuda(), None, input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32)
+    monkeypatch.setenv("VOYAGER_B200_FP32", "vendor")
+    b = Q.linear_mx(qa.cuda(), qb.cuda(), None, input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32)
+    assert _rel(a, b.cpu()) <= 1e-5

@@ -109,6 +109,7 @@ def _load():
         "vq_gemm_bf16_tn": [vp, vp, vp, vp, i64, i64, i64, vp, vp],
         "vq_slice_csr": [vp, vp, vp, ci, i64, i64, ci, i64, i64, i64, vp, vp, vp, vp, C.c_size_t, vp],
         "vq_gemm_bf16_tn_batched": [vp, vp, vp, i64, i64, i64, i64, ci, ci, vp, vp],
+        "vq_gemm_f32_tn_batched": [vp, vp, vp, vp, i64, i64, i64, i64, ci, ci, vp, vp],
         "vq_dequantize_transpose": [vp, vp, i64, i64, i64, i64, i64, vp, vp],
         "vq_gemm_bf16_tn_scatter": [vp, vp, vp, C.POINTER(C.c_void_p), ci, i64, i64, i64, i64, i64, vp, vp],
         "vq_linear_mx": [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp],

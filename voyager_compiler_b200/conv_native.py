@@ -42,19 +42,25 @@ def implicit_ok(channels: int, groups: int) -> bool:
 def supported(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], groups: int, layout: str = "nchw") -> bool:
     if os.environ.get("VOYAGER_B200_CONV", "native") == "vendor":
         return False
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.ndim != 4 or w.ndim != 4 or groups < 1:
+    if x.dtype != w.dtype or x.ndim != 4 or w.ndim != 4 or groups < 1:
+        return False
+    if x.dtype == torch.float32:
+        # fp32: patch matrix + the tf32 contraction (VOYAGER_B200_FP32=vendor keeps the vendor kernel), one group
+        if os.environ.get("VOYAGER_B200_FP32", "tensor") == "vendor" or groups != 1:
+            return False
+    elif x.dtype != torch.bfloat16:
         return False
     channels = x.shape[1] if layout == "nchw" else x.shape[3]
     outputs = w.shape[0] if weight_layout(layout, groups) == "nchw" else w.shape[3]
     if groups != 1 and not (implicit_ok(channels, groups) and outputs % groups == 0):
         return False
-    return bias is None or (bias.dtype == torch.bfloat16 and bias.ndim == 1)
+    return bias is None or (bias.dtype == x.dtype and bias.ndim == 1)
 
 
 def _weight_matrix_one_pass(weight, weight_scale, weight_code, block_size, layout) -> Optional[torch.Tensor]:
     """The [O, K] weight by one launch of the patch kernel (a transposition with the block scales multiplied
     in), for plain or MX-scaled weights without a codebook; None when that form does not apply."""
-    if weight_code is not None or not weight.is_contiguous() or weight.data_ptr() % 16:
+    if weight_code is not None or not weight.is_contiguous() or weight.data_ptr() % 16 or weight.dtype != torch.bfloat16:
         return None
     dev = weight.device
     if layout == "nchw":
@@ -243,7 +249,7 @@ def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_c
     multiplied by ``x_scale`` (see :func:`fusable_scale`).  Returns the result in the layout's logical shape;
     for ``"nchw"`` its memory is channels-last (the kernels write [N*Ho*Wo, O])."""
     channels = x.shape[1] if layout == "nchw" else x.shape[3]
-    if implicit_ok(channels, groups):
+    if x.dtype == torch.bfloat16 and implicit_ok(channels, groups):
         y = _conv2d_implicit(x, weight, bias, stride, padding, dilation, weight_scale, weight_code, block_size, layout, x_scale,
                              groups)
         if y is not None:
@@ -252,6 +258,7 @@ def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_c
         raise NotImplementedError("conv2d_mx: grouped convolutions need channels per group in multiples of 8 and "
                                   "16-byte aligned pixels")
     wm = _weight_matrix(weight, weight_scale, weight_code, block_size, layout)
+    dt = _lib.VQ_BF16 if x.dtype == torch.bfloat16 else _lib.VQ_F32
     sc_args = (None, 0, 0, 0, 0, 0)
     if layout == "nchw":
         N, C, H, W = x.shape
@@ -279,7 +286,7 @@ def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_c
         raise RuntimeError("conv2d_mx: the kernel window is larger than the padded input")
     M = N * Ho * Wo
     dev = x.device
-    out = torch.empty((M, O), dtype=torch.bfloat16, device=dev)
+    out = torch.empty((M, O), dtype=x.dtype, device=dev)
     if M and O:
         stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
@@ -288,11 +295,11 @@ def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_c
                 # matrix), so that the patch rows below are copied in 16-byte pieces
                 # (scaled on the way when the scale was not applied yet); image rows that follow one another in
                 # memory are handed over as one long row
-                xt = torch.empty((N, H, W, C), dtype=torch.bfloat16, device=dev)
+                xt = torch.empty((N, H, W, C), dtype=x.dtype, device=dev)
                 flat = sh == W * sw and (sc_args[0] is None or sc_args[3] == W * sc_args[4])
                 h_, w_, sh_ = (1, H * W, H * W * sw) if flat else (H, W, sh)
                 ssh_ = (H * W * sc_args[4] if flat else sc_args[3])
-                _lib.check(_lib.lib.vq_conv_patches(x.data_ptr(), _lib.VQ_BF16, N, h_, w_, C, sn, sh_, sw, sc, 1, 1, 1, 1, 0, 0, 1, 1,
+                _lib.check(_lib.lib.vq_conv_patches(x.data_ptr(), dt, N, h_, w_, C, sn, sh_, sw, sc, 1, 1, 1, 1, 0, 0, 1, 1,
                                                     sc_args[0], sc_args[1], sc_args[2], ssh_, sc_args[4], sc_args[5],
                                                     xt.data_ptr(), C, stream), "conv2d_mx")
                 x = xt
@@ -304,12 +311,18 @@ def conv2d_mx(x, weight, bias, stride, padding, dilation, weight_scale, weight_c
             if pointwise:
                 a = x
             else:
-                a = torch.empty((M, Kp), dtype=torch.bfloat16, device=dev)
+                a = torch.empty((M, Kp), dtype=x.dtype, device=dev)
                 _lib.check(_lib.lib.vq_conv_patches(
-                    x.data_ptr(), _lib.VQ_BF16, N, H, W, C, sn, sh, sw, sc, kh, kw, stride[0], stride[1], padding[0], padding[1],
+                    x.data_ptr(), dt, N, H, W, C, sn, sh, sw, sc, kh, kw, stride[0], stride[1], padding[0], padding[1],
                     dilation[0], dilation[1], *sc_args, a.data_ptr(), Kp, stream), "conv2d_mx")
             bias_c = bias.contiguous() if bias is not None else None
-            _lib.check(_lib.lib.vq_gemm_bf16_tn(a.data_ptr(), wm.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
-                                                out.data_ptr(), M, O, Kp, _status_tensor(dev).data_ptr(), stream), "conv2d_mx")
+            bias_p = bias_c.data_ptr() if bias_c is not None else None
+            if x.dtype == torch.bfloat16:
+                rc = _lib.lib.vq_gemm_bf16_tn(a.data_ptr(), wm.data_ptr(), bias_p, out.data_ptr(), M, O, Kp,
+                                              _status_tensor(dev).data_ptr(), stream)
+            else:                                                     # fp32: the tensor cores read the operands as tf32
+                rc = _lib.lib.vq_gemm_f32_tn_batched(a.data_ptr(), wm.data_ptr(), bias_p, out.data_ptr(), 1, M, O, Kp, 0, 1,
+                                                     _status_tensor(dev).data_ptr(), stream)
+            _lib.check(rc, "conv2d_mx")
     y = out.view(N, Ho, Wo, O)
     return y.permute(0, 3, 1, 2) if layout == "nchw" else y

@@ -78,7 +78,9 @@ __device__ __forceinline__ uint4 scale_chunk(uint4 c, uint32_t s2) {
     return o;
 }
 
-template <bool FUSED>
+// TF32: the operands are fp32 matrices read by the tensor cores as tf32 (K step 32 elements = the same 128-byte
+// rows), the result and the bias are fp32; plain (TMA-fed) variant only.
+template <bool FUSED, bool TF32 = false>
 __global__ void __launch_bounds__(FUSED ? (PRODUCER_WARPS_FUSED + 5) * 32 : 192, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -94,7 +96,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int NPROD = FUSED ? PRODUCER_WARPS_FUSED : 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mma_warp = NPROD, epi_warp0 = NPROD + 1;
-    const int num_k = (p.K + BK - 1) / BK;
+    static_assert(!(FUSED && TF32), "the fused producer stages bf16 codes");
+    constexpr int BKE = TF32 ? BK / 2 : BK;                    // elements per k-step: 128 bytes either way
+    const int num_k = (p.K + BKE - 1) / BKE;
     const int tiles_per_batch = p.tiles_m * p.tiles_n;
     const int n_tiles = tiles_per_batch * p.batch;
 
@@ -136,8 +140,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int k = 0; k < num_k; ++k) {
                         if (!tc::mbar_wait(EMPTY0 + 8u * stage, phase ^ 1u, WAIT_BUDGET)) { ok = false; break; }
                         tc::mbar_expect_tx(FULL0 + 8u * stage, STAGE_BYTES);
-                        tc::tma_load_2d(base + stage * STAGE_BYTES, &tmA, k * BK, m0, FULL0 + 8u * stage);
-                        tc::tma_load_2d(base + stage * STAGE_BYTES + A_BYTES, &tmB, k * BK, n0, FULL0 + 8u * stage);
+                        tc::tma_load_2d(base + stage * STAGE_BYTES, &tmA, k * BKE, m0, FULL0 + 8u * stage);
+                        tc::tma_load_2d(base + stage * STAGE_BYTES + A_BYTES, &tmB, k * BKE, n0, FULL0 + 8u * stage);
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
                 }
@@ -158,6 +162,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int k = 0; k < num_k; ++k) {
                     uint4 c[SLOTS];
                     uint32_t s2[SLOTS];
+                    uint32_t outside = 0u;
 #pragma unroll
                     for (int j = 0; j < SLOTS; ++j) {
                         const int slot = j * NT + t;
@@ -167,14 +172,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const int rows = isA ? p.M : p.N;
                         const uint16_t* codes = isA ? p.a_codes : p.b_codes;
                         const uint16_t* scl = isA ? p.a_scale : p.b_scale;
-                        if (grow < rows) {
-                            c[j] = __ldg(reinterpret_cast<const uint4*>(codes + (size_t)grow * p.K + k * BK + ch * 8));
-                            uint32_t s = __ldg(scl + (size_t)grow * p.blocks_per_row + k * 2 + (ch >> 2));
-                            s2[j] = s * 0x00010001u;
-                        } else {
-                            c[j] = make_uint4(0, 0, 0, 0);
-                            s2[j] = 0;
-                        }
+                        // loads only: the SM issues in order, and an instruction that consumes a loaded value here
+                        // (a select against zero, the widening of the scale) would hold back the loads behind it;
+                        // rows past the end read row 0 and are zeroed when they are stored
+                        const size_t srow = grow < rows ? (size_t)grow : 0;
+                        c[j] = __ldg(reinterpret_cast<const uint4*>(codes + srow * p.K + k * BK + ch * 8));
+                        s2[j] = __ldg(scl + srow * p.blocks_per_row + k * 2 + (ch >> 2));
+                        outside |= (grow >= rows ? 1u : 0u) << j;
                     }
                     if (lane == 0) ok = tc::mbar_wait(EMPTY0 + 8u * stage, phase ^ 1u, WAIT_BUDGET);
                     ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
@@ -188,7 +192,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         // 16-byte chunk index xor-ed with (r mod 8): the 128-byte swizzle
                         const int rr = r < BM ? r : r - BM;
                         uint8_t* tilep = st + (r < BM ? 0 : A_BYTES);
-                        *reinterpret_cast<uint4*>(tilep + rr * 128 + ((ch ^ (rr & 7)) << 4)) = scale_chunk(c[j], s2[j]);
+                        const uint4 v = ((outside >> j) & 1u) ? make_uint4(0, 0, 0, 0) : scale_chunk(c[j], s2[j] * 0x00010001u);
+                        *reinterpret_cast<uint4*>(tilep + rr * 128 + ((ch ^ (rr & 7)) << 4)) = v;
                     }
                     tc::fence_proxy_async();      // make the generic-proxy stores visible to the MMA
                     __syncwarp();
@@ -201,7 +206,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else if (warp == mma_warp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = tc::idesc_bf16_f32(BM, BN);
+            const uint32_t idesc = TF32 ? tc::idesc_tf32_f32(BM, BN) : tc::idesc_bf16_f32(BM, BN);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
@@ -215,8 +220,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
                     const uint64_t da = tc::smem_desc_k_sw128(sa), db = tc::smem_desc_k_sw128(sb);
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)   // 32 bytes of K per instruction: +2 in 16-byte units
-                        tc::mma_f16(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < BK / 16; ++kk) {  // 32 bytes of K per instruction: +2 in 16-byte units
+                        if (TF32) tc::mma_tf32(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                        else tc::mma_f16(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                    }
                     tc::mma_commit(EMPTY0 + 8u * stage);  // frees the stage once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -247,6 +254,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 tc::tmem_ld_32x32(taddr + c * 32, r);
                 tc::tmem_ld_wait();
                 const int col0 = n0 + c * 32;
+                if (TF32) {
+                    if (row < p.M && col0 < p.N) {
+                        const float* bias = reinterpret_cast<const float*>(p.bias);
+                        if (bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __ldg(bias + col0 + j)));
+                        }
+                        const size_t off = (size_t)bi * p.y_batch_stride + (size_t)row * p.ldy + p.col_offset + col0;
+                        for (int d = 0; d < p.n_outputs; ++d) {
+                            float* dst = reinterpret_cast<float*>(p.Y[d]) + off;
+                            if (col0 + 32 <= p.N && (off & 3) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    *reinterpret_cast<uint4*>(dst + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                            } else {
+                                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+                            }
+                        }
+                    }
+                    continue;
+                }
                 if (row < p.M && col0 < p.N) {
                     uint32_t o[16];
 #pragma unroll
@@ -321,6 +350,21 @@ int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box
     return 0;
 }
 
+// [rows, K] fp32 row-major tensor, zero fill outside; operand tiles of box_rows x 32 elements (128 bytes), 128-byte swizzle
+int make_map_f32(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return vq_set_error(VQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 4};
+    cuuint32_t box[2] = {(cuuint32_t)(BK / 2), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return vq_set_error(VQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
 // [rows, K] tensor of bytes (packed int8 codes), zero fill outside; tiles of box_rows x 64 bytes, no swizzle
 int make_map_u8(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
     EncodeTiledFn fn = encode_fn();
@@ -336,7 +380,7 @@ int make_map_u8(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int 
     return 0;
 }
 
-int launch_gemm(bool fused, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t st) {
+int launch_gemm(bool fused, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, cudaStream_t st, bool tf32 = false) {
     p.tiles_m = (p.M + BM - 1) / BM;
     p.tiles_n = (p.N + BN - 1) / BN;
     if (p.batch < 1) p.batch = 1;
@@ -345,7 +389,11 @@ int launch_gemm(bool fused, const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     const int grid = n_tiles < sms ? n_tiles : sms;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 256 + 1024;
     if ((int)smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "device offers too little shared memory for the GEMM");
-    if (fused) {
+    if (tf32) {
+        auto k = mx_gemm_kernel<false, true>;
+        VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<grid, 192, smem, st>>>(tmA, tmB, p);
+    } else if (fused) {
         auto k = mx_gemm_kernel<true>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         k<<<grid, (PRODUCER_WARPS_FUSED + 5) * 32, smem, st>>>(tmA, tmB, p);
@@ -406,6 +454,35 @@ int vq_gemm_bf16_tn_batched(const void* A, const void* B, void* Y, int64_t batch
     p.y_batch_stride = M * N;
     p.status = status;
     return launch_gemm(false, tmA, tmB, p, (cudaStream_t)stream);
+}
+
+int vq_gemm_f32_tn_batched(const void* A, const void* B, const void* bias, void* Y, int64_t batch, int64_t M, int64_t N,
+                           int64_t K, int a_shared, int b_shared, int32_t* status, void* stream) {
+    const char* name = "vq_gemm_f32_tn_batched";
+    VQ_REQUIRE(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "%s: negative size", name);
+    if (batch == 0 || M == 0 || N == 0) return 0;
+    VQ_REQUIRE(A && B && Y, "%s: null pointer", name);
+    VQ_REQUIRE(K > 0 && K % 4 == 0, "%s: K must be a positive multiple of 4 (16-byte rows)", name);
+    VQ_REQUIRE(batch * M < (1ll << 31) && batch * N < (1ll << 31) && K < (1ll << 31), "%s: batch * rows must be below 2^31", name);
+    VQ_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)B % 16 == 0 && (uintptr_t)Y % 4 == 0, "%s: operands must be 16-byte aligned", name);
+    VQ_REQUIRE(bias == nullptr || batch == 1, "%s: a bias goes with one problem only", name);
+    const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+    VQ_REQUIRE(tiles * batch < (1ll << 31), "%s: too many output tiles", name);
+    CUtensorMap tmA, tmB;
+    if (int rc = make_map_f32(&tmA, A, a_shared ? M : batch * M, K, BM)) return rc;
+    if (int rc = make_map_f32(&tmB, B, b_shared ? N : batch * N, K, BN)) return rc;
+    GemmParams p{};
+    p.Y[0] = reinterpret_cast<uint16_t*>(Y);
+    p.n_outputs = 1;
+    p.ldy = N;
+    p.bias = reinterpret_cast<const uint16_t*>(bias);
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.batch = (int)batch;
+    p.a_batch_rows = a_shared ? 0 : (int)M;
+    p.b_batch_rows = b_shared ? 0 : (int)N;
+    p.y_batch_stride = M * N;
+    p.status = status;
+    return launch_gemm(false, tmA, tmB, p, (cudaStream_t)stream, true);
 }
 
 int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bias, void* const* Ys, int n_outputs, int64_t ldy,

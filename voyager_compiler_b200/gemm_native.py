@@ -348,3 +348,53 @@ def linear_mx_packed(x, w, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
                                           out.data_ptr(), M, N, K, st.data_ptr(), stream)
             _lib.check(rc, "linear_mx_packed")
     return out.reshape(*lead, N)
+
+
+def f32_supported(a, b, bias, b_is_nk: bool) -> bool:
+    """fp32 operands go to the tensor cores as tf32 (``vq_gemm_f32_tn_batched``) unless ``VOYAGER_B200_FP32=vendor``.
+    Shapes: a 2-D right operand shared by every row of ``a``, or equal batch dimensions on both sides."""
+    if os.environ.get("VOYAGER_B200_FP32", "tensor") == "vendor" or _mode() == "cublas":
+        return False
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.ndim < 1 or b.ndim < 2 or not a.is_cuda:
+        return False
+    K = a.shape[-1]
+    if K <= 0 or K % 4 or K != (b.shape[-1] if b_is_nk else b.shape[-2]):
+        return False
+    N = b.shape[-2] if b_is_nk else b.shape[-1]
+    if bias is not None and (bias.dtype != torch.float32 or bias.ndim != 1 or bias.shape[0] != N):
+        return False
+    return b.ndim == 2 or (a.ndim == b.ndim and a.shape[:-2] == b.shape[:-2])
+
+
+def native_f32_gemm(name, a, b, bias, a_scale, b_scale, block_size, a_code, b_code, b_is_nk: bool) -> torch.Tensor:
+    """``deq(a) @ deq(b)^T`` (``b_is_nk``) or ``deq(a) @ deq(b)`` for fp32 operands: decoded by this package's kernels
+    (the 2-D linear weight kept between calls), a ``[.., K, N]`` right operand made ``[.., N, K]`` by one copy, then the
+    tf32 tensor-core contraction with fp32 accumulation and an fp32 result."""
+    from . import ops
+
+    dev = a.device
+    da = ops._decode_operand(name, a, a_code, a_scale, block_size).contiguous()
+    if b_is_nk and b.ndim == 2:
+        db = _decoded_weight(name, b, b_code, b_scale, block_size)
+    else:
+        db = ops._decode_operand(name, b, b_code, b_scale, block_size)
+        db = (db if b_is_nk else db.transpose(-1, -2)).contiguous()
+    K = da.shape[-1]
+    N = db.shape[-2]
+    if db.ndim == 2:
+        batch, M, b_shared, lead = 1, da.numel() // K, 1, da.shape[:-1]
+    else:
+        M, b_shared, lead = da.shape[-2], 0, da.shape[:-1]
+        batch = da.numel() // (M * K) if M else 0
+    out = torch.empty((*lead, N), dtype=torch.float32, device=dev)
+    if out.numel() == 0:
+        return out
+    fused_bias = bias is not None and batch == 1
+    bias_c = bias.contiguous() if fused_bias else None
+    with torch.cuda.device(dev):
+        rc = _lib.lib.vq_gemm_f32_tn_batched(da.data_ptr(), db.data_ptr(), bias_c.data_ptr() if bias_c is not None else None,
+                                             out.data_ptr(), batch, M, N, K, 0, b_shared, _status_tensor(dev).data_ptr(),
+                                             torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(rc, name)
+    _debug_check(dev, name)
+    return out if bias is None or fused_bias else out + bias

@@ -500,7 +500,8 @@ def conv2d_mx(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=
     """ops/quantized.py:239-283: operands are decoded and scaled by this package's kernels (blocks
     along the channel axis go through the strided scale layout).  bf16 convolutions run on this library's
     tensor-core kernels (``conv_native``: implicit GEMM, grouped included, or patch matrix + GEMM; an ``"nchw"``
-    result then comes back with channels-last strides); other dtypes use the vendor kernel, as upstream.
+    result then comes back with channels-last strides), fp32 ones with one group as patch matrix + the tf32
+    contraction; grouped fp32 and depthwise convolutions use the vendor kernel, as upstream.
     ``"nhwc"``: NHWC activations, HWIO weight, NHWC result."""
     assert layout in ("nchw", "nhwc"), layout
     _require_cuda(input, "conv2d_mx")
