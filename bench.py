@@ -322,8 +322,48 @@ def run_extras(dev, iters=20):
        activation_quantize_mismatches=bad_q, rows_checked=512)
     tc("cfg5_linear_mx_dynamic_one_pass_activation",
        lambda: gemm_native.linear_mx_dynamic(xg, wq, None, qmap=q8g, weight_scale=ws, block_size=32, quant_max=127.0))
+    # ---- fp32 operands of the same linear on a quarter of the rows: tf32 contraction (fp32 result)
+    Mf = 2048
+    xs_f, xq_f = Q.quantize_mx(xg[:Mf].float(), q8g, (-1,), 32, 127.0, True)
+    ws_f, wq_f = ws.float(), wq.float()
+    yf_ref = y_ref[:Mf]
+    yf = Q.linear_mx(xq_f, wq_f, None, input_scale=xs_f, weight_scale=ws_f, block_size=32)
+    torch.cuda.synchronize()
+    rel_f = float(((yf.cpu().double() - yf_ref).norm() / yf_ref.norm()).item())
+    med, best = _timed_flushed(torch, lambda: Q.linear_mx(xq_f, wq_f, None, input_scale=xs_f, weight_scale=ws_f, block_size=32), iters, flush)
+    out["linear_mx_fp32_operands_tf32_2048_rows"] = {
+        "ms": med, "value": flops / 4 / med / 1e9, "unit": "TFLOP/s", "flops": flops / 4, "rel_frobenius_error_vs_oracle": rel_f,
+        "tolerance": 1e-2, "within_tolerance": rel_f <= 1e-2, "note": "reference: the bf16 oracle result of the same codes and scales"}
     out["cfg5_status_ok"] = gemm_native.gemm_status(dev) == 0
-    del xg, wg, xq, wq, xs, ws
+    del xg, wg, xq, wq, xs, ws, xq_f, wq_f, xs_f, ws_f
+
+    # ---- conv2d_mx (the survey's next row after the linear): one ResNet-50 layer, MXINT8 block 32 along the channels,
+    # NHWC; implicit GEMM (default), patch matrix + GEMM, decode + vendor convolution; checked against the oracle
+    torch.manual_seed(6)
+    xc = torch.randn(32, 28, 28, 128).bfloat16()
+    wc = (torch.randn(3, 3, 128, 128) * 0.05).bfloat16()
+    xcs, xcq = vo.quantize_mx(xc, q8, (3,), 32, 127.0, True)
+    wcs, wcq = vo.quantize_mx(wc, q8, (2,), 32, 127.0, True)
+    yc_ref = vo.conv2d_mx(xcq.float(), wcq.float(), None, 1, 1, 1, 1, input_scale=xcs.float(), weight_scale=wcs.float(),
+                          block_size=32, layout="nhwc").double()
+    cargs = [t.to(dev) for t in (xcq, wcq, xcs, wcs)]
+    cflops = 2.0 * 32 * 28 * 28 * 128 * 128 * 9
+
+    def conv():
+        return Q.conv2d_mx(cargs[0], cargs[1], None, (1, 1), (1, 1), (1, 1), 1, input_scale=cargs[2], weight_scale=cargs[3],
+                           block_size=32, layout="nhwc")
+    for form in ("native", "patches", "vendor"):
+        os.environ["VOYAGER_B200_CONV"] = form
+        yc = conv()
+        torch.cuda.synchronize()
+        rel = float(((yc.cpu().double() - yc_ref).norm() / yc_ref.norm()).item())
+        med, best = _timed_flushed(torch, conv, iters, flush)
+        name = {"native": "implicit_gemm", "patches": "patch_matrix_plus_gemm", "vendor": "decode_plus_vendor_convolution"}[form]
+        out[f"conv2d_mx_3x3_128to128_28x28_batch32_{name}"] = {
+            "ms": med, "value": cflops / med / 1e9, "unit": "TFLOP/s", "flops": cflops, "rel_frobenius_error_vs_oracle": rel,
+            "tolerance": 1e-2, "within_tolerance": rel <= 1e-2}
+    os.environ.pop("VOYAGER_B200_CONV", None)
+    out["conv_status_ok"] = gemm_native.gemm_status(dev) == 0
 
     # ---- the reference's composite of torch operators on this GPU (one layer of the headline workload)
     nf4 = vo.value_table("nf4")
