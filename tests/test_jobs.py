@@ -105,3 +105,55 @@ def test_manifest_resume_skips_finished_items(tmp_path):
     assert sorted(calls) == sorted(i.key for i in ITEMS[5:])      # only the unfinished ones ran
     assert len(Manifest(path).done) == len(ITEMS)
     assert Manifest(path).done[ITEMS[0].key]["crc"] == _crc(ITEMS[0])
+
+
+def test_manifest_merges_the_other_ranks_files_on_resume(tmp_path):
+    """One file per rank; a rerun sees what any rank finished, whichever rank gets the item this time."""
+    p0, p1 = str(tmp_path / "manifest_0.json"), str(tmp_path / "manifest_1.json")
+    m0, m1 = Manifest(p0), Manifest(p1)
+    m0.record(ITEMS[0], 11, 0)
+    m1.record(ITEMS[1], 22, 1)
+    again = Manifest(p0, peers=str(tmp_path / "manifest_*.json"))
+    assert again.finished(ITEMS[0]) and again.finished(ITEMS[1]) and not again.finished(ITEMS[2])
+    assert again.done[ITEMS[1].key] == {"crc": 22, "rank": 1}
+    again.record(ITEMS[2], 33, 0)                      # rewrites only its own file
+    assert set(Manifest(p1).done) == {ITEMS[1].key}
+    assert set(Manifest(p0).done) == {ITEMS[0].key, ITEMS[1].key, ITEMS[2].key}
+    assert Manifest(p0, peers=[p1]).finished(ITEMS[1])
+
+
+def test_waiting_rank_does_not_time_out_while_the_others_make_progress():
+    """Phase 2: the pending set shrinking counts as progress even when this rank takes nothing."""
+    class FakeStore:
+        def __init__(self):
+            self.d, self.t = {}, 0.0
+        def set(self, k, v): self.d[k] = v.encode() if isinstance(v, str) else v
+        def get(self, k): return self.d[k]
+        def check(self, ks): return all(k in self.d for k in ks)
+        def add(self, k, v):
+            self.d[k] = str(int(self.d.get(k, b"0")) + v).encode()
+            return int(self.d[k])
+        def compare_set(self, k, old, new):
+            cur = self.d.get(k, b"").decode()
+            if cur == old:
+                self.d[k] = new.encode()
+            return self.d[k]
+
+    store = FakeStore()
+    items = ITEMS[:4]
+    # another rank (7) has claimed everything and is alive; it finishes one item every 4 "seconds"
+    store.add("next_item", len(items))
+    for i in range(len(items)):
+        store.set(f"claim/{i}", "7:0.0")
+    finished = {"n": 0}
+
+    def clock():
+        store.t += 1.0
+        store.set("hb/7", repr(store.t))
+        if int(store.t) % 4 == 0 and finished["n"] < len(items):
+            store.set(f"done/{finished['n']}", "7:1")
+            finished["n"] += 1
+        return store.t
+
+    mine = run_items(store, 0, items, lambda it: 1, heartbeat_timeout=50.0, poll=0.0, give_up_after=6.0, clock=clock)
+    assert mine == [] and finished["n"] == len(items)

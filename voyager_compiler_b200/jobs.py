@@ -46,14 +46,29 @@ def checksum(*buffers: bytes) -> int:
 
 
 class Manifest:
-    """``{item key: {"crc": int, "rank": int}}`` persisted as JSON with atomic replace."""
+    """``{item key: {"crc": int, "rank": int}}`` persisted as JSON with atomic replace.
 
-    def __init__(self, path: Optional[str]):
+    ``path`` is this rank's own file (one writer per file: a rewrite never loses another rank's records).
+    ``peers`` are the other ranks' files, or a glob pattern that matches them; their records are merged in when
+    the manifest is opened, so that a rerun skips what ANY rank finished, however the items were dealt the
+    first time."""
+
+    def __init__(self, path: Optional[str], peers: Optional[object] = None):
         self.path = path
         self.done: Dict[str, dict] = {}
-        if path and os.path.exists(path):
-            with open(path) as f:
-                self.done = json.load(f).get("done", {})
+        paths = [path] if path else []
+        if isinstance(peers, str):
+            import glob
+            paths += sorted(glob.glob(peers))
+        elif peers:
+            paths += list(peers)
+        for p in paths:
+            if p and os.path.exists(p):
+                try:
+                    with open(p) as f:
+                        self.done.update(json.load(f).get("done", {}))
+                except (OSError, ValueError):
+                    continue                     # a peer's file that is being replaced right now: its records come next time
 
     def record(self, item: WorkItem, crc: int, rank: int) -> None:
         self.done[item.key] = {"crc": int(crc), "rank": int(rank)}
@@ -121,11 +136,15 @@ def run_items(store, rank: int, items: Sequence[WorkItem], work: Callable[[WorkI
         run(i)
     # phase 2: wait for stragglers, take over items whose claimant stopped beating
     last_progress = phase2_start = clock()
+    n_pending = n + 1
     while True:
         beat()
         pending = [i for i in range(n) if not is_done(i)]
         if not pending:
             return mine
+        if len(pending) < n_pending:             # the peers are getting on: slow is not stuck
+            n_pending = len(pending)
+            last_progress = clock()
         took = False
         for i in pending:
             claim = _get(store, f"claim/{i}")
