@@ -382,6 +382,9 @@ def run_extras(dev, iters=20):
     return out
 
 
+EXTRAS_MULTI_LIMIT_S = 180
+
+
 def run_extras_multi(dev, world, rank, iters=10):
     """cfg5 sharded by output columns over the ranks (every rank calls this): the local GEMM alone,
     GEMM + NCCL all-gather, and the GEMM whose epilogue stores its columns into every rank's copy of
@@ -635,7 +638,28 @@ def run_ours(args):
     extra = None
     if not args.no_extras:
         if world > 1:
-            extra = run_extras_multi(dev, world, rank)
+            # The headline line must come out whatever the additional multi-GPU measurements do: if they raise on
+            # one rank the others wait in a collective for ever, so every rank arms a timer that prints the line
+            # (rank 0) and leaves the process; a rank that raises prints and leaves at once.
+            import threading
+
+            def bail(reason):
+                if rank == 0:
+                    line["extra"] = {"error": reason}
+                    print(json.dumps(line), flush=True)
+                sys.stdout.flush()
+                os._exit(0)
+            timer = threading.Timer(EXTRAS_MULTI_LIMIT_S, bail, args=(f"multi-GPU extras did not finish within {EXTRAS_MULTI_LIMIT_S} s",))
+            timer.daemon = True
+            timer.start()
+            try:
+                extra = run_extras_multi(dev, world, rank)
+            except Exception as e:  # noqa: BLE001
+                import traceback
+                traceback.print_exc()
+                timer.cancel()
+                bail(f"{type(e).__name__}: {e}"[:300])
+            timer.cancel()
         elif rank == 0:
             del host, host_out
             torch.cuda.empty_cache()
