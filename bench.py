@@ -56,6 +56,12 @@ def make_tensor(idx, shape, device, rows=None):
     return w
 
 
+# Written between timed iterations of the additional measurements: larger than L2 (126 MB), and long enough on the
+# device (about 0.16 ms) for the host to have queued the next call before it ends, so that the events bracket device
+# time and not the Python path of the op.
+FLUSH_BYTES = int(os.environ.get("VOYAGER_B200_BENCH_FLUSH_MB", "1024")) << 20
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -188,6 +194,37 @@ def _bits_differ(torch, got, want):
     return int((ai != bi).sum())
 
 
+def _timed_graph(torch, fns, iters, flush):
+    """Median time per call of ``fns`` captured together in one CUDA graph (L2 flushed before every replay);
+    None when the calls cannot be captured."""
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for f in fns:
+                f()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = [f() for f in fns]                            # noqa: F841  (outputs live as long as the graph)
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); graph.replay(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / len(fns))
+        return statistics.median(ts)
+    except Exception as e:  # noqa: BLE001
+        sys.stderr.write(f"graph timing skipped: {type(e).__name__}: {e}\n")
+        torch.cuda.synchronize()
+        return None
+
+
 def run_extras(dev, iters=20):
     """The other configurations of the baseline on one GPU, each timed (CUDA events, L2 flushed
     between iterations) and compared with the CPU oracle on the same tensors: cfg1 (MXINT8 block 32
@@ -203,17 +240,25 @@ def run_extras(dev, iters=20):
     vo = oracle_module()
     Q = torch.ops.quantized_ops
     peaks, kind = measured_peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    out = {"peak_kind": kind, "l2": "256 MB written between timed iterations"}
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    out = {"peak_kind": kind, "l2": f"{FLUSH_BYTES >> 20} MB written between timed iterations"}
 
     def tab(name):
         return torch.from_numpy(vb.tables.build_table(name).view(np.int16).copy()).view(torch.bfloat16)
 
-    def hbm(name, fn, nbytes, mismatches=None, **more):
+    def hbm(name, fn, nbytes, mismatches=None, rotating=None, **more):
         med, best = _timed_flushed(torch, fn, iters, flush)
         gbs = nbytes / med / 1e6
         out[name] = {"ms": med, "value": gbs, "unit": "GB/s", "best": nbytes / best / 1e6, "algorithmic_bytes": int(nbytes),
                      "frac": gbs / peaks["hbm_gbs"], **({"mismatches": mismatches} if mismatches is not None else {}), **more}
+        if rotating:
+            # the same call on `len(rotating)` different input buffers (together larger than L2, so every launch reads
+            # cold data), replayed as ONE CUDA graph: launch gaps and event overhead are shared by all of them
+            g_ms = _timed_graph(torch, rotating, iters, flush)
+            if g_ms is not None:
+                out[name]["graph_of"] = len(rotating)
+                out[name]["graph_ms_per_call"] = g_ms
+                out[name]["graph_frac"] = nbytes / g_ms / 1e6 / peaks["hbm_gbs"]
 
     # ---- cfg1
     torch.manual_seed(0)
@@ -226,23 +271,32 @@ def run_extras(dev, iters=20):
     n = x1.numel()
     s, c = Q.quantize_mx(xg, q8g, (-1,), 32, 127.0, True)
     d = Q.dequantize(c, s, None, (-1,), 32)
+    R = 8                                                        # rotating copies: 8 x 67 MB of input
+    xr = [xg] + [xg.clone() for _ in range(R - 1)]
+    cr = [c] + [c.clone() for _ in range(R - 1)]
     hbm("cfg1_quantize_mx_fp32", lambda: Q.quantize_mx(xg, q8g, (-1,), 32, 127.0, True), n * (4 + 4 + 4 / 32),
-        _bits_differ(torch, s, s_ref) + _bits_differ(torch, c, c_ref))
-    hbm("cfg1_dequantize_fp32", lambda: Q.dequantize(c, s, None, (-1,), 32), n * (4 + 4 + 4 / 32), _bits_differ(torch, d, d_ref))
+        _bits_differ(torch, s, s_ref) + _bits_differ(torch, c, c_ref),
+        rotating=[(lambda t=t: Q.quantize_mx(t, q8g, (-1,), 32, 127.0, True)) for t in xr])
+    hbm("cfg1_dequantize_fp32", lambda: Q.dequantize(c, s, None, (-1,), 32), n * (4 + 4 + 4 / 32), _bits_differ(torch, d, d_ref),
+        rotating=[(lambda t=t: Q.dequantize(t, s, None, (-1,), 32)) for t in cr])
     sq = Q.calculate_mx_qparam(xg, (-1,), 32, 127.0, True)
     hbm("cfg1_calculate_mx_qparam_fp32", lambda: Q.calculate_mx_qparam(xg, (-1,), 32, 127.0, True), n * (4 + 4 / 32),
-        _bits_differ(torch, sq, s_ref))
-    plan1 = mq.MXQuantPlan([xg], q8, 32, 127.0, True, code_bits=8, want_exp=True)
-    (p1,) = plan1.run()
+        _bits_differ(torch, sq, s_ref), rotating=[(lambda t=t: Q.calculate_mx_qparam(t, (-1,), 32, 127.0, True)) for t in xr])
+    plans = [mq.MXQuantPlan([t], q8, 32, 127.0, True, code_bits=8, want_exp=True) for t in xr]
+    plan1 = plans[0]
+    packed = [pl.run()[0] for pl in plans]
+    p1 = packed[0]
     torch.cuda.synchronize()
     bad = _bits_differ(torch, p1.scale, s_ref) + int((p1.codes.cpu().view(torch.int8).float() != c_ref).sum()) + \
         int((p1.exp_e8.cpu() != torch.log2(s_ref).clamp(-127, 127).to(torch.int8)).sum())
-    hbm("cfg1_packed_int8_codes_e8_exponents", plan1.run, n * (4 + 1 + 4 / 32 + 1 / 32), bad)
+    hbm("cfg1_packed_int8_codes_e8_exponents", plan1.run, n * (4 + 1 + 4 / 32 + 1 / 32), bad, rotating=[pl.run for pl in plans])
     dp = mq.dequantize_packed(p1, torch.float32, use_exponent=True)
     hbm("cfg1_dequantize_packed_int8_e8_to_fp32", lambda: mq.dequantize_packed(p1, torch.float32, use_exponent=True),
-        n * (1 + 1 / 32 + 4), int((dp.cpu() != d_ref).sum()))
-    plan1.close()
-    del xg, s, c, d, sq, p1, dp, plan1
+        n * (1 + 1 / 32 + 4), int((dp.cpu() != d_ref).sum()),
+        rotating=[(lambda pk=pk: mq.dequantize_packed(pk, torch.float32, use_exponent=True)) for pk in packed])
+    for pl in plans:
+        pl.close()
+    del xg, s, c, d, sq, p1, dp, plan1, plans, packed, xr, cr
 
     # ---- cfg2
     torch.manual_seed(1)
@@ -266,7 +320,12 @@ def run_extras(dev, iters=20):
         bad += int((r.levels[r.codes.cpu().long().clamp(max=r.levels.numel() - 1)][ok] != qv.float()[ok]).sum())
     del plan2, res2
     plan2 = mq.ChannelQuantPlan(rg, qp, 4096.0, want_codes=True, want_dequant=True)
-    hbm("cfg2_posit8_per_channel_54_tensors_codes_and_dequant", plan2.run, n2 * 9, bad, launches_per_pass=1)
+    more_plans = [mq.ChannelQuantPlan([t.clone() for t in rg], qp, 4096.0, want_codes=True, want_dequant=True) for _ in range(3)]
+    hbm("cfg2_posit8_per_channel_54_tensors_codes_and_dequant", plan2.run, n2 * 9, bad, launches_per_pass=1,
+        rotating=[plan2.run] + [pl.run for pl in more_plans])
+    for pl in more_plans:
+        pl.close()
+    del more_plans
     plan2b = mq.ChannelQuantPlan(rg, qp, 4096.0, want_values=True, want_dequant=False)
     hbm("cfg2_posit8_per_channel_54_tensors_values", plan2b.run, n2 * 8)
     del plan2, plan2b, rg, rn
@@ -397,7 +456,7 @@ def run_extras_multi(dev, world, rank, iters=10):
 
     Q = torch.ops.quantized_ops
     peaks, _ = measured_peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
     M, N, K = 8192, 11008, 4096
     g = torch.Generator(device=dev); g.manual_seed(4)
     x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
@@ -740,7 +799,7 @@ def run_conv(args):
     g = torch.Generator(device=dev); g.manual_seed(4)
     Q = torch.ops.quantized_ops
     qmap = torch.from_numpy(vb.tables.build_table("int8").view("int16").copy()).view(torch.bfloat16).to(dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
     def timed(fn, iters):
         for _ in range(3):
@@ -783,7 +842,7 @@ def run_linear(args):
     ws, wq = Q.quantize_mx(w, qmap, (-1,), 32, 127.0, True)
     xs, xq = Q.quantize_mx(x, qmap, (-1,), 32, 127.0, True)
     flops = 2.0 * M * N * K
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
     def timed(fn, iters):
         for _ in range(3):
@@ -926,14 +985,14 @@ def resnet50_weight_shapes():
 def run_channel(args):
     """cfg2 alone: the 54 ResNet-50-shaped weight tensors, posit8_1 per output channel (scale = channel
     maximum / 4096), code byte + dequantized fp32 from one prepared launch; ``--steps`` timed launches with
-    256 MB written in between.  Small enough for a full profiler capture of the kernel."""
+    ``FLUSH_BYTES`` written in between.  Small enough for a full profiler capture of the kernel."""
     import torch
     import voyager_compiler_b200 as vb
     from voyager_compiler_b200 import model_quant as mq
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
     qp = torch.from_numpy(vb.tables.build_table("posit8_1").view("int16").copy()).view(torch.bfloat16).to(dev)
     torch.manual_seed(1)
     ws = []
@@ -972,7 +1031,7 @@ def run_elementwise(args):
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     Q = torch.ops.quantized_ops
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
     def tab(name):
         return torch.from_numpy(vb.tables.build_table(name).view("int16").copy()).view(torch.bfloat16).to(dev)
