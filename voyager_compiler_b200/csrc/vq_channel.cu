@@ -471,7 +471,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
         // ------------------------------------------------------------------ producer
         if (threadIdx.x == 0) {
             bool ok = true;
-            int i = 0;
             // Every consumer group has its own sequence of batches (group g: this CTA's batches g, g + G, ...) and
             // its own stage.  The producer serves whichever group has given its stage back, not the groups in turn:
             // a group that is ahead of the others gets its next batch at once.
@@ -819,10 +818,447 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) channel_pipe_kernel(const Bat
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streaming variant: warps in ROLES that never meet at a barrier.
+//
+//   producer warp      bulk-copies batches of whole channels (<= RS_BATCH elements) into an RS_STAGES-deep ring,
+//                      serving whichever stage has been returned; before a copy it clears the stage's per-channel
+//                      scratch (maximum and smallest non-zero |x|);
+//   reduction warps    RS_ATEAMS teams of RS_AW warps; team t takes the batches t, t + RS_ATEAMS, ...: every warp
+//                      reads one contiguous run of the batch from the stage (16 bytes per lane and piece), keeps a
+//                      running maximum while its run stays inside a channel, and adds it to the scratch with one
+//                      warp reduction + one pair of shared-memory atomics per channel it touched; arrives on amax[s];
+//   quantization warps RS_QTEAMS teams of RS_QW warps; team t takes the batches t, t + RS_QTEAMS, ...: after amax[s]
+//                      lane l of a warp prepares scale and division of channel c_lo + l of the warp's run (at most
+//                      RS_MAXCH / ... channels; a run of six pieces touches at most seven), the warp walks its run
+//                      from the stage, fetches a channel's numbers by shuffle when the run enters it, quantizes and
+//                      stores; the lane whose channel starts inside the run writes the channel's scale and maximum;
+//                      arrives on empty[s].
+// Nothing is held in registers across phases (64 registers, 31 warps per SM) and no phase waits for a whole
+// group: what a warp waits for is data (mbarriers), never a slower neighbour.  Batches that do not qualify for
+// the walk in 128-element pieces (channel length no multiple of 128, unaligned tensors) are handled channel by
+// channel, the warps of the quantization team taking the channels in turn, with warp reductions; they are rare.
+// A stage always belongs to the same reduction team and the same quantization team (RS_STAGES is a multiple of
+// both team counts), so every waiter sees every phase of the barriers it waits on.  Every wait is bounded.
+constexpr int RS_STAGES = 8, RS_QTEAMS = 4, RS_QW = 6, RS_ATEAMS = 2, RS_AW = 3;
+constexpr int RS_PIECES_Q = 6;                                  // 128-element pieces per quantization warp and batch
+constexpr int RS_BATCH = RS_QW * RS_PIECES_Q * 128;             // 4608 elements
+constexpr int RS_MAXCH = 64;                                    // channels per batch
+constexpr int RS_WARPS = 1 + RS_ATEAMS * RS_AW + RS_QTEAMS * RS_QW;
+constexpr int RS_THREADS = RS_WARPS * 32;                       // 992
+static_assert(RS_STAGES % RS_QTEAMS == 0 && RS_STAGES % RS_ATEAMS == 0, "a stage must belong to one team of each role");
+static_assert(RS_PIECES_Q + 1 <= 32 && RS_BATCH / 128 <= RS_MAXCH, "a warp's run touches at most one channel per piece plus one");
+
+// One batch, everything the warps need already worked out on the host (96 bytes): pointers advanced to the
+// batch's first element / first channel, so that no warp touches the tensor descriptors or multiplies offsets.
+struct StreamBatch {
+    const void* x;
+    void* values;
+    void* dequant;
+    uint8_t* codes;
+    void* amax_out;
+    void* scale_out;            // null when scales are supplied
+    const void* scale_in;
+    uint32_t L, nc;
+    FastDiv len;                // flat index -> channel
+    uint32_t flags;             // bit 0: bulk-copied (aligned, whole vectors), bit 1: walked in 128-element pieces
+    uint32_t pad[3];
+};
+static_assert(sizeof(StreamBatch) == 96, "StreamBatch is copied to shared memory in 16-byte pieces");
+constexpr int kSmemStream = 48;        // batch records a CTA keeps in shared memory (the rest is read from global memory)
+
+struct StreamScratch {
+    uint32_t amax[RS_MAXCH];
+    uint32_t minnz[RS_MAXCH];        // smallest non-zero |x| bit pattern minus one
+};
+
+// Four elements of one channel whose quotients are in the range of the corrected-reciprocal division
+// (q = x y, q += (x - s q) y: the correctly rounded x / s), two elements per packed fp32 instruction.
+template <typename T, int TK>
+__device__ __forceinline__ void stream_quantize4(const uint8_t* s_codes, const float* s_lv2, float lo, float hi, const float* v,
+                                                 float sc, float y, float* q, float* d, uint32_t& packed) {
+    float t[4], r[4];
+    t[0] = v[0]; t[1] = v[1]; t[2] = v[2]; t[3] = v[3];
+    mul2(t[0], t[1], y);
+    mul2(t[2], t[3], y);
+    fma2(r[0], r[1], t[0], t[1], -sc, v[0], v[1]);
+    fma2(r[2], r[3], t[2], t[3], -sc, v[2], v[3]);
+    fma2(t[0], t[1], r[0], r[1], y, t[0], t[1]);
+    fma2(t[2], t[3], r[2], r[3], y, t[2], t[3]);
+    packed = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t pat = bf16_pattern(__uint_as_float((__float_as_uint(t[k]) & 0x7FFFFFFFu) | (__float_as_uint(v[k]) & 0x80000000u)));
+        uint32_t code;
+        pipe_lookup<TK>(s_codes, s_lv2, lo, hi, pat, q[k], code);
+        packed |= code << (8 * k);
+        d[k] = q[k];
+    }
+    mul2(d[0], d[1], sc);
+    mul2(d[2], d[3], sc);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) d[k] = Arith<T>::rnd(d[k]);
+}
+
+template <typename T, int TK>
+__global__ void __launch_bounds__(RS_THREADS, 1) channel_stream_kernel(const BatchParams p) {
+    extern __shared__ uint4 smem[];
+    // layout: [code table 64 KB + levels2 2 KB (TK_LUT)] [ring] [scratch per stage] [batch descriptors] [barriers]
+    constexpr uint32_t TAB_BYTES = TK == TK_LUT ? 65536u + 2048u : 0u;
+    constexpr uint32_t STAGE_BYTES = RS_BATCH * sizeof(T);
+    uint8_t* base = reinterpret_cast<uint8_t*>(smem);
+    const uint8_t* s_codes = base;
+    const float* s_lv2 = reinterpret_cast<const float*>(base + 65536);
+    uint8_t* ring = base + TAB_BYTES;
+    StreamScratch* scratch = reinterpret_cast<StreamScratch*>(ring + RS_STAGES * STAGE_BYTES);
+    StreamBatch* sbatches = reinterpret_cast<StreamBatch*>(scratch + RS_STAGES);    // this CTA's first kSmemStream batches
+    const uint32_t bar0 = tc::smem_u32(sbatches + kSmemStream);
+    const uint32_t FULL0 = bar0, AMAX0 = bar0 + 8u * RS_STAGES, EMPTY0 = bar0 + 16u * RS_STAGES, TABLE_BAR = bar0 + 24u * RS_STAGES;
+    volatile int* team_ok = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(sbatches + kSmemStream) + 8 * (3 * RS_STAGES + 1));
+    const StreamBatch* gbatches = reinterpret_cast<const StreamBatch*>(p.batches);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < RS_STAGES; ++s) {
+                tc::mbar_init(FULL0 + 8u * s, 1);
+                tc::mbar_init(AMAX0 + 8u * s, RS_AW);
+                tc::mbar_init(EMPTY0 + 8u * s, RS_QW);
+            }
+            tc::mbar_init(TABLE_BAR, 1);
+            tc::fence_barrier_init();
+        }
+        __syncwarp();
+        if (lane == 0 && TK == TK_LUT) {
+            tc::mbar_expect_tx(TABLE_BAR, 65536u + 2048u);
+            bulk_load(tc::smem_u32(base), p.common.tab.lut8, 65536u, TABLE_BAR);
+            bulk_load(tc::smem_u32(base + 65536), p.common.tab.levels2, 2048u, TABLE_BAR);
+        }
+    }
+    for (int c = threadIdx.x; c < RS_STAGES * RS_MAXCH; c += blockDim.x) {       // every stage's scratch starts empty
+        scratch[c / RS_MAXCH].amax[c % RS_MAXCH] = 0u;
+        scratch[c / RS_MAXCH].minnz[c % RS_MAXCH] = 0xFFFFFFFFu;
+    }
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(gbatches);
+        uint4* dst = reinterpret_cast<uint4*>(sbatches);
+        constexpr int W = sizeof(StreamBatch) / 16;
+        for (int t = threadIdx.x; t < kSmemStream * W; t += blockDim.x) {
+            const int64_t b = blockIdx.x + (int64_t)(t / W) * gridDim.x;
+            if (b < p.n_batches) dst[t] = __ldg(src + b * W + t % W);
+        }
+    }
+    __syncthreads();
+    const float lo = p.common.tab.lo, hi = p.common.tab.hi;
+    auto batch_of = [&](int i, int64_t b) -> const StreamBatch& {
+        return *(i < kSmemStream ? static_cast<const StreamBatch*>(sbatches + i) : gbatches + b);
+    };
+    // A team waits through its first warp: one lane polls, the others sit at the team's named barrier (a waiting warp
+    // then issues nothing).  Returns false for the whole team when the wait ran out.
+    auto team_wait = [&](int bar_id, int team_threads, bool leader, int slot, uint32_t bar_a, uint32_t bar_b, uint32_t bar_c,
+                         uint32_t parity) -> bool {
+        if (leader && lane == 0) {
+            bool ok = tc::mbar_wait_relaxed(bar_a, parity, p.wait_budget);
+            if (ok && bar_b) ok = tc::mbar_wait_relaxed(bar_b, parity, p.wait_budget);
+            if (ok && bar_c) ok = tc::mbar_wait_relaxed(bar_c, 0u, p.wait_budget);
+            team_ok[slot] = ok ? 1 : 0;
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(team_threads) : "memory");
+        return team_ok[slot] != 0;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        int k[RS_STAGES];                                       // batches loaded into stage s so far
+#pragma unroll
+        for (int s = 0; s < RS_STAGES; ++s) k[s] = 0;
+        int left = 0;
+        for (int64_t b = blockIdx.x; b < p.n_batches; b += gridDim.x) ++left;
+        long long idle_since = clock64();
+        bool ok = true;
+        while (left > 0 && ok) {
+            bool progress = false;
+#pragma unroll
+            for (int s = 0; s < RS_STAGES; ++s) {
+                const int i = s + k[s] * RS_STAGES;
+                const int64_t b = blockIdx.x + (int64_t)i * gridDim.x;
+                bool go = b < p.n_batches;
+                if (go && i >= RS_STAGES) {
+                    bool free_ = true;
+                    if (lane == 0) free_ = tc::mbar_try_wait(EMPTY0 + 8u * s, ((uint32_t)(i / RS_STAGES) & 1u) ^ 1u);
+                    go = __shfl_sync(0xFFFFFFFFu, free_, 0);
+                }
+                if (!go) continue;                            // warp uniform
+                ++k[s];
+                --left;
+                progress = true;
+                // the stage's scratch starts empty: the whole warp clears it, then one lane starts the copy
+                for (int c = lane; c < RS_MAXCH; c += 32) {
+                    scratch[s].amax[c] = 0u;
+                    scratch[s].minnz[c] = 0xFFFFFFFFu;
+                }
+                __syncwarp();
+                if (lane == 0 && b != p.skip_batch) {         // skip_batch, tests only: the waits for this batch run out
+                    const StreamBatch& bt = batch_of(i, b);
+                    if (bt.flags & 1u) {
+                        const uint32_t bytes = bt.nc * bt.L * (uint32_t)sizeof(T);
+                        tc::mbar_expect_tx(FULL0 + 8u * s, bytes);
+                        bulk_load(tc::smem_u32(ring + s * STAGE_BYTES), bt.x, bytes, FULL0 + 8u * s);
+                    } else {
+                        tc::mbar_arrive(FULL0 + 8u * s);      // the quantization warp reads this batch itself
+                    }
+                }
+            }
+            if (progress) {
+                idle_since = clock64();
+            } else {
+                if (clock64() - idle_since > p.wait_budget) ok = false;
+                // nothing was free: sleep on the stage whose batch is the oldest outstanding (woken when it is
+                // returned, or after a microsecond to look at the others again)
+                int oldest = 0x7FFFFFFF, so = 0;
+#pragma unroll
+                for (int s = 0; s < RS_STAGES; ++s) {
+                    const int i = s + k[s] * RS_STAGES;
+                    if (blockIdx.x + (int64_t)i * gridDim.x < p.n_batches && i < oldest) {
+                        oldest = i;
+                        so = s;
+                    }
+                }
+                if (lane == 0 && oldest >= RS_STAGES && oldest != 0x7FFFFFFF)
+                    tc::mbar_try_wait_suspended(EMPTY0 + 8u * so, ((uint32_t)(oldest / RS_STAGES) & 1u) ^ 1u, 1000u);
+                __syncwarp();
+            }
+        }
+        if (!ok && lane == 0) {
+            atomicCAS(&g_channel_status, 0, 31);
+            // copies already under way get a bounded time to land before the CTA ends
+#pragma unroll
+            for (int s = 0; s < RS_STAGES; ++s)
+                if (k[s] > 0) tc::mbar_wait_relaxed(FULL0 + 8u * s, (uint32_t)(k[s] - 1) & 1u, p.wait_budget >> 4);
+        }
+        return;
+    }
+
+    if (warp <= RS_ATEAMS * RS_AW) {
+        // ------------------------------------------------------------------ reduction warps
+        const int team = (warp - 1) / RS_AW, idx = (warp - 1) % RS_AW;
+        for (int i = team;; i += RS_ATEAMS) {
+            const int64_t b = blockIdx.x + (int64_t)i * gridDim.x;
+            if (b >= p.n_batches) break;
+            const int s = i % RS_STAGES;
+            if (!team_wait(1 + team, RS_AW * 32, idx == 0, team * 2 + ((i / RS_ATEAMS) & 1), FULL0 + 8u * s, 0u, 0u,
+                           (uint32_t)(i / RS_STAGES) & 1u)) {
+                if (lane == 0) atomicCAS(&g_channel_status, 0, 32);
+                break;
+            }
+            const StreamBatch& bt = batch_of(i, b);
+            const bool need_amax = !bt.scale_in || bt.amax_out;
+            if ((bt.flags & 2u) && need_amax) {
+                const uint32_t L = bt.L, n = bt.nc * L;
+                const uint32_t pieces = n >> 7, per = (pieces + RS_AW - 1) / RS_AW, q0 = (uint32_t)idx * per;
+                const int cnt = q0 < pieces ? (int)min(per, pieces - q0) : 0;
+                if (cnt > 0) {
+                    const T* st = reinterpret_cast<const T*>(ring + s * STAGE_BYTES) + (q0 << 7) + (uint32_t)lane * 4u;
+                    StreamScratch& sc = scratch[s];
+                    uint32_t e0 = q0 << 7;
+                    uint32_t cur = fd_div(e0, bt.len), next = (cur + 1u) * L, m = 0u, mn = 0xFFFFFFFFu;
+                    auto flush = [&]() {
+                        const uint32_t wm = __reduce_max_sync(0xFFFFFFFFu, m), wn = __reduce_min_sync(0xFFFFFFFFu, mn);
+                        if (lane == 0) {
+                            atomicMax(&sc.amax[cur], wm);
+                            atomicMin(&sc.minnz[cur], wn);
+                        }
+                    };
+#pragma unroll 4
+                    for (int j = 0; j < cnt; ++j, e0 += 128u) {
+                        if (e0 >= next) {                     // warp uniform: the run has entered the next channel
+                            flush();
+                            ++cur;
+                            next += L;
+                            m = 0u;
+                            mn = 0xFFFFFFFFu;
+                        }
+                        RawVec<T> r;
+                        r.load_shared(st + (j << 7));
+                        float v[4];
+                        r.get(v);
+                        const uint32_t a0 = abs_bits(v[0]), a1 = abs_bits(v[1]), a2 = abs_bits(v[2]), a3 = abs_bits(v[3]);
+                        m = max(max(m, a0), max(a1, max(a2, a3)));
+                        mn = min(min(mn, a0 - 1u), min(a1 - 1u, min(a2 - 1u, a3 - 1u)));   // a zero wraps to the top and drops out
+                    }
+                    flush();
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(AMAX0 + 8u * s);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- quantization warps
+    const int qw = warp - 1 - RS_ATEAMS * RS_AW;
+    const int team = qw / RS_QW, idx = qw % RS_QW;
+    bool tables_ready = TK != TK_LUT;
+    for (int i = team;; i += RS_QTEAMS) {
+        const int64_t b = blockIdx.x + (int64_t)i * gridDim.x;
+        if (b >= p.n_batches) break;
+        const int s = i % RS_STAGES;
+        const uint32_t ph = (uint32_t)(i / RS_STAGES) & 1u;
+        // the reductions of this batch are in the scratch, the copy has landed, and (first batch) the tables are in place
+        if (!team_wait(1 + RS_ATEAMS + team, RS_QW * 32, idx == 0, 2 * RS_ATEAMS + team * 2 + ((i / RS_QTEAMS) & 1), AMAX0 + 8u * s,
+                       FULL0 + 8u * s, tables_ready ? 0u : TABLE_BAR, ph)) {
+            if (lane == 0) atomicCAS(&g_channel_status, 0, 33);
+            break;
+        }
+        tables_ready = true;
+        const StreamBatch& bt = batch_of(i, b);
+        const uint32_t L = bt.L, n = bt.nc * L;
+        const bool need_amax = !bt.scale_in || bt.amax_out;
+        T* const values = reinterpret_cast<T*>(bt.values);
+        T* const dequant = reinterpret_cast<T*>(bt.dequant);
+        uint8_t* const codes = bt.codes;
+        T* const amax_out = reinterpret_cast<T*>(bt.amax_out);
+        T* const scale_out = reinterpret_cast<T*>(bt.scale_out);
+        const T* const scale_in = reinterpret_cast<const T*>(bt.scale_in);
+        const T* const st = reinterpret_cast<const T*>(ring + s * STAGE_BYTES);
+        const StreamScratch& sc_s = scratch[s];
+        // scale of a channel from its maximum, as the settled observer derives it
+        auto scale_of = [&](uint32_t mb) -> float {
+            const float amax = __uint_as_float(mb);
+            const float ratio = p.inv_qmax != 0.0f ? __fmul_rn(amax, p.inv_qmax) : __fdiv_rn(amax, p.qmax);
+            return (mb != 0u && mb < 0x7F800000u) ? Arith<T>::rnd(ratio) : 1.0f;
+        };
+        if (bt.flags & 2u) {
+            const uint32_t pieces = n >> 7, per = (pieces + RS_QW - 1) / RS_QW, q0 = (uint32_t)idx * per;
+            const int cnt = q0 < pieces ? (int)min(per, pieces - q0) : 0;
+            if (cnt > 0) {
+                const uint32_t e_w = q0 << 7;
+                const uint32_t c_lo = fd_div(e_w, bt.len), c_hi = fd_div(e_w + ((uint32_t)cnt << 7) - 1u, bt.len);
+                const bool mine = c_lo + (uint32_t)lane <= c_hi;
+                const uint32_t c_mine = mine ? c_lo + (uint32_t)lane : c_hi;
+                const uint32_t cg = c_mine;                    // the channel pointers start at the batch's first channel
+                float sc_l = 1.0f;
+                uint32_t mb = 0u;
+                if (need_amax) {
+                    mb = sc_s.amax[c_mine];
+                    sc_l = scale_of(mb);
+                    if (mine && c_mine * L >= e_w) {          // the channel starts inside this warp's run
+                        if (amax_out) store_one<T>(amax_out + cg, __uint_as_float(mb));
+                        if (scale_out) store_one<T>(scale_out + cg, sc_l);
+                    }
+                }
+                if (scale_in) sc_l = elem_f32<T>(scale_in, cg);
+                const DivPlan dl = plan_division(sc_l);
+                const uint32_t sb = __float_as_uint(sc_l), ex = (sb >> 23) & 0xFFu;
+                const bool exact_l = dl.kind != 0 && (sb >> 31) == 0u && ex >= 97u && ex <= 157u && need_amax &&
+                                     mb < 0x5E000000u && sc_s.minnz[c_mine] >= 0x0D800000u - 1u;
+                const bool all_exact = __all_sync(0xFFFFFFFFu, exact_l);
+                if (values || dequant || codes) {
+                    const T* src = st + e_w + (uint32_t)lane * 4u;
+                    if (all_exact) {
+                        // the common case, without a branch per piece (the channel of a piece by division, its numbers
+                        // by two shuffles), two pieces per iteration so that their table reads overlap
+                        auto piece = [&](int j) {
+                            const uint32_t e0 = e_w + ((uint32_t)j << 7);
+                            const int from = (int)(fd_div(e0, bt.len) - c_lo);
+                            const float sc = __shfl_sync(0xFFFFFFFFu, sc_l, from), y = __shfl_sync(0xFFFFFFFFu, dl.y, from);
+                            RawVec<T> r;
+                            r.load_shared(src + (j << 7));
+                            float v[4], q[4], d[4];
+                            uint32_t packed;
+                            r.get(v);
+                            stream_quantize4<T, TK>(s_codes, s_lv2, lo, hi, v, sc, y, q, d, packed);
+                            const uint32_t e = e0 + (uint32_t)lane * 4u;
+                            if (values) store4<T>(values + e, q);
+                            if (dequant) store4<T>(dequant + e, d);
+                            if (codes) __stcs(reinterpret_cast<uint32_t*>(codes + e), packed);
+                        };
+                        int j = 0;
+                        for (; j + 2 <= cnt; j += 2) {
+                            piece(j);
+                            piece(j + 1);
+                        }
+                        if (j < cnt) piece(j);
+                    } else {
+                        // rare: some channel of the run needs the per-element checks of the division
+                        uint32_t cur = c_lo, next = (c_lo + 1u) * L, e0 = e_w;
+                        float sc = __shfl_sync(0xFFFFFFFFu, sc_l, 0), y = __shfl_sync(0xFFFFFFFFu, dl.y, 0);
+                        int kind = __shfl_sync(0xFFFFFFFFu, dl.kind, 0);
+#pragma unroll 1
+                        for (int j = 0; j < cnt; ++j, e0 += 128u) {
+                            if (e0 >= next) {                 // warp uniform
+                                ++cur;
+                                next += L;
+                                const int from = (int)(cur - c_lo);
+                                sc = __shfl_sync(0xFFFFFFFFu, sc_l, from);
+                                y = __shfl_sync(0xFFFFFFFFu, dl.y, from);
+                                kind = __shfl_sync(0xFFFFFFFFu, dl.kind, from);
+                            }
+                            RawVec<T> r;
+                            r.load_shared(src + (j << 7));
+                            float v[4], q[4], d[4];
+                            uint32_t packed = 0u;
+                            r.get(v);
+                            DivPlan dv;
+                            dv.s = sc;
+                            dv.y = y;
+                            dv.kind = kind;
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk) {
+                                uint32_t code;
+                                pipe_lookup<TK>(s_codes, s_lv2, lo, hi, bf16_pattern(divide(dv, v[kk])), q[kk], code);
+                                packed |= code << (8 * kk);
+                                d[kk] = Arith<T>::rnd(__fmul_rn(q[kk], sc));
+                            }
+                            const uint32_t e = e0 + (uint32_t)lane * 4u;
+                            if (values) store4<T>(values + e, q);
+                            if (dequant) store4<T>(dequant + e, d);
+                            if (codes) __stcs(reinterpret_cast<uint32_t*>(codes + e), packed);
+                        }
+                    }
+                }
+            }
+        } else {
+            // channel by channel, the team's warps taking the channels in turn (channel lengths that are no multiple
+            // of 128, unaligned tensors); everything stays inside a warp
+            const T* xs = (bt.flags & 1u) ? st : reinterpret_cast<const T*>(bt.x);
+            for (uint32_t c = (uint32_t)idx; c < bt.nc; c += RS_QW) {
+                const uint32_t e_c = c * L;
+                const uint32_t cg = c;
+                float sc = 1.0f;
+                if (need_amax) {
+                    uint32_t m = 0u;
+                    for (uint32_t e = lane; e < L; e += 32u) m = max(m, abs_bits(elem_f32<T>(xs, e_c + e)));
+                    m = __reduce_max_sync(0xFFFFFFFFu, m);
+                    sc = scale_of(m);
+                    if (lane == 0) {
+                        if (amax_out) store_one<T>(amax_out + cg, __uint_as_float(m));
+                        if (scale_out) store_one<T>(scale_out + cg, sc);
+                    }
+                }
+                if (scale_in) sc = elem_f32<T>(scale_in, cg);
+                if (values || dequant || codes) {
+                    const DivPlan dv = plan_division(sc);
+                    for (uint32_t e = lane; e < L; e += 32u) {
+                        float q;
+                        uint32_t code;
+                        pipe_lookup<TK>(s_codes, s_lv2, lo, hi, bf16_pattern(divide(dv, elem_f32<T>(xs, e_c + e))), q, code);
+                        if (values) store_one<T>(values + e_c + e, q);
+                        if (dequant) store_one<T>(dequant + e_c + e, Arith<T>::rnd(__fmul_rn(q, sc)));
+                        if (codes) codes[e_c + e] = (uint8_t)code;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(EMPTY0 + 8u * s);
+    }
+}
+
 // channels per batch / batches of one item, for batches of about `batch_elems` elements
-inline int64_t channels_per_batch(const vq_channel_item& it, int64_t batch_elems, int vec_elems = 1) {
+inline int64_t channels_per_batch(const vq_channel_item& it, int64_t batch_elems, int vec_elems = 1, int64_t max_channels = kBatchMaxChannels) {
     int64_t per = batch_elems / it.length;
-    per = per < 1 ? 1 : (per > kBatchMaxChannels ? kBatchMaxChannels : per);
+    per = per < 1 ? 1 : (per > max_channels ? max_channels : per);
     if (vec_elems > 1 && it.length % vec_elems) {
         // channel length no multiple of a 16-byte vector: a multiple of q channels is
         int64_t g = it.length, b = vec_elems;
@@ -839,12 +1275,14 @@ inline int batch_vec(const vq_channel_item& it, int64_t c0, int64_t nc, int dtyp
                          ((uintptr_t)it.codes & 3) == 0;
     return aligned && (c0 * it.length) % ve == 0 && (nc * it.length) % ve == 0;
 }
-inline int64_t batches_of(const vq_channel_item& it, int64_t batch_elems, int vec_elems = 1) {
+inline int64_t batches_of(const vq_channel_item& it, int64_t batch_elems, int vec_elems = 1, int64_t max_channels = kBatchMaxChannels) {
     if (it.channels <= 0) return 0;
-    const int64_t per = channels_per_batch(it, batch_elems, vec_elems);
+    const int64_t per = channels_per_batch(it, batch_elems, vec_elems, max_channels);
     return (it.channels + per - 1) / per;
 }
-constexpr int64_t kSmallestBatch = PIPE_BATCH;    // the workspace is sized for the finest split any kernel uses
+// the workspace is sized for the finest split any kernel uses
+constexpr int64_t kSmallestBatch = RS_BATCH < PIPE_BATCH ? RS_BATCH : PIPE_BATCH;
+constexpr int64_t kFewestChannels = RS_MAXCH;
 
 }  // namespace
 extern "C" size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items);
@@ -853,12 +1291,13 @@ namespace {
 // Everything a launch needs, decided once from the host descriptors.
 struct ChanLaunch {
     BatchParams p{};
-    int kernel = 0;                 // 0 two sweeps, 2 pipelined
+    int kernel = 0;                 // 0 two sweeps, 2 pipelined, 3 streaming roles
     int dtype = 0, mode = 0, n_items = 0;
     bool lut_tab = false;
     int threads = 0, blocks = 0;
     size_t smem = 0, items_bytes = 0;
     std::vector<ChanBatch> batches; // host copy until it has been uploaded
+    std::vector<StreamBatch> records;   // streaming kernel: what is uploaded instead of `batches`
 };
 
 // Argument checks, kernel choice, batch list.  0 on success; L.p.n_batches == 0: nothing to do.
@@ -923,9 +1362,12 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
     const bool pipe_table = table && ((table->kind == VQ_TABLE_INT && table->lo >= -128.0f && table->hi <= 255.0f) ||
                                       (table->kind == VQ_TABLE_LUT16 && table->nan_uniform && table->lut8 && table->levels2 &&
                                        (uintptr_t)table->lut8 % 16 == 0 && (uintptr_t)table->levels2 % 16 == 0));
+    //   stream the same tables and bulk copies with warps in roles and no barrier; channels up to RS_BATCH elements;
     bool use_pipe = big && (pipe_table || !any_table_out) && longest <= PIPE_BATCH;
     if (want_kernel && !strcmp(want_kernel, "sweep")) use_pipe = false;
-    const int64_t batch_elems = use_pipe ? PIPE_BATCH : kBatchElems;
+    const bool use_stream = use_pipe && longest <= RS_BATCH && !(want_kernel && !strcmp(want_kernel, "pipe"));
+    const int64_t batch_elems = use_stream ? RS_BATCH : (use_pipe ? PIPE_BATCH : kBatchElems);
+    const int64_t max_channels = use_stream ? RS_MAXCH : kBatchMaxChannels;
 
     const int vec_elems = use_pipe ? (dtype == VQ_F32 ? 4 : 8) : 1;
     // Batches of the pipelined kernel that cannot go through registers (channel length no multiple of 4
@@ -937,7 +1379,7 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
         return lean ? batch_elems : batch_elems / 8;
     };
     int64_t n_batches = 0;
-    for (int i = 0; i < n_items; ++i) n_batches += batches_of(items[i], item_batch(items[i]), vec_elems);
+    for (int i = 0; i < n_items; ++i) n_batches += batches_of(items[i], item_batch(items[i]), vec_elems, max_channels);
     VQ_REQUIRE(n_batches < (1ll << 31), "%s: too many channels", name);
     L.dtype = dtype;
     L.n_items = n_items;
@@ -952,7 +1394,7 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
     for (int i = 0; i < n_items; ++i) {
         const vq_channel_item& it = items[i];
         if (it.channels <= 0) continue;
-        const int64_t per = channels_per_batch(it, item_batch(it), vec_elems);
+        const int64_t per = channels_per_batch(it, item_batch(it), vec_elems, max_channels);
         const FastDiv fdv = make_fastdiv((uint32_t)it.length);
         for (int64_t c0 = 0; c0 < it.channels; c0 += per, ++k) {
             hb[k].item = i;
@@ -960,7 +1402,7 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
             hb[k].nc = (int)(it.channels - c0 < per ? it.channels - c0 : per);
             hb[k].len = fdv;
             hb[k].vec = batch_vec(it, hb[k].c0, hb[k].nc, dtype);
-            hb[k].fast = (use_pipe && hb[k].vec && it.length % 128 == 0) ? 1 : 0;
+            hb[k].fast = (use_pipe && hb[k].vec && it.length % 128 == 0 && it.length >= 128) ? 1 : 0;
         }
     }
     if (use_pipe) {
@@ -969,7 +1411,7 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
         auto cost = [&](const ChanBatch& b) -> int64_t {
             const vq_channel_item& it = items[b.item];
             const int64_t n = (int64_t)b.nc * it.length;
-            const int64_t per_elem = !b.vec ? 10 : (it.length % 4 ? 6 : 1);
+            const int64_t per_elem = !b.vec ? 10 : (it.length % 4 ? 6 : ((use_stream && !b.fast) ? 3 : 1));
             return n * per_elem + 64 * (int64_t)b.nc;
         };
         std::stable_sort(hb, hb + n_batches, [&](const ChanBatch& a, const ChanBatch& b) { return cost(a) > cost(b); });
@@ -977,9 +1419,41 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
     p.items = reinterpret_cast<const vq_channel_item*>(workspace);
     p.batches = reinterpret_cast<const ChanBatch*>((char*)workspace + items_bytes);
     p.n_batches = (int)n_batches;
+    if (use_stream) {
+        const size_t es = dtype == VQ_F32 ? 4 : 2;
+        L.records.resize((size_t)n_batches);
+        for (int64_t j = 0; j < n_batches; ++j) {
+            const ChanBatch& b = hb[j];
+            const vq_channel_item& it = items[b.item];
+            const size_t off = (size_t)b.c0 * (size_t)it.length;
+            StreamBatch& r = L.records[(size_t)j];
+            r = StreamBatch{};
+            r.x = (const char*)it.input + off * es;
+            r.values = it.values ? (char*)it.values + off * es : nullptr;
+            r.dequant = it.dequant ? (char*)it.dequant + off * es : nullptr;
+            r.codes = it.codes ? it.codes + off : nullptr;
+            r.amax_out = it.amax_out ? (char*)it.amax_out + (size_t)b.c0 * es : nullptr;
+            r.scale_out = (it.scale_out && !it.scale_in) ? (char*)it.scale_out + (size_t)b.c0 * es : nullptr;
+            r.scale_in = it.scale_in ? (const char*)it.scale_in + (size_t)b.c0 * es : nullptr;
+            r.L = (uint32_t)it.length;
+            r.nc = (uint32_t)b.nc;
+            r.len = b.len;
+            r.flags = (b.vec ? 1u : 0u) | (b.fast ? 2u : 0u);
+        }
+        L.batches.clear();
+    }
 
     const int sms = vq_sm_count();
-    if (use_pipe) {
+    if (use_stream) {
+        L.kernel = 3;
+        L.lut_tab = any_table_out && table->kind == VQ_TABLE_LUT16;     // no quantized output: no table is staged
+        const size_t esize = dtype == VQ_F32 ? 4 : 2;
+        L.smem = (L.lut_tab ? 65536 + 2048 : 0) + (size_t)RS_STAGES * RS_BATCH * esize + RS_STAGES * sizeof(StreamScratch) +
+                 kSmemStream * sizeof(StreamBatch) + 8 * (3 * RS_STAGES + 1) + 4 * 2 * (RS_ATEAMS + RS_QTEAMS) + 16;
+        if ((int)L.smem > vq_max_smem_optin()) return vq_set_error(VQ_ERR_UNSUPPORTED, "%s: device offers too little shared memory", name);
+        L.threads = RS_THREADS;
+        L.blocks = (int)(n_batches < sms ? n_batches : sms);
+    } else if (use_pipe) {
         L.kernel = 2;
         L.lut_tab = any_table_out && table->kind == VQ_TABLE_LUT16;     // no quantized output: no table is staged
         const size_t esize = dtype == VQ_F32 ? 4 : 2;
@@ -1003,8 +1477,9 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
 // Descriptors -> device workspace (pageable sources are staged before cudaMemcpyAsync returns).
 int channel_upload(const char* name, const ChanLaunch& L, const vq_channel_item* items, int n_items, void* workspace, cudaStream_t st) {
     cudaError_t e1 = cudaMemcpyAsync(workspace, items, (size_t)n_items * sizeof(vq_channel_item), cudaMemcpyHostToDevice, st);
-    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + L.items_bytes, L.batches.data(), L.batches.size() * sizeof(ChanBatch),
-                                     cudaMemcpyHostToDevice, st);
+    const void* list = L.kernel == 3 ? (const void*)L.records.data() : (const void*)L.batches.data();
+    const size_t list_bytes = L.kernel == 3 ? L.records.size() * sizeof(StreamBatch) : L.batches.size() * sizeof(ChanBatch);
+    cudaError_t e2 = cudaMemcpyAsync((char*)workspace + L.items_bytes, list, list_bytes, cudaMemcpyHostToDevice, st);
     if (e1 != cudaSuccess || e2 != cudaSuccess)
         return vq_set_error(VQ_ERR_CUDA, "%s: descriptor upload failed: %s", name, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     return 0;
@@ -1014,6 +1489,22 @@ int channel_launch(const ChanLaunch& L, cudaStream_t st) {
     const BatchParams& p = L.p;
     const int dtype = L.dtype, mode = L.mode, blocks = L.blocks, threads = L.threads, n_items = L.n_items;
     const size_t smem = L.smem;
+    if (L.kernel == 3) {
+#define VQ_CHS_LAUNCH(T, K)                                                                                           \
+    do {                                                                                                              \
+        auto kern = channel_stream_kernel<T, K>;                                                                      \
+        VQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                  \
+        kern<<<blocks, threads, smem, st>>>(p);                                                                       \
+    } while (0)
+        if (dtype == VQ_F32) {
+            if (L.lut_tab) VQ_CHS_LAUNCH(float, TK_LUT); else VQ_CHS_LAUNCH(float, TK_INT);
+        } else {
+            if (L.lut_tab) VQ_CHS_LAUNCH(bf16_t, TK_LUT); else VQ_CHS_LAUNCH(bf16_t, TK_INT);
+        }
+#undef VQ_CHS_LAUNCH
+        VQ_LAUNCH_CHECK("channel_stream_kernel");
+        return 0;
+    }
     if (L.kernel == 2) {
 #define VQ_CHP_LAUNCH(T, K)                                                                                           \
     do {                                                                                                              \
@@ -1068,8 +1559,8 @@ int vq_channel_status(void) {
 size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items) {
     if (n_items < 0 || !items) return 0;
     int64_t nb = 0;
-    for (int i = 0; i < n_items; ++i) nb += (items[i].length >= 1) ? batches_of(items[i], kSmallestBatch / 8, 8) : 0;
-    return (size_t)n_items * sizeof(vq_channel_item) + (size_t)nb * sizeof(ChanBatch) + 64;
+    for (int i = 0; i < n_items; ++i) nb += (items[i].length >= 1) ? batches_of(items[i], kSmallestBatch / 8, 8, kFewestChannels) : 0;
+    return (size_t)n_items * sizeof(vq_channel_item) + (size_t)nb * sizeof(StreamBatch) + 64;     // the larger of the two record kinds
 }
 
 int vq_channel_quantize_multi(const vq_channel_item* items, int n_items, int dtype, double quant_max, const vq_table* table,
@@ -1106,6 +1597,8 @@ int vq_channel_plan_create(const vq_channel_item* items, int n_items, int dtype,
     }
     plan->l.batches.clear();
     plan->l.batches.shrink_to_fit();
+    plan->l.records.clear();
+    plan->l.records.shrink_to_fit();
     *plan_out = plan;
     return 0;
 }

@@ -58,6 +58,31 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
     return true;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is pending (it
+// resumes at once when the phase completes): a waiting thread then costs a handful of instructions per microsecond
+__device__ __forceinline__ bool mbar_try_wait_suspended(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait built on it, for waits that may last many microseconds.
+__device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parity, long long budget) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait_suspended(bar, parity, 4000u)) {
+        if (clock64() - t0 > budget) return false;
+    }
+    return true;
+}
+
 // 2-D TMA tile load global -> shared, completion counted in bytes on `bar`.  c0 is the innermost
 // (contiguous) coordinate in elements.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
