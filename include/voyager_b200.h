@@ -478,9 +478,11 @@ VQ_API int vq_channel_plan_create(const vq_channel_item* items, int n_items, int
 VQ_API int vq_channel_plan_run(const vq_channel_plan* plan, void* stream);
 VQ_API void vq_channel_plan_destroy(vq_channel_plan* plan);
 
-/* Non-zero when a bounded wait inside the pipelined per-channel kernel ran out on the current device since
- * the last call (21: the producer waited for a free stage, 22: a consumer group waited for its batch);
- * the outputs of that launch are then incomplete.  Synchronises the device; clears the word. */
+/* Non-zero when a bounded wait inside a bulk-copy per-channel kernel ran out on the current device since the
+ * last call; the outputs of that launch are then incomplete.  Streaming-role kernel: 31 the producer waited for
+ * a free stage, 32 a reduction team for its batch, 33 a quantization team for the reductions, the batch or the
+ * tables.  Group pipeline (channels of 4609..6144 elements): 21 the producer, 22 a consumer group waiting for its
+ * batch, 23 for the tables.  Synchronises the device; clears the word. */
 VQ_API int vq_channel_status(void);
 
 /* out[i] = levels[code[i]] * scale[i / block] in `dtype` (one rounding), from the packed views that
