@@ -396,7 +396,7 @@ def run_extras(dev, iters=20):
     out["cfg5_status_ok"] = gemm_native.gemm_status(dev) == 0
     del xg, wg, xq, wq, xs, ws, xq_f, wq_f, xs_f, ws_f
 
-    # ---- conv2d_mx (the survey's next row after the linear): one ResNet-50 layer, MXINT8 block 32 along the channels,
+    # ---- conv2d_mx: one ResNet-50 layer, MXINT8 block 32 along the channels,
     # NHWC; implicit GEMM (default), patch matrix + GEMM, decode + vendor convolution; checked against the oracle
     torch.manual_seed(6)
     xc = torch.randn(32, 28, 28, 128).bfloat16()
