@@ -1288,6 +1288,8 @@ constexpr int64_t kFewestChannels = RS_MAXCH;
 extern "C" size_t vq_channel_quantize_multi_workspace(const vq_channel_item* items, int n_items);
 namespace {
 
+inline size_t items_bytes_of(int n_items) { return ((size_t)n_items * sizeof(vq_channel_item) + 31) / 32 * 32; }
+
 // Everything a launch needs, decided once from the host descriptors.
 struct ChanLaunch {
     BatchParams p{};
@@ -1376,7 +1378,11 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
     auto item_batch = [&](const vq_channel_item& it) -> int64_t {
         if (!use_pipe) return batch_elems;
         const bool lean = it.length % 4 == 0 && batch_vec(it, 0, 4, dtype);
-        return lean ? batch_elems : batch_elems / 8;
+        if (!lean) return batch_elems / 8;
+        // streaming kernel: channels that are not walked in 128-element pieces are taken channel by channel, which
+        // costs several times more per element
+        if (use_stream && (it.length % 128 != 0 || it.length < 128)) return batch_elems / 4;
+        return batch_elems;
     };
     int64_t n_batches = 0;
     for (int i = 0; i < n_items; ++i) n_batches += batches_of(items[i], item_batch(items[i]), vec_elems, max_channels);
@@ -1411,10 +1417,41 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
         auto cost = [&](const ChanBatch& b) -> int64_t {
             const vq_channel_item& it = items[b.item];
             const int64_t n = (int64_t)b.nc * it.length;
-            const int64_t per_elem = !b.vec ? 10 : (it.length % 4 ? 6 : ((use_stream && !b.fast) ? 3 : 1));
+            const int64_t per_elem = !b.vec ? (use_stream ? 16 : 10) : (it.length % 4 ? (use_stream ? 12 : 6) : ((use_stream && !b.fast) ? 8 : 1));
             return n * per_elem + 64 * (int64_t)b.nc;
         };
         std::stable_sort(hb, hb + n_batches, [&](const ChanBatch& a, const ChanBatch& b) { return cost(a) > cost(b); });
+        if (use_stream) {
+            // Streaming kernel: instead of dealing the ordered list round robin, every batch goes to the CTA with the
+            // least estimated work so far (longest processing time first); CTA c still walks positions c, c + grid, ...
+            // of the list, so its batches are written there and the shorter lists end in empty records (no channels).
+            const int grid = (int)(n_batches < vq_sm_count() ? n_batches : vq_sm_count());
+            std::vector<std::vector<int64_t>> lists((size_t)grid);
+            std::vector<std::pair<int64_t, int>> heap;         // (work, cta), smallest work on top
+            for (int c = 0; c < grid; ++c) heap.emplace_back(0, c);
+            auto cmp = [](const std::pair<int64_t, int>& a, const std::pair<int64_t, int>& b) { return a > b; };
+            std::make_heap(heap.begin(), heap.end(), cmp);
+            for (int64_t j = 0; j < n_batches; ++j) {
+                std::pop_heap(heap.begin(), heap.end(), cmp);
+                auto& top = heap.back();
+                lists[(size_t)top.second].push_back(j);
+                top.first += cost(hb[j]) + 600;                // a fixed share per batch: waits, division plans
+                std::push_heap(heap.begin(), heap.end(), cmp);
+            }
+            size_t longest_list = 0;
+            for (auto& l : lists) longest_list = l.size() > longest_list ? l.size() : longest_list;
+            const int64_t padded = (int64_t)longest_list * grid;
+            const size_t room = (workspace_bytes - items_bytes_of(n_items)) / sizeof(StreamBatch);
+            if (padded <= (int64_t)room && padded < (1ll << 31)) {
+                std::vector<ChanBatch> dealt((size_t)padded);
+                for (auto& b : dealt) b = ChanBatch{-1, 0, 0, make_fastdiv(1u), 0, 0};
+                for (int c = 0; c < grid; ++c)
+                    for (size_t i = 0; i < lists[(size_t)c].size(); ++i) dealt[i * (size_t)grid + (size_t)c] = hb[lists[(size_t)c][i]];
+                L.batches.swap(dealt);
+                hb = L.batches.data();
+                n_batches = padded;
+            }
+        }
     }
     p.items = reinterpret_cast<const vq_channel_item*>(workspace);
     p.batches = reinterpret_cast<const ChanBatch*>((char*)workspace + items_bytes);
@@ -1424,10 +1461,15 @@ int channel_prepare(const char* name, const vq_channel_item* items, int n_items,
         L.records.resize((size_t)n_batches);
         for (int64_t j = 0; j < n_batches; ++j) {
             const ChanBatch& b = hb[j];
-            const vq_channel_item& it = items[b.item];
-            const size_t off = (size_t)b.c0 * (size_t)it.length;
             StreamBatch& r = L.records[(size_t)j];
             r = StreamBatch{};
+            if (b.item < 0) {                                  // an empty record: every role passes it on at once
+                r.L = 1;
+                r.len = b.len;
+                continue;
+            }
+            const vq_channel_item& it = items[b.item];
+            const size_t off = (size_t)b.c0 * (size_t)it.length;
             r.x = (const char*)it.input + off * es;
             r.values = it.values ? (char*)it.values + off * es : nullptr;
             r.dequant = it.dequant ? (char*)it.dequant + off * es : nullptr;
