@@ -395,3 +395,34 @@ def test_pipeline_wait_that_runs_out_is_reported_and_the_context_stays_usable(ke
     _check_channel_results(ws, plan.run(), tab, 4096.0)
     assert _lib.lib.vq_channel_status() == 0
     plan.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["stream", "pipe", "sweep"])
+@pytest.mark.parametrize("outputs", [dict(want_values=True, want_codes=False, want_dequant=False),
+                                     dict(want_values=False, want_codes=True, want_dequant=False),
+                                     dict(want_values=False, want_codes=False, want_dequant=True),
+                                     dict(want_values=False, want_codes=False, want_dequant=False, want_amax=True)])
+def test_per_channel_kernels_with_every_single_output(kernel, outputs, monkeypatch):
+    """One output at a time (the kernels predicate their stores on it), and the maxima / scales alone; large enough
+    for the bulk-copy kernels, channel lengths that are and are not multiples of 128."""
+    monkeypatch.setenv("VOYAGER_B200_CHANNEL_KERNEL", kernel)
+    g = torch.Generator().manual_seed(23)
+    ws = [torch.randn(700, 2304, generator=g) * 0.05, torch.randn(512, 576, generator=g) * 0.05, torch.randn(3000, 256, generator=g)]
+    ws[0][5] = 0
+    tab = golden_table("posit8_1")
+    got = mq.quantize_tensors_per_channel([w.cuda() for w in ws], tab, 4096.0, **outputs)
+    for w, r in zip(ws, got):
+        s_ref = vo.channel_scale(w, 4096.0)
+        q_ref = vo.quantize(w, s_ref, None, None, None, tab)
+        assert same_bits(r.scale, s_ref)[0]
+        if outputs.get("want_amax"):
+            assert same_bits(r.amax, w.abs().amax(dim=1, keepdim=True))[0]
+        if outputs["want_values"]:
+            assert same_bits(r.values, q_ref)[0]
+        if outputs["want_dequant"]:
+            assert same_bits(r.dequant, vo.dequantize(q_ref, s_ref))[0]
+        if outputs["want_codes"]:
+            lv = r.levels[r.codes.cpu().long().clamp(max=r.levels.numel() - 1)]
+            assert torch.equal(lv, q_ref.float())
+    assert _status() == 0
