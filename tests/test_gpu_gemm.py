@@ -334,3 +334,32 @@ def test_fp32_vendor_switch(monkeypatch):
     monkeypatch.setenv("VOYAGER_B200_FP32", "vendor")
     b = Q.linear_mx(qa.cuda(), qb.cuda(), None, input_scale=sa.cuda(), weight_scale=sb.cuda(), block_size=32)
     assert _rel(a, b.cpu()) <= 1e-5
+
+
+@pytest.mark.parametrize("stores", ["tiles", "rows"])
+@pytest.mark.parametrize("M,N,K,ldy,col0,n_out", [(512, 512, 256, 1280, 256, 3), (300, 384, 128, 1024, 512, 2), (1000, 200, 64, 456, 256, 4),
+                                                  (256, 256, 64, 256, 0, 8)])
+def test_scatter_gemm_writes_its_columns_into_every_output_buffer(M, N, K, ldy, col0, n_out, stores, monkeypatch):
+    """``vq_gemm_bf16_tn_scatter`` (the epilogue of the column-parallel linear): the [M, N] result goes to columns
+    [col0, col0 + N) of every output buffer, here several buffers on one GPU; whole 128 x 64 sub-tiles by tensor
+    stores or one bulk copy per row, partial tiles by plain stores; nothing outside the column range is touched."""
+    import ctypes
+    monkeypatch.setenv("VOYAGER_B200_SCATTER_STORES", stores)
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).bfloat16().cuda()
+    b = (torch.randn(N, K, generator=g) * 0.1).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda()
+    outs = [torch.full((M, ldy), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(n_out)]
+    ptrs = (ctypes.c_void_p * n_out)(*[o.data_ptr() for o in outs])
+    st = gemm_native._status_tensor(torch.device("cuda"))
+    rc = _lib.lib.vq_gemm_bf16_tn_scatter(a.data_ptr(), b.data_ptr(), bias.data_ptr(), ptrs, n_out, ldy, col0, M, N, K, st.data_ptr(),
+                                          torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "scatter")
+    torch.cuda.synchronize()
+    assert gemm_native.gemm_status("cuda") == 0
+    want = (a.float() @ b.float().t() + bias.float()).bfloat16()
+    for o in outs:
+        assert torch.equal(o[:, col0:col0 + N].view(torch.int16), outs[0][:, col0:col0 + N].view(torch.int16))
+        assert bool((o[:, :col0] == 7).all()) and bool((o[:, col0 + N:] == 7).all())
+    rel = (outs[0][:, col0:col0 + N].float() - want.float()).norm() / want.float().norm()
+    assert rel <= 5e-3, rel

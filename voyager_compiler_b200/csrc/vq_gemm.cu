@@ -27,7 +27,8 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
                         cudaStream_t st, const CUtensorMap* tmSA = nullptr, const CUtensorMap* tmSB = nullptr,
                         const void* a_codes = nullptr, const void* b_codes = nullptr, bool packed_codes = false, int batch = 1,
-                        int64_t a_batch_rows = 0, int64_t b_batch_rows = 0, int64_t y_batch_stride = 0);
+                        int64_t a_batch_rows = 0, int64_t b_batch_rows = 0, int64_t y_batch_stride = 0,
+                        const CUtensorMap* out_maps = nullptr);
 
 namespace {
 
@@ -503,7 +504,15 @@ int vq_gemm_bf16_tn_scatter(const void* A, const void* B, const void* bias, void
     const char* tile = getenv("VOYAGER_B200_GEMM_TILE");       // "1cta" forces the one-CTA 128x256 tile
     if (M > 128 && !(tile && !strcmp(tile, "1cta"))) {
         if (int rc = make_map(&tmB, B, N, K, 128)) return rc;
-        return vq_gemm_pair_launch(tmA, tmB, Ys, n_outputs, ldy, col_offset, bias, M, N, K, status, (cudaStream_t)stream);
+        // several output buffers (peers): whole sub-tiles leave by tensor stores; VOYAGER_B200_SCATTER_STORES=rows keeps
+        // the one-bulk-copy-per-row form
+        CUtensorMap outs[MAX_OUTPUTS];
+        const char* how = getenv("VOYAGER_B200_SCATTER_STORES");
+        bool tiles = n_outputs > 1 && ldy % 8 == 0 && !(how && !strcmp(how, "rows"));
+        for (int d = 0; d < n_outputs && tiles; ++d)
+            if ((uintptr_t)Ys[d] % 16 || make_map(&outs[d], Ys[d], M, ldy, 128)) tiles = false;
+        return vq_gemm_pair_launch(tmA, tmB, Ys, n_outputs, ldy, col_offset, bias, M, N, K, status, (cudaStream_t)stream, nullptr,
+                                   nullptr, nullptr, nullptr, false, 1, 0, 0, 0, tiles ? outs : nullptr);
     }
     if (int rc = make_map(&tmB, B, N, K, BN)) return rc;
     GemmParams p{};

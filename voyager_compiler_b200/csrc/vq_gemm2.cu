@@ -16,6 +16,8 @@
 // the column-parallel linear, every peer GPU's copy of Y over NVLink).
 #include <cuda.h>
 
+#include <cstring>
+
 #include "vq_common.cuh"
 #include "vq_tc.cuh"
 
@@ -46,11 +48,23 @@ struct PairParams {
     int a_batch_rows, b_batch_rows;   // rows between consecutive batches of A / B (0: shared operand)
     int64_t y_batch_stride;    // elements between consecutive outputs
     int bulk_ok;               // output rows are 16-byte aligned: the epilogue may use bulk stores
+    int tma_out;               // tensor maps of the output buffers are given: whole 128 x 64 sub-tiles leave by one TMA store each
     int32_t* status;
     int blocks_per_row;        // fused variant: the operand maps cover the CODES, two more maps the [rows, K/32] scales
     const uint16_t* a_codes;   // register-staged variant: the code tensors themselves, [M, K] and [N, K]
     const uint16_t* b_codes;
 };
+
+// tensor maps of up to P_MAX_OUT output buffers ([M, ldy] bf16, boxes of 128 rows x 64 columns, 128-byte swizzle)
+struct OutMaps {
+    CUtensorMap m[P_MAX_OUT];
+};
+
+// shared -> global tile store through a tensor map (rows and columns outside the tensor are dropped)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1), "r"(src_smem)
+                 : "memory");
+}
 
 // shared -> global asynchronous bulk copy of `bytes` (multiple of 16) issued by one thread
 __device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
@@ -81,7 +95,8 @@ __device__ __forceinline__ void record_fail(int32_t* status, int code) {
 template <int FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 448 : 192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const PairParams p) {
+                    const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
+                    const __grid_constant__ OutMaps outs, const PairParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sc_base = base + PSTAGES * PSTAGE_BYTES;       // fused: block-scale tiles, one pair per stage
@@ -90,7 +105,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t FULL0 = bar_base, EMPTY0 = bar_base + 8u * PSTAGES, TFULL0 = bar_base + 16u * PSTAGES,
                    TEMPTY0 = TFULL0 + 16u, SLOT = TEMPTY0 + 16u, RAW0 = SLOT + 8u,
                    SCF0 = RAW0 + 8u * PSTAGES, SCE0 = SCF0 + 8u * SC_BUFS, ABORT = SCE0 + 8u * SC_BUFS,
-                   RAWE0 = ABORT + 8u;       // packed variant: "raw stage free" barriers
+                   RAWE0 = ABORT + 8u,       // packed variant: "raw stage free" barriers
+                   EPI_OK = RAWE0 + 8u * PSTAGES;   // tensor-store epilogue: outcome of the accumulator wait, shared by its four warps
 
     constexpr int OST = FUSED == 3 ? 3 : PSTAGES;            // operand ring stages
     constexpr int RST = 4;                                   // packed variant: raw ring stages (16 KB each)
@@ -429,8 +445,22 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int bi = tile / tiles_per_batch, rem = tile - bi * tiles_per_batch;
             const int m0 = (rem % p.tiles_m) * 256 + (int)rank * PM, n0 = (rem / p.tiles_m) * PN;
             const size_t ybase = (size_t)bi * p.y_batch_stride;
-            if (lane == 0) ok = tc::mbar_wait_cluster(TFULL0 + 8u * acc, acc_phase, PWAIT);
-            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (p.tma_out) {
+                // the four warps meet at a named barrier further down, so they must agree on going on: one thread waits
+                // for the accumulator and tells the others
+                if (warp == 2 && lane == 0) {
+                    const bool good = tc::mbar_wait_cluster(TFULL0 + 8u * acc, acc_phase, PWAIT);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(EPI_OK), "r"(good ? 1u : 0u) : "memory");
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                uint32_t good;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(good) : "r"(EPI_OK));
+                ok = good != 0u;
+                asm volatile("bar.sync 2, 128;" ::: "memory");   // everyone has read the word before the next tile rewrites it
+            } else {
+                if (lane == 0) ok = tc::mbar_wait_cluster(TFULL0 + 8u * acc, acc_phase, PWAIT);
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            }
             if (!ok) break;
             tc::tc_fence_after();
             const int row = m0 + q * 32 + lane;
@@ -456,7 +486,36 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 const int half0 = n0 + (c >> 2) * OUT_COLS;                 // first column of this 128-column half
                 const bool bulk = p.bulk_ok && half0 + OUT_COLS <= p.N;      // whole half inside the matrix
-                if (bulk) {
+                if (bulk && p.tma_out) {
+                    // The four epilogue warps stage the half as two sub-tiles of 128 rows x 64 columns in the 128-byte
+                    // swizzled layout of the output maps' boxes; one thread then sends each sub-tile to every output
+                    // buffer (own memory and the peers') with ONE tensor store: 4 stores per buffer and tile instead of
+                    // a 256-byte bulk copy per row and half.  Rows past the end of the matrix are dropped by the store.
+                    const bool issuer = warp == 2 && lane == 0;
+                    if ((c & 3) == 0) {
+                        if (issuer) bulk_wait_read();            // the stores of the previous half have read the buffer
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                    }
+                    const uint32_t sub = out_base + ((uint32_t)(c & 3) >> 1) * (128u * 128u) + (uint32_t)rloc * 128u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t ch = (uint32_t)(c & 1) * 4u + (uint32_t)j;
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sub + ((ch ^ ((uint32_t)rloc & 7u)) << 4)), "r"(o[4 * j]),
+                                     "r"(o[4 * j + 1]), "r"(o[4 * j + 2]), "r"(o[4 * j + 3]) : "memory");
+                    }
+                    if ((c & 3) == 3) {
+                        tc::fence_proxy_async();
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (issuer) {
+                            const int x0 = (int)p.col_offset + half0, y0 = m0;
+                            for (int d = 0; d < p.n_outputs; ++d) {
+                                tma_store_2d(&outs.m[d], out_base, x0, y0);
+                                tma_store_2d(&outs.m[d], out_base + 128u * 128u, x0 + 64, y0);
+                            }
+                            bulk_commit();
+                        }
+                    }
+                } else if (bulk) {
                     // every thread stages only its own row and later copies only its own row, so the
                     // only ordering needed is with its own earlier bulk reads of that row
                     if ((c & 3) == 0) bulk_wait_read();
@@ -514,7 +573,7 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
                         int64_t col_offset, const void* bias, int64_t M, int64_t N, int64_t K, int32_t* status,
                         cudaStream_t st, const CUtensorMap* tmSA, const CUtensorMap* tmSB, const void* a_codes,
                         const void* b_codes, bool packed_codes, int batch, int64_t a_batch_rows, int64_t b_batch_rows,
-                        int64_t y_batch_stride) {
+                        int64_t y_batch_stride, const CUtensorMap* out_maps) {
     const bool fused = tmSA != nullptr && tmSB != nullptr;
     // VOYAGER_B200_FUSED_STAGING=regs selects the register-staged variant (measured slower: one k-step
     // of global loads in flight per thread does not cover the L2 latency); default: TMA + in-place multiply
@@ -538,6 +597,12 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     for (int d = 0; d < n_outputs; ++d)
         if ((uintptr_t)Ys[d] % 16) p.bulk_ok = 0;
     p.blocks_per_row = (int)(K / 32);
+    OutMaps outs;
+    memset(&outs, 0, sizeof(outs));
+    if (out_maps && p.bulk_ok && batch == 1) {
+        for (int d = 0; d < n_outputs; ++d) outs.m[d] = out_maps[d];
+        p.tma_out = 1;
+    }
     const int n_tiles = p.tiles_m * p.tiles_n * batch;
     const int sms = vq_sm_count();
     int pairs = sms / 2;
@@ -549,19 +614,19 @@ int vq_gemm_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* co
     if (fused && packed_codes) {
         auto k = mx_gemm_pair_kernel<3>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
+        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, outs, p);
     } else if (regs) {
         auto k = mx_gemm_pair_kernel<2>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
+        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, outs, p);
     } else if (fused) {
         auto k = mx_gemm_pair_kernel<1>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, p);
+        k<<<pairs * 2, 448, smem, st>>>(tmA, tmB, *tmSA, *tmSB, outs, p);
     } else {
         auto k = mx_gemm_pair_kernel<0>;
         VQ_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<pairs * 2, 192, smem, st>>>(tmA, tmB, tmA, tmB, p);
+        k<<<pairs * 2, 192, smem, st>>>(tmA, tmB, tmA, tmB, outs, p);
     }
     VQ_LAUNCH_CHECK("mx_gemm_pair_kernel");
     return 0;
