@@ -359,9 +359,12 @@ VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t 
  * src/voyager_compiler/quantization/fake_quantize.py:327-341): amax = max over history[history_len, channels]
  * before amax_cur enters it; the history is rolled by -1 along its first axis and slot 0 set to
  * amax_cur; scale = amax / quant_max, unchanged where amax is 0, NaN or Inf; pow2 != 0 rounds the
- * scale up to a power of two (2 ** ceil(log2(scale)) in device arithmetic).  All fp32, in place. */
+ * scale up to a power of two, 2 ** ceil(log2(scale)).  `pow2_stay` (device, 256 bytes, may be NULL): for every
+ * biased fp32 exponent, how many of the values 2^e (1 + m 2^-23), m = 0, 1, ..., the reference arithmetic (the CPU's
+ * fp32 log2, rounded) still maps to e; with it the result equals upstream's bit for bit, without it the device's
+ * log2f decides those few values.  All fp32, in place. */
 VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
-                              double quant_max, int pow2, void* stream);
+                              double quant_max, int pow2, const uint8_t* pow2_stay, void* stream);
 
 /* Group-wise affine fake-quantize of a tensor viewed as [rows, K] with blocks of `block` elements along K (the last
  * block of a row may be short; its zero padding takes part in the extrema as upstream pads it):

@@ -216,3 +216,48 @@ def test_per_channel_observer_refuses_a_new_channel_count_and_loads_a_checkpoint
     with pytest.raises(RuntimeError, match="same device"):
         cpu_mod(x)
     del y1, y2
+
+
+def test_pow2_stay_table_reproduces_ceil_log2_of_the_cpu():
+    """The table the observer kernel uses for ``2 ** ceil(log2(scale))`` against the CPU formula itself, on the
+    values where it matters (just above a power of two, every exponent) and on random scales."""
+    import numpy as np
+    from voyager_compiler_b200 import qtables
+    stay = qtables.derive_pow2_stay_host()
+    g = torch.Generator().manual_seed(1)
+    e = np.arange(1, 255, dtype=np.uint32)
+    near = ((e[:, None] << 23) | np.arange(0, 300, dtype=np.uint32)[None, :]).reshape(-1)
+    rnd = torch.randint(1 << 23, 255 << 23, (200000,), generator=g).numpy().astype(np.uint32)
+    bits = np.concatenate([near, rnd])
+    x = torch.from_numpy(bits.view(np.float32).copy())
+    want = torch.pow(2, torch.ceil(torch.log2(x)))
+    E = (bits >> 23) & 0xFF
+    mant = bits & 0x7FFFFF
+    r = E.astype(np.int64) - 127 + (mant >= stay[E]).astype(np.int64)
+    got = torch.where(torch.from_numpy(r > 127), torch.tensor(float("inf")), torch.pow(2.0, torch.from_numpy(r.astype(np.float32))))
+    assert torch.equal(got, want)
+
+
+@pytest.mark.gpu
+def test_observer_power_of_two_scale_equals_the_cpu_formula_near_powers_of_two():
+    """``force_scale_power_of_two`` in the per-channel observer: channel maxima chosen so that amax / quant_max lands on
+    and just above powers of two, where a device log2 could round differently from the CPU's."""
+    import numpy as np
+    from voyager_compiler_b200.fake_quantize import FusedAmaxObsFakeQuantize
+    qmax = 127.0
+    ks = np.arange(-20, 20)
+    ms = np.arange(0, 40, dtype=np.uint32)
+    sbits = (((ks[:, None] + 127).astype(np.uint32) << 23) | ms[None, :]).reshape(-1)
+    target = torch.from_numpy(sbits.view(np.float32).copy())           # the scales we want to hit
+    amax = (target.double() * qmax).float()                             # amax / qmax lands on or next to them
+    C = amax.numel()
+    x = torch.zeros(C, 8)
+    x[:, 0] = amax
+    x[:, 1] = -amax / 3
+    mod = FusedAmaxObsFakeQuantize("int8", qscheme="per_channel_symmetric", quant_max=qmax, ch_axis=0, amax_history_len=1,
+                                   force_scale_power_of_two=True, device="cuda")
+    mod(x.cuda())
+    mod(x.cuda())                                                       # the second call uses the first call's maximum
+    sf = x.abs().amax(dim=1, keepdim=True) / qmax
+    want = torch.pow(2, torch.ceil(torch.log2(sf)))
+    assert torch.equal(mod.scale.cpu().view(torch.int32), want.view(torch.int32))

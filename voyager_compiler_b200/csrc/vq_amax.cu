@@ -246,11 +246,15 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
 //   amax = max over the history (BEFORE the current maximum enters it);
 //   history <- roll(history, -1, 0); history[0] <- amax_cur;
 //   sf = amax / quant_max, keeping the previous scale where amax is 0, NaN or Inf;
-//   optionally sf <- 2 ** ceil(log2(sf)).
+//   optionally sf <- 2 ** ceil(log2(sf)).  The CPU's fp32 log2 rounds the logarithm of the first few values above a
+//   power of two to the integer itself, so ceil keeps them at that power; how many values that is per exponent
+//   comes from the host (`stay`, one count per biased exponent, derived from the CPU arithmetic the observer is
+//   defined in), which makes the result equal to upstream's bit for bit.  Without the table (and for subnormal
+//   scales) the device's own log2f / exp2f are used.
 // Upstream issues about a dozen tiny tensor operations for this.
 namespace {
 __global__ void observer_update_kernel(const float* __restrict__ amax_cur, float* __restrict__ history, float* __restrict__ scale,
-                                       int H, int64_t C, float qmax, int pow2) {
+                                       int H, int64_t C, float qmax, int pow2, const uint8_t* __restrict__ stay) {
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     // torch.amax propagates NaN
@@ -271,18 +275,26 @@ __global__ void observer_update_kernel(const float* __restrict__ amax_cur, float
     const float prev = scale[c];
     sf = (m > 0.0f) ? sf : prev;
     sf = (fabsf(m) < CUDART_INF_F) ? sf : prev;
-    if (pow2) sf = exp2f(ceilf(log2f(sf)));
+    if (pow2) {
+        const uint32_t b = __float_as_uint(sf), E = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
+        if (stay && (b >> 31) == 0u && E >= 1u && E <= 254u) {
+            const int e = (int)E - 127 + (mant < (uint32_t)stay[E] ? 0 : 1);
+            sf = e > 127 ? CUDART_INF_F : __uint_as_float((uint32_t)(e + 127) << 23);    // e >= -126 here
+        } else {
+            sf = exp2f(ceilf(log2f(sf)));
+        }
+    }
     scale[c] = sf;
 }
 }  // namespace
 
 extern "C" int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
-                                  double quant_max, int pow2, void* stream) {
+                                  double quant_max, int pow2, const uint8_t* pow2_stay, void* stream) {
     const char* name = "vq_observer_update";
     VQ_REQUIRE(amax_cur && history && scale, "%s: null pointer", name);
     VQ_REQUIRE(history_len >= 1 && channels >= 1, "%s: bad sizes", name);
     observer_update_kernel<<<(unsigned)((channels + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
-        amax_cur, history, scale, history_len, channels, (float)quant_max, pow2);
+        amax_cur, history, scale, history_len, channels, (float)quant_max, pow2, pow2_stay);
     VQ_LAUNCH_CHECK("observer_update_kernel");
     return 0;
 }

@@ -30,7 +30,7 @@ from typing import List, Optional, Sequence, Tuple, Union
 import numpy as np
 import torch
 
-from . import _lib, ops, tables
+from . import _lib, ops, qtables, tables
 from .qtables import table_handle
 
 __all__ = ["QScheme", "amax", "fake_quantize", "mx_fake_quantize", "FakeQuantizeFunction", "MXFakeQuantizeFunction",
@@ -428,9 +428,11 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         with torch.cuda.device(x.device):
             stream = torch.cuda.current_stream(x.device).cuda_stream
             _lib.check(_lib.lib.vq_amax(xc.data_ptr(), _DT[x.dtype], outer, ch, inner, self._amax_cur.data_ptr(), stream), "amax")
+            stay = qtables.pow2_stay_table(x.device) if self.force_scale_power_of_two else None
             _lib.check(_lib.lib.vq_observer_update(self._amax_cur.data_ptr(), self.amax_history.data_ptr(),
                                                    self.scale.data_ptr(), self.amax_history_len, ch, float(self.quant_max),
-                                                   1 if self.force_scale_power_of_two else 0, stream), "observer update")
+                                                   1 if self.force_scale_power_of_two else 0,
+                                                   stay.data_ptr() if stay is not None else None, stream), "observer update")
 
     # -- outlier filtering (fake_quantize.py:373-394)
     @property

@@ -237,3 +237,37 @@ def exp_tables(dtype: torch.dtype, quant_max: float, device) -> ExpTables:
         with _lock:
             _exp_cache[key] = t
     return t
+
+
+_pow2_stay_cache: dict = {}
+
+
+def derive_pow2_stay_host() -> np.ndarray:
+    """For every biased fp32 exponent E, the number of consecutive values ``2^(E-127) * (1 + m 2^-23)``, m = 0, 1, ...,
+    for which ``ceil(log2(x))`` evaluated in the CPU's fp32 arithmetic is still ``E - 127`` (the logarithm of a value
+    just above a power of two rounds to the integer).  This is what ``2 ** ceil(log2(scale))`` of the observer
+    (quantization/fake_quantize.py:339-340) depends on; uint8[256], entries 0 and 255 unused."""
+    span = 256
+    e = np.arange(1, 255, dtype=np.uint32)
+    bits = (e[:, None] << 23) | np.arange(span, dtype=np.uint32)[None, :]
+    x = torch.from_numpy(bits.view(np.float32).copy())
+    same = torch.ceil(torch.log2(x)) == torch.from_numpy((e.astype(np.int64) - 127).astype(np.float32))[:, None]
+    # length of the leading run of True in every row
+    stay = torch.cumprod(same.to(torch.int64), dim=1).sum(dim=1)
+    if int(stay.max()) >= span or int(stay.min()) < 1:
+        raise RuntimeError("unexpected log2 behaviour on this host")
+    out = np.zeros(256, dtype=np.uint8)
+    out[1:255] = stay.numpy().astype(np.uint8)
+    return out
+
+
+def pow2_stay_table(device) -> torch.Tensor:
+    device = torch.device(device)
+    key = str(device)
+    with _lock:
+        t = _pow2_stay_cache.get(key)
+    if t is None:
+        t = torch.from_numpy(derive_pow2_stay_host()).to(device)
+        with _lock:
+            _pow2_stay_cache[key] = t
+    return t
