@@ -789,6 +789,35 @@ def conv_cases(res, timed, Q, qmap, g, dev, steps, only=None):
             res[f"conv2d_mx_{name}_{layout}"] = entry
 
 
+def run_linear_f32(args):
+    """linear_mx on fp32 operands (MXINT8 codes and power-of-two scales in fp32 containers): the tf32 contraction,
+    ``--m`` rows (default 8192; the bench's extra block uses 2048) x 11008 x 4096.  One JSON line."""
+    import torch
+    import voyager_compiler_b200 as vb
+    from voyager_compiler_b200.gemm_native import gemm_status
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    M, N, K = args.m, 11008, 4096
+    g = torch.Generator(device=dev); g.manual_seed(4)
+    Q = torch.ops.quantized_ops
+    qmap = torch.from_numpy(vb.tables.build_table("int8").view("int16").copy()).view(torch.bfloat16).to(dev)
+    xs, xq = Q.quantize_mx(torch.randn(M, K, generator=g, device=dev), qmap, (-1,), 32, 127.0, True)
+    ws, wq = Q.quantize_mx(torch.randn(N, K, generator=g, device=dev) * 0.02, qmap, (-1,), 32, 127.0, True)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    fn = lambda: Q.linear_mx(xq, wq, None, input_scale=xs, weight_scale=ws, block_size=32)
+    y = fn()
+    ref = torch.nn.functional.linear((xq * xs.repeat_interleave(32, 1)).double(), (wq * ws.repeat_interleave(32, 1)).double())
+    rel = float(((y.double() - ref).norm() / ref.norm()).item())
+    med, best = _timed_flushed(torch, fn, args.steps, flush)
+    peaks, kind = measured_peaks()
+    flops = 2.0 * M * N * K
+    print(json.dumps({"workload": f"linear_mx, fp32 operands, {M} x {N} x {K}: decode kernels + tf32 tcgen05 GEMM", "ms": med,
+                      "tflops": flops / med / 1e9, "best_tflops": flops / best / 1e9,
+                      "frac_of_half_the_measured_bf16_peak": flops / med / 1e9 / (peaks["bf16_tflops"] / 2), "peak_kind": kind,
+                      "rel_frobenius_error_vs_fp64_product": rel, "gemm_status": gemm_status(dev)}))
+
+
 def run_conv(args):
     """The conv2d_mx cases alone (see conv_cases): one JSON line."""
     import torch
@@ -1193,7 +1222,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32, help="fewer than 32: reduced model for profiler captures")
     ap.add_argument("--kernel-only", action="store_true", help="device-timed part only (profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (skip the other configurations)")
-    ap.add_argument("--workload", default="model", choices=["model", "linear", "elementwise", "channel", "conv"],
+    ap.add_argument("--workload", default="model", choices=["model", "linear", "linear_f32", "elementwise", "channel", "conv"],
                     help="model: NF4 whole-model quantization (headline); linear: the cfg5 MX linear")
     ap.add_argument("--only", default=None, help="--workload conv: run the cases whose name contains this text")
     ap.add_argument("--m", type=int, default=8192, help="rows of the activation for --workload linear")
@@ -1209,6 +1238,9 @@ def main():
         return
     if args.workload == "conv":
         run_conv(args)
+        return
+    if args.workload == "linear_f32":
+        run_linear_f32(args)
         return
     if args.impl == "reference":
         run_reference(args)
