@@ -181,6 +181,36 @@ def _timed_flushed(torch, fn, iters, flush):
     return statistics.median(ts), min(ts)
 
 
+def _timing_context(torch, flush, copy_bytes=None, iters=50):
+    """What the timing method itself contributes to a small launch, measured with the vendor's kernels under the same
+    bracket (L2 overwritten, event, call, event): ``floor_us`` is a 4-byte fill (a launch that moves nothing), and
+    ``copy_us`` a device-to-device ``copy_`` that reads and writes ``copy_bytes`` in total.  Means over ``iters``
+    calls (the event clock ticks in steps of about a microsecond, so medians of short launches are quantised)."""
+    one = torch.zeros(1, device=flush.device)
+
+    def mean_us(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.fmean(ts) * 1e3
+
+    ctx = {"floor_us": mean_us(one.zero_), "floor_is": "torch fill of 4 bytes, same bracket"}
+    if copy_bytes:
+        a = torch.empty(int(copy_bytes) // 2, dtype=torch.uint8, device=flush.device)
+        b = torch.empty_like(a)
+        ctx["copy_us"] = mean_us(lambda: b.copy_(a))
+        ctx["copy_is"] = f"torch copy_ moving {int(copy_bytes)} bytes in total (half read, half written), same bracket"
+        del a, b
+    return ctx
+
+
 def _bits_differ(torch, got, want):
     """Number of elements whose values differ (NaN == NaN, -0 != +0)."""
     a, b = got.detach().cpu().contiguous(), want.detach().cpu().contiguous()
@@ -242,6 +272,7 @@ def run_extras(dev, iters=20):
     peaks, kind = measured_peaks()
     flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
     out = {"peak_kind": kind, "l2": f"{FLUSH_BYTES >> 20} MB written between timed iterations"}
+    out["timing_context"] = _timing_context(torch, flush, copy_bytes=25_502_912 * 9, iters=iters)
 
     def tab(name):
         return torch.from_numpy(vb.tables.build_table(name).view(np.int16).copy()).view(torch.bfloat16)
@@ -1043,9 +1074,12 @@ def run_channel(args):
         ts.append(e0.elapsed_time(e1))
     peaks, kind = measured_peaks()
     med = statistics.median(ts)
+    ctx = _timing_context(torch, flush, copy_bytes=n * 9, iters=min(args.steps, 50))
     print(json.dumps({"workload": "cfg2: posit8_1 per output channel, 54 ResNet-50-shaped tensors, codes + dequantized fp32",
-                      "elements": n, "bytes_per_launch": n * 9, "us_per_launch": med * 1e3, "gbs": n * 9 / med / 1e6,
+                      "elements": n, "bytes_per_launch": n * 9, "us_per_launch": med * 1e3, "mean_us_per_launch": statistics.fmean(ts) * 1e3,
+                      "gbs": n * 9 / med / 1e6,
                       "frac_of_measured_hbm_peak": n * 9 / med / 1e6 / peaks["hbm_gbs"], "peak_kind": kind,
+                      "timing_context": ctx, "same_bytes_copy_frac_of_measured_hbm_peak": n * 9 / ctx["copy_us"] / 1e3 / peaks["hbm_gbs"],
                       "steps": args.steps, "channel_status": vb._lib.lib.vq_channel_status()}))
     plan.close()
 
@@ -1210,7 +1244,7 @@ def run_elementwise(args):
     for k, v in res.items():
         v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]
     print(json.dumps({"workload": "element-wise configs (cfg1, cfg2, cfg4 shapes)", "results": res, "peak_hbm_gbs": peaks["hbm_gbs"],
-                      "peak_kind": kind}))
+                      "peak_kind": kind, "timing_context": _timing_context(torch, flush, copy_bytes=4096 * 4096 * 8)}))
 
 
 def main():
