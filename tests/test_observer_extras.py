@@ -163,3 +163,38 @@ def test_group_affine_fake_quantize_matches_oracle(dtype, shape, axis, block, qm
         sf, zp, y = fq.group_affine_fake_quantize(x.cuda(), axis, block, qmin, qmax, None if sq is None else sq.cuda())
         sf_ref, zp_ref, y_ref = vo.group_affine_fake_quantize(x, axis, block, qmin, qmax, sq)
         assert _same(sf, sf_ref) and _same(zp, zp_ref) and _same(y, y_ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("block", [32, 64, 128, 256, 512])
+@pytest.mark.parametrize("form", ["held", "sweeps"])
+def test_group_affine_blocks_held_in_registers_and_extreme_values(dtype, block, form, monkeypatch):
+    """Block sizes that take the kernel which keeps a block in registers and multiplies by a reciprocal where that
+    gives the same quotient, against the two-sweep form and the oracle: blocks of tiny (the checked division), huge,
+    zero, constant, infinite and NaN values, negative-only and positive-only blocks, a range that overflows."""
+    from voyager_compiler_b200 import fake_quantize as fq
+    if form == "sweeps":
+        monkeypatch.setenv("VOYAGER_B200_GROUP_AFFINE", "sweeps")
+    g = torch.Generator().manual_seed(block)
+    rows, K = 96, 2048
+    x = torch.randn(rows, K, generator=g) * torch.logspace(-3, 3, rows).unsqueeze(1)
+    x[3] *= 1e-30
+    x[4] *= 1e-38
+    x[5] *= 1e25
+    x[6] *= 1e35                                                # max - min overflows in places
+    x[7] = 0.0
+    x[8] = 0.37
+    x[9, 5] = float("inf")
+    x[10, 7] = float("-inf")
+    x[11, 9] = float("nan")
+    x[12] = x[12].abs() + 1.0
+    x[13] = -x[13].abs() - 1.0
+    x[14, ::3] = 0.0
+    x[15, :40] = torch.tensor([1e-19, -1e-19, 8.7e-19, 1e-18] * 10)    # around 2^-60
+    x[16] *= 1e-17
+    x = x.to(dtype)
+    for qmin, qmax in ((0.0, 15.0), (-128.0, 127.0)):
+        sf, zp, y = fq.group_affine_fake_quantize(x.cuda(), -1, block, qmin, qmax, None)
+        sf_ref, zp_ref, y_ref = vo.group_affine_fake_quantize(x, -1, block, qmin, qmax, None)
+        assert _same(sf, sf_ref) and _same(zp, zp_ref) and _same(y, y_ref)

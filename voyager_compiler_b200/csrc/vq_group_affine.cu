@@ -10,7 +10,19 @@
 // Every operation is the IEEE operation upstream's expression performs, rounded to the tensor dtype after
 // each step for bf16.  One launch: a group of G lanes takes a block, sweeps it once for the extrema and once
 // (from L1/L2) for the values; HBM sees sizeof(T) read + sizeof(T) written per element plus two numbers per block.
+//
+// Blocks of exactly four 16-byte pieces per lane (block sizes 32 ... 512 that divide the row) take
+// group_affine_held_kernel: the block stays in registers between the two sweeps, two elements go through every
+// rounding, addition and multiplication together (cvt.rn.bf16x2, fma.rn.f32x2), the clamp is min.NaN / max.NaN,
+// and x / sf is a multiplication wherever that gives the same rounded quotient:
+//   * fp32: the corrected reciprocal of vq_divide.cuh (checked per element);
+//   * bf16: x * rcp.approx(sf) rounded to bf16.  x and sf carry 8-bit significands, so the exact quotient stays at
+//     least 2^-17 (relative) away from every bf16 rounding boundary while the product is within 2^-22 of it (the
+//     argument at the top of vq_mx_fast.cuh); it needs a normal quotient: 2^-63 <= sf <= 2^63 and |x| >= 2^-60 or zero.
 #include "vq_common.cuh"
+#include "vq_divide.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace {
 
@@ -132,6 +144,147 @@ __global__ void __launch_bounds__(256) group_affine_kernel(const GroupAffinePara
     }
 }
 
+__device__ __forceinline__ float min_nan(float a, float b) {
+    float d;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float d;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+// {a, b} = {a, b} * m + c as one packed fp32x2 operation (two correctly rounded results)
+__device__ __forceinline__ void fma_pair(float& a, float& b, float m, float c) {
+    asm("{\n\t.reg .b64 x, y, z;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %2};\n\tmov.b64 z, {%3, %3};\n\t"
+        "fma.rn.f32x2 x, x, y, z;\n\tmov.b64 {%0, %1}, x;\n\t}"
+        : "+f"(a), "+f"(b)
+        : "f"(m), "f"(c));
+}
+__device__ __forceinline__ void mul_pair(float& a, float& b, float m) {
+    asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %2};\n\tmul.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+        : "+f"(a), "+f"(b)
+        : "f"(m));
+}
+// both values rounded to the tensor dtype; `packed` receives the two bf16 patterns (a low, b high)
+template <typename T>
+__device__ __forceinline__ void rnd_pair(float& a, float& b, uint32_t& packed);
+template <>
+__device__ __forceinline__ void rnd_pair<float>(float&, float&, uint32_t&) {}
+template <>
+__device__ __forceinline__ void rnd_pair<bf16_t>(float& a, float& b, uint32_t& packed) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(b), "f"(a));
+    a = __uint_as_float(packed << 16);
+    b = __uint_as_float(packed & 0xFFFF0000u);
+}
+
+// x / sf for all elements of a block, prepared once
+template <typename T>
+struct BlockQuotient;
+template <>
+struct BlockQuotient<float> {
+    DivPlan d;
+    __device__ __forceinline__ explicit BlockQuotient(float sf) : d(plan_division(sf)) {}
+    __device__ __forceinline__ void pair(float& a, float& b) const {
+        a = divide(d, a);
+        b = divide(d, b);
+    }
+};
+template <>
+struct BlockQuotient<bf16_t> {
+    float sf, y;
+    bool mul;
+    __device__ __forceinline__ explicit BlockQuotient(float s) : sf(s) {
+        const uint32_t sb = __float_as_uint(s), ex = (sb >> 23) & 0xFFu;
+        mul = (sb >> 31) == 0u && ex >= 64u && ex <= 190u;
+        asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(s));
+    }
+    // the caller rounds the results to bf16
+    __device__ __forceinline__ void pair(float& a, float& b) const {
+        const uint32_t aa = __float_as_uint(a) & 0x7FFFFFFFu, ab = __float_as_uint(b) & 0x7FFFFFFFu;
+        // zero, or at least 2^-60 (a NaN or an infinity gives the same through the product)
+        if (mul && (aa - 1u) >= 0x217FFFFFu && (ab - 1u) >= 0x217FFFFFu) {
+            mul_pair(a, b, y);
+        } else {
+            a = __fdiv_rn(a, sf);
+            b = __fdiv_rn(b, sf);
+        }
+    }
+};
+
+// Blocks of exactly 4 * G 16-byte pieces, K a multiple of the block: see the head of the file.
+template <typename T>
+__global__ void __launch_bounds__(256) group_affine_held_kernel(const GroupAffineParams p) {
+    constexpr int V = Vec<T>::N;
+    const T* x = reinterpret_cast<const T*>(p.in);
+    T* out = reinterpret_cast<T*>(p.out);
+    const int G = p.lanes;
+    const int lane = threadIdx.x & 31, sub = lane & (G - 1);
+    const uint32_t gmask = (G == 32) ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+    const int64_t groups = ((int64_t)gridDim.x * blockDim.x) / G;
+    const int64_t rounds = (p.n_blocks + groups - 1) / groups;
+    const int64_t g0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const float lo = rnd<T>(p.qmin), hi = rnd<T>(p.qmax);
+    for (int64_t r = 0; r < rounds; ++r) {               // all lanes of a warp stay in the loop together
+        const int64_t b = g0 + r * groups;
+        const bool live = b < p.n_blocks;
+        const T* src = x + (live ? b : 0) * (int64_t)p.block + sub * V;     // rows are whole blocks: block b starts at b * block
+        Vec<T> v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k].load_stream(src + k * G * V);
+        float mn = v[0].v[0], mx = v[0].v[0];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                mn = min_nan(mn, v[k].v[j]);
+                mx = max_nan(mx, v[k].v[j]);
+            }
+        for (int o = G >> 1; o > 0; o >>= 1) {
+            mn = min_nan(mn, __shfl_xor_sync(gmask, mn, o));
+            mx = max_nan(mx, __shfl_xor_sync(gmask, mx, o));
+        }
+        if (mn != mn || mx != mx) mn = mx = __uint_as_float(0x7FC00000u);
+        float sf = rnd<T>(__fdiv_rn(rnd<T>(__fsub_rn(mx, mn)), p.qrange));
+        sf = (sf > 0.0f) ? sf : 1.0f;
+        float zp = rnd<T>(__fadd_rn(rnd<T>(__fdiv_rn(-mn, sf)), p.qmin));
+        sf = through_table<T>(p.table, sf);
+        zp = through_table<T>(p.table, zp);
+        if (live && sub == 0) {
+            store_one<T>(reinterpret_cast<T*>(p.scale) + b, sf);
+            store_one<T>(reinterpret_cast<T*>(p.zero_point) + b, zp);
+        }
+        const BlockQuotient<T> quot(sf);
+        const float nzp = -zp;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t w[V / 2];
+#pragma unroll
+            for (int j = 0; j < V; j += 2) {
+                float a = v[k].v[j], c = v[k].v[j + 1];
+                uint32_t& pk = w[j / 2];
+                quot.pair(a, c);
+                rnd_pair<T>(a, c, pk);
+                fma_pair(a, c, 1.0f, zp);                  // t + zp (the product with one is exact)
+                rnd_pair<T>(a, c, pk);
+                a = min_nan(max_nan(rintf(a), lo), hi);    // keeps a NaN, as torch.clamp does
+                c = min_nan(max_nan(rintf(c), lo), hi);
+                fma_pair(a, c, 1.0f, nzp);                 // q - zp
+                rnd_pair<T>(a, c, pk);
+                mul_pair(a, c, sf);
+                rnd_pair<T>(a, c, pk);
+                v[k].v[j] = a;
+                v[k].v[j + 1] = c;
+            }
+            if (live) {
+                T* dst = out + b * (int64_t)p.block + sub * V + k * G * V;
+                if (sizeof(T) == 2) __stcs(reinterpret_cast<uint4*>(dst), make_uint4(w[0], w[1], w[(V / 2) > 2 ? 2 : 0], w[(V / 2) > 3 ? 3 : 0]));
+                else v[k].store(dst);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" int vq_group_affine_fake_quantize(const void* in, int dtype, int64_t rows, int64_t K, int64_t block, double quant_min,
@@ -160,8 +313,16 @@ extern "C" int vq_group_affine_fake_quantize(const void* in, int dtype, int64_t 
     const int64_t want = (p.n_blocks * lanes + threads - 1) / threads;
     const int64_t cap = (int64_t)vq_sm_count() * 8;
     const int blocks = (int)(want < cap ? want : cap);
-    if (dtype == VQ_F32) group_affine_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
-    else group_affine_kernel<bf16_t><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    // the block held in registers: exactly four pieces per lane and rows of whole blocks (VOYAGER_B200_GROUP_AFFINE=sweeps: never)
+    const char* form = getenv("VOYAGER_B200_GROUP_AFFINE");
+    const bool held = p.vec && K % block == 0 && chunks == 4ll * lanes && !(form && !strcmp(form, "sweeps"));
+    if (held) {
+        if (dtype == VQ_F32) group_affine_held_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+        else group_affine_held_kernel<bf16_t><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    } else {
+        if (dtype == VQ_F32) group_affine_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+        else group_affine_kernel<bf16_t><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    }
     VQ_LAUNCH_CHECK("group_affine_kernel");
     return 0;
 }
