@@ -106,9 +106,16 @@ def test_module_steps_like_upstream(case):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n", [1, 31, 4099, 1 << 20, (1 << 22) + 5])
-def test_exponent_histogram_matches_oracle(dtype, n):
+@pytest.mark.parametrize("n,form", [(1, None), (31, None), (4099, None), (1 << 20, None), ((1 << 22) + 5, None),
+                                    ((1 << 22) + 5, "match"), ((1 << 23) + 3, "flush")])
+def test_exponent_histogram_matches_oracle(dtype, n, form, monkeypatch):
+    """From 2^18 aligned elements on every lane counts into its own column of shared-memory counters; "match" keeps the
+    warp-vote kernel for the large case too, "flush" makes the lanes empty their 16-bit counters every 8 vectors (three rounds at this size)."""
     from voyager_compiler_b200 import fake_quantize as fq
+    if form == "match":
+        monkeypatch.setenv("VOYAGER_B200_HISTOGRAM", "match")
+    if form == "flush":
+        monkeypatch.setenv("VOYAGER_B200_HISTOGRAM_FLUSH_EVERY", "8")
     g = torch.Generator().manual_seed(n)
     x = torch.randn(n, generator=g) * torch.exp2(torch.randint(-140, 130, (n,), generator=g).float())
     k = min(n, 2000)
@@ -198,3 +205,27 @@ def test_group_affine_blocks_held_in_registers_and_extreme_values(dtype, block, 
         sf, zp, y = fq.group_affine_fake_quantize(x.cuda(), -1, block, qmin, qmax, None)
         sf_ref, zp_ref, y_ref = vo.group_affine_fake_quantize(x, -1, block, qmin, qmax, None)
         assert _same(sf, sf_ref) and _same(zp, zp_ref) and _same(y, y_ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [(1 << 20) + 7, 3 << 20])
+def test_exponent_histogram_on_ordinary_data(dtype, n):
+    """Values as tensors hold them (a few binades around one, many exact zeros), which the large-tensor kernel counts
+    without looking at the thresholds, with a sprinkling of what sends a batch to the exact rule: patterns just below a
+    power of two, subnormals, values outside 2^-62 .. 2^65, infinities."""
+    from voyager_compiler_b200 import fake_quantize as fq
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g) * 3
+    x[torch.rand(n, generator=g) < 0.3] = 0.0
+    k = 300
+    at = torch.randint(0, n, (k,), generator=g)
+    e = torch.randint(-3, 4, (k,), generator=g)
+    x[at] = (torch.exp2(e.float()).view(torch.int32) - torch.randint(0, 50, (k,), generator=g).int()).view(torch.float32)
+    x[torch.randint(0, n, (40,), generator=g)] = torch.tensor([1e-39, -3e-42, 1e-25, 1e30, float("inf"), -1e-20, 7e19, 2.0 ** -62] * 5)
+    x = x.to(dtype)
+    hist = torch.zeros(254, device="cuda")
+    fq.exponent_histogram(x.cuda(), hist)
+    assert torch.equal(hist.cpu(), vo.exponent_histogram(x))
+    fq.exponent_histogram(x.cuda(), hist)                       # accumulates
+    assert torch.equal(hist.cpu(), 2 * vo.exponent_histogram(x))

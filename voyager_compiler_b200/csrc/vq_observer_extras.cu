@@ -16,6 +16,8 @@
 // All three kernels are HBM streams: sizeof(T) read per element for the histogram, sizeof(T) read +
 // sizeof(T) written for the split, 2 x sizeof(T) read + sizeof(T) written for the merge.
 #include "vq_common.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace {
 
@@ -82,6 +84,178 @@ __global__ void __launch_bounds__(kHistThreads) exp_histogram_kernel(const T* __
 #pragma unroll
         for (int w = 0; w < kHistThreads / 32; ++w) c += hist[w][b];
         if (c) atomicAdd(counts + b, c);
+    }
+}
+
+// The same histogram for large aligned tensors, without any exchange between lanes: every lane of every warp owns a
+// column of 16-bit counters in shared memory (32 lanes per row: a warp's update touches 32 different counters, two
+// per bank word, whatever the rows are), so an element costs a few integer operations for its row and one load / add /
+// store; two elements go together (both loads, then both stores, the second one higher when the rows are the same).
+// A column has 128 rows: row r counts exponent field 64 + r, that is bin 63 + r (2^-62 <= |x| < 2^65 covers what tensors
+// hold), row 0 collects the zeros.  Everything else takes the exact rule element by element, into the CTA's totals by
+// shared-memory atomics: a batch of vectors with an element outside that window, a non-zero subnormal, an infinity or
+// NaN, or one of the 256 patterns at the top of a binade, which alone have to look at the thresholds (one running
+// maximum and two running minima over the batch tell).  The prologue checks what that relies on (`fast`: every
+// threshold of a normal binade lies among those 256 patterns; else every batch takes the exact rule).  A lane counts
+// at most 65 528 elements between two flushes of its counters; 24 warps of 8 KB each hide the latency of the updates.
+constexpr int kLaneWarps = 24;
+constexpr int kLaneThreads = kLaneWarps * 32;
+constexpr int kLaneUnroll = 4;                       // 16-byte loads per lane and buffer (two buffers take turns)
+constexpr int kLaneRows = 128;
+constexpr uint32_t kLaneFirstField = 64;             // row r <-> exponent field 64 + r
+constexpr size_t kLaneSmem = 1120 + 1024 + (size_t)kLaneWarps * kLaneRows * 32 * sizeof(uint16_t);
+
+// the exact rule for one element (b: fp32 pattern without the sign), added to the CTA's totals (index: bin + 1)
+__device__ __noinline__ void lane_count_exact(uint32_t* totals, uint32_t b, const uint32_t* bump) {
+    const int bin = exponent_bin(b, bump);
+    if (bin >= 0) atomicAdd(totals + bin + 1, 1u);
+}
+// two elements whose rows are at byte offsets o0 and o1 of the column
+__device__ __forceinline__ void lane_count_pair(char* col, uint32_t o0, uint32_t o1) {
+    uint16_t* p0 = reinterpret_cast<uint16_t*>(col + o0);
+    uint16_t* p1 = reinterpret_cast<uint16_t*>(col + o1);
+    const uint32_t c0 = *p0, c1 = *p1;
+    *p0 = (uint16_t)(c0 + 1u);
+    *p1 = (uint16_t)(c1 + 1u + (o0 == o1 ? 1u : 0u));
+}
+
+// kLaneUnroll vectors of one lane
+template <typename T>
+__device__ __forceinline__ void lane_count_batch(char* col, uint32_t* totals, const uint4 (&v)[kLaneUnroll], const uint32_t* bump,
+                                                 bool fast) {
+    // t: pattern of |x| with the exponent field at bits 30..23 (fp32) or 14..7 (bf16 halves)
+    constexpr uint32_t kOne = sizeof(T) == 4 ? (1u << 23) : (1u << 7);
+    constexpr uint32_t kFloor = (kLaneFirstField + 1u) * kOne;             // smallest pattern with a row of its own
+    constexpr uint32_t kCeil = (kLaneFirstField + kLaneRows) * kOne;       // first pattern above the window
+    uint32_t top = 0u, low = 0xFFFFFFFFu, high = 0u;
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (sizeof(T) == 4) {
+                const uint32_t t = w[k] & 0x7FFFFFFFu;
+                top = max(top, w[k] | 0xFF800000u);                  // mantissa field, all ones above it
+                low = min(low, t - 1u);                              // a zero wraps to the top
+                high = max(high, t);
+            } else {
+                // a bf16 mantissa ends in 16 zero bits as fp32: never among the top 256 patterns of a binade
+                const uint32_t t0 = w[k] & 0x7FFFu, t1 = (w[k] >> 16) & 0x7FFFu;
+                low = min(low, min(t0 - 1u, t1 - 1u));
+                high = max(high, max(t0, t1));
+            }
+        }
+    }
+    if (fast && top < 0xFFFFFF00u && low >= kFloor - 1u && high < kCeil) {
+        // byte offset of a row: (field - 64) * 64, a zero (field 0) raised to row 0
+        constexpr uint32_t kBase = kLaneFirstField * 64u;
+#pragma unroll
+        for (int u = 0; u < kLaneUnroll; ++u) {
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            if (sizeof(T) == 4) {
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] = max((w[k] >> 17) & 0x3FC0u, kBase) - kBase;
+                lane_count_pair(col, o[0], o[1]);
+                lane_count_pair(col, o[2], o[3]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    lane_count_pair(col, max((w[k] >> 1) & 0x3FC0u, kBase) - kBase, max((w[k] >> 17) & 0x3FC0u, kBase) - kBase);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < kLaneUnroll; ++u) {                     // registers only: no indexing by a loop variable
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (sizeof(T) == 4) {
+                    lane_count_exact(totals, w[k] & 0x7FFFFFFFu, bump);
+                } else {
+                    lane_count_exact(totals, (w[k] << 16) & 0x7FFF0000u, bump);
+                    lane_count_exact(totals, w[k] & 0x7FFF0000u, bump);
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(const T* __restrict__ x, int64_t n,
+                                                                              const uint32_t* __restrict__ bump_at,
+                                                                              unsigned long long* __restrict__ counts, int epoch_vectors) {
+    extern __shared__ uint4 lanes_smem[];
+    uint32_t* bump = reinterpret_cast<uint32_t*>(lanes_smem);                 // 277 thresholds (1120 bytes reserved)
+    uint32_t* totals = bump + 280;                                            // this CTA's counts, index bin + 1
+    uint16_t* hist = reinterpret_cast<uint16_t*>(totals + 256);               // [warp][row][lane]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kColumn16 = kLaneRows * 32 * 2 / 16;                        // 16-byte pieces of a warp's counters
+    uint4* mine4 = reinterpret_cast<uint4*>(hist + (size_t)warp * kLaneRows * 32);
+    uint16_t* mine = hist + (size_t)warp * kLaneRows * 32 + lane;
+    char* col = reinterpret_cast<char*>(mine);
+    bool ok = true;
+    for (int i = threadIdx.x; i < 277; i += blockDim.x) {
+        const uint32_t t = bump_at[i];
+        bump[i] = t;
+        // binade i - 149 is normal from i = 23 on; its patterns start at (i - 22) << 23
+        if (i >= 23 && t < (((uint32_t)(i - 22) << 23) | 0x007FFF00u)) ok = false;
+    }
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) totals[i] = 0u;
+    for (int i = lane; i < kColumn16; i += 32) mine4[i] = make_uint4(0u, 0u, 0u, 0u);
+    const bool fast = __syncthreads_and(ok ? 1 : 0) != 0;
+    constexpr int V = 16 / (int)sizeof(T);
+    const int64_t nv = n / V, stride = (int64_t)gridDim.x * blockDim.x;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    if (blockIdx.x == 0 && threadIdx.x < (int)(n - nv * V))                   // fewer than V tail elements
+        lane_count_exact(totals, abs_f32_bits<T>(x[nv * V + threadIdx.x]), bump);
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    bool more = true;
+    while (more) {
+        // two register buffers take turns: the loads of the next kLaneUnroll vectors are under way while this batch is
+        // counted (no copy between the buffers: an instruction that reads a loaded register waits for the load)
+        if (i < nv) {
+            uint4 a[kLaneUnroll], b[kLaneUnroll];
+            auto load = [&](uint4(&v)[kLaneUnroll], int64_t at0) {
+#pragma unroll
+                for (int u = 0; u < kLaneUnroll; ++u) {
+                    const int64_t at = at0 + u * stride;
+                    v[u] = at < nv ? __ldcs(xv + at) : make_uint4(0u, 0u, 0u, 0u);  // zeros are not counted
+                }
+            };
+            auto count = [&](const uint4(&v)[kLaneUnroll]) { lane_count_batch<T>(col, totals, v, bump, fast); };
+            const int64_t step = kLaneUnroll * stride;
+            int done = 0;
+            load(a, i);
+            while (true) {
+                const bool has_b = i + step < nv && done + kLaneUnroll < epoch_vectors;
+                if (has_b) load(b, i + step);
+                count(a);
+                done += kLaneUnroll;
+                i += step;
+                if (!has_b) break;
+                const bool has_a = i + step < nv && done + kLaneUnroll < epoch_vectors;
+                if (has_a) load(a, i + step);
+                count(b);
+                done += kLaneUnroll;
+                i += step;
+                if (!has_a) break;
+            }
+        }
+        more = __syncthreads_or(i < nv ? 1 : 0) != 0;        // also: every lane's counters are final for this round
+        for (int row = 1; row < kLaneRows; ++row) {
+            const uint32_t c = __reduce_add_sync(0xFFFFFFFFu, (uint32_t)mine[row * 32]);
+            if (lane == (row & 31) && c) atomicAdd(totals + kLaneFirstField + row, c);     // field f is bin f - 1, index f
+        }
+        __syncwarp();
+        if (more)
+            for (int k = lane; k < kColumn16; k += 32) mine4[k] = make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads();
+        for (int b = threadIdx.x; b < kBins; b += blockDim.x) {
+            if (totals[b + 1]) atomicAdd(counts + b, (unsigned long long)totals[b + 1]);
+            totals[b + 1] = 0u;
+        }
+        __syncthreads();                                     // the exact rule adds to `totals` at any time of the next round
     }
 }
 
@@ -184,6 +358,31 @@ int vq_exp_histogram(const void* in, int dtype, int64_t n, const vq_exp_tables* 
     VQ_CUDA(cudaMemsetAsync(counts, 0, kBins * sizeof(unsigned long long), st));
     const int vec = ((uintptr_t)in % 16 == 0) ? 1 : 0;
     const int V = dtype == VQ_F32 ? 4 : 8;
+    // large aligned tensors: a column of counters per lane (VOYAGER_B200_HISTOGRAM=match keeps the warp-vote kernel)
+    const char* form = getenv("VOYAGER_B200_HISTOGRAM");
+    if (vec && n >= (1ll << 18) && (int)kLaneSmem <= vq_max_smem_optin() && !(form && !strcmp(form, "match"))) {
+        const int64_t want = (n / V + kLaneThreads - 1) / kLaneThreads;
+        // a 16-bit counter holds what a lane sees between two flushes (VOYAGER_B200_HISTOGRAM_FLUSH_EVERY, tests: fewer vectors)
+        int epoch = 65528 / V / kLaneUnroll * kLaneUnroll;
+        if (const char* e = getenv("VOYAGER_B200_HISTOGRAM_FLUSH_EVERY")) {
+            const int v = atoi(e) / kLaneUnroll * kLaneUnroll;
+            if (v >= kLaneUnroll && v < epoch) epoch = v;
+        }
+        const int blocks = (int)(want < vq_sm_count() ? want : vq_sm_count());
+        if (dtype == VQ_F32) {
+            auto kern = exp_histogram_lanes_kernel<float>;
+            VQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLaneSmem));
+            kern<<<blocks, kLaneThreads, kLaneSmem, st>>>(reinterpret_cast<const float*>(in), n, exp->bump_at, counts, epoch);
+        } else {
+            auto kern = exp_histogram_lanes_kernel<bf16_t>;
+            VQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLaneSmem));
+            kern<<<blocks, kLaneThreads, kLaneSmem, st>>>(reinterpret_cast<const bf16_t*>(in), n, exp->bump_at, counts, epoch);
+        }
+        VQ_LAUNCH_CHECK("exp_histogram_lanes_kernel");
+        exp_histogram_add_kernel<<<1, 256, 0, st>>>(counts, histogram);
+        VQ_LAUNCH_CHECK("exp_histogram_add_kernel");
+        return 0;
+    }
     const int blocks = stream_blocks(vec ? (n + V - 1) / V : n, kHistThreads);
     if (dtype == VQ_F32)
         exp_histogram_kernel<float><<<blocks, kHistThreads, 0, st>>>(reinterpret_cast<const float*>(in), n, exp->bump_at, counts, vec);
