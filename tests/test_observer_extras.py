@@ -175,14 +175,15 @@ def test_group_affine_fake_quantize_matches_oracle(dtype, shape, axis, block, qm
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("block", [32, 64, 128, 256, 512])
-@pytest.mark.parametrize("form", ["held", "sweeps"])
+@pytest.mark.parametrize("form", ["default", "held", "sweeps"])
 def test_group_affine_blocks_held_in_registers_and_extreme_values(dtype, block, form, monkeypatch):
     """Block sizes that take the kernel which keeps a block in registers and multiplies by a reciprocal where that
     gives the same quotient, against the two-sweep form and the oracle: blocks of tiny (the checked division), huge,
     zero, constant, infinite and NaN values, negative-only and positive-only blocks, a range that overflows."""
     from voyager_compiler_b200 import fake_quantize as fq
-    if form == "sweeps":
-        monkeypatch.setenv("VOYAGER_B200_GROUP_AFFINE", "sweeps")
+    # default: bf16 blocks in packed bf16x2 arithmetic; "held": the fp32-register form for bf16 too; "sweeps": two sweeps
+    if form != "default":
+        monkeypatch.setenv("VOYAGER_B200_GROUP_AFFINE", form)
     g = torch.Generator().manual_seed(block)
     rows, K = 96, 2048
     x = torch.randn(rows, K, generator=g) * torch.logspace(-3, 3, rows).unsqueeze(1)
@@ -201,7 +202,7 @@ def test_group_affine_blocks_held_in_registers_and_extreme_values(dtype, block, 
     x[15, :40] = torch.tensor([1e-19, -1e-19, 8.7e-19, 1e-18] * 10)    # around 2^-60
     x[16] *= 1e-17
     x = x.to(dtype)
-    for qmin, qmax in ((0.0, 15.0), (-128.0, 127.0)):
+    for qmin, qmax in ((0.0, 15.0), (-128.0, 127.0), (-8.0, 7.0), (0.0, 255.0), (-7.0, 119.0), (1.0, 3.0), (-64.0, -2.0)):
         sf, zp, y = fq.group_affine_fake_quantize(x.cuda(), -1, block, qmin, qmax, None)
         sf_ref, zp_ref, y_ref = vo.group_affine_fake_quantize(x, -1, block, qmin, qmax, None)
         assert _same(sf, sf_ref) and _same(zp, zp_ref) and _same(y, y_ref)

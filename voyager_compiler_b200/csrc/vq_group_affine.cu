@@ -214,7 +214,7 @@ struct BlockQuotient<bf16_t> {
 
 // Blocks of exactly 4 * G 16-byte pieces, K a multiple of the block: see the head of the file.
 template <typename T>
-__global__ void __launch_bounds__(256) group_affine_held_kernel(const GroupAffineParams p) {
+__global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2) group_affine_held_kernel(const GroupAffineParams p) {
     constexpr int V = Vec<T>::N;
     const T* x = reinterpret_cast<const T*>(p.in);
     T* out = reinterpret_cast<T*>(p.out);
@@ -267,8 +267,12 @@ __global__ void __launch_bounds__(256) group_affine_held_kernel(const GroupAffin
                 rnd_pair<T>(a, c, pk);
                 fma_pair(a, c, 1.0f, zp);                  // t + zp (the product with one is exact)
                 rnd_pair<T>(a, c, pk);
-                a = min_nan(max_nan(rintf(a), lo), hi);    // keeps a NaN, as torch.clamp does
-                c = min_nan(max_nan(rintf(c), lo), hi);
+                a = rintf(a);
+                c = rintf(c);
+                a = (a < lo) ? lo : a;                     // comparisons keep a NaN and the sign of a zero, as torch.clamp does
+                c = (c < lo) ? lo : c;
+                a = (a > hi) ? hi : a;
+                c = (c > hi) ? hi : c;
                 fma_pair(a, c, 1.0f, nzp);                 // q - zp
                 rnd_pair<T>(a, c, pk);
                 mul_pair(a, c, sf);
@@ -281,6 +285,133 @@ __global__ void __launch_bounds__(256) group_affine_held_kernel(const GroupAffin
                 if (sizeof(T) == 2) __stcs(reinterpret_cast<uint4*>(dst), make_uint4(w[0], w[1], w[(V / 2) > 2 ? 2 : 0], w[(V / 2) > 3 ? 3 : 0]));
                 else v[k].store(dst);
             }
+        }
+    }
+}
+
+// ---- bf16 blocks in packed arithmetic -----------------------------------------------------------------------------
+// After the quotient every step of the expression is one bf16 operation on bf16 operands, so it can run on both
+// halves of a 32-bit word at once with the same results: add / sub / mul.rn.bf16x2 round the exact result once, as
+// the fp32 operation followed by the conversion does (a sum of two bf16 numbers that does not fit fp32 is further
+// than 2^16 ulps from any bf16 rounding boundary; a product always fits).  Three things need care:
+//   * clamp(round(t)) is computed as round(clamp(t)): the same for integer bounds;
+//   * round to integer: for quant_max - quant_min <= 126 by adding and subtracting an even M with 128 <= q + M <= 255
+//     (bf16 numbers in [128, 256) are the integers, ties go to the even one, M even keeps the parity), then the sign
+//     of t is put back (a zero result keeps the sign of what was rounded, as rint does); otherwise through fp32;
+//   * a negative zero in front of a lower bound of +0 would lose its sign in max(): without a scale table t is never
+//     negative when quant_min is 0 (x >= min gives x / sf + zp >= 0 after the monotone roundings), so this kernel is
+//     used without a table and with quant_min <= 0 < quant_max or quant_min > 0 only.
+__device__ __forceinline__ uint32_t bf2_min_nan(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf2_max_nan(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t u16x2_min(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf2_both(float v) {       // v is a bf16 number: its pattern in both halves
+    const uint32_t h = __float_as_uint(v) >> 16;
+    return h | (h << 16);
+}
+
+__global__ void __launch_bounds__(256, 4) group_affine_packed_kernel(const GroupAffineParams p, float magic) {
+    const uint4* x = reinterpret_cast<const uint4*>(p.in);
+    uint4* out = reinterpret_cast<uint4*>(p.out);
+    const int G = p.lanes;
+    const int lane = threadIdx.x & 31, sub = lane & (G - 1);
+    const uint32_t gmask = (G == 32) ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+    const int64_t groups = ((int64_t)gridDim.x * blockDim.x) / G;
+    const int64_t rounds = (p.n_blocks + groups - 1) / groups;
+    const int64_t g0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const uint32_t lo2 = bf2_both(p.qmin), hi2 = bf2_both(p.qmax), m2 = bf2_both(magic);
+    const int per_block = p.block / 8;                   // 16-byte pieces of a block
+    for (int64_t r = 0; r < rounds; ++r) {               // all lanes of a warp stay in the loop together
+        const int64_t b = g0 + r * groups;
+        const bool live = b < p.n_blocks;
+        const uint4* src = x + (live ? b : 0) * per_block + sub;
+        uint32_t w[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 t = __ldcs(src + k * G);
+            w[4 * k] = t.x; w[4 * k + 1] = t.y; w[4 * k + 2] = t.z; w[4 * k + 3] = t.w;
+        }
+        // extrema of both halves, and the smallest non-zero magnitude as a 16-bit key (|h| - 1, a zero wraps to 0xFFFF)
+        uint32_t mn2 = w[0], mx2 = w[0], key = 0xFFFFFFFFu;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            mn2 = bf2_min_nan(mn2, w[k]);
+            mx2 = bf2_max_nan(mx2, w[k]);
+            key = u16x2_min(key, (((w[k] & 0x7FFF7FFFu) | 0x80008000u) - 0x00010001u) ^ 0x80008000u);
+        }
+        float mn = min_nan(__uint_as_float(mn2 << 16), __uint_as_float(mn2 & 0xFFFF0000u));
+        float mx = max_nan(__uint_as_float(mx2 << 16), __uint_as_float(mx2 & 0xFFFF0000u));
+        uint32_t smallest = min(key & 0xFFFFu, key >> 16);
+        for (int o = G >> 1; o > 0; o >>= 1) {
+            mn = min_nan(mn, __shfl_xor_sync(gmask, mn, o));
+            mx = max_nan(mx, __shfl_xor_sync(gmask, mx, o));
+            smallest = min(smallest, __shfl_xor_sync(gmask, smallest, o));
+        }
+        if (mn != mn || mx != mx) mn = mx = __uint_as_float(0x7FC00000u);
+        float sf = rnd<bf16_t>(__fdiv_rn(rnd<bf16_t>(__fsub_rn(mx, mn)), p.qrange));
+        sf = (sf > 0.0f) ? sf : 1.0f;
+        const float zp = rnd<bf16_t>(__fadd_rn(rnd<bf16_t>(__fdiv_rn(-mn, sf)), p.qmin));
+        if (live && sub == 0) {
+            store_one<bf16_t>(reinterpret_cast<bf16_t*>(p.scale) + b, sf);
+            store_one<bf16_t>(reinterpret_cast<bf16_t*>(p.zero_point) + b, zp);
+        }
+        // x / sf as a product: sf in [2^-63, 2^63] and no element of the block below 2^-60 other than zeros
+        const uint32_t sb = __float_as_uint(sf), ex = (sb >> 23) & 0xFFu;
+        const bool by_product = ex >= 64u && ex <= 190u && smallest >= 0x217Fu;
+        float y;
+        asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(sf));
+        const uint32_t sf2 = bf2_both(sf), zp2 = bf2_both(zp);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float a = __uint_as_float(w[k] << 16), c = __uint_as_float(w[k] & 0xFFFF0000u);
+            if (by_product) {                              // the same for the whole block
+                mul_pair(a, c, y);
+            } else {
+                a = __fdiv_rn(a, sf);
+                c = __fdiv_rn(c, sf);
+            }
+            uint32_t t;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(t) : "f"(c), "f"(a));
+            t = bf2_min_nan(bf2_max_nan(bf2_add(t, zp2), lo2), hi2);
+            if (magic != 0.0f) {
+                t = bf2_sub(bf2_add(t, m2), m2) | (t & 0x80008000u);
+            } else {
+                a = rintf(__uint_as_float(t << 16));
+                c = rintf(__uint_as_float(t & 0xFFFF0000u));
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(t) : "f"(c), "f"(a));
+            }
+            w[k] = bf2_mul(bf2_sub(t, zp2), sf2);
+        }
+        if (live) {
+            uint4* dst = out + b * per_block + sub;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) __stcs(dst + k * G, make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]));
         }
     }
 }
@@ -316,8 +447,22 @@ extern "C" int vq_group_affine_fake_quantize(const void* in, int dtype, int64_t 
     // the block held in registers: exactly four pieces per lane and rows of whole blocks (VOYAGER_B200_GROUP_AFFINE=sweeps: never)
     const char* form = getenv("VOYAGER_B200_GROUP_AFFINE");
     const bool held = p.vec && K % block == 0 && chunks == 4ll * lanes && !(form && !strcmp(form, "sweeps"));
-    if (held) {
-        if (dtype == VQ_F32) group_affine_held_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+    // bf16 in packed arithmetic: integer bounds of at most 256 in magnitude, no scale table, the zero not an upper bound
+    const bool packed = held && dtype == VQ_BF16 && !scale_table && quant_min == (double)(int64_t)quant_min &&
+                        quant_max == (double)(int64_t)quant_max && quant_min >= -256.0 && quant_max <= 256.0 && quant_max > 0.0 &&
+                        !(form && !strcmp(form, "held"));
+    if (packed) {
+        // round to integer by an even M with 128 <= quant_min + M and quant_max + M <= 255; 0: through fp32
+        double magic = 0.0;
+        if (quant_max - quant_min <= 126.0) {
+            magic = 128.0 - quant_min;
+            if ((int64_t)magic & 1) magic += 1.0;
+        }
+        const int64_t resident = (int64_t)vq_sm_count() * 4;                  // four CTAs of this kernel fit an SM
+        group_affine_packed_kernel<<<(int)(want < resident ? want : resident), threads, 0, (cudaStream_t)stream>>>(p, (float)magic);
+    } else if (held) {
+        const int64_t resident = (int64_t)vq_sm_count() * 4;
+        if (dtype == VQ_F32) group_affine_held_kernel<float><<<(int)(want < resident ? want : resident), threads, 0, (cudaStream_t)stream>>>(p);
         else group_affine_held_kernel<bf16_t><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
     } else {
         if (dtype == VQ_F32) group_affine_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
