@@ -264,6 +264,12 @@ VQ_API int vq_lcq_accumulate(const void* x, int dtype, int64_t n, int64_t block,
                              int64_t n_weights, const float* edges, int bins, double* weight, double* total,
                              double* square, void* stream);
 
+/* The 65 536-entry bf16 table a fitted codebook is used through: table[p] = the entry nearest to the value of bf16
+ * pattern p clamped to [min(entries), max(entries)], distances in fp32, the first of equal distances, entry 0 for a NaN
+ * pattern; `entries` are n fp32 numbers on the device (1 <= n <= 8192), rounded to bf16 in the table.
+ * Replaces `codebook_qmap`, src/voyager_compiler/quantization/lcq.py:270-291. */
+VQ_API int vq_codebook_qmap(const float* entries, int n, uint16_t* table, void* stream);
+
 /* One microscaling block of the GPTQ column walk, all rows at once
  * (src/voyager_compiler/quantization/gptq.py:238-259 with block_scale, :79-137): for every row r of
  * work[rows, ld] (fp32) the scale s_r = where(t > 0, t, 1) with t = scale_table(amax_r / quant_max) over the

@@ -100,3 +100,38 @@ def test_cpu_tensors_rejected():
     from voyager_compiler_b200 import lcq
     with pytest.raises(RuntimeError):
         lcq.Histogram(-7.0, 7.0).add(torch.zeros(8), torch.ones(8))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("entries", [
+    [-7.0, -5.0, -3.0, -2.0, -1.0, 0.0, 1.0, 2.0, 3.0, 4.0, 5.0, 7.0],
+    [0.0],
+    [3.0, -1.0, 2.0, 2.0, -6.0, 0.5, 0.5],                     # unsorted, repeated entries: the first of equal distances
+    [-0.0, 0.0, 1e-40, 1.0, 3.3895e38],                        # signed zeros, a subnormal, the largest bf16
+    [float("-inf"), -1.0, 1.0, float("inf")],
+    [-1.0, float("nan"), 1.0],                                 # a NaN entry poisons min / max: every pattern takes it
+    "random16", "random256",
+])
+def test_codebook_qmap_on_the_device_is_upstreams_table(entries):
+    """``lcq.codebook_qmap`` (one kernel) against upstream's tensor expression (lcq.py:270-291) evaluated by torch on
+    the CPU, for all 65 536 patterns, bit for bit (NaN == NaN); entries given as a list and as a device tensor."""
+    from voyager_compiler_b200 import lcq
+    if isinstance(entries, str):
+        g = torch.Generator().manual_seed(len(entries))
+        entries = (torch.randn(int(entries[6:]), generator=g) * 4).tolist()
+    cb = torch.tensor(entries, dtype=torch.float32)
+    every = torch.arange(2 ** 16, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).float()
+    index = (every.clamp(cb.min(), cb.max()).unsqueeze(-1) - cb).abs().argmin(-1)
+    want = cb[index].to(torch.bfloat16).view(torch.int16)
+    for given in (entries, cb.cuda()):
+        got = lcq.codebook_qmap(given, "cuda")
+        assert got.dtype == torch.bfloat16 and got.shape == (65536,) and got.is_cuda
+        g16 = got.cpu().view(torch.int16)
+        same = (g16 == want) | (torch.isnan(got.cpu().float()) & torch.isnan(want.view(torch.bfloat16).float()))
+        assert bool(same.all()), int((~same).sum())
+
+
+def test_codebook_qmap_rejects_cpu_devices():
+    from voyager_compiler_b200 import lcq
+    with pytest.raises(RuntimeError):
+        lcq.codebook_qmap([0.0, 1.0], "cpu")

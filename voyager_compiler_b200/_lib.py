@@ -100,6 +100,7 @@ def _load():
         "vq_row_codebook": [vp, ci, i64, i64, vp, ci, ci, vp, vp, vp, C.c_size_t, vp],
         "vq_row_quantile": [vp, ci, i64, i64, ci, vp, vp],
         "vq_lcq_accumulate": [vp, ci, i64, i64, C.c_double, vp, i64, vp, ci, vp, vp, vp, vp],
+        "vq_codebook_qmap": [vp, ci, vp, vp],
         "vq_gptq_block": [vp, i64, i64, i64, ci, vp, i64, vp, ci, C.c_double, vp, vp, vp, i64, vp, vp, vp],
         "vq_conv_patches": [vp, ci, i64, i64, i64, i64, i64, i64, i64, i64, ci, ci, ci, ci, ci, ci, ci, ci,
                             vp, i64, i64, i64, i64, i64, vp, i64, vp],

@@ -89,7 +89,63 @@ __global__ void __launch_bounds__(kLcqThreads) lcq_accumulate_kernel(const __gri
     }
 }
 
+// The table a fitted codebook is used through (lcq.py:270-291): for every bf16 pattern the entry nearest to its value
+// clamped to the codebook's range, distances taken in fp32 as upstream's tensor expression does, the first of equal
+// distances, entry 0 for a NaN.  One thread per pattern, the entries in shared memory.
+constexpr int kQmapThreads = 256;
+__global__ void __launch_bounds__(kQmapThreads) codebook_qmap_kernel(const float* __restrict__ entries, int n, uint16_t* __restrict__ table) {
+    extern __shared__ float cb[];
+    __shared__ float s_lo, s_hi;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) cb[i] = entries[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // minimum and maximum as torch.min / torch.max give them: a NaN entry makes both NaN
+        float lo = cb[0], hi = cb[0];
+        bool nan = cb[0] != cb[0];
+        for (int i = 1; i < n; ++i) {
+            nan |= cb[i] != cb[i];
+            lo = fminf(lo, cb[i]);
+            hi = fmaxf(hi, cb[i]);
+        }
+        s_lo = nan ? __uint_as_float(0x7FC00000u) : lo;
+        s_hi = nan ? __uint_as_float(0x7FC00000u) : hi;
+    }
+    __syncthreads();
+    const uint32_t pat = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pat >= 65536u) return;
+    const float x = __uint_as_float(pat << 16);
+    int best = 0;
+    if (x == x) {
+        // clamp(x, lo, hi) = min(max(x, lo), hi); a NaN bound passes through as torch.clamp does and ends at entry 0
+        float v = (x < s_lo) ? s_lo : x;
+        v = (v > s_hi) ? s_hi : v;
+        if (s_lo != s_lo) v = s_lo;
+        float dmin = fabsf(__fsub_rn(v, cb[0]));
+        bool found_nan = dmin != dmin;
+        for (int j = 1; j < n && !found_nan; ++j) {
+            const float d = fabsf(__fsub_rn(v, cb[j]));
+            if (d != d) {                                  // argmin takes the first NaN for the minimum
+                best = j;
+                found_nan = true;
+            } else if (d < dmin) {
+                dmin = d;
+                best = j;
+            }
+        }
+    }
+    table[pat] = (uint16_t)(f32_to_bf16_bits(cb[best]));
+}
+
 }  // namespace
+
+extern "C" int vq_codebook_qmap(const float* entries, int n, uint16_t* table, void* stream) {
+    const char* name = "vq_codebook_qmap";
+    VQ_REQUIRE(n >= 1 && n <= 8192, "%s: between 1 and 8192 entries", name);
+    VQ_REQUIRE(entries && table, "%s: null pointer", name);
+    codebook_qmap_kernel<<<65536 / kQmapThreads, kQmapThreads, (size_t)n * sizeof(float), (cudaStream_t)stream>>>(entries, n, table);
+    VQ_LAUNCH_CHECK("codebook_qmap_kernel");
+    return 0;
+}
 
 extern "C" int vq_lcq_accumulate(const void* x, int dtype, int64_t n, int64_t block, double quant_max, const float* weights,
                                  int64_t n_weights, const float* edges, int bins, double* weight, double* total,

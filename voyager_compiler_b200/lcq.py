@@ -57,6 +57,25 @@ def accumulate_moments(weight, total, square, quant_min, quant_max, x, block, un
             weight.data_ptr(), total.data_ptr(), square.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream), "lcq")
 
 
+def codebook_qmap(entries, device=None) -> torch.Tensor:
+    """The bf16 ``[65536]`` lookup table of a codebook on ``device`` (lcq.py:270-291): one launch of
+    ``vq_codebook_qmap`` instead of a ``[65536, n]`` distance matrix; ``entries`` is a sequence of numbers or a tensor
+    (one on the device is used where it lies, so a fit that ends on the GPU does not come back to the host)."""
+    if isinstance(entries, torch.Tensor):
+        dev = torch.device(device) if device is not None else entries.device
+        cb = entries.detach().to(device=dev, dtype=torch.float32).contiguous().reshape(-1)
+    else:
+        dev = torch.device(device if device is not None else "cuda")
+        cb = torch.tensor(list(entries), dtype=torch.float32, device=dev)
+    if dev.type != "cuda":
+        raise RuntimeError("lcq.codebook_qmap: CUDA devices only; there is no CPU path")
+    table = torch.empty(1 << 16, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.vq_codebook_qmap(cb.data_ptr(), cb.numel(), table.data_ptr(),
+                                             torch.cuda.current_stream(dev).cuda_stream), "codebook_qmap")
+    return table
+
+
 class Histogram:
     """Weighted moments of a tensor's normalised values per bin: total weight, weighted sum, weighted sum of
     squares (fp64), between ``quant_min - 0.5`` and ``quant_max + 0.5``; same fields and methods as upstream's
