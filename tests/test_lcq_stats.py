@@ -135,3 +135,34 @@ def test_codebook_qmap_rejects_cpu_devices():
     from voyager_compiler_b200 import lcq
     with pytest.raises(RuntimeError):
         lcq.codebook_qmap([0.0, 1.0], "cpu")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("block,channels,energy_len", [(4, 64, 64), (8, 96, 0), (64, 1024, 1024), (128, 384, 384), (64, 192, 192),
+                                                      (24, 96, 96), (256, 512, 0), (64, 192, 1)])
+def test_statistics_pass_for_block_sizes_and_weight_layouts(dtype, block, channels, energy_len):
+    """Blocks of 4 ... 128 elements go to the kernel in which a group of lanes takes a block (weights read four at a time
+    when the channel count allows), other sizes and unaligned tensors to the one in which a thread takes a block; both
+    against the oracle: the same bins hit, equal counts without weights, fp64 sums equal up to the order of addition.
+    Includes an all-zero block, a NaN and huge values."""
+    from voyager_compiler_b200 import lcq
+    g = torch.Generator().manual_seed(block * 1000 + channels)
+    x = torch.randn(768, channels, generator=g) * torch.logspace(-2, 2, 768).unsqueeze(1)    # 768 and 640 rows: whole blocks
+    x[3] = 0.0
+    x[5, 7] = 3e38
+    x = x.to(dtype)
+    energy = None if energy_len == 0 else torch.rand(energy_len, generator=g) + 0.1
+    for xs in (x, x.reshape(-1)[block:block + 640 * channels].reshape(640, channels)):   # the second starts `block` elements in
+        want = vo.lcq_accumulate(None, xs, block, 7.0, -7.0, energy, 4001)
+        h = lcq.Histogram(-7.0, 7.0)
+        e_dev = None if energy is None else energy.cuda()
+        if energy_len == 192:                                # weights that do not start on a 16-byte boundary: read one by one
+            e_dev = torch.cat([torch.zeros(1), energy]).cuda()[1:]
+        h.accumulate(xs.cuda(), block, 7.0, e_dev)
+        got = [h.weight.cpu(), h.total.cpu(), h.square.cpu()]
+        assert torch.equal(got[0] != 0, want[0] != 0)
+        if energy is None:
+            assert torch.equal(got[0], want[0])
+        for a, b in zip(got, want):
+            assert torch.allclose(a, b, rtol=1e-11, atol=1e-9 * float(b.abs().max()))

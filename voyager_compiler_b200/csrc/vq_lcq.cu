@@ -8,7 +8,7 @@
 
 namespace {
 
-constexpr int kLcqThreads = 256;
+constexpr int kLcqThreads = 512;
 constexpr float kLcqEps = 1e-12f;                                // lcq.py:34, as fp32
 
 struct LcqParams {
@@ -76,6 +76,85 @@ __global__ void __launch_bounds__(kLcqThreads) lcq_accumulate_kernel(const __gri
                 if (p.n_weights) w = p.weights[c];
                 if (p.n_weights > 1 && ++c == p.n_weights) c = 0;
                 add(__fdiv_rn(load_one<T>(xb + j), scale), w);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.bins; i += blockDim.x) {
+        if (sw[i] != 0.0 || st[i] != 0.0 || ss[i] != 0.0) {
+            atomicAdd(p.weight + i, sw[i]);
+            atomicAdd(p.total + i, st[i]);
+            atomicAdd(p.square + i, ss[i]);
+        }
+    }
+}
+
+// Blocks of 4 * G elements (G a power of two up to 32, so blocks of 4 ... 128): G lanes take a block, four
+// consecutive elements each (one 16- or 8-byte load, coalesced over the warp), the block's maximum goes round the
+// group by shuffles, and every lane bins its own four quotients.  The loads of a warp are whole lines and a lane has
+// 4 elements in flight instead of a whole block read one element at a time.
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float* v);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float* v) {
+    const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<bf16_t>(const bf16_t* p, float* v) {
+    const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xFFFF0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xFFFF0000u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLcqThreads) lcq_accumulate_group_kernel(const __grid_constant__ LcqParams p, int G) {
+    extern __shared__ double sm_moments[];                       // [3][bins] doubles, then bins + 1 floats
+    double* sw = sm_moments;
+    double* st = sw + p.bins;
+    double* ss = st + p.bins;
+    float* edges = reinterpret_cast<float*>(ss + p.bins);
+    for (int i = threadIdx.x; i < 3 * p.bins; i += blockDim.x) sm_moments[i] = 0.0;
+    for (int i = threadIdx.x; i <= p.bins; i += blockDim.x) edges[i] = p.edges[i];
+    __syncthreads();
+    const T* x = reinterpret_cast<const T*>(p.x);
+    const float inv_step = (float)p.bins / (edges[p.bins] - edges[0]);
+    const int lane = threadIdx.x & 31, sub = lane & (G - 1);
+    const uint32_t gmask = (G == 32) ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(G - 1)));
+    const int64_t groups = ((int64_t)gridDim.x * blockDim.x) / G, nblk = p.n / p.block;
+    const int64_t rounds = (nblk + groups - 1) / groups;
+    const int64_t g0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const bool w4 = p.n_weights > 1 && p.n_weights % 4 == 0 && (reinterpret_cast<uintptr_t>(p.weights) & 15) == 0;
+    for (int64_t r = 0; r < rounds; ++r) {               // all lanes of a warp stay in the loop together
+        const int64_t b = g0 + r * groups;
+        const bool live = b < nblk;
+        const int64_t e0 = (live ? b : 0) * p.block + sub * 4;
+        float v[4], w[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+        load4<T>(x + e0, v);
+        if (p.n_weights == 1) {
+            w[0] = w[1] = w[2] = w[3] = p.weights[0];
+        } else if (p.n_weights > 1) {
+            const int64_t c = e0 % p.n_weights;
+            if (w4) {                                     // e0 and the channel count are multiples of 4: no wrap inside
+                const float4 t = __ldg(reinterpret_cast<const float4*>(p.weights + c));
+                w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) w[k] = p.weights[(c + k) % p.n_weights];
+            }
+        }
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        for (int o = G >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+        const float scale = __fdiv_rn(fmaxf(amax, kLcqEps), p.qmax);
+        if (live) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float q = __fdiv_rn(v[k], scale);
+                const int bin = bin_of(edges, p.bins + 1, q, inv_step);
+                const double dv = (double)q, dw = (double)w[k];
+                atomicAdd(&sw[bin], dw);
+                atomicAdd(&st[bin], dw * dv);
+                atomicAdd(&ss[bin], dw * dv * dv);
             }
         }
     }
@@ -164,15 +243,30 @@ extern "C" int vq_lcq_accumulate(const void* x, int dtype, int64_t n, int64_t bl
     p.x = x; p.n = n; p.block = block; p.qmax = (float)quant_max;
     p.weights = weights; p.n_weights = n_weights; p.edges = edges; p.bins = bins;
     p.weight = weight; p.total = total; p.square = square;
-    const int64_t items = block ? n / block : n;
+    // blocks of 4, 8, ... 128 elements of an aligned tensor: a group of lanes per block
+    const int64_t esize = dtype == VQ_F32 ? 4 : 2;
+    int G = 0;
+    if (block >= 4 && block <= 128 && (block & (block - 1)) == 0 && (uintptr_t)x % (4 * esize) == 0) G = (int)(block / 4);
+    const int64_t items = G ? n / 4 : (block ? n / block : n);      // what a thread takes per round
     const int sms = vq_sm_count();
-    const int per_sm = smem > 100 * 1024 ? 2 : 4;
+    const int per_sm = smem > 100 * 1024 ? 2 : (smem > 50 * 1024 ? 3 : 4);
     int64_t want = (items + kLcqThreads - 1) / kLcqThreads;
-    // a CTA pays for clearing and flushing its arrays: at least a few thousand items each
-    const int64_t by_work = (items + 4095) / 4096;
+    // a CTA pays for clearing and flushing its arrays: at least some tens of thousands of elements each
+    const int64_t by_work = (n + 32767) / 32768;
     if (want > by_work) want = by_work;
     const int blocks = (int)(want < 1 ? 1 : (want > (int64_t)sms * per_sm ? (int64_t)sms * per_sm : want));
     cudaStream_t st = (cudaStream_t)stream;
+    if (G) {
+        if (dtype == VQ_F32) {
+            VQ_CUDA(cudaFuncSetAttribute(lcq_accumulate_group_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            lcq_accumulate_group_kernel<float><<<blocks, kLcqThreads, smem, st>>>(p, G);
+        } else {
+            VQ_CUDA(cudaFuncSetAttribute(lcq_accumulate_group_kernel<bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            lcq_accumulate_group_kernel<bf16_t><<<blocks, kLcqThreads, smem, st>>>(p, G);
+        }
+        VQ_LAUNCH_CHECK("lcq_accumulate_group_kernel");
+        return 0;
+    }
     if (dtype == VQ_F32) {
         VQ_CUDA(cudaFuncSetAttribute(lcq_accumulate_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         lcq_accumulate_kernel<float><<<blocks, kLcqThreads, smem, st>>>(p);
