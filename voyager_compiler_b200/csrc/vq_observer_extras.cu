@@ -88,11 +88,11 @@ __global__ void __launch_bounds__(kHistThreads) exp_histogram_kernel(const T* __
 }
 
 // The same histogram for large aligned tensors, without any exchange between lanes: every lane of every warp owns a
-// column of 16-bit counters in shared memory (32 lanes per row: a warp's update touches 32 different counters, two
-// per bank word, whatever the rows are), so an element costs a few integer operations for its row and one load / add /
-// store; two elements go together (both loads, then both stores, the second one higher when the rows are the same).
+// column of 16-bit counters in shared memory, two to a 32-bit word and the words of a warp's 32 lanes in 32 different
+// banks, so an element costs a few integer operations for its word and half and one `red.shared.add.u32` of 1 or 65 536:
+// no lane ever meets another one's word, nothing is returned and nothing waits.
 // A column has 128 rows: row r counts exponent field 64 + r, that is bin 63 + r (2^-62 <= |x| < 2^65 covers what tensors
-// hold), row 0 collects the zeros.  Everything else takes the exact rule element by element, into the CTA's totals by
+// hold), row 0 collects the zeros; rows 2j and 2j + 1 share word j.  Everything else takes the exact rule element by element, into the CTA's totals by
 // shared-memory atomics: a batch of vectors with an element outside that window, a non-zero subnormal, an infinity or
 // NaN, or one of the 256 patterns at the top of a binade, which alone have to look at the thresholds (one running
 // maximum and two running minima over the batch tell).  The prologue checks what that relies on (`fast`: every
@@ -110,19 +110,21 @@ __device__ __noinline__ void lane_count_exact(uint32_t* totals, uint32_t b, cons
     const int bin = exponent_bin(b, bump);
     if (bin >= 0) atomicAdd(totals + bin + 1, 1u);
 }
-// two elements whose rows are at byte offsets o0 and o1 of the column
-__device__ __forceinline__ void lane_count_pair(char* col, uint32_t o0, uint32_t o1) {
-    uint16_t* p0 = reinterpret_cast<uint16_t*>(col + o0);
-    uint16_t* p1 = reinterpret_cast<uint16_t*>(col + o1);
-    const uint32_t c0 = *p0, c1 = *p1;
-    *p0 = (uint16_t)(c0 + 1u);
-    *p1 = (uint16_t)(c1 + 1u + (o0 == o1 ? 1u : 0u));
+// One element, given as its word shifted so that the exponent field sits at bits 14..7 (`f`: fp32 >> 16, the high bf16
+// half >> 16, the low bf16 half as it is; other bits are ignored).  Fields 2j and 2j + 1 share word j - 32 of the lane's
+// column (low and high half); a zero (field 0) is raised to word 0, whose low half no counted field uses (the window
+// starts at field 65).  `col32`: shared-memory address of the column minus 32 words.  The addition returns nothing, so
+// nothing waits for it.
+__device__ __forceinline__ void lane_count_one(uint32_t col32, uint32_t f) {
+    const uint32_t addr = col32 + max(f & 0x7F00u, (kLaneFirstField / 2u) << 8) / 2u;  // (field >> 1) * 128 bytes
+    const uint32_t inc = 1u << ((f >> 3) & 16u);                                        // the field's lowest bit chooses the half
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(inc) : "memory");
 }
 
 // kLaneUnroll vectors of one lane
 template <typename T>
-__device__ __forceinline__ void lane_count_batch(char* col, uint32_t* totals, const uint4 (&v)[kLaneUnroll], const uint32_t* bump,
-                                                 bool fast) {
+__device__ __forceinline__ void lane_count_batch(uint32_t col_addr, uint32_t* totals, const uint4 (&v)[kLaneUnroll],
+                                                 const uint32_t* bump, bool fast) {
     // t: pattern of |x| with the exponent field at bits 30..23 (fp32) or 14..7 (bf16 halves)
     constexpr uint32_t kOne = sizeof(T) == 4 ? (1u << 23) : (1u << 7);
     constexpr uint32_t kFloor = (kLaneFirstField + 1u) * kOne;             // smallest pattern with a row of its own
@@ -147,21 +149,13 @@ __device__ __forceinline__ void lane_count_batch(char* col, uint32_t* totals, co
         }
     }
     if (fast && top < 0xFFFFFF00u && low >= kFloor - 1u && high < kCeil) {
-        // byte offset of a row: (field - 64) * 64, a zero (field 0) raised to row 0
-        constexpr uint32_t kBase = kLaneFirstField * 64u;
 #pragma unroll
         for (int u = 0; u < kLaneUnroll; ++u) {
             const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-            if (sizeof(T) == 4) {
-                uint32_t o[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) o[k] = max((w[k] >> 17) & 0x3FC0u, kBase) - kBase;
-                lane_count_pair(col, o[0], o[1]);
-                lane_count_pair(col, o[2], o[3]);
-            } else {
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    lane_count_pair(col, max((w[k] >> 1) & 0x3FC0u, kBase) - kBase, max((w[k] >> 17) & 0x3FC0u, kBase) - kBase);
+            for (int k = 0; k < 4; ++k) {
+                if (sizeof(T) != 4) lane_count_one(col_addr, w[k]);
+                lane_count_one(col_addr, w[k] >> 16);
             }
         }
     } else {
@@ -188,12 +182,12 @@ __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(co
     extern __shared__ uint4 lanes_smem[];
     uint32_t* bump = reinterpret_cast<uint32_t*>(lanes_smem);                 // 277 thresholds (1120 bytes reserved)
     uint32_t* totals = bump + 280;                                            // this CTA's counts, index bin + 1
-    uint16_t* hist = reinterpret_cast<uint16_t*>(totals + 256);               // [warp][row][lane]
+    uint32_t* hist = totals + 256;                                            // [warp][word][lane], two 16-bit rows per word
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kColumn16 = kLaneRows * 32 * 2 / 16;                        // 16-byte pieces of a warp's counters
-    uint4* mine4 = reinterpret_cast<uint4*>(hist + (size_t)warp * kLaneRows * 32);
-    uint16_t* mine = hist + (size_t)warp * kLaneRows * 32 + lane;
-    char* col = reinterpret_cast<char*>(mine);
+    uint4* mine4 = reinterpret_cast<uint4*>(hist + (size_t)warp * (kLaneRows / 2) * 32);
+    uint32_t* mine = hist + (size_t)warp * (kLaneRows / 2) * 32 + lane;
+    const uint32_t col_addr = (uint32_t)__cvta_generic_to_shared(mine) - (kLaneFirstField / 2u) * 128u;   // minus 32 words
     bool ok = true;
     for (int i = threadIdx.x; i < 277; i += blockDim.x) {
         const uint32_t t = bump_at[i];
@@ -223,7 +217,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(co
                     v[u] = at < nv ? __ldcs(xv + at) : make_uint4(0u, 0u, 0u, 0u);  // zeros are not counted
                 }
             };
-            auto count = [&](const uint4(&v)[kLaneUnroll]) { lane_count_batch<T>(col, totals, v, bump, fast); };
+            auto count = [&](const uint4(&v)[kLaneUnroll]) { lane_count_batch<T>(col_addr, totals, v, bump, fast); };
             const int64_t step = kLaneUnroll * stride;
             int done = 0;
             load(a, i);
@@ -243,9 +237,13 @@ __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(co
             }
         }
         more = __syncthreads_or(i < nv ? 1 : 0) != 0;        // also: every lane's counters are final for this round
-        for (int row = 1; row < kLaneRows; ++row) {
-            const uint32_t c = __reduce_add_sync(0xFFFFFFFFu, (uint32_t)mine[row * 32]);
-            if (lane == (row & 31) && c) atomicAdd(totals + kLaneFirstField + row, c);     // field f is bin f - 1, index f
+        for (int word = 0; word < kLaneRows / 2; ++word) {
+            const uint32_t both = mine[word * 32];
+            const uint32_t c0 = __reduce_add_sync(0xFFFFFFFFu, both & 0xFFFFu), c1 = __reduce_add_sync(0xFFFFFFFFu, both >> 16);
+            if (lane == (word & 31)) {                       // fields 64 + 2 word and 65 + 2 word; field f is bin f - 1, index f
+                if (c0 && word) atomicAdd(totals + kLaneFirstField + 2 * word, c0);         // word 0, low half: the zeros
+                if (c1) atomicAdd(totals + kLaneFirstField + 2 * word + 1, c1);
+            }
         }
         __syncwarp();
         if (more)
