@@ -387,8 +387,9 @@ VQ_API int vq_group_affine_fake_quantize(const void* in, int dtype, int64_t rows
 /* histogram[b] += number of elements of `in` with floor(log2(|x| as fp32)) == b - 126, b = 0..253, as one fp32
  * addition per bin: the observer's exponent histogram, `histogram += torch.histc(floor(log2(|x|)), 254, min=-126,
  * max=127)`, src/voyager_compiler/quantization/fake_quantize.py:369-371.  Zeros, subnormals, infinities and NaNs are
- * not counted.  `exp` holds the fp32 thresholds (bump_at) of the shared-exponent rule; `workspace` is 2032 bytes of
- * device scratch, 8-byte aligned. */
+ * not counted.  `exp` holds the fp32 thresholds (bump_at) of the shared-exponent rule; `workspace` is at least 2032 bytes
+ * of device scratch, 8-byte aligned; with 2040 bytes or more, large tensors finish in the counting launch itself (its last
+ * CTA adds the counts to `histogram`) instead of a launch of their own. */
 VQ_API int vq_exp_histogram(const void* in, int dtype, int64_t n, const vq_exp_tables* exp, float* histogram, void* workspace,
                             size_t workspace_bytes, void* stream);
 

@@ -230,3 +230,22 @@ def test_exponent_histogram_on_ordinary_data(dtype, n):
     assert torch.equal(hist.cpu(), vo.exponent_histogram(x))
     fq.exponent_histogram(x.cuda(), hist)                       # accumulates
     assert torch.equal(hist.cpu(), 2 * vo.exponent_histogram(x))
+
+
+@pytest.mark.gpu
+def test_exponent_histogram_with_the_smallest_workspace_takes_a_launch_for_the_addition():
+    """2032 bytes of workspace leave no room for the ticket by which the counting kernel's last CTA finishes the call:
+    the counts are then added to the histogram by a launch of its own, with the same result."""
+    from voyager_compiler_b200 import _lib
+    from voyager_compiler_b200.qtables import exp_tables
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(1 << 20, generator=g) * 5).cuda()
+    et = exp_tables(torch.float32, 1.0, x.device)
+    want = vo.exponent_histogram(x.cpu())
+    for words in (254, 255, 256):
+        hist = torch.zeros(254, device="cuda")
+        ws = torch.empty(words, dtype=torch.int64, device="cuda")
+        rc = _lib.lib.vq_exp_histogram(x.data_ptr(), _lib.VQ_F32, x.numel(), et.ptr(), hist.data_ptr(), ws.data_ptr(), words * 8,
+                                       torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        assert torch.equal(hist.cpu(), want), words

@@ -178,7 +178,8 @@ __device__ __forceinline__ void lane_count_batch(uint32_t col_addr, uint32_t* to
 template <typename T>
 __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(const T* __restrict__ x, int64_t n,
                                                                               const uint32_t* __restrict__ bump_at,
-                                                                              unsigned long long* __restrict__ counts, int epoch_vectors) {
+                                                                              unsigned long long* __restrict__ counts, int epoch_vectors,
+                                                                              float* __restrict__ histogram) {
     extern __shared__ uint4 lanes_smem[];
     uint32_t* bump = reinterpret_cast<uint32_t*>(lanes_smem);                 // 277 thresholds (1120 bytes reserved)
     uint32_t* totals = bump + 280;                                            // this CTA's counts, index bin + 1
@@ -254,6 +255,20 @@ __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(co
             totals[b + 1] = 0u;
         }
         __syncthreads();                                     // the exact rule adds to `totals` at any time of the next round
+    }
+    // `histogram` given: counts[kBins] is a ticket, and the CTA that draws the last one adds the counts to the histogram
+    // (the one fp32 addition per bin that `histogram += histc(...)` makes) instead of a launch of its own
+    if (histogram) {
+        __shared__ int last;
+        __threadfence();                                     // this CTA's additions to `counts` before its ticket
+        __syncthreads();
+        if (threadIdx.x == 0) last = atomicAdd(counts + kBins, 1ull) == (unsigned long long)gridDim.x - 1ull;
+        __syncthreads();
+        if (last) {
+            __threadfence();
+            for (int b = threadIdx.x; b < kBins; b += blockDim.x)
+                histogram[b] = __fadd_rn(histogram[b], (float)__ldcg(counts + b));
+        }
     }
 }
 
@@ -353,7 +368,8 @@ int vq_exp_histogram(const void* in, int dtype, int64_t n, const vq_exp_tables* 
                "%s: workspace of at least 2032 bytes, 8-byte aligned", name);
     cudaStream_t st = (cudaStream_t)stream;
     unsigned long long* counts = reinterpret_cast<unsigned long long*>(workspace);
-    VQ_CUDA(cudaMemsetAsync(counts, 0, kBins * sizeof(unsigned long long), st));
+    const bool ticket = workspace_bytes >= (kBins + 1) * sizeof(unsigned long long);      // room for the last-CTA ticket
+    VQ_CUDA(cudaMemsetAsync(counts, 0, (kBins + (ticket ? 1 : 0)) * sizeof(unsigned long long), st));
     const int vec = ((uintptr_t)in % 16 == 0) ? 1 : 0;
     const int V = dtype == VQ_F32 ? 4 : 8;
     // large aligned tensors: a column of counters per lane (VOYAGER_B200_HISTOGRAM=match keeps the warp-vote kernel)
@@ -370,15 +386,17 @@ int vq_exp_histogram(const void* in, int dtype, int64_t n, const vq_exp_tables* 
         if (dtype == VQ_F32) {
             auto kern = exp_histogram_lanes_kernel<float>;
             VQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLaneSmem));
-            kern<<<blocks, kLaneThreads, kLaneSmem, st>>>(reinterpret_cast<const float*>(in), n, exp->bump_at, counts, epoch);
+            kern<<<blocks, kLaneThreads, kLaneSmem, st>>>(reinterpret_cast<const float*>(in), n, exp->bump_at, counts, epoch, ticket ? histogram : nullptr);
         } else {
             auto kern = exp_histogram_lanes_kernel<bf16_t>;
             VQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLaneSmem));
-            kern<<<blocks, kLaneThreads, kLaneSmem, st>>>(reinterpret_cast<const bf16_t*>(in), n, exp->bump_at, counts, epoch);
+            kern<<<blocks, kLaneThreads, kLaneSmem, st>>>(reinterpret_cast<const bf16_t*>(in), n, exp->bump_at, counts, epoch, ticket ? histogram : nullptr);
         }
         VQ_LAUNCH_CHECK("exp_histogram_lanes_kernel");
-        exp_histogram_add_kernel<<<1, 256, 0, st>>>(counts, histogram);
-        VQ_LAUNCH_CHECK("exp_histogram_add_kernel");
+        if (!ticket) {
+            exp_histogram_add_kernel<<<1, 256, 0, st>>>(counts, histogram);
+            VQ_LAUNCH_CHECK("exp_histogram_add_kernel");
+        }
         return 0;
     }
     const int blocks = stream_blocks(vec ? (n + V - 1) / V : n, kHistThreads);
