@@ -124,7 +124,7 @@ __device__ __forceinline__ void lane_count_one(uint32_t col32, uint32_t f) {
 // kLaneUnroll vectors of one lane
 template <typename T>
 __device__ __forceinline__ void lane_count_batch(uint32_t col_addr, uint32_t* totals, const uint4 (&v)[kLaneUnroll],
-                                                 const uint32_t* bump, bool fast) {
+                                                 const uint32_t* bump, bool fast, uint32_t top_floor) {
     // t: pattern of |x| with the exponent field at bits 30..23 (fp32) or 14..7 (bf16 halves)
     constexpr uint32_t kOne = sizeof(T) == 4 ? (1u << 23) : (1u << 7);
     constexpr uint32_t kFloor = (kLaneFirstField + 1u) * kOne;             // smallest pattern with a row of its own
@@ -148,7 +148,7 @@ __device__ __forceinline__ void lane_count_batch(uint32_t col_addr, uint32_t* to
             }
         }
     }
-    if (fast && top < 0xFFFFFF00u && low >= kFloor - 1u && high < kCeil) {
+    if (fast && (sizeof(T) == 2 || top - 0xFF800000u < top_floor) && low >= kFloor - 1u && high < kCeil) {
 #pragma unroll
         for (int u = 0; u < kLaneUnroll; ++u) {
             const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
@@ -159,16 +159,24 @@ __device__ __forceinline__ void lane_count_batch(uint32_t col_addr, uint32_t* to
             }
         }
     } else {
+        // a batch with an element that needs the thresholds: that element takes the exact rule, the others stay plain
+        // (a warp with such a batch would otherwise fall far behind the others of its CTA)
+        auto one = [&](uint32_t b, uint32_t f) {             // b: fp32 pattern of |x|, f: as for lane_count_one
+            const bool plain = fast && (b == 0u || (b >= (kLaneFirstField + 1u) << 23 && b < (kLaneFirstField + kLaneRows) << 23)) &&
+                               (b & 0x007FFFFFu) < top_floor;
+            if (plain) lane_count_one(col_addr, f);
+            else lane_count_exact(totals, b, bump);
+        };
 #pragma unroll
         for (int u = 0; u < kLaneUnroll; ++u) {                     // registers only: no indexing by a loop variable
             const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 if (sizeof(T) == 4) {
-                    lane_count_exact(totals, w[k] & 0x7FFFFFFFu, bump);
+                    one(w[k] & 0x7FFFFFFFu, w[k] >> 16);
                 } else {
-                    lane_count_exact(totals, (w[k] << 16) & 0x7FFF0000u, bump);
-                    lane_count_exact(totals, w[k] & 0x7FFF0000u, bump);
+                    one((w[k] << 16) & 0x7FFF0000u, w[k]);
+                    one(w[k] & 0x7FFF0000u, w[k] >> 16);
                 }
             }
         }
@@ -189,16 +197,23 @@ __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(co
     uint4* mine4 = reinterpret_cast<uint4*>(hist + (size_t)warp * (kLaneRows / 2) * 32);
     uint32_t* mine = hist + (size_t)warp * (kLaneRows / 2) * 32 + lane;
     const uint32_t col_addr = (uint32_t)__cvta_generic_to_shared(mine) - (kLaneFirstField / 2u) * 128u;   // minus 32 words
-    bool ok = true;
+    // The smallest mantissa at which any normal binade's threshold lies (binade i - 149 is normal from i = 23 on; its
+    // patterns start at (i - 22) << 23): elements below it never look at the thresholds.  `fast` wants it among the
+    // top 256 patterns, so that a bf16 value (mantissa ending in 16 zero bits) never reaches it.
+    __shared__ uint32_t s_top_floor;
+    if (threadIdx.x == 0) s_top_floor = 0x00800000u;
+    __syncthreads();
     for (int i = threadIdx.x; i < 277; i += blockDim.x) {
         const uint32_t t = bump_at[i];
         bump[i] = t;
-        // binade i - 149 is normal from i = 23 on; its patterns start at (i - 22) << 23
-        if (i >= 23 && t < (((uint32_t)(i - 22) << 23) | 0x007FFF00u)) ok = false;
+        const uint32_t base = (uint32_t)(i - 22) << 23;
+        if (i >= 23) atomicMin(&s_top_floor, t < base ? 0u : (t - base < 0x00800000u ? t - base : 0x00800000u));
     }
     for (int i = threadIdx.x; i < 256; i += blockDim.x) totals[i] = 0u;
     for (int i = lane; i < kColumn16; i += 32) mine4[i] = make_uint4(0u, 0u, 0u, 0u);
-    const bool fast = __syncthreads_and(ok ? 1 : 0) != 0;
+    __syncthreads();
+    const uint32_t top_floor = s_top_floor;
+    const bool fast = top_floor >= 0x007FFF00u;
     constexpr int V = 16 / (int)sizeof(T);
     const int64_t nv = n / V, stride = (int64_t)gridDim.x * blockDim.x;
     const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -218,7 +233,7 @@ __global__ void __launch_bounds__(kLaneThreads, 1) exp_histogram_lanes_kernel(co
                     v[u] = at < nv ? __ldcs(xv + at) : make_uint4(0u, 0u, 0u, 0u);  // zeros are not counted
                 }
             };
-            auto count = [&](const uint4(&v)[kLaneUnroll]) { lane_count_batch<T>(col_addr, totals, v, bump, fast); };
+            auto count = [&](const uint4(&v)[kLaneUnroll]) { lane_count_batch<T>(col_addr, totals, v, bump, fast, top_floor); };
             const int64_t step = kLaneUnroll * stride;
             int done = 0;
             load(a, i);
