@@ -181,11 +181,12 @@ def _timed_flushed(torch, fn, iters, flush):
     return statistics.median(ts), min(ts)
 
 
-def _timing_context(torch, flush, copy_bytes=None, iters=50):
+def _timing_context(torch, flush, copy_bytes=None, iters=50, read_bytes=None):
     """What the timing method itself contributes to a small launch, measured with the vendor's kernels under the same
     bracket (L2 overwritten, event, call, event): ``floor_us`` is a 4-byte fill (a launch that moves nothing), and
     ``copy_us`` a device-to-device ``copy_`` that reads and writes ``copy_bytes`` in total.  Means over ``iters``
-    calls (the event clock ticks in steps of about a microsecond, so medians of short launches are quantised)."""
+    calls (the event clock ticks in steps of about a microsecond, so medians of short launches are quantised).
+    ``read_us``: torch's ``amax`` over ``read_bytes`` of fp32, a read-only pass of the size of the cfg1 tensor."""
     one = torch.zeros(1, device=flush.device)
 
     def mean_us(fn):
@@ -208,6 +209,11 @@ def _timing_context(torch, flush, copy_bytes=None, iters=50):
         ctx["copy_us"] = mean_us(lambda: b.copy_(a))
         ctx["copy_is"] = f"torch copy_ moving {int(copy_bytes)} bytes in total (half read, half written), same bracket"
         del a, b
+    if read_bytes:
+        r = torch.empty(int(read_bytes) // 4, dtype=torch.float32, device=flush.device).normal_()
+        ctx["read_us"] = mean_us(lambda: torch.amax(r))
+        ctx["read_is"] = f"torch amax over {int(read_bytes)} bytes of fp32 (a read-only pass by the vendor's reduction), same bracket"
+        del r
     return ctx
 
 
@@ -272,7 +278,7 @@ def run_extras(dev, iters=20):
     peaks, kind = measured_peaks()
     flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
     out = {"peak_kind": kind, "l2": f"{FLUSH_BYTES >> 20} MB written between timed iterations"}
-    out["timing_context"] = _timing_context(torch, flush, copy_bytes=25_502_912 * 9, iters=iters)
+    out["timing_context"] = _timing_context(torch, flush, copy_bytes=25_502_912 * 9, iters=iters, read_bytes=4096 * 4096 * 4)
 
     def tab(name):
         return torch.from_numpy(vb.tables.build_table(name).view(np.int16).copy()).view(torch.bfloat16)
@@ -1244,7 +1250,7 @@ def run_elementwise(args):
     for k, v in res.items():
         v["frac_of_measured_hbm_peak"] = v["gbs"] / peaks["hbm_gbs"]
     print(json.dumps({"workload": "element-wise configs (cfg1, cfg2, cfg4 shapes)", "results": res, "peak_hbm_gbs": peaks["hbm_gbs"],
-                      "peak_kind": kind, "timing_context": _timing_context(torch, flush, copy_bytes=4096 * 4096 * 8)}))
+                      "peak_kind": kind, "timing_context": _timing_context(torch, flush, copy_bytes=4096 * 4096 * 8, read_bytes=4096 * 4096 * 4)}))
 
 
 def main():
