@@ -372,6 +372,15 @@ VQ_API int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int64_t 
 VQ_API int vq_observer_update(const float* amax_cur, float* history, float* scale, int history_len, int64_t channels,
                               double quant_max, int pow2, const uint8_t* pow2_stay, void* stream);
 
+/* vq_amax and vq_observer_update as ONE launch: the reduction's CTA that finishes last runs the state update.
+ * `amax_scratch`: channels + 1 fp32 words of device memory owned by the observer, ALL ZERO on entry (allocate it zeroed
+ * once) and all zero again when the launch completes: the per-channel maxima of this step and a ticket.  No memset and
+ * no second launch per step; two steps on the same scratch must not overlap.  Arguments otherwise as the two calls.
+ * Replaces `FusedAmaxObsFakeQuantize._update_amax_scale`, src/voyager_compiler/quantization/fake_quantize.py:309-341. */
+VQ_API int vq_observer_step(const void* in, int dtype, int64_t outer, int64_t channels, int64_t inner, float* amax_scratch,
+                            float* history, float* scale, int history_len, double quant_max, int pow2, const uint8_t* pow2_stay,
+                            void* stream);
+
 /* Group-wise affine fake-quantize of a tensor viewed as [rows, K] with blocks of `block` elements along K (the last
  * block of a row may be short; its zero padding takes part in the extrema as upstream pads it):
  *   sf = (max - min) / (quant_max - quant_min), 1 where that is not positive;  zp = -min / sf + quant_min;

@@ -261,3 +261,54 @@ def test_observer_power_of_two_scale_equals_the_cpu_formula_near_powers_of_two()
     sf = x.abs().amax(dim=1, keepdim=True) / qmax
     want = torch.pow(2, torch.ceil(torch.log2(sf)))
     assert torch.equal(mod.scale.cpu().view(torch.int32), want.view(torch.int32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,ch_axis,pow2", [((64, 4096), None, False), ((64, 4096), None, True), ((96, 32, 3, 3), 0, False),
+                                                ((8, 40, 100), 1, True), ((300, 129), 1, False), ((5, 7, 11), 1, False),
+                                                ((4, 6, 33), 2, True), ((0, 16), None, False)])
+def test_observer_step_in_one_launch_equals_the_separate_launches(dtype, shape, ch_axis, pow2, monkeypatch):
+    """The state update by the reduction's last CTA (one launch per step, scratch left at zero) against the memset +
+    reduction + update launches, over six steps of changing data including an all-zero, a NaN and an Inf step: history,
+    scale and outputs bit for bit, for the three shapes of the reduction (rows, columns, flat) and an empty tensor."""
+    from voyager_compiler_b200 import fake_quantize as fq
+    from voyager_compiler_b200.fake_quantize import QScheme
+
+    def make():
+        kw = dict(dtype="int8", quant_max=127.0, amax_history_len=4, force_scale_power_of_two=pow2, device="cuda")
+        if ch_axis is not None:
+            kw.update(qscheme=QScheme.PER_CHANNEL_SYMMETRIC, ch_axis=ch_axis)
+        return fq.FusedAmaxObsFakeQuantize(**kw)
+
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    steps = []
+    for t in range(6):
+        x = (torch.randn(shape, generator=g) * (0.3 + t)).to(dtype)
+        if x.numel():
+            if t == 2:
+                x.zero_()
+            if t == 3:
+                x.view(-1)[x.numel() // 2] = float("nan")
+            if t == 4:
+                x.view(-1)[0] = float("inf")
+        steps.append(x.cuda())
+    results = {}
+    for mode in ("separate", "fused"):
+        if mode == "separate":
+            monkeypatch.setenv("VOYAGER_B200_OBSERVER", "separate")
+        else:
+            monkeypatch.delenv("VOYAGER_B200_OBSERVER", raising=False)
+        m = make()
+        outs = []
+        for x in steps:
+            outs.append(m(x).cpu())
+            outs.append(m.scale.detach().cpu().clone())
+            outs.append(m.amax_history.detach().cpu().clone())
+        if mode == "fused" and m._amax_cur is not None:
+            assert int((m._amax_cur.view(torch.int32) != 0).sum()) == 0        # maxima and ticket back at zero
+        results[mode] = outs
+    for a, b in zip(results["separate"], results["fused"]):
+        assert a.shape == b.shape and a.dtype == b.dtype
+        same = (a.view(torch.int32 if a.element_size() == 4 else torch.int16) == b.view(torch.int32 if b.element_size() == 4 else torch.int16))
+        assert bool((same | (torch.isnan(a.float()) & torch.isnan(b.float()))).all())

@@ -91,6 +91,7 @@ def _load():
         "vq_filter_outlier": [vp, ci, i64, i64, i64, dbl, i64, C.c_int32, vp, vp, vp, vp, vp, C.c_size_t, vp],
         "vq_spmm_csr": [vp, vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, vp, vp, vp],
         "vq_observer_update": [vp, vp, vp, ci, i64, dbl, ci, vp, vp],
+        "vq_observer_step": [vp, ci, i64, i64, i64, vp, vp, vp, ci, dbl, ci, vp, vp],
         "vq_exp_histogram": [vp, ci, i64, E, vp, vp, C.c_size_t, vp],
         "vq_group_affine_fake_quantize": [vp, ci, i64, i64, i64, dbl, dbl, vp, vp, vp, vp, vp],
         "vq_outlier_split": [vp, ci, i64, vp, vp, vp, vp],

@@ -26,7 +26,47 @@ struct AmaxParams {
     FastDiv div_inner, div_C;                 // flat mode (n < 2^31)
     int vec;                                  // 16-byte loads usable
     int smem_cols;                            // column mode: per-CTA maxima staged in shared memory
+    // the observer's state update by the CTA that finishes last (history == nullptr: the reduction alone)
+    float* history;
+    float* scale;
+    unsigned int* ticket;                     // zero between launches
+    const uint8_t* stay;
+    int H, pow2;
+    float qmax;
 };
+
+// The observer's state update for channel c (quantization/fake_quantize.py:327-341; see observer_update_kernel below).
+__device__ __forceinline__ void observer_update_one(int64_t c, float cur, float* __restrict__ history, float* __restrict__ scale, int H,
+                                                    int64_t C, float qmax, int pow2, const uint8_t* __restrict__ stay) {
+    // torch.amax propagates NaN
+    float m = history[c];
+    bool nan = m != m;
+    for (int h = 1; h < H; ++h) {
+        const float v = history[(int64_t)h * C + c];
+        nan |= v != v;
+        m = fmaxf(m, v);
+    }
+    if (nan) m = __int_as_float(0x7FC00000);
+    // roll by -1 along the history axis, then overwrite slot 0
+    const float first = history[c];
+    for (int h = 0; h + 1 < H; ++h) history[(int64_t)h * C + c] = history[(int64_t)(h + 1) * C + c];
+    history[(int64_t)(H - 1) * C + c] = first;
+    history[c] = cur;
+    float sf = __fdiv_rn(m, qmax);
+    const float prev = scale[c];
+    sf = (m > 0.0f) ? sf : prev;
+    sf = (fabsf(m) < CUDART_INF_F) ? sf : prev;
+    if (pow2) {
+        const uint32_t b = __float_as_uint(sf), E = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
+        if (stay && (b >> 31) == 0u && E >= 1u && E <= 254u) {
+            const int e = (int)E - 127 + (mant < (uint32_t)stay[E] ? 0 : 1);
+            sf = e > 127 ? CUDART_INF_F : __uint_as_float((uint32_t)(e + 127) << 23);    // e >= -126 here
+        } else {
+            sf = exp2f(ceilf(log2f(sf)));
+        }
+    }
+    scale[c] = sf;
+}
 
 template <typename T>
 __device__ __forceinline__ uint32_t abs16(const T* p);   // max |x| bits of the 16 bytes at p
@@ -174,7 +214,27 @@ __global__ void __launch_bounds__(MODE == 1 ? 1024 : 256) amax_kernel(const Amax
         }
         if (cur != 0xFFFFFFFFu && m) atomicMax(p.out + cur, m);
     }
+    if (p.history) {
+        // The CTA that draws the last ticket has every CTA's maxima behind it: it runs the observer's update for all
+        // channels and leaves the maxima and the ticket at zero for the next step (no memset, no second launch).
+        __shared__ int last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) last = atomicAdd(p.ticket, 1u) == gridDim.x - 1u;
+        __syncthreads();
+        if (last) {
+            __threadfence();
+            for (int64_t c = threadIdx.x; c < p.C; c += blockDim.x) {
+                observer_update_one(c, __uint_as_float(__ldcg(p.out + c)), p.history, p.scale, p.H, p.C, p.qmax, p.pow2, p.stay);
+                p.out[c] = 0u;
+            }
+            if (threadIdx.x == 0) *p.ticket = 0u;
+        }
+    }
 }
+
+// the reduction's launch; with `fused` the last CTA updates the observer's state (p.history etc. set by the caller)
+int amax_launch(const char* name, AmaxParams p, const void* in, int dtype, int64_t outer, int64_t C, int64_t inner, cudaStream_t st);
 
 }  // namespace
 
@@ -189,8 +249,14 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
     if (n == 0) return 0;
     VQ_REQUIRE(in != nullptr, "%s: null input", name);
     AmaxParams p{};
-    p.in = in;
     p.out = reinterpret_cast<uint32_t*>(out);
+    return amax_launch(name, p, in, dtype, outer, C, inner, st);
+}
+
+namespace {
+int amax_launch(const char* name, AmaxParams p, const void* in, int dtype, int64_t outer, int64_t C, int64_t inner, cudaStream_t st) {
+    const int64_t n = outer * C * inner;
+    p.in = in;
     p.outer = outer; p.C = C; p.inner = inner; p.n = n;
     const size_t es = dtype == VQ_F32 ? 4 : 2;
     const int V = (int)(16 / es);
@@ -240,6 +306,7 @@ extern "C" int vq_amax(const void* in, int dtype, int64_t outer, int64_t C, int6
     VQ_LAUNCH_CHECK("amax_kernel");
     return 0;
 }
+}  // namespace
 
 // ---------------------------------------------------------------------------------------------
 // The observer's state update, quantization/fake_quantize.py:327-341, as one small kernel:
@@ -257,34 +324,7 @@ __global__ void observer_update_kernel(const float* __restrict__ amax_cur, float
                                        int H, int64_t C, float qmax, int pow2, const uint8_t* __restrict__ stay) {
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    // torch.amax propagates NaN
-    float m = history[c];
-    bool nan = m != m;
-    for (int h = 1; h < H; ++h) {
-        const float v = history[(int64_t)h * C + c];
-        nan |= v != v;
-        m = fmaxf(m, v);
-    }
-    if (nan) m = __int_as_float(0x7FC00000);
-    // roll by -1 along the history axis, then overwrite slot 0
-    const float first = history[c];
-    for (int h = 0; h + 1 < H; ++h) history[(int64_t)h * C + c] = history[(int64_t)(h + 1) * C + c];
-    history[(int64_t)(H - 1) * C + c] = first;
-    history[c] = amax_cur[c];
-    float sf = __fdiv_rn(m, qmax);
-    const float prev = scale[c];
-    sf = (m > 0.0f) ? sf : prev;
-    sf = (fabsf(m) < CUDART_INF_F) ? sf : prev;
-    if (pow2) {
-        const uint32_t b = __float_as_uint(sf), E = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
-        if (stay && (b >> 31) == 0u && E >= 1u && E <= 254u) {
-            const int e = (int)E - 127 + (mant < (uint32_t)stay[E] ? 0 : 1);
-            sf = e > 127 ? CUDART_INF_F : __uint_as_float((uint32_t)(e + 127) << 23);    // e >= -126 here
-        } else {
-            sf = exp2f(ceilf(log2f(sf)));
-        }
-    }
-    scale[c] = sf;
+    observer_update_one(c, amax_cur[c], history, scale, H, C, qmax, pow2, stay);
 }
 }  // namespace
 
@@ -297,4 +337,27 @@ extern "C" int vq_observer_update(const float* amax_cur, float* history, float* 
         amax_cur, history, scale, history_len, channels, (float)quant_max, pow2, pow2_stay);
     VQ_LAUNCH_CHECK("observer_update_kernel");
     return 0;
+}
+
+extern "C" int vq_observer_step(const void* in, int dtype, int64_t outer, int64_t channels, int64_t inner, float* amax_scratch,
+                                float* history, float* scale, int history_len, double quant_max, int pow2, const uint8_t* pow2_stay,
+                                void* stream) {
+    const char* name = "vq_observer_step";
+    VQ_REQUIRE(dtype == VQ_F32 || dtype == VQ_BF16, "%s: dtype must be VQ_F32 or VQ_BF16", name);
+    VQ_REQUIRE(outer >= 0 && channels >= 1 && inner >= 0, "%s: bad shape", name);
+    VQ_REQUIRE(amax_scratch && history && scale, "%s: null pointer", name);
+    VQ_REQUIRE(history_len >= 1, "%s: bad history length", name);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (outer * channels * inner == 0) {                  // nothing to reduce: the maxima are the zeros of the scratch
+        observer_update_kernel<<<(unsigned)((channels + 127) / 128), 128, 0, st>>>(amax_scratch, history, scale, history_len, channels,
+                                                                                 (float)quant_max, pow2, pow2_stay);
+        VQ_LAUNCH_CHECK("observer_update_kernel");
+        return 0;
+    }
+    VQ_REQUIRE(in != nullptr, "%s: null input", name);
+    AmaxParams p{};
+    p.out = reinterpret_cast<uint32_t*>(amax_scratch);
+    p.ticket = reinterpret_cast<unsigned int*>(amax_scratch) + channels;
+    p.history = history; p.scale = scale; p.H = history_len; p.qmax = (float)quant_max; p.pow2 = pow2; p.stay = pow2_stay;
+    return amax_launch(name, p, in, dtype, outer, channels, inner, st);
 }

@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from enum import Enum
 from typing import List, Optional, Sequence, Tuple, Union
 
@@ -400,8 +401,8 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
     @torch.no_grad()
     def _update_amax_scale(self, x: torch.Tensor) -> None:
         """fake_quantize.py:309-341: the scale is derived from the history BEFORE the current amax
-        enters it; 0 / NaN / Inf maxima keep the previous scale.  Two launches: the reduction and
-        one kernel for the whole state update."""
+        enters it; 0 / NaN / Inf maxima keep the previous scale.  One launch: the reduction, whose last
+        CTA runs the whole state update (``VOYAGER_B200_OBSERVER=separate``: a memset and two launches)."""
         _require_cuda(x, "FusedAmaxObsFakeQuantize")
         _require_same_device(x, "FusedAmaxObsFakeQuantize", amax_history=self.amax_history, scale=self.scale)
         xc = x.contiguous()
@@ -423,16 +424,26 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         if not (self.amax_history.is_contiguous() and self.scale.is_contiguous()
                 and self.amax_history.dtype == torch.float32 and self.scale.dtype == torch.float32):
             raise RuntimeError("FusedAmaxObsFakeQuantize: amax_history and scale must be contiguous fp32 buffers")
-        if self._amax_cur is None or self._amax_cur.numel() != ch or self._amax_cur.device != x.device:
-            self._amax_cur = torch.empty(ch, dtype=torch.float32, device=x.device)
+        if self._amax_cur is None or self._amax_cur.numel() != ch + 1 or self._amax_cur.device != x.device:
+            # the step's maxima and a ticket: zero now, and left at zero by every fused step
+            self._amax_cur = torch.zeros(ch + 1, dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
             stream = torch.cuda.current_stream(x.device).cuda_stream
-            _lib.check(_lib.lib.vq_amax(xc.data_ptr(), _DT[x.dtype], outer, ch, inner, self._amax_cur.data_ptr(), stream), "amax")
             stay = qtables.pow2_stay_table(x.device) if self.force_scale_power_of_two else None
-            _lib.check(_lib.lib.vq_observer_update(self._amax_cur.data_ptr(), self.amax_history.data_ptr(),
-                                                   self.scale.data_ptr(), self.amax_history_len, ch, float(self.quant_max),
-                                                   1 if self.force_scale_power_of_two else 0,
-                                                   stay.data_ptr() if stay is not None else None, stream), "observer update")
+            stay_ptr = stay.data_ptr() if stay is not None else None
+            pow2 = 1 if self.force_scale_power_of_two else 0
+            if os.environ.get("VOYAGER_B200_OBSERVER") == "separate":
+                # the reduction (with its memset) and the state update as launches of their own
+                _lib.check(_lib.lib.vq_amax(xc.data_ptr(), _DT[x.dtype], outer, ch, inner, self._amax_cur.data_ptr(), stream), "amax")
+                _lib.check(_lib.lib.vq_observer_update(self._amax_cur.data_ptr(), self.amax_history.data_ptr(),
+                                                       self.scale.data_ptr(), self.amax_history_len, ch, float(self.quant_max),
+                                                       pow2, stay_ptr, stream), "observer update")
+                self._amax_cur[:ch].zero_()
+            else:
+                # one launch: the reduction's last CTA updates the history and the scale and clears the scratch
+                _lib.check(_lib.lib.vq_observer_step(xc.data_ptr(), _DT[x.dtype], outer, ch, inner, self._amax_cur.data_ptr(),
+                                                     self.amax_history.data_ptr(), self.scale.data_ptr(), self.amax_history_len,
+                                                     float(self.quant_max), pow2, stay_ptr, stream), "observer step")
 
     # -- outlier filtering (fake_quantize.py:373-394)
     @property
