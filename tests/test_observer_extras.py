@@ -249,3 +249,46 @@ def test_exponent_histogram_with_the_smallest_workspace_takes_a_launch_for_the_a
                                        torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         assert torch.equal(hist.cpu(), want), words
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("lower_by", [0, 0x40, 0x2000, 0x200000])
+@pytest.mark.parametrize("form", ["lanes", "match"])
+def test_exponent_histogram_follows_the_thresholds_it_is_given(dtype, lower_by, form, monkeypatch):
+    """The kernels take the patterns at which floor(log2) rounds up from a table; with thresholds moved down by 64 patterns
+    the large-tensor kernel still counts most elements without looking at them, with 2^13 or 2^21 patterns it must look
+    for every element (and a bf16 value can now reach a threshold).  Checked against the rule itself in numpy."""
+    import numpy as np
+    from voyager_compiler_b200 import _lib, qtables
+    if form == "match":
+        monkeypatch.setenv("VOYAGER_B200_HISTOGRAM", "match")
+    bump, scale_of = qtables.derive_exp_tables_host(torch.float32, 0)
+    bump = bump.astype(np.int64)
+    first = np.array([((i - 149 + 127) << 23) if i - 149 >= -126 else (1 << i) for i in range(277)], dtype=np.int64)
+    bump = np.maximum(bump - lower_by, first)                 # never below the binade's first pattern
+    g = torch.Generator().manual_seed(lower_by + 1)
+    n = (1 << 20) + 3
+    x = torch.randn(n, generator=g) * 2
+    x[torch.rand(n, generator=g) < 0.1] = 0.0
+    k = 5000
+    e = torch.randint(-130, 20, (k,), generator=g)
+    near = (torch.exp2(e.float().clamp(min=-126)).view(torch.int32) - torch.randint(0, 2 * max(lower_by, 64), (k,), generator=g).int())
+    x[torch.randint(0, n, (k,), generator=g)] = near.view(torch.float32)
+    x[:4] = torch.tensor([float("inf"), float("nan"), 1e-40, -3e38])
+    x = x.to(dtype)
+    bits = x.float().view(torch.int32).numpy().astype(np.int64) & 0x7FFFFFFF
+    valid = (bits != 0) & (bits < 0x7F800000)
+    b = bits[valid]
+    ex = np.where(b >= 0x00800000, (b >> 23) - 127, np.floor(np.log2(np.maximum(b, 1))).astype(np.int64) - 149)
+    ex = ex + (b >= bump[ex + 149])
+    ok = (ex >= -126) & (ex <= 127)
+    want = np.bincount(ex[ok] + 126, minlength=254).astype(np.float32)
+    et = qtables.ExpTables(torch.from_numpy(bump.astype(np.uint32).view(np.int32).copy()).cuda(), torch.from_numpy(scale_of).cuda())
+    hist = torch.zeros(254, device="cuda")
+    ws = torch.empty(256, dtype=torch.int64, device="cuda")
+    xd = x.cuda()
+    rc = _lib.lib.vq_exp_histogram(xd.data_ptr(), _lib.VQ_F32 if dtype == torch.float32 else _lib.VQ_BF16, n, et.ptr(), hist.data_ptr(),
+                                   ws.data_ptr(), 2048, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert np.array_equal(hist.cpu().numpy(), want)
